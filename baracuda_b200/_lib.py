@@ -1,0 +1,68 @@
+"""ctypes binding of the flat C ABI (include/baracuda_kernels_q.h).
+
+The library is the product: if it is missing this module raises — there is no
+Python, torch or CPU fallback for any of the kernels.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libbaracuda_kernels_q.so"
+
+_i32, _i64, _f32, _vp, _sz = C.c_int32, C.c_int64, C.c_float, C.c_void_p, C.c_size_t
+
+_GEMM_PREFIX = [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64]
+_GEMM_CAN = (_i32, _GEMM_PREFIX)
+_GEMM_WS = (_sz, [_i32, _i32, _i32])
+_TAIL = [_vp, _sz, _vp]  # workspace, workspace_bytes, stream
+
+_GEMV_HEAD = [_i32, _i32, _i32, _i32, _i32, _f32, _f32, _vp, _i64, _i64, _vp, _i64, _i64]
+_GEMV_CAN = (_i32, [_i32] * 5 + [_i64] * 6)
+_GEMV_WS = (_sz, [_i32] * 5)
+
+# symbol -> (restype, argtypes); every symbol the header declares is listed here
+SIGNATURES: dict[str, tuple] = {
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run": (_i32, _GEMM_PREFIX + [_vp, _vp, _f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_s8_rcr_s32_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run": (_i32, _GEMM_PREFIX + [_vp, _vp, _i32, _f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_run": (
+        _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement": _GEMV_CAN,
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size": _GEMV_WS,
+    "baracuda_kernels_gemv_q8_m1_s32_sm100a_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
+    "baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement": _GEMV_CAN,
+    "baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size": _GEMV_WS,
+    "baracuda_kernels_q_device_status": (_i32, []),
+    "baracuda_kernels_q_set_tuning": (_i32, [_i32, _i32]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the CUDA library and attach the prototypes; raise if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m baracuda_b200.build`. "
+            "The kernels have no fallback path."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means the ABI and the binding disagree
+        fn.restype = res
+        fn.argtypes = list(args)
+    _lib = lib
+    return lib

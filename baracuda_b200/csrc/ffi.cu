@@ -1,0 +1,258 @@
+// The flat C symbols of include/baracuda_kernels_q.h: argument validation in
+// the reference's order (negative dims -> 2, empty -> 0 without a launch, null
+// pointers -> 2, leading-dimension minimums -> 2, alignment -> 1), then the
+// launch.  No allocation, no host synchronisation, no library state.
+
+#include <atomic>
+
+#include "../../include/baracuda_kernels_q.h"
+#include "launch.h"
+
+namespace {
+
+std::atomic<int32_t> g_force_block_n{0};
+std::atomic<int32_t> g_gemv_variant{0};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Shape / leading-dimension / alignment rules shared by run and can_implement.
+// Pointer arguments may be null here (can_implement is callable before the
+// buffers exist); alignment of a null pointer is not judged.
+int32_t gemm_rcr_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                          const void* c, int64_t ldc, const void* d, int64_t ldd) {
+    (void)ldc;
+    (void)d;
+    if (m < 0 || n < 0 || k < 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    const int64_t min_k = k > 0 ? k : 1;
+    const int64_t min_n = n > 0 ? n : 1;
+    if (lda < min_k || ldb < min_k || ldd < min_n) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (c != nullptr) return bq::BQ_STATUS_UNSUPPORTED;
+    // TMA reads both operands: 16-byte aligned bases and row pitches
+    if ((a && !aligned16(a)) || (b && !aligned16(b))) return bq::BQ_STATUS_MISALIGNED;
+    if ((m > 1 && (lda & 15)) || (n > 1 && (ldb & 15))) return bq::BQ_STATUS_MISALIGNED;
+    return bq::BQ_STATUS_OK;
+}
+
+int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                     const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd,
+                     const void* scale_a, const void* scale_b, int32_t scale_mode, float alpha, float beta,
+                     void* stream) {
+    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
+    if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (beta != 0.0f) return bq::BQ_STATUS_UNSUPPORTED;
+    if (raw) {
+        if (alpha != 1.0f) return bq::BQ_STATUS_UNSUPPORTED;
+    } else {
+        if (!scale_a || !scale_b) return bq::BQ_STATUS_INVALID_PROBLEM;
+        if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
+            return bq::BQ_STATUS_INVALID_PROBLEM;
+    }
+    bq::GemmDesc g;
+    g.kind = kind;
+    g.raw_out = raw;
+    g.m = m;
+    g.n = n;
+    g.k = k;
+    g.a = a;
+    g.lda = lda;
+    g.b = b;
+    g.ldb = ldb;
+    g.scale_a = static_cast<const float*>(scale_a);
+    g.scale_b = static_cast<const float*>(scale_b);
+    g.scale_mode = scale_mode;
+    g.alpha = alpha;
+    g.d = d;
+    g.ldd = ldd;
+    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
+}
+
+// Mirrors gemv_validate of the reference (gemv_dense.cu:101-122), widened to
+// m <= 8 and to the second weight layout.
+int32_t gemv_validate(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, int64_t lda, int64_t ldb,
+                      int64_t ldd, int64_t stride_d) {
+    if (m < 0 || n < 0 || k < 0 || batch < 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (m > 8) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (layout != bq::BQ_LAYOUT_RRR && layout != bq::BQ_LAYOUT_RCR) return bq::BQ_STATUS_INVALID_PROBLEM;
+    const int64_t min_k = k > 0 ? k : 1;
+    const int64_t min_n = n > 0 ? n : 1;
+    const int64_t min_ldb = (layout == bq::BQ_LAYOUT_RRR) ? min_n : min_k;
+    if (lda < min_k || ldb < min_ldb || ldd < min_n) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (batch > 1 && stride_d == 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    return bq::BQ_STATUS_OK;
+}
+
+int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, float alpha,
+                 float beta, const void* a, int64_t lda, int64_t stride_a, const void* b, int64_t ldb,
+                 int64_t stride_b, const void* scale_a, int64_t stride_scale_a, const void* scale_b,
+                 int64_t stride_scale_b, void* d, int64_t ldd, int64_t stride_d, void* workspace,
+                 size_t workspace_bytes, void* stream) {
+    const int32_t st = gemv_validate(m, n, k, batch, layout, lda, ldb, ldd, stride_d);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0 || batch == 0) return bq::BQ_STATUS_OK;
+    if (!a || !b || !d) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (raw) {
+        if (alpha != 1.0f || beta != 0.0f) return bq::BQ_STATUS_UNSUPPORTED;
+    } else if (!scale_a || !scale_b) {
+        return bq::BQ_STATUS_INVALID_PROBLEM;
+    }
+    bq::GemvDesc g;
+    g.raw_out = raw;
+    g.m = m;
+    g.n = n;
+    g.k = k;
+    g.batch = batch;
+    g.layout = layout;
+    g.alpha = alpha;
+    g.beta = beta;
+    g.a = static_cast<const int8_t*>(a);
+    g.lda = lda;
+    g.stride_a = stride_a;
+    g.b = static_cast<const int8_t*>(b);
+    g.ldb = ldb;
+    g.stride_b = stride_b;
+    g.scale_a = static_cast<const float*>(scale_a);
+    g.stride_scale_a = stride_scale_a;
+    g.scale_b = static_cast<const float*>(scale_b);
+    g.stride_scale_b = stride_scale_b;
+    g.d = d;
+    g.ldd = ldd;
+    g.stride_d = stride_d;
+    g.workspace = workspace;
+    g.workspace_bytes = workspace_bytes;
+    g.variant = g_gemv_variant.load(std::memory_order_relaxed);
+    return bq::launch_gemv_q8(g, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- W8A8 -> bf16 ------------------------------------------------------------
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_rcr_run(bq::BQ_KIND_S8, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
+                        BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream);
+}
+size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+// ---- s8 -> s32 accumulators --------------------------------------------------
+int32_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_rcr_run(bq::BQ_KIND_S8, 1, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, nullptr, nullptr, 0, alpha,
+                        beta, stream);
+}
+size_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+// ---- e4m3 -> bf16 --------------------------------------------------------------
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode, float alpha,
+    float beta, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_rcr_run(bq::BQ_KIND_E4M3, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b, scale_mode,
+                        alpha, beta, stream);
+}
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+// ---- e4m3 -> f32 accumulators ---------------------------------------------------
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_rcr_run(bq::BQ_KIND_E4M3, 1, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, nullptr, nullptr, 0, alpha,
+                        beta, stream);
+}
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+// ---- int8 GEMV ---------------------------------------------------------------------
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, float alpha, float beta, const void* a,
+    int64_t lda, int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, const void* scale_a,
+    int64_t stride_scale_a, const void* scale_b, int64_t stride_scale_b, void* d, int64_t ldd, int64_t stride_d,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    return gemv_run(0, m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb, stride_b, scale_a,
+                    stride_scale_a, scale_b, stride_scale_b, d, ldd, stride_d, workspace, workspace_bytes, stream);
+}
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, int64_t lda, int64_t ldb, int64_t ldd,
+    int64_t stride_a, int64_t stride_b, int64_t stride_d) {
+    (void)stride_a;
+    (void)stride_b;
+    return gemv_validate(m, n, k, batch, layout, lda, ldb, ldd, stride_d);
+}
+size_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size(int32_t m, int32_t n, int32_t k, int32_t batch,
+                                                              int32_t layout) {
+    return bq::gemv_q8_workspace_bytes(m, n, k, batch, layout);
+}
+
+int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, float alpha, float beta, const void* a,
+    int64_t lda, int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, void* d, int64_t ldd,
+    int64_t stride_d, void* workspace, size_t workspace_bytes, void* stream) {
+    return gemv_run(1, m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb, stride_b, nullptr, 0, nullptr,
+                    0, d, ldd, stride_d, workspace, workspace_bytes, stream);
+}
+int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, int64_t lda, int64_t ldb, int64_t ldd,
+    int64_t stride_a, int64_t stride_b, int64_t stride_d) {
+    (void)stride_a;
+    (void)stride_b;
+    return gemv_validate(m, n, k, batch, layout, lda, ldb, ldd, stride_d);
+}
+size_t baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size(int32_t m, int32_t n, int32_t k, int32_t batch,
+                                                             int32_t layout) {
+    return bq::gemv_q8_workspace_bytes(m, n, k, batch, layout);
+}
+
+// ---- diagnostics / tuning -------------------------------------------------------------
+int32_t baracuda_kernels_q_device_status(void) { return bq::read_and_clear_gemm_device_status(); }
+
+int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
+    switch (key) {
+        case 0:
+            if (value != 0 && value != 64 && value != 128 && value != 256) return bq::BQ_STATUS_INVALID_PROBLEM;
+            g_force_block_n.store(value);
+            return bq::BQ_STATUS_OK;
+        case 1:
+            g_gemv_variant.store(value);
+            return bq::BQ_STATUS_OK;
+        default:
+            return bq::BQ_STATUS_INVALID_PROBLEM;
+    }
+}
+
+}  // extern "C"

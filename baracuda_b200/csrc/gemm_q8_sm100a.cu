@@ -1,0 +1,433 @@
+// 8-bit tensor-core GEMM for sm_100a: D[M,N] = epilogue(A[M,K] x B[K,N]) with
+// A row-major and B column-major ("RCR": both operands K-contiguous).
+//
+// One persistent CTA per SM, six warps with fixed roles:
+//   warp 0    TMA producer: streams 128-byte-swizzled A and B tiles through a
+//             ring of shared-memory stages, one mbarrier pair per stage;
+//   warp 1    owns TMEM and issues tcgen05.mma (s8 x s8 -> s32 or
+//             e4m3 x e4m3 -> f32), 128 x BLOCK_N x 32 per instruction;
+//   warps 2-5 epilogue: tcgen05.ld the accumulator, apply the fused
+//             per-row x per-column dequant scale, write bf16 (or the raw
+//             32-bit accumulators).
+// The accumulator is double-buffered in TMEM so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Every barrier wait is bounded; a wait that runs
+// out records a status word and all roles leave.
+//
+// Replaces, for the bf16-out W8A8 / FP8 use, the reference's
+//   crates/baracuda-cutlass-kernels-sys/kernels/gemm_s8_rcr_sm80.cu:48-198 (s8 RCR tensor-core GEMM)
+//   crates/baracuda-kernels-sys/kernels/include/baracuda_fp8_rcr_sm89.cuh:102-323 (e4m3 RCR GEMM)
+//   crates/baracuda-kernels-sys/kernels/include/baracuda_quantize_compose.cuh:245-301 (W8A8 dequant math)
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "launch.h"
+#include "ptx_sm100a.cuh"
+
+namespace bq {
+
+__device__ int g_gemm_device_status = 0;
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 128;  // bytes of K per stage == one 128-byte swizzle row
+constexpr int UMMA_K = 32;    // K per tcgen05.mma for 8-bit operands
+constexpr int GEMM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr long long WAIT_LIMIT_CYCLES = 1LL << 31;  // about a second
+
+struct GemmParams {
+    void* d;
+    int64_t ldd;
+    const float* sa;
+    const float* sb;
+    int scale_mode;  // 0: sa/sb point at one float each; 1: sa[M], sb[N]
+    float alpha;
+    int m, n, k;
+    int m_tiles, n_tiles;
+    int vec_store;  // 1 when d and ldd allow 16-byte row stores
+};
+
+template <int BLOCK_N, int STAGES>
+struct Smem {
+    static constexpr int A_BYTES = BLOCK_M * BLOCK_K;
+    static constexpr int B_BYTES = BLOCK_N * BLOCK_K;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int SB_BYTES = 4 * BLOCK_N * 4;  // one private copy of the column scales per epilogue warp
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int TOTAL = TILE_BYTES + SB_BYTES + BAR_BYTES + 1024;  // + alignment slack
+    static constexpr int TMEM_COLS = (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64
+                                     : (2 * BLOCK_N <= 128) ? 128 : (2 * BLOCK_N <= 256) ? 256 : 512;
+};
+
+__device__ __forceinline__ void record_timeout(volatile uint32_t* abort_word, int code) {
+    *abort_word = 1u;
+    atomicCAS(&g_gemm_device_status, 0, code);
+}
+
+template <uint32_t KIND, bool RAW, int BLOCK_N, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+    using L = Smem<BLOCK_N, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    float* sb_s = reinterpret_cast<float*>(smem + L::TILE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::TILE_BYTES + L::SB_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tfull_bar = empty_bar + STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull_bar[b], 1);
+            mbar_init(&tempty_bar[b], EPI_THREADS);
+        }
+        *abort_word = 0u;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, L::TMEM_COLS);
+        tmem_relinquish_alloc_permit();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_kb = (p.k + BLOCK_K - 1) / BLOCK_K;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+                const int m_blk = tile % p.m_tiles;
+                const int n_blk = tile / p.m_tiles;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, WAIT_LIMIT_CYCLES)) {
+                        record_timeout(abort_word, 101);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa_tile = tiles + stage * L::STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+                    tma_load_2d(sa_tile, &tmap_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
+                    tma_load_2d(sa_tile + L::A_BYTES, &tmap_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(KIND, BLOCK_M, BLOCK_N);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait_bounded(&tempty_bar[buf], acc_phase ^ 1u, abort_word, WAIT_LIMIT_CYCLES)) {
+                    record_timeout(abort_word, 102);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BLOCK_N);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, abort_word, WAIT_LIMIT_CYCLES)) {
+                        record_timeout(abort_word, 103);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + stage * L::STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::A_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < BLOCK_K / UMMA_K; ++ks) {
+                        // advancing K inside the swizzle row = adding the byte offset (in 16-byte units)
+                        const uint64_t koff = static_cast<uint64_t>((ks * UMMA_K) >> 4);
+                        umma_ss<KIND>(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit(&tfull_bar[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const int m_blk = tile % p.m_tiles;
+            const int n_blk = tile / p.m_tiles;
+            // each warp stages its own copy of this tile's column scales, so the
+            // epilogue warps never have to meet at a barrier
+            float* sb_tile = sb_s + (warp - 2) * BLOCK_N;
+            if constexpr (!RAW) {
+                __syncwarp();
+                for (int i = lane; i < BLOCK_N; i += 32) {
+                    const int col = n_blk * BLOCK_N + i;
+                    sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                }
+                __syncwarp();
+            }
+            if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, WAIT_LIMIT_CYCLES)) {
+                record_timeout(abort_word, 104);
+                break;
+            }
+            tc_fence_after_sync();
+            const int row = m_blk * BLOCK_M + q * 32 + lane;
+            const bool row_ok = row < p.m;
+            float sa_row = 1.0f;
+            if constexpr (!RAW) {
+                sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
+            }
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                   static_cast<uint32_t>(buf * BLOCK_N);
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c) {
+                const int col0 = n_blk * BLOCK_N + c * 32;
+                if (col0 >= p.n) break;  // warp-uniform
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
+                tmem_ld_wait();
+                if (!row_ok) {
+                    // rows past M hold zero-filled padding; nothing to store
+                } else if constexpr (RAW) {
+                    uint32_t* drow = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+                    if (p.vec_store && col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            reinterpret_cast<uint4*>(drow)[v] =
+                                make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) drow[j] = r[j];
+                        }
+                    }
+                } else {
+                    __nv_bfloat16* drow =
+                        reinterpret_cast<__nv_bfloat16*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+                    float y[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float acc;
+                        if constexpr (KIND == UMMA_KIND_I8) {
+                            acc = static_cast<float>(static_cast<int32_t>(r[j]));
+                        } else {
+                            acc = __uint_as_float(r[j]);
+                        }
+                        // (sa*sb) first, then the accumulator, then alpha: the
+                        // reference's W8A8 product order, no fused multiply-add.
+                        const float s = __fmul_rn(sa_row, sb_tile[c * 32 + j]);
+                        y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
+                    }
+                    if (p.vec_store && col0 + 32 <= p.n) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]);
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]);
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
+                            uint4 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                            reinterpret_cast<uint4*>(drow)[v] = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            if (col0 + j < p.n) drow[j] = __float2bfloat16_rn(y[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[buf]);
+        }
+    }
+
+    // Teardown.  On the error path give copies and MMAs still in flight a
+    // bounded time to land before TMEM goes back.
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_word != 0u) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, L::TMEM_COLS);
+    }
+}
+
+// K == 0: the contraction is empty, every output is the scaled zero.
+template <typename T>
+__global__ void fill_zero_kernel(T* d, int64_t ldd, int m, int n) {
+    const int64_t total = static_cast<int64_t>(m) * n;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / n, c = i % n;
+        d[r * ldd + c] = T(0);
+    }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            p = nullptr;
+        }
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }();
+    return fn;
+}
+
+// rows x k bytes, K contiguous, row pitch ld bytes; box = box_rows x 128 bytes, 128-byte swizzle.
+bool make_kmajor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+    auto enc = tensor_map_encoder();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    // a single row never uses its pitch; any 16-byte multiple satisfies the encoder
+    cuuint64_t pitch = static_cast<cuuint64_t>(rows > 1 ? ld : ((k + 15) / 16) * 16);
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+int sm_count_of_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    static std::mutex mu;
+    static int cache[64] = {0};
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && cache[dev] > 0) return cache[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < 64) cache[dev] = n;
+    return n;
+}
+
+template <uint32_t KIND, bool RAW, int BLOCK_N, int STAGES>
+int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
+    using L = Smem<BLOCK_N, STAGES>;
+    CUtensorMap map_a, map_b;
+    if (!make_kmajor_map(&map_a, g.a, g.m, g.k, g.lda, BLOCK_M)) return BQ_STATUS_LAUNCH_FAILURE;
+    if (!make_kmajor_map(&map_b, g.b, g.n, g.k, g.ldb, BLOCK_N)) return BQ_STATUS_LAUNCH_FAILURE;
+    GemmParams p;
+    p.d = g.d;
+    p.ldd = g.ldd;
+    p.sa = g.scale_a;
+    p.sb = g.scale_b;
+    p.scale_mode = g.scale_mode;
+    p.alpha = g.alpha;
+    p.m = g.m;
+    p.n = g.n;
+    p.k = g.k;
+    p.m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
+    p.n_tiles = (g.n + BLOCK_N - 1) / BLOCK_N;
+    const int64_t elem = RAW ? 4 : 2;
+    p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
+    auto kern = gemm_q8_kernel<KIND, RAW, BLOCK_N, STAGES>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+    kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(map_a, map_b, p);
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
+
+template <uint32_t KIND, bool RAW>
+int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
+    const int sms = sm_count_of_current_device();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
+    auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
+    int bn = g.force_block_n;
+    if (bn == 0) {
+        // the widest tile that still gives every SM a tile; narrow tiles for small problems
+        bn = tiles_at(256) >= sms ? 256 : (tiles_at(128) >= sms ? 128 : 64);
+    }
+    switch (bn) {
+        case 256: return launch_config<KIND, RAW, 256, 4>(g, sms, stream);
+        case 128: return launch_config<KIND, RAW, 128, 6>(g, sms, stream);
+        case 64: return launch_config<KIND, RAW, 64, 8>(g, sms, stream);
+        default: return BQ_STATUS_INVALID_PROBLEM;
+    }
+}
+
+}  // namespace
+
+int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
+    if (g.k == 0) {
+        const int64_t total = static_cast<int64_t>(g.m) * g.n;
+        const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+        if (g.raw_out) {
+            fill_zero_kernel<uint32_t><<<blocks, 256, 0, stream>>>(static_cast<uint32_t*>(g.d), g.ldd, g.m, g.n);
+        } else {
+            fill_zero_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(g.d), g.ldd,
+                                                                        g.m, g.n);
+        }
+        return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+    }
+    if (g.kind == BQ_KIND_S8) {
+        return g.raw_out ? launch_kind<UMMA_KIND_I8, true>(g, stream) : launch_kind<UMMA_KIND_I8, false>(g, stream);
+    }
+    return g.raw_out ? launch_kind<UMMA_KIND_F8, true>(g, stream) : launch_kind<UMMA_KIND_F8, false>(g, stream);
+}
+
+int32_t read_and_clear_gemm_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        int zero = 0;
+        (void)cudaMemcpyToSymbol(g_gemm_device_status, &zero, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace bq

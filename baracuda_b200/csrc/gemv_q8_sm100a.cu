@@ -1,0 +1,444 @@
+// Skinny int8 GEMV for decode (m = 1..8 activation rows), HBM-bandwidth bound:
+//   D[g, r, j] = bf16( alpha * (sa[r]*sb[j]) * sum_k A[g,r,k] * B[g,k,j] + beta * D[g,r,j] )
+// or the raw int32 sums.  The weight matrix is streamed exactly once with
+// 128-bit loads that bypass L1; the int32 dot products use dp4a; partial sums
+// meet through warp shuffles (and, for the row-major weight layout, a shared
+// memory + workspace split-K reduction).
+//
+// Takes the role of the reference's dense m=1 GEMV
+//   crates/baracuda-kernels-sys/kernels/gemm/gemv_dense.cu:101-219 (validation + launcher)
+//   crates/baracuda-kernels-sys/kernels/gemm/gemv_dense.cu:128-171 (thread-per-column kernel)
+// for int8 weights with the W8A8 dequant of
+//   crates/baracuda-kernels-sys/kernels/include/baracuda_quantize_compose.cuh:271-274.
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "launch.h"
+
+namespace bq {
+namespace {
+
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+constexpr int KB_BYTES = 4096;       // activation bytes per row staged in shared memory at a time
+constexpr int RRR_COLS_PER_CTA = 512;  // one warp-wide row segment of 16-byte loads
+
+struct GemvParams {
+    const int8_t* a;
+    int64_t lda, stride_a;
+    const int8_t* b;
+    int64_t ldb, stride_b;
+    const float* sa;
+    int64_t stride_sa;
+    const float* sb;
+    int64_t stride_sb;
+    void* d;
+    int64_t ldd, stride_d;
+    float alpha, beta;
+    int m, n, k;
+    // split-K plan of the row-major-weight kernel
+    int kslice_rows, num_kslices;
+    int32_t* ws_partials;
+    unsigned int* ws_tickets;
+};
+
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ int dot16(const uint4& w, const uint4& x, int acc) {
+    acc = __dp4a(static_cast<int>(w.x), static_cast<int>(x.x), acc);
+    acc = __dp4a(static_cast<int>(w.y), static_cast<int>(x.y), acc);
+    acc = __dp4a(static_cast<int>(w.z), static_cast<int>(x.z), acc);
+    acc = __dp4a(static_cast<int>(w.w), static_cast<int>(x.w), acc);
+    return acc;
+}
+
+__device__ __forceinline__ int warp_sum(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+template <bool RAW>
+__device__ __forceinline__ void store_result(const GemvParams& p, int64_t batch, int r, int col, int acc) {
+    if constexpr (RAW) {
+        reinterpret_cast<int32_t*>(p.d)[batch * p.stride_d + static_cast<int64_t>(r) * p.ldd + col] = acc;
+    } else {
+        __nv_bfloat16* dp =
+            reinterpret_cast<__nv_bfloat16*>(p.d) + batch * p.stride_d + static_cast<int64_t>(r) * p.ldd + col;
+        const float s = __fmul_rn(__ldg(p.sa + batch * p.stride_sa + r), __ldg(p.sb + batch * p.stride_sb + col));
+        float y = __fmul_rn(__fmul_rn(s, static_cast<float>(acc)), p.alpha);
+        if (p.beta != 0.0f) y = __fadd_rn(y, __fmul_rn(p.beta, __bfloat162float(*dp)));
+        *dp = __float2bfloat16_rn(y);
+    }
+}
+
+// ---- weights stored [N, K] (K contiguous): one warp owns CPW output columns ----
+template <int MR, int CPW, bool RAW>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_q8_rcr_kernel(const GemvParams p) {
+    extern __shared__ uint4 xs[];  // MR rows x KB_BYTES/16
+    constexpr int KB16 = KB_BYTES / 16;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int64_t g = blockIdx.y;
+    const int8_t* a = p.a + g * p.stride_a;
+    const int8_t* b = p.b + g * p.stride_b;
+    const int col_base = (blockIdx.x * GEMV_WARPS + warp) * CPW;
+
+    int acc[CPW][MR];
+#pragma unroll
+    for (int c = 0; c < CPW; ++c)
+#pragma unroll
+        for (int r = 0; r < MR; ++r) acc[c][r] = 0;
+
+    const uint4* wrow[CPW];
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) {
+        int col = col_base + c;
+        if (col >= p.n) col = p.n - 1;  // clamp; the duplicate result is never stored
+        wrow[c] = reinterpret_cast<const uint4*>(b + static_cast<int64_t>(col) * p.ldb);
+    }
+
+    for (int k0 = 0; k0 < p.k; k0 += KB_BYTES) {
+        const int klen16 = ((p.k - k0 < KB_BYTES) ? (p.k - k0) : KB_BYTES) >> 4;
+        __syncthreads();
+        for (int i = threadIdx.x; i < MR * klen16; i += GEMV_THREADS) {
+            const int r = i / klen16, c = i - r * klen16;
+            xs[r * KB16 + c] = __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda + k0) + c);
+        }
+        __syncthreads();
+        if (col_base < p.n) {
+            const int kq = k0 >> 4;
+            for (int kk = lane; kk < klen16; kk += 64) {
+                const bool second = (kk + 32) < klen16;
+                uint4 w0[CPW], w1[CPW];
+#pragma unroll
+                for (int c = 0; c < CPW; ++c) w0[c] = ldg_stream_v4(wrow[c] + kq + kk);
+#pragma unroll
+                for (int c = 0; c < CPW; ++c)
+                    w1[c] = second ? ldg_stream_v4(wrow[c] + kq + kk + 32) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int r = 0; r < MR; ++r) {
+                    const uint4 x0 = xs[r * KB16 + kk];
+                    const uint4 x1 = second ? xs[r * KB16 + kk + 32] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int c = 0; c < CPW; ++c) {
+                        acc[c][r] = dot16(w0[c], x0, acc[c][r]);
+                        acc[c][r] = dot16(w1[c], x1, acc[c][r]);
+                    }
+                }
+            }
+        }
+    }
+
+#pragma unroll
+    for (int c = 0; c < CPW; ++c) {
+#pragma unroll
+        for (int r = 0; r < MR; ++r) {
+            const int v = warp_sum(acc[c][r]);
+            const int col = col_base + c;
+            if (lane == ((c * MR + r) & 31) && col < p.n) store_result<RAW>(p, g, r, col, v);
+        }
+    }
+}
+
+// ---- weights stored [K, N] (N contiguous): a thread owns 16 adjacent columns,
+// a CTA owns a 512-column strip of one K slice; slices meet in the workspace ----
+__device__ __forceinline__ void transpose4x4_bytes(uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
+                                                   uint32_t (&c)[4]) {
+    const uint32_t t0 = __byte_perm(r0, r1, 0x5140);
+    const uint32_t t1 = __byte_perm(r0, r1, 0x7362);
+    const uint32_t t2 = __byte_perm(r2, r3, 0x5140);
+    const uint32_t t3 = __byte_perm(r2, r3, 0x7362);
+    c[0] = __byte_perm(t0, t2, 0x5410);
+    c[1] = __byte_perm(t0, t2, 0x7632);
+    c[2] = __byte_perm(t1, t3, 0x5410);
+    c[3] = __byte_perm(t1, t3, 0x7632);
+}
+
+template <int MR, bool RAW>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_q8_rrr_kernel(const GemvParams p) {
+    extern __shared__ uint32_t smem_u32s[];
+    // layout: x words [MR][kslice_rows/4], then red [MR][512] int32
+    const int xw_per_row = p.kslice_rows >> 2;
+    uint32_t* xs = smem_u32s;
+    int* red = reinterpret_cast<int*>(smem_u32s + MR * xw_per_row);
+    __shared__ int s_is_last;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int cb = blockIdx.x;
+    const int ks = blockIdx.y;
+    const int64_t g = blockIdx.z;
+    const int8_t* a = p.a + g * p.stride_a;
+    const int8_t* b = p.b + g * p.stride_b;
+    const int k_begin = ks * p.kslice_rows;
+    const int k_end = (k_begin + p.kslice_rows < p.k) ? (k_begin + p.kslice_rows) : p.k;
+
+    // stage this slice of the activations (zero beyond K) and clear the reduction buffer
+    for (int i = threadIdx.x; i < MR * xw_per_row; i += GEMV_THREADS) {
+        const int r = i / xw_per_row, w = i - r * xw_per_row;
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int kk = k_begin + w * 4 + j;
+            if (kk < k_end) word |= static_cast<uint32_t>(static_cast<uint8_t>(a[static_cast<int64_t>(r) * p.lda + kk])) << (8 * j);
+        }
+        xs[i] = word;
+    }
+    for (int i = threadIdx.x; i < MR * RRR_COLS_PER_CTA; i += GEMV_THREADS) red[i] = 0;
+    __syncthreads();
+
+    const int col0 = cb * RRR_COLS_PER_CTA + lane * 16;
+    const bool col_ok = col0 < p.n;  // n is a multiple of 16 on this path
+    int acc[16][MR];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+#pragma unroll
+        for (int r = 0; r < MR; ++r) acc[j][r] = 0;
+
+    const int rows_per_warp = p.kslice_rows / GEMV_WARPS;  // multiple of 4
+    const int wk_begin = k_begin + warp * rows_per_warp;
+    if (col_ok) {
+        for (int kk = wk_begin; kk < wk_begin + rows_per_warp && kk < k_end; kk += 4) {
+            uint4 w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                w[j] = (kk + j < k_end) ? ldg_stream_v4(b + static_cast<int64_t>(kk + j) * p.ldb + col0)
+                                        : make_uint4(0, 0, 0, 0);
+            }
+            uint32_t cols[16];
+            {
+                uint32_t t[4];
+                transpose4x4_bytes(w[0].x, w[1].x, w[2].x, w[3].x, t);
+                cols[0] = t[0]; cols[1] = t[1]; cols[2] = t[2]; cols[3] = t[3];
+                transpose4x4_bytes(w[0].y, w[1].y, w[2].y, w[3].y, t);
+                cols[4] = t[0]; cols[5] = t[1]; cols[6] = t[2]; cols[7] = t[3];
+                transpose4x4_bytes(w[0].z, w[1].z, w[2].z, w[3].z, t);
+                cols[8] = t[0]; cols[9] = t[1]; cols[10] = t[2]; cols[11] = t[3];
+                transpose4x4_bytes(w[0].w, w[1].w, w[2].w, w[3].w, t);
+                cols[12] = t[0]; cols[13] = t[1]; cols[14] = t[2]; cols[15] = t[3];
+            }
+            const int xw = (kk - k_begin) >> 2;
+#pragma unroll
+            for (int r = 0; r < MR; ++r) {
+                const int xv = static_cast<int>(xs[r * xw_per_row + xw]);  // same word for every lane
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[j][r] = __dp4a(static_cast<int>(cols[j]), xv, acc[j][r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < MR; ++r)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) atomicAdd(&red[r * RRR_COLS_PER_CTA + lane * 16 + j], acc[j][r]);
+    }
+    __syncthreads();
+
+    const int ncols_here = (p.n - cb * RRR_COLS_PER_CTA < RRR_COLS_PER_CTA) ? (p.n - cb * RRR_COLS_PER_CTA)
+                                                                             : RRR_COLS_PER_CTA;
+    if (p.num_kslices == 1) {
+        for (int i = threadIdx.x; i < MR * ncols_here; i += GEMV_THREADS) {
+            const int r = i / ncols_here, c = i - r * ncols_here;
+            store_result<RAW>(p, g, r, cb * RRR_COLS_PER_CTA + c, red[r * RRR_COLS_PER_CTA + c]);
+        }
+        return;
+    }
+
+    // publish this slice's partial sums, then take a ticket; the CTA that draws
+    // the last ticket of its column strip folds the slices in slice order.
+    int32_t* part = p.ws_partials + (g * p.num_kslices + ks) * static_cast<int64_t>(MR) * p.n;
+    for (int i = threadIdx.x; i < MR * ncols_here; i += GEMV_THREADS) {
+        const int r = i / ncols_here, c = i - r * ncols_here;
+        __stcg(part + static_cast<int64_t>(r) * p.n + cb * RRR_COLS_PER_CTA + c, red[r * RRR_COLS_PER_CTA + c]);
+    }
+    __threadfence();
+    __syncthreads();
+    unsigned int* ticket = p.ws_tickets + g * gridDim.x + cb;
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(ticket, 1u);
+        s_is_last = (t == static_cast<unsigned int>(p.num_kslices - 1)) ? 1 : 0;
+    }
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+    const int32_t* all = p.ws_partials + g * p.num_kslices * static_cast<int64_t>(MR) * p.n;
+    for (int i = threadIdx.x; i < MR * ncols_here; i += GEMV_THREADS) {
+        const int r = i / ncols_here, c = i - r * ncols_here;
+        const int col = cb * RRR_COLS_PER_CTA + c;
+        int sum = 0;
+        for (int s = 0; s < p.num_kslices; ++s) {
+            sum += __ldcg(all + (static_cast<int64_t>(s) * MR + r) * p.n + col);
+        }
+        store_result<RAW>(p, g, r, col, sum);
+    }
+    if (threadIdx.x == 0) *ticket = 0u;  // leave the ticket ready for the next call
+}
+
+// ---- any layout, any alignment: one warp per output column, byte loads ----
+template <bool RAW>
+__global__ void __launch_bounds__(GEMV_THREADS)
+gemv_q8_generic_kernel(const GemvParams p, int layout) {
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int64_t g = blockIdx.y;
+    const int col = blockIdx.x * GEMV_WARPS + warp;
+    if (col >= p.n) return;
+    const int8_t* a = p.a + g * p.stride_a;
+    const int8_t* b = p.b + g * p.stride_b;
+    int acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) acc[r] = 0;
+    for (int kk = lane; kk < p.k; kk += 32) {
+        const int wv = (layout == BQ_LAYOUT_RCR) ? b[static_cast<int64_t>(col) * p.ldb + kk]
+                                                 : b[static_cast<int64_t>(kk) * p.ldb + col];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < p.m) acc[r] += wv * static_cast<int>(a[static_cast<int64_t>(r) * p.lda + kk]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        if (r < p.m) {
+            const int v = warp_sum(acc[r]);
+            if (lane == r) store_result<RAW>(p, g, r, col, v);
+        }
+    }
+}
+
+struct RrrPlan {
+    int kslice_rows;
+    int num_kslices;
+    int col_blocks;
+};
+
+// Depends on the problem shape only, so workspace_size() and run() agree.
+RrrPlan plan_rrr(int32_t n, int32_t k) {
+    RrrPlan pl;
+    pl.col_blocks = (n + RRR_COLS_PER_CTA - 1) / RRR_COLS_PER_CTA;
+    if (pl.col_blocks < 1) pl.col_blocks = 1;
+    // aim for about 512 CTAs; a slice is a multiple of 32 rows (4 rows x 8 warps)
+    int want_slices = (512 + pl.col_blocks - 1) / pl.col_blocks;
+    int rows = (k + want_slices - 1) / want_slices;
+    rows = ((rows + 31) / 32) * 32;
+    if (rows < 32) rows = 32;
+    if (rows > 2048) rows = 2048;
+    pl.kslice_rows = rows;
+    pl.num_kslices = (k + rows - 1) / rows;
+    if (pl.num_kslices < 1) pl.num_kslices = 1;
+    return pl;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int MR, bool RAW>
+int32_t launch_rcr(const GemvParams& p, int batch, cudaStream_t stream) {
+    // enough warps to cover the machine several times over, else fewer columns per warp
+    const size_t smem = static_cast<size_t>(MR) * KB_BYTES;
+    auto blocks_for = [&](int cpw) { return (p.n + GEMV_WARPS * cpw - 1) / (GEMV_WARPS * cpw); };
+    if (p.n >= 8192) {
+        auto kern = gemv_q8_rcr_kernel<MR, 4, RAW>;
+        kern<<<dim3(blocks_for(4), batch), GEMV_THREADS, smem, stream>>>(p);
+    } else if (p.n >= 2048) {
+        auto kern = gemv_q8_rcr_kernel<MR, 2, RAW>;
+        kern<<<dim3(blocks_for(2), batch), GEMV_THREADS, smem, stream>>>(p);
+    } else {
+        auto kern = gemv_q8_rcr_kernel<MR, 1, RAW>;
+        kern<<<dim3(blocks_for(1), batch), GEMV_THREADS, smem, stream>>>(p);
+    }
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
+
+template <int MR, bool RAW>
+int32_t launch_rrr(GemvParams p, int batch, const GemvDesc& gd, cudaStream_t stream) {
+    const RrrPlan pl = plan_rrr(p.n, p.k);
+    p.kslice_rows = pl.kslice_rows;
+    p.num_kslices = pl.num_kslices;
+    if (pl.num_kslices > 1) {
+        const size_t need = gemv_q8_workspace_bytes(p.m, p.n, p.k, batch, BQ_LAYOUT_RRR);
+        if (gd.workspace == nullptr || gd.workspace_bytes < need) return BQ_STATUS_WORKSPACE;
+        if (!aligned16(gd.workspace)) return BQ_STATUS_MISALIGNED;
+        const size_t tickets_bytes = align_up(static_cast<size_t>(batch) * pl.col_blocks * sizeof(unsigned int), 256);
+        p.ws_tickets = static_cast<unsigned int*>(gd.workspace);
+        p.ws_partials = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(gd.workspace) + tickets_bytes);
+        // the workspace is opaque scratch: the tickets must start at zero on every call
+        if (cudaMemsetAsync(p.ws_tickets, 0, tickets_bytes, stream) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return BQ_STATUS_LAUNCH_FAILURE;
+        }
+    }
+    const size_t smem = static_cast<size_t>(MR) * (pl.kslice_rows / 4) * 4 + static_cast<size_t>(MR) * RRR_COLS_PER_CTA * 4;
+    auto kern = gemv_q8_rrr_kernel<MR, RAW>;
+    kern<<<dim3(pl.col_blocks, pl.num_kslices, batch), GEMV_THREADS, smem, stream>>>(p);
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
+
+template <bool RAW>
+int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
+    GemvParams p;
+    p.a = g.a; p.lda = g.lda; p.stride_a = g.stride_a;
+    p.b = g.b; p.ldb = g.ldb; p.stride_b = g.stride_b;
+    p.sa = g.scale_a; p.stride_sa = g.stride_scale_a;
+    p.sb = g.scale_b; p.stride_sb = g.stride_scale_b;
+    p.d = g.d; p.ldd = g.ldd; p.stride_d = g.stride_d;
+    p.alpha = g.alpha; p.beta = g.beta;
+    p.m = g.m; p.n = g.n; p.k = g.k;
+    p.kslice_rows = 0; p.num_kslices = 1;
+    p.ws_partials = nullptr; p.ws_tickets = nullptr;
+
+    // the streaming kernels need 16-byte alignment of every weight row segment they load
+    bool fast = g.k > 0 && aligned16(g.a) && aligned16(g.b) && (g.stride_b % 16 == 0) && (g.ldb % 16 == 0);
+    if (g.layout == BQ_LAYOUT_RCR) {
+        fast = fast && (g.k % 16 == 0) && (g.lda % 16 == 0 || g.m == 1) && (g.stride_a % 16 == 0);
+    } else {
+        fast = fast && (g.n % 16 == 0);
+    }
+    if (g.variant == 9) fast = false;  // tests: force the byte-load kernel
+    if (!fast) {
+        const int blocks = (g.n + GEMV_WARPS - 1) / GEMV_WARPS;
+        gemv_q8_generic_kernel<RAW><<<dim3(blocks, g.batch), GEMV_THREADS, 0, stream>>>(p, g.layout);
+        return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+    }
+#define BQ_GEMV_CASE(MRV)                                                                  \
+    case MRV:                                                                              \
+        return g.layout == BQ_LAYOUT_RCR ? launch_rcr<MRV, RAW>(p, g.batch, stream)        \
+                                         : launch_rrr<MRV, RAW>(p, g.batch, g, stream);
+    switch (g.m) {
+        BQ_GEMV_CASE(1)
+        BQ_GEMV_CASE(2)
+        BQ_GEMV_CASE(3)
+        BQ_GEMV_CASE(4)
+        BQ_GEMV_CASE(5)
+        BQ_GEMV_CASE(6)
+        BQ_GEMV_CASE(7)
+        BQ_GEMV_CASE(8)
+        default: return BQ_STATUS_INVALID_PROBLEM;
+    }
+#undef BQ_GEMV_CASE
+}
+
+}  // namespace
+
+size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout) {
+    if (layout != BQ_LAYOUT_RRR || m <= 0 || n <= 0 || k <= 0 || batch <= 0) return 0;
+    const RrrPlan pl = plan_rrr(n, k);
+    if (pl.num_kslices <= 1) return 0;
+    const size_t tickets = align_up(static_cast<size_t>(batch) * pl.col_blocks * sizeof(unsigned int), 256);
+    const size_t partials = static_cast<size_t>(batch) * pl.num_kslices * m * n * sizeof(int32_t);
+    return tickets + partials;
+}
+
+int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream) {
+    return g.raw_out ? dispatch<true>(g, stream) : dispatch<false>(g, stream);
+}
+
+}  // namespace bq

@@ -1,0 +1,405 @@
+"""Typed Plan facade over the flat C ABI — the host-side mirror of the
+reference's Plan triple (`select` → `can_implement` → `workspace_size` → `run`,
+plus `sku()` / `precision_guarantee()`; ARCHITECTURE.md:67-110 of the reference,
+crates/baracuda-kernels/src/gemm/int_gemm.rs:48-637, fp8_gemm.rs:36-741,
+gemv_dense.rs:48-412).
+
+The plans are plain data: a validated descriptor plus the SKU fixed at
+`select`.  Tensors are torch CUDA tensors used purely as device-buffer
+handles (pointer, length, dtype); all compute happens in the CUDA library.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .vocab import (
+    OP_FP8_SCALED_GEMM,
+    OP_GEMV_Q8,
+    OP_W8A8_GEMM,
+    ArchSku,
+    BackendKind,
+    BufferTooSmall,
+    ElementKind,
+    EpilogueKind,
+    InvalidProblem,
+    KernelSku,
+    LayoutSku,
+    MathPrecision,
+    OpCategory,
+    PlanPreference,
+    PrecisionGuarantee,
+    Unsupported,
+    WorkspaceTooSmall,
+    status_to_result,
+)
+
+SCALE_PER_TENSOR = 0
+SCALE_PER_ROW_COL = 1
+
+_INT_GUARANTEE = PrecisionGuarantee(MathPrecision.Int8, ElementKind.I32, True, True)
+# tcgen05 accumulates each tile in a fixed order; one CTA owns one output tile
+_FP8_GUARANTEE = PrecisionGuarantee(MathPrecision.Fp8E4M3, ElementKind.F32, True, True)
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, int):
+        return stream
+    return stream.cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, elems: int, name: str) -> None:
+    """The typed layer is the soundness boundary for buffer lengths
+    (gemv_dense.rs:218-268): refuse a launch that would run off a buffer."""
+    if t.numel() < elems:
+        raise BufferTooSmall(f"{name}: need {elems} elements, buffer holds {t.numel()}")
+
+
+def _check_backend(pref: PlanPreference) -> None:
+    if pref.prefer_backend not in (None, BackendKind.Bespoke):
+        raise Unsupported("these plans are bespoke-only")
+
+
+def _span(rows: int, cols: int, ld: int) -> int:
+    return 0 if rows == 0 or cols == 0 else (rows - 1) * ld + cols
+
+
+# --------------------------------------------------------------------------- GEMM
+@dataclass(frozen=True)
+class QGemmDescriptor:
+    """Shape and layout of an 8-bit GEMM (IntGemmDescriptor, types.rs:187-198)."""
+    m: int
+    n: int
+    k: int
+    layout: LayoutSku = LayoutSku.Rcr
+    epilogue: EpilogueKind = EpilogueKind.Identity
+
+
+@dataclass
+class QGemmArgs:
+    """Device views for one run.  `a` is [M,K] with row pitch lda, `b` is the
+    weight stored [N,K] with row pitch ldb (column-major [K,N]), `d` is [M,N]."""
+    a: torch.Tensor
+    b: torch.Tensor
+    d: torch.Tensor
+    scale_a: Optional[torch.Tensor] = None
+    scale_b: Optional[torch.Tensor] = None
+    lda: Optional[int] = None
+    ldb: Optional[int] = None
+    ldd: Optional[int] = None
+    alpha: float = 1.0
+    beta: float = 0.0
+    c: Optional[torch.Tensor] = None
+    ldc: int = 0
+
+
+class _QGemmPlanBase:
+    _run_symbol = ""
+    _can_symbol = ""
+    _ws_symbol = ""
+    _in_dtypes: tuple = ()
+    _out_dtype = torch.bfloat16
+    _needs_scales = True
+
+    def __init__(self, desc: QGemmDescriptor, sku: KernelSku):
+        self.desc = desc
+        self._sku = sku
+
+    @classmethod
+    def _validate_desc(cls, desc: QGemmDescriptor, pref: PlanPreference) -> None:
+        _check_backend(pref)
+        if desc.m < 0 or desc.n < 0 or desc.k < 0:
+            raise InvalidProblem("negative dimension")
+        if max(desc.m, desc.n, desc.k) >= 2**31:
+            raise InvalidProblem("dimension exceeds int32")
+        if desc.layout is not LayoutSku.Rcr:
+            raise Unsupported("only the RCR layout (K-contiguous weights) has an sm_100a GEMM kernel")
+        if desc.epilogue is not EpilogueKind.Identity:
+            raise Unsupported("bias / activation epilogues are not built for the sm_100a SKUs")
+
+    def sku(self) -> KernelSku:
+        return self._sku
+
+    def precision_guarantee(self) -> PrecisionGuarantee:
+        return self._sku.precision_guarantee
+
+    def workspace_size(self) -> int:
+        lib = _lib.load()
+        return int(getattr(lib, self._ws_symbol)(self.desc.m, self.desc.n, self.desc.k))
+
+    def _lds(self, args: QGemmArgs):
+        d = self.desc
+        lda = args.lda if args.lda is not None else max(d.k, 1)
+        ldb = args.ldb if args.ldb is not None else max(d.k, 1)
+        ldd = args.ldd if args.ldd is not None else max(d.n, 1)
+        return lda, ldb, ldd
+
+    def can_implement(self, args: QGemmArgs) -> None:
+        d = self.desc
+        lda, ldb, ldd = self._lds(args)
+        for t, name in ((args.a, "a"), (args.b, "b")):
+            if t.dtype not in self._in_dtypes:
+                raise InvalidProblem(f"{name}: dtype {t.dtype} not accepted by this plan")
+        if args.d.dtype != self._out_dtype:
+            raise InvalidProblem(f"d: expected {self._out_dtype}")
+        if not (args.a.is_cuda and args.b.is_cuda and args.d.is_cuda):
+            raise InvalidProblem("operands must be device buffers")
+        lib = _lib.load()
+        st = getattr(lib, self._can_symbol)(d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb,
+                                            _ptr(args.c), args.ldc, _ptr(args.d), ldd)
+        status_to_result(st, type(self).__name__)
+        _need(args.a, _span(d.m, d.k, lda), "a")
+        _need(args.b, _span(d.n, d.k, ldb), "b")
+        _need(args.d, _span(d.m, d.n, ldd), "d")
+        if self._needs_scales:
+            self._check_scales(args)
+
+    def _check_scales(self, args: QGemmArgs) -> None:
+        raise NotImplementedError
+
+    def _call(self, lib, args: QGemmArgs, lda: int, ldb: int, ldd: int, ws_ptr, ws_bytes, stream) -> int:
+        raise NotImplementedError
+
+    def run(self, stream, workspace: Optional[torch.Tensor], args: QGemmArgs) -> None:
+        self.can_implement(args)
+        need = self.workspace_size()
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        if need > ws_bytes:
+            raise WorkspaceTooSmall(need, ws_bytes)
+        lib = _lib.load()
+        lda, ldb, ldd = self._lds(args)
+        st = self._call(lib, args, lda, ldb, ldd, _ptr(workspace), ws_bytes, _stream_ptr(stream))
+        status_to_result(st, type(self).__name__)
+
+
+class W8A8GemmPlan(_QGemmPlanBase):
+    """s8 x s8 -> s32 on tcgen05 with the fused per-token x per-channel dequant
+    to bf16 (or, with `raw_accumulators`, the int32 sums themselves)."""
+
+    _in_dtypes = (torch.int8,)
+
+    def __init__(self, desc, sku, raw: bool):
+        super().__init__(desc, sku)
+        self.raw = raw
+        base = "baracuda_kernels_gemm_s8_rcr_s32_sm100a" if raw else "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a"
+        self._run_symbol, self._can_symbol, self._ws_symbol = base + "_run", base + "_can_implement", base + "_workspace_size"
+        self._out_dtype = torch.int32 if raw else torch.bfloat16
+        self._needs_scales = not raw
+
+    @classmethod
+    def select(cls, stream, desc: QGemmDescriptor, pref: PlanPreference = PlanPreference(),
+               raw_accumulators: bool = False) -> "W8A8GemmPlan":
+        cls._validate_desc(desc, pref)
+        sku = KernelSku(OpCategory.Gemm, OP_W8A8_GEMM, ElementKind.S8,
+                        ElementKind.I32 if raw_accumulators else ElementKind.Bf16,
+                        desc.layout, desc.epilogue, ArchSku.Sm100a, BackendKind.Bespoke, _INT_GUARANTEE)
+        return cls(desc, sku, raw_accumulators)
+
+    def _check_scales(self, args):
+        if args.scale_a is None or args.scale_b is None:
+            raise InvalidProblem("scale_a and scale_b are required")
+        for t, n, name in ((args.scale_a, self.desc.m, "scale_a"), (args.scale_b, self.desc.n, "scale_b")):
+            if t.dtype != torch.float32:
+                raise InvalidProblem(f"{name}: expected float32")
+            _need(t, n, name)
+
+    def _call(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
+        d = self.desc
+        if self.raw:
+            return lib.baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+        return lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
+            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+            _ptr(args.scale_a), _ptr(args.scale_b), args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+
+
+class Fp8ScaledGemmPlan(_QGemmPlanBase):
+    """e4m3 x e4m3 -> f32 on tcgen05 with f32 scales (per tensor, or per row and
+    per column) fused into a bf16 store; `raw_accumulators` writes the f32 sums."""
+
+    _in_dtypes = (torch.uint8, torch.float8_e4m3fn)
+
+    def __init__(self, desc, sku, raw: bool, scale_mode: int):
+        super().__init__(desc, sku)
+        self.raw = raw
+        self.scale_mode = scale_mode
+        base = ("baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a" if raw
+                else "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a")
+        self._run_symbol, self._can_symbol, self._ws_symbol = base + "_run", base + "_can_implement", base + "_workspace_size"
+        self._out_dtype = torch.float32 if raw else torch.bfloat16
+        self._needs_scales = not raw
+
+    @classmethod
+    def select(cls, stream, desc: QGemmDescriptor, pref: PlanPreference = PlanPreference(),
+               scale_mode: int = SCALE_PER_TENSOR, raw_accumulators: bool = False) -> "Fp8ScaledGemmPlan":
+        cls._validate_desc(desc, pref)
+        if scale_mode not in (SCALE_PER_TENSOR, SCALE_PER_ROW_COL):
+            raise InvalidProblem("scale_mode must be 0 (per tensor) or 1 (per row / per column)")
+        sku = KernelSku(OpCategory.Gemm, OP_FP8_SCALED_GEMM, ElementKind.Fp8E4M3,
+                        ElementKind.F32 if raw_accumulators else ElementKind.Bf16,
+                        desc.layout, desc.epilogue, ArchSku.Sm100a, BackendKind.Bespoke, _FP8_GUARANTEE)
+        return cls(desc, sku, raw_accumulators, scale_mode)
+
+    def _check_scales(self, args):
+        if args.scale_a is None or args.scale_b is None:
+            raise InvalidProblem("scale_a and scale_b are required")
+        na = self.desc.m if self.scale_mode == SCALE_PER_ROW_COL else 1
+        nb = self.desc.n if self.scale_mode == SCALE_PER_ROW_COL else 1
+        for t, n, name in ((args.scale_a, na, "scale_a"), (args.scale_b, nb, "scale_b")):
+            if t.dtype != torch.float32:
+                raise InvalidProblem(f"{name}: expected float32")
+            _need(t, n, name)
+
+    def _call(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
+        d = self.desc
+        if self.raw:
+            return lib.baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+        return lib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
+            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+            _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+
+
+# --------------------------------------------------------------------------- GEMV
+@dataclass(frozen=True)
+class GemvQ8Descriptor:
+    """GemvDenseDescriptor (gemv_dense.rs:48-75) for int8 weights; m may be 1..8."""
+    m: int
+    n: int
+    k: int
+    batch: int = 1
+    layout: LayoutSku = LayoutSku.Rrr
+
+
+@dataclass
+class GemvQ8Args:
+    """GemvDenseArgs (gemv_dense.rs:77-110) plus the two scale vectors."""
+    a: torch.Tensor
+    b: torch.Tensor
+    d: torch.Tensor
+    scale_a: Optional[torch.Tensor] = None
+    scale_b: Optional[torch.Tensor] = None
+    lda: Optional[int] = None
+    ldb: Optional[int] = None
+    ldd: Optional[int] = None
+    stride_a: int = 0
+    stride_b: int = 0
+    stride_d: int = 0
+    stride_scale_a: int = 0
+    stride_scale_b: int = 0
+    alpha: float = 1.0
+    beta: float = 0.0
+
+
+class GemvQ8Plan:
+    """Decode GEMV with int8 weights, bf16 out (or the int32 sums)."""
+
+    def __init__(self, desc: GemvQ8Descriptor, sku: KernelSku, raw: bool):
+        self.desc, self._sku, self.raw = desc, sku, raw
+        self._base = "baracuda_kernels_gemv_q8_m1_s32_sm100a" if raw else "baracuda_kernels_gemv_q8_m1_bf16_sm100a"
+
+    @classmethod
+    def select(cls, stream, desc: GemvQ8Descriptor, pref: PlanPreference = PlanPreference(),
+               raw_accumulators: bool = False) -> "GemvQ8Plan":
+        _check_backend(pref)
+        if min(desc.m, desc.n, desc.k, desc.batch) < 0:
+            raise InvalidProblem("negative dimension")
+        if desc.m > 8:
+            raise InvalidProblem("the GEMV family serves m <= 8; larger m belongs on the GEMM plans")
+        sku = KernelSku(OpCategory.Gemm, OP_GEMV_Q8, ElementKind.S8,
+                        ElementKind.I32 if raw_accumulators else ElementKind.Bf16,
+                        desc.layout, None, ArchSku.Sm100a, BackendKind.Bespoke, _INT_GUARANTEE)
+        plan = cls(desc, sku, raw_accumulators)
+        if plan.workspace_size() > pref.max_workspace_bytes:
+            raise Unsupported("workspace budget too small for this shape")
+        return plan
+
+    def sku(self) -> KernelSku:
+        return self._sku
+
+    def precision_guarantee(self) -> PrecisionGuarantee:
+        return self._sku.precision_guarantee
+
+    def _layout_code(self) -> int:
+        return 0 if self.desc.layout is LayoutSku.Rrr else 1
+
+    def workspace_size(self) -> int:
+        lib = _lib.load()
+        d = self.desc
+        return int(getattr(lib, self._base + "_workspace_size")(d.m, d.n, d.k, d.batch, self._layout_code()))
+
+    def _lds(self, args: GemvQ8Args):
+        d = self.desc
+        lda = args.lda if args.lda is not None else max(d.k, 1)
+        ldb_min = d.n if d.layout is LayoutSku.Rrr else d.k
+        ldb = args.ldb if args.ldb is not None else max(ldb_min, 1)
+        ldd = args.ldd if args.ldd is not None else max(d.n, 1)
+        return lda, ldb, ldd
+
+    def can_implement(self, args: GemvQ8Args) -> None:
+        d = self.desc
+        lda, ldb, ldd = self._lds(args)
+        if args.a.dtype != torch.int8 or args.b.dtype != torch.int8:
+            raise InvalidProblem("a and b must be int8")
+        if args.d.dtype != (torch.int32 if self.raw else torch.bfloat16):
+            raise InvalidProblem("d has the wrong dtype for this plan")
+        lib = _lib.load()
+        st = getattr(lib, self._base + "_can_implement")(d.m, d.n, d.k, d.batch, self._layout_code(), lda, ldb, ldd,
+                                                         args.stride_a, args.stride_b, args.stride_d)
+        status_to_result(st, "GemvQ8Plan")
+        if min(args.stride_a, args.stride_b, args.stride_d) < 0:
+            raise InvalidProblem("negative batch stride")
+        last = max(d.batch - 1, 0)
+        b_rows, b_cols = (d.k, d.n) if d.layout is LayoutSku.Rrr else (d.n, d.k)
+        if d.batch > 0:
+            _need(args.a, last * args.stride_a + _span(d.m, d.k, lda), "a")
+            _need(args.b, last * args.stride_b + _span(b_rows, b_cols, ldb), "b")
+            _need(args.d, last * args.stride_d + _span(d.m, d.n, ldd), "d")
+            if not self.raw:
+                if args.scale_a is None or args.scale_b is None:
+                    raise InvalidProblem("scale_a and scale_b are required")
+                _need(args.scale_a, last * args.stride_scale_a + d.m, "scale_a")
+                _need(args.scale_b, last * args.stride_scale_b + d.n, "scale_b")
+
+    def run(self, stream, workspace: Optional[torch.Tensor], args: GemvQ8Args) -> None:
+        self.can_implement(args)
+        need = self.workspace_size()
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        if need > ws_bytes:
+            raise WorkspaceTooSmall(need, ws_bytes)
+        lib = _lib.load()
+        d = self.desc
+        lda, ldb, ldd = self._lds(args)
+        s = _stream_ptr(stream)
+        if self.raw:
+            st = lib.baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
+                d.m, d.n, d.k, d.batch, self._layout_code(), args.alpha, args.beta,
+                _ptr(args.a), lda, args.stride_a, _ptr(args.b), ldb, args.stride_b,
+                _ptr(args.d), ldd, args.stride_d, _ptr(workspace), ws_bytes, s)
+        else:
+            st = lib.baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
+                d.m, d.n, d.k, d.batch, self._layout_code(), args.alpha, args.beta,
+                _ptr(args.a), lda, args.stride_a, _ptr(args.b), ldb, args.stride_b,
+                _ptr(args.scale_a), args.stride_scale_a, _ptr(args.scale_b), args.stride_scale_b,
+                _ptr(args.d), ldd, args.stride_d, _ptr(workspace), ws_bytes, s)
+        status_to_result(st, "GemvQ8Plan")
+
+
+def device_status() -> int:
+    """Read-and-clear the word a kernel sets when a bounded wait ran out (0 = none)."""
+    return int(_lib.load().baracuda_kernels_q_device_status())
+
+
+def set_tuning(key: int, value: int) -> None:
+    status_to_result(_lib.load().baracuda_kernels_q_set_tuning(key, value), "set_tuning")

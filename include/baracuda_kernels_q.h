@@ -1,0 +1,190 @@
+/*
+ * Flat C ABI of the sm_100a quantized-GEMM hot path.
+ *
+ * These are the symbols a `baracuda-kernels-sys`-style binding declares as
+ * `unsafe extern "C"` and the safe Plan layer calls from `run`.  They follow
+ * the conventions of the reference's bespoke kernels
+ * (crates/baracuda-kernels-sys/src/lib.rs:19-27 for the status codes;
+ *  crates/baracuda-kernels-sys/kernels/gemm/gemm_s8_rrr_sm80.cu:28-64 and
+ *  crates/baracuda-kernels-sys/kernels/gemm/gemv_dense.cu:235-343 for the
+ *  run / can_implement / workspace_size triples):
+ *
+ *   - every pointer is a DEVICE pointer owned by the caller; nothing here
+ *     allocates or frees; scratch is passed in as `workspace` and sized by the
+ *     matching *_workspace_size;
+ *   - dims are int32, leading dimensions and batch strides are int64 counted
+ *     in ELEMENTS; `stream` is a cudaStream_t; launches are asynchronous and
+ *     never synchronise the host;
+ *   - the return value is a status: 0 ok, 1 misaligned operand, 2 invalid
+ *     problem, 3 unsupported, 4 workspace missing or too small, 5 launch
+ *     failure.  Empty problems (m == 0 or n == 0) return 0 without launching;
+ *   - *_can_implement and *_workspace_size are pure host functions.
+ *
+ * Layout tags: "rcr" = A row-major [M,K], B column-major [K,N] (that is, the
+ * weight stored [N,K] with K contiguous, ldb >= K), D row-major [M,N].
+ * For the GEMV the `layout` argument selects 0 = RRR (B row-major [K,N],
+ * ldb >= N — the only layout of the reference's gemv_dense_m1) or
+ * 1 = RCR (B stored [N,K], ldb >= K).
+ */
+#ifndef BARACUDA_KERNELS_Q_H
+#define BARACUDA_KERNELS_Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BARACUDA_Q_STATUS_OK 0
+#define BARACUDA_Q_STATUS_MISALIGNED 1
+#define BARACUDA_Q_STATUS_INVALID_PROBLEM 2
+#define BARACUDA_Q_STATUS_UNSUPPORTED 3
+#define BARACUDA_Q_STATUS_WORKSPACE 4
+#define BARACUDA_Q_STATUS_LAUNCH_FAILURE 5
+
+#define BARACUDA_Q_LAYOUT_RRR 0
+#define BARACUDA_Q_LAYOUT_RCR 1
+
+#define BARACUDA_Q_SCALE_PER_TENSOR 0 /* scale_a, scale_b each point at ONE float on the device */
+#define BARACUDA_Q_SCALE_PER_ROW_COL 1 /* scale_a is float[M], scale_b is float[N] */
+
+/* ---------------------------------------------------------------------------
+ * W8A8 GEMM, s8 x s8 -> s32 on tcgen05, fused dequant to bf16:
+ *   D[i,j] = bf16( alpha * ((scale_a[i] * scale_b[j]) * (float)acc[i,j]) )
+ * The product order is the reference's W8A8 formula
+ * (crates/baracuda-kernels-sys/kernels/include/baracuda_quantize_compose.cuh:271-274),
+ * so with alpha == 1 the result equals it bit for bit.
+ * Replaces the two-pass route of the reference: the s8-out tensor-core GEMM
+ *   baracuda_cutlass_gemm_s8_rcr_sm80_run
+ *   (crates/baracuda-cutlass-kernels-sys/kernels/gemm_s8_rcr_sm80.cu:169-183)
+ * followed by a dequant pass, and the one-thread-per-cell
+ *   baracuda_kernels_quantized_linear_w8a8_f32_run
+ *   (crates/baracuda-kernels-sys/kernels/include/baracuda_quantize_compose.cuh:340-370).
+ * `c` / `ldc` / `beta` keep the GEMM family's argument order; this SKU needs
+ * c == NULL and beta == 0 (anything else returns 3).
+ * Alignment: a and b 16-byte aligned, lda and ldb multiples of 16.
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd,
+    const void* scale_a, const void* scale_b,
+    float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, const void* d, int64_t ldd);
+
+/* The same contraction with the int32 accumulators written as they are
+ * (D is int32 [M,N]).  Exists so callers and tests can check the integer
+ * result bit for bit, as the reference's CPU oracle defines it
+ * (crates/baracuda-kernelgen/src/oracle.rs:1289-1372 over I32 operands).
+ * alpha must be 1 and beta 0. */
+int32_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd,
+    float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, const void* d, int64_t ldd);
+
+/* ---------------------------------------------------------------------------
+ * FP8 e4m3 GEMM, f32 accumulate on tcgen05, f32 scales, bf16 out:
+ *   D[i,j] = bf16( alpha * ((sa * sb) * acc[i,j]) )
+ * with (sa, sb) = (scale_a[0], scale_b[0]) for scale_mode 0 and
+ * (scale_a[i], scale_b[j]) for scale_mode 1.
+ * Replaces baracuda_kernels_gemm_fp8_e4m3_rcr_sm89_run
+ *   (crates/baracuda-kernels-sys/kernels/gemm/gemm_fp8_e4m3_rcr_sm89.cu:31-50),
+ * whose output is e4m3 with a scalar alpha only.
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd,
+    const void* scale_a, const void* scale_b, int32_t scale_mode,
+    float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, const void* d, int64_t ldd);
+
+/* f32 accumulators of the e4m3 contraction (D is float [M,N]); alpha 1, beta 0. */
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd,
+    float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, const void* d, int64_t ldd);
+
+/* ---------------------------------------------------------------------------
+ * Decode GEMV with int8 weights, m = 1 (and the skinny extension m <= 8):
+ *   D[g,r,j] = bf16( alpha * ((scale_a[g,r] * scale_b[g,j]) * (float)acc) + beta * D[g,r,j] )
+ * Argument order is that of baracuda_kernels_gemv_dense_m1_bf16_run
+ *   (crates/baracuda-kernels-sys/kernels/gemm/gemv_dense.cu:267-281)
+ * with the two scale vectors (and their batch strides) inserted before `d`.
+ * stride_b == 0 broadcasts the weights over batch slots, as in the reference.
+ * Misaligned or ragged operands are served by a slower byte-load kernel, so
+ * status 1 is never returned by this family.
+ * layout 0 (row-major weights) needs a workspace when K is split over CTAs:
+ * query *_workspace_size and pass at least that much, 16-byte aligned.
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    float alpha, float beta,
+    const void* a, int64_t lda, int64_t stride_a,
+    const void* b, int64_t ldb, int64_t stride_b,
+    const void* scale_a, int64_t stride_scale_a,
+    const void* scale_b, int64_t stride_scale_b,
+    void* d, int64_t ldd, int64_t stride_d,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    int64_t lda, int64_t ldb, int64_t ldd,
+    int64_t stride_a, int64_t stride_b, int64_t stride_d);
+size_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
+
+/* The int32 sums of the same GEMV (D is int32); alpha 1, beta 0, no scales. */
+int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    float alpha, float beta,
+    const void* a, int64_t lda, int64_t stride_a,
+    const void* b, int64_t ldb, int64_t stride_b,
+    void* d, int64_t ldd, int64_t stride_d,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    int64_t lda, int64_t ldb, int64_t ldd,
+    int64_t stride_a, int64_t stride_b, int64_t stride_d);
+size_t baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
+
+/* ---------------------------------------------------------------------------
+ * Diagnostics and tuning (no counterpart in the reference).
+ * device_status: synchronous read-and-clear of the word a GEMM kernel sets
+ * when one of its bounded barrier waits ran out (0 = none; 101..104 name the
+ * waiting role).  Call it after synchronising the stream.
+ * set_tuning: key 0 forces the GEMM N-tile (0 = automatic, 64, 128, 256);
+ * process-wide, meant for benchmarks and tests.
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_q_device_status(void);
+int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BARACUDA_KERNELS_Q_H */

@@ -1,0 +1,203 @@
+"""GPU parity of the tcgen05 GEMMs, through the Plan layer / C ABI, against the
+CPU oracle and the committed fixtures.
+
+W8A8: int32 accumulators bit-exact; bf16 outputs bit-exact with the oracle's
+(sa*sb)*(float)acc -> RNE (the contract allows 1 bf16 ulp; 0 is asserted).
+FP8: f32 accumulators within rel 1e-3 (+ a small absolute floor) of the oracle's
+f64-accumulated value, bf16 outputs within rel 1e-2 — the tolerance the
+benchmark definition states — and bit-exact on the reference's exactly
+representable smoke patterns."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import baracuda_b200 as bq
+from helpers import bf16_bits, dev, fp8_case, pad_rows, w8a8_case
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _run_w8a8(m, n, k, a, b, sa=None, sb=None, raw=False, lda=None, ldb=None, ldd=None, alpha=1.0):
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k), raw_accumulators=raw)
+    ldd_eff = ldd or max(n, 1)
+    d = torch.full((max(m, 1) * ldd_eff,), -7 if raw else 123.0, dtype=torch.int32 if raw else torch.bfloat16,
+                   device="cuda")
+    args = bq.QGemmArgs(a=dev(a), b=dev(b), d=d, scale_a=None if raw else dev(sa), scale_b=None if raw else dev(sb),
+                        lda=lda, ldb=ldb, ldd=ldd, alpha=alpha)
+    plan.run(None, None, args)
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    return d
+
+
+def _run_fp8(m, n, k, a, b, sa=None, sb=None, raw=False, mode=bq.SCALE_PER_ROW_COL):
+    plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), scale_mode=mode, raw_accumulators=raw)
+    d = torch.full((m, n), float("nan"), dtype=torch.float32 if raw else torch.bfloat16, device="cuda")
+    args = bq.QGemmArgs(a=dev(a), b=dev(b), d=d, scale_a=None if raw else dev(sa), scale_b=None if raw else dev(sb))
+    plan.run(None, None, args)
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    return d
+
+
+def _int8_patterns(m, n, k):
+    a = np.array([((i * 7) % 15) - 7 for i in range(m * k)], dtype=np.int8).reshape(m, k)
+    b = np.array([((i * 11) % 13) - 6 for i in range(k * n)], dtype=np.int8).reshape(n, k)
+    return a, b
+
+
+def test_committed_fixtures(oracle):
+    data = np.load(GOLDEN / "w8a8_fp8_cases.npz")
+    for tag in ("c0s", "ragged"):
+        a, b = data[f"{tag}_a_q"], data[f"{tag}_b_q"]
+        m, k = a.shape
+        n = b.shape[0]
+        acc = _run_w8a8(m, n, k, a, b, raw=True).view(m, n).cpu().numpy()
+        assert oracle.compare_bitexact(data[f"{tag}_acc"], acc) == -1
+        out = _run_w8a8(m, n, k, a, b, data[f"{tag}_sa"], data[f"{tag}_sb"])
+        assert oracle.compare_bitexact(data[f"{tag}_out_bf16"], bf16_bits(out).reshape(m, n)) == -1
+    a, b = data["fp8_a_q"], data["fp8_b_q"]
+    m, k = a.shape
+    n = b.shape[0]
+    acc = _run_fp8(m, n, k, a, b, raw=True).cpu().numpy()
+    scale = float(np.abs(data["fp8_acc"]).max())
+    assert oracle.compare_tolerant(data["fp8_acc"], acc, 1e-3, 1e-5 * scale) == -1
+    out = _run_fp8(m, n, k, a, b, data["fp8_sa"], data["fp8_sb"]).to(torch.float32).cpu().numpy()
+    want = oracle.bf16_bits_to_f32(data["fp8_out_bf16"])
+    assert oracle.compare_tolerant(want, out, 1e-2, 1e-2 * float(np.abs(want).max()) * 1e-2) == -1
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 32), (128, 128, 128), (256, 128, 64), (100, 70, 50)])
+def test_reference_int8_smoke_shapes(oracle, shape):
+    """Shapes and integer patterns of crates/baracuda-kernels/tests/int8_rrr_smoke.rs:159-172, 442-500, read as
+    the RCR operands of crates/baracuda-cutlass/tests/int8_smoke.rs:85-124.  Row pitches are padded to the
+    16-byte multiple the TMA path needs (the unpadded 100x70x50 case is rejected as misaligned, like the
+    reference's CUTLASS RCR path)."""
+    m, n, k = shape
+    a, b = _int8_patterns(m, n, k)
+    ld = (k + 15) // 16 * 16
+    acc_ref = oracle.gemm_s8_s32(a, b, oracle.RCR, m, n, k)
+    acc = _run_w8a8(m, n, k, pad_rows(a, ld, 99), pad_rows(b, ld, -99), raw=True, lda=ld, ldb=ld)
+    assert oracle.compare_bitexact(acc_ref, acc.view(m, n).cpu().numpy()) == -1
+    if k % 16:
+        plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k), raw_accumulators=True)
+        with pytest.raises(bq.MisalignedOperand):
+            plan.run(None, None, bq.QGemmArgs(a=dev(a), b=dev(b), d=torch.zeros(m * n, dtype=torch.int32, device="cuda")))
+
+
+def test_config0_w8a8_128x1024x1024(oracle):
+    m, n, k = 128, 1024, 1024
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=1234)
+    acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    acc = _run_w8a8(m, n, k, aq, wq, raw=True).view(m, n).cpu().numpy()
+    assert oracle.compare_bitexact(acc_ref, acc) == -1
+    out = _run_w8a8(m, n, k, aq, wq, sa, sb)
+    assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
+
+
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+def test_every_tile_config_many_tiles_and_tails(oracle, block_n):
+    """More tiles than SMs (persistent loop, both TMEM buffers, ring wrap-around) with ragged M, N and K."""
+    m, n, k = 1100, 2100, 656
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=block_n)
+    acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    want = oracle.dequant_s32_bf16(acc_ref, sa, sb)
+    bq.set_tuning(0, block_n)
+    try:
+        ldd = n + 3  # odd pitch: the scalar store path
+        acc = _run_w8a8(m, n, k, aq, wq, raw=True).view(m, n).cpu().numpy()
+        out = _run_w8a8(m, n, k, aq, wq, sa, sb)
+        out_odd = _run_w8a8(m, n, k, aq, wq, sa, sb, ldd=ldd)
+    finally:
+        bq.set_tuning(0, 0)
+    assert oracle.compare_bitexact(acc_ref, acc) == -1
+    assert oracle.compare_bitexact(want, bf16_bits(out).reshape(m, n)) == -1
+    got_odd = bf16_bits(out_odd).reshape(m, ldd)
+    assert np.array_equal(got_odd[:, :n], want)
+    canary = bf16_bits(torch.tensor([123.0], dtype=torch.bfloat16))[0]
+    assert np.all(got_odd[:, n:] == canary)
+
+
+def test_alpha_and_empty_k(oracle):
+    m, n, k = 130, 200, 256
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=8)
+    acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k).astype(np.float32)
+    y = ((sa[:, None] * sb[None, :]) * acc_ref) * np.float32(0.5)
+    out = _run_w8a8(m, n, k, aq, wq, sa, sb, alpha=0.5)
+    assert np.array_equal(bf16_bits(out).reshape(m, n), bf16_bits(torch.from_numpy(y.astype(np.float32)).to(torch.bfloat16)))
+    # K == 0: an empty contraction is all zeros
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(4, 8, 0), raw_accumulators=True)
+    d = torch.full((32,), 5, dtype=torch.int32, device="cuda")
+    z = torch.zeros(16, dtype=torch.int8, device="cuda")
+    plan.run(None, None, bq.QGemmArgs(a=z, b=z, d=d))
+    torch.cuda.synchronize()
+    assert not d.any()
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 32), (128, 128, 128), (256, 128, 64), (100, 70, 50)])
+def test_reference_fp8_smoke_patterns_exact(oracle, shape):
+    """crates/baracuda-kernels/tests/fp8_e4m3_rcr_smoke.rs:113-127, 225-247: values on the e4m3 grid whose
+    products and sums are exact in f32, so the accumulators must equal the oracle's exactly."""
+    m, n, k = shape
+    av = np.array([(((i * 5) % 13) - 6) * 0.125 for i in range(m * k)], dtype=np.float32).reshape(m, k)
+    bv = np.array([(((i * 7) % 11) - 5) * 0.125 for i in range(k * n)], dtype=np.float32).reshape(n, k)
+    a_bits, b_bits = oracle.f32_to_e4m3(av), oracle.f32_to_e4m3(bv)
+    acc_ref = oracle.gemm_e4m3_f32(a_bits, b_bits, oracle.RCR, m, n, k)
+    ld = (k + 15) // 16 * 16
+    plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), raw_accumulators=True)
+    d = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    plan.run(None, None, bq.QGemmArgs(a=dev(pad_rows(a_bits, ld, 0x7E)), b=dev(pad_rows(b_bits, ld, 0x7E)), d=d,
+                                      lda=ld, ldb=ld))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert oracle.compare_bitexact(acc_ref, d.cpu().numpy()) == -1
+
+
+@pytest.mark.parametrize("per_tensor", [True, False])
+def test_fp8_scaled_bf16(oracle, per_tensor):
+    m, n, k = 384, 640, 1024
+    aq, wq, sa, sb = fp8_case(oracle, m, n, k, seed=21, per_tensor=per_tensor)
+    acc_ref = oracle.gemm_e4m3_f32(aq, wq, oracle.RCR, m, n, k)
+    acc = _run_fp8(m, n, k, aq, wq, raw=True).cpu().numpy()
+    floor = 1e-5 * float(np.abs(acc_ref).max())
+    assert oracle.compare_tolerant(acc_ref, acc, 1e-3, floor) == -1
+    mode = bq.SCALE_PER_TENSOR if per_tensor else bq.SCALE_PER_ROW_COL
+    out = _run_fp8(m, n, k, aq, wq, sa, sb, mode=mode).to(torch.float32).cpu().numpy()
+    want = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(acc_ref, sa, sb))
+    assert oracle.compare_tolerant(want, out, 1e-2, 1e-4 * float(np.abs(want).max())) == -1
+
+
+def test_full_size_4096_cubed_properties(oracle):
+    """At 4096^3 the oracle checks a row sample exactly, and two size-independent properties cover every
+    output: the checksum identity sum_ij acc[i,j] = sum_k (sum_i A[i,k]) (sum_j B[j,k]) in exact integers,
+    and, for FP8, the same identity within f32 rounding."""
+    m = n = k = 4096
+    rng = np.random.default_rng(4096)
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=1236)
+    acc = _run_w8a8(m, n, k, aq, wq, raw=True).view(m, n).cpu().numpy()
+    rows = np.sort(rng.choice(m, 24, replace=False))
+    assert np.array_equal(acc[rows], oracle.gemm_s8_s32(aq[rows], wq, oracle.RCR, len(rows), n, k))
+    col_a = aq.astype(np.int64).sum(axis=0)
+    col_b = wq.astype(np.int64).sum(axis=0)
+    assert int(acc.astype(np.int64).sum()) == int((col_a * col_b).sum())
+    out = _run_w8a8(m, n, k, aq, wq, sa, sb)
+    want_rows = oracle.dequant_s32_bf16(acc[rows], sa[rows], sb)
+    assert np.array_equal(bf16_bits(out).reshape(m, n)[rows], want_rows)
+
+    a8, w8, s8a, s8b = fp8_case(oracle, m, n, k, seed=1237, per_tensor=True)
+    acc8 = _run_fp8(m, n, k, a8, w8, raw=True).cpu().numpy()
+    ref_rows = oracle.gemm_e4m3_f32(a8[rows], w8, oracle.RCR, len(rows), n, k)
+    assert oracle.compare_tolerant(ref_rows, acc8[rows], 1e-3, 1e-5 * float(np.abs(ref_rows).max())) == -1
+    table = oracle.e4m3_decode_table().astype(np.float64)
+    ca = table[a8].sum(axis=0)
+    cb = table[w8].sum(axis=0)
+    total_ref = float((ca * cb).sum())
+    total = float(acc8.astype(np.float64).sum())
+    l1 = float((np.abs(table[a8]).sum(axis=0) * np.abs(table[w8]).sum(axis=0)).sum())
+    assert abs(total - total_ref) <= 1e-6 * l1
+    out8 = _run_fp8(m, n, k, a8, w8, s8a, s8b, mode=bq.SCALE_PER_TENSOR).to(torch.float32).cpu().numpy()
+    want8 = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(ref_rows, s8a, s8b))
+    assert oracle.compare_tolerant(want8, out8[rows], 1e-2, 1e-4 * float(np.abs(want8).max())) == -1

@@ -1,0 +1,159 @@
+"""GPU parity of the int8 decode GEMV, through the C ABI, against the CPU oracle.
+Integer sums must match bit for bit; the bf16 outputs equal the oracle's
+f32-dequant-then-RNE bit for bit as well (tolerance 0 ulp; the contract allows 1)."""
+import numpy as np
+import pytest
+import torch
+
+import baracuda_b200 as bq
+from helpers import bf16_bits, dev, pad_rows, w8a8_case
+
+pytestmark = pytest.mark.gpu
+
+LAYOUTS = {"rcr": bq.LayoutSku.Rcr, "rrr": bq.LayoutSku.Rrr}
+
+
+def _weights_for(layout, wq_nk):
+    """wq_nk is the weight as [N,K]; RRR stores it [K,N]."""
+    return wq_nk if layout is bq.LayoutSku.Rcr else np.ascontiguousarray(wq_nk.T)
+
+
+def _run(m, n, k, layout, aq, wq_nk, sa, sb, raw, **kw):
+    desc = bq.GemvQ8Descriptor(m, n, k, batch=1, layout=layout)
+    plan = bq.GemvQ8Plan.select(None, desc, raw_accumulators=raw)
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    d = torch.full((m, n), -7 if raw else float("nan"), dtype=torch.int32 if raw else torch.bfloat16, device="cuda")
+    args = bq.GemvQ8Args(a=dev(aq), b=dev(_weights_for(layout, wq_nk)), d=d,
+                         scale_a=None if raw else dev(sa), scale_b=None if raw else dev(sb), **kw)
+    plan.run(None, ws, args)
+    torch.cuda.synchronize()
+    return d
+
+
+@pytest.mark.parametrize("layout", ["rcr", "rrr"])
+@pytest.mark.parametrize("m", [1, 2, 4, 8])
+def test_decode_shape_bit_exact(oracle, layout, m):
+    """K=4096, N=14336, m in {1,2,4,8}: the decode configuration at full size."""
+    n, k = 14336, 4096
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=1235)
+    acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    lay = LAYOUTS[layout]
+    acc = _run(m, n, k, lay, aq, wq, sa, sb, raw=True).cpu().numpy()
+    assert oracle.compare_bitexact(acc_ref, acc) == -1
+    out = _run(m, n, k, lay, aq, wq, sa, sb, raw=False)
+    assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out)) == -1
+
+
+@pytest.mark.parametrize("layout", ["rcr", "rrr"])
+@pytest.mark.parametrize("shape", [(1, 70, 50), (3, 100, 77), (1, 64, 32), (5, 1040, 2064), (8, 16, 16), (1, 1, 1),
+                                   (2, 4112, 8208), (7, 528, 6000)])
+def test_ragged_and_small_shapes(oracle, layout, shape):
+    """Ragged shapes in the spirit of the reference's 100x70x50 case; both the streaming and the byte-load kernels."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=77 + n)
+    acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    lay = LAYOUTS[layout]
+    acc = _run(m, n, k, lay, aq, wq, sa, sb, raw=True).cpu().numpy()
+    assert oracle.compare_bitexact(acc_ref, acc) == -1
+    out = _run(m, n, k, lay, aq, wq, sa, sb, raw=False)
+    assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out)) == -1
+
+
+@pytest.mark.parametrize("layout", ["rcr", "rrr"])
+def test_byte_load_kernel_equals_streaming_kernel(oracle, layout):
+    m, n, k = 4, 2048, 1024
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=5)
+    lay = LAYOUTS[layout]
+    fast = _run(m, n, k, lay, aq, wq, sa, sb, raw=True).cpu().numpy()
+    bq.set_tuning(1, 9)
+    try:
+        slow = _run(m, n, k, lay, aq, wq, sa, sb, raw=True).cpu().numpy()
+    finally:
+        bq.set_tuning(1, 0)
+    assert np.array_equal(fast, slow)
+    assert np.array_equal(fast, oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k))
+
+
+@pytest.mark.parametrize("layout", ["rcr", "rrr"])
+def test_padded_leading_dims_batch_broadcast_and_canaries(oracle, layout):
+    """Padded lda/ldb/ldd, strided batch with the weights broadcast (stride_b == 0, the reference's GQA use,
+    gemv_dense_smoke.rs), and untouched padding between output rows and batch slots."""
+    lay = LAYOUTS[layout]
+    m, n, k, batch = 2, 272, 160, 3
+    lda, ldd = k + 16, n + 24
+    stride_a, stride_d, stride_sa = m * lda + 32, m * ldd + 40, m
+    rng = np.random.default_rng(3)
+    aq_all, sa_all = [], []
+    for g in range(batch):
+        aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=100 + g)
+        aq_all.append(aq)
+        sa_all.append(sa)
+    _, wq, _, sb = w8a8_case(oracle, m, n, k, seed=100)
+    a_buf = np.zeros(batch * stride_a, dtype=np.int8)
+    for g in range(batch):
+        a_buf[g * stride_a: g * stride_a + m * lda] = pad_rows(aq_all[g], lda, fill=55).ravel()
+    if lay is bq.LayoutSku.Rcr:
+        ldb = k + 32
+        b_buf = pad_rows(wq, ldb, fill=-99).ravel()
+    else:
+        ldb = n + 16
+        b_buf = pad_rows(np.ascontiguousarray(wq.T), ldb, fill=-99).ravel()
+    d = torch.full((batch * stride_d,), 123.0, dtype=torch.bfloat16, device="cuda")
+    desc = bq.GemvQ8Descriptor(m, n, k, batch=batch, layout=lay)
+    plan = bq.GemvQ8Plan.select(None, desc)
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    args = bq.GemvQ8Args(a=dev(a_buf), b=dev(b_buf), d=d, scale_a=dev(np.concatenate(sa_all)), scale_b=dev(sb),
+                         lda=lda, ldb=ldb, ldd=ldd, stride_a=stride_a, stride_b=0, stride_d=stride_d,
+                         stride_scale_a=stride_sa, stride_scale_b=0)
+    plan.run(None, ws, args)
+    torch.cuda.synchronize()
+    got = bf16_bits(d)
+    canary = bf16_bits(torch.tensor([123.0], dtype=torch.bfloat16))[0]
+    touched = np.zeros(batch * stride_d, dtype=bool)
+    for g in range(batch):
+        acc = oracle.gemm_s8_s32(aq_all[g], wq, oracle.RCR, m, n, k)
+        want = oracle.dequant_s32_bf16(acc, sa_all[g], sb)
+        for r in range(m):
+            lo = g * stride_d + r * ldd
+            assert np.array_equal(got[lo: lo + n], want[r]), (g, r)
+            touched[lo: lo + n] = True
+    assert np.all(got[~touched] == canary), "padding between rows / batch slots was clobbered"
+
+
+def test_alpha_beta(oracle):
+    """D = alpha*(sa*sb*acc) + beta*D, each product and the sum rounded in f32 (gemv_dense.cu FFI contract)."""
+    m, n, k = 2, 512, 256
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=9)
+    acc = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    d0 = (np.random.default_rng(1).standard_normal((m, n))).astype(np.float32)
+    d0_bf = torch.from_numpy(d0).to(torch.bfloat16)
+    alpha, beta = np.float32(0.75), np.float32(-1.5)
+    y = (sa[:, None] * sb[None, :]) * acc.astype(np.float32)
+    y = (y * alpha).astype(np.float32) + (beta * d0_bf.to(torch.float32).numpy()).astype(np.float32)
+    want = bf16_bits(torch.from_numpy(y.astype(np.float32)).to(torch.bfloat16))
+    for lay in (bq.LayoutSku.Rcr, bq.LayoutSku.Rrr):
+        plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=lay))
+        ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+        d = d0_bf.clone().cuda()
+        b = wq if lay is bq.LayoutSku.Rcr else np.ascontiguousarray(wq.T)
+        plan.run(None, ws, bq.GemvQ8Args(a=dev(aq), b=dev(b), d=d, scale_a=dev(sa), scale_b=dev(sb),
+                                         alpha=float(alpha), beta=float(beta)))
+        torch.cuda.synchronize()
+        assert np.array_equal(bf16_bits(d), want)
+
+
+def test_workspace_contract():
+    plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(1, 14336, 4096, layout=bq.LayoutSku.Rrr))
+    assert plan.workspace_size() > 0
+    z8 = torch.zeros(14336 * 4096, dtype=torch.int8, device="cuda")
+    args = bq.GemvQ8Args(a=z8[:4096], b=z8, d=torch.zeros(14336, dtype=torch.bfloat16, device="cuda"),
+                         scale_a=torch.ones(1, device="cuda"), scale_b=torch.ones(14336, device="cuda"))
+    with pytest.raises(bq.WorkspaceTooSmall):
+        plan.run(None, None, args)
+    # the flat symbol reports status 4 as well
+    from baracuda_b200 import _lib
+    st = _lib.load().baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
+        1, 14336, 4096, 1, 0, 1.0, 0.0, args.a.data_ptr(), 4096, 0, args.b.data_ptr(), 14336, 0,
+        args.scale_a.data_ptr(), 0, args.scale_b.data_ptr(), 0, args.d.data_ptr(), 14336, 0, None, 0,
+        torch.cuda.current_stream().cuda_stream)
+    assert st == 4

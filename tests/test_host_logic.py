@@ -1,0 +1,144 @@
+"""Host-side checks that need no GPU: the C-ABI library loads and exports every
+symbol the header declares, the pure-host validators follow the reference's
+status contract, and the typed plans validate / identify themselves."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+import baracuda_b200 as bq
+from baracuda_b200 import _lib
+
+ROOT = Path(__file__).resolve().parent.parent
+W8A8 = "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a"
+GEMV = "baracuda_kernels_gemv_q8_m1_bf16_sm100a"
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "baracuda_kernels_q.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(baracuda_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(qlib):
+    names = _declared_symbols()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(qlib, n), f"{n} declared in the header but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes prototype"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_gemm_can_implement_status_table(qlib):
+    can = getattr(qlib, W8A8 + "_can_implement")
+    A, B, D = 0x10000, 0x20000, 0x30000
+    assert can(128, 256, 512, A, 512, B, 512, None, 0, D, 256) == 0
+    assert can(-1, 256, 512, A, 512, B, 512, None, 0, D, 256) == 2          # negative dim
+    assert can(128, 256, 512, A, 511, B, 512, None, 0, D, 256) == 2         # lda < k
+    assert can(128, 256, 512, A, 512, B, 100, None, 0, D, 256) == 2         # ldb < k
+    assert can(128, 256, 512, A, 512, B, 512, None, 0, D, 255) == 2         # ldd < n
+    assert can(128, 256, 512, A + 4, 512, B, 512, None, 0, D, 256) == 1     # a not 16-byte aligned
+    assert can(128, 256, 500, A, 500, B, 512, None, 0, D, 256) == 1         # lda not a multiple of 16
+    assert can(128, 256, 500, A, 512, B, 512, None, 0, D, 256) == 0         # ragged k with padded pitch is fine
+    assert can(128, 256, 512, A, 512, B, 512, D, 256, D, 256) == 3          # beta*C not built
+    assert can(0, 0, 0, None, 1, None, 1, None, 0, None, 1) == 0            # empty
+    assert getattr(qlib, W8A8 + "_workspace_size")(128, 256, 512) == 0
+
+
+def test_gemv_can_implement_status_table(qlib):
+    """Mirrors the rejection table of crates/baracuda-kernels/tests/gemv_dense_smoke.rs:399-432."""
+    can = getattr(qlib, GEMV + "_can_implement")
+    ok = dict(m=1, n=64, k=32, batch=1, layout=0, lda=32, ldb=64, ldd=64, sa=0, sb=0, sd=0)
+
+    def call(**kw):
+        a = {**ok, **kw}
+        return can(a["m"], a["n"], a["k"], a["batch"], a["layout"], a["lda"], a["ldb"], a["ldd"], a["sa"], a["sb"], a["sd"])
+
+    assert call() == 0
+    assert call(m=0) == 0 and call(n=0, ldb=1, ldd=1) == 0
+    assert call(m=8) == 0 and call(m=9) == 2
+    assert call(m=-1) == 2 and call(batch=-1) == 2
+    assert call(layout=2) == 2
+    assert call(lda=31) == 2 and call(ldb=63) == 2 and call(ldd=63) == 2
+    assert call(layout=1, ldb=32) == 0 and call(layout=1, ldb=31) == 2      # RCR: ldb >= k
+    assert call(batch=4, sd=0) == 2 and call(batch=4, sd=64) == 0          # overlapping outputs
+    ws = getattr(qlib, GEMV + "_workspace_size")
+    assert ws(1, 14336, 4096, 1, 1) == 0                                    # K-contiguous weights: no scratch
+    assert ws(1, 14336, 4096, 1, 0) > 0                                     # row-major weights: split-K scratch
+    assert ws(0, 14336, 4096, 1, 0) == 0
+
+
+def test_run_rejects_and_empty_without_a_gpu(qlib):
+    run = getattr(qlib, W8A8 + "_run")
+    # empty problem: status 0, nothing launched (no CUDA call is made)
+    assert run(0, 256, 512, None, 512, None, 512, None, 0, None, 256, None, None, 1.0, 0.0, None, 0, None) == 0
+    # null operands on a non-empty problem
+    assert run(128, 256, 512, None, 512, None, 512, None, 0, None, 256, None, None, 1.0, 0.0, None, 0, None) == 2
+    # beta != 0 is not built
+    assert run(128, 256, 512, 0x1000, 512, 0x2000, 512, None, 0, 0x3000, 256, 0x4000, 0x5000, 1.0, 0.5, None, 0, None) == 3
+    assert qlib.baracuda_kernels_q_set_tuning(0, 100) == 2
+    assert qlib.baracuda_kernels_q_set_tuning(0, 0) == 0
+
+
+def test_plan_select_and_sku():
+    desc = bq.QGemmDescriptor(m=128, n=1024, k=1024)
+    p = bq.W8A8GemmPlan.select(None, desc)
+    s = p.sku()
+    assert s.arch is bq.ArchSku.Sm100a and s.backend is bq.BackendKind.Bespoke
+    assert s.layout is bq.LayoutSku.Rcr and s.element is bq.ElementKind.S8 and s.aux_element is bq.ElementKind.Bf16
+    g = p.precision_guarantee()
+    assert g.accumulator is bq.ElementKind.I32 and g.bit_stable_on_same_hardware and g.deterministic
+    # sku is a usable cache key
+    assert {s: 1}[bq.W8A8GemmPlan.select(None, desc).sku()] == 1
+    assert bq.W8A8GemmPlan.select(None, desc, raw_accumulators=True).sku() != s
+    f = bq.Fp8ScaledGemmPlan.select(None, desc, scale_mode=bq.SCALE_PER_ROW_COL)
+    assert f.sku().element is bq.ElementKind.Fp8E4M3 and f.precision_guarantee().accumulator is bq.ElementKind.F32
+    with pytest.raises(bq.Unsupported):
+        bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, layout=bq.LayoutSku.Rrr))
+    with pytest.raises(bq.Unsupported):
+        bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, epilogue=bq.EpilogueKind.BiasRelu))
+    with pytest.raises(bq.Unsupported):
+        bq.W8A8GemmPlan.select(None, desc, bq.PlanPreference(prefer_backend=bq.BackendKind.Cublas))
+    with pytest.raises(bq.InvalidProblem):
+        bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(-1, 1, 1))
+    gv = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(1, 14336, 4096, layout=bq.LayoutSku.Rcr))
+    assert gv.workspace_size() == 0 and gv.sku().layout is bq.LayoutSku.Rcr
+    with pytest.raises(bq.InvalidProblem):
+        bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(9, 64, 64))
+    with pytest.raises(bq.Unsupported):
+        bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(1, 14336, 4096), bq.PlanPreference(max_workspace_bytes=16))
+
+
+def test_typed_layer_refuses_short_buffers():
+    """The typed layer owns buffer-length soundness (gemv_dense.rs:218-268)."""
+    class FakeCuda:
+        """Shape/dtype stand-in so the length checks run without a device."""
+        def __init__(self, n, dtype):
+            self._n, self.dtype, self.is_cuda = n, dtype, True
+        def numel(self):
+            return self._n
+        def data_ptr(self):
+            return 0x10000
+        def element_size(self):
+            return 1
+    p = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(128, 256, 512))
+    good = dict(a=FakeCuda(128 * 512, torch.int8), b=FakeCuda(256 * 512, torch.int8), d=FakeCuda(128 * 256, torch.bfloat16),
+                scale_a=FakeCuda(128, torch.float32), scale_b=FakeCuda(256, torch.float32))
+    p.can_implement(bq.QGemmArgs(**good))
+    with pytest.raises(bq.BufferTooSmall):
+        p.can_implement(bq.QGemmArgs(**{**good, "b": FakeCuda(256 * 512 - 1, torch.int8)}))
+    with pytest.raises(bq.BufferTooSmall):
+        p.can_implement(bq.QGemmArgs(**{**good, "scale_b": FakeCuda(255, torch.float32)}))
+    with pytest.raises(bq.InvalidProblem):
+        p.can_implement(bq.QGemmArgs(**{**good, "d": FakeCuda(128 * 256, torch.float16)}))
+    with pytest.raises(bq.MisalignedOperand):
+        p.can_implement(bq.QGemmArgs(**{**good, "lda": 520}))
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
