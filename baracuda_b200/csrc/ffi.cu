@@ -29,7 +29,7 @@ int32_t gemm_rcr_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_
     if (c != nullptr) return bq::BQ_STATUS_UNSUPPORTED;
     // TMA reads both operands: 16-byte aligned bases and row pitches
     if ((a && !aligned16(a)) || (b && !aligned16(b))) return bq::BQ_STATUS_MISALIGNED;
-    if ((m > 1 && (lda & 15)) || (n > 1 && (ldb & 15))) return bq::BQ_STATUS_MISALIGNED;
+    if (k > 0 && ((m > 1 && (lda & 15)) || (n > 1 && (ldb & 15)))) return bq::BQ_STATUS_MISALIGNED;
     return bq::BQ_STATUS_OK;
 }
 

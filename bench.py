@@ -1,0 +1,415 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-GEMM hot path.
+
+    python bench.py --gpus N --steps K --warmup W            (this library)
+    python bench.py --impl reference --gpus N --steps K ...  (the CPU restatement of the reference, host cores)
+
+Headline workload: the column-parallel FP8 e4m3 GEMM at the 70B-FFN shape
+(M=8192, K=8192, N=28672, per-token x per-channel f32 scales, bf16 out) with
+the weights split evenly by N over the N GPUs (strong scaling, no data-path
+collective; the optional all-gather is timed separately).  A "step" is one
+pass of that GEMM.  With one GPU the same JSON line also carries the decode
+GEMV bandwidth, the 4096^3 W8A8 / FP8 GEMMs, the 128x1024x1024 W8A8 case and
+the 8B-class prefill set under "others".
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+C4_M, C4_K, C4_N = 8192, 8192, 28672
+FLUSH_BYTES = 256 << 20  # larger than the 126 MB L2
+
+
+# --------------------------------------------------------------------------- helpers
+def load_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        import torch
+
+        self.lines: list[str] = []
+        self.proc = None
+        try:
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def event_time_ms(fn, steps: int, warmup: int, flush=None) -> list[float]:
+    """Per-step device times: CUDA events on the current stream around each step, L2 flushed in between."""
+    import torch
+
+    for _ in range(warmup):
+        if flush is not None:
+            flush()
+        fn()
+    torch.cuda.synchronize()
+    pairs = []
+    for _ in range(steps):
+        if flush is not None:
+            flush()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        pairs.append((s, e))
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in pairs]
+
+
+def graph_launch_ms(launchers, replays: int = 20, warmup: int = 3) -> float:
+    """Mean device time per launch of a CUDA graph that holds `launchers` back to back (launch-bound
+    kernels: the graph takes the Python and driver launch cost out of the measurement)."""
+    import torch
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in launchers:
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in launchers:
+            f()
+    for _ in range(warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(replays):
+        graph.replay()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / (replays * len(launchers))
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args, rank: int, world: int) -> None:
+    """The CPU restatement of the reference's oracle, all host threads, on a bounded row sample of the
+    headline configuration (the reference's own Rust interpreter cannot be built here)."""
+    if rank != 0:
+        return
+    import numpy as np
+
+    from oracle import pyoracle as orc
+
+    rows = 8
+    rng = np.random.default_rng(1238)
+    a = rng.integers(0, 0x7E, size=(rows, C4_K), dtype=np.uint8)
+    b = rng.integers(0, 0x7E, size=(C4_N, C4_K), dtype=np.uint8)
+    for _ in range(max(args.warmup, 1)):
+        orc.gemm_e4m3_f32(a[:2], b, orc.RCR, 2, C4_N, C4_K)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.gemm_e4m3_f32(a, b, orc.RCR, rows, C4_N, C4_K)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 2.0 * rows * C4_N * C4_K / dt / 1e12
+    sample = f"{rows} of {C4_M} activation rows x all {C4_N} columns x K={C4_K} per step, f64 accumulate"
+    print(json.dumps({
+        "impl": "reference", "metric": "fp8_gemm_throughput", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (f64 accumulate on the CPU)", "data": "synthetic",
+        "config": {"workload": "c4_fp8_nshard", "M": C4_M, "N": C4_N, "K": C4_K, "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": orc.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------- side workloads (1 GPU)
+def side_workloads(peaks: dict) -> dict:
+    import torch
+
+    import baracuda_b200 as bq
+
+    out = {}
+    flush_buf = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+    flush = lambda: flush_buf.zero_()
+
+    # decode GEMV: K=4096, N=14336, m in {1,2,4,8}; a different weight buffer every launch (6 x 56 MiB > L2)
+    n, k, nbuf = 14336, 4096, 6
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1235)
+    for layout in (bq.LayoutSku.Rcr, bq.LayoutSku.Rrr):
+        weights = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device="cuda", generator=g) for _ in range(nbuf)]
+        for m in (1, 2, 4, 8):
+            x = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda", generator=g)
+            sa = torch.rand(m, device="cuda", generator=g)
+            sb = torch.rand(n, device="cuda", generator=g)
+            d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+            plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=layout))
+            ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+            argl = [bq.GemvQ8Args(a=x, b=w, d=d, scale_a=sa, scale_b=sb) for w in weights]
+            # 12 launches per graph, each on the next weight buffer, replayed 20 times
+            launchers = [(lambda i=i: plan.run(None, ws, argl[i % nbuf])) for i in range(2 * nbuf)]
+            t = graph_launch_ms(launchers) * 1e-3
+            byts = k * n + m * k + m * 4 + n * 4 + m * n * 2
+            out[f"gemv_{layout.value}_m{m}"] = {
+                "us": t * 1e6, "GBps": byts / t / 1e9, "algorithmic_bytes": byts,
+                "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"], "peak": f"{peaks['hbm_gbs']} GB/s of {peaks['source']}"}
+        del weights
+
+    def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False):
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(m + n + k)
+        if kind == "s8":
+            a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
+            b = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=gen)
+            plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k))
+        else:
+            a = torch.randn(m, k, device="cuda", generator=gen).to(torch.float8_e4m3fn).view(torch.uint8)
+            b = (torch.randn(n, k, device="cuda", generator=gen) * 0.02).clamp_(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+            plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), scale_mode=bq.SCALE_PER_ROW_COL)
+        sa = torch.rand(m, device="cuda", generator=gen)
+        sb = torch.rand(n, device="cuda", generator=gen)
+        d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        args = bq.QGemmArgs(a=a, b=b, d=d, scale_a=sa, scale_b=sb)
+        if graph:  # launch-latency-bound shape: time a CUDA graph of 8 launches, operands stay in L2
+            t = graph_launch_ms([lambda: plan.run(None, None, args)] * 8) * 1e-3
+        else:
+            ms = event_time_ms(lambda: plan.run(None, None, args), steps=steps, warmup=3, flush=flush)
+            t = statistics.median(ms) * 1e-3
+        tops = 2.0 * m * n * k / t / 1e12
+        return {"us": t * 1e6, "TOPS": tops, "frac_of_2x_bf16_peak": tops / (2 * peaks["bf16_tflops"]),
+                "frac_of_nominal_4500": tops / 4500.0}
+
+    out["w8a8_4096x4096x4096"] = gemm("s8", 4096, 4096, 4096)
+    out["fp8_4096x4096x4096"] = gemm("fp8", 4096, 4096, 4096)
+    out["w8a8_128x1024x1024"] = gemm("s8", 128, 1024, 1024, graph=True)
+    prefill = {}
+    for m in (512, 2048, 8192):
+        tot_ops, tot_t = 0.0, 0.0
+        for name, (kk, nn) in {"qkv": (4096, 6144), "o": (4096, 4096), "gate_up": (4096, 28672), "down": (14336, 4096)}.items():
+            r = gemm("s8", m, nn, kk, steps=5)
+            prefill[f"M{m}_{name}"] = r
+            tot_ops += 2.0 * m * nn * kk
+            tot_t += r["us"] * 1e-6
+        prefill[f"M{m}_layer_TOPS"] = tot_ops / tot_t / 1e12
+    out["prefill_w8a8"] = prefill
+    return out
+
+
+def cpu_baseline_sample() -> dict:
+    import numpy as np
+
+    from oracle import pyoracle as orc
+
+    rng = np.random.default_rng(1238)
+    b = rng.integers(0, 0x7E, size=(C4_N, C4_K), dtype=np.uint8)
+    a = rng.integers(0, 0x7E, size=(4, C4_K), dtype=np.uint8)
+    t0 = time.perf_counter()
+    orc.gemm_e4m3_f32(a, b, orc.RCR, 4, C4_N, C4_K)
+    probe = time.perf_counter() - t0
+    rows = int(max(4, min(256, 4 * (12.0 / max(probe, 1e-3)) // 4 * 4)))
+    a = rng.integers(0, 0x7E, size=(rows, C4_K), dtype=np.uint8)
+    t0 = time.perf_counter()
+    orc.gemm_e4m3_f32(a, b, orc.RCR, rows, C4_N, C4_K)
+    dt = time.perf_counter() - t0
+    return {"value": 2.0 * rows * C4_N * C4_K / dt / 1e12, "unit": "TFLOP/s", "cores": orc.num_threads(), "kind": "port",
+            "sample": f"{rows} of {C4_M} activation rows x all {C4_N} columns x K={C4_K}, one pass, {dt:.1f} s, f64 accumulate"}
+
+
+# --------------------------------------------------------------------------- headline
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-others", action="store_true", help="skip the side workloads and the CPU baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import baracuda_b200 as bq
+    from baracuda_b200 import synth
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = load_peaks()
+    if C4_N % world:
+        raise SystemExit("N must divide evenly over the GPUs")
+    n_local = C4_N // world
+
+    # seeded inputs: activations N(0,1) per-token e4m3 (replicated), this rank's weight rows N(0,0.02) per-channel e4m3
+    a_q, sa = synth.quantize_rows_e4m3(synth.normal((C4_M, C4_K), 1.0, seed=1238, device="cuda"))
+    w_q, sb = synth.quantize_rows_e4m3(synth.normal((n_local, C4_K), 0.02, seed=2000 + rank, device="cuda"))
+    d = torch.empty((C4_M, n_local), dtype=torch.bfloat16, device="cuda")
+    plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(C4_M, n_local, C4_K), scale_mode=bq.SCALE_PER_ROW_COL)
+    run_args = bq.QGemmArgs(a=a_q, b=w_q, d=d, scale_a=sa, scale_b=sb)
+    flush_buf = torch.empty(FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+    flush = lambda: flush_buf.zero_()
+    step = lambda: plan.run(None, None, run_args)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = event_time_ms(step, steps=args.steps, warmup=args.warmup, flush=flush)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    status = bq.device_status()
+    total_ms = max_over_ranks(sum(ms))
+    ops_total = 2.0 * C4_M * C4_N * C4_K
+    value = ops_total * args.steps / (total_ms * 1e-3) / 1e12
+    launch_ms = statistics.mean(ms)
+    achieved = 2.0 * C4_M * n_local * C4_K / (launch_ms * 1e-3) / 1e12
+
+    # ---- end to end through the Plan API with host buffers (activations and scales in, result out, weights resident)
+    a_host = a_q.cpu().pin_memory()
+    sa_host = sa.cpu().pin_memory()
+    d_host = torch.empty((C4_M, n_local), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        a_q.copy_(a_host, non_blocking=True)
+        sa.copy_(sa_host, non_blocking=True)
+        plan.run(None, None, run_args)
+        d_host.copy_(d, non_blocking=True)
+
+    barrier()
+    e2e_steps = max(3, min(args.steps, 10))
+    e2e_ms = event_time_ms(e2e_step, steps=e2e_steps, warmup=2)
+    barrier()
+    e2e_total = max_over_ranks(sum(e2e_ms))
+    e2e_value = ops_total * e2e_steps / (e2e_total * 1e-3) / 1e12
+
+    others = {}
+    if world > 1:
+        # the optional replicated output: NCCL all-gather of the bf16 slices, rank-major [G, M, N/G]
+        full = torch.empty((world, C4_M, n_local), dtype=torch.bfloat16, device="cuda")
+
+        def gathered_step():
+            plan.run(None, None, run_args)
+            dist.all_gather_into_tensor(full, d)
+
+        barrier()
+        g_ms = event_time_ms(gathered_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+        barrier()
+        g_total = max_over_ranks(sum(g_ms))
+        others["with_nccl_all_gather"] = {
+            "TFLOPs": ops_total * len(g_ms) / (g_total * 1e-3) / 1e12, "ms_per_step": g_total / len(g_ms),
+            "gathered_bytes": C4_M * C4_N * 2, "layout": "rank-major [G, M, N/G]"}
+
+    cpu_base = None
+    if world == 1 and not args.no_others:
+        others.update(side_workloads(peaks))
+        cpu_base = cpu_baseline_sample()
+
+    if rank == 0:
+        peak = 2.0 * peaks["bf16_tflops"]
+        line = {
+            "metric": "fp8_gemm_throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (f32 accumulate, bf16 out)", "data": "synthetic",
+            "config": {"workload": "c4_fp8_nshard", "M": C4_M, "N": C4_N, "K": C4_K, "n_per_gpu": n_local,
+                       "parallelism": f"column-parallel, N split over {world} GPU(s), output left sharded",
+                       "l2": "256 MiB buffer written between timed iterations", "scales": "per-token x per-channel f32"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None,
+                         "peak_is": f"2 x bf16 burst of {peaks['source']} peaks (no fp8 entry is measured)",
+                         "frac_of_nominal_4500": achieved / 4500.0},
+            "cpu_baseline": cpu_base,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": int(a_host.numel() + sa_host.numel() * 4),
+                    "d2h_bytes_per_step": int(d_host.numel() * 2),
+                    "note": "activations + activation scales copied in, bf16 result copied out, every step; "
+                            "weights and weight scales stay resident like model parameters"},
+            "gpu_launches": args.steps * world,
+            "clocks": clocks,
+            "device_status": status,
+            "others": others,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
