@@ -157,6 +157,8 @@ class _QGemmPlanBase:
         st = getattr(lib, self._can_symbol)(d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb,
                                             _ptr(args.c), args.ldc, _ptr(args.d), ldd)
         status_to_result(st, type(self).__name__)
+        if d.m == 0 or d.n == 0:
+            return  # empty problem: nothing is read or written
         _need(args.a, _span(d.m, d.k, lda), "a")
         _need(args.b, _span(d.n, d.k, ldb), "b")
         _need(args.d, _span(d.m, d.n, ldd), "d")
@@ -362,7 +364,7 @@ class GemvQ8Plan:
             raise InvalidProblem("negative batch stride")
         last = max(d.batch - 1, 0)
         b_rows, b_cols = (d.k, d.n) if d.layout is LayoutSku.Rrr else (d.n, d.k)
-        if d.batch > 0:
+        if d.batch > 0 and d.m > 0 and d.n > 0:
             _need(args.a, last * args.stride_a + _span(d.m, d.k, lda), "a")
             _need(args.b, last * args.stride_b + _span(b_rows, b_cols, ldb), "b")
             _need(args.d, last * args.stride_d + _span(d.m, d.n, ldd), "d")

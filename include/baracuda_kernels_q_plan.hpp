@@ -1,0 +1,356 @@
+// Typed Plan layer over the flat C ABI, in C++17 — the compiled-language twin
+// of the reference's safe Rust facade (`<Op>Descriptor` / `<Op>Args` /
+// `<Op>Plan::{select, can_implement, workspace_size, run, sku,
+// precision_guarantee}`; crates/baracuda-kernels/src/gemm/int_gemm.rs:48-637,
+// fp8_gemm.rs:36-741, gemv_dense.rs:48-412; vocabulary from
+// crates/baracuda-kernel-vocab/src/{layout,sku,plan}.rs).
+//
+// Header-only; link against libbaracuda_kernels_q.so.  Plans are plain data
+// (descriptor + SKU), `Copy`-like, usable from any thread; `run` launches on
+// the caller's stream and returns a typed error instead of throwing.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <functional>
+#include <limits>
+#include <optional>
+
+#include "baracuda_kernels_q.h"
+
+namespace baracuda {
+
+enum class LayoutSku : uint8_t { Rcr, Rrr };                      // layout.rs:17-34
+enum class ArchSku : uint8_t { Sm80, Sm89, Sm90a, Sm100a };       // layout.rs:43-53 (+ Sm100a)
+enum class EpilogueKind : uint8_t { Identity, Bias, BiasRelu, BiasGelu, BiasSilu };  // layout.rs:69-96
+enum class BackendKind : uint8_t { Bespoke, Cutlass, Cublas };    // sku.rs:123-204 (subset)
+enum class OpCategory : uint8_t { Gemm, Quantization };
+enum class ElementKind : uint8_t { S8, Fp8E4M3, Bf16, F32, I32 };
+enum class MathPrecision : uint8_t { Int8, Fp8E4M3 };
+enum class ScaleMode : int32_t { PerTensor = 0, PerRowCol = 1 };
+
+inline bool requires_bias(EpilogueKind e) { return e != EpilogueKind::Identity; }
+
+// crates/baracuda-cutlass/src/error.rs:23-70
+enum class Error : uint8_t {
+    Ok,
+    Unsupported,
+    InvalidProblem,
+    MisalignedOperand,
+    WorkspaceTooSmall,
+    BufferTooSmall,
+    LaunchFailure,
+};
+
+// status -> Error (error.rs:83-93, int_gemm.rs:640-653)
+inline Error status_to_error(int32_t st) {
+    switch (st) {
+        case 0: return Error::Ok;
+        case 1: return Error::MisalignedOperand;
+        case 2: return Error::InvalidProblem;
+        case 3: return Error::Unsupported;
+        case 4: return Error::WorkspaceTooSmall;
+        default: return Error::LaunchFailure;
+    }
+}
+
+struct PrecisionGuarantee {  // plan.rs:68-86
+    MathPrecision math_precision;
+    ElementKind accumulator;
+    bool bit_stable_on_same_hardware;
+    bool deterministic;
+    bool operator==(const PrecisionGuarantee& o) const {
+        return math_precision == o.math_precision && accumulator == o.accumulator &&
+               bit_stable_on_same_hardware == o.bit_stable_on_same_hardware && deterministic == o.deterministic;
+    }
+};
+
+struct PlanPreference {  // plan.rs:19-57
+    size_t max_workspace_bytes = std::numeric_limits<size_t>::max();
+    bool allow_sm90a = true;
+    std::optional<BackendKind> prefer_backend = std::nullopt;
+};
+
+struct KernelSku {  // sku.rs:259-285
+    OpCategory category;
+    uint16_t op;
+    ElementKind element;
+    std::optional<ElementKind> aux_element;
+    std::optional<LayoutSku> layout;
+    std::optional<EpilogueKind> epilogue;
+    ArchSku arch;
+    BackendKind backend;
+    PrecisionGuarantee precision_guarantee;
+    bool operator==(const KernelSku& o) const {
+        return category == o.category && op == o.op && element == o.element && aux_element == o.aux_element &&
+               layout == o.layout && epilogue == o.epilogue && arch == o.arch && backend == o.backend &&
+               precision_guarantee == o.precision_guarantee;
+    }
+    size_t hash() const {
+        size_t h = static_cast<size_t>(category) * 1315423911u + op;
+        h = h * 31 + static_cast<size_t>(element);
+        h = h * 31 + (aux_element ? 1 + static_cast<size_t>(*aux_element) : 0);
+        h = h * 31 + (layout ? 1 + static_cast<size_t>(*layout) : 0);
+        h = h * 31 + (epilogue ? 1 + static_cast<size_t>(*epilogue) : 0);
+        h = h * 31 + static_cast<size_t>(arch);
+        return h * 31 + static_cast<size_t>(backend);
+    }
+};
+
+constexpr uint16_t OP_W8A8_GEMM = 100;
+constexpr uint16_t OP_FP8_SCALED_GEMM = 101;
+constexpr uint16_t OP_GEMV_Q8 = 102;
+
+// A device view with its length in elements, so the typed layer can refuse a
+// launch that would run off a buffer (the soundness boundary of
+// gemv_dense.rs:218-268).
+template <typename T>
+struct DeviceSpan {
+    T* ptr = nullptr;
+    size_t len = 0;
+};
+
+struct Workspace {  // crates/baracuda-kernels-types/src/plan.rs:26-32
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    static Workspace none() { return {}; }
+};
+
+namespace detail {
+inline size_t span_elems(int64_t rows, int64_t cols, int64_t ld) {
+    return (rows == 0 || cols == 0) ? 0 : static_cast<size_t>((rows - 1) * ld + cols);
+}
+inline bool backend_ok(const PlanPreference& p) {
+    return !p.prefer_backend || *p.prefer_backend == BackendKind::Bespoke;
+}
+}  // namespace detail
+
+// ---------------------------------------------------------------------------- GEMM
+struct QGemmDescriptor {  // IntGemmDescriptor, crates/baracuda-cutlass/src/types.rs:187-198
+    int32_t m = 0, n = 0, k = 0;
+    LayoutSku layout = LayoutSku::Rcr;
+    EpilogueKind epilogue = EpilogueKind::Identity;
+};
+
+struct QGemmArgs {
+    DeviceSpan<const void> a;   // [M,K] bytes, row pitch lda
+    int64_t lda = 0;
+    DeviceSpan<const void> b;   // weight stored [N,K] bytes, row pitch ldb
+    int64_t ldb = 0;
+    DeviceSpan<void> d;         // [M,N] elements of the plan's output type, row pitch ldd
+    int64_t ldd = 0;
+    DeviceSpan<const float> scale_a;
+    DeviceSpan<const float> scale_b;
+    float alpha = 1.0f;
+    float beta = 0.0f;
+};
+
+class W8A8GemmPlan {
+  public:
+    // Validates once and fixes the SKU.  `raw_accumulators` selects the int32-out symbol.
+    static Error select(const QGemmDescriptor& desc, const PlanPreference& pref, bool raw_accumulators,
+                        W8A8GemmPlan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
+        if (desc.layout != LayoutSku::Rcr || desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
+        out->desc_ = desc;
+        out->raw_ = raw_accumulators;
+        out->sku_ = KernelSku{OpCategory::Gemm, OP_W8A8_GEMM, ElementKind::S8,
+                              raw_accumulators ? ElementKind::I32 : ElementKind::Bf16, desc.layout, desc.epilogue,
+                              ArchSku::Sm100a, BackendKind::Bespoke,
+                              PrecisionGuarantee{MathPrecision::Int8, ElementKind::I32, true, true}};
+        return Error::Ok;
+    }
+    const KernelSku& sku() const { return sku_; }
+    PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
+    const QGemmDescriptor& descriptor() const { return desc_; }
+    size_t workspace_size() const {
+        return raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size(desc_.m, desc_.n, desc_.k)
+                    : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
+    }
+    Error can_implement(const QGemmArgs& x) const {
+        const int32_t st =
+            raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda,
+                                                                         x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd)
+                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
+                       desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
+        if (st != 0) return status_to_error(st);
+        if (desc_.m == 0 || desc_.n == 0) return Error::Ok;  // empty problem: nothing is read or written
+        if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
+        if (x.b.len < detail::span_elems(desc_.n, desc_.k, x.ldb)) return Error::BufferTooSmall;
+        if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
+        if (!raw_) {
+            if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
+            if (x.scale_a.len < static_cast<size_t>(desc_.m) || x.scale_b.len < static_cast<size_t>(desc_.n))
+                return Error::BufferTooSmall;
+        }
+        return Error::Ok;
+    }
+    Error run(void* stream, Workspace ws, const QGemmArgs& x) const {
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        const int32_t st =
+            raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb,
+                                                               nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta, ws.ptr,
+                                                               ws.bytes, stream)
+                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
+                       desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd,
+                       x.scale_a.ptr, x.scale_b.ptr, x.alpha, x.beta, ws.ptr, ws.bytes, stream);
+        return status_to_error(st);
+    }
+
+  private:
+    QGemmDescriptor desc_{};
+    KernelSku sku_{};
+    bool raw_ = false;
+};
+
+class Fp8ScaledGemmPlan {
+  public:
+    static Error select(const QGemmDescriptor& desc, const PlanPreference& pref, ScaleMode mode, bool raw_accumulators,
+                        Fp8ScaledGemmPlan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
+        if (desc.layout != LayoutSku::Rcr || desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
+        out->desc_ = desc;
+        out->raw_ = raw_accumulators;
+        out->mode_ = mode;
+        out->sku_ = KernelSku{OpCategory::Gemm, OP_FP8_SCALED_GEMM, ElementKind::Fp8E4M3,
+                              raw_accumulators ? ElementKind::F32 : ElementKind::Bf16, desc.layout, desc.epilogue,
+                              ArchSku::Sm100a, BackendKind::Bespoke,
+                              PrecisionGuarantee{MathPrecision::Fp8E4M3, ElementKind::F32, true, true}};
+        return Error::Ok;
+    }
+    const KernelSku& sku() const { return sku_; }
+    PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
+    size_t workspace_size() const {
+        return baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
+    }
+    Error can_implement(const QGemmArgs& x) const {
+        const int32_t st = baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement(
+            desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
+        if (st != 0) return status_to_error(st);
+        if (desc_.m == 0 || desc_.n == 0) return Error::Ok;  // empty problem: nothing is read or written
+        if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
+        if (x.b.len < detail::span_elems(desc_.n, desc_.k, x.ldb)) return Error::BufferTooSmall;
+        if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
+        if (!raw_) {
+            if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
+            const size_t na = mode_ == ScaleMode::PerRowCol ? static_cast<size_t>(desc_.m) : 1;
+            const size_t nb = mode_ == ScaleMode::PerRowCol ? static_cast<size_t>(desc_.n) : 1;
+            if (x.scale_a.len < na || x.scale_b.len < nb) return Error::BufferTooSmall;
+        }
+        return Error::Ok;
+    }
+    Error run(void* stream, Workspace ws, const QGemmArgs& x) const {
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        const int32_t st =
+            raw_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr,
+                                                                     x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta,
+                                                                     ws.ptr, ws.bytes, stream)
+                 : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
+                       desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd,
+                       x.scale_a.ptr, x.scale_b.ptr, static_cast<int32_t>(mode_), x.alpha, x.beta, ws.ptr, ws.bytes,
+                       stream);
+        return status_to_error(st);
+    }
+
+  private:
+    QGemmDescriptor desc_{};
+    KernelSku sku_{};
+    ScaleMode mode_ = ScaleMode::PerTensor;
+    bool raw_ = false;
+};
+
+// ---------------------------------------------------------------------------- GEMV
+struct GemvQ8Descriptor {  // GemvDenseDescriptor, gemv_dense.rs:48-75 (m widened to 1..8)
+    int32_t m = 1, n = 0, k = 0, batch = 1;
+    LayoutSku layout = LayoutSku::Rrr;
+};
+
+struct GemvQ8Args {  // GemvDenseArgs, gemv_dense.rs:77-110, plus the scale vectors
+    DeviceSpan<const int8_t> a;
+    int64_t lda = 0, stride_a = 0;
+    DeviceSpan<const int8_t> b;
+    int64_t ldb = 0, stride_b = 0;
+    DeviceSpan<const float> scale_a;
+    int64_t stride_scale_a = 0;
+    DeviceSpan<const float> scale_b;
+    int64_t stride_scale_b = 0;
+    DeviceSpan<void> d;  // bf16 elements (or int32 for the raw plan)
+    int64_t ldd = 0, stride_d = 0;
+    float alpha = 1.0f, beta = 0.0f;
+};
+
+class GemvQ8Plan {
+  public:
+    static Error select(const GemvQ8Descriptor& desc, const PlanPreference& pref, bool raw_accumulators,
+                        GemvQ8Plan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.m < 0 || desc.n < 0 || desc.k < 0 || desc.batch < 0 || desc.m > 8) return Error::InvalidProblem;
+        out->desc_ = desc;
+        out->raw_ = raw_accumulators;
+        out->sku_ = KernelSku{OpCategory::Gemm, OP_GEMV_Q8, ElementKind::S8,
+                              raw_accumulators ? ElementKind::I32 : ElementKind::Bf16, desc.layout, std::nullopt,
+                              ArchSku::Sm100a, BackendKind::Bespoke,
+                              PrecisionGuarantee{MathPrecision::Int8, ElementKind::I32, true, true}};
+        if (out->workspace_size() > pref.max_workspace_bytes) return Error::Unsupported;
+        return Error::Ok;
+    }
+    const KernelSku& sku() const { return sku_; }
+    PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
+    int32_t layout_code() const { return desc_.layout == LayoutSku::Rrr ? 0 : 1; }
+    size_t workspace_size() const {
+        return baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k, desc_.batch,
+                                                                      layout_code());
+    }
+    Error can_implement(const GemvQ8Args& x) const {
+        const int32_t st = baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(
+            desc_.m, desc_.n, desc_.k, desc_.batch, layout_code(), x.lda, x.ldb, x.ldd, x.stride_a, x.stride_b,
+            x.stride_d);
+        if (st != 0) return status_to_error(st);
+        if (x.stride_a < 0 || x.stride_b < 0 || x.stride_d < 0) return Error::InvalidProblem;
+        if (desc_.batch == 0 || desc_.m == 0 || desc_.n == 0) return Error::Ok;
+        const int64_t last = desc_.batch - 1;
+        const bool rrr = desc_.layout == LayoutSku::Rrr;
+        if (x.a.len < last * x.stride_a + detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
+        if (x.b.len < last * x.stride_b + detail::span_elems(rrr ? desc_.k : desc_.n, rrr ? desc_.n : desc_.k, x.ldb))
+            return Error::BufferTooSmall;
+        if (x.d.len < last * x.stride_d + detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
+        if (!raw_) {
+            if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
+            if (x.scale_a.len < static_cast<size_t>(last * x.stride_scale_a + desc_.m)) return Error::BufferTooSmall;
+            if (x.scale_b.len < static_cast<size_t>(last * x.stride_scale_b + desc_.n)) return Error::BufferTooSmall;
+        }
+        return Error::Ok;
+    }
+    Error run(void* stream, Workspace ws, const GemvQ8Args& x) const {
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        const int32_t st =
+            raw_ ? baracuda_kernels_gemv_q8_m1_s32_sm100a_run(desc_.m, desc_.n, desc_.k, desc_.batch, layout_code(),
+                                                              x.alpha, x.beta, x.a.ptr, x.lda, x.stride_a, x.b.ptr, x.ldb,
+                                                              x.stride_b, x.d.ptr, x.ldd, x.stride_d, ws.ptr, ws.bytes,
+                                                              stream)
+                 : baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
+                       desc_.m, desc_.n, desc_.k, desc_.batch, layout_code(), x.alpha, x.beta, x.a.ptr, x.lda, x.stride_a,
+                       x.b.ptr, x.ldb, x.stride_b, x.scale_a.ptr, x.stride_scale_a, x.scale_b.ptr, x.stride_scale_b,
+                       x.d.ptr, x.ldd, x.stride_d, ws.ptr, ws.bytes, stream);
+        return status_to_error(st);
+    }
+
+  private:
+    GemvQ8Descriptor desc_{};
+    KernelSku sku_{};
+    bool raw_ = false;
+};
+
+}  // namespace baracuda
+
+namespace std {
+template <>
+struct hash<baracuda::KernelSku> {
+    size_t operator()(const baracuda::KernelSku& s) const noexcept { return s.hash(); }
+};
+}  // namespace std

@@ -1,0 +1,109 @@
+// Host-only checks of the C++ Plan layer (no GPU work: select / sku / can_implement /
+// workspace_size are pure host functions, and an empty problem returns before any launch).
+#include <cstdio>
+#include <unordered_map>
+
+#include "baracuda_kernels_q_plan.hpp"
+
+using namespace baracuda;
+
+static int failures = 0;
+#define CHECK(cond)                                                          \
+    do {                                                                     \
+        if (!(cond)) {                                                       \
+            std::printf("FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond);    \
+            ++failures;                                                      \
+        }                                                                    \
+    } while (0)
+
+int main() {
+    PlanPreference pref;
+    W8A8GemmPlan p, raw;
+    QGemmDescriptor desc{128, 1024, 1024, LayoutSku::Rcr, EpilogueKind::Identity};
+    CHECK(W8A8GemmPlan::select(desc, pref, false, &p) == Error::Ok);
+    CHECK(W8A8GemmPlan::select(desc, pref, true, &raw) == Error::Ok);
+    CHECK(p.sku().arch == ArchSku::Sm100a && p.sku().backend == BackendKind::Bespoke);
+    CHECK(p.sku().element == ElementKind::S8 && *p.sku().aux_element == ElementKind::Bf16);
+    CHECK(p.precision_guarantee().accumulator == ElementKind::I32 && p.precision_guarantee().deterministic);
+    CHECK(!(p.sku() == raw.sku()));
+    std::unordered_map<KernelSku, int> cache;  // sku() is an autotuner cache key
+    cache[p.sku()] = 1;
+    W8A8GemmPlan again;
+    W8A8GemmPlan::select(desc, pref, false, &again);
+    CHECK(cache.count(again.sku()) == 1 && cache.count(raw.sku()) == 0);
+    CHECK(p.workspace_size() == 0);
+
+    QGemmDescriptor rrr = desc;
+    rrr.layout = LayoutSku::Rrr;
+    CHECK(W8A8GemmPlan::select(rrr, pref, false, &p) == Error::Unsupported);
+    QGemmDescriptor bias = desc;
+    bias.epilogue = EpilogueKind::BiasRelu;
+    CHECK(W8A8GemmPlan::select(bias, pref, false, &p) == Error::Unsupported);
+    PlanPreference cublas;
+    cublas.prefer_backend = BackendKind::Cublas;
+    CHECK(W8A8GemmPlan::select(desc, cublas, false, &p) == Error::Unsupported);
+    QGemmDescriptor neg = desc;
+    neg.m = -1;
+    CHECK(W8A8GemmPlan::select(neg, pref, false, &p) == Error::InvalidProblem);
+
+    CHECK(W8A8GemmPlan::select(desc, pref, false, &p) == Error::Ok);
+    auto fake = [](uintptr_t addr) { return reinterpret_cast<void*>(addr); };
+    QGemmArgs x;
+    x.a = {fake(0x10000), 128u * 1024u};
+    x.lda = 1024;
+    x.b = {fake(0x200000), 1024u * 1024u};
+    x.ldb = 1024;
+    x.d = {fake(0x400000), 128u * 1024u};
+    x.ldd = 1024;
+    x.scale_a = {static_cast<const float*>(fake(0x500000)), 128};
+    x.scale_b = {static_cast<const float*>(fake(0x600000)), 1024};
+    CHECK(p.can_implement(x) == Error::Ok);
+    QGemmArgs y = x;
+    y.b.len -= 1;
+    CHECK(p.can_implement(y) == Error::BufferTooSmall);
+    y = x;
+    y.lda = 1000;
+    CHECK(p.can_implement(y) == Error::InvalidProblem);
+    y = x;
+    y.lda = 1032;
+    y.a.len = 128u * 1032u;
+    CHECK(p.can_implement(y) == Error::MisalignedOperand);
+    y = x;
+    y.scale_b.len = 1023;
+    CHECK(p.can_implement(y) == Error::BufferTooSmall);
+
+    Fp8ScaledGemmPlan f;
+    CHECK(Fp8ScaledGemmPlan::select(desc, pref, ScaleMode::PerTensor, false, &f) == Error::Ok);
+    CHECK(f.sku().element == ElementKind::Fp8E4M3 && f.precision_guarantee().accumulator == ElementKind::F32);
+    y = x;
+    y.scale_a.len = 1;
+    y.scale_b.len = 1;
+    CHECK(f.can_implement(y) == Error::Ok);  // per-tensor scales are single floats
+
+    GemvQ8Plan g;
+    GemvQ8Descriptor gd{1, 14336, 4096, 1, LayoutSku::Rcr};
+    CHECK(GemvQ8Plan::select(gd, pref, false, &g) == Error::Ok);
+    CHECK(g.workspace_size() == 0);
+    gd.layout = LayoutSku::Rrr;
+    CHECK(GemvQ8Plan::select(gd, pref, false, &g) == Error::Ok);
+    CHECK(g.workspace_size() > 0);
+    PlanPreference tiny;
+    tiny.max_workspace_bytes = 16;
+    CHECK(GemvQ8Plan::select(gd, tiny, false, &g) == Error::Unsupported);
+    gd.m = 9;
+    CHECK(GemvQ8Plan::select(gd, pref, false, &g) == Error::InvalidProblem);
+
+    // an empty problem runs to status 0 without touching the device
+    W8A8GemmPlan e;
+    CHECK(W8A8GemmPlan::select(QGemmDescriptor{0, 16, 16}, pref, false, &e) == Error::Ok);
+    QGemmArgs ex;
+    ex.lda = 16;
+    ex.ldb = 16;
+    ex.ldd = 16;
+    ex.scale_a = {static_cast<const float*>(fake(0x500000)), 0};
+    ex.scale_b = {static_cast<const float*>(fake(0x600000)), 16};
+    CHECK(e.run(nullptr, Workspace::none(), ex) == Error::Ok);
+
+    if (failures == 0) std::printf("plan_host_test ok\n");
+    return failures == 0 ? 0 : 1;
+}

@@ -142,3 +142,16 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.load()
+
+
+def test_cpp_plan_layer(qlib, tmp_path):
+    """Compiles and runs the host-only checks of include/baracuda_kernels_q_plan.hpp against the library."""
+    import subprocess
+
+    exe = tmp_path / "plan_host_test"
+    libdir = _lib.LIB_PATH.parent
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", str(ROOT / "include"), str(ROOT / "tests" / "cpp" / "plan_host_test.cpp"),
+                    "-o", str(exe), "-L", str(libdir), "-lbaracuda_kernels_q", f"-Wl,-rpath,{libdir}"], check=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "plan_host_test ok" in res.stdout
