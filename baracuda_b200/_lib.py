@@ -42,6 +42,17 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size": _GEMV_WS,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run": (
+        _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _f32,
+               _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run": (
+        _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _f32,
+               _vp, _vp, _i64] + _TAIL),
+    "baracuda_q_nccl_version": (_i32, []),
+    "baracuda_q_nccl_unique_id": (_i32, [_vp]),
+    "baracuda_q_nccl_comm_init_rank": (_i32, [C.POINTER(_vp), _i32, _vp, _i32]),
+    "baracuda_q_nccl_comm_destroy": (_i32, [_vp]),
+    "baracuda_q_nccl_stream_barrier": (_i32, [_vp, _vp, _vp]),
     "baracuda_kernels_q_device_status": (_i32, []),
     "baracuda_kernels_q_set_tuning": (_i32, [_i32, _i32]),
 }

@@ -66,6 +66,10 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
     g.d = d;
     g.ldd = ldd;
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.n_peers = 0;
+    g.peer_ld = 0;
+    g.peer_col0 = 0;
+    for (auto& pd : g.peer_d) pd = nullptr;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -127,6 +131,46 @@ int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, in
 }
 
 }  // namespace
+
+int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                                    const void* b, int64_t ldb, void* d, int64_t ldd, const void* scale_a,
+                                    const void* scale_b, int32_t scale_mode, float alpha, void* const* peer_d,
+                                    int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream) {
+    if (!peer_d) {
+        return gemm_rcr_run(kind, 0, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd, scale_a, scale_b, scale_mode, alpha,
+                            0.0f, stream);
+    }
+    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
+    if (!d || (k > 0 && (!a || !b)) || !scale_a || !scale_b) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
+        return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
+    bq::GemmDesc g;
+    g.kind = kind;
+    g.raw_out = 0;
+    g.m = m;
+    g.n = n;
+    g.k = k;
+    g.a = a;
+    g.lda = lda;
+    g.b = b;
+    g.ldb = ldb;
+    g.scale_a = static_cast<const float*>(scale_a);
+    g.scale_b = static_cast<const float*>(scale_b);
+    g.scale_mode = scale_mode;
+    g.alpha = alpha;
+    g.d = d;
+    g.ldd = ldd;
+    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.n_peers = world;
+    g.peer_ld = peer_ld;
+    g.peer_col0 = rank * n;
+    for (int r = 0; r < 8; ++r) g.peer_d[r] = r < world ? peer_d[r] : nullptr;
+    return bq::launch_gemm_q8(g, stream);
+}
 
 extern "C" {
 
@@ -239,12 +283,18 @@ size_t baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size(int32_t m, int32_t 
 }
 
 // ---- diagnostics / tuning -------------------------------------------------------------
-int32_t baracuda_kernels_q_device_status(void) { return bq::read_and_clear_gemm_device_status(); }
+int32_t baracuda_kernels_q_device_status(void) {
+    int32_t gemm = bq::read_and_clear_gemm_device_status();
+    const int32_t pair = bq::read_and_clear_gemm_pair_device_status();
+    if (gemm == 0) gemm = pair;
+    const int32_t gemv = bq::read_and_clear_gemv_device_status();
+    return gemm != 0 ? gemm : gemv;
+}
 
 int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
     switch (key) {
         case 0:
-            if (value != 0 && value != 64 && value != 128 && value != 256) return bq::BQ_STATUS_INVALID_PROBLEM;
+            if (value != 0 && value != 64 && value != 128 && value != 256 && value != 512) return bq::BQ_STATUS_INVALID_PROBLEM;
             g_force_block_n.store(value);
             return bq::BQ_STATUS_OK;
         case 1:

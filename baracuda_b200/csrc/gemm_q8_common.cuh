@@ -1,0 +1,107 @@
+// Pieces shared by the 1-CTA and the 2-CTA tcgen05 GEMM kernels: the kernel
+// parameter block and the epilogue that turns 32 accumulator columns of one
+// output row into bf16 (fused dequant) or raw 32-bit stores.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx_sm100a.cuh"
+
+namespace bq {
+
+struct GemmParams {
+    void* d;
+    int64_t ldd;
+    const float* sa;
+    const float* sb;
+    int scale_mode;  // 0: sa/sb point at one float each; 1: sa[M], sb[N]
+    float alpha;
+    int m, n, k;
+    int m_tiles, n_tiles;
+    int vec_store;  // 1 when d and ldd allow 16-byte row stores
+    // fused replicated output (FUSED kernels only)
+    void* peer_d[8];
+    int n_peers;
+    int64_t peer_ld;
+    int peer_col0;
+    int peer_vec;  // 1 when every peer buffer allows 16-byte row stores at its column offset
+};
+
+// One thread, one output row, 32 consecutive columns starting at col0 (a multiple of 32).
+// `r` holds the accumulators as read from TMEM, `sb32` the 32 column scales.
+template <uint32_t KIND, bool RAW, bool FUSED>
+__device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
+                                                  float sa_row, const float* sb32) {
+    if constexpr (RAW) {
+        uint32_t* drow = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+        if (p.vec_store && col0 + 32 <= p.n) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                reinterpret_cast<uint4*>(drow)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.n) drow[j] = r[j];
+            }
+        }
+    } else {
+        __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+        float y[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float acc;
+            if constexpr (KIND == UMMA_KIND_I8) {
+                acc = static_cast<float>(static_cast<int32_t>(r[j]));
+            } else {
+                acc = __uint_as_float(r[j]);
+            }
+            // (sa*sb) first, then the accumulator, then alpha: the reference's W8A8
+            // product order, no fused multiply-add.
+            const float s = __fmul_rn(sa_row, sb32[j]);
+            y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
+        }
+        uint4 pk[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
+            pk[v].x = *reinterpret_cast<uint32_t*>(&h0);
+            pk[v].y = *reinterpret_cast<uint32_t*>(&h1);
+            pk[v].z = *reinterpret_cast<uint32_t*>(&h2);
+            pk[v].w = *reinterpret_cast<uint32_t*>(&h3);
+        }
+        if (p.vec_store && col0 + 32 <= p.n) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(drow)[v] = pk[v];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.n) drow[j] = __float2bfloat16_rn(y[j]);
+            }
+        }
+        if constexpr (FUSED) {
+            // the replicated output: plain stores into every rank's row-major buffer
+            // (peer-mapped memory), at this rank's column offset
+            for (int pr = 0; pr < p.n_peers; ++pr) {
+                __nv_bfloat16* prow = reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
+                                      static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0;
+                if (p.peer_vec && col0 + 32 <= p.n) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) reinterpret_cast<uint4*>(prow)[v] = pk[v];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (col0 + j < p.n) prow[j] = __float2bfloat16_rn(y[j]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+}  // namespace bq

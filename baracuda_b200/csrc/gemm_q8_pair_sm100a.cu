@@ -1,0 +1,306 @@
+// 8-bit tensor-core GEMM on CTA pairs (tcgen05 cta_group::2): two SMs of a
+// 2-CTA cluster share every MMA and together own a 256 x 256 output tile.
+// Each CTA streams its own 128 rows of A and its own 128 rows of the weight
+// tile (no operand is loaded twice, no multicast is involved), the leader CTA
+// issues 256 x 256 x 32 MMAs that read both CTAs' shared memory, and each CTA
+// keeps its 128 accumulator rows in its own TMEM.  Compared with the 1-CTA
+// kernel this halves the shared-memory and L2 traffic of the weight operand
+// per MAC and leaves room for a deeper TMA ring (6 stages of 32 KiB per CTA).
+//
+// Same roles per CTA as the 1-CTA kernel (warp 0 TMA producer, warp 1 TMEM
+// owner / MMA issuer on the leader, warps 2-5 epilogue), same double-buffered
+// accumulator, same bounded waits.  Serves the same C symbols; replaces the
+// same reference kernels as gemm_q8_sm100a.cu.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "gemm_q8_common.cuh"
+#include "launch.h"
+#include "ptx_sm100a.cuh"
+
+namespace bq {
+
+__device__ int g_gemm_pair_device_status = 0;
+
+namespace {
+
+constexpr int PAIR_TILE_M = 256;   // rows per CTA pair
+constexpr int PAIR_TILE_N = 256;   // columns per CTA pair
+constexpr int CTA_ROWS = 128;      // A rows and weight rows each CTA loads
+constexpr int PAIR_BLOCK_K = 128;  // bytes of K per stage
+constexpr int PAIR_UMMA_K = 32;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_THREADS = 192;
+constexpr int PAIR_A_BYTES = CTA_ROWS * PAIR_BLOCK_K;
+constexpr int PAIR_B_BYTES = CTA_ROWS * PAIR_BLOCK_K;
+constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_TILE_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES;
+constexpr int PAIR_SB_BYTES = 4 * PAIR_TILE_N * 4;
+constexpr int PAIR_BAR_BYTES = (2 * PAIR_STAGES + 4) * 8 + 16;
+constexpr int PAIR_SMEM_TOTAL = PAIR_TILE_BYTES + PAIR_SB_BYTES + PAIR_BAR_BYTES + 1024;
+constexpr int PAIR_TMEM_COLS = 512;
+constexpr long long PAIR_WAIT_LIMIT = 1LL << 31;
+
+__device__ __forceinline__ void pair_timeout(volatile uint32_t* abort_word, int code) {
+    *abort_word = 1u;
+    atomicCAS(&g_gemm_pair_device_status, 0, code);
+}
+
+template <uint32_t KIND, bool RAW, bool FUSED>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    float* sb_s = reinterpret_cast<float*>(smem + PAIR_TILE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + PAIR_TILE_BYTES + PAIR_SB_BYTES);
+    uint64_t* empty_bar = full_bar + PAIR_STAGES;
+    uint64_t* tfull_bar = empty_bar + PAIR_STAGES;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = leader (issues the MMAs), 1 = partner
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);   // the leader producer's arrive + both CTAs' TMA bytes
+            mbar_init(&empty_bar[s], 1);  // one commit arrival from the leader's MMA thread
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tfull_bar[b], 1);   // one commit arrival
+            mbar_init(&tempty_bar[b], 8);  // one arrival per epilogue warp of both CTAs (leader's copy is used)
+        }
+        *abort_word = 0u;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, PAIR_TMEM_COLS);
+        tmem_relinquish_alloc_permit_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_kb = (p.k + PAIR_BLOCK_K - 1) / PAIR_BLOCK_K;
+    const int total_tiles = p.m_tiles * p.n_tiles;  // counted in 256 x 256 pair tiles
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
+                const int m_blk = tile % p.m_tiles;
+                const int n_blk = tile / p.m_tiles;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, PAIR_WAIT_LIMIT)) {
+                        pair_timeout(abort_word, 111);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* a_tile = tiles + stage * PAIR_STAGE_BYTES;
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * PAIR_STAGE_BYTES);
+                    // completion bytes of both CTAs' loads are counted on the leader's barrier
+                    const uint32_t full_on_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                    tma_load_2d_pair(a_tile, &tmap_a, full_on_leader, kb * PAIR_BLOCK_K,
+                                     m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS);
+                    tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
+                                     n_blk * PAIR_TILE_N + static_cast<int>(rank) * CTA_ROWS);
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc(KIND, PAIR_TILE_M, PAIR_TILE_N);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs, ++it) {
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait_bounded(&tempty_bar[buf], acc_phase ^ 1u, abort_word, PAIR_WAIT_LIMIT)) {
+                    pair_timeout(abort_word, 112);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * PAIR_TILE_N);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait_bounded(&full_bar[stage], phase, abort_word, PAIR_WAIT_LIMIT)) {
+                        pair_timeout(abort_word, 113);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = smem_u32(tiles + stage * PAIR_STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + PAIR_A_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < PAIR_BLOCK_K / PAIR_UMMA_K; ++ks) {
+                        const uint64_t koff = static_cast<uint64_t>((ks * PAIR_UMMA_K) >> 4);
+                        umma_ss_pair<KIND>(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(&empty_bar[stage], 0x3);  // frees this stage in both CTAs
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) umma_commit_pair(&tfull_bar[buf], 0x3);  // accumulator ready, both CTAs' epilogues
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int it = 0;
+        for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++it) {
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            const int m_blk = tile % p.m_tiles;
+            const int n_blk = tile / p.m_tiles;
+            float* sb_tile = sb_s + (warp - 2) * PAIR_TILE_N;
+            if constexpr (!RAW) {
+                __syncwarp();
+                for (int i = lane; i < PAIR_TILE_N; i += 32) {
+                    const int col = n_blk * PAIR_TILE_N + i;
+                    sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                }
+                __syncwarp();
+            }
+            if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, PAIR_WAIT_LIMIT)) {
+                pair_timeout(abort_word, 114);
+                break;
+            }
+            tc_fence_after_sync();
+            const int row = m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32 + lane;
+            const bool row_ok = row < p.m;
+            float sa_row = 1.0f;
+            if constexpr (!RAW) {
+                sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
+            }
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                   static_cast<uint32_t>(buf * PAIR_TILE_N);
+#pragma unroll 1
+            for (int c = 0; c < PAIR_TILE_N / 32; ++c) {
+                const int col0 = n_blk * PAIR_TILE_N + c * 32;
+                if (col0 >= p.n) break;  // warp-uniform
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
+                tmem_ld_wait();
+                if (row_ok) epilogue_store_32<KIND, RAW, FUSED>(p, row, col0, r, sa_row, sb_tile + c * 32);
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+        }
+    }
+
+    // Teardown: nobody leaves (or frees TMEM) while the partner may still signal or read.
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_word != 0u) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, PAIR_TMEM_COLS);
+    }
+}
+
+template <uint32_t KIND, bool RAW, bool FUSED>
+int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
+    const int sms = sm_count_of_current_device();
+    if (sms < 2) return BQ_STATUS_LAUNCH_FAILURE;
+    CUtensorMap map_a, map_b;
+    if (!make_kmajor_tensor_map(&map_a, g.a, g.m, g.k, g.lda, CTA_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
+    if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, CTA_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
+    GemmParams p;
+    p.d = g.d;
+    p.ldd = g.ldd;
+    p.sa = g.scale_a;
+    p.sb = g.scale_b;
+    p.scale_mode = g.scale_mode;
+    p.alpha = g.alpha;
+    p.m = g.m;
+    p.n = g.n;
+    p.k = g.k;
+    p.m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
+    p.n_tiles = (g.n + PAIR_TILE_N - 1) / PAIR_TILE_N;
+    const int64_t elem = RAW ? 4 : 2;
+    p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
+    p.n_peers = FUSED ? g.n_peers : 0;
+    p.peer_ld = g.peer_ld;
+    p.peer_col0 = g.peer_col0;
+    p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
+    for (int r = 0; r < 8; ++r) {
+        p.peer_d[r] = g.peer_d[r];
+        if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
+    }
+    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_TOTAL) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
+    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(PAIR_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PAIR_SMEM_TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, map_a, map_b, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    return BQ_STATUS_OK;
+}
+
+}  // namespace
+
+int32_t launch_gemm_q8_pair(const GemmDesc& g, cudaStream_t stream) {
+    const bool fused = g.n_peers > 0 && !g.raw_out;
+    if (g.kind == BQ_KIND_S8) {
+        if (g.raw_out) return launch_pair<UMMA_KIND_I8, true, false>(g, stream);
+        return fused ? launch_pair<UMMA_KIND_I8, false, true>(g, stream) : launch_pair<UMMA_KIND_I8, false, false>(g, stream);
+    }
+    if (g.raw_out) return launch_pair<UMMA_KIND_F8, true, false>(g, stream);
+    return fused ? launch_pair<UMMA_KIND_F8, false, true>(g, stream) : launch_pair<UMMA_KIND_F8, false, false>(g, stream);
+}
+
+int32_t read_and_clear_gemm_pair_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_pair_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        int zero = 0;
+        (void)cudaMemcpyToSymbol(g_gemm_pair_device_status, &zero, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace bq

@@ -25,6 +25,7 @@
 
 #include <mutex>
 
+#include "gemm_q8_common.cuh"
 #include "launch.h"
 #include "ptx_sm100a.cuh"
 
@@ -41,17 +42,6 @@ constexpr int GEMM_THREADS = 192;
 constexpr int EPI_THREADS = 128;
 constexpr long long WAIT_LIMIT_CYCLES = 1LL << 31;  // about a second
 
-struct GemmParams {
-    void* d;
-    int64_t ldd;
-    const float* sa;
-    const float* sb;
-    int scale_mode;  // 0: sa/sb point at one float each; 1: sa[M], sb[N]
-    float alpha;
-    int m, n, k;
-    int m_tiles, n_tiles;
-    int vec_store;  // 1 when d and ldd allow 16-byte row stores
-};
 
 template <int BLOCK_N, int STAGES>
 struct Smem {
@@ -71,7 +61,7 @@ __device__ __forceinline__ void record_timeout(volatile uint32_t* abort_word, in
     atomicCAS(&g_gemm_device_status, 0, code);
 }
 
-template <uint32_t KIND, bool RAW, int BLOCK_N, int STAGES>
+template <uint32_t KIND, bool RAW, int BLOCK_N, int STAGES, bool FUSED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const GemmParams p) {
@@ -223,60 +213,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 __syncwarp();
                 tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
                 tmem_ld_wait();
-                if (!row_ok) {
-                    // rows past M hold zero-filled padding; nothing to store
-                } else if constexpr (RAW) {
-                    uint32_t* drow = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
-                    if (p.vec_store && col0 + 32 <= p.n) {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            reinterpret_cast<uint4*>(drow)[v] =
-                                make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (col0 + j < p.n) drow[j] = r[j];
-                        }
-                    }
-                } else {
-                    __nv_bfloat16* drow =
-                        reinterpret_cast<__nv_bfloat16*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
-                    float y[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float acc;
-                        if constexpr (KIND == UMMA_KIND_I8) {
-                            acc = static_cast<float>(static_cast<int32_t>(r[j]));
-                        } else {
-                            acc = __uint_as_float(r[j]);
-                        }
-                        // (sa*sb) first, then the accumulator, then alpha: the
-                        // reference's W8A8 product order, no fused multiply-add.
-                        const float s = __fmul_rn(sa_row, sb_tile[c * 32 + j]);
-                        y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
-                    }
-                    if (p.vec_store && col0 + 32 <= p.n) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]);
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]);
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
-                            uint4 pk;
-                            pk.x = *reinterpret_cast<uint32_t*>(&h0);
-                            pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                            pk.z = *reinterpret_cast<uint32_t*>(&h2);
-                            pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                            reinterpret_cast<uint4*>(drow)[v] = pk;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            if (col0 + j < p.n) drow[j] = __float2bfloat16_rn(y[j]);
-                        }
-                    }
-                }
+                if (row_ok) epilogue_store_32<KIND, RAW, FUSED>(p, row, col0, r, sa_row, sb_tile + c * 32);
             }
             tc_fence_before_sync();
             mbar_arrive(&tempty_bar[buf]);
@@ -337,7 +274,7 @@ bool make_kmajor_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k
     return r == CUDA_SUCCESS;
 }
 
-int sm_count_of_current_device() {
+int sm_count_impl() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     static std::mutex mu;
@@ -350,7 +287,7 @@ int sm_count_of_current_device() {
     return n;
 }
 
-template <uint32_t KIND, bool RAW, int BLOCK_N, int STAGES>
+template <uint32_t KIND, bool RAW, int BLOCK_N, int STAGES, bool FUSED = false>
 int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     using L = Smem<BLOCK_N, STAGES>;
     CUtensorMap map_a, map_b;
@@ -370,7 +307,15 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.n_tiles = (g.n + BLOCK_N - 1) / BLOCK_N;
     const int64_t elem = RAW ? 4 : 2;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
-    auto kern = gemm_q8_kernel<KIND, RAW, BLOCK_N, STAGES>;
+    p.n_peers = FUSED ? g.n_peers : 0;
+    p.peer_ld = g.peer_ld;
+    p.peer_col0 = g.peer_col0;
+    p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
+    for (int r = 0; r < 8; ++r) {
+        p.peer_d[r] = g.peer_d[r];
+        if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
+    }
+    auto kern = gemm_q8_kernel<KIND, RAW, BLOCK_N, STAGES, FUSED>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -383,14 +328,29 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
 
 template <uint32_t KIND, bool RAW>
 int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
-    const int sms = sm_count_of_current_device();
+    const int sms = sm_count_impl();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
+    // large problems: 256 x 256 tiles on CTA pairs (force_block_n 512 forces it, 256/128/64 forces it off)
+    if ((g.force_block_n == 0 && g.m >= 512 && g.n >= 512 && m_tiles * ((g.n + 255) / 256) >= sms) ||
+        g.force_block_n == 512) {
+        return launch_gemm_q8_pair(g, stream);
+    }
     int bn = g.force_block_n;
     if (bn == 0) {
         // the widest tile that still gives every SM a tile; narrow tiles for small problems
         bn = tiles_at(256) >= sms ? 256 : (tiles_at(128) >= sms ? 128 : 64);
+    }
+    if constexpr (!RAW) {
+        if (g.n_peers > 0) {
+            switch (bn) {
+                case 256: return launch_config<KIND, RAW, 256, 4, true>(g, sms, stream);
+                case 128: return launch_config<KIND, RAW, 128, 6, true>(g, sms, stream);
+                case 64: return launch_config<KIND, RAW, 64, 8, true>(g, sms, stream);
+                default: return BQ_STATUS_INVALID_PROBLEM;
+            }
+        }
     }
     switch (bn) {
         case 256: return launch_config<KIND, RAW, 256, 4>(g, sms, stream);
@@ -418,6 +378,12 @@ int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
         return g.raw_out ? launch_kind<UMMA_KIND_I8, true>(g, stream) : launch_kind<UMMA_KIND_I8, false>(g, stream);
     }
     return g.raw_out ? launch_kind<UMMA_KIND_F8, true>(g, stream) : launch_kind<UMMA_KIND_F8, false>(g, stream);
+}
+
+int sm_count_of_current_device() { return sm_count_impl(); }
+
+bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
+    return make_kmajor_map(static_cast<CUtensorMap*>(map_out), base, rows, k, ld, box_rows);
 }
 
 int32_t read_and_clear_gemm_device_status() {

@@ -15,8 +15,12 @@
 #include <cuda_runtime.h>
 
 #include "launch.h"
+#include "ptx_sm100a.cuh"
 
 namespace bq {
+
+__device__ int g_gemv_device_status = 0;
+
 namespace {
 
 constexpr int GEMV_THREADS = 256;
@@ -146,6 +150,168 @@ gemv_q8_rcr_kernel(const GemvParams p) {
             const int col = col_base + c;
             if (lane == ((c * MR + r) & 31) && col < p.n) store_result<RAW>(p, g, r, col, v);
         }
+    }
+}
+
+// ---- weights stored [N, K], bulk-copy fed: one persistent CTA per SM.  A producer
+// warp streams whole weight rows (up to 4 KiB of K per copy) into a shared-memory
+// ring with cp.async.bulk, eight consumer warps each take a row from the ring, dot it
+// with the activations held in registers (dp4a) and fold the 32 lane sums with
+// shuffles.  The copies keep ~100 KiB per SM in flight no matter how the consumers
+// are scheduled, which is what a 9 us HBM-bound kernel needs. ----
+constexpr int STREAM_CHUNK = 4096;   // bytes of K per ring slot
+constexpr int STREAM_SLOTS = 26;     // 104 KiB of weights in flight per SM
+constexpr long long STREAM_WAIT_LIMIT = 1LL << 31;
+
+// STREAM_CONSUMERS consumer warps + 1 producer warp; more activation rows need more registers per
+// thread (the activations live in registers), hence fewer consumer warps.
+template <int MR, bool RAW, int STREAM_CONSUMERS>
+__global__ void __launch_bounds__((STREAM_CONSUMERS + 1) * 32, 1)
+gemv_q8_rcr_stream_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t stream_smem[];
+    uint8_t* ring = stream_smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(stream_smem + STREAM_SLOTS * STREAM_CHUNK);
+    uint64_t* empty_bar = full_bar + STREAM_SLOTS;
+    volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(empty_bar + STREAM_SLOTS);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int64_t g = blockIdx.y;
+    const int8_t* a = p.a + g * p.stride_a;
+    const int8_t* b = p.b + g * p.stride_b;
+
+    // this CTA's contiguous share of the output columns
+    const int ctas = gridDim.x;
+    const int base = p.n / ctas, rem = p.n % ctas;
+    const int col_begin = blockIdx.x * base + (static_cast<int>(blockIdx.x) < rem ? static_cast<int>(blockIdx.x) : rem);
+    const int ncols = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
+    const int chunks = (p.k + STREAM_CHUNK - 1) / STREAM_CHUNK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STREAM_SLOTS; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        *abort_word = 0u;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    __syncthreads();
+
+    if (warp == STREAM_CONSUMERS) {
+        if (lane == 0) {
+            const int items = ncols * chunks;
+            for (int i = 0; i < items; ++i) {
+                const int slot = i % STREAM_SLOTS;
+                const uint32_t parity = ((i / STREAM_SLOTS) & 1) ^ 1u;
+                if (!mbar_wait_bounded(&empty_bar[slot], parity, abort_word, STREAM_WAIT_LIMIT)) {
+                    *abort_word = 1u;
+                    atomicCAS(&g_gemv_device_status, 0, 201);
+                    break;
+                }
+                const int j = i / chunks, kc = i - j * chunks;
+                const int k0 = kc * STREAM_CHUNK;
+                const uint32_t bytes = static_cast<uint32_t>((p.k - k0 < STREAM_CHUNK) ? (p.k - k0) : STREAM_CHUNK);
+                mbar_arrive_expect_tx(&full_bar[slot], bytes);
+                bulk_load_1d(ring + slot * STREAM_CHUNK, b + static_cast<int64_t>(col_begin + j) * p.ldb + k0, bytes,
+                             &full_bar[slot]);
+            }
+        }
+    } else {
+        // activations: with a single K chunk every lane keeps its 8 x 16 bytes per row in registers
+        uint4 xr[MR][8];
+        const bool x_in_regs = (chunks == 1);
+        if (x_in_regs) {
+#pragma unroll
+            for (int r = 0; r < MR; ++r)
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const int k16 = s * 32 + lane;
+                    xr[r][s] = (k16 * 16 < p.k)
+                                   ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + k16)
+                                   : make_uint4(0, 0, 0, 0);
+                }
+        }
+        // Each warp parks the finished sum of its i-th column in lane (i mod 32) and writes 32 columns
+        // at a time, so the scale loads and the stores of the epilogue are paid once per batch, in
+        // parallel, instead of once per column on the critical path.
+        int keep[MR];
+#pragma unroll
+        for (int r = 0; r < MR; ++r) keep[r] = 0;
+        bool ok = true;
+        int done = 0;  // columns this warp has finished
+        for (int j = warp; ok && j < ncols; j += STREAM_CONSUMERS) {
+            int acc0[MR], acc1[MR];
+#pragma unroll
+            for (int r = 0; r < MR; ++r) acc0[r] = acc1[r] = 0;
+            for (int kc = 0; kc < chunks; ++kc) {
+                const int i = j * chunks + kc;
+                const int slot = i % STREAM_SLOTS;
+                const uint32_t parity = (i / STREAM_SLOTS) & 1;
+                if (!mbar_wait_bounded(&full_bar[slot], parity, abort_word, STREAM_WAIT_LIMIT)) {
+                    *abort_word = 1u;
+                    atomicCAS(&g_gemv_device_status, 0, 202);
+                    ok = false;
+                    break;
+                }
+                const int k0 = kc * STREAM_CHUNK;
+                const int valid16 = ((p.k - k0 < STREAM_CHUNK) ? (p.k - k0) : STREAM_CHUNK) >> 4;
+                const uint4* wv = reinterpret_cast<const uint4*>(ring + slot * STREAM_CHUNK);
+                uint4 w[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const int k16 = s * 32 + lane;
+                    w[s] = (k16 < valid16) ? wv[k16] : make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[slot]);  // the slot is in registers now
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    const int k16 = s * 32 + lane;
+#pragma unroll
+                    for (int r = 0; r < MR; ++r) {
+                        uint4 x;
+                        if (x_in_regs) {
+                            x = xr[r][s];
+                        } else {
+                            x = (k16 < valid16)
+                                    ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda + k0) + k16)
+                                    : make_uint4(0, 0, 0, 0);
+                        }
+                        if (s & 1) {
+                            acc1[r] = dot16(w[s], x, acc1[r]);
+                        } else {
+                            acc0[r] = dot16(w[s], x, acc0[r]);
+                        }
+                    }
+                }
+            }
+            if (!ok) break;
+#pragma unroll
+            for (int r = 0; r < MR; ++r) {
+                const int v = warp_sum(acc0[r] + acc1[r]);
+                if (lane == (done & 31)) keep[r] = v;
+            }
+            ++done;
+            if ((done & 31) == 0) {
+                const int col = col_begin + warp + (done - 32 + lane) * STREAM_CONSUMERS;
+#pragma unroll
+                for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
+            }
+        }
+        if (ok && (done & 31) != 0) {
+            const int first = done & ~31;
+            if (lane < done - first) {
+                const int col = col_begin + warp + (first + lane) * STREAM_CONSUMERS;
+#pragma unroll
+                for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
+            }
+        }
+    }
+    // leave together; on the error path give copies still in flight a bounded time to land
+    __syncthreads();
+    if (*abort_word != 0u) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
 }
 
@@ -340,6 +506,33 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+int sm_count_cached() {
+    static int cached = 0;
+    if (cached > 0) return cached;
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached = n;  // the GPUs of one box are identical
+    return n;
+}
+
+template <int MR, bool RAW>
+int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    const size_t smem = static_cast<size_t>(STREAM_SLOTS) * STREAM_CHUNK + 2 * STREAM_SLOTS * 8 + 16;
+    constexpr int NC = (MR == 1) ? 16 : 8;
+    constexpr int STREAM_THREADS = (NC + 1) * 32;
+    auto kern = gemv_q8_rcr_stream_kernel<MR, RAW, NC>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    const int ctas = p.n < sms ? p.n : sms;
+    kern<<<dim3(ctas, batch), STREAM_THREADS, smem, stream>>>(p);
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
+
 template <int MR, bool RAW>
 int32_t launch_rcr(const GemvParams& p, int batch, cudaStream_t stream) {
     // enough warps to cover the machine several times over, else fewer columns per warp
@@ -408,6 +601,16 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
         gemv_q8_generic_kernel<RAW><<<dim3(blocks, g.batch), GEMV_THREADS, 0, stream>>>(p, g.layout);
         return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
     }
+    // K-contiguous weights with few activation rows: the bulk-copy streaming kernel
+    // (variant 2 forces it off, variant 1 forces it on where it is legal)
+    if (g.layout == BQ_LAYOUT_RCR && g.m <= 4 && g.variant != 2 && (g.n * static_cast<int64_t>(g.k) >= (1 << 20) || g.variant == 1)) {
+        switch (g.m) {
+            case 1: return launch_rcr_stream<1, RAW>(p, g.batch, stream);
+            case 2: return launch_rcr_stream<2, RAW>(p, g.batch, stream);
+            case 3: return launch_rcr_stream<3, RAW>(p, g.batch, stream);
+            default: return launch_rcr_stream<4, RAW>(p, g.batch, stream);
+        }
+    }
 #define BQ_GEMV_CASE(MRV)                                                                  \
     case MRV:                                                                              \
         return g.layout == BQ_LAYOUT_RCR ? launch_rcr<MRV, RAW>(p, g.batch, stream)        \
@@ -439,6 +642,16 @@ size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, i
 
 int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream) {
     return g.raw_out ? dispatch<true>(g, stream) : dispatch<false>(g, stream);
+}
+
+int32_t read_and_clear_gemv_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemv_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        int zero = 0;
+        (void)cudaMemcpyToSymbol(g_gemv_device_status, &zero, sizeof(int));
+    }
+    return v;
 }
 
 }  // namespace bq

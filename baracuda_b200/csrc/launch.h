@@ -36,10 +36,28 @@ struct GemmDesc {
     void* d;
     int64_t ldd;
     int32_t force_block_n;  // 0 = choose; else 64 / 128 / 256 (tuning and tests)
+    // fused replicated output: the epilogue also stores each tile into these row-major
+    // [M, peer_ld] buffers (one per rank, peer-mapped) at column offset peer_col0
+    void* peer_d[8];
+    int32_t n_peers;  // 0 = off
+    int64_t peer_ld;
+    int32_t peer_col0;
 };
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);
+// Validates like the flat *_run symbols, then launches the bf16-out GEMM; with `peer_d` the epilogue
+// additionally stores into the `world` peer buffers at column offset rank * n.
+int32_t launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                                const void* b, int64_t ldb, void* d, int64_t ldd, const void* scale_a,
+                                const void* scale_b, int32_t scale_mode, float alpha, void* const* peer_d,
+                                int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream);
 int32_t read_and_clear_gemm_device_status();
+// CTA-pair (cta_group::2) variant: 256 x 256 output tiles shared by two SMs.
+int32_t launch_gemm_q8_pair(const GemmDesc& g, cudaStream_t stream);
+int32_t read_and_clear_gemm_pair_device_status();
+// helpers exported by the 1-CTA GEMM file
+bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
+int sm_count_of_current_device();
 
 struct GemvDesc {
     int32_t raw_out;  // 1: int32 accumulators, 0: bf16
@@ -62,6 +80,7 @@ struct GemvDesc {
 };
 
 int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream);
+int32_t read_and_clear_gemv_device_status();
 size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
 
 }  // namespace bq

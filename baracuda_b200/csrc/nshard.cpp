@@ -1,0 +1,186 @@
+// Column-parallel (N-sharded) entry points: each rank runs the tcgen05 GEMM on
+// its slice of the weight rows and, when the caller wants the output
+// replicated, either NCCL all-gathers the bf16 slices (rank-major
+// [world, M, N/world], the reference's contract) or — fused — lets the GEMM
+// epilogue store every tile straight into each peer's row-major [M, N] buffer
+// over NVLink while the tensor cores work on the next tile.
+//
+// Follows the forward of the reference's ColumnParallelLinearPlan
+//   crates/baracuda-megatron/src/lib.rs:729-905 (local GEMM, then all_gather)
+// and the communicator calls of
+//   crates/baracuda-nccl/src/lib.rs:243-261, 468-489 (init by unique id, all_gather).
+// NCCL is resolved at run time (dlopen of libnccl.so.2, as the reference's
+// baracuda-nccl-sys does, crates/baracuda-nccl-sys/src/lib.rs:347-431); a
+// library that is already loaded in the process is reused.
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "../../include/baracuda_kernels_q.h"
+#include "launch.h"
+
+namespace {
+
+// The few NCCL declarations used here (stable across NCCL 2.x).
+struct NcclUniqueId {
+    char internal[128];
+};
+using NcclComm = void*;
+constexpr int kNcclInt8 = 0, kNcclFloat32 = 7, kNcclBfloat16 = 9;
+constexpr int kNcclSum = 0;
+
+struct NcclApi {
+    int (*GetVersion)(int*) = nullptr;
+    int (*GetUniqueId)(NcclUniqueId*) = nullptr;
+    int (*CommInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
+    int (*CommDestroy)(NcclComm) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+    bool ok = false;
+};
+
+const NcclApi& nccl() {
+    static NcclApi api = [] {
+        NcclApi a;
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);  // reuse a copy the process already has
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+        if (!h) return a;
+        a.GetVersion = reinterpret_cast<decltype(a.GetVersion)>(dlsym(h, "ncclGetVersion"));
+        a.GetUniqueId = reinterpret_cast<decltype(a.GetUniqueId)>(dlsym(h, "ncclGetUniqueId"));
+        a.CommInitRank = reinterpret_cast<decltype(a.CommInitRank)>(dlsym(h, "ncclCommInitRank"));
+        a.CommDestroy = reinterpret_cast<decltype(a.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+        a.AllGather = reinterpret_cast<decltype(a.AllGather)>(dlsym(h, "ncclAllGather"));
+        a.AllReduce = reinterpret_cast<decltype(a.AllReduce)>(dlsym(h, "ncclAllReduce"));
+        a.ok = a.GetVersion && a.GetUniqueId && a.CommInitRank && a.CommDestroy && a.AllGather && a.AllReduce;
+        return a;
+    }();
+    return api;
+}
+
+int32_t nshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local,
+                   int32_t k, const void* a, int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd,
+                   const void* scale_a, const void* scale_b_local, int32_t scale_mode, float alpha, void* d_full,
+                   void* const* peer_d, int64_t ldd_full, void* stream) {
+    if (world < 1 || rank < 0 || rank >= world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (gather < BARACUDA_Q_GATHER_NONE || gather > BARACUDA_Q_GATHER_FUSED_PEER_STORE)
+        return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (m < 0 || n_local < 0 || k < 0) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    if (gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE) {
+        if (world > BARACUDA_Q_MAX_PEERS || !peer_d) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+        if (ldd_full < static_cast<int64_t>(n_local) * world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+        for (int r = 0; r < world; ++r) {
+            if (!peer_d[r]) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+        }
+    }
+    if (gather == BARACUDA_Q_GATHER_NCCL) {
+        if (!d_full || (world > 1 && !comm)) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+        // ncclAllGather sends one contiguous block per rank
+        if (ldd != (n_local > 0 ? n_local : 1)) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    }
+
+    int32_t st;
+    if (kind == bq::BQ_KIND_S8) {
+        st = bq::launch_gemm_rcr_checked(kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
+                                         BARACUDA_Q_SCALE_PER_ROW_COL, alpha,
+                                         gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE ? peer_d : nullptr, world, rank,
+                                         ldd_full, s);
+    } else {
+        st = bq::launch_gemm_rcr_checked(kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
+                                         scale_mode, alpha,
+                                         gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE ? peer_d : nullptr, world, rank,
+                                         ldd_full, s);
+    }
+    if (st != BARACUDA_Q_STATUS_OK) return st;
+    if (gather != BARACUDA_Q_GATHER_NCCL) return BARACUDA_Q_STATUS_OK;
+
+    const size_t count = static_cast<size_t>(m) * static_cast<size_t>(n_local);
+    if (count == 0) return BARACUDA_Q_STATUS_OK;
+    if (world == 1) {
+        // degenerate world: the collective is a device-to-device copy (the reference does the same,
+        // crates/baracuda-megatron/src/lib.rs:53-57)
+        if (d_full != d_local &&
+            cudaMemcpyAsync(d_full, d_local, count * 2, cudaMemcpyDeviceToDevice, s) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return BARACUDA_Q_STATUS_LAUNCH_FAILURE;
+        }
+        return BARACUDA_Q_STATUS_OK;
+    }
+    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    if (nccl().AllGather(d_local, d_full, count, kNcclBfloat16, comm, s) != 0) return BARACUDA_Q_STATUS_COMM_FAILURE;
+    return BARACUDA_Q_STATUS_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t baracuda_q_nccl_version(void) {
+    if (!nccl().ok) return 0;
+    int v = 0;
+    return nccl().GetVersion(&v) == 0 ? v : 0;
+}
+
+int32_t baracuda_q_nccl_unique_id(void* id_out_128_bytes) {
+    if (!id_out_128_bytes) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    NcclUniqueId id;
+    if (nccl().GetUniqueId(&id) != 0) return BARACUDA_Q_STATUS_COMM_FAILURE;
+    memcpy(id_out_128_bytes, &id, sizeof(id));
+    return BARACUDA_Q_STATUS_OK;
+}
+
+int32_t baracuda_q_nccl_comm_init_rank(void** comm_out, int32_t world, const void* id_128_bytes, int32_t rank) {
+    if (!comm_out || !id_128_bytes || world < 1 || rank < 0 || rank >= world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    NcclUniqueId id;
+    memcpy(&id, id_128_bytes, sizeof(id));
+    NcclComm c = nullptr;
+    if (nccl().CommInitRank(&c, world, id, rank) != 0) return BARACUDA_Q_STATUS_COMM_FAILURE;
+    *comm_out = c;
+    return BARACUDA_Q_STATUS_OK;
+}
+
+int32_t baracuda_q_nccl_comm_destroy(void* comm) {
+    if (!comm) return BARACUDA_Q_STATUS_OK;
+    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    return nccl().CommDestroy(comm) == 0 ? BARACUDA_Q_STATUS_OK : BARACUDA_Q_STATUS_COMM_FAILURE;
+}
+
+int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void* stream) {
+    if (!comm || !scratch_one_float) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    return nccl().AllReduce(scratch_one_float, scratch_one_float, 1, kNcclFloat32, kNcclSum, comm,
+                            static_cast<cudaStream_t>(stream)) == 0
+               ? BARACUDA_Q_STATUS_OK
+               : BARACUDA_Q_STATUS_COMM_FAILURE;
+}
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local, int32_t k, const void* a,
+    int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd, const void* scale_a,
+    const void* scale_b_local, int32_t scale_mode, float alpha, void* d_full, void* const* peer_d, int64_t ldd_full,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return nshard_run(bq::BQ_KIND_E4M3, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb, d_local, ldd,
+                      scale_a, scale_b_local, scale_mode, alpha, d_full, peer_d, ldd_full, stream);
+}
+
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local, int32_t k, const void* a,
+    int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd, const void* scale_a,
+    const void* scale_b_local, float alpha, void* d_full, void* const* peer_d, int64_t ldd_full, void* workspace,
+    size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return nshard_run(bq::BQ_KIND_S8, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb, d_local, ldd,
+                      scale_a, scale_b_local, BARACUDA_Q_SCALE_PER_ROW_COL, alpha, d_full, peer_d, ldd_full, stream);
+}
+
+}  // extern "C"

@@ -43,6 +43,10 @@ extern "C" {
 #define BARACUDA_Q_STATUS_WORKSPACE 4
 #define BARACUDA_Q_STATUS_LAUNCH_FAILURE 5
 
+/* codes above 5 are free in the reference's contract (ARCHITECTURE.md:370); the sharded entry points use two */
+#define BARACUDA_Q_STATUS_COMM_UNAVAILABLE 6 /* libnccl.so.2 could not be loaded */
+#define BARACUDA_Q_STATUS_COMM_FAILURE 7     /* an NCCL call returned an error */
+
 #define BARACUDA_Q_LAYOUT_RRR 0
 #define BARACUDA_Q_LAYOUT_RCR 1
 
@@ -174,11 +178,65 @@ size_t baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
 
 /* ---------------------------------------------------------------------------
+ * Column-parallel (N-sharded) GEMM inside one NVLink box.  Rank r owns rows
+ * [r*n_local, (r+1)*n_local) of the [N,K] weight and the matching scale_b slice;
+ * activations and scale_a are replicated; every rank computes D[:, slice].
+ * Follows ColumnParallelLinearPlan::forward
+ *   (crates/baracuda-megatron/src/lib.rs:842-905: local GEMM, then all_gather)
+ * with the reference's cuBLAS GEMM replaced by the tcgen05 kernels above.
+ * `gather` selects what happens to the output:
+ *   0  leave it sharded: d_local [M, n_local] only;
+ *   1  ncclAllGather of d_local (contiguous, ldd == n_local) into d_full,
+ *      rank-major [world, M, n_local] — the reference's layout (lib.rs:824-836);
+ *   2  fused: the GEMM epilogue stores each bf16 tile into all `world` buffers
+ *      peer_d[0..world) (row-major [M, ldd_full], peer-mapped device pointers,
+ *      peer_d[rank] being this rank's own) at column offset rank*n_local, so the
+ *      NVLink transfer overlaps the tensor-core work tile by tile and the result
+ *      is a true row-major [M, N].  The caller orders the ranks afterwards
+ *      (baracuda_q_nccl_stream_barrier or a host barrier) before reading.
+ * `comm` is the ncclComm_t of this rank (may be NULL for gather 0 and 2).
+ * Extra statuses: 6 NCCL not loadable, 7 NCCL call failed.
+ * ------------------------------------------------------------------------- */
+#define BARACUDA_Q_GATHER_NONE 0
+#define BARACUDA_Q_GATHER_NCCL 1
+#define BARACUDA_Q_GATHER_FUSED_PEER_STORE 2
+#define BARACUDA_Q_MAX_PEERS 8
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather,
+    int32_t m, int32_t n_local, int32_t k,
+    const void* a, int64_t lda, const void* b_local, int64_t ldb,
+    void* d_local, int64_t ldd,
+    const void* scale_a, const void* scale_b_local, int32_t scale_mode, float alpha,
+    void* d_full, void* const* peer_d, int64_t ldd_full,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather,
+    int32_t m, int32_t n_local, int32_t k,
+    const void* a, int64_t lda, const void* b_local, int64_t ldb,
+    void* d_local, int64_t ldd,
+    const void* scale_a, const void* scale_b_local, float alpha,
+    void* d_full, void* const* peer_d, int64_t ldd_full,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Communicator helpers over the run-time-loaded NCCL
+ * (Communicator::{new_with_id, all_gather}, crates/baracuda-nccl/src/lib.rs:243-261, 468-489).
+ * unique_id writes the 128-byte ncclUniqueId; rank 0 creates it and the caller
+ * distributes it.  stream_barrier is a one-float all-reduce used to order the
+ * ranks on their streams after the fused peer-store mode. */
+int32_t baracuda_q_nccl_version(void);
+int32_t baracuda_q_nccl_unique_id(void* id_out_128_bytes);
+int32_t baracuda_q_nccl_comm_init_rank(void** comm_out, int32_t world, const void* id_128_bytes, int32_t rank);
+int32_t baracuda_q_nccl_comm_destroy(void* comm);
+int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Diagnostics and tuning (no counterpart in the reference).
  * device_status: synchronous read-and-clear of the word a GEMM kernel sets
  * when one of its bounded barrier waits ran out (0 = none; 101..104 name the
  * waiting role).  Call it after synchronising the stream.
- * set_tuning: key 0 forces the GEMM N-tile (0 = automatic, 64, 128, 256);
+ * set_tuning: key 0 forces the GEMM tile (0 = automatic; 64, 128, 256 = 1-CTA kernel with that N-tile;
+ * 512 = the 256 x 256 CTA-pair kernel); key 1 forces a GEMV kernel variant;
  * process-wide, meant for benchmarks and tests.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_q_device_status(void);

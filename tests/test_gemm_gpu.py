@@ -98,7 +98,7 @@ def test_config0_w8a8_128x1024x1024(oracle):
     assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
 
 
-@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("block_n", [64, 128, 256, 512])  # 512 = the CTA-pair kernel
 def test_every_tile_config_many_tiles_and_tails(oracle, block_n):
     """More tiles than SMs (persistent loop, both TMEM buffers, ring wrap-around) with ragged M, N and K."""
     m, n, k = 1100, 2100, 656
@@ -119,6 +119,29 @@ def test_every_tile_config_many_tiles_and_tails(oracle, block_n):
     assert np.array_equal(got_odd[:, :n], want)
     canary = bf16_bits(torch.tensor([123.0], dtype=torch.bfloat16))[0]
     assert np.all(got_odd[:, n:] == canary)
+
+
+@pytest.mark.parametrize("kind", ["s8", "fp8"])
+def test_cta_pair_kernel_small_and_odd_shapes(oracle, kind):
+    """The 256 x 256 CTA-pair kernel forced onto shapes with a single tile, with M below one CTA's rows,
+    and with ragged M / N / K, for both operand kinds."""
+    bq.set_tuning(0, 512)
+    try:
+        for (m, n, k) in [(256, 256, 128), (100, 70, 64), (513, 300, 1040), (129, 257, 4096)]:
+            if kind == "s8":
+                aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n)
+                acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+                acc = _run_w8a8(m, n, k, aq, wq, raw=True).view(m, n).cpu().numpy()
+                assert oracle.compare_bitexact(acc_ref, acc) == -1, (m, n, k)
+                out = _run_w8a8(m, n, k, aq, wq, sa, sb)
+                assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
+            else:
+                aq, wq, sa, sb = fp8_case(oracle, m, n, k, seed=m + n)
+                acc_ref = oracle.gemm_e4m3_f32(aq, wq, oracle.RCR, m, n, k)
+                acc = _run_fp8(m, n, k, aq, wq, raw=True).cpu().numpy()
+                assert oracle.compare_tolerant(acc_ref, acc, 1e-3, 1e-5 * float(np.abs(acc_ref).max())) == -1, (m, n, k)
+    finally:
+        bq.set_tuning(0, 0)
 
 
 def test_alpha_and_empty_k(oracle):

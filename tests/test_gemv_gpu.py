@@ -74,8 +74,28 @@ def test_byte_load_kernel_equals_streaming_kernel(oracle, layout):
     assert np.array_equal(fast, oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k))
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("shape", [(1, 300, 512), (2, 149, 4096), (3, 1000, 4112), (4, 2048, 9000 // 16 * 16), (1, 7, 16)])
+def test_both_k_contiguous_kernels_on_the_same_shapes(oracle, shape, variant):
+    """The bulk-copy streaming kernel (variant 1) and the register-streaming kernel (variant 2) are both
+    exercised on shapes that include partial K chunks, several chunks per row and fewer columns than SMs."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=31 + n)
+    acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    bq.set_tuning(1, variant)
+    try:
+        acc = _run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=True).cpu().numpy()
+        out = _run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=False)
+    finally:
+        bq.set_tuning(1, 0)
+    assert bq.device_status() == 0
+    assert oracle.compare_bitexact(acc_ref, acc) == -1
+    assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out)) == -1
+
+
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("layout", ["rcr", "rrr"])
-def test_padded_leading_dims_batch_broadcast_and_canaries(oracle, layout):
+def test_padded_leading_dims_batch_broadcast_and_canaries(oracle, layout, variant):
     """Padded lda/ldb/ldd, strided batch with the weights broadcast (stride_b == 0, the reference's GQA use,
     gemv_dense_smoke.rs), and untouched padding between output rows and batch slots."""
     lay = LAYOUTS[layout]
@@ -105,8 +125,12 @@ def test_padded_leading_dims_batch_broadcast_and_canaries(oracle, layout):
     args = bq.GemvQ8Args(a=dev(a_buf), b=dev(b_buf), d=d, scale_a=dev(np.concatenate(sa_all)), scale_b=dev(sb),
                          lda=lda, ldb=ldb, ldd=ldd, stride_a=stride_a, stride_b=0, stride_d=stride_d,
                          stride_scale_a=stride_sa, stride_scale_b=0)
-    plan.run(None, ws, args)
-    torch.cuda.synchronize()
+    bq.set_tuning(1, variant)
+    try:
+        plan.run(None, ws, args)
+        torch.cuda.synchronize()
+    finally:
+        bq.set_tuning(1, 0)
     got = bf16_bits(d)
     canary = bf16_bits(torch.tensor([123.0], dtype=torch.bfloat16))[0]
     touched = np.zeros(batch * stride_d, dtype=bool)
