@@ -153,29 +153,32 @@ gemv_q8_rcr_kernel(const GemvParams p) {
     }
 }
 
-// ---- weights stored [N, K], bulk-copy fed: one persistent CTA per SM.  A producer
-// warp streams whole weight rows (up to 4 KiB of K per copy) into a shared-memory
-// ring with cp.async.bulk, eight consumer warps each take a row from the ring, dot it
-// with the activations held in registers (dp4a) and fold the 32 lane sums with
-// shuffles.  The copies keep ~100 KiB per SM in flight no matter how the consumers
-// are scheduled, which is what a 9 us HBM-bound kernel needs. ----
-constexpr int STREAM_CHUNK = 4096;   // bytes of K per ring slot
-constexpr int STREAM_SLOTS = 26;     // 104 KiB of weights in flight per SM
+// ---- weights stored [N, K], bulk-copy fed: one persistent CTA per SM, every warp its own
+// stream.  Warp w owns the CTA's columns w, w+W, w+2W, ... and a private ring of shared-memory
+// slots; its lane 0 keeps the ring full with cp.async.bulk copies of whole weight rows (up to
+// 4 KiB of K each, completion counted on an mbarrier), the warp pulls a landed row into
+// registers, immediately re-arms the slot with the copy for a later column, then dots the row
+// with the activations held in registers (dp4a) and folds the 32 lane sums with shuffles.
+// About 190 KiB of weights are in flight per SM regardless of how the warps are scheduled,
+// which is what a 9 us HBM-bound kernel needs. ----
+constexpr int STREAM_CHUNK = 4096;        // bytes of K per ring slot
+constexpr int STREAM_RING_BYTES = 196608;  // all warps' rings together
 constexpr long long STREAM_WAIT_LIMIT = 1LL << 31;
 
-// STREAM_CONSUMERS consumer warps + 1 producer warp; more activation rows need more registers per
-// thread (the activations live in registers), hence fewer consumer warps.
-template <int MR, bool RAW, int STREAM_CONSUMERS>
-__global__ void __launch_bounds__((STREAM_CONSUMERS + 1) * 32, 1)
+// STREAM_WARPS warps; more activation rows need more registers per thread (the activations
+// live in registers), hence fewer warps with deeper rings.
+template <int MR, bool RAW, int STREAM_WARPS>
+__global__ void __launch_bounds__(STREAM_WARPS * 32, 1)
 gemv_q8_rcr_stream_kernel(const GemvParams p) {
+    constexpr int SLOTS = STREAM_RING_BYTES / STREAM_CHUNK / STREAM_WARPS;  // per warp
     extern __shared__ __align__(128) uint8_t stream_smem[];
-    uint8_t* ring = stream_smem;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(stream_smem + STREAM_SLOTS * STREAM_CHUNK);
-    uint64_t* empty_bar = full_bar + STREAM_SLOTS;
-    volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(empty_bar + STREAM_SLOTS);
-
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    uint8_t* ring = stream_smem + warp * SLOTS * STREAM_CHUNK;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(stream_smem + STREAM_RING_BYTES) + warp * SLOTS;
+    volatile uint32_t* abort_word =
+        reinterpret_cast<volatile uint32_t*>(stream_smem + STREAM_RING_BYTES + STREAM_WARPS * SLOTS * 8);
+
     const int64_t g = blockIdx.y;
     const int8_t* a = p.a + g * p.stride_a;
     const int8_t* b = p.b + g * p.stride_b;
@@ -186,126 +189,122 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
     const int col_begin = blockIdx.x * base + (static_cast<int>(blockIdx.x) < rem ? static_cast<int>(blockIdx.x) : rem);
     const int ncols = base + (static_cast<int>(blockIdx.x) < rem ? 1 : 0);
     const int chunks = (p.k + STREAM_CHUNK - 1) / STREAM_CHUNK;
+    // this warp's work items: (its c-th column, K chunk kc), item = c * chunks + kc
+    const int my_cols = (ncols > warp) ? (ncols - warp + STREAM_WARPS - 1) / STREAM_WARPS : 0;
+    const int my_items = my_cols * chunks;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STREAM_SLOTS; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 1);
-        }
-        *abort_word = 0u;
+    if (threadIdx.x == 0) *abort_word = 0u;
+    if (lane == 0) {
+        for (int s = 0; s < SLOTS; ++s) mbar_init(&full_bar[s], 1);
         fence_barrier_init();
         fence_proxy_async_smem();
     }
     __syncthreads();
 
-    if (warp == STREAM_CONSUMERS) {
-        if (lane == 0) {
-            const int items = ncols * chunks;
-            for (int i = 0; i < items; ++i) {
-                const int slot = i % STREAM_SLOTS;
-                const uint32_t parity = ((i / STREAM_SLOTS) & 1) ^ 1u;
-                if (!mbar_wait_bounded(&empty_bar[slot], parity, abort_word, STREAM_WAIT_LIMIT)) {
-                    *abort_word = 1u;
-                    atomicCAS(&g_gemv_device_status, 0, 201);
-                    break;
-                }
-                const int j = i / chunks, kc = i - j * chunks;
-                const int k0 = kc * STREAM_CHUNK;
-                const uint32_t bytes = static_cast<uint32_t>((p.k - k0 < STREAM_CHUNK) ? (p.k - k0) : STREAM_CHUNK);
-                mbar_arrive_expect_tx(&full_bar[slot], bytes);
-                bulk_load_1d(ring + slot * STREAM_CHUNK, b + static_cast<int64_t>(col_begin + j) * p.ldb + k0, bytes,
-                             &full_bar[slot]);
+    auto issue = [&](int item) {  // lane 0 only
+        const int c = item / chunks, kc = item - c * chunks;
+        const int k0 = kc * STREAM_CHUNK;
+        const uint32_t bytes = static_cast<uint32_t>((p.k - k0 < STREAM_CHUNK) ? (p.k - k0) : STREAM_CHUNK);
+        const int slot = item % SLOTS;
+        mbar_arrive_expect_tx(&full_bar[slot], bytes);
+        bulk_load_1d(ring + slot * STREAM_CHUNK,
+                     b + static_cast<int64_t>(col_begin + warp + c * STREAM_WARPS) * p.ldb + k0, bytes, &full_bar[slot]);
+    };
+    if (lane == 0) {
+        for (int i = 0; i < SLOTS && i < my_items; ++i) issue(i);
+    }
+
+    // activations: with a single K chunk every lane keeps its 8 x 16 bytes per row in registers
+    uint4 xr[MR][8];
+    const bool x_in_regs = (chunks == 1);
+    if (x_in_regs) {
+#pragma unroll
+        for (int r = 0; r < MR; ++r)
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const int k16 = s * 32 + lane;
+                xr[r][s] = (k16 * 16 < p.k)
+                               ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + k16)
+                               : make_uint4(0, 0, 0, 0);
             }
-        }
-    } else {
-        // activations: with a single K chunk every lane keeps its 8 x 16 bytes per row in registers
-        uint4 xr[MR][8];
-        const bool x_in_regs = (chunks == 1);
-        if (x_in_regs) {
+    }
+
+    // Each warp parks the finished sum of its c-th column in lane (c mod 32) and writes 32 columns
+    // at a time, so the scale loads and the stores of the epilogue are paid once per batch, in
+    // parallel, instead of once per column on the critical path.
+    int keep[MR];
 #pragma unroll
-            for (int r = 0; r < MR; ++r)
+    for (int r = 0; r < MR; ++r) keep[r] = 0;
+    bool ok = true;
+    int done = 0;
+    for (int c = 0; ok && c < my_cols; ++c) {
+        int acc0[MR], acc1[MR];
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    const int k16 = s * 32 + lane;
-                    xr[r][s] = (k16 * 16 < p.k)
-                                   ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + k16)
-                                   : make_uint4(0, 0, 0, 0);
-                }
-        }
-        // Each warp parks the finished sum of its i-th column in lane (i mod 32) and writes 32 columns
-        // at a time, so the scale loads and the stores of the epilogue are paid once per batch, in
-        // parallel, instead of once per column on the critical path.
-        int keep[MR];
+        for (int r = 0; r < MR; ++r) acc0[r] = acc1[r] = 0;
+        for (int kc = 0; kc < chunks; ++kc) {
+            const int item = c * chunks + kc;
+            const int slot = item % SLOTS;
+            const uint32_t parity = (item / SLOTS) & 1;
+            if (!mbar_wait_bounded(&full_bar[slot], parity, abort_word, STREAM_WAIT_LIMIT)) {
+                *abort_word = 1u;
+                atomicCAS(&g_gemv_device_status, 0, 202);
+                ok = false;
+                break;
+            }
+            const int k0 = kc * STREAM_CHUNK;
+            const int valid16 = ((p.k - k0 < STREAM_CHUNK) ? (p.k - k0) : STREAM_CHUNK) >> 4;
+            const uint4* wv = reinterpret_cast<const uint4*>(ring + slot * STREAM_CHUNK);
+            uint4 w[8];
 #pragma unroll
-        for (int r = 0; r < MR; ++r) keep[r] = 0;
-        bool ok = true;
-        int done = 0;  // columns this warp has finished
-        for (int j = warp; ok && j < ncols; j += STREAM_CONSUMERS) {
-            int acc0[MR], acc1[MR];
+            for (int s = 0; s < 8; ++s) {
+                const int k16 = s * 32 + lane;
+                w[s] = (k16 < valid16) ? wv[k16] : make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();  // every lane holds its part of the row: the slot can be refilled
+            if (lane == 0 && item + SLOTS < my_items) {
+                fence_proxy_async_smem();
+                issue(item + SLOTS);
+            }
 #pragma unroll
-            for (int r = 0; r < MR; ++r) acc0[r] = acc1[r] = 0;
-            for (int kc = 0; kc < chunks; ++kc) {
-                const int i = j * chunks + kc;
-                const int slot = i % STREAM_SLOTS;
-                const uint32_t parity = (i / STREAM_SLOTS) & 1;
-                if (!mbar_wait_bounded(&full_bar[slot], parity, abort_word, STREAM_WAIT_LIMIT)) {
-                    *abort_word = 1u;
-                    atomicCAS(&g_gemv_device_status, 0, 202);
-                    ok = false;
-                    break;
-                }
-                const int k0 = kc * STREAM_CHUNK;
-                const int valid16 = ((p.k - k0 < STREAM_CHUNK) ? (p.k - k0) : STREAM_CHUNK) >> 4;
-                const uint4* wv = reinterpret_cast<const uint4*>(ring + slot * STREAM_CHUNK);
-                uint4 w[8];
+            for (int s = 0; s < 8; ++s) {
+                const int k16 = s * 32 + lane;
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    const int k16 = s * 32 + lane;
-                    w[s] = (k16 < valid16) ? wv[k16] : make_uint4(0, 0, 0, 0);
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty_bar[slot]);  // the slot is in registers now
-#pragma unroll
-                for (int s = 0; s < 8; ++s) {
-                    const int k16 = s * 32 + lane;
-#pragma unroll
-                    for (int r = 0; r < MR; ++r) {
-                        uint4 x;
-                        if (x_in_regs) {
-                            x = xr[r][s];
-                        } else {
-                            x = (k16 < valid16)
-                                    ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda + k0) + k16)
-                                    : make_uint4(0, 0, 0, 0);
-                        }
-                        if (s & 1) {
-                            acc1[r] = dot16(w[s], x, acc1[r]);
-                        } else {
-                            acc0[r] = dot16(w[s], x, acc0[r]);
-                        }
+                for (int r = 0; r < MR; ++r) {
+                    uint4 x;
+                    if (x_in_regs) {
+                        x = xr[r][s];
+                    } else {
+                        x = (k16 < valid16)
+                                ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda + k0) + k16)
+                                : make_uint4(0, 0, 0, 0);
+                    }
+                    if (s & 1) {
+                        acc1[r] = dot16(w[s], x, acc1[r]);
+                    } else {
+                        acc0[r] = dot16(w[s], x, acc0[r]);
                     }
                 }
             }
-            if (!ok) break;
-#pragma unroll
-            for (int r = 0; r < MR; ++r) {
-                const int v = warp_sum(acc0[r] + acc1[r]);
-                if (lane == (done & 31)) keep[r] = v;
-            }
-            ++done;
-            if ((done & 31) == 0) {
-                const int col = col_begin + warp + (done - 32 + lane) * STREAM_CONSUMERS;
-#pragma unroll
-                for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
-            }
         }
-        if (ok && (done & 31) != 0) {
-            const int first = done & ~31;
-            if (lane < done - first) {
-                const int col = col_begin + warp + (first + lane) * STREAM_CONSUMERS;
+        if (!ok) break;
 #pragma unroll
-                for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
-            }
+        for (int r = 0; r < MR; ++r) {
+            const int v = warp_sum(acc0[r] + acc1[r]);
+            if (lane == (done & 31)) keep[r] = v;
+        }
+        ++done;
+        if ((done & 31) == 0) {
+            const int col = col_begin + warp + (done - 32 + lane) * STREAM_WARPS;
+#pragma unroll
+            for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
+        }
+    }
+    if (ok && (done & 31) != 0) {
+        const int first = done & ~31;
+        if (lane < done - first) {
+            const int col = col_begin + warp + (first + lane) * STREAM_WARPS;
+#pragma unroll
+            for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
         }
     }
     // leave together; on the error path give copies still in flight a bounded time to land
@@ -520,16 +519,15 @@ template <int MR, bool RAW>
 int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
     const int sms = sm_count_cached();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
-    const size_t smem = static_cast<size_t>(STREAM_SLOTS) * STREAM_CHUNK + 2 * STREAM_SLOTS * 8 + 16;
-    constexpr int NC = (MR == 1) ? 16 : 8;
-    constexpr int STREAM_THREADS = (NC + 1) * 32;
-    auto kern = gemv_q8_rcr_stream_kernel<MR, RAW, NC>;
+    constexpr int NW = (MR == 1) ? 16 : 8;
+    const size_t smem = static_cast<size_t>(STREAM_RING_BYTES) + (STREAM_RING_BYTES / STREAM_CHUNK) * 8 + 16;
+    auto kern = gemv_q8_rcr_stream_kernel<MR, RAW, NW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
     }
     const int ctas = p.n < sms ? p.n : sms;
-    kern<<<dim3(ctas, batch), STREAM_THREADS, smem, stream>>>(p);
+    kern<<<dim3(ctas, batch), NW * 32, smem, stream>>>(p);
     return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
 }
 

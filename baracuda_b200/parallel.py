@@ -1,0 +1,167 @@
+"""Column-parallel (N-sharded) quantized linear inside one NVLink box.
+
+Host-side mirror of the forward half of the reference's tensor-parallel layer
+(`TensorParallelContext` and `ColumnParallelLinearPlan::{new, forward}`,
+crates/baracuda-megatron/src/lib.rs:153-240, 729-905): rank r owns rows
+[r*N/G, (r+1)*N/G) of the [N,K] weight and the matching weight scales, the
+activations are replicated, every rank computes its output slice with the
+tcgen05 GEMM, and the output is left sharded, NCCL all-gathered (rank-major
+[G, M, N/G], the reference's contract) or written straight into every rank's
+row-major [M, N] buffer by the GEMM epilogue over NVLink (fused mode).
+
+One process per GPU.  torch.distributed is only used to hand the NCCL unique
+id around; the collective itself is issued by the C library on the caller's
+stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from .plans import SCALE_PER_ROW_COL, _ptr, _stream_ptr
+from .vocab import BaracudaError, InvalidProblem, status_to_result
+
+GATHER_NONE = 0
+GATHER_NCCL = 1
+GATHER_FUSED_PEER_STORE = 2
+
+
+class CommUnavailable(BaracudaError):
+    """libnccl.so.2 could not be loaded (status 6)."""
+
+
+class CommFailure(BaracudaError):
+    """An NCCL call returned an error (status 7)."""
+
+
+def _check(status: int, what: str) -> None:
+    if status == 6:
+        raise CommUnavailable(f"{what}: NCCL is not loadable in this process")
+    if status == 7:
+        raise CommFailure(f"{what}: NCCL call failed")
+    status_to_result(status, what)
+
+
+def shard_range(out_features: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows of the [N,K] weight that `rank` owns.  N must divide evenly (lib.rs:781-785)."""
+    if world < 1 or not (0 <= rank < world):
+        raise InvalidProblem(f"rank {rank} outside world {world}")
+    if out_features % world != 0:
+        raise InvalidProblem(f"out_features {out_features} is not divisible by the world size {world}")
+    per = out_features // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_rows(t: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """This rank's contiguous row slice of a weight ([N,K]) or of a per-channel vector ([N])."""
+    lo, hi = shard_range(t.shape[0], world, rank)
+    return t[lo:hi].contiguous()
+
+
+def gathered_to_row_major(y_full: torch.Tensor) -> torch.Tensor:
+    """[G, M, N/G] (what the all-gather produces, lib.rs:824-836) -> row-major [M, N]."""
+    g, m, n_local = y_full.shape
+    return y_full.permute(1, 0, 2).reshape(m, g * n_local)
+
+
+class TensorParallelContext:
+    """Rank, world size and this rank's NCCL communicator (lib.rs:153-240)."""
+
+    def __init__(self, rank: int, world: int, comm: Optional[int] = None):
+        if world < 1 or not (0 <= rank < world):
+            raise InvalidProblem(f"rank {rank} outside world {world}")
+        self.rank, self.world, self.comm = rank, world, comm
+
+    @classmethod
+    def from_torch_distributed(cls, group=None) -> "TensorParallelContext":
+        """Rank 0 creates the NCCL unique id, torch.distributed broadcasts its 128 bytes, every rank joins."""
+        import torch.distributed as dist
+
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        if world == 1:
+            return cls(0, 1, None)
+        lib = _lib.load()
+        buf = (C.c_uint8 * 128)()
+        if rank == 0:
+            _check(lib.baracuda_q_nccl_unique_id(buf), "nccl_unique_id")
+        backend = dist.get_backend(group)
+        dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
+        t = torch.tensor(list(buf), dtype=torch.uint8, device=dev)
+        dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        id_bytes = (C.c_uint8 * 128)(*t.cpu().tolist())
+        comm = C.c_void_p()
+        _check(lib.baracuda_q_nccl_comm_init_rank(C.byref(comm), world, id_bytes, rank), "nccl_comm_init_rank")
+        return cls(rank, world, comm.value)
+
+    def stream_barrier(self, scratch: torch.Tensor, stream=None) -> None:
+        """Orders the ranks on their streams (one-float all-reduce); used after the fused peer-store mode."""
+        if self.world == 1:
+            return
+        _check(_lib.load().baracuda_q_nccl_stream_barrier(self.comm, scratch.data_ptr(), _stream_ptr(stream)),
+               "nccl_stream_barrier")
+
+    def destroy(self) -> None:
+        if self.comm:
+            _check(_lib.load().baracuda_q_nccl_comm_destroy(self.comm), "nccl_comm_destroy")
+            self.comm = None
+
+
+class ColumnParallelQGemmPlan:
+    """N-sharded FP8 or W8A8 GEMM with an optional replicated output."""
+
+    def __init__(self, ctx: TensorParallelContext, m: int, out_features: int, k: int, kind: str = "fp8",
+                 scale_mode: int = SCALE_PER_ROW_COL, gather: int = GATHER_NONE):
+        if kind not in ("fp8", "w8a8"):
+            raise InvalidProblem("kind must be 'fp8' or 'w8a8'")
+        if gather not in (GATHER_NONE, GATHER_NCCL, GATHER_FUSED_PEER_STORE):
+            raise InvalidProblem("unknown gather mode")
+        if min(m, out_features, k) < 0:
+            raise InvalidProblem("negative dimension")
+        lo, hi = shard_range(out_features, ctx.world, ctx.rank)
+        self.ctx, self.m, self.n, self.k = ctx, m, out_features, k
+        self.n_local, self.col0 = hi - lo, lo
+        self.kind, self.scale_mode, self.gather = kind, scale_mode, gather
+
+    def forward(self, stream, a: torch.Tensor, scale_a: torch.Tensor, w_local: torch.Tensor,
+                scale_b_local: torch.Tensor, y_local: torch.Tensor, y_full: Optional[torch.Tensor] = None,
+                peer_ptrs: Optional[Sequence[int]] = None, ldd_full: int = 0, alpha: float = 1.0) -> None:
+        """Y_local[M, N/G] = dequant(A x W_local^T); then the selected gather.  Asynchronous on `stream`."""
+        if a.numel() < self.m * self.k or w_local.numel() < self.n_local * self.k:
+            raise InvalidProblem("operand shorter than the descriptor says")
+        if y_local.numel() < self.m * self.n_local:
+            raise InvalidProblem("y_local shorter than [M, N/G]")
+        if self.gather == GATHER_NCCL and (y_full is None or y_full.numel() < self.m * self.n):
+            raise InvalidProblem("y_full must hold [G, M, N/G]")
+        peers = None
+        if self.gather == GATHER_FUSED_PEER_STORE:
+            if peer_ptrs is None or len(peer_ptrs) != self.ctx.world:
+                raise InvalidProblem("fused mode needs one peer buffer pointer per rank")
+            peers = (C.c_void_p * self.ctx.world)(*peer_ptrs)
+            ldd_full = ldd_full or self.n
+        lib = _lib.load()
+        common = (self.ctx.rank, self.ctx.world, self.ctx.comm, self.gather, self.m, self.n_local, self.k,
+                  _ptr(a), max(self.k, 1), _ptr(w_local), max(self.k, 1), _ptr(y_local), max(self.n_local, 1),
+                  _ptr(scale_a), _ptr(scale_b_local))
+        tail = (_ptr(y_full), peers, ldd_full, None, 0, _stream_ptr(stream))
+        if self.kind == "fp8":
+            st = lib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(*common, self.scale_mode, alpha, *tail)
+        else:
+            st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(*common, alpha, *tail)
+        _check(st, "ColumnParallelQGemmPlan.forward")
+
+
+def alloc_peer_buffers(shape, dtype=torch.bfloat16, group=None):
+    """One buffer of `shape` per rank, each mapped into every rank's address space (NVLink peer
+    memory), for the fused peer-store mode.  Returns (this rank's tensor, [device pointer per rank]).
+    Uses torch's symmetric-memory allocator as plumbing; the stores themselves are issued by the
+    GEMM epilogue."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group if group is not None else dist.group.WORLD
+    local = symm_mem.empty(*shape, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+    handle = symm_mem.rendezvous(local, group=group)
+    return local, [int(p) for p in handle.buffer_ptrs]

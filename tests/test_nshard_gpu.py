@@ -1,0 +1,97 @@
+"""Two-GPU parity of the column-parallel GEMM: each rank computes its N-slice with the tcgen05 kernel;
+the sharded output, the NCCL-gathered output (rank-major) and the fused peer-store output (row-major)
+must all equal the unsharded oracle result.  Skipped with fewer than two GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import baracuda_b200 as bq
+        from baracuda_b200 import parallel as par
+        from oracle import pyoracle as orc
+
+        ctx = par.TensorParallelContext.from_torch_distributed()
+        dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+        bits = lambda t: t.cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+        for kind, (m, n, k) in (("w8a8", (300, 1024, 512)), ("fp8", (1024, 2048, 1024))):
+            rng = np.random.default_rng(5)
+            a = rng.standard_normal((m, k)).astype(np.float32)
+            w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+            if kind == "w8a8":
+                aq, sa = orc.quantize_rows_s8(a)
+                wq, sb = orc.quantize_rows_s8(w)
+                want = orc.dequant_s32_bf16(orc.gemm_s8_s32(aq, wq, orc.RCR, m, n, k), sa, sb)
+            else:
+                aq, sa = orc.quantize_rows_e4m3(a)
+                wq, sb = orc.quantize_rows_e4m3(w)
+                want = orc.scale_f32_bf16(orc.gemm_e4m3_f32(aq, wq, orc.RCR, m, n, k), sa, sb)
+            want_f = orc.bf16_bits_to_f32(want)
+            w_local = par.shard_rows(torch.from_numpy(wq), world, rank).cuda()
+            sb_local = par.shard_rows(torch.from_numpy(sb), world, rank).cuda()
+            n_local = n // world
+            lo = rank * n_local
+
+            def check(got_bits, ref_bits, what):
+                if kind == "w8a8":
+                    assert np.array_equal(got_bits, ref_bits), f"{kind} {what} rank {rank}"
+                else:
+                    g, r = orc.bf16_bits_to_f32(got_bits), orc.bf16_bits_to_f32(ref_bits)
+                    assert orc.compare_tolerant(r, g, 1e-2, 1e-4 * float(np.abs(want_f).max())) == -1, f"{kind} {what}"
+
+            # sharded output
+            y_local = torch.zeros((m, n_local), dtype=torch.bfloat16, device="cuda")
+            plan = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind=kind, gather=par.GATHER_NONE)
+            plan.forward(None, dev(aq), dev(sa), w_local, sb_local, y_local)
+            torch.cuda.synchronize()
+            check(bits(y_local), want[:, lo:lo + n_local], "sharded")
+            # NCCL all-gather, rank-major [G, M, N/G]
+            y_full = torch.zeros((world, m, n_local), dtype=torch.bfloat16, device="cuda")
+            plan = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind=kind, gather=par.GATHER_NCCL)
+            plan.forward(None, dev(aq), dev(sa), w_local, sb_local, y_local, y_full=y_full)
+            torch.cuda.synchronize()
+            check(bits(par.gathered_to_row_major(y_full)), want, "nccl gather")
+            # fused: the epilogue stores into every rank's row-major [M, N] buffer
+            full_rm, ptrs = par.alloc_peer_buffers((m, n))
+            full_rm.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            plan = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind=kind, gather=par.GATHER_FUSED_PEER_STORE)
+            plan.forward(None, dev(aq), dev(sa), w_local, sb_local, y_local, peer_ptrs=ptrs, ldd_full=n)
+            scratch = torch.zeros(1, device="cuda")
+            ctx.stream_barrier(scratch)
+            torch.cuda.synchronize()
+            dist.barrier()
+            check(bits(full_rm), want, "fused peer store")
+            assert bq.device_status() == 0
+        ctx.destroy()
+        with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
+            f.write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_parallel_two_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
