@@ -12,6 +12,7 @@ namespace {
 
 std::atomic<int32_t> g_force_block_n{0};
 std::atomic<int32_t> g_gemv_variant{0};
+std::atomic<int32_t> g_force_pair_tile_n{0};
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -66,6 +67,7 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
     g.d = d;
     g.ldd = ldd;
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
@@ -165,6 +167,7 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     g.d = d;
     g.ldd = ldd;
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
     g.n_peers = world;
     g.peer_ld = peer_ld;
     g.peer_col0 = rank * n;
@@ -299,6 +302,11 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             return bq::BQ_STATUS_OK;
         case 1:
             g_gemv_variant.store(value);
+            return bq::BQ_STATUS_OK;
+        case 2:
+            if (value != 0 && value != 256 && value != 224 && value != 192 && value != 128)
+                return bq::BQ_STATUS_INVALID_PROBLEM;
+            g_force_pair_tile_n.store(value);
             return bq::BQ_STATUS_OK;
         default:
             return bq::BQ_STATUS_INVALID_PROBLEM;

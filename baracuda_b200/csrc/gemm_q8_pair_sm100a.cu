@@ -27,31 +27,43 @@ __device__ int g_gemm_pair_device_status = 0;
 namespace {
 
 constexpr int PAIR_TILE_M = 256;   // rows per CTA pair
-constexpr int PAIR_TILE_N = 256;   // columns per CTA pair
+// columns per CTA pair: template parameter TN (256, 224, 192 or 128; any multiple of 32 works for the MMA)
 constexpr int CTA_ROWS = 128;      // A rows and weight rows each CTA loads
 constexpr int PAIR_BLOCK_K = 128;  // bytes of K per stage
 constexpr int PAIR_UMMA_K = 32;
-constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_THREADS = 192;
 constexpr int PAIR_A_BYTES = CTA_ROWS * PAIR_BLOCK_K;
-constexpr int PAIR_B_BYTES = CTA_ROWS * PAIR_BLOCK_K;
-constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
-constexpr int PAIR_TILE_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES;
-constexpr int PAIR_SB_BYTES = 4 * PAIR_TILE_N * 4;
-constexpr int PAIR_BAR_BYTES = (2 * PAIR_STAGES + 4) * 8 + 16;
-constexpr int PAIR_SMEM_TOTAL = PAIR_TILE_BYTES + PAIR_SB_BYTES + PAIR_BAR_BYTES + 1024;
-constexpr int PAIR_TMEM_COLS = 512;
 constexpr long long PAIR_WAIT_LIMIT = 1LL << 31;
+
+template <int TN>
+struct PairCfg {
+    static constexpr int B_ROWS = TN / 2;  // weight rows each CTA loads
+    static constexpr int B_BYTES = B_ROWS * PAIR_BLOCK_K;
+    static constexpr int STAGE_BYTES = PAIR_A_BYTES + B_BYTES;  // a multiple of 1024 for TN % 16 == 0
+    static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
+    static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int SB_BYTES = 4 * TN * 4;
+    static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+    static constexpr int SMEM_TOTAL = TILE_BYTES + SB_BYTES + BAR_BYTES + 1024;
+    static constexpr int TMEM_COLS = (2 * TN <= 256) ? 256 : 512;
+};
 
 __device__ __forceinline__ void pair_timeout(volatile uint32_t* abort_word, int code) {
     *abort_word = 1u;
     atomicCAS(&g_gemm_pair_device_status, 0, code);
 }
 
-template <uint32_t KIND, bool RAW, bool FUSED>
+template <uint32_t KIND, bool RAW, bool FUSED, int TN>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
+    using C = PairCfg<TN>;
+    constexpr int PAIR_TILE_N = TN;
+    constexpr int PAIR_STAGES = C::STAGES;
+    constexpr int PAIR_STAGE_BYTES = C::STAGE_BYTES;
+    constexpr int PAIR_TILE_BYTES = C::TILE_BYTES;
+    constexpr int PAIR_SB_BYTES = C::SB_BYTES;
+    constexpr int PAIR_TMEM_COLS = C::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
@@ -118,7 +130,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tma_load_2d_pair(a_tile, &tmap_a, full_on_leader, kb * PAIR_BLOCK_K,
                                      m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS);
                     tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
-                                     n_blk * PAIR_TILE_N + static_cast<int>(rank) * CTA_ROWS);
+                                     n_blk * PAIR_TILE_N + static_cast<int>(rank) * C::B_ROWS);
                     if (++stage == PAIR_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -141,7 +153,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * PAIR_TILE_N);
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, abort_word, PAIR_WAIT_LIMIT)) {
                         pair_timeout(abort_word, 113);
@@ -195,7 +207,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                                   static_cast<uint32_t>(buf * PAIR_TILE_N);
+                                   static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
 #pragma unroll 1
             for (int c = 0; c < PAIR_TILE_N / 32; ++c) {
                 const int col0 = n_blk * PAIR_TILE_N + c * 32;
@@ -226,13 +238,16 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
 }
 
-template <uint32_t KIND, bool RAW, bool FUSED>
-int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
+template <uint32_t KIND, bool RAW, bool FUSED, int TN>
+int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
+    using C = PairCfg<TN>;
+    constexpr int PAIR_TILE_N = TN;
+    constexpr int PAIR_SMEM_TOTAL = C::SMEM_TOTAL;
     const int sms = sm_count_of_current_device();
     if (sms < 2) return BQ_STATUS_LAUNCH_FAILURE;
     CUtensorMap map_a, map_b;
     if (!make_kmajor_tensor_map(&map_a, g.a, g.m, g.k, g.lda, CTA_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
-    if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, CTA_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
+    if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, C::B_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
     GemmParams p;
     p.d = g.d;
     p.ldd = g.ldd;
@@ -255,7 +270,7 @@ int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
         p.peer_d[r] = g.peer_d[r];
         if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
     }
-    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED>;
+    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -279,6 +294,39 @@ int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
         return BQ_STATUS_LAUNCH_FAILURE;
     }
     return BQ_STATUS_OK;
+}
+
+// Tile width: the one that minimises (waves of pair tiles) x (tile width / relative efficiency).
+int pick_tile_n(const GemmDesc& g) {
+    if (g.force_pair_tile_n != 0) return g.force_pair_tile_n;
+    const int sms = sm_count_of_current_device();
+    const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
+    const int64_t m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
+    const int cand[4] = {256, 224, 192, 128};
+    const double eff[4] = {1.0, 0.985, 0.965, 0.93};
+    int best = 256;
+    double best_cost = 1e300;
+    for (int i = 0; i < 4; ++i) {
+        const int64_t tiles = m_tiles * ((g.n + cand[i] - 1) / cand[i]);
+        const int64_t waves = (tiles + pairs - 1) / pairs;
+        const double cost = static_cast<double>(waves) * cand[i] / eff[i];
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = cand[i];
+        }
+    }
+    return best;
+}
+
+template <uint32_t KIND, bool RAW, bool FUSED>
+int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
+    switch (pick_tile_n(g)) {
+        case 256: return launch_pair_tn<KIND, RAW, FUSED, 256>(g, stream);
+        case 224: return launch_pair_tn<KIND, RAW, FUSED, 224>(g, stream);
+        case 192: return launch_pair_tn<KIND, RAW, FUSED, 192>(g, stream);
+        case 128: return launch_pair_tn<KIND, RAW, FUSED, 128>(g, stream);
+        default: return BQ_STATUS_INVALID_PROBLEM;
+    }
 }
 
 }  // namespace

@@ -176,8 +176,9 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
     const int lane = threadIdx.x & 31;
     uint8_t* ring = stream_smem + warp * SLOTS * STREAM_CHUNK;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(stream_smem + STREAM_RING_BYTES) + warp * SLOTS;
+    // one abort word per warp: the warps never meet, so nothing in the prologue needs a CTA-wide barrier
     volatile uint32_t* abort_word =
-        reinterpret_cast<volatile uint32_t*>(stream_smem + STREAM_RING_BYTES + STREAM_WARPS * SLOTS * 8);
+        reinterpret_cast<volatile uint32_t*>(stream_smem + STREAM_RING_BYTES + STREAM_WARPS * SLOTS * 8) + warp;
 
     const int64_t g = blockIdx.y;
     const int8_t* a = p.a + g * p.stride_a;
@@ -193,13 +194,13 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
     const int my_cols = (ncols > warp) ? (ncols - warp + STREAM_WARPS - 1) / STREAM_WARPS : 0;
     const int my_items = my_cols * chunks;
 
-    if (threadIdx.x == 0) *abort_word = 0u;
     if (lane == 0) {
+        *abort_word = 0u;
         for (int s = 0; s < SLOTS; ++s) mbar_init(&full_bar[s], 1);
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    __syncthreads();
+    __syncwarp();
 
     auto issue = [&](int item) {  // lane 0 only
         const int c = item / chunks, kc = item - c * chunks;
@@ -235,6 +236,33 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
     int keep[MR];
 #pragma unroll
     for (int r = 0; r < MR; ++r) keep[r] = 0;
+    // the scales of the columns this lane will write are fetched now, off the critical path
+    float sb_pre = 0.0f, sa_pre[MR];
+    if constexpr (!RAW) {
+        const int col = col_begin + warp + lane * STREAM_WARPS;
+        if (lane < my_cols) sb_pre = __ldg(p.sb + g * p.stride_sb + col);
+#pragma unroll
+        for (int r = 0; r < MR; ++r) sa_pre[r] = __ldg(p.sa + g * p.stride_sa + r);
+    }
+    auto flush_batch = [&](int first, int count) {
+        if (lane < count) {
+            const int col = col_begin + warp + (first + lane) * STREAM_WARPS;
+#pragma unroll
+            for (int r = 0; r < MR; ++r) {
+                if constexpr (RAW) {
+                    store_result<RAW>(p, g, r, col, keep[r]);
+                } else {
+                    const float sbv = (first == 0) ? sb_pre : __ldg(p.sb + g * p.stride_sb + col);
+                    __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.d) + g * p.stride_d +
+                                        static_cast<int64_t>(r) * p.ldd + col;
+                    const float sc = __fmul_rn(sa_pre[r], sbv);
+                    float y = __fmul_rn(__fmul_rn(sc, static_cast<float>(keep[r])), p.alpha);
+                    if (p.beta != 0.0f) y = __fadd_rn(y, __fmul_rn(p.beta, __bfloat162float(*dp)));
+                    *dp = __float2bfloat16_rn(y);
+                }
+            }
+        }
+    };
     bool ok = true;
     int done = 0;
     for (int c = 0; ok && c < my_cols; ++c) {
@@ -293,22 +321,11 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
             if (lane == (done & 31)) keep[r] = v;
         }
         ++done;
-        if ((done & 31) == 0) {
-            const int col = col_begin + warp + (done - 32 + lane) * STREAM_WARPS;
-#pragma unroll
-            for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
-        }
+        if ((done & 31) == 0) flush_batch(done - 32, 32);
     }
-    if (ok && (done & 31) != 0) {
-        const int first = done & ~31;
-        if (lane < done - first) {
-            const int col = col_begin + warp + (first + lane) * STREAM_WARPS;
-#pragma unroll
-            for (int r = 0; r < MR; ++r) store_result<RAW>(p, g, r, col, keep[r]);
-        }
-    }
-    // leave together; on the error path give copies still in flight a bounded time to land
-    __syncthreads();
+    if (ok && (done & 31) != 0) flush_batch(done & ~31, done & 31);
+    // on the error path give this warp's copies still in flight a bounded time to land
+    __syncwarp();
     if (*abort_word != 0u) {
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
@@ -520,7 +537,7 @@ int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
     const int sms = sm_count_cached();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     constexpr int NW = (MR == 1) ? 16 : 8;
-    const size_t smem = static_cast<size_t>(STREAM_RING_BYTES) + (STREAM_RING_BYTES / STREAM_CHUNK) * 8 + 16;
+    const size_t smem = static_cast<size_t>(STREAM_RING_BYTES) + (STREAM_RING_BYTES / STREAM_CHUNK) * 8 + NW * 4;
     auto kern = gemv_q8_rcr_stream_kernel<MR, RAW, NW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();

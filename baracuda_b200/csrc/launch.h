@@ -35,7 +35,8 @@ struct GemmDesc {
     float alpha;
     void* d;
     int64_t ldd;
-    int32_t force_block_n;  // 0 = choose; else 64 / 128 / 256 (tuning and tests)
+    int32_t force_block_n;  // 0 = choose; 64 / 128 / 256 = 1-CTA kernel with that N-tile; 512 = CTA-pair kernel
+    int32_t force_pair_tile_n;  // 0 = choose; else 256 / 224 / 192 / 128 (tuning and tests)
     // fused replicated output: the epilogue also stores each tile into these row-major
     // [M, peer_ld] buffers (one per rank, peer-mapped) at column offset peer_col0
     void* peer_d[8];

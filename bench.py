@@ -157,12 +157,12 @@ def run_reference(args, rank: int, world: int) -> None:
 
     from oracle import pyoracle as orc
 
-    rows = 8
+    rows = 128
     rng = np.random.default_rng(1238)
     a = rng.integers(0, 0x7E, size=(rows, C4_K), dtype=np.uint8)
     b = rng.integers(0, 0x7E, size=(C4_N, C4_K), dtype=np.uint8)
     for _ in range(max(args.warmup, 1)):
-        orc.gemm_e4m3_f32(a[:2], b, orc.RCR, 2, C4_N, C4_K)
+        orc.gemm_e4m3_f32(a[:32], b, orc.RCR, 32, C4_N, C4_K)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         orc.gemm_e4m3_f32(a, b, orc.RCR, rows, C4_N, C4_K)
@@ -361,13 +361,14 @@ def main() -> None:
 
     others = {}
     if world > 1:
-        # the optional replicated output: NCCL all-gather of the bf16 slices, rank-major [G, M, N/G]
+        from baracuda_b200 import parallel as par
+
+        ctx = par.TensorParallelContext.from_torch_distributed()
+        # (1) the optional replicated output the reference way: ncclAllGather of the contiguous bf16
+        #     slices on the same stream, rank-major [G, M, N/G] (issued by the C library)
         full = torch.empty((world, C4_M, n_local), dtype=torch.bfloat16, device="cuda")
-
-        def gathered_step():
-            plan.run(None, None, run_args)
-            dist.all_gather_into_tensor(full, d)
-
+        gather_plan = par.ColumnParallelQGemmPlan(ctx, C4_M, C4_N, C4_K, kind="fp8", gather=par.GATHER_NCCL)
+        gathered_step = lambda: gather_plan.forward(None, a_q, sa, w_q, sb, d, y_full=full)
         barrier()
         g_ms = event_time_ms(gathered_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
         barrier()
@@ -375,6 +376,26 @@ def main() -> None:
         others["with_nccl_all_gather"] = {
             "TFLOPs": ops_total * len(g_ms) / (g_total * 1e-3) / 1e12, "ms_per_step": g_total / len(g_ms),
             "gathered_bytes": C4_M * C4_N * 2, "layout": "rank-major [G, M, N/G]"}
+        # (2) fused: the GEMM epilogue stores every tile into all ranks' row-major [M, N] buffers over NVLink
+        try:
+            full_rm, ptrs = par.alloc_peer_buffers((C4_M, C4_N))
+            fused_plan = par.ColumnParallelQGemmPlan(ctx, C4_M, C4_N, C4_K, kind="fp8", gather=par.GATHER_FUSED_PEER_STORE)
+            scratch = torch.zeros(1, device="cuda")
+
+            def fused_step():
+                fused_plan.forward(None, a_q, sa, w_q, sb, d, peer_ptrs=ptrs, ldd_full=C4_N)
+                ctx.stream_barrier(scratch)
+
+            barrier()
+            f_ms = event_time_ms(fused_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+            barrier()
+            f_total = max_over_ranks(sum(f_ms))
+            others["with_fused_peer_stores"] = {
+                "TFLOPs": ops_total * len(f_ms) / (f_total * 1e-3) / 1e12, "ms_per_step": f_total / len(f_ms),
+                "layout": "row-major [M, N] on every rank", "nvlink_bytes_out_per_rank": C4_M * n_local * 2 * (world - 1)}
+        except Exception as exc:  # symmetric memory not available on this box
+            others["with_fused_peer_stores"] = {"unavailable": repr(exc)[:200]}
+        ctx.destroy()
 
     cpu_base = None
     if world == 1 and not args.no_others:

@@ -236,7 +236,8 @@ int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void
  * when one of its bounded barrier waits ran out (0 = none; 101..104 name the
  * waiting role).  Call it after synchronising the stream.
  * set_tuning: key 0 forces the GEMM tile (0 = automatic; 64, 128, 256 = 1-CTA kernel with that N-tile;
- * 512 = the 256 x 256 CTA-pair kernel); key 1 forces a GEMV kernel variant;
+ * 512 = the CTA-pair kernel); key 1 forces a GEMV kernel variant; key 2 forces the CTA-pair kernel's
+ * tile width (0 = automatic, 256, 224, 192, 128);
  * process-wide, meant for benchmarks and tests.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_q_device_status(void);

@@ -98,14 +98,15 @@ def test_config0_w8a8_128x1024x1024(oracle):
     assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
 
 
-@pytest.mark.parametrize("block_n", [64, 128, 256, 512])  # 512 = the CTA-pair kernel
-def test_every_tile_config_many_tiles_and_tails(oracle, block_n):
+@pytest.mark.parametrize("block_n,pair_tn", [(64, 0), (128, 0), (256, 0), (512, 256), (512, 224), (512, 192), (512, 128)])
+def test_every_tile_config_many_tiles_and_tails(oracle, block_n, pair_tn):
     """More tiles than SMs (persistent loop, both TMEM buffers, ring wrap-around) with ragged M, N and K."""
     m, n, k = 1100, 2100, 656
-    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=block_n)
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=block_n + pair_tn)
     acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
     want = oracle.dequant_s32_bf16(acc_ref, sa, sb)
-    bq.set_tuning(0, block_n)
+    bq.set_tuning(0, block_n)  # 512 = the CTA-pair kernel, pair_tn its tile width
+    bq.set_tuning(2, pair_tn)
     try:
         ldd = n + 3  # odd pitch: the scalar store path
         acc = _run_w8a8(m, n, k, aq, wq, raw=True).view(m, n).cpu().numpy()
@@ -113,6 +114,7 @@ def test_every_tile_config_many_tiles_and_tails(oracle, block_n):
         out_odd = _run_w8a8(m, n, k, aq, wq, sa, sb, ldd=ldd)
     finally:
         bq.set_tuning(0, 0)
+        bq.set_tuning(2, 0)
     assert oracle.compare_bitexact(acc_ref, acc) == -1
     assert oracle.compare_bitexact(want, bf16_bits(out).reshape(m, n)) == -1
     got_odd = bf16_bits(out_odd).reshape(m, ldd)
@@ -127,7 +129,7 @@ def test_cta_pair_kernel_small_and_odd_shapes(oracle, kind):
     and with ragged M / N / K, for both operand kinds."""
     bq.set_tuning(0, 512)
     try:
-        for (m, n, k) in [(256, 256, 128), (100, 70, 64), (513, 300, 1040), (129, 257, 4096)]:
+        for (m, n, k) in [(256, 256, 128), (100, 70, 64), (513, 300, 1040), (129, 257, 4096), (700, 3584, 512)]:
             if kind == "s8":
                 aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n)
                 acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
