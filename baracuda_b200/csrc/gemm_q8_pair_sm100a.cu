@@ -296,20 +296,21 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     return BQ_STATUS_OK;
 }
 
-// Tile width: the one that minimises (waves of pair tiles) x (tile width / relative efficiency).
+// Tile width: the kernel is fed through L2, so a tile costs what each CTA loads per K step
+// (128 rows of A plus TN/2 rows of the weight); pick the width that minimises
+// (waves of pair tiles) x (that cost).  Narrow tiles only win when they remove a whole wave.
 int pick_tile_n(const GemmDesc& g) {
     if (g.force_pair_tile_n != 0) return g.force_pair_tile_n;
     const int sms = sm_count_of_current_device();
     const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
     const int64_t m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
     const int cand[4] = {256, 224, 192, 128};
-    const double eff[4] = {1.0, 0.985, 0.965, 0.93};
     int best = 256;
-    double best_cost = 1e300;
+    int64_t best_cost = INT64_MAX;
     for (int i = 0; i < 4; ++i) {
         const int64_t tiles = m_tiles * ((g.n + cand[i] - 1) / cand[i]);
         const int64_t waves = (tiles + pairs - 1) / pairs;
-        const double cost = static_cast<double>(waves) * cand[i] / eff[i];
+        const int64_t cost = waves * (CTA_ROWS + cand[i] / 2);
         if (cost < best_cost) {
             best_cost = cost;
             best = cand[i];
