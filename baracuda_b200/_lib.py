@@ -39,6 +39,9 @@ SIGNATURES: dict[str, tuple] = {
         _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size": _GEMV_WS,
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run": (
+        _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp]),
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_capacity": (_sz, []),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size": _GEMV_WS,

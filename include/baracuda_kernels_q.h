@@ -162,6 +162,34 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(
 size_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
 
+/* The same GEMV for callers that must not allocate device memory (a serving loop that has
+ * given every byte to its own arena, a plugin host that forbids side allocations): the
+ * split-K scratch of the row-major weight layout comes from a fixed array inside the loaded
+ * library instead of a caller workspace, so only inputs and outputs are passed.
+ * This entry point has no counterpart in the reference.
+ *   - The array holds BARACUDA_Q_GEMV_STATIC_SCRATCH_BYTES (8 MiB) on every GPU that loads
+ *     the library, until the process exits.  A shape whose *_workspace_size exceeds it is
+ *     rejected with status 4; *_static_ws_capacity returns the limit.
+ *   - Nothing is allocated or freed, here or in any routine it calls.
+ *   - The first call on a device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls share the one array and it keeps whatever the last call left; the part that
+ *     must start at zero is cleared on the stream at the start of each call.  Two calls that
+ *     can overlap on the GPU (different streams, no ordering between them) race on it: order
+ *     them, or use the workspace entry point for one of them.
+ * Results are identical to baracuda_kernels_gemv_q8_m1_bf16_sm100a_run. */
+#define BARACUDA_Q_GEMV_STATIC_SCRATCH_BYTES (8u << 20)
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    float alpha, float beta,
+    const void* a, int64_t lda, int64_t stride_a,
+    const void* b, int64_t ldb, int64_t stride_b,
+    const void* scale_a, int64_t stride_scale_a,
+    const void* scale_b, int64_t stride_scale_b,
+    void* d, int64_t ldd, int64_t stride_d,
+    void* stream);
+size_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_capacity(void);
+
 /* The int32 sums of the same GEMV (D is int32); alpha 1, beta 0, no scales. */
 int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
