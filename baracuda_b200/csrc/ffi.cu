@@ -13,6 +13,7 @@ namespace {
 std::atomic<int32_t> g_force_block_n{0};
 std::atomic<int32_t> g_gemv_variant{0};
 std::atomic<int32_t> g_force_pair_tile_n{0};
+std::atomic<int32_t> g_gemv_pdl{0};
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -129,6 +130,7 @@ int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, in
     g.workspace = workspace;
     g.workspace_bytes = workspace_bytes;
     g.variant = g_gemv_variant.load(std::memory_order_relaxed);
+    g.pdl = g_gemv_pdl.load(std::memory_order_relaxed);
     return bq::launch_gemv_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -302,6 +304,9 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             return bq::BQ_STATUS_OK;
         case 1:
             g_gemv_variant.store(value);
+            return bq::BQ_STATUS_OK;
+        case 3:
+            g_gemv_pdl.store(value != 0 ? 1 : 0);
             return bq::BQ_STATUS_OK;
         case 2:
             if (value != 0 && value != 256 && value != 224 && value != 192 && value != 128)

@@ -45,6 +45,7 @@ struct GemvParams {
     int kslice_rows, num_kslices;
     int32_t* ws_partials;
     unsigned int* ws_tickets;
+    int pdl;  // launched with programmatic stream serialization: weights may be fetched before the dependency wait
 };
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
@@ -162,14 +163,16 @@ gemv_q8_rcr_kernel(const GemvParams p) {
 // About 190 KiB of weights are in flight per SM regardless of how the warps are scheduled,
 // which is what a 9 us HBM-bound kernel needs. ----
 constexpr int STREAM_CHUNK = 4096;        // bytes of K per ring slot
-constexpr int STREAM_RING_BYTES = 196608;  // all warps' rings together
+constexpr int STREAM_RING_FULL = 196608;  // all warps' rings together, one CTA per SM
+constexpr int STREAM_RING_HALF = 98304;   // two CTAs per SM, so the next launch's prologue can overlap this one
 constexpr long long STREAM_WAIT_LIMIT = 1LL << 31;
 
 // STREAM_WARPS warps; more activation rows need more registers per thread (the activations
 // live in registers), hence fewer warps with deeper rings.
-template <int MR, bool RAW, int STREAM_WARPS>
+template <int MR, bool RAW, int STREAM_WARPS, int RING_BYTES>
 __global__ void __launch_bounds__(STREAM_WARPS * 32, 1)
 gemv_q8_rcr_stream_kernel(const GemvParams p) {
+    constexpr int STREAM_RING_BYTES = RING_BYTES;
     constexpr int SLOTS = STREAM_RING_BYTES / STREAM_CHUNK / STREAM_WARPS;  // per warp
     extern __shared__ __align__(128) uint8_t stream_smem[];
     const int warp = threadIdx.x >> 5;
@@ -213,6 +216,13 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
     };
     if (lane == 0) {
         for (int i = 0; i < SLOTS && i < my_items; ++i) issue(i);
+    }
+    if (p.pdl) {
+        // The weights are static, so their first copies are already in flight.  Let the next launch in
+        // the stream start its own prologue, then wait until everything before this launch (the producer
+        // of the activations, the previous user of the output) has completed and is visible.
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
     }
 
     // activations: with a single K chunk every lane keeps its 8 x 16 bytes per row in registers
@@ -532,20 +542,38 @@ int sm_count_cached() {
     return n;
 }
 
-template <int MR, bool RAW>
-int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
-    const int sms = sm_count_cached();
-    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
-    constexpr int NW = (MR == 1) ? 16 : 8;
-    const size_t smem = static_cast<size_t>(STREAM_RING_BYTES) + (STREAM_RING_BYTES / STREAM_CHUNK) * 8 + NW * 4;
-    auto kern = gemv_q8_rcr_stream_kernel<MR, RAW, NW>;
+template <int MR, bool RAW, int NW, int RING>
+int32_t launch_rcr_stream_cfg(const GemvParams& p, int batch, int sms, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(RING) + (RING / STREAM_CHUNK) * 8 + NW * 4;
+    auto kern = gemv_q8_rcr_stream_kernel<MR, RAW, NW, RING>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
     }
     const int ctas = p.n < sms ? p.n : sms;
-    kern<<<dim3(ctas, batch), NW * 32, smem, stream>>>(p);
-    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas, batch, 1);
+    cfg.blockDim = dim3(NW * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    return BQ_STATUS_OK;
+}
+
+template <int MR, bool RAW>
+int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    if (p.pdl) return launch_rcr_stream_cfg<MR, RAW, 8, STREAM_RING_HALF>(p, batch, sms, stream);
+    return launch_rcr_stream_cfg<MR, RAW, (MR == 1) ? 16 : 8, STREAM_RING_FULL>(p, batch, sms, stream);
 }
 
 template <int MR, bool RAW>
@@ -602,6 +630,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     p.m = g.m; p.n = g.n; p.k = g.k;
     p.kslice_rows = 0; p.num_kslices = 1;
     p.ws_partials = nullptr; p.ws_tickets = nullptr;
+    p.pdl = g.pdl;
 
     // the streaming kernels need 16-byte alignment of every weight row segment they load
     bool fast = g.k > 0 && aligned16(g.a) && aligned16(g.b) && (g.stride_b % 16 == 0) && (g.ldb % 16 == 0);

@@ -78,6 +78,7 @@ struct GemvDesc {
     void* workspace;
     size_t workspace_bytes;
     int32_t variant;  // 0 = choose (tuning and tests)
+    int32_t pdl;      // 1: launch the streaming kernel with programmatic stream serialization
 };
 
 int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream);

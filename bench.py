@@ -148,7 +148,7 @@ def graph_launch_ms(launchers, replays: int = 20, warmup: int = 3) -> float:
 
 
 # --------------------------------------------------------------------------- reference arm
-def run_reference(args, rank: int, world: int) -> None:
+def run_reference(args, rank: int, world: int, out) -> None:
     """The CPU restatement of the reference's oracle, all host threads, on a bounded row sample of the
     headline configuration (the reference's own Rust interpreter cannot be built here)."""
     if rank != 0:
@@ -169,14 +169,14 @@ def run_reference(args, rank: int, world: int) -> None:
     dt = (time.perf_counter() - t0) / args.steps
     tflops = 2.0 * rows * C4_N * C4_K / dt / 1e12
     sample = f"{rows} of {C4_M} activation rows x all {C4_N} columns x K={C4_K} per step, f64 accumulate"
-    print(json.dumps({
+    print(file=out, flush=True, *[json.dumps({
         "impl": "reference", "metric": "fp8_gemm_throughput", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (f64 accumulate on the CPU)", "data": "synthetic",
         "config": {"workload": "c4_fp8_nshard", "M": C4_M, "N": C4_N, "K": C4_K, "sample": sample},
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": orc.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    })])
 
 
 # --------------------------------------------------------------------------- side workloads (1 GPU)
@@ -210,6 +210,16 @@ def side_workloads(peaks: dict) -> dict:
             out[f"gemv_{layout.value}_m{m}"] = {
                 "us": t * 1e6, "GBps": byts / t / 1e9, "algorithmic_bytes": byts,
                 "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"], "peak": f"{peaks['hbm_gbs']} GB/s of {peaks['source']}"}
+            if layout is bq.LayoutSku.Rcr and m <= 4:
+                # the same graph with programmatic dependent launch between consecutive GEMVs: each launch
+                # starts fetching its (static) weights while the previous one drains
+                bq.set_tuning(3, 1)
+                try:
+                    tp = graph_launch_ms(launchers) * 1e-3
+                finally:
+                    bq.set_tuning(3, 0)
+                out[f"gemv_{layout.value}_m{m}_pdl"] = {
+                    "us": tp * 1e6, "GBps": byts / tp / 1e9, "frac_of_hbm_peak": byts / tp / 1e9 / peaks["hbm_gbs"]}
         del weights
 
     def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False):
@@ -273,7 +283,16 @@ def cpu_baseline_sample() -> dict:
 
 
 # --------------------------------------------------------------------------- headline
+def claim_stdout():
+    """Keep stdout for the one JSON line: libraries that print to fd 1 (NCCL's version banner) go to stderr."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(saved, "w")
+
+
 def main() -> None:
+    out = claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -288,7 +307,7 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank, world, out)
         return
 
     import torch
@@ -427,7 +446,7 @@ def main() -> None:
             "device_status": status,
             "others": others,
         }
-        print(json.dumps(line))
+        print(json.dumps(line), file=out, flush=True)
     if world > 1:
         dist.destroy_process_group()
 

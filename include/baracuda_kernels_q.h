@@ -265,7 +265,10 @@ int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void
  * waiting role).  Call it after synchronising the stream.
  * set_tuning: key 0 forces the GEMM tile (0 = automatic; 64, 128, 256 = 1-CTA kernel with that N-tile;
  * 512 = the CTA-pair kernel); key 1 forces a GEMV kernel variant; key 2 forces the CTA-pair kernel's
- * tile width (0 = automatic, 256, 224, 192, 128);
+ * tile width (0 = automatic, 256, 224, 192, 128); key 3 = 1 launches the K-contiguous streaming GEMV with
+ * programmatic stream serialization: it starts fetching weights while the previous kernel of the stream is
+ * still finishing and touches activations, scales and outputs only after that kernel has completed — use it
+ * only when the kernel launched just before never writes the weights;
  * process-wide, meant for benchmarks and tests.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_q_device_status(void);

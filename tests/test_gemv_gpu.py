@@ -181,3 +181,24 @@ def test_workspace_contract():
         args.scale_a.data_ptr(), 0, args.scale_b.data_ptr(), 0, args.d.data_ptr(), 14336, 0, None, 0,
         torch.cuda.current_stream().cuda_stream)
     assert st == 4
+
+
+def test_dependent_launch_mode_gives_the_same_results(oracle):
+    """Programmatic stream serialization (tuning key 3): a chain of GEMVs on one stream, each consuming the
+    previous launch's output buffer as its canvas, equals the same chain launched normally."""
+    m, n, k = 2, 4096, 4096
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=44)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+    plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=bq.LayoutSku.Rcr))
+    a_d, b_d, sa_d, sb_d = dev(aq), dev(wq), dev(sa), dev(sb)
+    outs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
+    bq.set_tuning(3, 1)
+    try:
+        for d in outs:
+            plan.run(None, None, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d))
+        torch.cuda.synchronize()
+    finally:
+        bq.set_tuning(3, 0)
+    assert bq.device_status() == 0
+    for d in outs:
+        assert np.array_equal(bf16_bits(d), want)
