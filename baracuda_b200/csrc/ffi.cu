@@ -292,6 +292,8 @@ int32_t baracuda_kernels_q_device_status(void) {
     int32_t gemm = bq::read_and_clear_gemm_device_status();
     const int32_t pair = bq::read_and_clear_gemm_pair_device_status();
     if (gemm == 0) gemm = pair;
+    const int32_t wide = bq::read_and_clear_gemm_wide_device_status();
+    if (gemm == 0) gemm = wide;
     const int32_t gemv = bq::read_and_clear_gemv_device_status();
     return gemm != 0 ? gemm : gemv;
 }
@@ -299,7 +301,7 @@ int32_t baracuda_kernels_q_device_status(void) {
 int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
     switch (key) {
         case 0:
-            if (value != 0 && value != 64 && value != 128 && value != 256 && value != 512) return bq::BQ_STATUS_INVALID_PROBLEM;
+            if (value != 0 && value != 64 && value != 128 && value != 256 && value != 512 && value != 1024) return bq::BQ_STATUS_INVALID_PROBLEM;
             g_force_block_n.store(value);
             return bq::BQ_STATUS_OK;
         case 1:

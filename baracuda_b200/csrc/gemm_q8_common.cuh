@@ -104,4 +104,91 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
     }
 }
 
+
+// Converts 32 accumulator columns of this thread's row into 32 bf16 (four 16-byte packets).
+template <uint32_t KIND>
+__device__ __forceinline__ void dequant_pack_32(const GemmParams& p, const uint32_t (&r)[32], float sa_row,
+                                                const float* sb32, uint4 (&pk)[4]) {
+    float y[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        float acc;
+        if constexpr (KIND == UMMA_KIND_I8) {
+            acc = static_cast<float>(static_cast<int32_t>(r[j]));
+        } else {
+            acc = __uint_as_float(r[j]);
+        }
+        const float s = __fmul_rn(sa_row, sb32[j]);
+        y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(y[8 * v + 2], y[8 * v + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(y[8 * v + 4], y[8 * v + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(y[8 * v + 6], y[8 * v + 7]);
+        pk[v].x = *reinterpret_cast<uint32_t*>(&h0);
+        pk[v].y = *reinterpret_cast<uint32_t*>(&h1);
+        pk[v].z = *reinterpret_cast<uint32_t*>(&h2);
+        pk[v].w = *reinterpret_cast<uint32_t*>(&h3);
+    }
+}
+
+// bf16 epilogue for a 32-row x 64-column block owned by one warp (lane = row), with the rows
+// re-shaped through a 4 KiB shared-memory staging area so that every store instruction writes
+// four complete 128-byte row segments (8 lanes x 16 bytes each) instead of 32 scattered 16-byte
+// pieces.  That is what the local L2 wants and, in fused mode, what NVLink needs for the peer
+// stores.  `t_addr` is the TMEM address of the block's first column for this warp's lanes.
+// Requires 16-byte-aligned output rows (vec_store) and the full 64 columns in range.
+// `stage` is this warp's private 4 KiB buffer; `row_base` is the global row of lane 0.
+template <uint32_t KIND, bool FUSED>
+__device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t t_addr, int row_base, int lane,
+                                                  int col0, float sa_row, const float* sb64, uint4* stage) {
+    // 16-byte packet c of row r lives at stage[r * 8 + (c ^ (r & 7))]: conflict-free both ways
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(t_addr + static_cast<uint32_t>(half * 32), r);
+        tmem_ld_wait();
+        uint4 pk[4];
+        dequant_pack_32<KIND>(p, r, sa_row, sb64 + half * 32, pk);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const int c = half * 4 + v;
+            stage[lane * 8 + (c ^ (lane & 7))] = pk[v];
+        }
+    }
+    __syncwarp();
+    const int sub_row = lane >> 3;  // 0..3
+    const int c = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + sub_row;
+        const int row = row_base + rr;
+        const uint4 v = stage[rr * 8 + (c ^ (rr & 7))];
+        if (row < p.m) {
+            if (p.d != nullptr) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0 +
+                                          c * 8) = v;
+            }
+            if constexpr (FUSED) {
+                for (int pr = 0; pr < p.n_peers; ++pr) {
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
+                                              static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+// True when the 64-column block starting at col0 can take the coalesced path.
+template <bool FUSED>
+__device__ __forceinline__ bool block_64_ok(const GemmParams& p, int col0) {
+    bool ok = p.vec_store && (col0 + 64 <= p.n);
+    if constexpr (FUSED) ok = ok && p.peer_vec;
+    return ok;
+}
+
 }  // namespace bq

@@ -42,7 +42,8 @@ struct PairCfg {
     static constexpr int STAGE_BYTES = PAIR_A_BYTES + B_BYTES;  // a multiple of 1024 for TN % 16 == 0
     static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int SB_BYTES = 4 * TN * 4;
+    static constexpr int STG_BYTES = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes of output staging
+    static constexpr int SB_BYTES = STG_BYTES + 4 * TN * 4;
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
     static constexpr int SMEM_TOTAL = TILE_BYTES + SB_BYTES + BAR_BYTES + 1024;
     static constexpr int TMEM_COLS = (2 * TN <= 256) ? 256 : 512;
@@ -67,7 +68,8 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
-    float* sb_s = reinterpret_cast<float*>(smem + PAIR_TILE_BYTES);
+    uint4* stage_all = reinterpret_cast<uint4*>(smem + PAIR_TILE_BYTES);
+    float* sb_s = reinterpret_cast<float*>(smem + PAIR_TILE_BYTES + C::STG_BYTES);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + PAIR_TILE_BYTES + PAIR_SB_BYTES);
     uint64_t* empty_bar = full_bar + PAIR_STAGES;
     uint64_t* tfull_bar = empty_bar + PAIR_STAGES;
@@ -180,6 +182,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else {
         const int q = warp & 3;
+        uint4* stage_buf = stage_all + (warp - 2) * 256;
         int it = 0;
         for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++it) {
             const int buf = it & 1;
@@ -208,15 +211,28 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
+            {
+                int c = 0;
+                if constexpr (!RAW) {
+                    // 64 columns at a time through the warp's staging buffer (coalesced 128-byte row segments)
+                    for (; c + 2 <= PAIR_TILE_N / 32; c += 2) {
+                        const int col0 = n_blk * PAIR_TILE_N + c * 32;
+                        if (col0 >= p.n) break;  // warp-uniform
+                        if (!block_64_ok<FUSED>(p, col0)) break;
+                        epilogue_block_64<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
+                                                       sb_tile + c * 32, stage_buf);
+                    }
+                }
 #pragma unroll 1
-            for (int c = 0; c < PAIR_TILE_N / 32; ++c) {
-                const int col0 = n_blk * PAIR_TILE_N + c * 32;
-                if (col0 >= p.n) break;  // warp-uniform
-                uint32_t r[32];
-                __syncwarp();
-                tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
-                tmem_ld_wait();
-                if (row_ok) epilogue_store_32<KIND, RAW, FUSED>(p, row, col0, r, sa_row, sb_tile + c * 32);
+                for (; c < PAIR_TILE_N / 32; ++c) {
+                    const int col0 = n_blk * PAIR_TILE_N + c * 32;
+                    if (col0 >= p.n) break;  // warp-uniform
+                    uint32_t r[32];
+                    __syncwarp();
+                    tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
+                    tmem_ld_wait();
+                    if (row_ok) epilogue_store_32<KIND, RAW, FUSED>(p, row, col0, r, sa_row, sb_tile + c * 32);
+                }
             }
             tc_fence_before_sync();
             __syncwarp();

@@ -49,7 +49,8 @@ struct Smem {
     static constexpr int B_BYTES = BLOCK_N * BLOCK_K;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int SB_BYTES = 4 * BLOCK_N * 4;  // one private copy of the column scales per epilogue warp
+    static constexpr int STG_BYTES = 4 * 4096;        // per epilogue warp: 32 rows x 128 bytes of output staging
+    static constexpr int SB_BYTES = STG_BYTES + 4 * BLOCK_N * 4;  // + one private copy of the column scales per epilogue warp
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
     static constexpr int TOTAL = TILE_BYTES + SB_BYTES + BAR_BYTES + 1024;  // + alignment slack
     static constexpr int TMEM_COLS = (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64
@@ -69,7 +70,8 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
-    float* sb_s = reinterpret_cast<float*>(smem + L::TILE_BYTES);
+    uint4* stage_all = reinterpret_cast<uint4*>(smem + L::TILE_BYTES);
+    float* sb_s = reinterpret_cast<float*>(smem + L::TILE_BYTES + L::STG_BYTES);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::TILE_BYTES + L::SB_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
     uint64_t* tfull_bar = empty_bar + STAGES;
@@ -175,6 +177,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
     } else {
         const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint4* stage_buf = stage_all + (warp - 2) * 256;
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int buf = it & 1;
@@ -205,15 +208,28 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * BLOCK_N);
+            {
+                int c = 0;
+                if constexpr (!RAW) {
+                    // 64 columns at a time through the warp's staging buffer (coalesced 128-byte row segments)
+                    for (; c + 2 <= BLOCK_N / 32; c += 2) {
+                        const int col0 = n_blk * BLOCK_N + c * 32;
+                        if (col0 >= p.n) break;  // warp-uniform
+                        if (!block_64_ok<FUSED>(p, col0)) break;
+                        epilogue_block_64<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * BLOCK_M + q * 32, lane, col0, sa_row,
+                                                       sb_tile + c * 32, stage_buf);
+                    }
+                }
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
-                const int col0 = n_blk * BLOCK_N + c * 32;
-                if (col0 >= p.n) break;  // warp-uniform
-                uint32_t r[32];
-                __syncwarp();
-                tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
-                tmem_ld_wait();
-                if (row_ok) epilogue_store_32<KIND, RAW, FUSED>(p, row, col0, r, sa_row, sb_tile + c * 32);
+                for (; c < BLOCK_N / 32; ++c) {
+                    const int col0 = n_blk * BLOCK_N + c * 32;
+                    if (col0 >= p.n) break;  // warp-uniform
+                    uint32_t r[32];
+                    __syncwarp();
+                    tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
+                    tmem_ld_wait();
+                    if (row_ok) epilogue_store_32<KIND, RAW, FUSED>(p, row, col0, r, sa_row, sb_tile + c * 32);
+                }
             }
             tc_fence_before_sync();
             mbar_arrive(&tempty_bar[buf]);
@@ -332,6 +348,7 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
+    if (g.force_block_n == 1024) return launch_gemm_q8_wide(g, stream);
     // large problems: 256 x 256 tiles on CTA pairs (force_block_n 512 forces it, 256/128/64 forces it off)
     if ((g.force_block_n == 0 && g.m >= 512 && g.n >= 512 && m_tiles * ((g.n + 255) / 256) >= sms) ||
         g.force_block_n == 512) {

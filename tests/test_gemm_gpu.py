@@ -98,7 +98,7 @@ def test_config0_w8a8_128x1024x1024(oracle):
     assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
 
 
-@pytest.mark.parametrize("block_n,pair_tn", [(64, 0), (128, 0), (256, 0), (512, 256), (512, 224), (512, 192), (512, 128)])
+@pytest.mark.parametrize("block_n,pair_tn", [(64, 0), (128, 0), (256, 0), (512, 256), (512, 224), (512, 192), (512, 128), (1024, 0)])  # 1024 = 256x512 pair tiles
 def test_every_tile_config_many_tiles_and_tails(oracle, block_n, pair_tn):
     """More tiles than SMs (persistent loop, both TMEM buffers, ring wrap-around) with ragged M, N and K."""
     m, n, k = 1100, 2100, 656
@@ -123,13 +123,14 @@ def test_every_tile_config_many_tiles_and_tails(oracle, block_n, pair_tn):
     assert np.all(got_odd[:, n:] == canary)
 
 
+@pytest.mark.parametrize("tile", [512, 1024])
 @pytest.mark.parametrize("kind", ["s8", "fp8"])
-def test_cta_pair_kernel_small_and_odd_shapes(oracle, kind):
+def test_cta_pair_kernel_small_and_odd_shapes(oracle, kind, tile):
     """The 256 x 256 CTA-pair kernel forced onto shapes with a single tile, with M below one CTA's rows,
     and with ragged M / N / K, for both operand kinds."""
-    bq.set_tuning(0, 512)
+    bq.set_tuning(0, tile)
     try:
-        for (m, n, k) in [(256, 256, 128), (100, 70, 64), (513, 300, 1040), (129, 257, 4096), (700, 3584, 512)]:
+        for (m, n, k) in [(256, 256, 128), (100, 70, 64), (513, 300, 1040), (129, 257, 4096), (700, 3584, 512), (300, 1100, 256), (2304, 1536, 384)]:
             if kind == "s8":
                 aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n)
                 acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
