@@ -14,6 +14,7 @@ std::atomic<int32_t> g_force_block_n{0};
 std::atomic<int32_t> g_gemv_variant{0};
 std::atomic<int32_t> g_force_pair_tile_n{0};
 std::atomic<int32_t> g_gemv_pdl{0};
+std::atomic<int32_t> g_direct_stores{0};
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -69,6 +70,7 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
     g.ldd = ldd;
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
     g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.direct_stores = g_direct_stores.load(std::memory_order_relaxed);
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
@@ -170,6 +172,7 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     g.ldd = ldd;
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
     g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.direct_stores = g_direct_stores.load(std::memory_order_relaxed);
     g.n_peers = world;
     g.peer_ld = peer_ld;
     g.peer_col0 = rank * n;
@@ -309,6 +312,10 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             return bq::BQ_STATUS_OK;
         case 3:
             g_gemv_pdl.store(value != 0 ? 1 : 0);
+            return bq::BQ_STATUS_OK;
+        case 4:
+            if (value < 0 || value > 2) return bq::BQ_STATUS_INVALID_PROBLEM;
+            g_direct_stores.store(value);
             return bq::BQ_STATUS_OK;
         case 2:
             if (value != 0 && value != 256 && value != 224 && value != 192 && value != 128)

@@ -27,6 +27,7 @@ struct GemmParams {
     int64_t peer_ld;
     int peer_col0;
     int peer_vec;  // 1 when every peer buffer allows 16-byte row stores at its column offset
+    int coalesce;  // 1: 64-column blocks go through the shared-memory staging path
 };
 
 // One thread, one output row, 32 consecutive columns starting at col0 (a multiple of 32).
@@ -186,7 +187,7 @@ __device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t 
 // True when the 64-column block starting at col0 can take the coalesced path.
 template <bool FUSED>
 __device__ __forceinline__ bool block_64_ok(const GemmParams& p, int col0) {
-    bool ok = p.vec_store && (col0 + 64 <= p.n);
+    bool ok = p.coalesce && p.vec_store && (col0 + 64 <= p.n);
     if constexpr (FUSED) ok = ok && p.peer_vec;
     return ok;
 }

@@ -338,6 +338,7 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     }
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+    p.coalesce = (g.direct_stores == 2) || (g.direct_stores == 0 && (FUSED || (tiles + grid - 1) / grid <= 6));
     kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(map_a, map_b, p);
     return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
 }

@@ -314,6 +314,7 @@ int32_t launch_wide(const GemmDesc& g, cudaStream_t stream) {
     }
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    p.coalesce = g.direct_stores == 1 ? 0 : 1;  // the epilogue of this kernel is partly exposed: staged stores win
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
     cfg.blockDim = dim3(W_THREADS, 1, 1);

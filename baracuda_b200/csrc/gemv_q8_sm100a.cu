@@ -341,6 +341,152 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
     }
 }
 
+// ---- weights stored [N, K], several activation rows (m = 2..8): the same per-warp bulk-copy
+// streaming, but the dot products run on the tensor cores.  An item is 8 weight rows x 1 KiB of K;
+// the warp feeds it to mma.sync m16n8k32 as the B operand (8 output columns), the activations
+// (8 rows, zero beyond m) are the A operand read from shared memory, and the instruction itself
+// sums over K across the lanes, so no shuffles are needed and the cost per weight byte does not
+// grow with m.  Items of one column group that belong to different K chunks (and warps) meet in a
+// small shared-memory accumulator. ----
+constexpr int MMA_KCHUNK = 1024;               // bytes of K per item and row
+constexpr int MMA_PITCH = MMA_KCHUNK + 64;     // row pitch in the ring: 16-byte reads of 8 rows hit 8 distinct bank groups
+constexpr int MMA_COLS = 8;                    // weight rows (output columns) per item
+constexpr int MMA_RING = 2;                    // items in flight per warp
+constexpr int MMA_WARPS = 8;
+constexpr int MMA_ITEM_BYTES = MMA_COLS * MMA_PITCH;
+constexpr int MMA_MAX_GROUPS = 64;             // column groups per CTA the accumulator holds
+constexpr int MMA_MAX_K = 8192;
+
+__device__ __forceinline__ void mma_s8_16x8x32(int (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8..15 of A are zero (a1 = a3 = 0): only 8 activation rows exist
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <bool RAW>
+__global__ void __launch_bounds__(MMA_WARPS * 32, 1)
+gemv_q8_rcr_mma_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t mma_smem[];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int gq = lane >> 2;  // MMA group id: activation row for A and D, weight row (column) for B
+    const int tq = lane & 3;
+    const int xpitch = p.k + 64;
+    uint8_t* ring = mma_smem + warp * MMA_RING * MMA_ITEM_BYTES;
+    uint8_t* xs = mma_smem + MMA_WARPS * MMA_RING * MMA_ITEM_BYTES;
+    int* acc_s = reinterpret_cast<int*>(xs + 8 * xpitch);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(acc_s + MMA_MAX_GROUPS * 64) + warp * MMA_RING;
+    volatile uint32_t* abort_word =
+        reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint64_t*>(acc_s + MMA_MAX_GROUPS * 64) + MMA_WARPS * MMA_RING) + warp;
+
+    const int64_t g = blockIdx.y;
+    const int8_t* a = p.a + g * p.stride_a;
+    const int8_t* b = p.b + g * p.stride_b;
+
+    // this CTA's contiguous share of the 8-column groups
+    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = gridDim.x;
+    const int base = total_groups / ctas, rem = total_groups % ctas;
+    const int bx = static_cast<int>(blockIdx.x);
+    const int group_begin = bx * base + (bx < rem ? bx : rem);
+    const int ngroups = base + (bx < rem ? 1 : 0);
+    const int chunks = (p.k + MMA_KCHUNK - 1) / MMA_KCHUNK;
+    const int items = ngroups * chunks;
+    const int my_items = (items > warp) ? (items - warp + MMA_WARPS - 1) / MMA_WARPS : 0;
+
+    if (lane == 0) {
+        *abort_word = 0u;
+        for (int s = 0; s < MMA_RING; ++s) mbar_init(&full_bar[s], 1);
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    __syncwarp();
+
+    auto issue = [&](int mine) {  // lane 0 only; `mine` counts this warp's items
+        const int item = warp + mine * MMA_WARPS;
+        const int gi = item / chunks, kc = item - gi * chunks;
+        const int k0 = kc * MMA_KCHUNK;
+        const uint32_t bytes = static_cast<uint32_t>((p.k - k0 < MMA_KCHUNK) ? (p.k - k0) : MMA_KCHUNK);
+        const int col0 = (group_begin + gi) * MMA_COLS;
+        const int rows = (p.n - col0 < MMA_COLS) ? (p.n - col0) : MMA_COLS;
+        const int slot = mine % MMA_RING;
+        mbar_arrive_expect_tx(&full_bar[slot], bytes * static_cast<uint32_t>(rows));
+        for (int r = 0; r < rows; ++r) {
+            bulk_load_1d(ring + slot * MMA_ITEM_BYTES + r * MMA_PITCH, b + static_cast<int64_t>(col0 + r) * p.ldb + k0, bytes,
+                         &full_bar[slot]);
+        }
+    };
+    if (lane == 0) {
+        for (int i = 0; i < MMA_RING && i < my_items; ++i) issue(i);
+    }
+    if (p.pdl) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+
+    // activations into shared memory (rows beyond m are zero), accumulators cleared
+    {
+        const int k16 = p.k >> 4;
+        for (int i = threadIdx.x; i < 8 * k16; i += MMA_WARPS * 32) {
+            const int r = i / k16, c = i - r * k16;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < p.m) v = __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + c);
+            *reinterpret_cast<uint4*>(xs + r * xpitch + c * 16) = v;
+        }
+        for (int i = threadIdx.x; i < ngroups * 64; i += MMA_WARPS * 32) acc_s[i] = 0;
+    }
+    __syncthreads();
+
+    bool ok = true;
+    for (int mine = 0; mine < my_items; ++mine) {
+        const int item = warp + mine * MMA_WARPS;
+        const int gi = item / chunks, kc = item - gi * chunks;
+        const int k0 = kc * MMA_KCHUNK;
+        const int bytes = (p.k - k0 < MMA_KCHUNK) ? (p.k - k0) : MMA_KCHUNK;  // a multiple of 64 on this path
+        const int slot = mine % MMA_RING;
+        const uint32_t parity = (mine / MMA_RING) & 1;
+        if (!mbar_wait_bounded(&full_bar[slot], parity, abort_word, STREAM_WAIT_LIMIT)) {
+            *abort_word = 1u;
+            atomicCAS(&g_gemv_device_status, 0, 203);
+            ok = false;
+            break;
+        }
+        const uint8_t* wrow = ring + slot * MMA_ITEM_BYTES + gq * MMA_PITCH + tq * 16;
+        const uint8_t* xrow = xs + gq * xpitch + k0 + tq * 16;
+        int d[4] = {0, 0, 0, 0};
+#pragma unroll 4
+        for (int kb = 0; kb < bytes; kb += 64) {
+            const uint4 w = *reinterpret_cast<const uint4*>(wrow + kb);
+            const uint4 x = *reinterpret_cast<const uint4*>(xrow + kb);
+            mma_s8_16x8x32(d, x.x, x.y, w.x, w.y);
+            mma_s8_16x8x32(d, x.z, x.w, w.z, w.w);
+        }
+        __syncwarp();  // the whole item has been read: its slot can be refilled
+        if (lane == 0 && mine + MMA_RING < my_items) {
+            fence_proxy_async_smem();
+            issue(mine + MMA_RING);
+        }
+        // d[0], d[1]: activation row gq, columns 2*tq and 2*tq+1 of this group (d[2], d[3] belong to the zero rows)
+        if (gq < p.m) {
+            atomicAdd(&acc_s[gi * 64 + gq * 8 + 2 * tq], d[0]);
+            atomicAdd(&acc_s[gi * 64 + gq * 8 + 2 * tq + 1], d[1]);
+        }
+    }
+    (void)ok;
+    __syncthreads();
+    for (int i = threadIdx.x; i < ngroups * 64; i += MMA_WARPS * 32) {
+        const int gi = i >> 6, r = (i >> 3) & 7, c = i & 7;
+        const int col = (group_begin + gi) * MMA_COLS + c;
+        if (r < p.m && col < p.n) store_result<RAW>(p, g, r, col, acc_s[i]);
+    }
+    __syncwarp();
+    if (*abort_word != 0u) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    }
+}
+
 // ---- weights stored [K, N] (N contiguous): a thread owns 16 adjacent columns,
 // a CTA owns a 512-column strip of one K slice; slices meet in the workspace ----
 __device__ __forceinline__ void transpose4x4_bytes(uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3,
@@ -576,6 +722,47 @@ int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
     return launch_rcr_stream_cfg<MR, RAW, (MR == 1) ? 16 : 8, STREAM_RING_FULL>(p, batch, sms, stream);
 }
 
+template <bool RAW>
+int32_t launch_rcr_mma(const GemvParams& p, int batch, cudaStream_t stream) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    const size_t smem = static_cast<size_t>(MMA_WARPS) * MMA_RING * MMA_ITEM_BYTES + 8 * static_cast<size_t>(p.k + 64) +
+                        MMA_MAX_GROUPS * 64 * 4 + MMA_WARPS * MMA_RING * 8 + MMA_WARPS * 4;
+    auto kern = gemv_q8_rcr_mma_kernel<RAW>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = total_groups < sms ? total_groups : sms;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ctas, batch, 1);
+    cfg.blockDim = dim3(MMA_WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    return BQ_STATUS_OK;
+}
+
+// The tensor-core GEMV serves K-contiguous weights when K is a multiple of 64 bytes, fits the
+// activation staging, and every CTA's share of 8-column groups fits the shared accumulator.
+bool mma_gemv_ok(const GemvParams& p) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return false;
+    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = total_groups < sms ? total_groups : sms;
+    const int per_cta = (total_groups + ctas - 1) / ctas;
+    return (p.k % 64 == 0) && p.k <= MMA_MAX_K && per_cta <= MMA_MAX_GROUPS;
+}
+
 template <int MR, bool RAW>
 int32_t launch_rcr(const GemvParams& p, int batch, cudaStream_t stream) {
     // enough warps to cover the machine several times over, else fewer columns per warp
@@ -644,6 +831,12 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
         const int blocks = (g.n + GEMV_WARPS - 1) / GEMV_WARPS;
         gemv_q8_generic_kernel<RAW><<<dim3(blocks, g.batch), GEMV_THREADS, 0, stream>>>(p, g.layout);
         return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+    }
+    // K-contiguous weights, two or more activation rows: tensor-core streaming kernel
+    // (variant 3 forces it also for m == 1, variant 2 and 1 keep it off)
+    if (g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
+        ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3)) {
+        return launch_rcr_mma<RAW>(p, g.batch, stream);
     }
     // K-contiguous weights with few activation rows: the bulk-copy streaming kernel
     // (variant 2 forces it off, variant 1 forces it on where it is legal)

@@ -268,7 +268,8 @@ int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void
  * tile width (0 = automatic, 256, 224, 192, 128); key 3 = 1 launches the K-contiguous streaming GEMV with
  * programmatic stream serialization: it starts fetching weights while the previous kernel of the stream is
  * still finishing and touches activations, scales and outputs only after that kernel has completed — use it
- * only when the kernel launched just before never writes the weights;
+ * only when the kernel launched just before never writes the weights; key 4 picks the GEMM epilogue's store
+ * path (0 = automatic, 1 = per-thread direct stores, 2 = rows staged through shared memory);
  * process-wide, meant for benchmarks and tests.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_q_device_status(void);

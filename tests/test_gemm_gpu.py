@@ -147,6 +147,23 @@ def test_cta_pair_kernel_small_and_odd_shapes(oracle, kind, tile):
         bq.set_tuning(0, 0)
 
 
+@pytest.mark.parametrize("store_path", [1, 2])
+def test_both_epilogue_store_paths(oracle, store_path):
+    """Per-thread direct stores and the shared-memory staged stores give the same bytes."""
+    m, n, k = 700, 1216, 512
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=3)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+    bq.set_tuning(4, store_path)
+    try:
+        for tile in (256, 512):
+            bq.set_tuning(0, tile)
+            out = _run_w8a8(m, n, k, aq, wq, sa, sb)
+            assert oracle.compare_bitexact(want, bf16_bits(out).reshape(m, n)) == -1, (store_path, tile)
+    finally:
+        bq.set_tuning(0, 0)
+        bq.set_tuning(4, 0)
+
+
 def test_alpha_and_empty_k(oracle):
     m, n, k = 130, 200, 256
     aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=8)
