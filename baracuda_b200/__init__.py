@@ -33,6 +33,11 @@ from .plans import (  # noqa: F401
     GemvQ8Plan,
     QGemmArgs,
     QGemmDescriptor,
+    QuantizedLinearArgs,
+    QuantizedLinearDescriptor,
+    QuantizedLinearPlan,
+    QuantizePerTokenDescriptor,
+    QuantizePerTokenPlan,
     W8A8GemmPlan,
     device_status,
     set_tuning,

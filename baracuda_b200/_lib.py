@@ -45,6 +45,10 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size": _GEMV_WS,
+    "baracuda_kernels_quantize_per_token_sym_f32_s8_sm100a_run": (_i32, [_i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_quantize_per_token_sym_bf16_s8_sm100a_run": (_i32, [_i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_quantize_per_token_sym_f32_e4m3_sm100a_run": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_quantize_per_token_sym_bf16_e4m3_sm100a_run": (_i32, [_i32, _i32, _vp, _i64, _vp, _vp, _i64] + _TAIL),
     "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run": (
         _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _f32,
                _vp, _vp, _i64] + _TAIL),

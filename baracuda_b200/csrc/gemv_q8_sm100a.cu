@@ -348,12 +348,8 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
 // sums over K across the lanes, so no shuffles are needed and the cost per weight byte does not
 // grow with m.  Items of one column group that belong to different K chunks (and warps) meet in a
 // small shared-memory accumulator. ----
-constexpr int MMA_KCHUNK = 1024;               // bytes of K per item and row
-constexpr int MMA_PITCH = MMA_KCHUNK + 64;     // row pitch in the ring: 16-byte reads of 8 rows hit 8 distinct bank groups
 constexpr int MMA_COLS = 8;                    // weight rows (output columns) per item
 constexpr int MMA_RING = 2;                    // items in flight per warp
-constexpr int MMA_WARPS = 8;
-constexpr int MMA_ITEM_BYTES = MMA_COLS * MMA_PITCH;
 constexpr int MMA_MAX_GROUPS = 64;             // column groups per CTA the accumulator holds
 constexpr int MMA_MAX_K = 8192;
 
@@ -365,9 +361,13 @@ __device__ __forceinline__ void mma_s8_16x8x32(int (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
 }
 
-template <bool RAW>
+// MMA_KCHUNK: bytes of K per item and row; MMA_WARPS: streaming warps.  The row pitch in the ring is
+// KCHUNK + 64 so that 16-byte reads of 8 rows hit 8 distinct bank groups.
+template <bool RAW, int MMA_KCHUNK, int MMA_WARPS>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 1)
 gemv_q8_rcr_mma_kernel(const GemvParams p) {
+    constexpr int MMA_PITCH = MMA_KCHUNK + 64;
+    constexpr int MMA_ITEM_BYTES = MMA_COLS * MMA_PITCH;
     extern __shared__ __align__(128) uint8_t mma_smem[];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -377,21 +377,24 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     uint8_t* ring = mma_smem + warp * MMA_RING * MMA_ITEM_BYTES;
     uint8_t* xs = mma_smem + MMA_WARPS * MMA_RING * MMA_ITEM_BYTES;
     int* acc_s = reinterpret_cast<int*>(xs + 8 * xpitch);
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(acc_s + MMA_MAX_GROUPS * 64) + warp * MMA_RING;
-    volatile uint32_t* abort_word =
-        reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint64_t*>(acc_s + MMA_MAX_GROUPS * 64) + MMA_WARPS * MMA_RING) + warp;
+    float* sb_s = reinterpret_cast<float*>(acc_s + MMA_MAX_GROUPS * 64);  // this CTA's column scales
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sb_s + MMA_MAX_GROUPS * MMA_COLS);
+    uint64_t* full_bar = bars + warp * MMA_RING;
+    volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + MMA_WARPS * MMA_RING) + warp;
 
     const int64_t g = blockIdx.y;
     const int8_t* a = p.a + g * p.stride_a;
     const int8_t* b = p.b + g * p.stride_b;
 
-    // this CTA's contiguous share of the 8-column groups
-    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
+    // this CTA's contiguous share of the output columns (balanced to one column), cut into groups of 8;
+    // the last group may be short, in which case only its real rows are copied
     const int ctas = gridDim.x;
-    const int base = total_groups / ctas, rem = total_groups % ctas;
+    const int base = p.n / ctas, rem = p.n % ctas;
     const int bx = static_cast<int>(blockIdx.x);
-    const int group_begin = bx * base + (bx < rem ? bx : rem);
-    const int ngroups = base + (bx < rem ? 1 : 0);
+    const int col_begin = bx * base + (bx < rem ? bx : rem);
+    const int ncols = base + (bx < rem ? 1 : 0);
+    const int col_end = col_begin + ncols;
+    const int ngroups = (ncols + MMA_COLS - 1) / MMA_COLS;
     const int chunks = (p.k + MMA_KCHUNK - 1) / MMA_KCHUNK;
     const int items = ngroups * chunks;
     const int my_items = (items > warp) ? (items - warp + MMA_WARPS - 1) / MMA_WARPS : 0;
@@ -409,8 +412,8 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         const int gi = item / chunks, kc = item - gi * chunks;
         const int k0 = kc * MMA_KCHUNK;
         const uint32_t bytes = static_cast<uint32_t>((p.k - k0 < MMA_KCHUNK) ? (p.k - k0) : MMA_KCHUNK);
-        const int col0 = (group_begin + gi) * MMA_COLS;
-        const int rows = (p.n - col0 < MMA_COLS) ? (p.n - col0) : MMA_COLS;
+        const int col0 = col_begin + gi * MMA_COLS;
+        const int rows = (col_end - col0 < MMA_COLS) ? (col_end - col0) : MMA_COLS;
         const int slot = mine % MMA_RING;
         mbar_arrive_expect_tx(&full_bar[slot], bytes * static_cast<uint32_t>(rows));
         for (int r = 0; r < rows; ++r) {
@@ -429,13 +432,18 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     // activations into shared memory (rows beyond m are zero), accumulators cleared
     {
         const int k16 = p.k >> 4;
-        for (int i = threadIdx.x; i < 8 * k16; i += MMA_WARPS * 32) {
+        for (int i = threadIdx.x; i < p.m * k16; i += MMA_WARPS * 32) {
             const int r = i / k16, c = i - r * k16;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < p.m) v = __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + c);
-            *reinterpret_cast<uint4*>(xs + r * xpitch + c * 16) = v;
+            *reinterpret_cast<uint4*>(xs + r * xpitch + c * 16) =
+                __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + c);
         }
         for (int i = threadIdx.x; i < ngroups * 64; i += MMA_WARPS * 32) acc_s[i] = 0;
+        if constexpr (!RAW) {  // scales fetched now, off the tail of the kernel
+            for (int i = threadIdx.x; i < ngroups * MMA_COLS; i += MMA_WARPS * 32) {
+                const int col = col_begin + i;
+                sb_s[i] = col < col_end ? __ldg(p.sb + g * p.stride_sb + col) : 0.0f;
+            }
+        }
     }
     __syncthreads();
 
@@ -455,14 +463,24 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         }
         const uint8_t* wrow = ring + slot * MMA_ITEM_BYTES + gq * MMA_PITCH + tq * 16;
         const uint8_t* xrow = xs + gq * xpitch + k0 + tq * 16;
-        int d[4] = {0, 0, 0, 0};
-#pragma unroll 4
-        for (int kb = 0; kb < bytes; kb += 64) {
+        const bool has_row = gq < p.m;  // activation rows beyond m are zero operands, never read
+        // four independent accumulators: consecutive MMAs never wait on each other's result
+        int d[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0}, d3[4] = {0, 0, 0, 0};
+#pragma unroll 2
+        for (int kb = 0; kb < bytes; kb += 128) {
             const uint4 w = *reinterpret_cast<const uint4*>(wrow + kb);
-            const uint4 x = *reinterpret_cast<const uint4*>(xrow + kb);
+            const uint4 x = has_row ? *reinterpret_cast<const uint4*>(xrow + kb) : make_uint4(0, 0, 0, 0);
             mma_s8_16x8x32(d, x.x, x.y, w.x, w.y);
-            mma_s8_16x8x32(d, x.z, x.w, w.z, w.w);
+            mma_s8_16x8x32(d1, x.z, x.w, w.z, w.w);
+            if (kb + 64 < bytes) {
+                const uint4 w2 = *reinterpret_cast<const uint4*>(wrow + kb + 64);
+                const uint4 x2 = has_row ? *reinterpret_cast<const uint4*>(xrow + kb + 64) : make_uint4(0, 0, 0, 0);
+                mma_s8_16x8x32(d2, x2.x, x2.y, w2.x, w2.y);
+                mma_s8_16x8x32(d3, x2.z, x2.w, w2.z, w2.w);
+            }
         }
+        d[0] += d1[0] + d2[0] + d3[0];
+        d[1] += d1[1] + d2[1] + d3[1];
         __syncwarp();  // the whole item has been read: its slot can be refilled
         if (lane == 0 && mine + MMA_RING < my_items) {
             fence_proxy_async_smem();
@@ -478,8 +496,19 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     __syncthreads();
     for (int i = threadIdx.x; i < ngroups * 64; i += MMA_WARPS * 32) {
         const int gi = i >> 6, r = (i >> 3) & 7, c = i & 7;
-        const int col = (group_begin + gi) * MMA_COLS + c;
-        if (r < p.m && col < p.n) store_result<RAW>(p, g, r, col, acc_s[i]);
+        const int col = col_begin + gi * MMA_COLS + c;
+        if (r < p.m && col < col_end) {
+            if constexpr (RAW) {
+                store_result<RAW>(p, g, r, col, acc_s[i]);
+            } else {
+                __nv_bfloat16* dp =
+                    reinterpret_cast<__nv_bfloat16*>(p.d) + g * p.stride_d + static_cast<int64_t>(r) * p.ldd + col;
+                const float sc = __fmul_rn(__ldg(p.sa + g * p.stride_sa + r), sb_s[gi * MMA_COLS + c]);
+                float y = __fmul_rn(__fmul_rn(sc, static_cast<float>(acc_s[i])), p.alpha);
+                if (p.beta != 0.0f) y = __fadd_rn(y, __fmul_rn(p.beta, __bfloat162float(*dp)));
+                *dp = __float2bfloat16_rn(y);
+            }
+        }
     }
     __syncwarp();
     if (*abort_word != 0u) {
@@ -722,22 +751,20 @@ int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
     return launch_rcr_stream_cfg<MR, RAW, (MR == 1) ? 16 : 8, STREAM_RING_FULL>(p, batch, sms, stream);
 }
 
-template <bool RAW>
-int32_t launch_rcr_mma(const GemvParams& p, int batch, cudaStream_t stream) {
-    const int sms = sm_count_cached();
-    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
-    const size_t smem = static_cast<size_t>(MMA_WARPS) * MMA_RING * MMA_ITEM_BYTES + 8 * static_cast<size_t>(p.k + 64) +
-                        MMA_MAX_GROUPS * 64 * 4 + MMA_WARPS * MMA_RING * 8 + MMA_WARPS * 4;
-    auto kern = gemv_q8_rcr_mma_kernel<RAW>;
+template <bool RAW, int KCHUNK, int WARPS>
+int32_t launch_rcr_mma_cfg(const GemvParams& p, int batch, int sms, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(WARPS) * MMA_RING * MMA_COLS * (KCHUNK + 64) + 8 * static_cast<size_t>(p.k + 64) +
+                        MMA_MAX_GROUPS * 64 * 4 + MMA_MAX_GROUPS * MMA_COLS * 4 + WARPS * MMA_RING * 8 + WARPS * 4;
+    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
     }
-    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
-    const int ctas = total_groups < sms ? total_groups : sms;
+    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;  // no more CTAs than 8-column groups
+    const int ctas = want < sms ? want : sms;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, batch, 1);
-    cfg.blockDim = dim3(MMA_WARPS * 32, 1, 1);
+    cfg.blockDim = dim3(WARPS * 32, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -752,14 +779,26 @@ int32_t launch_rcr_mma(const GemvParams& p, int batch, cudaStream_t stream) {
     return BQ_STATUS_OK;
 }
 
+template <bool RAW>
+int32_t launch_rcr_mma(const GemvParams& p, int batch, int shape_variant, cudaStream_t stream) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    // 2 KiB copies on 4 warps when the activations leave room for the bigger ring, else 1 KiB copies on 8 warps
+    // 1 KiB copies on 8 warps by default; 32 = 2 KiB copies on 4 warps, 33 = 512-byte copies on 16 warps
+    if (shape_variant == 32 && p.k <= 4096) return launch_rcr_mma_cfg<RAW, 2048, 4>(p, batch, sms, stream);
+    if (shape_variant == 33) return launch_rcr_mma_cfg<RAW, 512, 16>(p, batch, sms, stream);
+    return launch_rcr_mma_cfg<RAW, 1024, 8>(p, batch, sms, stream);
+}
+
 // The tensor-core GEMV serves K-contiguous weights when K is a multiple of 64 bytes, fits the
 // activation staging, and every CTA's share of 8-column groups fits the shared accumulator.
 bool mma_gemv_ok(const GemvParams& p) {
     const int sms = sm_count_cached();
     if (sms <= 0) return false;
-    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
-    const int ctas = total_groups < sms ? total_groups : sms;
-    const int per_cta = (total_groups + ctas - 1) / ctas;
+    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = want < sms ? want : sms;
+    const int cols_per_cta = (p.n + ctas - 1) / ctas;
+    const int per_cta = (cols_per_cta + MMA_COLS - 1) / MMA_COLS;
     return (p.k % 64 == 0) && p.k <= MMA_MAX_K && per_cta <= MMA_MAX_GROUPS;
 }
 
@@ -835,8 +874,9 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     // K-contiguous weights, two or more activation rows: tensor-core streaming kernel
     // (variant 3 forces it also for m == 1, variant 2 and 1 keep it off)
     if (g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
-        ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3)) {
-        return launch_rcr_mma<RAW>(p, g.batch, stream);
+        ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3 ||
+         g.variant == 31 || g.variant == 32 || g.variant == 33)) {  // 31 / 32 / 33 force a copy-size configuration
+        return launch_rcr_mma<RAW>(p, g.batch, g.variant, stream);
     }
     // K-contiguous weights with few activation rows: the bulk-copy streaming kernel
     // (variant 2 forces it off, variant 1 forces it on where it is legal)

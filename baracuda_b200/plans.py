@@ -405,3 +405,118 @@ def device_status() -> int:
 
 def set_tuning(key: int, value: int) -> None:
     status_to_result(_lib.load().baracuda_kernels_q_set_tuning(key, value), "set_tuning")
+
+
+# --------------------------------------------------------------------------- activation quantizer
+@dataclass(frozen=True)
+class QuantizePerTokenDescriptor:
+    """Per-token symmetric quantizer (DynamicRangeQuantizeDescriptor of the reference's quantize family,
+    crates/baracuda-kernels/src/quantize/dynamic_range.rs): `out` is "s8" or "e4m3"."""
+    rows: int
+    cols: int
+    out: str = "s8"
+    q_min: int = -127
+    q_max: int = 127
+
+
+class QuantizePerTokenPlan:
+    """scale[r] = absmax/qmax (1.0 for a zero row); q = clamp(rint(x * (1/scale))) — f32 or bf16 in, f32 scales out."""
+
+    def __init__(self, desc: QuantizePerTokenDescriptor):
+        self.desc = desc
+
+    @classmethod
+    def select(cls, stream, desc: QuantizePerTokenDescriptor, pref: PlanPreference = PlanPreference()):
+        _check_backend(pref)
+        if desc.rows < 0 or desc.cols < 0:
+            raise InvalidProblem("negative dimension")
+        if desc.out not in ("s8", "e4m3"):
+            raise InvalidProblem("out must be 's8' or 'e4m3'")
+        if desc.out == "s8" and (desc.q_min > desc.q_max or desc.q_max <= 0):
+            raise InvalidProblem("bad quantization range")
+        return cls(desc)
+
+    def workspace_size(self) -> int:
+        return 0
+
+    def run(self, stream, x: torch.Tensor, scale: torch.Tensor, q: torch.Tensor,
+            ld_in: Optional[int] = None, ld_out: Optional[int] = None) -> None:
+        d = self.desc
+        if x.dtype not in (torch.float32, torch.bfloat16):
+            raise InvalidProblem("input must be float32 or bfloat16")
+        if scale.dtype != torch.float32:
+            raise InvalidProblem("scale must be float32")
+        ld_in = ld_in if ld_in is not None else max(d.cols, 1)
+        ld_out = ld_out if ld_out is not None else max(d.cols, 1)
+        _need(x, _span(d.rows, d.cols, ld_in), "input")
+        _need(q, _span(d.rows, d.cols, ld_out), "output")
+        _need(scale, d.rows, "scale")
+        lib = _lib.load()
+        tin = "f32" if x.dtype == torch.float32 else "bf16"
+        fn = getattr(lib, f"baracuda_kernels_quantize_per_token_sym_{tin}_{d.out}_sm100a_run")
+        if d.out == "s8":
+            st = fn(d.rows, d.cols, d.q_min, d.q_max, _ptr(x), ld_in, _ptr(scale), _ptr(q), ld_out, None, 0,
+                    _stream_ptr(stream))
+        else:
+            st = fn(d.rows, d.cols, _ptr(x), ld_in, _ptr(scale), _ptr(q), ld_out, None, 0, _stream_ptr(stream))
+        status_to_result(st, "QuantizePerTokenPlan")
+
+
+# --------------------------------------------------------------------------- W8A8 linear (quantize + GEMM)
+@dataclass(frozen=True)
+class QuantizedLinearDescriptor:
+    """QuantizedLinearDescriptor (crates/baracuda-kernels/src/quantize/quantized_linear.rs:55-80)."""
+    m: int
+    c_out: int
+    k: int
+    q_min: int = -127
+    q_max: int = 127
+
+
+@dataclass
+class QuantizedLinearArgs:
+    """QuantizedLinearArgs (quantized_linear.rs:82-120): f32/bf16 activation, offline-quantized int8 weight
+    [C_out, K] with per-channel f32 scales, bf16 output, caller-owned scratch for the quantized activation."""
+    activation: torch.Tensor
+    weight_q: torch.Tensor
+    weight_scale: torch.Tensor
+    output: torch.Tensor
+    act_q_scratch: torch.Tensor
+    act_scale_scratch: torch.Tensor
+
+
+class QuantizedLinearPlan:
+    """The reference's two-launch W8A8 linear (quantized_linear.rs:262-355) on the sm_100a kernels:
+    per-token quantize, then the tcgen05 GEMM (m > 8) or the streaming GEMV (m <= 8), bf16 out."""
+
+    def __init__(self, desc: QuantizedLinearDescriptor, quant: QuantizePerTokenPlan, mm):
+        self.desc, self._quant, self._mm = desc, quant, mm
+
+    @classmethod
+    def select(cls, stream, desc: QuantizedLinearDescriptor, pref: PlanPreference = PlanPreference()):
+        quant = QuantizePerTokenPlan.select(stream, QuantizePerTokenDescriptor(desc.m, desc.k, "s8", desc.q_min, desc.q_max), pref)
+        if 0 < desc.m <= 8:
+            mm = GemvQ8Plan.select(stream, GemvQ8Descriptor(desc.m, desc.c_out, desc.k, layout=LayoutSku.Rcr), pref)
+        else:
+            mm = W8A8GemmPlan.select(stream, QGemmDescriptor(desc.m, desc.c_out, desc.k), pref)
+        return cls(desc, quant, mm)
+
+    def sku(self) -> KernelSku:
+        return self._mm.sku()
+
+    def precision_guarantee(self) -> PrecisionGuarantee:
+        return self._mm.precision_guarantee()
+
+    def workspace_size(self) -> int:
+        return self._mm.workspace_size()
+
+    def run(self, stream, workspace: Optional[torch.Tensor], args: QuantizedLinearArgs) -> None:
+        if args.act_q_scratch.dtype != torch.int8:
+            raise InvalidProblem("act_q_scratch must be int8")
+        self._quant.run(stream, args.activation, args.act_scale_scratch, args.act_q_scratch)
+        if isinstance(self._mm, GemvQ8Plan):
+            self._mm.run(stream, workspace, GemvQ8Args(a=args.act_q_scratch, b=args.weight_q, d=args.output,
+                                                       scale_a=args.act_scale_scratch, scale_b=args.weight_scale))
+        else:
+            self._mm.run(stream, workspace, QGemmArgs(a=args.act_q_scratch, b=args.weight_q, d=args.output,
+                                                      scale_a=args.act_scale_scratch, scale_b=args.weight_scale))

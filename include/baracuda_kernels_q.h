@@ -206,6 +206,34 @@ size_t baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
 
 /* ---------------------------------------------------------------------------
+ * Per-token (per-row) symmetric activation quantizer, the step in front of the GEMM / GEMV:
+ *   scale[r] = absmax(x[r,:]) / qmax (1.0 for an all-zero row)
+ *   q[r,c]   = clamp(rint_even(x[r,c] * (1/scale[r])), qmin, qmax)       (s8)
+ *   q[r,c]   = e4m3_satfinite(x[r,c] * (1/scale[r])), qmax = 448         (e4m3)
+ * Same recipe and argument order as
+ *   baracuda_kernels_dynamic_range_quantize_per_token_sym_f32_s8_run
+ *   (crates/baracuda-kernels-sys/kernels/include/baracuda_quantize_compose.cuh:144-201, 309-326),
+ * with row pitches added (elements) and the scale always written as f32 (what the GEMM epilogues
+ * read).  Input f32 or bf16 [rows, cols]; no limit on rows (the reference stops at 65 535).
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_quantize_per_token_sym_f32_s8_sm100a_run(
+    int32_t rows, int32_t cols, int32_t qmin, int32_t qmax,
+    const void* input, int64_t ld_in, void* scale, void* output, int64_t ld_out,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_quantize_per_token_sym_bf16_s8_sm100a_run(
+    int32_t rows, int32_t cols, int32_t qmin, int32_t qmax,
+    const void* input, int64_t ld_in, void* scale, void* output, int64_t ld_out,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_quantize_per_token_sym_f32_e4m3_sm100a_run(
+    int32_t rows, int32_t cols,
+    const void* input, int64_t ld_in, void* scale, void* output, int64_t ld_out,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_quantize_per_token_sym_bf16_e4m3_sm100a_run(
+    int32_t rows, int32_t cols,
+    const void* input, int64_t ld_in, void* scale, void* output, int64_t ld_out,
+    void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Column-parallel (N-sharded) GEMM inside one NVLink box.  Rank r owns rows
  * [r*n_local, (r+1)*n_local) of the [N,K] weight and the matching scale_b slice;
  * activations and scale_a are replicated; every rank computes D[:, slice].

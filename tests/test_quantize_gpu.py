@@ -1,0 +1,87 @@
+"""GPU parity of the per-token activation quantizer and of the two-launch W8A8 linear built on it,
+against the CPU oracle's restatement of the reference recipe: scales and codes bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import baracuda_b200 as bq
+from helpers import bf16_bits, dev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [(1, 4096), (8, 4096), (128, 1024), (37, 50), (5, 8200), (3, 20000), (2048, 8192)])
+@pytest.mark.parametrize("in_dtype", ["f32", "bf16"])
+def test_per_token_s8(oracle, shape, in_dtype):
+    rows, cols = shape
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    x[0, :] = 0.0 if rows > 1 else x[0, :]  # an all-zero row gets scale 1 and zeros (compose.cuh:183-189)
+    xt = torch.from_numpy(x)
+    if in_dtype == "bf16":
+        xt = xt.to(torch.bfloat16)
+        x = xt.to(torch.float32).numpy()
+    q_ref, s_ref = oracle.quantize_rows_s8(x)
+    plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "s8"))
+    scale = torch.full((rows,), float("nan"), device="cuda")
+    q = torch.full((rows, cols), 99, dtype=torch.int8, device="cuda")
+    plan.run(None, xt.cuda(), scale, q)
+    torch.cuda.synchronize()
+    assert np.array_equal(scale.cpu().numpy(), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+@pytest.mark.parametrize("shape", [(8, 4096), (100, 70), (512, 8192)])
+def test_per_token_e4m3(oracle, shape):
+    rows, cols = shape
+    x = np.random.default_rng(cols).standard_normal((rows, cols)).astype(np.float32)
+    q_ref, s_ref = oracle.quantize_rows_e4m3(x)
+    plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "e4m3"))
+    scale = torch.empty(rows, device="cuda")
+    q = torch.empty((rows, cols), dtype=torch.uint8, device="cuda")
+    plan.run(None, dev(x), scale, q)
+    torch.cuda.synchronize()
+    assert np.array_equal(scale.cpu().numpy(), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+def test_padded_pitches_and_canaries(oracle):
+    rows, cols, ld_in, ld_out = 9, 100, 117, 131  # odd pitches: the scalar path
+    x = np.random.default_rng(1).standard_normal((rows, ld_in)).astype(np.float32)
+    q_ref, s_ref = oracle.quantize_rows_s8(x[:, :cols])
+    plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "s8"))
+    scale = torch.empty(rows, device="cuda")
+    q = torch.full((rows, ld_out), 77, dtype=torch.int8, device="cuda")
+    plan.run(None, dev(x), scale, q, ld_in=ld_in, ld_out=ld_out)
+    torch.cuda.synchronize()
+    got = q.cpu().numpy()
+    assert np.array_equal(got[:, :cols], q_ref) and np.all(got[:, cols:] == 77)
+    assert np.array_equal(scale.cpu().numpy(), s_ref)
+
+
+@pytest.mark.parametrize("m", [1, 4, 300])
+def test_quantized_linear_two_launch_path(oracle, m):
+    """QuantizedLinearPlan (quantize, then GEMV for m <= 8 or GEMM): bit-equal to the oracle's
+    quantize -> int32 contraction -> (sa*sw)*acc -> bf16, and within 3 % of the full-precision product
+    where that is not near zero (the reference's own acceptance rule, quantized_linear_smoke.rs:171-184)."""
+    c_out, k = 1024, 2048
+    rng = np.random.default_rng(m)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((c_out, k)) * 0.02).astype(np.float32)
+    wq, sw = oracle.quantize_rows_s8(w)
+    aq, sa = oracle.quantize_rows_s8(a)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, c_out, k), sa, sw)
+    plan = bq.QuantizedLinearPlan.select(None, bq.QuantizedLinearDescriptor(m, c_out, k))
+    assert plan.sku().arch is bq.ArchSku.Sm100a
+    out = torch.empty((m, c_out), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    plan.run(None, ws, bq.QuantizedLinearArgs(
+        activation=dev(a), weight_q=dev(wq), weight_scale=dev(sw), output=out,
+        act_q_scratch=torch.empty((m, k), dtype=torch.int8, device="cuda"),
+        act_scale_scratch=torch.empty(m, device="cuda")))
+    torch.cuda.synchronize()
+    assert np.array_equal(bf16_bits(out), want)
+    full = a @ w.T
+    got = out.to(torch.float32).cpu().numpy()
+    big = np.abs(full) > 0.25 * np.abs(full).max()
+    assert np.all(np.abs(got - full)[big] / np.abs(full)[big] < 0.03)
