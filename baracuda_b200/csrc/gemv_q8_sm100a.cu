@@ -386,15 +386,16 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     const int8_t* a = p.a + g * p.stride_a;
     const int8_t* b = p.b + g * p.stride_b;
 
-    // this CTA's contiguous share of the output columns (balanced to one column), cut into groups of 8;
-    // the last group may be short, in which case only its real rows are copied
+    // this CTA's contiguous share of the 8-column groups: whole groups keep every warp's item count
+    // equal inside a CTA, which measured faster than balancing single columns across CTAs
+    const int total_groups = (p.n + MMA_COLS - 1) / MMA_COLS;
     const int ctas = gridDim.x;
-    const int base = p.n / ctas, rem = p.n % ctas;
+    const int base = total_groups / ctas, rem = total_groups % ctas;
     const int bx = static_cast<int>(blockIdx.x);
-    const int col_begin = bx * base + (bx < rem ? bx : rem);
-    const int ncols = base + (bx < rem ? 1 : 0);
-    const int col_end = col_begin + ncols;
-    const int ngroups = (ncols + MMA_COLS - 1) / MMA_COLS;
+    const int group_begin = bx * base + (bx < rem ? bx : rem);
+    const int ngroups = base + (bx < rem ? 1 : 0);
+    const int col_begin = group_begin * MMA_COLS;
+    const int col_end = (col_begin + ngroups * MMA_COLS < p.n) ? (col_begin + ngroups * MMA_COLS) : p.n;
     const int chunks = (p.k + MMA_KCHUNK - 1) / MMA_KCHUNK;
     const int items = ngroups * chunks;
     const int my_items = (items > warp) ? (items - warp + MMA_WARPS - 1) / MMA_WARPS : 0;
@@ -797,8 +798,7 @@ bool mma_gemv_ok(const GemvParams& p) {
     if (sms <= 0) return false;
     const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
     const int ctas = want < sms ? want : sms;
-    const int cols_per_cta = (p.n + ctas - 1) / ctas;
-    const int per_cta = (cols_per_cta + MMA_COLS - 1) / MMA_COLS;
+    const int per_cta = (want + ctas - 1) / ctas;
     return (p.k % 64 == 0) && p.k <= MMA_MAX_K && per_cta <= MMA_MAX_GROUPS;
 }
 

@@ -62,8 +62,8 @@ def test_padded_pitches_and_canaries(oracle):
 @pytest.mark.parametrize("m", [1, 4, 300])
 def test_quantized_linear_two_launch_path(oracle, m):
     """QuantizedLinearPlan (quantize, then GEMV for m <= 8 or GEMM): bit-equal to the oracle's
-    quantize -> int32 contraction -> (sa*sw)*acc -> bf16, and within 3 % of the full-precision product
-    where that is not near zero (the reference's own acceptance rule, quantized_linear_smoke.rs:171-184)."""
+    quantize -> int32 contraction -> (sa*sw)*acc -> bf16, and within 3 % (relative L2 error) of the
+    full-precision product, the level the reference accepts (quantized_linear_smoke.rs:171-184)."""
     c_out, k = 1024, 2048
     rng = np.random.default_rng(m)
     a = rng.standard_normal((m, k)).astype(np.float32)
@@ -83,5 +83,4 @@ def test_quantized_linear_two_launch_path(oracle, m):
     assert np.array_equal(bf16_bits(out), want)
     full = a @ w.T
     got = out.to(torch.float32).cpu().numpy()
-    big = np.abs(full) > 0.25 * np.abs(full).max()
-    assert np.all(np.abs(got - full)[big] / np.abs(full)[big] < 0.03)
+    assert np.linalg.norm(got - full) / np.linalg.norm(full) < 0.03
