@@ -29,6 +29,12 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemm_s8_rcr_s32_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
     "baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size": _GEMM_WS,
     "baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_s8_rcr_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_s8_rcr_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_s8_rcr_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_can_implement": _GEMM_CAN,
     "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run": (_i32, _GEMM_PREFIX + [_vp, _vp, _i32, _f32, _f32] + _TAIL),
     "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size": _GEMM_WS,
     "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement": _GEMM_CAN,

@@ -75,6 +75,58 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
     g.peer_ld = 0;
     g.peer_col0 = 0;
     for (auto& pd : g.peer_d) pd = nullptr;
+    g.q8_out = 0;
+    g.c = nullptr;
+    g.ldc = 0;
+    g.beta = 0.0f;
+    return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
+}
+
+// The reference's own contract for the 8-bit GEMMs: D has the input type, D = sat(alpha*(A x B) + beta*C).
+int32_t gemm_rcr_q8_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                             const void* c, int64_t ldc, const void* d, int64_t ldd) {
+    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (c != nullptr && ldc < (n > 0 ? n : 1)) return bq::BQ_STATUS_INVALID_PROBLEM;
+    return bq::BQ_STATUS_OK;
+}
+
+int32_t gemm_rcr_q8_run(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,
+                        int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
+                        void* stream) {
+    const int32_t st = gemm_rcr_q8_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
+    if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (beta != 0.0f && !c) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
+    bq::GemmDesc g;
+    g.kind = kind;
+    g.raw_out = 0;
+    g.q8_out = 1;
+    g.c = (beta != 0.0f) ? c : nullptr;
+    g.ldc = ldc;
+    g.beta = beta;
+    g.m = m;
+    g.n = n;
+    g.k = k;
+    g.a = a;
+    g.lda = lda;
+    g.b = b;
+    g.ldb = ldb;
+    g.scale_a = nullptr;
+    g.scale_b = nullptr;
+    g.scale_mode = 0;
+    g.alpha = alpha;
+    g.d = d;
+    g.ldd = ldd;
+    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.direct_stores = 1;
+    g.n_peers = 0;
+    g.peer_ld = 0;
+    g.peer_col0 = 0;
+    for (auto& pd : g.peer_d) pd = nullptr;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -173,6 +225,10 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
     g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
     g.direct_stores = g_direct_stores.load(std::memory_order_relaxed);
+    g.q8_out = 0;
+    g.c = nullptr;
+    g.ldc = 0;
+    g.beta = 0.0f;
     g.n_peers = world;
     g.peer_ld = peer_ld;
     g.peer_col0 = rank * n;
@@ -248,6 +304,36 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
     return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+// ---- the reference's own 8-bit-out contracts ------------------------------------------------
+int32_t baracuda_kernels_gemm_s8_rcr_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_rcr_q8_run(bq::BQ_KIND_S8, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
+}
+size_t baracuda_kernels_gemm_s8_rcr_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_s8_rcr_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_rcr_q8_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_rcr_q8_run(bq::BQ_KIND_E4M3, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
+}
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_rcr_q8_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
 
 // ---- int8 GEMV ---------------------------------------------------------------------

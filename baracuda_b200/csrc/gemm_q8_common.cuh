@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -28,6 +29,11 @@ struct GemmParams {
     int peer_col0;
     int peer_vec;  // 1 when every peer buffer allows 16-byte row stores at its column offset
     int coalesce;  // 1: 64-column blocks go through the shared-memory staging path
+    // 8-bit output mode (the reference's IntGemm / Fp8Gemm contract): d = sat(alpha*acc + beta*C), same type as the inputs
+    int out_q8;
+    const void* c;
+    int64_t ldc;
+    float beta;
 };
 
 // One thread, one output row, 32 consecutive columns starting at col0 (a multiple of 32).
@@ -46,6 +52,50 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 if (col0 + j < p.n) drow[j] = r[j];
+            }
+        }
+    } else if (p.out_q8) {
+        // z = alpha * acc (+ beta * C), each product and the sum rounded in f32; s8: round half to even and
+        // clamp to [-128, 127]; e4m3: round to nearest even, saturate to +-448 (no infinities)
+        uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+        const uint8_t* crow =
+            p.c ? reinterpret_cast<const uint8_t*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0 : nullptr;
+        uint32_t packed[8];
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            uint32_t word = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int j = 4 * w + b;
+                float z;
+                uint8_t out;
+                if constexpr (KIND == UMMA_KIND_I8) {
+                    z = __fmul_rn(p.alpha, static_cast<float>(static_cast<int32_t>(r[j])));
+                    if (crow && col0 + j < p.n) {
+                        z = __fadd_rn(z, __fmul_rn(p.beta, static_cast<float>(static_cast<int8_t>(crow[j]))));
+                    }
+                    int q = __float2int_rn(z);
+                    q = q < -128 ? -128 : (q > 127 ? 127 : q);
+                    out = static_cast<uint8_t>(static_cast<int8_t>(q));
+                } else {
+                    z = __fmul_rn(p.alpha, __uint_as_float(r[j]));
+                    if (crow && col0 + j < p.n) {
+                        const __half_raw hr = __nv_cvt_fp8_to_halfraw(crow[j], __NV_E4M3);
+                        z = __fadd_rn(z, __fmul_rn(p.beta, __half2float(__half(hr))));
+                    }
+                    out = static_cast<uint8_t>(__nv_cvt_float_to_fp8(z, __NV_SATFINITE, __NV_E4M3));
+                }
+                word |= static_cast<uint32_t>(out) << (8 * b);
+            }
+            packed[w] = word;
+        }
+        if (p.vec_store && col0 + 32 <= p.n) {
+            reinterpret_cast<uint4*>(drow)[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            reinterpret_cast<uint4*>(drow)[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.n) drow[j] = static_cast<uint8_t>(packed[j >> 2] >> (8 * (j & 3)));
             }
         }
     } else {

@@ -190,7 +190,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
             float* sb_tile = sb_s + (warp - 2) * PAIR_TILE_N;
-            if constexpr (!RAW) {
+            if (!RAW && !p.out_q8) {
                 __syncwarp();
                 for (int i = lane; i < PAIR_TILE_N; i += 32) {
                     const int col = n_blk * PAIR_TILE_N + i;
@@ -206,7 +206,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int row = m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32 + lane;
             const bool row_ok = row < p.m;
             float sa_row = 1.0f;
-            if constexpr (!RAW) {
+            if (!RAW && !p.out_q8) {
                 sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
@@ -276,7 +276,11 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     p.k = g.k;
     p.m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
     p.n_tiles = (g.n + PAIR_TILE_N - 1) / PAIR_TILE_N;
-    const int64_t elem = RAW ? 4 : 2;
+    const int64_t elem = RAW ? 4 : (g.q8_out ? 1 : 2);
+    p.out_q8 = RAW ? 0 : g.q8_out;
+    p.c = g.c;
+    p.ldc = g.ldc;
+    p.beta = g.beta;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;
@@ -299,6 +303,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     // to the tensor cores and measure 2-5 % faster.  direct_stores: 1 forces direct, 2 forces staged.
     const int64_t waves = (tiles + pairs - 1) / pairs;
     p.coalesce = (g.direct_stores == 2) || (g.direct_stores == 0 && (FUSED || waves <= 6));
+    if (p.out_q8) p.coalesce = 0;  // the staging path is bf16-only
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
     cfg.blockDim = dim3(PAIR_THREADS, 1, 1);

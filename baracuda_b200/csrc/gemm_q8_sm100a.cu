@@ -187,7 +187,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // each warp stages its own copy of this tile's column scales, so the
             // epilogue warps never have to meet at a barrier
             float* sb_tile = sb_s + (warp - 2) * BLOCK_N;
-            if constexpr (!RAW) {
+            if (!RAW && !p.out_q8) {
                 __syncwarp();
                 for (int i = lane; i < BLOCK_N; i += 32) {
                     const int col = n_blk * BLOCK_N + i;
@@ -203,7 +203,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const int row = m_blk * BLOCK_M + q * 32 + lane;
             const bool row_ok = row < p.m;
             float sa_row = 1.0f;
-            if constexpr (!RAW) {
+            if (!RAW && !p.out_q8) {
                 sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
@@ -321,7 +321,11 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.k = g.k;
     p.m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     p.n_tiles = (g.n + BLOCK_N - 1) / BLOCK_N;
-    const int64_t elem = RAW ? 4 : 2;
+    const int64_t elem = RAW ? 4 : (g.q8_out ? 1 : 2);
+    p.out_q8 = RAW ? 0 : g.q8_out;
+    p.c = g.c;
+    p.ldc = g.ldc;
+    p.beta = g.beta;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;
@@ -339,6 +343,7 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
     const int grid = static_cast<int>(tiles < sms ? tiles : sms);
     p.coalesce = (g.direct_stores == 2) || (g.direct_stores == 0 && (FUSED || (tiles + grid - 1) / grid <= 6));
+    if (p.out_q8) p.coalesce = 0;  // the staging path is bf16-only
     kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(map_a, map_b, p);
     return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
 }

@@ -135,6 +135,42 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_can_implement(
     const void* c, int64_t ldc, const void* d, int64_t ldd);
 
 /* ---------------------------------------------------------------------------
+ * The reference's own 8-bit-out GEMM contracts on tcgen05, same signatures, arch tag sm100a:
+ *   s8:   D = sat_s8( rint_even( alpha*(float)acc + beta*(float)C ) )            (D, C int8)
+ *         drop-in for baracuda_cutlass_gemm_s8_rcr_sm80_run / IntGemmPlan<S8> Rcr, identity epilogue
+ *         (crates/baracuda-cutlass-kernels-sys/kernels/gemm_s8_rcr_sm80.cu:169-198,
+ *          crates/baracuda-kernels/src/gemm/int_gemm.rs:48-637)
+ *   e4m3: D = sat_e4m3( alpha*acc + beta*dequant(C) )                            (D, C e4m3)
+ *         drop-in for baracuda_kernels_gemm_fp8_e4m3_rcr_sm89_run / Fp8GemmPlan Rcr, identity epilogue
+ *         (crates/baracuda-kernels-sys/kernels/gemm/gemm_fp8_e4m3_rcr_sm89.cu:31-67)
+ * Each product and the sum are rounded in f32, as the reference's test oracles compute them
+ * (crates/baracuda-kernels/tests/int8_rrr_smoke.rs:76-131, fp8_e4m3_rcr_smoke.rs:66-93).
+ * beta != 0 needs C (ldc >= n); with beta == 0, C is not read.
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_gemm_s8_rcr_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd,
+    float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_s8_rcr_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_gemm_s8_rcr_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, const void* d, int64_t ldd);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd,
+    float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, const void* d, int64_t ldd);
+
+/* ---------------------------------------------------------------------------
  * Decode GEMV with int8 weights, m = 1 (and the skinny extension m <= 8):
  *   D[g,r,j] = bf16( alpha * ((scale_a[g,r] * scale_b[g,j]) * (float)acc) + beta * D[g,r,j] )
  * Argument order is that of baracuda_kernels_gemv_dense_m1_bf16_run
