@@ -27,7 +27,9 @@ from .vocab import (  # noqa: F401
 from .plans import (  # noqa: F401
     SCALE_PER_ROW_COL,
     SCALE_PER_TENSOR,
+    Fp8GemmPlan,
     Fp8ScaledGemmPlan,
+    IntGemmPlan,
     GemvQ8Args,
     GemvQ8Descriptor,
     GemvQ8Plan,

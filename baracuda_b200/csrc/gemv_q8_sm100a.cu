@@ -408,7 +408,8 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     }
     __syncwarp();
 
-    auto issue = [&](int mine) {  // lane 0 only; `mine` counts this warp's items
+    // whole warp: lane 0 arms the barrier, lanes 0..rows-1 each issue one row's copy (8 copies in one go)
+    auto issue = [&](int mine) {  // `mine` counts this warp's items
         const int item = warp + mine * MMA_WARPS;
         const int gi = item / chunks, kc = item - gi * chunks;
         const int k0 = kc * MMA_KCHUNK;
@@ -416,15 +417,17 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         const int col0 = col_begin + gi * MMA_COLS;
         const int rows = (col_end - col0 < MMA_COLS) ? (col_end - col0) : MMA_COLS;
         const int slot = mine % MMA_RING;
-        mbar_arrive_expect_tx(&full_bar[slot], bytes * static_cast<uint32_t>(rows));
-        for (int r = 0; r < rows; ++r) {
-            bulk_load_1d(ring + slot * MMA_ITEM_BYTES + r * MMA_PITCH, b + static_cast<int64_t>(col0 + r) * p.ldb + k0, bytes,
-                         &full_bar[slot]);
+        if (lane == 0) {
+            fence_proxy_async_smem();
+            mbar_arrive_expect_tx(&full_bar[slot], bytes * static_cast<uint32_t>(rows));
+        }
+        __syncwarp();
+        if (lane < rows) {
+            bulk_load_1d(ring + slot * MMA_ITEM_BYTES + lane * MMA_PITCH, b + static_cast<int64_t>(col0 + lane) * p.ldb + k0,
+                         bytes, &full_bar[slot]);
         }
     };
-    if (lane == 0) {
-        for (int i = 0; i < MMA_RING && i < my_items; ++i) issue(i);
-    }
+    for (int i = 0; i < MMA_RING && i < my_items; ++i) issue(i);
     if (p.pdl) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -483,10 +486,7 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         d[0] += d1[0] + d2[0] + d3[0];
         d[1] += d1[1] + d2[1] + d3[1];
         __syncwarp();  // the whole item has been read: its slot can be refilled
-        if (lane == 0 && mine + MMA_RING < my_items) {
-            fence_proxy_async_smem();
-            issue(mine + MMA_RING);
-        }
+        if (mine + MMA_RING < my_items) issue(mine + MMA_RING);
         // d[0], d[1]: activation row gq, columns 2*tq and 2*tq+1 of this group (d[2], d[3] belong to the zero rows)
         if (gq < p.m) {
             atomicAdd(&acc_s[gi * 64 + gq * 8 + 2 * tq], d[0]);

@@ -520,3 +520,47 @@ class QuantizedLinearPlan:
         else:
             self._mm.run(stream, workspace, QGemmArgs(a=args.act_q_scratch, b=args.weight_q, d=args.output,
                                                       scale_a=args.act_scale_scratch, scale_b=args.weight_scale))
+
+
+# --------------------------------------------------------------------------- the reference's 8-bit-out plans
+class IntGemmPlan(_QGemmPlanBase):
+    """`IntGemmPlan<S8>` of the reference (crates/baracuda-kernels/src/gemm/int_gemm.rs:48-637), Rcr layout,
+    identity epilogue, on tcgen05: D[s8] = sat(rint(alpha * acc + beta * C))."""
+
+    _in_dtypes = (torch.int8,)
+    _out_dtype = torch.int8
+    _needs_scales = False
+    _base = "baracuda_kernels_gemm_s8_rcr_sm100a"
+    _element = ElementKind.S8
+    _guarantee = _INT_GUARANTEE
+    _op = OP_W8A8_GEMM
+
+    def __init__(self, desc, sku):
+        super().__init__(desc, sku)
+        self._run_symbol, self._can_symbol, self._ws_symbol = (self._base + "_run", self._base + "_can_implement",
+                                                               self._base + "_workspace_size")
+
+    @classmethod
+    def select(cls, stream, desc: QGemmDescriptor, pref: PlanPreference = PlanPreference()):
+        cls._validate_desc(desc, pref)
+        sku = KernelSku(OpCategory.Gemm, cls._op, cls._element, None, desc.layout, desc.epilogue, ArchSku.Sm100a,
+                        BackendKind.Bespoke, cls._guarantee)
+        return cls(desc, sku)
+
+    def _call(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
+        d = self.desc
+        return getattr(lib, self._run_symbol)(d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c),
+                                              args.ldc or max(d.n, 1), _ptr(args.d), ldd, args.alpha, args.beta,
+                                              ws_ptr, ws_bytes, stream)
+
+
+class Fp8GemmPlan(IntGemmPlan):
+    """`Fp8GemmPlan<Fp8E4M3>` of the reference (crates/baracuda-kernels/src/gemm/fp8_gemm.rs:36-741), Rcr layout,
+    identity epilogue: D[e4m3] = sat(alpha * acc + beta * dequant(C))."""
+
+    _in_dtypes = (torch.uint8, torch.float8_e4m3fn)
+    _out_dtype = torch.uint8
+    _base = "baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a"
+    _element = ElementKind.Fp8E4M3
+    _guarantee = _FP8_GUARANTEE
+    _op = OP_FP8_SCALED_GEMM
