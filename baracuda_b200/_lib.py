@@ -41,6 +41,21 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
     "baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_workspace_size": _GEMM_WS,
     "baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run": (_i32, _GEMM_PREFIX + [_vp, _vp, _f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run": (_i32, _GEMM_PREFIX + [_vp, _vp, _i32, _f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_s8_rrr_s32_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_s8_rrr_s32_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_s8_rrr_s32_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_s8_rrr_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_s8_rrr_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_s8_rrr_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_can_implement": _GEMM_CAN,
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_run": (
         _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement": _GEMV_CAN,

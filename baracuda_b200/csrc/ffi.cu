@@ -21,26 +21,45 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // Shape / leading-dimension / alignment rules shared by run and can_implement.
 // Pointer arguments may be null here (can_implement is callable before the
 // buffers exist); alignment of a null pointer is not judged.
-int32_t gemm_rcr_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
-                          const void* c, int64_t ldc, const void* d, int64_t ldd) {
+// `layout` is the weight storage: RCR = [N,K] rows of K (ldb >= k), RRR = row-major [K,N] (ldb >= n).
+int32_t gemm_validate(int32_t layout, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,
+                      int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd) {
     (void)ldc;
     (void)d;
     if (m < 0 || n < 0 || k < 0) return bq::BQ_STATUS_INVALID_PROBLEM;
     const int64_t min_k = k > 0 ? k : 1;
     const int64_t min_n = n > 0 ? n : 1;
-    if (lda < min_k || ldb < min_k || ldd < min_n) return bq::BQ_STATUS_INVALID_PROBLEM;
+    const bool rrr = layout == bq::BQ_LAYOUT_RRR;
+    if (lda < min_k || ldb < (rrr ? min_n : min_k) || ldd < min_n) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (c != nullptr) return bq::BQ_STATUS_UNSUPPORTED;
     // TMA reads both operands: 16-byte aligned bases and row pitches
     if ((a && !aligned16(a)) || (b && !aligned16(b))) return bq::BQ_STATUS_MISALIGNED;
-    if (k > 0 && ((m > 1 && (lda & 15)) || (n > 1 && (ldb & 15)))) return bq::BQ_STATUS_MISALIGNED;
+    const int64_t b_rows = rrr ? k : n;
+    if (k > 0 && ((m > 1 && (lda & 15)) || (b_rows > 1 && (ldb & 15)))) return bq::BQ_STATUS_MISALIGNED;
     return bq::BQ_STATUS_OK;
 }
+
+int32_t gemm_rcr_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                          const void* c, int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                 const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
+                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream);
 
 int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                      const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd,
                      const void* scale_a, const void* scale_b, int32_t scale_mode, float alpha, float beta,
                      void* stream) {
-    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return gemm_run(bq::BQ_LAYOUT_RCR, kind, raw, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b, scale_mode,
+                    alpha, beta, stream);
+}
+
+int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                 const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
+                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream) {
+    const int32_t st = gemm_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
@@ -53,6 +72,7 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
             return bq::BQ_STATUS_INVALID_PROBLEM;
     }
     bq::GemmDesc g;
+    g.b_layout = layout;
     g.kind = kind;
     g.raw_out = raw;
     g.m = m;
@@ -83,24 +103,25 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
 }
 
 // The reference's own contract for the 8-bit GEMMs: D has the input type, D = sat(alpha*(A x B) + beta*C).
-int32_t gemm_rcr_q8_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
-                             const void* c, int64_t ldc, const void* d, int64_t ldd) {
-    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
+int32_t gemm_q8_validate(int32_t layout, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,
+                         int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd) {
+    const int32_t st = gemm_validate(layout, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (c != nullptr && ldc < (n > 0 ? n : 1)) return bq::BQ_STATUS_INVALID_PROBLEM;
     return bq::BQ_STATUS_OK;
 }
 
-int32_t gemm_rcr_q8_run(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,
-                        int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
-                        void* stream) {
-    const int32_t st = gemm_rcr_q8_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                    const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
+                    void* stream) {
+    const int32_t st = gemm_q8_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (beta != 0.0f && !c) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
     bq::GemmDesc g;
+    g.b_layout = layout;
     g.kind = kind;
     g.raw_out = 0;
     g.q8_out = 1;
@@ -207,6 +228,7 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
     bq::GemmDesc g;
+    g.b_layout = bq::BQ_LAYOUT_RCR;
     g.kind = kind;
     g.raw_out = 0;
     g.m = m;
@@ -313,13 +335,13 @@ int32_t baracuda_kernels_gemm_s8_rcr_sm100a_run(
     void* stream) {
     (void)workspace;
     (void)workspace_bytes;
-    return gemm_rcr_q8_run(bq::BQ_KIND_S8, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
+    return gemm_q8_run(bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
 }
 size_t baracuda_kernels_gemm_s8_rcr_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
 int32_t baracuda_kernels_gemm_s8_rcr_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_rcr_q8_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return gemm_q8_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
@@ -327,14 +349,75 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run(
     void* stream) {
     (void)workspace;
     (void)workspace_bytes;
-    return gemm_rcr_q8_run(bq::BQ_KIND_E4M3, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
+    return gemm_q8_run(bq::BQ_LAYOUT_RCR, bq::BQ_KIND_E4M3, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
 }
 size_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_rcr_q8_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return gemm_q8_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
+
+// ---- row-major weights ("rrr": B is [K,N] with ldb >= n), the layout of the reference's bespoke GEMMs ------
+#define BQ_GEMM_TRIPLE_TAIL(NAME, VALIDATE)                                                                          \
+    size_t NAME##_workspace_size(int32_t, int32_t, int32_t) { return 0; }                                           \
+    int32_t NAME##_can_implement(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,         \
+                                 int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd) {              \
+        return VALIDATE(bq::BQ_LAYOUT_RRR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);                                  \
+    }
+
+int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
+                    BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream);
+}
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a, gemm_validate)
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode, float alpha,
+    float beta, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
+                    scale_mode, alpha, beta, stream);
+}
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a, gemm_validate)
+
+int32_t baracuda_kernels_gemm_s8_rrr_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, 1, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, nullptr, nullptr, 0, alpha,
+                    beta, stream);
+}
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_s8_rrr_s32_sm100a, gemm_validate)
+
+int32_t baracuda_kernels_gemm_s8_rrr_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_q8_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
+}
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_s8_rrr_sm100a, gemm_q8_validate)
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
+    int64_t ldc, void* d, int64_t ldd, float alpha, float beta, void* workspace, size_t workspace_bytes,
+    void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_q8_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
+}
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a, gemm_q8_validate)
 
 // ---- int8 GEMV ---------------------------------------------------------------------
 int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(

@@ -54,7 +54,9 @@ __device__ __forceinline__ void pair_timeout(volatile uint32_t* abort_word, int 
     atomicCAS(&g_gemm_pair_device_status, 0, code);
 }
 
-template <uint32_t KIND, bool RAW, bool FUSED, int TN>
+// B_MN: the weight is row-major [K, N] (N contiguous): its tile is loaded as [128 K-rows x 128 N-bytes] and
+// described to the MMA as an MN-major operand.  Needs TN == 256 (one 128-byte atom of N per CTA).
+template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -131,8 +133,13 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     const uint32_t full_on_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
                     tma_load_2d_pair(a_tile, &tmap_a, full_on_leader, kb * PAIR_BLOCK_K,
                                      m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS);
-                    tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
-                                     n_blk * PAIR_TILE_N + static_cast<int>(rank) * C::B_ROWS);
+                    if constexpr (B_MN) {
+                        tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader,
+                                         n_blk * PAIR_TILE_N + static_cast<int>(rank) * C::B_ROWS, kb * PAIR_BLOCK_K);
+                    } else {
+                        tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
+                                         n_blk * PAIR_TILE_N + static_cast<int>(rank) * C::B_ROWS);
+                    }
                     if (++stage == PAIR_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -142,7 +149,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = umma_idesc(KIND, PAIR_TILE_M, PAIR_TILE_N);
+            constexpr uint32_t idesc = umma_idesc(KIND, PAIR_TILE_M, PAIR_TILE_N, B_MN);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -165,11 +172,14 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(tiles + stage * PAIR_STAGE_BYTES);
                     const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
-                    const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + PAIR_A_BYTES);
+                    const uint64_t b_desc = B_MN ? umma_desc_mnmajor_sw128(a_addr + PAIR_A_BYTES, C::B_BYTES, 1024)
+                                                 : umma_desc_kmajor_sw128(a_addr + PAIR_A_BYTES);
 #pragma unroll
                     for (int ks = 0; ks < PAIR_BLOCK_K / PAIR_UMMA_K; ++ks) {
                         const uint64_t koff = static_cast<uint64_t>((ks * PAIR_UMMA_K) >> 4);
-                        umma_ss_pair<KIND>(d_tmem, a_desc + koff, b_desc + koff, idesc, (kb | ks) != 0 ? 1u : 0u);
+                        // MN-major: 32 K-rows are four 1024-byte atoms further down the tile
+                        const uint64_t boff = B_MN ? static_cast<uint64_t>((ks * PAIR_UMMA_K * 128) >> 4) : koff;
+                        umma_ss_pair<KIND>(d_tmem, a_desc + koff, b_desc + boff, idesc, (kb | ks) != 0 ? 1u : 0u);
                     }
                     umma_commit_pair(&empty_bar[stage], 0x3);  // frees this stage in both CTAs
                     if (++stage == PAIR_STAGES) {
@@ -254,7 +264,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
 }
 
-template <uint32_t KIND, bool RAW, bool FUSED, int TN>
+template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false>
 int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     using C = PairCfg<TN>;
     constexpr int PAIR_TILE_N = TN;
@@ -263,7 +273,11 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     if (sms < 2) return BQ_STATUS_LAUNCH_FAILURE;
     CUtensorMap map_a, map_b;
     if (!make_kmajor_tensor_map(&map_a, g.a, g.m, g.k, g.lda, CTA_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
-    if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, C::B_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
+    if constexpr (B_MN) {
+        if (!make_mnmajor_tensor_map(&map_b, g.b, g.k, g.n, g.ldb, PAIR_BLOCK_K)) return BQ_STATUS_LAUNCH_FAILURE;
+    } else {
+        if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, C::B_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
+    }
     GemmParams p;
     p.d = g.d;
     p.ldd = g.ldd;
@@ -290,7 +304,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
         p.peer_d[r] = g.peer_d[r];
         if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
     }
-    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN>;
+    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN, B_MN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -348,6 +362,13 @@ int pick_tile_n(const GemmDesc& g) {
 
 template <uint32_t KIND, bool RAW, bool FUSED>
 int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
+    if (g.b_layout == BQ_LAYOUT_RRR) {
+        if constexpr (FUSED) {
+            return BQ_STATUS_UNSUPPORTED;
+        } else {
+            return launch_pair_tn<KIND, RAW, false, 256, true>(g, stream);
+        }
+    }
     switch (pick_tile_n(g)) {
         case 256: return launch_pair_tn<KIND, RAW, FUSED, 256>(g, stream);
         case 224: return launch_pair_tn<KIND, RAW, FUSED, 224>(g, stream);

@@ -354,6 +354,7 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
+    if (g.b_layout == BQ_LAYOUT_RRR) return launch_gemm_q8_pair(g, stream);  // row-major weights: CTA-pair kernel only
     if (g.force_block_n == 1024) return launch_gemm_q8_wide(g, stream);
     // large problems: 256 x 256 tiles on CTA pairs (force_block_n 512 forces it, 256/128/64 forces it off)
     if ((g.force_block_n == 0 && g.m >= 512 && g.n >= 512 && m_tiles * ((g.n + 255) / 256) >= sms) ||
@@ -404,6 +405,20 @@ int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
 }
 
 int sm_count_of_current_device() { return sm_count_impl(); }
+
+bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k) {
+    auto enc = tensor_map_encoder();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(n_cols), static_cast<cuuint64_t>(k_rows)};
+    cuuint64_t pitch = static_cast<cuuint64_t>(k_rows > 1 ? ld : ((n_cols + 15) / 16) * 16);
+    cuuint64_t strides[1] = {pitch};
+    cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_k)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(static_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
 
 bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows) {
     return make_kmajor_map(static_cast<CUtensorMap*>(map_out), base, rows, k, ld, box_rows);

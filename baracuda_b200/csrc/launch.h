@@ -24,6 +24,7 @@ enum : int32_t { BQ_LAYOUT_RRR = 0, BQ_LAYOUT_RCR = 1 };
 struct GemmDesc {
     int32_t kind;     // BQ_KIND_*
     int32_t raw_out;  // 1: write the 32-bit accumulators, 0: fused dequant -> bf16
+    int32_t b_layout; // BQ_LAYOUT_RCR: weight [N,K]; BQ_LAYOUT_RRR: weight row-major [K,N] (served by the CTA-pair kernel)
     int32_t q8_out;   // 1 (with raw_out 0): d = sat(alpha*acc + beta*C) in the input type (s8 / e4m3), no scales
     const void* c;    // q8_out only
     int64_t ldc;
@@ -66,6 +67,8 @@ int32_t launch_gemm_q8_wide(const GemmDesc& g, cudaStream_t stream);
 int32_t read_and_clear_gemm_wide_device_status();
 // helpers exported by the 1-CTA GEMM file
 bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
+// [k_rows x n_cols] bytes, N contiguous, row pitch ld; box = box_k rows x 128 bytes, 128-byte swizzle
+bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k);
 int sm_count_of_current_device();
 
 struct GemvDesc {

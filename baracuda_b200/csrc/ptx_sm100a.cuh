@@ -136,12 +136,25 @@ __device__ __forceinline__ uint64_t umma_desc_kmajor_sw128(uint32_t smem_addr) {
     return d;
 }
 
+// Descriptor for an MN-major operand tile (the contraction index K runs across rows): rows of 128 bytes
+// along MN (one swizzle atom wide), 8 K-rows per 1024-byte atom, atoms stacked along K `sbo` bytes apart
+// and along MN `lbo` bytes apart — the layout a 128-byte-swizzled TMA box of [K rows x 128 MN bytes] lands in.
+__device__ __forceinline__ uint64_t umma_desc_mnmajor_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
 enum : uint32_t { UMMA_KIND_I8 = 0, UMMA_KIND_F8 = 1 };
 
 // 32-bit instruction descriptor: D format at [4,6), A/B formats at [7,10) and
 // [10,13), both operands K-major, N/8 at [17,23), M/16 at [24,29).
-__host__ __device__ constexpr uint32_t umma_idesc(uint32_t kind, uint32_t m, uint32_t n) {
-    return (kind == UMMA_KIND_I8
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t kind, uint32_t m, uint32_t n, bool b_mn_major = false) {
+    return (b_mn_major ? (1u << 16) : 0u) | (kind == UMMA_KIND_I8
                 ? ((2u << 4) /* s32 accumulate */ | (1u << 7) /* A s8 */ | (1u << 10) /* B s8 */)
                 : ((1u << 4) /* f32 accumulate */ | (0u << 7) /* A e4m3 */ | (0u << 10) /* B e4m3 */)) |
            ((n >> 3) << 17) | ((m >> 4) << 24);

@@ -121,8 +121,6 @@ class _QGemmPlanBase:
             raise InvalidProblem("negative dimension")
         if max(desc.m, desc.n, desc.k) >= 2**31:
             raise InvalidProblem("dimension exceeds int32")
-        if desc.layout is not LayoutSku.Rcr:
-            raise Unsupported("only the RCR layout (K-contiguous weights) has an sm_100a GEMM kernel")
         if desc.epilogue is not EpilogueKind.Identity:
             raise Unsupported("bias / activation epilogues are not built for the sm_100a SKUs")
 
@@ -139,7 +137,7 @@ class _QGemmPlanBase:
     def _lds(self, args: QGemmArgs):
         d = self.desc
         lda = args.lda if args.lda is not None else max(d.k, 1)
-        ldb = args.ldb if args.ldb is not None else max(d.k, 1)
+        ldb = args.ldb if args.ldb is not None else max(d.k if d.layout is LayoutSku.Rcr else d.n, 1)
         ldd = args.ldd if args.ldd is not None else max(d.n, 1)
         return lda, ldb, ldd
 
@@ -160,7 +158,7 @@ class _QGemmPlanBase:
         if d.m == 0 or d.n == 0:
             return  # empty problem: nothing is read or written
         _need(args.a, _span(d.m, d.k, lda), "a")
-        _need(args.b, _span(d.n, d.k, ldb), "b")
+        _need(args.b, _span(d.n, d.k, ldb) if d.layout is LayoutSku.Rcr else _span(d.k, d.n, ldb), "b")
         _need(args.d, _span(d.m, d.n, ldd), "d")
         if self._needs_scales:
             self._check_scales(args)
@@ -192,7 +190,8 @@ class W8A8GemmPlan(_QGemmPlanBase):
     def __init__(self, desc, sku, raw: bool):
         super().__init__(desc, sku)
         self.raw = raw
-        base = "baracuda_kernels_gemm_s8_rcr_s32_sm100a" if raw else "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a"
+        lay = desc.layout.value
+        base = f"baracuda_kernels_gemm_s8_{lay}_s32_sm100a" if raw else f"baracuda_kernels_gemm_w8a8_s8_{lay}_bf16_sm100a"
         self._run_symbol, self._can_symbol, self._ws_symbol = base + "_run", base + "_can_implement", base + "_workspace_size"
         self._out_dtype = torch.int32 if raw else torch.bfloat16
         self._needs_scales = not raw
@@ -217,10 +216,10 @@ class W8A8GemmPlan(_QGemmPlanBase):
     def _call(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
         d = self.desc
         if self.raw:
-            return lib.baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(
+            return getattr(lib, self._run_symbol)(
                 d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
-        return lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
+        return getattr(lib, self._run_symbol)(
             d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
             _ptr(args.scale_a), _ptr(args.scale_b), args.alpha, args.beta, ws_ptr, ws_bytes, stream)
 
@@ -235,8 +234,10 @@ class Fp8ScaledGemmPlan(_QGemmPlanBase):
         super().__init__(desc, sku)
         self.raw = raw
         self.scale_mode = scale_mode
+        if raw and desc.layout is not LayoutSku.Rcr:
+            raise Unsupported("raw f32 accumulators are exported for the RCR layout only")
         base = ("baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a" if raw
-                else "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a")
+                else f"baracuda_kernels_gemm_fp8_e4m3_{desc.layout.value}_bf16_sm100a")
         self._run_symbol, self._can_symbol, self._ws_symbol = base + "_run", base + "_can_implement", base + "_workspace_size"
         self._out_dtype = torch.float32 if raw else torch.bfloat16
         self._needs_scales = not raw
@@ -268,7 +269,7 @@ class Fp8ScaledGemmPlan(_QGemmPlanBase):
             return lib.baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(
                 d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
-        return lib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
+        return getattr(lib, self._run_symbol)(
             d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
             _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, args.alpha, args.beta, ws_ptr, ws_bytes, stream)
 
@@ -537,8 +538,8 @@ class IntGemmPlan(_QGemmPlanBase):
 
     def __init__(self, desc, sku):
         super().__init__(desc, sku)
-        self._run_symbol, self._can_symbol, self._ws_symbol = (self._base + "_run", self._base + "_can_implement",
-                                                               self._base + "_workspace_size")
+        base = self._base.replace("_rcr_", f"_{desc.layout.value}_")
+        self._run_symbol, self._can_symbol, self._ws_symbol = base + "_run", base + "_can_implement", base + "_workspace_size"
 
     @classmethod
     def select(cls, stream, desc: QGemmDescriptor, pref: PlanPreference = PlanPreference()):

@@ -171,6 +171,43 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_can_implement(
     const void* c, int64_t ldc, const void* d, int64_t ldd);
 
 /* ---------------------------------------------------------------------------
+ * "rrr" twins: the weight is row-major [K,N] (ldb >= n), the layout of the reference's bespoke GEMMs
+ *   baracuda_kernels_gemm_s8_rrr_sm80_run (crates/baracuda-kernels-sys/kernels/gemm/gemm_s8_rrr_sm80.cu:28-64)
+ *   baracuda_kernels_gemm_fp8_e4m3_rrr_sm89_run (crates/baracuda-kernels-sys/kernels/include/baracuda_fp8_rrr_sm89.cuh).
+ * Same arguments and results as the "rcr" symbols of the same name; the weight tile is fed to tcgen05 as an
+ * MN-major operand.  Alignment: b 16-byte aligned, ldb a multiple of 16.
+ * ------------------------------------------------------------------------- */
+#define BARACUDA_Q_DECLARE_GEMM_TAIL(NAME)                                                                  \
+    size_t NAME##_workspace_size(int32_t m, int32_t n, int32_t k);                                          \
+    int32_t NAME##_can_implement(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, \
+                                 int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd);
+int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b,
+    float alpha, float beta, void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_GEMM_TAIL(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a)
+int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,
+    float alpha, float beta, void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_GEMM_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a)
+int32_t baracuda_kernels_gemm_s8_rrr_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_GEMM_TAIL(baracuda_kernels_gemm_s8_rrr_s32_sm100a)
+int32_t baracuda_kernels_gemm_s8_rrr_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_GEMM_TAIL(baracuda_kernels_gemm_s8_rrr_sm100a)
+int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+    const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
+    void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_GEMM_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a)
+
+/* ---------------------------------------------------------------------------
  * Decode GEMV with int8 weights, m = 1 (and the skinny extension m <= 8):
  *   D[g,r,j] = bf16( alpha * ((scale_a[g,r] * scale_b[g,j]) * (float)acc) + beta * D[g,r,j] )
  * Argument order is that of baracuda_kernels_gemv_dense_m1_bf16_run

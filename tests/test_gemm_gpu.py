@@ -244,3 +244,51 @@ def test_full_size_4096_cubed_properties(oracle):
     out8 = _run_fp8(m, n, k, a8, w8, s8a, s8b, mode=bq.SCALE_PER_TENSOR).to(torch.float32).cpu().numpy()
     want8 = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(ref_rows, s8a, s8b))
     assert oracle.compare_tolerant(want8, out8[rows], 1e-2, 1e-4 * float(np.abs(want8).max())) == -1
+
+
+@pytest.mark.parametrize("shape", [(64, 64, 32), (128, 128, 128), (256, 128, 64), (100, 70, 50), (700, 1300, 656),
+                                   (2048, 2560, 1024)])
+def test_row_major_weights_rrr(oracle, shape):
+    """The reference's bespoke GEMM layout (B row-major [K,N]; int8_rrr_smoke.rs shapes and patterns, plus larger
+    ragged cases): int32 accumulators bit-exact, bf16 bit-exact, s8-out equal to the reference contract, FP8 exact on
+    the representable patterns."""
+    m, n, k = shape
+    a = np.array([((i * 7) % 15) - 7 for i in range(m * k)], dtype=np.int8).reshape(m, k)
+    b_kn = np.array([((i * 11) % 13) - 6 for i in range(k * n)], dtype=np.int8).reshape(k, n)
+    lda = (k + 15) // 16 * 16
+    ldb = (n + 15) // 16 * 16
+    acc_ref = oracle.gemm_s8_s32(a, b_kn, oracle.RRR, m, n, k)
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, layout=bq.LayoutSku.Rrr), raw_accumulators=True)
+    d = torch.full((m, n), -7, dtype=torch.int32, device="cuda")
+    a_d, b_d = dev(pad_rows(a, lda, 99)), dev(pad_rows(b_kn, ldb, -99))
+    plan.run(None, None, bq.QGemmArgs(a=a_d, b=b_d, d=d, lda=lda, ldb=ldb))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert oracle.compare_bitexact(acc_ref, d.cpu().numpy()) == -1
+    rng = np.random.default_rng(m)
+    sa = rng.random(m, dtype=np.float32) * 0.01
+    sb = rng.random(n, dtype=np.float32) * 0.001
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, layout=bq.LayoutSku.Rrr))
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    plan.run(None, None, bq.QGemmArgs(a=a_d, b=b_d, d=out, scale_a=dev(sa), scale_b=dev(sb), lda=lda, ldb=ldb))
+    torch.cuda.synchronize()
+    assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out)) == -1
+    # the reference's own s8-out contract in its own layout (baracuda_kernels_gemm_s8_rrr_sm80_run)
+    q = bq.IntGemmPlan.select(None, bq.QGemmDescriptor(m, n, k, layout=bq.LayoutSku.Rrr))
+    d8 = torch.zeros((m, n), dtype=torch.int8, device="cuda")
+    q.run(None, None, bq.QGemmArgs(a=a_d, b=b_d, d=d8, lda=lda, ldb=ldb, alpha=0.125))
+    torch.cuda.synchronize()
+    assert np.array_equal(d8.cpu().numpy(), oracle.int_gemm_s8_out(a, b_kn, oracle.RRR, m, n, k, alpha=0.125))
+    # FP8, values on the e4m3 grid
+    av = np.array([(((i * 5) % 13) - 6) * 0.125 for i in range(m * k)], dtype=np.float32).reshape(m, k)
+    bv = np.array([(((i * 7) % 11) - 5) * 0.125 for i in range(k * n)], dtype=np.float32).reshape(k, n)
+    a8, b8 = oracle.f32_to_e4m3(av), oracle.f32_to_e4m3(bv)
+    ref8 = oracle.gemm_e4m3_f32(a8, b8, oracle.RRR, m, n, k)
+    one = np.ones(1, dtype=np.float32)
+    f = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k, layout=bq.LayoutSku.Rrr), scale_mode=bq.SCALE_PER_TENSOR)
+    o8 = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    f.run(None, None, bq.QGemmArgs(a=dev(pad_rows(a8, lda)), b=dev(pad_rows(b8, ldb)), d=o8, scale_a=dev(one), scale_b=dev(one),
+                                   lda=lda, ldb=ldb))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert oracle.compare_bitexact(oracle.scale_f32_bf16(ref8, one, one), bf16_bits(o8)) == -1

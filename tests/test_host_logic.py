@@ -19,7 +19,11 @@ GEMV = "baracuda_kernels_gemv_q8_m1_bf16_sm100a"
 def _declared_symbols():
     text = (ROOT / "include" / "baracuda_kernels_q.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(baracuda_\w+)\s*\(", text)))
+    names = set(re.findall(r"\b(baracuda_\w+)\s*\(", text))
+    # the _workspace_size / _can_implement pair declared through BARACUDA_Q_DECLARE_GEMM_TAIL(NAME)
+    for base in re.findall(r"^BARACUDA_Q_DECLARE_GEMM_TAIL\((baracuda_\w+)\)", text, flags=re.M):
+        names.update({base + "_workspace_size", base + "_can_implement"})
+    return sorted(names)
 
 
 def test_library_exports_every_declared_symbol(qlib):
@@ -95,8 +99,8 @@ def test_plan_select_and_sku():
     assert bq.W8A8GemmPlan.select(None, desc, raw_accumulators=True).sku() != s
     f = bq.Fp8ScaledGemmPlan.select(None, desc, scale_mode=bq.SCALE_PER_ROW_COL)
     assert f.sku().element is bq.ElementKind.Fp8E4M3 and f.precision_guarantee().accumulator is bq.ElementKind.F32
-    with pytest.raises(bq.Unsupported):
-        bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, layout=bq.LayoutSku.Rrr))
+    rrr = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, layout=bq.LayoutSku.Rrr))
+    assert rrr.sku().layout is bq.LayoutSku.Rrr and rrr._run_symbol.endswith("s8_rrr_bf16_sm100a_run")
     with pytest.raises(bq.Unsupported):
         bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, epilogue=bq.EpilogueKind.BiasRelu))
     with pytest.raises(bq.Unsupported):
