@@ -94,6 +94,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
+    g.peer_rank = 0;
     for (auto& pd : g.peer_d) pd = nullptr;
     g.q8_out = 0;
     g.c = nullptr;
@@ -147,6 +148,7 @@ int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t 
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
+    g.peer_rank = 0;
     for (auto& pd : g.peer_d) pd = nullptr;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
@@ -254,6 +256,7 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     g.n_peers = world;
     g.peer_ld = peer_ld;
     g.peer_col0 = rank * n;
+    g.peer_rank = rank;
     for (int r = 0; r < 8; ++r) g.peer_d[r] = r < world ? peer_d[r] : nullptr;
     return bq::launch_gemm_q8(g, stream);
 }

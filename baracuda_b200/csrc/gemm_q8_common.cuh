@@ -28,6 +28,7 @@ struct GemmParams {
     int64_t peer_ld;
     int peer_col0;
     int peer_vec;  // 1 when every peer buffer allows 16-byte row stores at its column offset
+    int peer_rank; // this rank: peers are visited starting at the next rank so no buffer is everyone's target at once
     int coalesce;  // 1: 64-column blocks go through the shared-memory staging path
     // 8-bit output mode (the reference's IntGemm / Fp8Gemm contract): d = sat(alpha*acc + beta*C), same type as the inputs
     int out_q8;
@@ -138,7 +139,9 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
         if constexpr (FUSED) {
             // the replicated output: plain stores into every rank's row-major buffer
             // (peer-mapped memory), at this rank's column offset
-            for (int pr = 0; pr < p.n_peers; ++pr) {
+            for (int i = 1; i <= p.n_peers; ++i) {
+                int pr = p.peer_rank + i;
+                if (pr >= p.n_peers) pr -= p.n_peers;
                 __nv_bfloat16* prow = reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
                                       static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0;
                 if (p.peer_vec && col0 + 32 <= p.n) {
@@ -224,7 +227,9 @@ __device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t 
                                           c * 8) = v;
             }
             if constexpr (FUSED) {
-                for (int pr = 0; pr < p.n_peers; ++pr) {
+                for (int i = 1; i <= p.n_peers; ++i) {
+                    int pr = p.peer_rank + i;
+                    if (pr >= p.n_peers) pr -= p.n_peers;
                     *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
                                               static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
                 }
@@ -232,6 +237,55 @@ __device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t 
         }
     }
     __syncwarp();
+}
+
+// The same for a 32-column block (the tail of tile widths that are not a multiple of 64): 32 rows x 64 bytes,
+// 16-byte packet c of row r at stage[r * 4 + (c ^ ((r >> 1) & 3))]; each store instruction writes eight 64-byte
+// row segments.
+template <uint32_t KIND, bool FUSED>
+__device__ __forceinline__ void epilogue_block_32(const GemmParams& p, uint32_t t_addr, int row_base, int lane,
+                                                  int col0, float sa_row, const float* sb32, uint4* stage) {
+    {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(t_addr, r);
+        tmem_ld_wait();
+        uint4 pk[4];
+        dequant_pack_32<KIND>(p, r, sa_row, sb32, pk);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = pk[v];
+    }
+    __syncwarp();
+    const int sub_row = lane >> 2;  // 0..7
+    const int c = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rr = i * 8 + sub_row;
+        const int row = row_base + rr;
+        const uint4 v = stage[rr * 4 + (c ^ ((rr >> 1) & 3))];
+        if (row < p.m) {
+            if (p.d != nullptr) {
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0 +
+                                          c * 8) = v;
+            }
+            if constexpr (FUSED) {
+                for (int j = 1; j <= p.n_peers; ++j) {
+                    int pr = p.peer_rank + j;
+                    if (pr >= p.n_peers) pr -= p.n_peers;
+                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
+                                              static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
+template <bool FUSED>
+__device__ __forceinline__ bool block_32_ok(const GemmParams& p, int col0) {
+    bool ok = p.coalesce && p.vec_store && (col0 + 32 <= p.n);
+    if constexpr (FUSED) ok = ok && p.peer_vec;
+    return ok;
 }
 
 // True when the 64-column block starting at col0 can take the coalesced path.

@@ -237,6 +237,13 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 for (; c < PAIR_TILE_N / 32; ++c) {
                     const int col0 = n_blk * PAIR_TILE_N + c * 32;
                     if (col0 >= p.n) break;  // warp-uniform
+                    if constexpr (!RAW) {
+                        if (block_32_ok<FUSED>(p, col0)) {
+                            epilogue_block_32<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
+                                                           sb_tile + c * 32, stage_buf);
+                            continue;
+                        }
+                    }
                     uint32_t r[32];
                     __syncwarp();
                     tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
@@ -299,6 +306,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;
     p.peer_col0 = g.peer_col0;
+    p.peer_rank = g.peer_rank;
     p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
     for (int r = 0; r < 8; ++r) {
         p.peer_d[r] = g.peer_d[r];

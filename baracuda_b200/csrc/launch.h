@@ -49,6 +49,7 @@ struct GemmDesc {
     int32_t n_peers;  // 0 = off
     int64_t peer_ld;
     int32_t peer_col0;
+    int32_t peer_rank;
 };
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);

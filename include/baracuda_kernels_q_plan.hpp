@@ -152,7 +152,7 @@ class W8A8GemmPlan {
                         W8A8GemmPlan* out) {
         if (!detail::backend_ok(pref)) return Error::Unsupported;
         if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
-        if (desc.layout != LayoutSku::Rcr || desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
+        if (desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
         out->desc_ = desc;
         out->raw_ = raw_accumulators;
         out->sku_ = KernelSku{OpCategory::Gemm, OP_W8A8_GEMM, ElementKind::S8,
@@ -169,15 +169,17 @@ class W8A8GemmPlan {
                     : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
     }
     Error can_implement(const QGemmArgs& x) const {
-        const int32_t st =
-            raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda,
-                                                                         x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd)
-                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
-                       desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
+        const bool rrr = desc_.layout == LayoutSku::Rrr;
+        auto can = rrr ? (raw_ ? baracuda_kernels_gemm_s8_rrr_s32_sm100a_can_implement
+                               : baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_can_implement)
+                       : (raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement
+                               : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement);
+        const int32_t st = can(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
         if (st != 0) return status_to_error(st);
         if (desc_.m == 0 || desc_.n == 0) return Error::Ok;  // empty problem: nothing is read or written
         if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
-        if (x.b.len < detail::span_elems(desc_.n, desc_.k, x.ldb)) return Error::BufferTooSmall;
+        if (x.b.len < (rrr ? detail::span_elems(desc_.k, desc_.n, x.ldb) : detail::span_elems(desc_.n, desc_.k, x.ldb)))
+            return Error::BufferTooSmall;
         if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
         if (!raw_) {
             if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
@@ -189,13 +191,17 @@ class W8A8GemmPlan {
     Error run(void* stream, Workspace ws, const QGemmArgs& x) const {
         if (Error e = can_implement(x); e != Error::Ok) return e;
         if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
-        const int32_t st =
-            raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb,
-                                                               nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta, ws.ptr,
-                                                               ws.bytes, stream)
-                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
-                       desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd,
-                       x.scale_a.ptr, x.scale_b.ptr, x.alpha, x.beta, ws.ptr, ws.bytes, stream);
+        const bool rrr = desc_.layout == LayoutSku::Rrr;
+        int32_t st;
+        if (raw_) {
+            auto run = rrr ? baracuda_kernels_gemm_s8_rrr_s32_sm100a_run : baracuda_kernels_gemm_s8_rcr_s32_sm100a_run;
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta,
+                     ws.ptr, ws.bytes, stream);
+        } else {
+            auto run = rrr ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run;
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+                     x.scale_b.ptr, x.alpha, x.beta, ws.ptr, ws.bytes, stream);
+        }
         return status_to_error(st);
     }
 
@@ -261,6 +267,61 @@ class Fp8ScaledGemmPlan {
     KernelSku sku_{};
     ScaleMode mode_ = ScaleMode::PerTensor;
     bool raw_ = false;
+};
+
+// The reference's own 8-bit-out contract (IntGemmPlan<S8> / Fp8GemmPlan<Fp8E4M3>, identity epilogue, Rcr or Rrr):
+// D = sat(alpha * acc + beta * C) in the input type.  `c` may be empty when beta == 0.
+struct Q8OutGemmArgs {
+    DeviceSpan<const void> a;
+    int64_t lda = 0;
+    DeviceSpan<const void> b;
+    int64_t ldb = 0;
+    DeviceSpan<const void> c;
+    int64_t ldc = 0;
+    DeviceSpan<void> d;
+    int64_t ldd = 0;
+    float alpha = 1.0f;
+    float beta = 0.0f;
+};
+
+class IntGemmPlan {
+  public:
+    static Error select(const QGemmDescriptor& desc, const PlanPreference& pref, ElementKind element, IntGemmPlan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
+        if (desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
+        if (element != ElementKind::S8 && element != ElementKind::Fp8E4M3) return Error::Unsupported;
+        const bool fp8 = element == ElementKind::Fp8E4M3;
+        out->desc_ = desc;
+        out->fp8_ = fp8;
+        out->sku_ = KernelSku{OpCategory::Gemm, fp8 ? OP_FP8_SCALED_GEMM : OP_W8A8_GEMM, element, std::nullopt, desc.layout,
+                              desc.epilogue, ArchSku::Sm100a, BackendKind::Bespoke,
+                              PrecisionGuarantee{fp8 ? MathPrecision::Fp8E4M3 : MathPrecision::Int8,
+                                                 fp8 ? ElementKind::F32 : ElementKind::I32, true, true}};
+        return Error::Ok;
+    }
+    const KernelSku& sku() const { return sku_; }
+    PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
+    size_t workspace_size() const { return 0; }
+    Error run(void* stream, Workspace ws, const Q8OutGemmArgs& x) const {
+        const bool rrr = desc_.layout == LayoutSku::Rrr;
+        if (desc_.m > 0 && desc_.n > 0) {
+            if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
+            if (x.b.len < (rrr ? detail::span_elems(desc_.k, desc_.n, x.ldb) : detail::span_elems(desc_.n, desc_.k, x.ldb)))
+                return Error::BufferTooSmall;
+            if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
+            if (x.beta != 0.0f && x.c.len < detail::span_elems(desc_.m, desc_.n, x.ldc)) return Error::BufferTooSmall;
+        }
+        auto fn = fp8_ ? (rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run : baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run)
+                       : (rrr ? baracuda_kernels_gemm_s8_rrr_sm100a_run : baracuda_kernels_gemm_s8_rcr_sm100a_run);
+        return status_to_error(fn(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd,
+                                  x.alpha, x.beta, ws.ptr, ws.bytes, stream));
+    }
+
+  private:
+    QGemmDescriptor desc_{};
+    KernelSku sku_{};
+    bool fp8_ = false;
 };
 
 // ---------------------------------------------------------------------------- GEMV

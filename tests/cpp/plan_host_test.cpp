@@ -35,7 +35,18 @@ int main() {
 
     QGemmDescriptor rrr = desc;
     rrr.layout = LayoutSku::Rrr;
-    CHECK(W8A8GemmPlan::select(rrr, pref, false, &p) == Error::Unsupported);
+    CHECK(W8A8GemmPlan::select(rrr, pref, false, &p) == Error::Ok);
+    CHECK(*p.sku().layout == LayoutSku::Rrr);
+    IntGemmPlan q8;
+    CHECK(IntGemmPlan::select(desc, pref, ElementKind::S8, &q8) == Error::Ok);
+    CHECK(q8.sku().element == ElementKind::S8 && !q8.sku().aux_element);
+    CHECK(IntGemmPlan::select(desc, pref, ElementKind::Bf16, &q8) == Error::Unsupported);
+    CHECK(IntGemmPlan::select(rrr, pref, ElementKind::Fp8E4M3, &q8) == Error::Ok);
+    Q8OutGemmArgs qa;
+    qa.lda = 1024;
+    qa.ldb = 1024;
+    qa.ldd = 1024;
+    CHECK(q8.run(nullptr, Workspace::none(), qa) == Error::BufferTooSmall);  // the typed layer refuses empty views
     QGemmDescriptor bias = desc;
     bias.epilogue = EpilogueKind::BiasRelu;
     CHECK(W8A8GemmPlan::select(bias, pref, false, &p) == Error::Unsupported);
