@@ -59,7 +59,7 @@ class ClockSampler:
         try:
             uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -347,12 +347,11 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- device-resident timing
+    # ---- device-resident timing (clocks are sampled from here to the end of the end-to-end arm: same kernel, same load)
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms = event_time_ms(step, steps=args.steps, warmup=args.warmup, flush=flush)
     barrier()
-    clocks = sampler.stop() if sampler else None
     status = bq.device_status()
     total_ms = max_over_ranks(sum(ms))
     ops_total = 2.0 * C4_M * C4_N * C4_K
@@ -377,6 +376,7 @@ def main() -> None:
     barrier()
     e2e_total = max_over_ranks(sum(e2e_ms))
     e2e_value = ops_total * e2e_steps / (e2e_total * 1e-3) / 1e12
+    clocks = sampler.stop() if sampler else None
 
     others = {}
     if world > 1:

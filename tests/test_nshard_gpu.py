@@ -32,7 +32,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         ctx = par.TensorParallelContext.from_torch_distributed()
         dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
         bits = lambda t: t.cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
-        for kind, (m, n, k) in (("w8a8", (300, 1024, 512)), ("fp8", (1024, 2048, 1024))):
+        for kind, (m, n, k) in (("w8a8", (300, 1024, 512)), ("fp8", (1024, 2048, 1024)), ("w8a8", (300, 224 * 4 * world, 512))):
             rng = np.random.default_rng(5)
             a = rng.standard_normal((m, k)).astype(np.float32)
             w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
