@@ -56,6 +56,16 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
     "baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_workspace_size": _GEMM_WS,
     "baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_can_implement": _GEMM_CAN,
+    **{f"baracuda_kernels_gemm_{fam}_{lay}_sm100a_epilogue_run":
+           (_i32, _GEMM_PREFIX + [_vp, _i32, _i32, _f32, _f32] + _TAIL)
+       for fam in ("s8", "fp8_e4m3") for lay in ("rcr", "rrr")},
+    **{f"baracuda_kernels_gemm_s8_{lay}_sm100a_bias{act}_{bk}_run": (_i32, _GEMM_PREFIX + [_vp, _f32, _f32] + _TAIL)
+       for lay in ("rcr", "rrr") for act in ("", "_relu", "_gelu", "_silu") for bk in ("f32", "i32")},
+    **{f"baracuda_kernels_gemm_fp8_e4m3_{lay}_sm100a_bias{act}_run": (_i32, _GEMM_PREFIX + [_vp, _f32, _f32] + _TAIL)
+       for lay in ("rcr", "rrr") for act in ("", "_relu", "_gelu", "_silu")},
+    **{f"baracuda_kernels_gemm_{fam}_{lay}_bf16_sm100a_epilogue_run":
+           (_i32, _GEMM_PREFIX + [_vp, _vp, _i32, _vp, _i32, _f32, _f32] + _TAIL)
+       for fam in ("w8a8_s8", "fp8_e4m3") for lay in ("rcr", "rrr")},
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_run": (
         _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement": _GEMV_CAN,

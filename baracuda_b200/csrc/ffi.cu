@@ -44,9 +44,34 @@ int32_t gemm_rcr_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_
     return gemm_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
 
+// Fused epilogue chain of the reference's EpilogueKind (crates/baracuda-kernel-vocab/src/layout.rs:69-96):
+// 0 Identity, 1 Bias, 2 BiasRelu, 3 BiasGelu, 4 BiasSilu; bias_kind 1 = float[N], 2 = int32[N].
+struct Epilogue {
+    const void* bias = nullptr;
+    int32_t bias_kind = 0;
+    int32_t kind = 0;
+};
+
+// 0 ok; 2 when the chain and the bias pointer disagree
+int32_t epilogue_validate(const Epilogue& e, bool allow_i32_bias) {
+    if (e.kind < 0 || e.kind > 4) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (e.kind == 0) return bq::BQ_STATUS_OK;
+    if (!e.bias) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (e.bias_kind != 1 && !(allow_i32_bias && e.bias_kind == 2)) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (reinterpret_cast<uintptr_t>(e.bias) & 3u) return bq::BQ_STATUS_MISALIGNED;
+    return bq::BQ_STATUS_OK;
+}
+
+void epilogue_apply(const Epilogue& e, bq::GemmDesc& g) {
+    g.bias = e.kind > 0 ? e.bias : nullptr;
+    g.bias_kind = e.kind > 0 ? e.bias_kind : 0;
+    g.act = e.kind >= 2 ? e.kind - 1 : 0;  // 1 relu, 2 gelu, 3 silu
+}
+
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
-                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream);
+                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream,
+                 const Epilogue& epi = Epilogue());
 
 int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                      const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd,
@@ -58,9 +83,12 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
 
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
-                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream) {
+                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream, const Epilogue& epi) {
     const int32_t st = gemm_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
+    if (const int32_t es = epilogue_validate(epi, false); es != bq::BQ_STATUS_OK) return es;
+    if (raw && epi.kind != 0) return bq::BQ_STATUS_UNSUPPORTED;
+    if (k == 0 && epi.kind != 0) return bq::BQ_STATUS_UNSUPPORTED;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (beta != 0.0f) return bq::BQ_STATUS_UNSUPPORTED;
@@ -71,7 +99,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
         if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
             return bq::BQ_STATUS_INVALID_PROBLEM;
     }
-    bq::GemmDesc g;
+    bq::GemmDesc g = {};
     g.b_layout = layout;
     g.kind = kind;
     g.raw_out = raw;
@@ -96,6 +124,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.peer_col0 = 0;
     g.peer_rank = 0;
     for (auto& pd : g.peer_d) pd = nullptr;
+    epilogue_apply(epi, g);
     g.q8_out = 0;
     g.c = nullptr;
     g.ldc = 0;
@@ -114,14 +143,15 @@ int32_t gemm_q8_validate(int32_t layout, int32_t m, int32_t n, int32_t k, const 
 
 int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                     const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, float alpha, float beta,
-                    void* stream) {
+                    void* stream, const Epilogue& epi = Epilogue()) {
     const int32_t st = gemm_q8_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
+    if (const int32_t es = epilogue_validate(epi, kind == bq::BQ_KIND_S8); es != bq::BQ_STATUS_OK) return es;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (beta != 0.0f && !c) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
-    bq::GemmDesc g;
+    bq::GemmDesc g = {};
     g.b_layout = layout;
     g.kind = kind;
     g.raw_out = 0;
@@ -144,6 +174,7 @@ int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t 
     g.ldd = ldd;
     g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
     g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    epilogue_apply(epi, g);
     g.direct_stores = 1;
     g.n_peers = 0;
     g.peer_ld = 0;
@@ -229,7 +260,7 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
         return bq::BQ_STATUS_INVALID_PROBLEM;
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
-    bq::GemmDesc g;
+    bq::GemmDesc g = {};
     g.b_layout = bq::BQ_LAYOUT_RCR;
     g.kind = kind;
     g.raw_out = 0;
@@ -421,6 +452,76 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run(
     return gemm_q8_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
 }
 BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a, gemm_q8_validate)
+
+// ---- fused bias / activation epilogues -----------------------------------------------------------
+#define BQ_Q8_EPILOGUE_RUN(NAME, LAYOUT, KIND)                                                                           \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,   \
+                 int64_t ldc, void* d, int64_t ldd, const void* bias, int32_t bias_kind, int32_t epilogue, float alpha,    \
+                 float beta, void* workspace, size_t workspace_bytes, void* stream) {                                      \
+        (void)workspace;                                                                                                   \
+        (void)workspace_bytes;                                                                                             \
+        Epilogue e;                                                                                                        \
+        e.bias = bias;                                                                                                     \
+        e.bias_kind = bias_kind;                                                                                           \
+        e.kind = epilogue;                                                                                                 \
+        return gemm_q8_run(LAYOUT, KIND, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream, e);                 \
+    }
+BQ_Q8_EPILOGUE_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_epilogue_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8)
+BQ_Q8_EPILOGUE_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8)
+BQ_Q8_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_epilogue_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_E4M3)
+BQ_Q8_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3)
+
+// the reference's named variants: ..._bias[_relu|_gelu|_silu]_{f32,i32}_run (s8) and ..._bias[_act]_run (e4m3)
+#define BQ_Q8_NAMED_BIAS_RUN(NAME, LAYOUT, KIND, BIAS_KIND, EPI)                                                          \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,   \
+                 int64_t ldc, void* d, int64_t ldd, const void* bias, float alpha, float beta, void* workspace,            \
+                 size_t workspace_bytes, void* stream) {                                                                   \
+        (void)workspace;                                                                                                   \
+        (void)workspace_bytes;                                                                                             \
+        Epilogue e;                                                                                                        \
+        e.bias = bias;                                                                                                     \
+        e.bias_kind = BIAS_KIND;                                                                                           \
+        e.kind = EPI;                                                                                                      \
+        return gemm_q8_run(LAYOUT, KIND, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream, e);                 \
+    }
+#define BQ_S8_BIAS_FAMILY(LAY, LAYOUT)                                                                                     \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_f32_run, LAYOUT, bq::BQ_KIND_S8, 1, 1)              \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_relu_f32_run, LAYOUT, bq::BQ_KIND_S8, 1, 2)         \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_gelu_f32_run, LAYOUT, bq::BQ_KIND_S8, 1, 3)         \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_silu_f32_run, LAYOUT, bq::BQ_KIND_S8, 1, 4)         \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_i32_run, LAYOUT, bq::BQ_KIND_S8, 2, 1)              \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_relu_i32_run, LAYOUT, bq::BQ_KIND_S8, 2, 2)         \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_gelu_i32_run, LAYOUT, bq::BQ_KIND_S8, 2, 3)         \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_s8_##LAY##_sm100a_bias_silu_i32_run, LAYOUT, bq::BQ_KIND_S8, 2, 4)
+BQ_S8_BIAS_FAMILY(rcr, bq::BQ_LAYOUT_RCR)
+BQ_S8_BIAS_FAMILY(rrr, bq::BQ_LAYOUT_RRR)
+#define BQ_FP8_BIAS_FAMILY(LAY, LAYOUT)                                                                                    \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_##LAY##_sm100a_bias_run, LAYOUT, bq::BQ_KIND_E4M3, 1, 1)          \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_##LAY##_sm100a_bias_relu_run, LAYOUT, bq::BQ_KIND_E4M3, 1, 2)     \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_##LAY##_sm100a_bias_gelu_run, LAYOUT, bq::BQ_KIND_E4M3, 1, 3)     \
+    BQ_Q8_NAMED_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_##LAY##_sm100a_bias_silu_run, LAYOUT, bq::BQ_KIND_E4M3, 1, 4)
+BQ_FP8_BIAS_FAMILY(rcr, bq::BQ_LAYOUT_RCR)
+BQ_FP8_BIAS_FAMILY(rrr, bq::BQ_LAYOUT_RRR)
+
+// bf16-out SKUs with the fused chain: D = bf16( act( alpha * ((sa*sb) * acc) + bias[j] ) ), bias float[N]
+#define BQ_BF16_EPILOGUE_RUN(NAME, LAYOUT, KIND, HAS_MODE)                                                                 \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,   \
+                 int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,          \
+                 const void* bias, int32_t epilogue, float alpha, float beta, void* workspace, size_t workspace_bytes,     \
+                 void* stream) {                                                                                           \
+        (void)workspace;                                                                                                   \
+        (void)workspace_bytes;                                                                                             \
+        Epilogue e;                                                                                                        \
+        e.bias = bias;                                                                                                     \
+        e.bias_kind = 1;                                                                                                   \
+        e.kind = epilogue;                                                                                                 \
+        return gemm_run(LAYOUT, KIND, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,                        \
+                        HAS_MODE ? scale_mode : BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, e);                     \
+    }
+BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8, false)
+BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, false)
+BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_E4M3, true)
+BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, true)
 
 // ---- int8 GEMV ---------------------------------------------------------------------
 int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(

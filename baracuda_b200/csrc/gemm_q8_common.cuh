@@ -35,7 +35,29 @@ struct GemmParams {
     const void* c;
     int64_t ldc;
     float beta;
+    // fused epilogue chain of the reference's EpilogueKind: per-column bias (f32 or i32), then an activation
+    const void* bias;
+    int bias_kind;  // 0 none, 1 float[N], 2 int32[N]
+    int act;        // 0 none, 1 relu, 2 gelu (erf form), 3 silu
 };
+
+// bias[col] then activation, in f32 — the formulas of the reference's epilogue header
+// (crates/baracuda-kernels-sys/kernels/include/baracuda_epilogue_int8.cuh:52-95).
+__device__ __forceinline__ float apply_bias_act(const GemmParams& p, float z, int col) {
+    if (p.bias_kind == 1) {
+        z = __fadd_rn(z, __ldg(reinterpret_cast<const float*>(p.bias) + col));
+    } else if (p.bias_kind == 2) {
+        z = __fadd_rn(z, static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col)));
+    }
+    if (p.act == 1) {
+        z = fmaxf(z, 0.0f);
+    } else if (p.act == 2) {
+        z = 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+    } else if (p.act == 3) {
+        z = z / (1.0f + __expf(-z));
+    }
+    return z;
+}
 
 // One thread, one output row, 32 consecutive columns starting at col0 (a multiple of 32).
 // `r` holds the accumulators as read from TMEM, `sb32` the 32 column scales.
@@ -75,6 +97,7 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
                     if (crow && col0 + j < p.n) {
                         z = __fadd_rn(z, __fmul_rn(p.beta, static_cast<float>(static_cast<int8_t>(crow[j]))));
                     }
+                    if ((p.bias_kind | p.act) != 0 && col0 + j < p.n) z = apply_bias_act(p, z, col0 + j);
                     int q = __float2int_rn(z);
                     q = q < -128 ? -128 : (q > 127 ? 127 : q);
                     out = static_cast<uint8_t>(static_cast<int8_t>(q));
@@ -84,6 +107,7 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
                         const __half_raw hr = __nv_cvt_fp8_to_halfraw(crow[j], __NV_E4M3);
                         z = __fadd_rn(z, __fmul_rn(p.beta, __half2float(__half(hr))));
                     }
+                    if ((p.bias_kind | p.act) != 0 && col0 + j < p.n) z = apply_bias_act(p, z, col0 + j);
                     out = static_cast<uint8_t>(__nv_cvt_float_to_fp8(z, __NV_SATFINITE, __NV_E4M3));
                 }
                 word |= static_cast<uint32_t>(out) << (8 * b);
@@ -114,6 +138,12 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
             // product order, no fused multiply-add.
             const float s = __fmul_rn(sa_row, sb32[j]);
             y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
+        }
+        if ((p.bias_kind | p.act) != 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.n) y[j] = apply_bias_act(p, y[j], col0 + j);
+            }
         }
         uint4 pk[4];
 #pragma unroll
@@ -162,7 +192,7 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
 // Converts 32 accumulator columns of this thread's row into 32 bf16 (four 16-byte packets).
 template <uint32_t KIND>
 __device__ __forceinline__ void dequant_pack_32(const GemmParams& p, const uint32_t (&r)[32], float sa_row,
-                                                const float* sb32, uint4 (&pk)[4]) {
+                                                const float* sb32, uint4 (&pk)[4], int col0) {
     float y[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -174,6 +204,10 @@ __device__ __forceinline__ void dequant_pack_32(const GemmParams& p, const uint3
         }
         const float s = __fmul_rn(sa_row, sb32[j]);
         y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
+    }
+    if ((p.bias_kind | p.act) != 0) {  // the staged path only runs on full, in-range blocks
+#pragma unroll
+        for (int j = 0; j < 32; ++j) y[j] = apply_bias_act(p, y[j], col0 + j);
     }
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
@@ -206,7 +240,7 @@ __device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t 
         tmem_ld_32x32b_x32(t_addr + static_cast<uint32_t>(half * 32), r);
         tmem_ld_wait();
         uint4 pk[4];
-        dequant_pack_32<KIND>(p, r, sa_row, sb64 + half * 32, pk);
+        dequant_pack_32<KIND>(p, r, sa_row, sb64 + half * 32, pk, col0 + half * 32);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
             const int c = half * 4 + v;
@@ -251,7 +285,7 @@ __device__ __forceinline__ void epilogue_block_32(const GemmParams& p, uint32_t 
         tmem_ld_32x32b_x32(t_addr, r);
         tmem_ld_wait();
         uint4 pk[4];
-        dequant_pack_32<KIND>(p, r, sa_row, sb32, pk);
+        dequant_pack_32<KIND>(p, r, sa_row, sb32, pk, col0);
 #pragma unroll
         for (int v = 0; v < 4; ++v) stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = pk[v];
     }

@@ -302,6 +302,9 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     p.c = g.c;
     p.ldc = g.ldc;
     p.beta = g.beta;
+    p.bias = g.bias;
+    p.bias_kind = g.bias ? g.bias_kind : 0;
+    p.act = g.act;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;

@@ -45,6 +45,7 @@ struct GemvParams {
     int kslice_rows, num_kslices;
     int32_t* ws_partials;
     unsigned int* ws_tickets;
+    int mma_groups;  // tensor-core GEMV: 8-column groups per CTA (upper bound), sizes the shared accumulator
     int pdl;  // launched with programmatic stream serialization: weights may be fetched before the dependency wait
 };
 
@@ -349,7 +350,6 @@ gemv_q8_rcr_stream_kernel(const GemvParams p) {
 // grow with m.  Items of one column group that belong to different K chunks (and warps) meet in a
 // small shared-memory accumulator. ----
 constexpr int MMA_COLS = 8;                    // weight rows (output columns) per item
-constexpr int MMA_RING = 2;                    // items in flight per warp
 constexpr int MMA_MAX_GROUPS = 64;             // column groups per CTA the accumulator holds
 constexpr int MMA_MAX_K = 8192;
 
@@ -363,7 +363,8 @@ __device__ __forceinline__ void mma_s8_16x8x32(int (&d)[4], uint32_t a0, uint32_
 
 // MMA_KCHUNK: bytes of K per item and row; MMA_WARPS: streaming warps.  The row pitch in the ring is
 // KCHUNK + 64 so that 16-byte reads of 8 rows hit 8 distinct bank groups.
-template <bool RAW, int MMA_KCHUNK, int MMA_WARPS>
+// MMA_RING: items in flight per warp.
+template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 1)
 gemv_q8_rcr_mma_kernel(const GemvParams p) {
     constexpr int MMA_PITCH = MMA_KCHUNK + 64;
@@ -376,9 +377,10 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     const int xpitch = p.k + 64;
     uint8_t* ring = mma_smem + warp * MMA_RING * MMA_ITEM_BYTES;
     uint8_t* xs = mma_smem + MMA_WARPS * MMA_RING * MMA_ITEM_BYTES;
-    int* acc_s = reinterpret_cast<int*>(xs + 8 * xpitch);
-    float* sb_s = reinterpret_cast<float*>(acc_s + MMA_MAX_GROUPS * 64);  // this CTA's column scales
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sb_s + MMA_MAX_GROUPS * MMA_COLS);
+    // only the m real activation rows and this launch's groups per CTA take shared memory
+    int* acc_s = reinterpret_cast<int*>(xs + p.m * xpitch);
+    float* sb_s = reinterpret_cast<float*>(acc_s + p.mma_groups * 64);  // this CTA's column scales
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sb_s + p.mma_groups * MMA_COLS);
     uint64_t* full_bar = bars + warp * MMA_RING;
     volatile uint32_t* abort_word = reinterpret_cast<volatile uint32_t*>(bars + MMA_WARPS * MMA_RING) + warp;
 
@@ -752,17 +754,22 @@ int32_t launch_rcr_stream(const GemvParams& p, int batch, cudaStream_t stream) {
     return launch_rcr_stream_cfg<MR, RAW, (MR == 1) ? 16 : 8, STREAM_RING_FULL>(p, batch, sms, stream);
 }
 
-template <bool RAW, int KCHUNK, int WARPS>
-int32_t launch_rcr_mma_cfg(const GemvParams& p, int batch, int sms, cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(WARPS) * MMA_RING * MMA_COLS * (KCHUNK + 64) + 8 * static_cast<size_t>(p.k + 64) +
-                        MMA_MAX_GROUPS * 64 * 4 + MMA_MAX_GROUPS * MMA_COLS * 4 + WARPS * MMA_RING * 8 + WARPS * 4;
-    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS>;
+size_t mma_smem_bytes(int kchunk, int warps, int ring, int m, int k, int groups) {
+    return static_cast<size_t>(warps) * ring * MMA_COLS * (kchunk + 64) + static_cast<size_t>(m) * (k + 64) +
+           static_cast<size_t>(groups) * 64 * 4 + static_cast<size_t>(groups) * MMA_COLS * 4 + warps * ring * 8 + warps * 4 + 16;
+}
+
+template <bool RAW, int KCHUNK, int WARPS, int RING>
+int32_t launch_rcr_mma_cfg(GemvParams p, int batch, int sms, cudaStream_t stream) {
+    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;  // no more CTAs than 8-column groups
+    const int ctas = want < sms ? want : sms;
+    p.mma_groups = (want + ctas - 1) / ctas;
+    const size_t smem = mma_smem_bytes(KCHUNK, WARPS, RING, p.m, p.k, p.mma_groups);
+    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
     }
-    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;  // no more CTAs than 8-column groups
-    const int ctas = want < sms ? want : sms;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas, batch, 1);
     cfg.blockDim = dim3(WARPS * 32, 1, 1);
@@ -784,11 +791,17 @@ template <bool RAW>
 int32_t launch_rcr_mma(const GemvParams& p, int batch, int shape_variant, cudaStream_t stream) {
     const int sms = sm_count_cached();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
-    // 2 KiB copies on 4 warps when the activations leave room for the bigger ring, else 1 KiB copies on 8 warps
-    // 1 KiB copies on 8 warps by default; 32 = 2 KiB copies on 4 warps, 33 = 512-byte copies on 16 warps
-    if (shape_variant == 32 && p.k <= 4096) return launch_rcr_mma_cfg<RAW, 2048, 4>(p, batch, sms, stream);
-    if (shape_variant == 33) return launch_rcr_mma_cfg<RAW, 512, 16>(p, batch, sms, stream);
-    return launch_rcr_mma_cfg<RAW, 1024, 8>(p, batch, sms, stream);
+    // 32 = 2 KiB copies on 4 warps, 33 = 512-byte copies on 16 warps, 34 = three items in flight per warp
+    if (shape_variant == 32 && p.k <= 4096) return launch_rcr_mma_cfg<RAW, 2048, 4, 2>(p, batch, sms, stream);
+    if (shape_variant == 33) return launch_rcr_mma_cfg<RAW, 512, 16, 2>(p, batch, sms, stream);
+    // default: 1 KiB copies on 8 warps, two items in flight per warp (a third measured no faster)
+    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = want < sms ? want : sms;
+    const int groups = (want + ctas - 1) / ctas;
+    if (shape_variant == 34 && mma_smem_bytes(1024, 8, 3, p.m, p.k, groups) <= 232448) {
+        return launch_rcr_mma_cfg<RAW, 1024, 8, 3>(p, batch, sms, stream);
+    }
+    return launch_rcr_mma_cfg<RAW, 1024, 8, 2>(p, batch, sms, stream);
 }
 
 // The tensor-core GEMV serves K-contiguous weights when K is a multiple of 64 bytes, fits the
@@ -857,6 +870,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     p.kslice_rows = 0; p.num_kslices = 1;
     p.ws_partials = nullptr; p.ws_tickets = nullptr;
     p.pdl = g.pdl;
+    p.mma_groups = 0;
 
     // the streaming kernels need 16-byte alignment of every weight row segment they load
     bool fast = g.k > 0 && aligned16(g.a) && aligned16(g.b) && (g.stride_b % 16 == 0) && (g.ldb % 16 == 0);
@@ -875,7 +889,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     // (variant 3 forces it also for m == 1, variant 2 and 1 keep it off)
     if (g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
         ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3 ||
-         g.variant == 31 || g.variant == 32 || g.variant == 33)) {  // 31 / 32 / 33 force a copy-size configuration
+         (g.variant >= 31 && g.variant <= 34))) {  // 31..34 force a copy-size / ring configuration
         return launch_rcr_mma<RAW>(p, g.batch, g.variant, stream);
     }
     // K-contiguous weights with few activation rows: the bulk-copy streaming kernel

@@ -29,6 +29,9 @@ struct GemmDesc {
     const void* c;    // q8_out only
     int64_t ldc;
     float beta;
+    const void* bias;   // per-column bias of the fused epilogue, or null
+    int32_t bias_kind;  // 0 none, 1 float[N], 2 int32[N]
+    int32_t act;        // 0 none, 1 relu, 2 gelu, 3 silu
     int32_t m, n, k;
     const void* a;
     int64_t lda;

@@ -100,6 +100,12 @@ class QGemmArgs:
     beta: float = 0.0
     c: Optional[torch.Tensor] = None
     ldc: int = 0
+    bias: Optional[torch.Tensor] = None  # [N] float32 (or int32 on the s8 8-bit-out plan) when the epilogue has one
+
+
+# EpilogueKind -> the `epilogue` argument of the *_epilogue_run symbols
+_EPILOGUE_CODE = {EpilogueKind.Identity: 0, EpilogueKind.Bias: 1, EpilogueKind.BiasRelu: 2, EpilogueKind.BiasGelu: 3,
+                  EpilogueKind.BiasSilu: 4}
 
 
 class _QGemmPlanBase:
@@ -109,6 +115,7 @@ class _QGemmPlanBase:
     _in_dtypes: tuple = ()
     _out_dtype = torch.bfloat16
     _needs_scales = True
+    _bias_dtypes: tuple = (torch.float32,)
 
     def __init__(self, desc: QGemmDescriptor, sku: KernelSku):
         self.desc = desc
@@ -121,8 +128,8 @@ class _QGemmPlanBase:
             raise InvalidProblem("negative dimension")
         if max(desc.m, desc.n, desc.k) >= 2**31:
             raise InvalidProblem("dimension exceeds int32")
-        if desc.epilogue is not EpilogueKind.Identity:
-            raise Unsupported("bias / activation epilogues are not built for the sm_100a SKUs")
+        if desc.epilogue not in _EPILOGUE_CODE:
+            raise InvalidProblem("unknown epilogue")
 
     def sku(self) -> KernelSku:
         return self._sku
@@ -162,6 +169,15 @@ class _QGemmPlanBase:
         _need(args.d, _span(d.m, d.n, ldd), "d")
         if self._needs_scales:
             self._check_scales(args)
+        if d.epilogue.requires_bias():
+            if args.bias is None:
+                raise InvalidProblem(f"epilogue {d.epilogue.value} needs a bias vector")
+            if args.bias.dtype not in self._bias_dtypes or not args.bias.is_cuda:
+                raise InvalidProblem(f"bias: expected a device vector of {self._bias_dtypes}")
+            _need(args.bias, d.n, "bias")
+
+    def _bias_kind(self, args: QGemmArgs) -> int:
+        return 2 if args.bias is not None and args.bias.dtype == torch.int32 else 1
 
     def _check_scales(self, args: QGemmArgs) -> None:
         raise NotImplementedError
@@ -200,6 +216,8 @@ class W8A8GemmPlan(_QGemmPlanBase):
     def select(cls, stream, desc: QGemmDescriptor, pref: PlanPreference = PlanPreference(),
                raw_accumulators: bool = False) -> "W8A8GemmPlan":
         cls._validate_desc(desc, pref)
+        if raw_accumulators and desc.epilogue is not EpilogueKind.Identity:
+            raise Unsupported("the raw-accumulator SKU has the identity epilogue only")
         sku = KernelSku(OpCategory.Gemm, OP_W8A8_GEMM, ElementKind.S8,
                         ElementKind.I32 if raw_accumulators else ElementKind.Bf16,
                         desc.layout, desc.epilogue, ArchSku.Sm100a, BackendKind.Bespoke, _INT_GUARANTEE)
@@ -218,6 +236,11 @@ class W8A8GemmPlan(_QGemmPlanBase):
         if self.raw:
             return getattr(lib, self._run_symbol)(
                 d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+        if d.epilogue is not EpilogueKind.Identity:
+            return getattr(lib, self._run_symbol.replace("_run", "_epilogue_run"))(
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                _ptr(args.scale_a), _ptr(args.scale_b), SCALE_PER_ROW_COL, _ptr(args.bias), _EPILOGUE_CODE[d.epilogue],
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
         return getattr(lib, self._run_symbol)(
             d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
@@ -248,6 +271,8 @@ class Fp8ScaledGemmPlan(_QGemmPlanBase):
         cls._validate_desc(desc, pref)
         if scale_mode not in (SCALE_PER_TENSOR, SCALE_PER_ROW_COL):
             raise InvalidProblem("scale_mode must be 0 (per tensor) or 1 (per row / per column)")
+        if raw_accumulators and desc.epilogue is not EpilogueKind.Identity:
+            raise Unsupported("the raw-accumulator SKU has the identity epilogue only")
         sku = KernelSku(OpCategory.Gemm, OP_FP8_SCALED_GEMM, ElementKind.Fp8E4M3,
                         ElementKind.F32 if raw_accumulators else ElementKind.Bf16,
                         desc.layout, desc.epilogue, ArchSku.Sm100a, BackendKind.Bespoke, _FP8_GUARANTEE)
@@ -268,6 +293,11 @@ class Fp8ScaledGemmPlan(_QGemmPlanBase):
         if self.raw:
             return lib.baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(
                 d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+        if d.epilogue is not EpilogueKind.Identity:
+            return getattr(lib, self._run_symbol.replace("_run", "_epilogue_run"))(
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, _ptr(args.bias), _EPILOGUE_CODE[d.epilogue],
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
         return getattr(lib, self._run_symbol)(
             d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
@@ -526,11 +556,12 @@ class QuantizedLinearPlan:
 # --------------------------------------------------------------------------- the reference's 8-bit-out plans
 class IntGemmPlan(_QGemmPlanBase):
     """`IntGemmPlan<S8>` of the reference (crates/baracuda-kernels/src/gemm/int_gemm.rs:48-637), Rcr layout,
-    identity epilogue, on tcgen05: D[s8] = sat(rint(alpha * acc + beta * C))."""
+    on tcgen05: D[s8] = sat(rint(act(alpha * acc + beta * C + bias))), every EpilogueKind, f32 or i32 bias."""
 
     _in_dtypes = (torch.int8,)
     _out_dtype = torch.int8
     _needs_scales = False
+    _bias_dtypes = (torch.float32, torch.int32)
     _base = "baracuda_kernels_gemm_s8_rcr_sm100a"
     _element = ElementKind.S8
     _guarantee = _INT_GUARANTEE
@@ -550,6 +581,11 @@ class IntGemmPlan(_QGemmPlanBase):
 
     def _call(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
         d = self.desc
+        if d.epilogue is not EpilogueKind.Identity:
+            return getattr(lib, self._run_symbol.replace("_run", "_epilogue_run"))(
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1),
+                _ptr(args.d), ldd, _ptr(args.bias), self._bias_kind(args), _EPILOGUE_CODE[d.epilogue], args.alpha,
+                args.beta, ws_ptr, ws_bytes, stream)
         return getattr(lib, self._run_symbol)(d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c),
                                               args.ldc or max(d.n, 1), _ptr(args.d), ldd, args.alpha, args.beta,
                                               ws_ptr, ws_bytes, stream)
@@ -557,10 +593,11 @@ class IntGemmPlan(_QGemmPlanBase):
 
 class Fp8GemmPlan(IntGemmPlan):
     """`Fp8GemmPlan<Fp8E4M3>` of the reference (crates/baracuda-kernels/src/gemm/fp8_gemm.rs:36-741), Rcr layout,
-    identity epilogue: D[e4m3] = sat(alpha * acc + beta * dequant(C))."""
+    D[e4m3] = sat(act(alpha * acc + beta * dequant(C) + bias)), every EpilogueKind, f32 bias."""
 
     _in_dtypes = (torch.uint8, torch.float8_e4m3fn)
     _out_dtype = torch.uint8
+    _bias_dtypes = (torch.float32,)
     _base = "baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a"
     _element = ElementKind.Fp8E4M3
     _guarantee = _FP8_GUARANTEE

@@ -208,6 +208,78 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run(
 BARACUDA_Q_DECLARE_GEMM_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a)
 
 /* ---------------------------------------------------------------------------
+ * Fused bias / activation epilogues: the reference's EpilogueKind chain
+ * (crates/baracuda-kernel-vocab/src/layout.rs:69-96) on the 8-bit-out contracts above, computed in f32
+ * registers before the one saturating store (crates/baracuda-kernels-sys/kernels/include/
+ * baracuda_epilogue_int8.cuh:37-95; the bias pointer sits before alpha as in
+ * baracuda_kernels_gemm_s8_rrr_sm80_bias_relu_f32_run, crates/baracuda-kernels-sys/src/lib.rs):
+ *     z = alpha*acc + beta*C + bias[j]      bias: float[N] ("f32") or int32[N] ("i32", converted to float)
+ *     z = relu(z) | gelu(z) = z/2*(1+erf(z/sqrt 2)) | silu(z) = z/(1+exp(-z))
+ *     D = sat_s8(rint_even(z))   or   D = sat_e4m3(z)
+ * Named variants replace the reference's symbol of the same suffix; the *_epilogue_run forms take the chain as
+ * arguments: epilogue 0 identity (bias ignored), 1 bias, 2 bias+relu, 3 bias+gelu, 4 bias+silu;
+ * bias_kind 1 float[N], 2 int32[N] (s8 only).  Status 2 when epilogue > 0 and bias is null or bias_kind is not
+ * one of those.  workspace_size / can_implement are those of the identity symbol of the same family.
+ * ------------------------------------------------------------------------- */
+#define BARACUDA_Q_EPILOGUE_IDENTITY 0
+#define BARACUDA_Q_EPILOGUE_BIAS 1
+#define BARACUDA_Q_EPILOGUE_BIAS_RELU 2
+#define BARACUDA_Q_EPILOGUE_BIAS_GELU 3
+#define BARACUDA_Q_EPILOGUE_BIAS_SILU 4
+#define BARACUDA_Q_BIAS_F32 1
+#define BARACUDA_Q_BIAS_I32 2
+#define BARACUDA_Q_DECLARE_EPILOGUE_RUN(NAME)                                                                        \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,            \
+                 const void* c, int64_t ldc, void* d, int64_t ldd, const void* bias, int32_t bias_kind,              \
+                 int32_t epilogue, float alpha, float beta, void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_EPILOGUE_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_epilogue_run)
+BARACUDA_Q_DECLARE_EPILOGUE_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_epilogue_run)
+BARACUDA_Q_DECLARE_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_epilogue_run)
+BARACUDA_Q_DECLARE_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_epilogue_run)
+#define BARACUDA_Q_DECLARE_BIAS_RUN(NAME)                                                                            \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,            \
+                 const void* c, int64_t ldc, void* d, int64_t ldd, const void* bias, float alpha, float beta,        \
+                 void* workspace, size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_relu_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_gelu_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_silu_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_relu_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_gelu_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rcr_sm100a_bias_silu_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_relu_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_gelu_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_silu_f32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_relu_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_gelu_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_s8_rrr_sm100a_bias_silu_i32_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_relu_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_gelu_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_silu_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_relu_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_gelu_run)
+BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_silu_run)
+
+/* The bf16-out SKUs with the same chain (no counterpart symbol in the reference; the quantized-linear forward
+ * with a bias, bindings/burn/baracuda-burn/src/ops/quantize.rs, is the caller it serves):
+ *     D = bf16( act( alpha * ((scale_a[i]*scale_b[j]) * acc) + bias[j] ) ),  bias float[N], beta must be 0.
+ * scale_mode as for the fp8 bf16 symbol; the w8a8 symbols ignore it (always per row x per column). */
+#define BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(NAME)                                                                   \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,            \
+                 const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b,         \
+                 int32_t scale_mode, const void* bias, int32_t epilogue, float alpha, float beta, void* workspace,   \
+                 size_t workspace_bytes, void* stream);
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run)
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run)
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run)
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run)
+
+/* ---------------------------------------------------------------------------
  * Decode GEMV with int8 weights, m = 1 (and the skinny extension m <= 8):
  *   D[g,r,j] = bf16( alpha * ((scale_a[g,r] * scale_b[g,j]) * (float)acc) + beta * D[g,r,j] )
  * Argument order is that of baracuda_kernels_gemv_dense_m1_bf16_run

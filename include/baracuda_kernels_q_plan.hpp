@@ -143,6 +143,7 @@ struct QGemmArgs {
     DeviceSpan<const float> scale_b;
     float alpha = 1.0f;
     float beta = 0.0f;
+    DeviceSpan<const float> bias;  // [N], read when the descriptor's epilogue has a bias
 };
 
 class W8A8GemmPlan {
@@ -152,7 +153,7 @@ class W8A8GemmPlan {
                         W8A8GemmPlan* out) {
         if (!detail::backend_ok(pref)) return Error::Unsupported;
         if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
-        if (desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
+        if (raw_accumulators && desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
         out->desc_ = desc;
         out->raw_ = raw_accumulators;
         out->sku_ = KernelSku{OpCategory::Gemm, OP_W8A8_GEMM, ElementKind::S8,
@@ -186,6 +187,10 @@ class W8A8GemmPlan {
             if (x.scale_a.len < static_cast<size_t>(desc_.m) || x.scale_b.len < static_cast<size_t>(desc_.n))
                 return Error::BufferTooSmall;
         }
+        if (requires_bias(desc_.epilogue)) {
+            if (!x.bias.ptr) return Error::InvalidProblem;
+            if (x.bias.len < static_cast<size_t>(desc_.n)) return Error::BufferTooSmall;
+        }
         return Error::Ok;
     }
     Error run(void* stream, Workspace ws, const QGemmArgs& x) const {
@@ -197,6 +202,12 @@ class W8A8GemmPlan {
             auto run = rrr ? baracuda_kernels_gemm_s8_rrr_s32_sm100a_run : baracuda_kernels_gemm_s8_rcr_s32_sm100a_run;
             st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta,
                      ws.ptr, ws.bytes, stream);
+        } else if (desc_.epilogue != EpilogueKind::Identity) {
+            auto run = rrr ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run
+                           : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run;
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+                     x.scale_b.ptr, BARACUDA_Q_SCALE_PER_ROW_COL, x.bias.ptr, static_cast<int32_t>(desc_.epilogue), x.alpha,
+                     x.beta, ws.ptr, ws.bytes, stream);
         } else {
             auto run = rrr ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run;
             st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
@@ -217,7 +228,8 @@ class Fp8ScaledGemmPlan {
                         Fp8ScaledGemmPlan* out) {
         if (!detail::backend_ok(pref)) return Error::Unsupported;
         if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
-        if (desc.layout != LayoutSku::Rcr || desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
+        if (raw_accumulators && (desc.layout != LayoutSku::Rcr || desc.epilogue != EpilogueKind::Identity))
+            return Error::Unsupported;
         out->desc_ = desc;
         out->raw_ = raw_accumulators;
         out->mode_ = mode;
@@ -233,12 +245,15 @@ class Fp8ScaledGemmPlan {
         return baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
     }
     Error can_implement(const QGemmArgs& x) const {
-        const int32_t st = baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement(
-            desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
+        const bool rrr = desc_.layout == LayoutSku::Rrr;
+        auto can = rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_can_implement
+                       : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement;
+        const int32_t st = can(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
         if (st != 0) return status_to_error(st);
         if (desc_.m == 0 || desc_.n == 0) return Error::Ok;  // empty problem: nothing is read or written
         if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
-        if (x.b.len < detail::span_elems(desc_.n, desc_.k, x.ldb)) return Error::BufferTooSmall;
+        if (x.b.len < (rrr ? detail::span_elems(desc_.k, desc_.n, x.ldb) : detail::span_elems(desc_.n, desc_.k, x.ldb)))
+            return Error::BufferTooSmall;
         if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
         if (!raw_) {
             if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
@@ -246,19 +261,33 @@ class Fp8ScaledGemmPlan {
             const size_t nb = mode_ == ScaleMode::PerRowCol ? static_cast<size_t>(desc_.n) : 1;
             if (x.scale_a.len < na || x.scale_b.len < nb) return Error::BufferTooSmall;
         }
+        if (requires_bias(desc_.epilogue)) {
+            if (!x.bias.ptr) return Error::InvalidProblem;
+            if (x.bias.len < static_cast<size_t>(desc_.n)) return Error::BufferTooSmall;
+        }
         return Error::Ok;
     }
     Error run(void* stream, Workspace ws, const QGemmArgs& x) const {
         if (Error e = can_implement(x); e != Error::Ok) return e;
         if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
-        const int32_t st =
-            raw_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr,
-                                                                     x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta,
-                                                                     ws.ptr, ws.bytes, stream)
-                 : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
-                       desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd,
-                       x.scale_a.ptr, x.scale_b.ptr, static_cast<int32_t>(mode_), x.alpha, x.beta, ws.ptr, ws.bytes,
-                       stream);
+        const bool rrr = desc_.layout == LayoutSku::Rrr;
+        int32_t st;
+        if (raw_) {
+            st = baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb,
+                                                                   nullptr, 0, x.d.ptr, x.ldd, x.alpha, x.beta, ws.ptr,
+                                                                   ws.bytes, stream);
+        } else if (desc_.epilogue != EpilogueKind::Identity) {
+            auto run = rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run
+                           : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run;
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+                     x.scale_b.ptr, static_cast<int32_t>(mode_), x.bias.ptr, static_cast<int32_t>(desc_.epilogue), x.alpha,
+                     x.beta, ws.ptr, ws.bytes, stream);
+        } else {
+            auto run = rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run
+                           : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run;
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+                     x.scale_b.ptr, static_cast<int32_t>(mode_), x.alpha, x.beta, ws.ptr, ws.bytes, stream);
+        }
         return status_to_error(st);
     }
 
@@ -269,8 +298,9 @@ class Fp8ScaledGemmPlan {
     bool raw_ = false;
 };
 
-// The reference's own 8-bit-out contract (IntGemmPlan<S8> / Fp8GemmPlan<Fp8E4M3>, identity epilogue, Rcr or Rrr):
-// D = sat(alpha * acc + beta * C) in the input type.  `c` may be empty when beta == 0.
+// The reference's own 8-bit-out contract (IntGemmPlan<S8> / Fp8GemmPlan<Fp8E4M3>, every EpilogueKind, Rcr or Rrr):
+// D = sat(act(alpha * acc + beta * C + bias)) in the input type.  `c` may be empty when beta == 0; `bias` is N
+// elements of `bias_element` (BiasElement of the reference: F32, or I32 for the s8 plan).
 struct Q8OutGemmArgs {
     DeviceSpan<const void> a;
     int64_t lda = 0;
@@ -282,6 +312,8 @@ struct Q8OutGemmArgs {
     int64_t ldd = 0;
     float alpha = 1.0f;
     float beta = 0.0f;
+    DeviceSpan<const void> bias;
+    ElementKind bias_element = ElementKind::F32;
 };
 
 class IntGemmPlan {
@@ -289,7 +321,6 @@ class IntGemmPlan {
     static Error select(const QGemmDescriptor& desc, const PlanPreference& pref, ElementKind element, IntGemmPlan* out) {
         if (!detail::backend_ok(pref)) return Error::Unsupported;
         if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
-        if (desc.epilogue != EpilogueKind::Identity) return Error::Unsupported;
         if (element != ElementKind::S8 && element != ElementKind::Fp8E4M3) return Error::Unsupported;
         const bool fp8 = element == ElementKind::Fp8E4M3;
         out->desc_ = desc;
@@ -311,6 +342,18 @@ class IntGemmPlan {
                 return Error::BufferTooSmall;
             if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
             if (x.beta != 0.0f && x.c.len < detail::span_elems(desc_.m, desc_.n, x.ldc)) return Error::BufferTooSmall;
+        }
+        if (requires_bias(desc_.epilogue)) {
+            const bool i32 = x.bias_element == ElementKind::I32;
+            if (!x.bias.ptr || (!i32 && x.bias_element != ElementKind::F32) || (i32 && fp8_)) return Error::InvalidProblem;
+            if (x.bias.len < static_cast<size_t>(desc_.n)) return Error::BufferTooSmall;
+            auto run = fp8_ ? (rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_epilogue_run
+                                   : baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_epilogue_run)
+                            : (rrr ? baracuda_kernels_gemm_s8_rrr_sm100a_epilogue_run
+                                   : baracuda_kernels_gemm_s8_rcr_sm100a_epilogue_run);
+            return status_to_error(run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr,
+                                       x.ldd, x.bias.ptr, i32 ? BARACUDA_Q_BIAS_I32 : BARACUDA_Q_BIAS_F32,
+                                       static_cast<int32_t>(desc_.epilogue), x.alpha, x.beta, ws.ptr, ws.bytes, stream));
         }
         auto fn = fp8_ ? (rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run : baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run)
                        : (rrr ? baracuda_kernels_gemm_s8_rrr_sm100a_run : baracuda_kernels_gemm_s8_rcr_sm100a_run);

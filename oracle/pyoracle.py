@@ -193,6 +193,40 @@ def int_gemm_s8_out(a, b, layout, m, n, k, alpha, beta=0.0, c=None, bias=None, l
     return out
 
 
+EPILOGUE_IDENTITY, EPILOGUE_BIAS, EPILOGUE_BIAS_RELU, EPILOGUE_BIAS_GELU, EPILOGUE_BIAS_SILU = range(5)
+
+
+def epilogue_chain(z: np.ndarray, bias, kind: int) -> np.ndarray:
+    """z + bias[j], then the activation, as the reference's CPU loops state it
+    (crates/baracuda-kernels/tests/int8_rrr_smoke.rs:31-66,108-131; fp8_bias_smoke.rs:30-64,154):
+    relu = max(x, 0), gelu = 0.5*x*(1 + erf(x/sqrt 2)), silu = x/(1 + exp(-x)).
+    The bias add is one f32 rounding (bit-exact for Bias / BiasRelu); gelu and silu are evaluated in f64 and
+    rounded once to f32 -- the reference accepts +-1 output code (int8) / 2 grid steps (fp8) for those two."""
+    z = np.asarray(z, dtype=np.float32)
+    if kind == EPILOGUE_IDENTITY:
+        return z
+    b = np.asarray(bias)
+    assert b.shape == (z.shape[1],) and b.dtype in (np.float32, np.int32)
+    z = (z + b.astype(np.float32)[None, :]).astype(np.float32)
+    if kind == EPILOGUE_BIAS:
+        return z
+    if kind == EPILOGUE_BIAS_RELU:
+        return np.maximum(z, np.float32(0.0))
+    z64 = z.astype(np.float64)
+    if kind == EPILOGUE_BIAS_GELU:
+        import math
+        erf = np.vectorize(math.erf, otypes=[np.float64])
+        return (0.5 * z64 * (1.0 + erf(z64 / math.sqrt(2.0)))).astype(np.float32)
+    if kind == EPILOGUE_BIAS_SILU:
+        return (z64 / (1.0 + np.exp(-z64))).astype(np.float32)
+    raise ValueError(f"epilogue kind {kind}")
+
+
+def sat_s8(z: np.ndarray) -> np.ndarray:
+    """Round half to even, clamp to [-128, 127] (int8_rrr_smoke.rs:76-78)."""
+    return np.clip(np.rint(np.asarray(z, dtype=np.float32)), -128, 127).astype(np.int8)
+
+
 def quantize_rows_s8(x: np.ndarray, qmin: int = -127, qmax: int = 127):
     x = _c(x, np.float32)
     rows, cols = x.shape

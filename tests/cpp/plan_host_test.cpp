@@ -49,7 +49,26 @@ int main() {
     CHECK(q8.run(nullptr, Workspace::none(), qa) == Error::BufferTooSmall);  // the typed layer refuses empty views
     QGemmDescriptor bias = desc;
     bias.epilogue = EpilogueKind::BiasRelu;
-    CHECK(W8A8GemmPlan::select(bias, pref, false, &p) == Error::Unsupported);
+    CHECK(W8A8GemmPlan::select(bias, pref, true, &p) == Error::Unsupported);  // raw accumulators: identity only
+    CHECK(W8A8GemmPlan::select(bias, pref, false, &p) == Error::Ok);
+    CHECK(p.sku().epilogue && *p.sku().epilogue == EpilogueKind::BiasRelu);
+    {
+        auto fk = [](uintptr_t addr) { return reinterpret_cast<void*>(addr); };
+        QGemmArgs y;
+        y.a = {fk(0x10000), size_t(128) * 1024};
+        y.lda = 1024;
+        y.b = {fk(0x200000), size_t(1024) * 1024};
+        y.ldb = 1024;
+        y.d = {fk(0x400000), size_t(128) * 1024};
+        y.ldd = 1024;
+        y.scale_a = {static_cast<const float*>(fk(0x600000)), 128};
+        y.scale_b = {static_cast<const float*>(fk(0x601000)), 1024};
+        CHECK(p.can_implement(y) == Error::InvalidProblem);  // the chain needs a bias
+        y.bias = {static_cast<const float*>(fk(0x602000)), 1000};
+        CHECK(p.can_implement(y) == Error::BufferTooSmall);
+        y.bias.len = 1024;
+        CHECK(p.can_implement(y) == Error::Ok);
+    }
     PlanPreference cublas;
     cublas.prefer_backend = BackendKind::Cublas;
     CHECK(W8A8GemmPlan::select(desc, cublas, false, &p) == Error::Unsupported);

@@ -20,6 +20,8 @@ def _declared_symbols():
     text = (ROOT / "include" / "baracuda_kernels_q.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     names = set(re.findall(r"\b(baracuda_\w+)\s*\(", text))
+    # whole prototypes declared through a BARACUDA_Q_DECLARE_*_RUN(symbol) macro
+    names.update(re.findall(r"^BARACUDA_Q_DECLARE_\w*RUN\((baracuda_\w+)\)", text, flags=re.M))
     # the _workspace_size / _can_implement pair declared through BARACUDA_Q_DECLARE_GEMM_TAIL(NAME)
     for base in re.findall(r"^BARACUDA_Q_DECLARE_GEMM_TAIL\((baracuda_\w+)\)", text, flags=re.M):
         names.update({base + "_workspace_size", base + "_can_implement"})
@@ -102,7 +104,9 @@ def test_plan_select_and_sku():
     rrr = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, layout=bq.LayoutSku.Rrr))
     assert rrr.sku().layout is bq.LayoutSku.Rrr and rrr._run_symbol.endswith("s8_rrr_bf16_sm100a_run")
     with pytest.raises(bq.Unsupported):
-        bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, epilogue=bq.EpilogueKind.BiasRelu))
+        bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, epilogue=bq.EpilogueKind.BiasRelu), raw_accumulators=True)
+    fused = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1, epilogue=bq.EpilogueKind.BiasRelu))
+    assert fused.sku().epilogue is bq.EpilogueKind.BiasRelu and fused.sku() != bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(1, 1, 1)).sku()
     with pytest.raises(bq.Unsupported):
         bq.W8A8GemmPlan.select(None, desc, bq.PlanPreference(prefer_backend=bq.BackendKind.Cublas))
     with pytest.raises(bq.InvalidProblem):
