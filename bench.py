@@ -147,6 +147,12 @@ def graph_launch_ms(launchers, replays: int = 20, warmup: int = 3) -> float:
     return s.elapsed_time(e) / (replays * len(launchers))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of gemm_q8_pair_kernel at 8192 x 8192 x 4096 (70.9 + 97.5 MB),
+# divided by that launch's operand + output bytes (A 33.6 + B 33.6 + D 134.2 MB): each operand byte comes from
+# DRAM once, and part of the output is still in L2 when the kernel ends.
+NCU_TRAFFIC_PER_COMPULSORY_BYTE = 168_449_792 / 201_326_592
+
+
 # --------------------------------------------------------------------------- reference arm
 def run_reference(args, rank: int, world: int, out) -> None:
     """The CPU restatement of the reference's oracle, all host threads, on a bounded row sample of the
@@ -432,7 +438,10 @@ def main() -> None:
                        "parallelism": f"column-parallel, N split over {world} GPU(s), output left sharded",
                        "l2": "256 MiB buffer written between timed iterations", "scales": "per-token x per-channel f32"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None,
+                         "traffic": NCU_TRAFFIC_PER_COMPULSORY_BYTE * (C4_M * C4_K + n_local * C4_K + 2 * C4_M * n_local),
+                         "traffic_is": "bytes per launch: dram read+write of an ncu capture of the same kernel at "
+                                       "8192x8192x4096 (168.4 MB for 201.3 MB of operands + output), scaled by the "
+                                       "operand + output bytes of this launch",
                          "peak_is": f"2 x bf16 burst of {peaks['source']} peaks (no fp8 entry is measured)",
                          "frac_of_nominal_4500": achieved / 4500.0},
             "cpu_baseline": cpu_base,
