@@ -68,7 +68,8 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     constexpr int PAIR_SB_BYTES = C::SB_BYTES;
     constexpr int PAIR_TMEM_COLS = C::TMEM_COLS;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // round up inside the shared window (an offset added to the shared array keeps shared-memory addressing)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* tiles = smem;
     uint4* stage_all = reinterpret_cast<uint4*>(smem + PAIR_TILE_BYTES);
     float* sb_s = reinterpret_cast<float*>(smem + PAIR_TILE_BYTES + C::STG_BYTES);

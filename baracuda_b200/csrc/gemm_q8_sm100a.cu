@@ -68,7 +68,8 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                const GemmParams p) {
     using L = Smem<BLOCK_N, STAGES>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // round up inside the shared window (an offset added to the shared array keeps shared-memory addressing)
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* tiles = smem;
     uint4* stage_all = reinterpret_cast<uint4*>(smem + L::TILE_BYTES);
     float* sb_s = reinterpret_cast<float*>(smem + L::TILE_BYTES + L::STG_BYTES);

@@ -203,3 +203,53 @@ def test_dependent_launch_mode_gives_the_same_results(oracle):
     assert bq.device_status() == 0
     for d in outs:
         assert np.array_equal(bf16_bits(d), want)
+
+
+@pytest.mark.parametrize("variant", [0, 8])  # tensor-copy streaming kernel (default), direct-load split-K kernel
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (2, 1040, 2064), (3, 272, 1000), (5, 14336, 512), (8, 2048, 4100),
+                                   (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096)])
+def test_both_row_major_weight_kernels_on_the_same_shapes(oracle, shape, variant):
+    """Weights row-major [K, N] (the reference GEMV's layout, gemv_dense.cu:128-171): int32 sums are exact whichever
+    kernel runs; ragged K (not a multiple of the 32-row copy), N that is not a multiple of the 256-column block."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m * 1000 + n + k)
+    want = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    bq.set_tuning(1, variant)
+    try:
+        got = _run(m, n, k, bq.LayoutSku.Rrr, aq, wq, sa, sb, raw=True).cpu().numpy()
+        got_bf = bf16_bits(_run(m, n, k, bq.LayoutSku.Rrr, aq, wq, sa, sb, raw=False))
+    finally:
+        bq.set_tuning(1, 0)
+    assert bq.device_status() == 0
+    assert np.array_equal(got, want)
+    assert np.array_equal(got_bf, oracle.dequant_s32_bf16(want, sa, sb))
+
+
+def test_row_major_weights_strided_batch_and_dependent_launches(oracle):
+    """Distinct weights per batch entry (stride_b = K * ldb) through the streaming kernel, launched as a chain with
+    programmatic stream serialization on one shared workspace."""
+    m, n, k, batch = 2, 1024, 1024, 3
+    cases = [w8a8_case(oracle, m, n, k, seed=700 + g) for g in range(batch)]
+    a_buf = np.concatenate([c[0].ravel() for c in cases])
+    b_buf = np.concatenate([np.ascontiguousarray(c[1].T).ravel() for c in cases])
+    sa_buf = np.concatenate([c[2] for c in cases])
+    sb_buf = np.concatenate([c[3] for c in cases])
+    plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, batch=batch, layout=bq.LayoutSku.Rrr))
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    a_d, b_d, sa_d, sb_d = dev(a_buf), dev(b_buf), dev(sa_buf), dev(sb_buf)
+    outs = [torch.full((batch, m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    for pdl in (0, 1):
+        bq.set_tuning(3, pdl)
+        try:
+            for d in outs:
+                d.fill_(float("nan"))
+                plan.run(None, ws, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d, stride_a=m * k,
+                                                 stride_b=k * n, stride_d=m * n, stride_scale_a=m, stride_scale_b=n))
+            torch.cuda.synchronize()
+        finally:
+            bq.set_tuning(3, 0)
+        assert bq.device_status() == 0
+        for d in outs:
+            for g, (aq, wq, sa, sb) in enumerate(cases):
+                want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+                assert np.array_equal(bf16_bits(d[g]), want), (pdl, g)
