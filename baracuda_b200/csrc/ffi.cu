@@ -574,6 +574,10 @@ int32_t baracuda_kernels_q_device_status(void) {
     return gemm != 0 ? gemm : gemv;
 }
 
+int32_t baracuda_kernels_q_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+    return bq::launch_bounded_wait_selftest(static_cast<long long>(limit_cycles), static_cast<cudaStream_t>(stream));
+}
+
 int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
     switch (key) {
         case 0:

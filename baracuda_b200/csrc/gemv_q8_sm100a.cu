@@ -1278,6 +1278,26 @@ int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream) {
     return g.raw_out ? dispatch<true>(g, stream) : dispatch<false>(g, stream);
 }
 
+// ---- self-test of the bounded barrier wait every kernel of the library relies on ----
+// One thread waits, with the given cycle budget, on an mbarrier that nothing will ever complete.  The wait must
+// give up, record status 299 and let the kernel end; the context stays usable.
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0u;
+        mbar_init(&bar, 1);
+        fence_barrier_init();
+        if (!mbar_wait_bounded(&bar, 0u, &abort_flag, limit_cycles)) atomicCAS(&g_gemv_device_status, 0, 299);
+    }
+}
+
+int32_t launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t stream) {
+    if (limit_cycles < 1 || limit_cycles > (1LL << 28)) return BQ_STATUS_INVALID_PROBLEM;  // at most ~0.15 s
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(limit_cycles);
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
+
 int32_t read_and_clear_gemv_device_status() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_gemv_device_status, sizeof(int)) != cudaSuccess) return -1;

@@ -98,6 +98,8 @@ struct GemvDesc {
 
 int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream);
 int32_t read_and_clear_gemv_device_status();
+// Launches one thread that waits on a barrier nothing completes; the wait gives up after limit_cycles and sets status 299.
+int32_t launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t stream);
 size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
 
 }  // namespace bq

@@ -444,8 +444,12 @@ int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void
  * only when the kernel launched just before never writes the weights; key 4 picks the GEMM epilogue's store
  * path (0 = automatic, 1 = per-thread direct stores, 2 = rows staged through shared memory);
  * process-wide, meant for benchmarks and tests.
+ * selftest_bounded_wait: launches one thread that waits, for at most limit_cycles SM clock cycles
+ * (1 .. 2^28), on a barrier that nothing completes -- the time-out path of every kernel here.  After the
+ * stream is synchronised device_status() returns 299 once and the context is as usable as before.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_q_device_status(void);
+int32_t baracuda_kernels_q_selftest_bounded_wait(int64_t limit_cycles, void* stream);
 int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value);
 
 #ifdef __cplusplus

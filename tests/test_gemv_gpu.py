@@ -253,3 +253,54 @@ def test_row_major_weights_strided_batch_and_dependent_launches(oracle):
             for g, (aq, wq, sa, sb) in enumerate(cases):
                 want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
                 assert np.array_equal(bf16_bits(d[g]), want), (pdl, g)
+
+
+def test_bounded_wait_gives_up_and_the_context_survives(oracle):
+    """Failure detection without a fault: a barrier wait that nothing completes runs out of its (short) cycle budget,
+    the kernel records status 299 and ends, and the next launches on the same context work and report no status."""
+    from baracuda_b200 import _lib
+    lib = _lib.load()
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.baracuda_kernels_q_selftest_bounded_wait(0, s) == 2          # budget out of range
+    assert lib.baracuda_kernels_q_selftest_bounded_wait(1 << 40, s) == 2
+    assert lib.baracuda_kernels_q_selftest_bounded_wait(2_000_000, s) == 0  # about a millisecond
+    torch.cuda.synchronize()
+    assert bq.device_status() == 299
+    assert bq.device_status() == 0  # read-and-clear
+    m, n, k = 1, 1024, 1024
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=5)
+    got = bf16_bits(_run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=False))
+    assert np.array_equal(got, oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb))
+    assert bq.device_status() == 0
+
+
+@pytest.mark.parametrize("layout", ["rcr", "rrr"])
+def test_graph_capture_and_replay(oracle, layout):
+    """The reason the reference's GEMV exists (gemv_dense.cu:6-12; tests/capture_replay_gather_gemv.rs): the call records
+    into a CUDA graph -- no allocation, no host sync -- and replays read the buffers' current contents."""
+    lay = LAYOUTS[layout]
+    m, n, k = 1, 4096, 4096
+    cases = [w8a8_case(oracle, m, n, k, seed=900 + i) for i in range(2)]
+    wq, sb = cases[0][1], cases[0][3]
+    plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=lay))
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    a_d, sa_d = dev(cases[0][0]), dev(cases[0][2])
+    b_d, sb_d = dev(_weights_for(lay, wq)), dev(sb)
+    d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    args = bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d)
+    plan.run(None, ws, args)  # first call outside the capture: one-time function attributes
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            plan.run(side, ws, args)
+    for aq, _, sa, _ in cases[::-1]:
+        a_d.copy_(dev(aq))
+        sa_d.copy_(dev(sa))
+        d.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+        assert np.array_equal(bf16_bits(d), want)
+    assert bq.device_status() == 0
