@@ -74,6 +74,10 @@ bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64
 // [k_rows x n_cols] bytes, N contiguous, row pitch ld; box = box_k rows x 128 bytes, 128-byte swizzle
 bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k);
 int sm_count_of_current_device();
+// D = bf16((sa*sb) * acc * alpha (+ bias)) for an [m, n] matrix of int32 (BQ_KIND_S8) or f32 (BQ_KIND_E4M3) accumulators.
+int32_t launch_dequant_rows(int32_t kind, int32_t m, int32_t n, const void* acc, int64_t ld_acc, const float* scale_a,
+                            const float* scale_b, int32_t scale_mode, float alpha, const float* bias, void* d, int64_t ldd,
+                            cudaStream_t stream);
 
 struct GemvDesc {
     int32_t raw_out;  // 1: int32 accumulators, 0: bf16

@@ -30,7 +30,7 @@ struct NcclUniqueId {
     char internal[128];
 };
 using NcclComm = void*;
-constexpr int kNcclInt8 = 0, kNcclFloat32 = 7, kNcclBfloat16 = 9;
+constexpr int kNcclInt8 = 0, kNcclInt32 = 2, kNcclFloat32 = 7, kNcclBfloat16 = 9;
 constexpr int kNcclSum = 0;
 
 struct NcclApi {
@@ -116,6 +116,46 @@ int32_t nshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_
     return BARACUDA_Q_STATUS_OK;
 }
 
+// K-sharded ("row-parallel") forward: Y_partial = X_local x W_local^T on this rank's K slice, all-reduce of the raw
+// accumulators, then one dequant pass (crates/baracuda-megatron/src/lib.rs:1002-1200: local GEMM, all_reduce(Sum),
+// bias after the reduction).  Adding int32 sums is exact, so the W8A8 result has the bits of the unsharded GEMM.
+int32_t kshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_t reduce, int32_t m, int32_t n,
+                   int32_t k_local, const void* a_local, int64_t lda, const void* b_local, int64_t ldb, void* d,
+                   int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode, const void* bias, float alpha,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+    if (world < 1 || rank < 0 || rank >= world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (reduce != BARACUDA_Q_REDUCE_NONE && reduce != BARACUDA_Q_REDUCE_NCCL) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (m < 0 || n < 0 || k_local < 0) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (ldd < (n > 0 ? n : 1)) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (m == 0 || n == 0) return BARACUDA_Q_STATUS_OK;
+    if (!d || !scale_a || !scale_b) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
+        return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (reduce == BARACUDA_Q_REDUCE_NCCL && world > 1 && !comm) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    const size_t count = static_cast<size_t>(m) * static_cast<size_t>(n);
+    if (!workspace || workspace_bytes < count * 4) return BARACUDA_Q_STATUS_WORKSPACE;
+    if (reinterpret_cast<uintptr_t>(workspace) & 15u) return BARACUDA_Q_STATUS_MISALIGNED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    const int32_t st = kind == bq::BQ_KIND_S8
+                           ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(m, n, k_local, a_local, lda, b_local, ldb, nullptr, 0,
+                                                                         workspace, n, 1.0f, 0.0f, nullptr, 0, stream)
+                           : baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(m, n, k_local, a_local, lda, b_local, ldb,
+                                                                               nullptr, 0, workspace, n, 1.0f, 0.0f, nullptr,
+                                                                               0, stream);
+    if (st != BARACUDA_Q_STATUS_OK) return st;
+    if (reduce == BARACUDA_Q_REDUCE_NCCL && world > 1) {
+        if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+        if (nccl().AllReduce(workspace, workspace, count, kind == bq::BQ_KIND_S8 ? kNcclInt32 : kNcclFloat32, kNcclSum, comm,
+                             s) != 0) {
+            return BARACUDA_Q_STATUS_COMM_FAILURE;
+        }
+    }
+    return bq::launch_dequant_rows(kind, m, n, workspace, n, static_cast<const float*>(scale_a),
+                                   static_cast<const float*>(scale_b), scale_mode, alpha, static_cast<const float*>(bias), d,
+                                   ldd, s);
+}
+
 }  // namespace
 
 extern "C" {
@@ -181,6 +221,26 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
     (void)workspace_bytes;
     return nshard_run(bq::BQ_KIND_S8, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb, d_local, ldd,
                       scale_a, scale_b_local, BARACUDA_Q_SCALE_PER_ROW_COL, alpha, d_full, peer_d, ldd_full, stream);
+}
+
+size_t baracuda_kernels_gemm_q8_kshard_workspace_size(int32_t m, int32_t n) {
+    return (m > 0 && n > 0) ? static_cast<size_t>(m) * static_cast<size_t>(n) * 4 : 0;
+}
+
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t reduce, int32_t m, int32_t n, int32_t k_local, const void* a_local,
+    int64_t lda, const void* b_local, int64_t ldb, void* d, int64_t ldd, const void* scale_a, const void* scale_b,
+    const void* bias, float alpha, void* workspace, size_t workspace_bytes, void* stream) {
+    return kshard_run(bq::BQ_KIND_S8, rank, world, comm, reduce, m, n, k_local, a_local, lda, b_local, ldb, d, ldd, scale_a,
+                      scale_b, BARACUDA_Q_SCALE_PER_ROW_COL, bias, alpha, workspace, workspace_bytes, stream);
+}
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t reduce, int32_t m, int32_t n, int32_t k_local, const void* a_local,
+    int64_t lda, const void* b_local, int64_t ldb, void* d, int64_t ldd, const void* scale_a, const void* scale_b,
+    int32_t scale_mode, const void* bias, float alpha, void* workspace, size_t workspace_bytes, void* stream) {
+    return kshard_run(bq::BQ_KIND_E4M3, rank, world, comm, reduce, m, n, k_local, a_local, lda, b_local, ldb, d, ldd, scale_a,
+                      scale_b, scale_mode, bias, alpha, workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

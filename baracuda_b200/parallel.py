@@ -61,6 +61,13 @@ def shard_rows(t: torch.Tensor, world: int, rank: int) -> torch.Tensor:
     return t[lo:hi].contiguous()
 
 
+def shard_cols(t: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """This rank's contiguous K slice (columns) of a weight ([N,K]) or of the activations ([M,K]); K must divide
+    evenly (RowParallelLinearPlan::new, lib.rs:1080-1110)."""
+    lo, hi = shard_range(t.shape[1], world, rank)
+    return t[:, lo:hi].contiguous()
+
+
 def gathered_to_row_major(y_full: torch.Tensor) -> torch.Tensor:
     """[G, M, N/G] (what the all-gather produces, lib.rs:824-836) -> row-major [M, N]."""
     g, m, n_local = y_full.shape
@@ -151,6 +158,54 @@ class ColumnParallelQGemmPlan:
         else:
             st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(*common, alpha, *tail)
         _check(st, "ColumnParallelQGemmPlan.forward")
+
+
+REDUCE_NONE, REDUCE_NCCL = 0, 1
+
+
+class RowParallelQGemmPlan:
+    """K-sharded FP8 or W8A8 GEMM: every rank multiplies its K slice, the raw accumulators are all-reduced
+    (ncclAllReduce, sum) and dequantised once -- the forward of the reference's RowParallelLinearPlan
+    (crates/baracuda-megatron/src/lib.rs:1002-1200), for 8-bit operands.  `scale_a` is one per-token scale
+    taken over the whole K, the same on every rank."""
+
+    def __init__(self, ctx: TensorParallelContext, m: int, out_features: int, in_features: int, kind: str = "w8a8",
+                 scale_mode: int = SCALE_PER_ROW_COL, reduce: int = REDUCE_NCCL):
+        if kind not in ("fp8", "w8a8"):
+            raise InvalidProblem("kind must be 'fp8' or 'w8a8'")
+        if reduce not in (REDUCE_NONE, REDUCE_NCCL):
+            raise InvalidProblem("unknown reduce mode")
+        if min(m, out_features, in_features) < 0:
+            raise InvalidProblem("negative dimension")
+        lo, hi = shard_range(in_features, ctx.world, ctx.rank)
+        self.ctx, self.m, self.n, self.k = ctx, m, out_features, in_features
+        self.k_local, self.k0 = hi - lo, lo
+        self.kind, self.scale_mode, self.reduce = kind, scale_mode, reduce
+
+    def workspace_size(self) -> int:
+        return int(_lib.load().baracuda_kernels_gemm_q8_kshard_workspace_size(self.m, self.n))
+
+    def forward(self, stream, a_local: torch.Tensor, scale_a: torch.Tensor, w_local: torch.Tensor,
+                scale_b: torch.Tensor, y: torch.Tensor, workspace: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, alpha: float = 1.0) -> None:
+        """Y[M, N] = bf16((scale_a x scale_b) * sum_ranks(A_local x W_local^T) * alpha + bias) on every rank."""
+        if a_local.numel() < self.m * self.k_local or w_local.numel() < self.n * self.k_local:
+            raise InvalidProblem("operand shorter than the descriptor says")
+        if y.numel() < self.m * self.n:
+            raise InvalidProblem("y shorter than [M, N]")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() < self.n):
+            raise InvalidProblem("bias must be float32[N]")
+        ws_bytes = workspace.numel() * workspace.element_size()
+        lib = _lib.load()
+        common = (self.ctx.rank, self.ctx.world, self.ctx.comm, self.reduce, self.m, self.n, self.k_local,
+                  _ptr(a_local), max(self.k_local, 1), _ptr(w_local), max(self.k_local, 1), _ptr(y), max(self.n, 1),
+                  _ptr(scale_a), _ptr(scale_b))
+        tail = (_ptr(bias), alpha, _ptr(workspace), ws_bytes, _stream_ptr(stream))
+        if self.kind == "fp8":
+            st = lib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_run(*common, self.scale_mode, *tail)
+        else:
+            st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(*common, *tail)
+        _check(st, "RowParallelQGemmPlan.forward")
 
 
 def alloc_peer_buffers(shape, dtype=torch.bfloat16, group=None):

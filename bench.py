@@ -420,6 +420,28 @@ def main() -> None:
                 "layout": "row-major [M, N] on every rank", "nvlink_bytes_out_per_rank": C4_M * n_local * 2 * (world - 1)}
         except Exception as exc:  # symmetric memory not available on this box
             others["with_fused_peer_stores"] = {"unavailable": repr(exc)[:200]}
+        # (3) the partner layer of the MLP block: K-sharded (row-parallel) W8A8 down projection of the same model
+        #     (28672 -> 8192 at M = 8192): raw int32 partial sums, ncclAllReduce, one dequant pass (bit-equal to unsharded)
+        rp_m, rp_n, rp_k = C4_M, C4_K, C4_N
+        del full
+        rp_plan = par.RowParallelQGemmPlan(ctx, rp_m, rp_n, rp_k, kind="w8a8")
+        gen2 = torch.Generator(device="cuda")
+        gen2.manual_seed(4321 + rank)
+        xa = torch.randint(-127, 128, (rp_m, rp_plan.k_local), dtype=torch.int8, device="cuda", generator=gen2)
+        xw = torch.randint(-127, 128, (rp_n, rp_plan.k_local), dtype=torch.int8, device="cuda", generator=gen2)
+        xsa = torch.rand(rp_m, device="cuda") * 1e-2
+        xsb = torch.rand(rp_n, device="cuda") * 1e-2
+        xy = torch.empty((rp_m, rp_n), dtype=torch.bfloat16, device="cuda")
+        xws = torch.empty(rp_plan.workspace_size(), dtype=torch.uint8, device="cuda")
+        rp_step = lambda: rp_plan.forward(None, xa, xsa, xw, xsb, xy, xws)
+        barrier()
+        r_ms = event_time_ms(rp_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+        barrier()
+        r_total = max_over_ranks(sum(r_ms))
+        others["row_parallel_w8a8_allreduce"] = {
+            "shape": [rp_m, rp_n, rp_k], "TOPS": 2.0 * rp_m * rp_n * rp_k * len(r_ms) / (r_total * 1e-3) / 1e12,
+            "ms_per_step": r_total / len(r_ms), "allreduced_bytes": rp_m * rp_n * 4,
+            "note": "GEMM on K/G, ncclAllReduce of int32 sums, dequant pass; every rank holds the full bf16 result"}
         ctx.destroy()
 
     cpu_base = None

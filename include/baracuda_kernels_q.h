@@ -420,6 +420,36 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
     void* d_full, void* const* peer_d, int64_t ldd_full,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * K-sharded ("row-parallel") forward, the partner of the N-sharded one in an MLP block
+ * (RowParallelLinearPlan::forward, crates/baracuda-megatron/src/lib.rs:1002-1200): rank r holds
+ * X_local [M, K/world] and W_local [N, K/world]; Y = sum over ranks of X_local x W_local^T.
+ * Each rank's tcgen05 GEMM leaves raw accumulators (int32 / f32) in `workspace` ([M, N], 4 bytes
+ * each, 16-byte aligned; *_kshard_workspace_size), `reduce` = BARACUDA_Q_REDUCE_NCCL adds them with
+ * ncclAllReduce(sum) on the caller's stream, and one dequant pass writes
+ *     D = bf16( (scale_a[i] * scale_b[j]) * acc * alpha + bias[j] )      (bias float[N] or NULL, added once)
+ * on every rank.  scale_a must be the same on all ranks (quantise the activations with a per-token scale
+ * taken over the whole K); int32 sums add exactly, so the W8A8 result equals the unsharded GEMM bit for bit.
+ * BARACUDA_Q_REDUCE_NONE skips the collective (world 1, or a caller that reduces the workspace itself).
+ * ------------------------------------------------------------------------- */
+#define BARACUDA_Q_REDUCE_NONE 0
+#define BARACUDA_Q_REDUCE_NCCL 1
+size_t baracuda_kernels_gemm_q8_kshard_workspace_size(int32_t m, int32_t n);
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t reduce,
+    int32_t m, int32_t n, int32_t k_local,
+    const void* a_local, int64_t lda, const void* b_local, int64_t ldb,
+    void* d, int64_t ldd, const void* scale_a, const void* scale_b,
+    const void* bias, float alpha,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t reduce,
+    int32_t m, int32_t n, int32_t k_local,
+    const void* a_local, int64_t lda, const void* b_local, int64_t ldb,
+    void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,
+    const void* bias, float alpha,
+    void* workspace, size_t workspace_bytes, void* stream);
+
 /* Communicator helpers over the run-time-loaded NCCL
  * (Communicator::{new_with_id, all_gather}, crates/baracuda-nccl/src/lib.rs:243-261, 468-489).
  * unique_id writes the 128-byte ncclUniqueId; rank 0 creates it and the caller

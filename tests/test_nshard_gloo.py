@@ -34,6 +34,14 @@ def test_shard_range_rules():
         par.ColumnParallelQGemmPlan(par.TensorParallelContext(0, 2), 4, 8, 16, kind="bf16")
     plan = par.ColumnParallelQGemmPlan(par.TensorParallelContext(1, 2), 4, 8, 16, kind="w8a8", gather=par.GATHER_NCCL)
     assert (plan.n_local, plan.col0) == (4, 4)
+    # K-sharded (row-parallel) plan: in_features must divide, each rank owns a column slice
+    assert torch.equal(par.shard_cols(w, 2, 1), w[:, 2:4])
+    with pytest.raises(InvalidProblem):
+        par.RowParallelQGemmPlan(par.TensorParallelContext(0, 2), 4, 8, 15)
+    with pytest.raises(InvalidProblem):
+        par.RowParallelQGemmPlan(par.TensorParallelContext(0, 2), 4, 8, 16, reduce=5)
+    rp = par.RowParallelQGemmPlan(par.TensorParallelContext(1, 2), 4, 8, 16)
+    assert (rp.k_local, rp.k0) == (8, 8) and rp.workspace_size() == 4 * 8 * 4
 
 
 def _free_port() -> int:
@@ -68,6 +76,16 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         got = par.gathered_to_row_major(y_full).numpy().astype(np.uint16)
         want = orc.dequant_s32_bf16(orc.gemm_s8_s32(aq, wq, orc.RCR, m, n, k), sa, sb)
         assert np.array_equal(got, want), "sharded + gathered result differs from the unsharded one"
+
+        # K-sharded: every rank multiplies its K slice, the int32 partial sums are all-reduced (exact), one dequant
+        a_k = par.shard_cols(torch.from_numpy(aq), world, rank).numpy()
+        w_k = par.shard_cols(torch.from_numpy(wq), world, rank).numpy()
+        part = torch.from_numpy(orc.gemm_s8_s32(a_k, w_k, orc.RCR, m, n, k // world))
+        dist.all_reduce(part, op=dist.ReduceOp.SUM)
+        assert np.array_equal(orc.dequant_s32_bf16(part.numpy(), sa, sb), want), "K-sharded result differs"
+        st = lib_status = _lib.load().baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(
+            rank, world, None, 1, m, n, k // world, None, k, None, k, None, n, None, None, None, 1.0, None, 0, None)
+        assert st == 2  # no output, no scales
 
         # the unique id made on rank 0 reaches every rank unchanged
         lib = _lib.load()

@@ -1,4 +1,4 @@
-"""Two-GPU parity of the column-parallel GEMM: each rank computes its N-slice with the tcgen05 kernel;
+"""Two-GPU parity of the column-parallel and row-parallel GEMMs: each rank computes its N-slice with the tcgen05 kernel;
 the sharded output, the NCCL-gathered output (rank-major) and the fused peer-store output (row-major)
 must all equal the unsharded oracle result.  Skipped with fewer than two GPUs."""
 import os
@@ -81,6 +81,35 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             torch.cuda.synchronize()
             dist.barrier()
             check(bits(full_rm), want, "fused peer store")
+            assert bq.device_status() == 0
+        # K-sharded (row-parallel) forward: raw accumulators all-reduced, one dequant pass, bias added once
+        for kind, (m, n, k) in (("w8a8", (300, 1040, 1024)), ("fp8", (512, 1024, 2048))):
+            rng = np.random.default_rng(11)
+            a = rng.standard_normal((m, k)).astype(np.float32)
+            w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+            bias = rng.standard_normal(n).astype(np.float32)
+            if kind == "w8a8":
+                aq, sa = orc.quantize_rows_s8(a)      # one per-token scale over the whole K, shared by the ranks
+                wq, sb = orc.quantize_rows_s8(w)
+                y = orc.dequant_s32_f32(orc.gemm_s8_s32(aq, wq, orc.RCR, m, n, k), sa, sb)
+            else:
+                aq, sa = orc.quantize_rows_e4m3(a)
+                wq, sb = orc.quantize_rows_e4m3(w)
+                acc = orc.gemm_e4m3_f32(aq, wq, orc.RCR, m, n, k)
+                y = ((sa[:, None] * sb[None, :]).astype(np.float32) * acc).astype(np.float32)
+            want = orc.f32_to_bf16_bits((y + bias[None, :]).astype(np.float32))
+            want_f = orc.bf16_bits_to_f32(want)
+            plan = par.RowParallelQGemmPlan(ctx, m, n, k, kind=kind)
+            ws = torch.empty(plan.workspace_size(), dtype=torch.uint8, device="cuda")
+            y_d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+            plan.forward(None, par.shard_cols(torch.from_numpy(aq), world, rank).cuda(), dev(sa),
+                         par.shard_cols(torch.from_numpy(wq), world, rank).cuda(), dev(sb), y_d, ws, bias=dev(bias))
+            torch.cuda.synchronize()
+            if kind == "w8a8":
+                assert np.array_equal(bits(y_d), want), f"row-parallel w8a8 rank {rank}"
+            else:
+                g_f = orc.bf16_bits_to_f32(bits(y_d))
+                assert orc.compare_tolerant(want_f, g_f, 1e-2, 1e-4 * float(np.abs(want_f).max())) == -1, "row-parallel fp8"
             assert bq.device_status() == 0
         ctx.destroy()
         with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
