@@ -382,7 +382,9 @@ __device__ __forceinline__ void mma_s8_16x8x32_top(int& c0, int& c1, uint32_t a0
 // MMA_KCHUNK: bytes of K per item and row; MMA_WARPS: streaming warps.  The row pitch in the ring is
 // KCHUNK + 64 so that 16-byte reads of 8 rows hit 8 distinct bank groups.
 // MMA_RING: items in flight per warp.
-template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING>
+// XREG: the number of K chunks divides the number of warps, so a warp meets the same K chunk in all its items and
+// keeps its activation fragments in registers (no activation staging, half the shared-memory loads).
+template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING, bool XREG = false>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 1)
 gemv_q8_rcr_mma_kernel(const GemvParams p) {
     constexpr int MMA_PITCH = MMA_KCHUNK + 64;
@@ -396,7 +398,7 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     uint8_t* ring = mma_smem + warp * MMA_RING * MMA_ITEM_BYTES;
     uint8_t* xs = mma_smem + MMA_WARPS * MMA_RING * MMA_ITEM_BYTES;
     // only the m real activation rows and this launch's groups per CTA take shared memory
-    int* acc_s = reinterpret_cast<int*>(xs + p.m * xpitch);
+    int* acc_s = reinterpret_cast<int*>(xs + (XREG ? 0 : p.m * xpitch));
     float* sb_s = reinterpret_cast<float*>(acc_s + p.mma_groups * 64);  // this CTA's column scales
     uint64_t* bars = reinterpret_cast<uint64_t*>(sb_s + p.mma_groups * MMA_COLS);
     uint64_t* full_bar = bars + warp * MMA_RING;
@@ -453,13 +455,24 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
 
-    // activations into shared memory (rows beyond m are zero), accumulators cleared
+    // activations into shared memory (rows beyond m are zero) or, XREG, this warp's K chunk of activation row gq
+    // straight into registers in fragment order; accumulators cleared
+    uint4 xreg[XREG ? MMA_KCHUNK / 64 : 1];
     {
-        const int k16 = p.k >> 4;
-        for (int i = threadIdx.x; i < p.m * k16; i += MMA_WARPS * 32) {
-            const int r = i / k16, c = i - r * k16;
-            *reinterpret_cast<uint4*>(xs + r * xpitch + c * 16) =
-                __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + c);
+        if constexpr (XREG) {
+            const int k0 = (warp % chunks) * MMA_KCHUNK;
+#pragma unroll
+            for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
+                xreg[i] = gq < p.m ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(gq) * p.lda + k0 + i * 64 + tq * 16))
+                                   : make_uint4(0, 0, 0, 0);
+            }
+        } else {
+            const int k16 = p.k >> 4;
+            for (int i = threadIdx.x; i < p.m * k16; i += MMA_WARPS * 32) {
+                const int r = i / k16, c = i - r * k16;
+                *reinterpret_cast<uint4*>(xs + r * xpitch + c * 16) =
+                    __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(r) * p.lda) + c);
+            }
         }
         for (int i = threadIdx.x; i < ngroups * 64; i += MMA_WARPS * 32) acc_s[i] = 0;
         if constexpr (!RAW) {  // scales fetched now, off the tail of the kernel
@@ -490,6 +503,21 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         const bool has_row = gq < p.m;  // activation rows beyond m are zero operands, never read
         // four independent accumulators: consecutive MMAs never wait on each other's result
         int d[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0}, d3[4] = {0, 0, 0, 0};
+        if constexpr (XREG) {
+            // whole chunks only on this path: pull the item into registers, re-arm the slot, then multiply
+            uint4 w[MMA_KCHUNK / 64];
+#pragma unroll
+            for (int i = 0; i < MMA_KCHUNK / 64; ++i) w[i] = *reinterpret_cast<const uint4*>(wrow + i * 64);
+            __syncwarp();
+            if (mine + MMA_RING < my_items) issue(mine + MMA_RING);
+#pragma unroll
+            for (int i = 0; i < MMA_KCHUNK / 64; i += 2) {
+                mma_s8_16x8x32(d, xreg[i].x, xreg[i].y, w[i].x, w[i].y);
+                mma_s8_16x8x32(d1, xreg[i].z, xreg[i].w, w[i].z, w[i].w);
+                mma_s8_16x8x32(d2, xreg[i + 1].x, xreg[i + 1].y, w[i + 1].x, w[i + 1].y);
+                mma_s8_16x8x32(d3, xreg[i + 1].z, xreg[i + 1].w, w[i + 1].z, w[i + 1].w);
+            }
+        } else {
 #pragma unroll 2
         for (int kb = 0; kb < bytes; kb += 128) {
             const uint4 w = *reinterpret_cast<const uint4*>(wrow + kb);
@@ -503,10 +531,13 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
                 mma_s8_16x8x32(d3, x2.z, x2.w, w2.z, w2.w);
             }
         }
+        }
         d[0] += d1[0] + d2[0] + d3[0];
         d[1] += d1[1] + d2[1] + d3[1];
-        __syncwarp();  // the whole item has been read: its slot can be refilled
-        if (mine + MMA_RING < my_items) issue(mine + MMA_RING);
+        if constexpr (!XREG) {
+            __syncwarp();  // the whole item has been read: its slot can be refilled
+            if (mine + MMA_RING < my_items) issue(mine + MMA_RING);
+        }
         // d[0], d[1]: activation row gq, columns 2*tq and 2*tq+1 of this group (d[2], d[3] belong to the zero rows)
         if (gq < p.m) {
             atomicAdd(&acc_s[gi * 64 + gq * 8 + 2 * tq], d[0]);
@@ -1000,13 +1031,13 @@ size_t mma_smem_bytes(int kchunk, int warps, int ring, int m, int k, int groups)
            static_cast<size_t>(groups) * 64 * 4 + static_cast<size_t>(groups) * MMA_COLS * 4 + warps * ring * 8 + warps * 4 + 16;
 }
 
-template <bool RAW, int KCHUNK, int WARPS, int RING>
+template <bool RAW, int KCHUNK, int WARPS, int RING, bool XREG = false>
 int32_t launch_rcr_mma_cfg(GemvParams p, int batch, int sms, cudaStream_t stream) {
     const int want = (p.n + MMA_COLS - 1) / MMA_COLS;  // no more CTAs than 8-column groups
     const int ctas = want < sms ? want : sms;
     p.mma_groups = (want + ctas - 1) / ctas;
-    const size_t smem = mma_smem_bytes(KCHUNK, WARPS, RING, p.m, p.k, p.mma_groups);
-    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING>;
+    const size_t smem = mma_smem_bytes(KCHUNK, WARPS, RING, XREG ? 0 : p.m, p.k, p.mma_groups);
+    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING, XREG>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -1035,10 +1066,17 @@ int32_t launch_rcr_mma(const GemvParams& p, int batch, int shape_variant, cudaSt
     // 32 = 2 KiB copies on 4 warps, 33 = 512-byte copies on 16 warps, 34 = three items in flight per warp
     if (shape_variant == 32 && p.k <= 4096) return launch_rcr_mma_cfg<RAW, 2048, 4, 2>(p, batch, sms, stream);
     if (shape_variant == 33) return launch_rcr_mma_cfg<RAW, 512, 16, 2>(p, batch, sms, stream);
-    // default: 1 KiB copies on 8 warps, two items in flight per warp (a third measured no faster)
     const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
     const int ctas = want < sms ? want : sms;
     const int groups = (want + ctas - 1) / ctas;
+    // 35: 512-byte copies on 16 warps, three items in flight, activations in registers -- when K is a whole number of
+    // 512-byte chunks that divides 16 (K = 512, 1024, 2048, 4096, 8192)
+    // (the default where it applies: 13.3 us against 16.5 us at m = 2..8, K = 4096, N = 14336; 36 keeps it off)
+    if ((shape_variant == 35 || shape_variant == 0 || shape_variant == 3) && p.k % 512 == 0 && 16 % (p.k / 512) == 0 &&
+        mma_smem_bytes(512, 16, 3, 0, p.k, groups) <= 232448) {
+        return launch_rcr_mma_cfg<RAW, 512, 16, 3, true>(p, batch, sms, stream);
+    }
+    // otherwise: 1 KiB copies on 8 warps, two items in flight per warp (a third measured no faster)
     if (shape_variant == 34 && mma_smem_bytes(1024, 8, 3, p.m, p.k, groups) <= 232448) {
         return launch_rcr_mma_cfg<RAW, 1024, 8, 3>(p, batch, sms, stream);
     }
@@ -1216,7 +1254,9 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     // (variant 3 forces it also for m == 1, variant 2 and 1 keep it off)
     if (g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
         ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3 ||
-         (g.variant >= 31 && g.variant <= 34))) {  // 31..34 force a copy-size / ring configuration
+         (g.variant >= 31 && g.variant <= 36) ||  // 31..36 force a copy-size / ring configuration
+         (g.variant == 0 && g.m == 1 && g.pdl && g.k % 512 == 0 && 16 % (g.k / 512) == 0 &&
+          g.n * static_cast<int64_t>(g.k) >= (1 << 20)))) {  // dependent launch: the 16-warp tensor-core kernel also wins at m = 1
         return launch_rcr_mma<RAW>(p, g.batch, g.variant, stream);
     }
     // K-contiguous weights with few activation rows: the bulk-copy streaming kernel

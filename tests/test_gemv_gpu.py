@@ -74,7 +74,7 @@ def test_byte_load_kernel_equals_streaming_kernel(oracle, layout):
     assert np.array_equal(fast, oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k))
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 32, 33, 34])  # bulk-copy dp4a, register streaming, tensor-core (default / 2 KiB x 4 warps / 512 B x 16 warps / ring 2)
+@pytest.mark.parametrize("variant", [1, 2, 3, 32, 33, 34, 35, 36])  # bulk-copy dp4a, register streaming, tensor-core (default / 2 KiB x 4 warps / 512 B x 16 warps / ring 2)
 @pytest.mark.parametrize("shape", [(1, 300, 512), (2, 149, 4096), (3, 1000, 4112), (4, 2048, 9000 // 16 * 16), (1, 7, 16),
                                    (8, 520, 2048), (5, 1187, 8192), (7, 3000, 1088)])
 def test_both_k_contiguous_kernels_on_the_same_shapes(oracle, shape, variant):
