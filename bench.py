@@ -216,7 +216,7 @@ def side_workloads(peaks: dict) -> dict:
             out[f"gemv_{layout.value}_m{m}"] = {
                 "us": t * 1e6, "GBps": byts / t / 1e9, "algorithmic_bytes": byts,
                 "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"], "peak": f"{peaks['hbm_gbs']} GB/s of {peaks['source']}"}
-            if layout is bq.LayoutSku.Rcr and m <= 4:
+            if True:
                 # the same graph with programmatic dependent launch between consecutive GEMVs: each launch
                 # starts fetching its (static) weights while the previous one drains
                 bq.set_tuning(3, 1)
