@@ -46,9 +46,10 @@ struct GemvParams {
     int kslice_rows, num_kslices;
     int32_t* ws_partials;
     unsigned int* ws_tickets;
-    // row-major-weight streaming kernel: work items are [32 K rows x 256 columns] boxes, numbered column block
-    // major; CTA c owns items [c * total / ctas, (c + 1) * total / ctas)
-    int rs_items_per_block, rs_blocks, rs_slots, rs_jmax, rs_ctas;
+    // row-major-weight streaming kernel: chunks of [32 K rows x 2048 columns], numbered strip major; CTA c owns
+    // chunks [c * total / ctas, (c + 1) * total / ctas).  rs_items_per_block = chunks per strip, rs_blocks = strips,
+    // rs_slots = ring slots per warp, rs_run_max = longest run of any CTA
+    int rs_items_per_block, rs_blocks, rs_slots, rs_run_max, rs_ctas;
     int32_t* rs_partials;  // [batch][slot][m][2048]; slot(c, strip) = c + strip
     int rs_slots_total;
     int mma_groups;  // tensor-core GEMV: 8-column groups per CTA (upper bound), sizes the shared accumulator
@@ -730,7 +731,6 @@ constexpr int RS_WARPS = RS_STRIP / RS_COLS;
 constexpr int RS_THREADS = RS_WARPS * 32;
 constexpr int RS_BOX_BYTES = RS_COLS * RS_ROWS;
 constexpr int RS_MAX_CTAS = 160;             // sizes the scratch without asking the device
-constexpr int RS_MAX_RUN = 64;               // chunks per CTA whose activations fit the staging area
 constexpr long long RS_WAIT_LIMIT = 1LL << 31;
 
 __device__ __forceinline__ int64_t rs_begin(int c, int64_t total, int ctas) {
@@ -755,10 +755,11 @@ gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const Gemv
     const int slots = p.rs_slots;
     const int KC = p.rs_items_per_block;  // chunks per strip
     uint8_t* ring = rs_smem + static_cast<size_t>(warp) * slots * RS_BOX_BYTES;
-    uint32_t* xs = reinterpret_cast<uint32_t*>(rs_smem + static_cast<size_t>(RS_WARPS) * slots * RS_BOX_BYTES);  // [m][run][8]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + p.m * RS_MAX_RUN * 8) + warp * slots;
+    const int run_max = p.rs_run_max;  // longest run of any CTA: sizes the activation staging
+    uint32_t* xs = reinterpret_cast<uint32_t*>(rs_smem + static_cast<size_t>(RS_WARPS) * slots * RS_BOX_BYTES);  // [m][run_max][8]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + p.m * run_max * 8) + warp * slots;
     volatile uint32_t* abort_word =
-        reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint64_t*>(xs + p.m * RS_MAX_RUN * 8) + RS_WARPS * slots) + warp;
+        reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint64_t*>(xs + p.m * run_max * 8) + RS_WARPS * slots) + warp;
 
     const int64_t g = blockIdx.y;
     const int8_t* a = p.a + g * p.stride_a;
@@ -803,7 +804,7 @@ gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const Gemv
             const int kk = kc * RS_ROWS + rs_krow(half, t, j);
             if (kk < p.k) word |= static_cast<uint32_t>(static_cast<uint8_t>(__ldg(arow + kk))) << (8 * j);
         }
-        xs[(r * RS_MAX_RUN + lc) * 8 + (w & 7)] = word;
+        xs[(r * run_max + lc) * 8 + (w & 7)] = word;
     }
     __syncthreads();
 
@@ -873,8 +874,8 @@ gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const Gemv
                 for (int i = 0; i < 4; ++i) w[sb][h][i] = *reinterpret_cast<const uint2*>(box + h * 2048 + off[sb][i]);
         uint32_t a0 = 0, a2 = 0;
         if (g8 < p.m) {
-            a0 = xs[(g8 * RS_MAX_RUN + t) * 8 + t4];
-            a2 = xs[(g8 * RS_MAX_RUN + t) * 8 + 4 + t4];
+            a0 = xs[(g8 * run_max + t) * 8 + t4];
+            a2 = xs[(g8 * run_max + t) * 8 + 4 + t4];
         }
         __syncwarp();  // every lane holds its part of the box
         if (lane == 0 && t + slots < run) issue(t + slots);
@@ -1138,7 +1139,7 @@ int32_t launch_rrr(GemvParams p, int batch, const GemvDesc& gd, cudaStream_t str
 
 struct RsPlan {
     bool ok;
-    int chunks_per_strip, strips, ctas, slots, slots_total;
+    int chunks_per_strip, strips, ctas, slots, slots_total, run_max;
     size_t smem;
 };
 
@@ -1154,9 +1155,11 @@ RsPlan plan_rrr_stream(int m, int n, int k, int sms) {
     if (total < ctas) ctas = static_cast<int>(total);
     pl.ctas = ctas;
     const int64_t per_cta = (total + ctas - 1) / ctas;
-    if (per_cta > RS_MAX_RUN) return pl;
+    if (per_cta > 4096) return pl;
+    pl.run_max = static_cast<int>(per_cta);
     pl.slots_total = ctas + pl.strips;
-    const size_t x_bytes = static_cast<size_t>(m) * RS_MAX_RUN * 8 * 4;
+    const size_t x_bytes = static_cast<size_t>(m) * pl.run_max * 8 * 4;
+    if (1024 + x_bytes + 2 * RS_WARPS * RS_BOX_BYTES + 1024 > 232448) return pl;  // two ring slots must still fit
     const size_t fixed = 1024 + x_bytes + RS_WARPS * 3 * 8 + RS_WARPS * 4 + 64;
     const size_t budget = 232448;  // 227 KiB of shared memory per CTA
     int slots = static_cast<int>((budget - fixed) / (RS_WARPS * RS_BOX_BYTES));
@@ -1182,7 +1185,7 @@ int32_t launch_rrr_stream(GemvParams p, int batch, const RsPlan& pl, const GemvD
     p.rs_items_per_block = pl.chunks_per_strip;
     p.rs_blocks = pl.strips;
     p.rs_slots = pl.slots;
-    p.rs_jmax = 0;
+    p.rs_run_max = pl.run_max;
     p.rs_ctas = pl.ctas;
     p.rs_slots_total = pl.slots_total;
     p.rs_partials = static_cast<int32_t*>(gd.workspace);
@@ -1234,7 +1237,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     p.ws_partials = nullptr; p.ws_tickets = nullptr;
     p.pdl = g.pdl;
     p.mma_groups = 0;
-    p.rs_items_per_block = 0; p.rs_blocks = 0; p.rs_slots = 0; p.rs_jmax = 0; p.rs_ctas = 0;
+    p.rs_items_per_block = 0; p.rs_blocks = 0; p.rs_slots = 0; p.rs_run_max = 0; p.rs_ctas = 0;
     p.rs_partials = nullptr; p.rs_slots_total = 0;
 
     // the streaming kernels need 16-byte alignment of every weight row segment they load

@@ -207,7 +207,7 @@ def test_dependent_launch_mode_gives_the_same_results(oracle):
 
 @pytest.mark.parametrize("variant", [0, 8])  # tensor-copy streaming kernel (default), direct-load split-K kernel
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (2, 1040, 2064), (3, 272, 1000), (5, 14336, 512), (8, 2048, 4100),
-                                   (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096)])
+                                   (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096), (2, 32768, 8192)])
 def test_both_row_major_weight_kernels_on_the_same_shapes(oracle, shape, variant):
     """Weights row-major [K, N] (the reference GEMV's layout, gemv_dense.cu:128-171): int32 sums are exact whichever
     kernel runs; ragged K (not a multiple of the 32-row copy), N that is not a multiple of the 256-column block."""
