@@ -1,9 +1,12 @@
 // Skinny int8 GEMV for decode (m = 1..8 activation rows), HBM-bandwidth bound:
 //   D[g, r, j] = bf16( alpha * (sa[r]*sb[j]) * sum_k A[g,r,k] * B[g,k,j] + beta * D[g,r,j] )
-// or the raw int32 sums.  The weight matrix is streamed exactly once with
-// 128-bit loads that bypass L1; the int32 dot products use dp4a; partial sums
-// meet through warp shuffles (and, for the row-major weight layout, a shared
-// memory + workspace split-K reduction).
+// or the raw int32 sums.  The weight matrix is streamed exactly once.  Kernels, in the order the dispatcher tries them:
+//   gemv_q8_rcr_mma_kernel      weights [N, K], m >= 2 (and m = 1 under dependent launch): bulk copies, mma.sync
+//   gemv_q8_rcr_stream_kernel   weights [N, K], m <= 4: bulk copies, dp4a + warp shuffles
+//   gemv_q8_rrr_stream_kernel   weights [K, N]: tensor copies, byte-permute transposes, mma.sync; K is split over
+//                               CTAs, partial rows go to the caller's scratch, gemv_q8_rrr_reduce_kernel adds them
+//   gemv_q8_rcr_kernel / gemv_q8_rrr_kernel   128-bit loads that bypass L1 + dp4a, for shapes the above decline
+//   gemv_q8_generic_kernel      byte loads, any alignment
 //
 // Takes the role of the reference's dense m=1 GEMV
 //   crates/baracuda-kernels-sys/kernels/gemm/gemv_dense.cu:101-219 (validation + launcher)
