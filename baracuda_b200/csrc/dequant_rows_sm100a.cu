@@ -82,7 +82,125 @@ dequant_rows_kernel(const uint32_t* __restrict__ acc, int64_t ld_acc, const floa
     }
 }
 
+// The owner of a row block in the fused K-sharded forward: adds the `world` partial-sum slots that the ranks' GEMM
+// epilogues stored into its staging buffer, applies the scales like dequant_rows_kernel, and stores the bf16 rows into
+// every rank's output through peer pointers (plain stores over NVLink, peers visited from rank + 1 on so that no
+// buffer is every rank's target at once).  Eight columns per thread.
+struct PeerOut {
+    __nv_bfloat16* y[8];
+};
+
+template <bool INT_ACC>
+__global__ void __launch_bounds__(256)
+reduce_dequant_broadcast_kernel(const uint32_t* __restrict__ staging, int world, int rank, int rows, int n,
+                                const float* __restrict__ sa, const float* __restrict__ sb, int scale_mode, float alpha,
+                                const float* __restrict__ bias, PeerOut out, int64_t ldy, int vec) {
+    const int groups = (n + 7) / 8;
+    const int64_t total = static_cast<int64_t>(rows) * groups;
+    const int64_t slot_stride = static_cast<int64_t>(rows) * n;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int r = static_cast<int>(idx / groups);
+        const int col0 = static_cast<int>(idx - static_cast<int64_t>(r) * groups) * 8;
+        const int row = rank * rows + r;  // row of the whole [M, N] result
+        const bool full = col0 + 8 <= n;
+        float facc[8];
+        int iacc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            facc[j] = 0.0f;
+            iacc[j] = 0;
+        }
+        for (int s = 0; s < world; ++s) {  // slot order: the f32 sum does not depend on arrival order
+            const uint32_t* src = staging + s * slot_stride + static_cast<int64_t>(r) * n + col0;
+            uint32_t v[8];
+            if (vec && full) {
+                const uint4 lo = __ldcs(reinterpret_cast<const uint4*>(src));
+                const uint4 hi = __ldcs(reinterpret_cast<const uint4*>(src) + 1);
+                v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+                v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = col0 + j < n ? src[j] : 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if constexpr (INT_ACC) {
+                    iacc[j] += static_cast<int32_t>(v[j]);
+                } else {
+                    facc[j] = __fadd_rn(facc[j], __uint_as_float(v[j]));
+                }
+            }
+        }
+        const float sa_row = scale_mode == 1 ? __ldg(sa + row) : __ldg(sa);
+        float y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int col = col0 + j < n ? col0 + j : n - 1;
+            const float sb_col = scale_mode == 1 ? __ldg(sb + col) : __ldg(sb);
+            const float s = __fmul_rn(sa_row, sb_col);
+            const float a = INT_ACC ? static_cast<float>(iacc[j]) : facc[j];
+            y[j] = __fmul_rn(__fmul_rn(s, a), alpha);
+            if (bias) y[j] = __fadd_rn(y[j], __ldg(bias + col));
+        }
+        uint4 packed;
+        {
+            __nv_bfloat162 h;
+            h = __floats2bfloat162_rn(y[0], y[1]); packed.x = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2bfloat162_rn(y[2], y[3]); packed.y = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2bfloat162_rn(y[4], y[5]); packed.z = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2bfloat162_rn(y[6], y[7]); packed.w = *reinterpret_cast<uint32_t*>(&h);
+        }
+        for (int q = 0; q < world; ++q) {
+            int dst_rank = rank + 1 + q;
+            if (dst_rank >= world) dst_rank -= world;
+            __nv_bfloat16* dst = out.y[dst_rank] + static_cast<int64_t>(row) * ldy + col0;
+            if (vec && full) {
+                *reinterpret_cast<uint4*>(dst) = packed;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (col0 + j < n) dst[j] = __float2bfloat16_rn(y[j]);
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
+
+int32_t launch_reduce_dequant_broadcast(int32_t kind, int32_t rank, int32_t world, int32_t rows, int32_t n,
+                                        const void* staging_local, const float* scale_a, const float* scale_b,
+                                        int32_t scale_mode, float alpha, const float* bias, void* const* y, int64_t ldy,
+                                        cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return BQ_STATUS_OK;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || !y || !staging_local) return BQ_STATUS_INVALID_PROBLEM;
+    const int sms = sm_count_of_current_device();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    PeerOut out;
+    int vec = ((reinterpret_cast<uintptr_t>(staging_local) & 15u) == 0 && (n % 4) == 0 && ((ldy * 2) & 15) == 0) ? 1 : 0;
+    for (int q = 0; q < 8; ++q) {
+        out.y[q] = q < world ? static_cast<__nv_bfloat16*>(y[q]) : nullptr;
+        if (q < world && (!y[q] || (reinterpret_cast<uintptr_t>(y[q]) & 15u) != 0)) {
+            if (!y[q]) return BQ_STATUS_INVALID_PROBLEM;
+            vec = 0;
+        }
+    }
+    const int64_t total = static_cast<int64_t>(rows) * ((n + 7) / 8);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sms) * 16;
+    if (blocks > cap) blocks = cap;
+    if (kind == BQ_KIND_S8) {
+        reduce_dequant_broadcast_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            static_cast<const uint32_t*>(staging_local), world, rank, rows, n, scale_a, scale_b, scale_mode, alpha, bias, out,
+            ldy, vec);
+    } else {
+        reduce_dequant_broadcast_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            static_cast<const uint32_t*>(staging_local), world, rank, rows, n, scale_a, scale_b, scale_mode, alpha, bias, out,
+            ldy, vec);
+    }
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
 
 int32_t launch_dequant_rows(int32_t kind, int32_t m, int32_t n, const void* acc, int64_t ld_acc, const float* scale_a,
                             const float* scale_b, int32_t scale_mode, float alpha, const float* bias, void* d, int64_t ldd,

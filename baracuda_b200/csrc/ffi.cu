@@ -292,6 +292,43 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     return bq::launch_gemm_q8(g, stream);
 }
 
+int32_t bq::launch_gemm_raw_reduce_scatter_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a,
+                                                   int64_t lda, const void* b, int64_t ldb, void* const* staging,
+                                                   int32_t world, int32_t rank, cudaStream_t stream) {
+    if (!staging || world < 2 || world > BARACUDA_Q_MAX_PEERS || rank < 0 || rank >= world)
+        return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (m <= 0 || n <= 0 || k <= 0 || m % world != 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, nullptr, 0, staging[rank], n);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (!a || !b) return bq::BQ_STATUS_INVALID_PROBLEM;
+    for (int r = 0; r < world; ++r) {
+        if (!staging[r]) return bq::BQ_STATUS_INVALID_PROBLEM;
+        if (!aligned16(staging[r])) return bq::BQ_STATUS_MISALIGNED;
+    }
+    bq::GemmDesc g = {};
+    g.b_layout = bq::BQ_LAYOUT_RCR;
+    g.kind = kind;
+    g.raw_out = 1;
+    g.m = m;
+    g.n = n;
+    g.k = k;
+    g.a = a;
+    g.lda = lda;
+    g.b = b;
+    g.ldb = ldb;
+    g.alpha = 1.0f;
+    g.d = staging[rank];  // alignment probe only: every row is stored through peer_d
+    g.ldd = n;
+    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.direct_stores = 1;
+    g.peer_rank = rank;
+    g.rs_world = world;
+    g.rs_rows = m / world;
+    for (int r = 0; r < 8; ++r) g.peer_d[r] = r < world ? staging[r] : nullptr;
+    return bq::launch_gemm_q8(g, stream);
+}
+
 extern "C" {
 
 // ---- W8A8 -> bf16 ------------------------------------------------------------

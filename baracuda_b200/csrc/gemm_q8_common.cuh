@@ -39,6 +39,10 @@ struct GemmParams {
     const void* bias;
     int bias_kind;  // 0 none, 1 float[N], 2 int32[N]
     int act;        // 0 none, 1 relu, 2 gelu (erf form), 3 silu
+    // raw-accumulator reduce-scatter (K-sharded GEMM): output row r belongs to rank r / rs_rows and is stored
+    // into that rank's staging buffer peer_d[owner], slot peer_rank, row r % rs_rows (row pitch ldd); 0 = off
+    int rs_world;
+    int rs_rows;
 };
 
 // bias[col] then activation, in f32 — the formulas of the reference's epilogue header
@@ -65,7 +69,14 @@ template <uint32_t KIND, bool RAW, bool FUSED>
 __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
                                                   float sa_row, const float* sb32) {
     if constexpr (RAW) {
-        uint32_t* drow = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+        uint32_t* drow;
+        if (p.rs_world > 1) {
+            const int owner = row / p.rs_rows;
+            drow = reinterpret_cast<uint32_t*>(p.peer_d[owner]) +
+                   (static_cast<int64_t>(p.peer_rank) * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd + col0;
+        } else {
+            drow = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
+        }
         if (p.vec_store && col0 + 32 <= p.n) {
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
@@ -310,6 +321,40 @@ __device__ __forceinline__ void epilogue_block_32(const GemmParams& p, uint32_t 
                                               static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
                 }
             }
+        }
+    }
+    __syncwarp();
+}
+
+// Raw 32-bit accumulators of a 32-column block, reduce-scatter mode: 32 rows x 128 bytes go through the warp's
+// staging buffer (16-byte packet c of row r at stage[r * 8 + (c ^ (r & 7))]) so that every store instruction writes
+// four complete 128-byte row segments -- what stores that cross NVLink need.  Row r of the tile lands in the staging
+// buffer of the rank that owns it (see GemmParams::rs_world).
+__device__ __forceinline__ void epilogue_block_raw32_scatter(const GemmParams& p, uint32_t t_addr, int row_base, int lane,
+                                                             int col0, uint4* stage) {
+    {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(t_addr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+            stage[lane * 8 + (v ^ (lane & 7))] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
+    }
+    __syncwarp();
+    const int sub_row = lane >> 3;  // 0..3
+    const int c = lane & 7;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + sub_row;
+        const int row = row_base + rr;
+        const uint4 v = stage[rr * 8 + (c ^ (rr & 7))];
+        if (row < p.m) {
+            const int owner = row / p.rs_rows;
+            uint32_t* dst = reinterpret_cast<uint32_t*>(p.peer_d[owner]) +
+                            (static_cast<int64_t>(p.peer_rank) * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd + col0 + c * 4;
+            *reinterpret_cast<uint4*>(dst) = v;
         }
     }
     __syncwarp();

@@ -232,6 +232,12 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                             continue;
                         }
                     }
+                    if constexpr (RAW) {
+                        if (p.rs_world > 1 && p.vec_store && col0 + 32 <= p.n) {  // warp-uniform
+                            epilogue_block_raw32_scatter(p, t_row + static_cast<uint32_t>(c * 32), m_blk * BLOCK_M + q * 32, lane, col0, stage_buf);
+                            continue;
+                        }
+                    }
                     uint32_t r[32];
                     __syncwarp();
                     tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
@@ -342,6 +348,8 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.peer_ld = g.peer_ld;
     p.peer_col0 = g.peer_col0;
     p.peer_rank = g.peer_rank;
+    p.rs_world = RAW ? g.rs_world : 0;
+    p.rs_rows = g.rs_rows;
     p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
     for (int r = 0; r < 8; ++r) {
         p.peer_d[r] = g.peer_d[r];

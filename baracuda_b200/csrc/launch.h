@@ -53,9 +53,24 @@ struct GemmDesc {
     int64_t peer_ld;
     int32_t peer_col0;
     int32_t peer_rank;
+    // raw-accumulator reduce-scatter (raw_out only): row r goes to peer_d[r / rs_rows], slot peer_rank; 0 = off
+    int32_t rs_world;
+    int32_t rs_rows;
 };
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);
+// Raw-accumulator GEMM of a K shard whose epilogue scatters the [m, n] partial sums by row block: rows
+// [j * m / world, (j + 1) * m / world) go to rank j's staging buffer staging[j] ([world][m / world][n] 32-bit words,
+// peer-mapped), slot `rank`.  m must divide by world.
+int32_t launch_gemm_raw_reduce_scatter_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+                                               const void* b, int64_t ldb, void* const* staging, int32_t world,
+                                               int32_t rank, cudaStream_t stream);
+// Second half of the fused K-sharded forward on the owner of a row block: adds the `world` slots of `staging_local`,
+// applies scales / alpha / bias like launch_dequant_rows and stores the bf16 rows into every rank's y[q] (row pitch ldy).
+int32_t launch_reduce_dequant_broadcast(int32_t kind, int32_t rank, int32_t world, int32_t rows, int32_t n,
+                                        const void* staging_local, const float* scale_a, const float* scale_b,
+                                        int32_t scale_mode, float alpha, const float* bias, void* const* y, int64_t ldy,
+                                        cudaStream_t stream);
 // Validates like the flat *_run symbols, then launches the bf16-out GEMM; with `peer_d` the epilogue
 // additionally stores into the `world` peer buffers at column offset rank * n.
 int32_t launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,

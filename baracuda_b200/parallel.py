@@ -160,7 +160,7 @@ class ColumnParallelQGemmPlan:
         _check(st, "ColumnParallelQGemmPlan.forward")
 
 
-REDUCE_NONE, REDUCE_NCCL = 0, 1
+REDUCE_NONE, REDUCE_NCCL, REDUCE_FUSED_PEER = 0, 1, 2
 
 
 class RowParallelQGemmPlan:
@@ -173,8 +173,10 @@ class RowParallelQGemmPlan:
                  scale_mode: int = SCALE_PER_ROW_COL, reduce: int = REDUCE_NCCL):
         if kind not in ("fp8", "w8a8"):
             raise InvalidProblem("kind must be 'fp8' or 'w8a8'")
-        if reduce not in (REDUCE_NONE, REDUCE_NCCL):
+        if reduce not in (REDUCE_NONE, REDUCE_NCCL, REDUCE_FUSED_PEER):
             raise InvalidProblem("unknown reduce mode")
+        if reduce == REDUCE_FUSED_PEER and (ctx.world < 2 or m % ctx.world != 0):
+            raise InvalidProblem("the fused mode needs two or more ranks and M divisible by the world size")
         if min(m, out_features, in_features) < 0:
             raise InvalidProblem("negative dimension")
         lo, hi = shard_range(in_features, ctx.world, ctx.rank)
@@ -206,6 +208,31 @@ class RowParallelQGemmPlan:
         else:
             st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(*common, *tail)
         _check(st, "RowParallelQGemmPlan.forward")
+
+    def forward_fused(self, stream, a_local: torch.Tensor, scale_a: torch.Tensor, w_local: torch.Tensor,
+                      scale_b: torch.Tensor, peer_y: Sequence[int], peer_staging: Sequence[int], barrier_scratch: torch.Tensor,
+                      bias: Optional[torch.Tensor] = None, alpha: float = 1.0, ldy: int = 0) -> None:
+        """REDUCE_FUSED_PEER: the GEMM epilogue scatters the partial sums into the owners' staging buffers, each owner
+        adds, dequantises and stores its rows into every rank's result.  `peer_y` / `peer_staging`: one device pointer per
+        rank (see alloc_peer_buffers): [M, N] bf16 and [world, M/world, N] int32."""
+        if self.reduce != REDUCE_FUSED_PEER:
+            raise InvalidProblem("plan was not built for the fused mode")
+        if len(peer_y) != self.ctx.world or len(peer_staging) != self.ctx.world:
+            raise InvalidProblem("one pointer per rank is needed")
+        if a_local.numel() < self.m * self.k_local or w_local.numel() < self.n * self.k_local:
+            raise InvalidProblem("operand shorter than the descriptor says")
+        ys = (C.c_void_p * self.ctx.world)(*peer_y)
+        st_ptrs = (C.c_void_p * self.ctx.world)(*peer_staging)
+        lib = _lib.load()
+        common = (self.ctx.rank, self.ctx.world, self.ctx.comm, self.m, self.n, self.k_local, _ptr(a_local),
+                  max(self.k_local, 1), _ptr(w_local), max(self.k_local, 1), ys, ldy or max(self.n, 1), _ptr(scale_a),
+                  _ptr(scale_b))
+        tail = (_ptr(bias), alpha, st_ptrs, _ptr(barrier_scratch), _stream_ptr(stream))
+        if self.kind == "fp8":
+            st = lib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run(*common, self.scale_mode, *tail)
+        else:
+            st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_run(*common, *tail)
+        _check(st, "RowParallelQGemmPlan.forward_fused")
 
 
 def alloc_peer_buffers(shape, dtype=torch.bfloat16, group=None):

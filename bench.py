@@ -475,6 +475,24 @@ def main() -> None:
         r_ms = event_time_ms(rp_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
         barrier()
         r_total = max_over_ranks(sum(r_ms))
+        try:
+            y_sym, y_ptrs = par.alloc_peer_buffers((rp_m, rp_n))
+            st_sym, st_ptrs = par.alloc_peer_buffers((world, rp_m // world, rp_n), dtype=torch.int32)
+            rpf_plan = par.RowParallelQGemmPlan(ctx, rp_m, rp_n, rp_k, kind="w8a8", reduce=par.REDUCE_FUSED_PEER)
+            rp_scratch = torch.zeros(1, device="cuda")
+            rpf_step = lambda: rpf_plan.forward_fused(None, xa, xsa, xw, xsb, y_ptrs, st_ptrs, rp_scratch)
+            barrier()
+            rf_ms = event_time_ms(rpf_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+            barrier()
+            rf_total = max_over_ranks(sum(rf_ms))
+            others["row_parallel_w8a8_fused"] = {
+                "shape": [rp_m, rp_n, rp_k], "TOPS": 2.0 * rp_m * rp_n * rp_k * len(rf_ms) / (rf_total * 1e-3) / 1e12,
+                "ms_per_step": rf_total / len(rf_ms),
+                "nvlink_bytes_out_per_rank": (rp_m // world) * rp_n * (world - 1) * (4 + 2),
+                "note": "GEMM epilogue scatters int32 partial sums to the row-block owners over NVLink, owners add, "
+                        "dequantise and store their rows into every rank's result; two one-float all-reduces as barriers"}
+        except Exception as exc:  # symmetric memory not available on this box
+            others["row_parallel_w8a8_fused"] = {"unavailable": repr(exc)[:200]}
         others["row_parallel_w8a8_allreduce"] = {
             "shape": [rp_m, rp_n, rp_k], "TOPS": 2.0 * rp_m * rp_n * rp_k * len(r_ms) / (r_total * 1e-3) / 1e12,
             "ms_per_step": r_total / len(r_ms), "allreduced_bytes": rp_m * rp_n * 4,

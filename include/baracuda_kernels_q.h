@@ -450,6 +450,31 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_run(
     const void* bias, float alpha,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same forward with both exchanges fused into the kernels over peer-mapped memory (NVLink), no NCCL data path:
+ *   1. the raw-accumulator GEMM's epilogue stores rows [j*M/world, (j+1)*M/world) of its partial sums into rank j's
+ *      staging buffer peer_staging[j] -- [world][M/world][N] 32-bit words, slot = the storing rank -- while the
+ *      tensor cores work on the next tile (GEMM + reduce-scatter in one kernel);
+ *   2. each rank adds the `world` slots of its own staging buffer in slot order, applies scales / alpha / bias, and
+ *      stores its M/world bf16 rows into every rank's result peer_y[q] (row pitch ldy) (reduce + all-gather in one kernel).
+ * A one-float ncclAllReduce on `barrier_scratch` orders the ranks after each step, so `comm` is still needed.
+ * peer_y and peer_staging are arrays of `world` device pointers valid on this rank (CUDA IPC or a symmetric-memory
+ * allocator); M must divide by world, world <= BARACUDA_Q_MAX_PEERS; every rank passes the same arguments.
+ * No counterpart in the reference (its RowParallelLinearPlan calls ncclAllReduce). */
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_run(
+    int32_t rank, int32_t world, void* comm,
+    int32_t m, int32_t n, int32_t k_local,
+    const void* a_local, int64_t lda, const void* b_local, int64_t ldb,
+    void* const* peer_y, int64_t ldy, const void* scale_a, const void* scale_b,
+    const void* bias, float alpha,
+    void* const* peer_staging, void* barrier_scratch, void* stream);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run(
+    int32_t rank, int32_t world, void* comm,
+    int32_t m, int32_t n, int32_t k_local,
+    const void* a_local, int64_t lda, const void* b_local, int64_t ldb,
+    void* const* peer_y, int64_t ldy, const void* scale_a, const void* scale_b, int32_t scale_mode,
+    const void* bias, float alpha,
+    void* const* peer_staging, void* barrier_scratch, void* stream);
+
 /* Communicator helpers over the run-time-loaded NCCL
  * (Communicator::{new_with_id, all_gather}, crates/baracuda-nccl/src/lib.rs:243-261, 468-489).
  * unique_id writes the 128-byte ncclUniqueId; rank 0 creates it and the caller

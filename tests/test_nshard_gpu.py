@@ -83,7 +83,7 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             check(bits(full_rm), want, "fused peer store")
             assert bq.device_status() == 0
         # K-sharded (row-parallel) forward: raw accumulators all-reduced, one dequant pass, bias added once
-        for kind, (m, n, k) in (("w8a8", (300, 1040, 1024)), ("fp8", (512, 1024, 2048))):
+        for kind, (m, n, k) in (("w8a8", (300, 1040, 1024)), ("fp8", (512, 1024, 2048)), ("w8a8", (1024, 2048, 4096))):
             rng = np.random.default_rng(11)
             a = rng.standard_normal((m, k)).astype(np.float32)
             w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -105,12 +105,33 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             plan.forward(None, par.shard_cols(torch.from_numpy(aq), world, rank).cuda(), dev(sa),
                          par.shard_cols(torch.from_numpy(wq), world, rank).cuda(), dev(sb), y_d, ws, bias=dev(bias))
             torch.cuda.synchronize()
-            if kind == "w8a8":
-                assert np.array_equal(bits(y_d), want), f"row-parallel w8a8 rank {rank}"
-            else:
-                g_f = orc.bf16_bits_to_f32(bits(y_d))
-                assert orc.compare_tolerant(want_f, g_f, 1e-2, 1e-4 * float(np.abs(want_f).max())) == -1, "row-parallel fp8"
+            def check_rp(t, what):
+                if kind == "w8a8":
+                    assert np.array_equal(bits(t), want), f"{what} w8a8 rank {rank}"
+                else:
+                    g_f = orc.bf16_bits_to_f32(bits(t))
+                    assert orc.compare_tolerant(want_f, g_f, 1e-2, 1e-4 * float(np.abs(want_f).max())) == -1, f"{what} fp8"
+
+            check_rp(y_d, "row-parallel (nccl)")
             assert bq.device_status() == 0
+            # fused: GEMM epilogue scatters raw partial sums to the owners, owners reduce + dequant + store to every rank
+            if m % world == 0:
+                y_sym, y_ptrs = par.alloc_peer_buffers((m, n))
+                st_sym, st_ptrs = par.alloc_peer_buffers((world, m // world, n), dtype=torch.int32)
+                y_sym.zero_()
+                st_sym.fill_(0x7F7F7F7F)  # stale contents must not matter
+                torch.cuda.synchronize()
+                dist.barrier()
+                fplan = par.RowParallelQGemmPlan(ctx, m, n, k, kind=kind, reduce=par.REDUCE_FUSED_PEER)
+                scratch = torch.zeros(1, device="cuda")
+                a_l = par.shard_cols(torch.from_numpy(aq), world, rank).cuda()
+                w_l = par.shard_cols(torch.from_numpy(wq), world, rank).cuda()
+                for _ in range(2):  # twice: the staging buffers are reused
+                    fplan.forward_fused(None, a_l, dev(sa), w_l, dev(sb), y_ptrs, st_ptrs, scratch, bias=dev(bias))
+                torch.cuda.synchronize()
+                dist.barrier()
+                check_rp(y_sym, "row-parallel (fused)")
+                assert bq.device_status() == 0
         ctx.destroy()
         with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
             f.write("ok")
