@@ -746,7 +746,7 @@ __host__ __device__ __forceinline__ int rs_krow(int half, int t, int i) {
 }
 
 template <bool RAW>
-__global__ void __launch_bounds__(RS_THREADS, 1)
+__global__ void __maxnreg__(112)
 gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemvParams p) {
     extern __shared__ uint8_t rs_smem_raw[];
     // swizzled tensor copies land on 1024-byte boundaries; round up inside the shared window
@@ -899,7 +899,7 @@ gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const Gemv
 // Adds, for 256 columns of a strip and one activation row, the partial rows of the CTAs that shared the strip,
 // and stores the result.  Sixteen partial rows are requested at a time: the loads are all that this kernel waits for.
 template <bool RAW>
-__global__ void __launch_bounds__(256)
+__global__ void __maxnreg__(32)
 gemv_q8_rrr_reduce_kernel(const GemvParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the streaming kernel's partial rows are complete and visible
     const int col = blockIdx.x * 256 + threadIdx.x;

@@ -450,6 +450,150 @@ class GemvQ8Plan {
     bool raw_ = false;
 };
 
+// ---------------------------------------------------------------------------- tensor parallel
+// The reference's TensorParallelContext / ColumnParallelLinearPlan / RowParallelLinearPlan
+// (crates/baracuda-megatron/src/lib.rs:153-240, 729-905, 1002-1200) for 8-bit operands.  `comm` is the handle
+// made by baracuda_q_nccl_comm_init_rank (null with world 1).
+struct TensorParallelContext {
+    int32_t rank = 0;
+    int32_t world = 1;
+    void* comm = nullptr;
+    bool valid() const { return world >= 1 && rank >= 0 && rank < world; }
+};
+
+// [lo, hi) of `extent` that `rank` owns; `extent` must divide evenly (lib.rs:781-785).
+inline Error shard_range(int32_t extent, const TensorParallelContext& ctx, int32_t* lo, int32_t* hi) {
+    if (!ctx.valid() || extent < 0 || extent % ctx.world != 0) return Error::InvalidProblem;
+    const int32_t per = extent / ctx.world;
+    *lo = ctx.rank * per;
+    *hi = *lo + per;
+    return Error::Ok;
+}
+
+enum class GatherMode : int32_t { None = BARACUDA_Q_GATHER_NONE, Nccl = BARACUDA_Q_GATHER_NCCL,
+                                  FusedPeerStore = BARACUDA_Q_GATHER_FUSED_PEER_STORE };
+enum class ReduceMode : int32_t { None = BARACUDA_Q_REDUCE_NONE, Nccl = BARACUDA_Q_REDUCE_NCCL };
+
+struct ColumnParallelArgs {
+    DeviceSpan<const void> a;        // replicated activations [M, K]
+    DeviceSpan<const float> scale_a; // [M] (or one float, per-tensor FP8)
+    DeviceSpan<const void> w_local;  // this rank's weight rows [N/world, K]
+    DeviceSpan<const float> scale_b_local;
+    DeviceSpan<void> y_local;        // [M, N/world] bf16
+    DeviceSpan<void> y_full;         // Nccl: [world, M, N/world] bf16
+    void* const* peer_y = nullptr;   // FusedPeerStore: one row-major [M, N] buffer per rank
+    int64_t ldd_full = 0;
+    float alpha = 1.0f;
+};
+
+class ColumnParallelQGemmPlan {
+  public:
+    static Error make(const TensorParallelContext& ctx, int32_t m, int32_t out_features, int32_t k, ElementKind element,
+                      ScaleMode mode, GatherMode gather, ColumnParallelQGemmPlan* out) {
+        if (element != ElementKind::S8 && element != ElementKind::Fp8E4M3) return Error::Unsupported;
+        if (m < 0 || k < 0) return Error::InvalidProblem;
+        int32_t lo = 0, hi = 0;
+        if (Error e = shard_range(out_features, ctx, &lo, &hi); e != Error::Ok) return e;
+        out->ctx_ = ctx;
+        out->m_ = m;
+        out->n_ = out_features;
+        out->k_ = k;
+        out->n_local_ = hi - lo;
+        out->col0_ = lo;
+        out->fp8_ = element == ElementKind::Fp8E4M3;
+        out->mode_ = mode;
+        out->gather_ = gather;
+        return Error::Ok;
+    }
+    int32_t n_local() const { return n_local_; }
+    int32_t first_column() const { return col0_; }
+    Error forward(void* stream, const ColumnParallelArgs& x) const {
+        if (x.a.len < detail::span_elems(m_, k_, k_) || x.w_local.len < detail::span_elems(n_local_, k_, k_))
+            return Error::BufferTooSmall;
+        if (x.y_local.len < detail::span_elems(m_, n_local_, n_local_)) return Error::BufferTooSmall;
+        if (gather_ == GatherMode::Nccl && x.y_full.len < static_cast<size_t>(m_) * n_) return Error::BufferTooSmall;
+        if (gather_ == GatherMode::FusedPeerStore && !x.peer_y) return Error::InvalidProblem;
+        const int64_t ldk = k_ > 0 ? k_ : 1, ldn = n_local_ > 0 ? n_local_ : 1;
+        const int32_t st =
+            fp8_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(
+                       ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(gather_), m_, n_local_, k_, x.a.ptr, ldk,
+                       x.w_local.ptr, ldk, x.y_local.ptr, ldn, x.scale_a.ptr, x.scale_b_local.ptr,
+                       static_cast<int32_t>(mode_), x.alpha, x.y_full.ptr, x.peer_y, x.ldd_full ? x.ldd_full : n_, nullptr, 0,
+                       stream)
+                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
+                       ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(gather_), m_, n_local_, k_, x.a.ptr, ldk,
+                       x.w_local.ptr, ldk, x.y_local.ptr, ldn, x.scale_a.ptr, x.scale_b_local.ptr, x.alpha, x.y_full.ptr,
+                       x.peer_y, x.ldd_full ? x.ldd_full : n_, nullptr, 0, stream);
+        return status_to_error(st);
+    }
+
+  private:
+    TensorParallelContext ctx_{};
+    int32_t m_ = 0, n_ = 0, k_ = 0, n_local_ = 0, col0_ = 0;
+    bool fp8_ = false;
+    ScaleMode mode_ = ScaleMode::PerRowCol;
+    GatherMode gather_ = GatherMode::None;
+};
+
+struct RowParallelArgs {
+    DeviceSpan<const void> a_local;   // this rank's K slice of the activations [M, K/world]
+    DeviceSpan<const float> scale_a;  // one per-token scale over the whole K, the same on every rank
+    DeviceSpan<const void> w_local;   // [N, K/world]
+    DeviceSpan<const float> scale_b;
+    DeviceSpan<const float> bias;     // optional float[N], added once after the reduction
+    DeviceSpan<void> y;               // [M, N] bf16, written on every rank
+    float alpha = 1.0f;
+};
+
+class RowParallelQGemmPlan {
+  public:
+    static Error make(const TensorParallelContext& ctx, int32_t m, int32_t out_features, int32_t in_features,
+                      ElementKind element, ScaleMode mode, ReduceMode reduce, RowParallelQGemmPlan* out) {
+        if (element != ElementKind::S8 && element != ElementKind::Fp8E4M3) return Error::Unsupported;
+        if (m < 0 || out_features < 0) return Error::InvalidProblem;
+        int32_t lo = 0, hi = 0;
+        if (Error e = shard_range(in_features, ctx, &lo, &hi); e != Error::Ok) return e;
+        out->ctx_ = ctx;
+        out->m_ = m;
+        out->n_ = out_features;
+        out->k_local_ = hi - lo;
+        out->k0_ = lo;
+        out->fp8_ = element == ElementKind::Fp8E4M3;
+        out->mode_ = mode;
+        out->reduce_ = reduce;
+        return Error::Ok;
+    }
+    int32_t k_local() const { return k_local_; }
+    int32_t first_k() const { return k0_; }
+    size_t workspace_size() const { return baracuda_kernels_gemm_q8_kshard_workspace_size(m_, n_); }
+    Error forward(void* stream, Workspace ws, const RowParallelArgs& x) const {
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        if (x.a_local.len < detail::span_elems(m_, k_local_, k_local_) ||
+            x.w_local.len < detail::span_elems(n_, k_local_, k_local_))
+            return Error::BufferTooSmall;
+        if (x.y.len < detail::span_elems(m_, n_, n_)) return Error::BufferTooSmall;
+        if (x.bias.ptr && x.bias.len < static_cast<size_t>(n_)) return Error::BufferTooSmall;
+        const int64_t ldk = k_local_ > 0 ? k_local_ : 1, ldn = n_ > 0 ? n_ : 1;
+        const int32_t st =
+            fp8_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_run(
+                       ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(reduce_), m_, n_, k_local_, x.a_local.ptr, ldk,
+                       x.w_local.ptr, ldk, x.y.ptr, ldn, x.scale_a.ptr, x.scale_b.ptr, static_cast<int32_t>(mode_),
+                       x.bias.ptr, x.alpha, ws.ptr, ws.bytes, stream)
+                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(
+                       ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(reduce_), m_, n_, k_local_, x.a_local.ptr, ldk,
+                       x.w_local.ptr, ldk, x.y.ptr, ldn, x.scale_a.ptr, x.scale_b.ptr, x.bias.ptr, x.alpha, ws.ptr, ws.bytes,
+                       stream);
+        return status_to_error(st);
+    }
+
+  private:
+    TensorParallelContext ctx_{};
+    int32_t m_ = 0, n_ = 0, k_local_ = 0, k0_ = 0;
+    bool fp8_ = false;
+    ScaleMode mode_ = ScaleMode::PerRowCol;
+    ReduceMode reduce_ = ReduceMode::Nccl;
+};
+
 }  // namespace baracuda
 
 namespace std {

@@ -134,6 +134,34 @@ int main() {
     ex.scale_b = {static_cast<const float*>(fake(0x600000)), 16};
     CHECK(e.run(nullptr, Workspace::none(), ex) == Error::Ok);
 
+    // tensor-parallel plans: sharding rules and the typed checks in front of the sharded C entry points
+    {
+        TensorParallelContext ctx{1, 4, nullptr};
+        int32_t lo = 0, hi = 0;
+        CHECK(shard_range(28672, ctx, &lo, &hi) == Error::Ok && lo == 7168 && hi == 14336);
+        CHECK(shard_range(10, ctx, &lo, &hi) == Error::InvalidProblem);  // must divide evenly
+        TensorParallelContext bad{4, 4, nullptr};
+        CHECK(shard_range(16, bad, &lo, &hi) == Error::InvalidProblem);
+        ColumnParallelQGemmPlan cp;
+        CHECK(ColumnParallelQGemmPlan::make(ctx, 128, 1000, 512, ElementKind::S8, ScaleMode::PerRowCol, GatherMode::None,
+                                            &cp) == Error::Ok);
+        CHECK(cp.n_local() == 250 && cp.first_column() == 250);
+        CHECK(ColumnParallelQGemmPlan::make(ctx, 128, 1001, 512, ElementKind::S8, ScaleMode::PerRowCol, GatherMode::None,
+                                            &cp) == Error::InvalidProblem);
+        CHECK(ColumnParallelQGemmPlan::make(ctx, 128, 1000, 512, ElementKind::Bf16, ScaleMode::PerRowCol, GatherMode::None,
+                                            &cp) == Error::Unsupported);
+        ColumnParallelArgs ca;
+        CHECK(cp.forward(nullptr, ca) == Error::BufferTooSmall);  // empty views are refused before any launch
+        RowParallelQGemmPlan rp;
+        CHECK(RowParallelQGemmPlan::make(ctx, 64, 256, 4096, ElementKind::Fp8E4M3, ScaleMode::PerRowCol, ReduceMode::Nccl,
+                                         &rp) == Error::Ok);
+        CHECK(rp.k_local() == 1024 && rp.first_k() == 1024 && rp.workspace_size() == size_t(64) * 256 * 4);
+        CHECK(RowParallelQGemmPlan::make(ctx, 64, 256, 4098, ElementKind::Fp8E4M3, ScaleMode::PerRowCol, ReduceMode::Nccl,
+                                         &rp) == Error::InvalidProblem);
+        RowParallelArgs ra;
+        CHECK(rp.forward(nullptr, Workspace::none(), ra) == Error::WorkspaceTooSmall);
+    }
+
     if (failures == 0) std::printf("plan_host_test ok\n");
     return failures == 0 ? 0 : 1;
 }
