@@ -73,6 +73,9 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run": (
         _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _vp]),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_capacity": (_sz, []),
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run": (
+        _i32, [_i32, _i32, _i32, _i32, _i32, _f32, _f32, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement": (_i32, [_i32, _i32, _i32, _i64, _i64, _i64]),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size": _GEMV_WS,

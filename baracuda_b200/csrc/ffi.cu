@@ -600,6 +600,34 @@ size_t baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size(int32_t m, int32_t 
     return bq::gemv_q8_workspace_bytes(m, n, k, batch, layout);
 }
 
+// ---- decode GEMV with the per-token quantiser inside --------------------------------------------
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(int32_t m, int32_t n, int32_t k, int64_t ldx,
+                                                                         int64_t ldb, int64_t ldd) {
+    if (m < 0 || n < 0 || k < 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (m > 8) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (ldx < (k > 0 ? k : 1) || ldb < (k > 0 ? k : 1) || ldd < (n > 0 ? n : 1)) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
+    if ((ldx & 7) || (ldb & 15)) return bq::BQ_STATUS_UNSUPPORTED;  // 16-byte rows for the vector loads and bulk copies
+    return bq::gemv_q8_quant_bf16_supported(m, n, k) ? bq::BQ_STATUS_OK : bq::BQ_STATUS_UNSUPPORTED;
+}
+
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
+    int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta, const void* x_bf16,
+    int64_t ldx, const void* b, int64_t ldb, const void* scale_b, void* scale_a_out, void* d, int64_t ldd,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    const int32_t st = baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(m, n, k, ldx, ldb, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
+    if (!x_bf16 || !b || !scale_b || !d) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (qmin > qmax || qmax <= 0 || qmin < -128 || qmax > 127) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (!aligned16(x_bf16) || !aligned16(b)) return bq::BQ_STATUS_UNSUPPORTED;
+    return bq::launch_gemv_q8_quant_bf16(m, n, k, qmin, qmax, alpha, beta, x_bf16, ldx, static_cast<const int8_t*>(b), ldb,
+                                         static_cast<const float*>(scale_b), static_cast<float*>(scale_a_out), d, ldd,
+                                         g_gemv_pdl.load(std::memory_order_relaxed), static_cast<cudaStream_t>(stream));
+}
+
 // ---- diagnostics / tuning -------------------------------------------------------------
 int32_t baracuda_kernels_q_device_status(void) {
     int32_t gemm = bq::read_and_clear_gemm_device_status();

@@ -56,6 +56,11 @@ struct GemvParams {
     int32_t* rs_partials;  // [batch][slot][m][2048]; slot(c, strip) = c + strip
     int rs_slots_total;
     int mma_groups;  // tensor-core GEMV: 8-column groups per CTA (upper bound), sizes the shared accumulator
+    // fused per-token quantiser (XQ kernels): bf16 activations [m, ldx], clamp range, optional scale output [m]
+    const __nv_bfloat16* xq_x;
+    int64_t xq_ldx;
+    int xq_qmin, xq_qmax;
+    float* xq_scale_out;
     int pdl;  // launched with programmatic stream serialization: weights may be fetched before the dependency wait
 };
 
@@ -388,9 +393,17 @@ __device__ __forceinline__ void mma_s8_16x8x32_top(int& c0, int& c1, uint32_t a0
 // MMA_RING: items in flight per warp.
 // XREG: the number of K chunks divides the number of warps, so a warp meets the same K chunk in all its items and
 // keeps its activation fragments in registers (no activation staging, half the shared-memory loads).
-template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING, bool XREG = false>
+// XQ (with XREG): the activations arrive as bf16 and are quantised per token inside the kernel -- every CTA takes the
+// absolute maximum of each activation row (m x K bf16 from L2, while the first weight copies are in flight), derives
+// scale = absmax / qmax (1.0 for a zero row) and quantises just the fragments its warps keep, with the arithmetic of
+// quantize_rows_kernel (multiply by the f32 reciprocal, round half to even, clamp), so the result equals the
+// two-kernel path bit for bit and one launch disappears from the decode step.
+template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING, bool XREG = false, bool XQ = false>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 1)
 gemv_q8_rcr_mma_kernel(const GemvParams p) {
+    static_assert(!XQ || XREG, "the fused quantiser fills register fragments");
+    __shared__ float xq_red[XQ ? MMA_WARPS * 8 : 1];
+    __shared__ float xq_scale[8];
     constexpr int MMA_PITCH = MMA_KCHUNK + 64;
     constexpr int MMA_ITEM_BYTES = MMA_COLS * MMA_PITCH;
     extern __shared__ __align__(128) uint8_t mma_smem[];
@@ -453,7 +466,8 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
                          bytes, &full_bar[slot]);
         }
     };
-    for (int i = 0; i < MMA_RING && i < my_items; ++i) issue(i);
+    // XQ: the last slot's buffer first serves as this warp's staging area for the quantised activations
+    for (int i = 0; i < (XQ ? MMA_RING - 1 : MMA_RING) && i < my_items; ++i) issue(i);
     if (p.pdl) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -462,8 +476,35 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
     // activations into shared memory (rows beyond m are zero) or, XREG, this warp's K chunk of activation row gq
     // straight into registers in fragment order; accumulators cleared
     uint4 xreg[XREG ? MMA_KCHUNK / 64 : 1];
+    uint4 xraw[XQ ? 8 : 1][2];  // XQ: 16 bf16 values of every activation row, until the row scales are known
     {
-        if constexpr (XREG) {
+        if constexpr (XQ) {
+            // This warp's K chunk (MMA_KCHUNK values) of every activation row as bf16, 16 values per lane and row; the
+            // sixteen warps' chunks cover every row, so the row maxima come out of the same loads.
+            static_assert(MMA_KCHUNK == 512, "16 values per lane and row");
+            const int k0 = (warp % chunks) * MMA_KCHUNK;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float amax = 0.0f;
+                if (r < p.m) {
+                    const uint4* src = reinterpret_cast<const uint4*>(p.xq_x + static_cast<int64_t>(r) * p.xq_ldx + k0 + lane * 16);
+#pragma unroll
+                    for (int hv = 0; hv < 2; ++hv) {
+                        const uint4 v = __ldg(src + hv);
+                        xraw[r][hv] = v;
+                        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 f = __bfloat1622float2(h[j]);
+                            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                }
+                if (lane == 0) xq_red[warp * 8 + r] = amax;
+            }
+        } else if constexpr (XREG) {
             const int k0 = (warp % chunks) * MMA_KCHUNK;
 #pragma unroll
             for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
@@ -487,6 +528,49 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         }
     }
     __syncthreads();
+    if constexpr (XQ) {
+        if (threadIdx.x < p.m) {
+            float amax = 0.0f;
+            for (int w = 0; w < MMA_WARPS; ++w) amax = fmaxf(amax, xq_red[w * 8 + threadIdx.x]);
+            const float sc = (amax > 0.0f) ? __fdiv_rn(amax, static_cast<float>(p.xq_qmax)) : 1.0f;
+            xq_scale[threadIdx.x] = sc;
+            if (blockIdx.x == 0 && p.xq_scale_out) p.xq_scale_out[threadIdx.x] = sc;
+        }
+        __syncthreads();
+        // quantise the 16 values per row held as bf16 into the staging area (row pitch MMA_KCHUNK bytes), then pick up
+        // the fragments: lane (gq, tq) keeps the 16-byte pieces tq, tq + 4, ... of row gq
+        uint8_t* stage = ring + (MMA_RING - 1) * MMA_ITEM_BYTES;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < p.m) {
+                const float inv = __fdiv_rn(1.0f, xq_scale[r]);
+                uint32_t word[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+                for (int hv = 0; hv < 2; ++hv) {
+                    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&xraw[r][hv]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(h[j]);
+                        int q0 = __float2int_rn(__fmul_rn(f.x, inv));
+                        int q1 = __float2int_rn(__fmul_rn(f.y, inv));
+                        q0 = q0 < p.xq_qmin ? p.xq_qmin : (q0 > p.xq_qmax ? p.xq_qmax : q0);
+                        q1 = q1 < p.xq_qmin ? p.xq_qmin : (q1 > p.xq_qmax ? p.xq_qmax : q1);
+                        const int e = hv * 8 + j * 2;  // element index 0..15 of this lane's piece
+                        word[e >> 2] |= (static_cast<uint32_t>(q0) & 0xffu) << (8 * (e & 3));
+                        word[(e + 1) >> 2] |= (static_cast<uint32_t>(q1) & 0xffu) << (8 * ((e + 1) & 3));
+                    }
+                }
+                *reinterpret_cast<uint4*>(stage + r * MMA_KCHUNK + lane * 16) = make_uint4(word[0], word[1], word[2], word[3]);
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
+            xreg[i] = gq < p.m ? *reinterpret_cast<const uint4*>(stage + gq * MMA_KCHUNK + i * 64 + tq * 16) : make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();  // the staging area is free: it becomes the ring's last slot
+        if (MMA_RING - 1 < my_items) issue(MMA_RING - 1);
+    }
 
     bool ok = true;
     for (int mine = 0; mine < my_items; ++mine) {
@@ -559,7 +643,8 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
             } else {
                 __nv_bfloat16* dp =
                     reinterpret_cast<__nv_bfloat16*>(p.d) + g * p.stride_d + static_cast<int64_t>(r) * p.ldd + col;
-                const float sc = __fmul_rn(__ldg(p.sa + g * p.stride_sa + r), sb_s[gi * MMA_COLS + c]);
+                const float sa_r = XQ ? xq_scale[r] : __ldg(p.sa + g * p.stride_sa + r);
+                const float sc = __fmul_rn(sa_r, sb_s[gi * MMA_COLS + c]);
                 float y = __fmul_rn(__fmul_rn(sc, static_cast<float>(acc_s[i])), p.alpha);
                 if (p.beta != 0.0f) y = __fadd_rn(y, __fmul_rn(p.beta, __bfloat162float(*dp)));
                 *dp = __float2bfloat16_rn(y);
@@ -746,8 +831,7 @@ __host__ __device__ __forceinline__ int rs_krow(int half, int t, int i) {
 }
 
 template <bool RAW>
-__global__ void __maxnreg__(112)
-gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemvParams p) {
+__device__ __forceinline__ void rrr_stream_body(const CUtensorMap& tmap_b, const GemvParams& p) {
     extern __shared__ uint8_t rs_smem_raw[];
     // swizzled tensor copies land on 1024-byte boundaries; round up inside the shared window
     uint8_t* rs_smem = rs_smem_raw + ((1024u - (smem_u32(rs_smem_raw) & 1023u)) & 1023u);
@@ -896,11 +980,27 @@ gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const Gemv
     if (ok && cur_strip >= 0) finish_strip();
 }
 
+// Two builds of the streaming kernel.  The plain one may use the whole register file.  The other is capped at 112
+// registers so that, with the reduce kernel capped at 32, one reduce block fits on every SM beside a streaming CTA: under
+// programmatic stream serialization the reduce blocks are then already resident when the streaming kernel ends and their
+// launch latency disappears (23.1 -> 19.4 us at m = 1, 2).  That only pays while all reduce blocks fit (56 x m <= SMs);
+// with more rows the cap's spills cost more than the launch it hides (m = 4: 23.4 -> 24.6 us), so m > 2 uses the plain pair.
+template <bool RAW>
+__global__ void __launch_bounds__(RS_THREADS, 1)
+gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemvParams p) {
+    rrr_stream_body<RAW>(tmap_b, p);
+}
+
+template <bool RAW>
+__global__ void __maxnreg__(112)
+gemv_q8_rrr_stream_lean_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemvParams p) {
+    rrr_stream_body<RAW>(tmap_b, p);
+}
+
 // Adds, for 256 columns of a strip and one activation row, the partial rows of the CTAs that shared the strip,
 // and stores the result.  Sixteen partial rows are requested at a time: the loads are all that this kernel waits for.
 template <bool RAW>
-__global__ void __maxnreg__(32)
-gemv_q8_rrr_reduce_kernel(const GemvParams p) {
+__device__ __forceinline__ void rrr_reduce_body(const GemvParams& p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");  // the streaming kernel's partial rows are complete and visible
     const int col = blockIdx.x * 256 + threadIdx.x;
     const int strip = col / RS_STRIP;
@@ -926,6 +1026,18 @@ gemv_q8_rrr_reduce_kernel(const GemvParams p) {
         for (int u = 0; u < 16; ++u) sum += v[u];
     }
     store_result<RAW>(p, g, r, col, sum);
+}
+
+template <bool RAW>
+__global__ void __launch_bounds__(256)
+gemv_q8_rrr_reduce_kernel(const GemvParams p) {
+    rrr_reduce_body<RAW>(p);
+}
+
+template <bool RAW>
+__global__ void __maxnreg__(32)
+gemv_q8_rrr_reduce_lean_kernel(const GemvParams p) {
+    rrr_reduce_body<RAW>(p);
 }
 
 // ---- any layout, any alignment: one warp per output column, byte loads ----
@@ -1035,13 +1147,13 @@ size_t mma_smem_bytes(int kchunk, int warps, int ring, int m, int k, int groups)
            static_cast<size_t>(groups) * 64 * 4 + static_cast<size_t>(groups) * MMA_COLS * 4 + warps * ring * 8 + warps * 4 + 16;
 }
 
-template <bool RAW, int KCHUNK, int WARPS, int RING, bool XREG = false>
+template <bool RAW, int KCHUNK, int WARPS, int RING, bool XREG = false, bool XQ = false>
 int32_t launch_rcr_mma_cfg(GemvParams p, int batch, int sms, cudaStream_t stream) {
     const int want = (p.n + MMA_COLS - 1) / MMA_COLS;  // no more CTAs than 8-column groups
     const int ctas = want < sms ? want : sms;
     p.mma_groups = (want + ctas - 1) / ctas;
     const size_t smem = mma_smem_bytes(KCHUNK, WARPS, RING, XREG ? 0 : p.m, p.k, p.mma_groups);
-    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING, XREG>;
+    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING, XREG, XQ>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -1192,7 +1304,9 @@ int32_t launch_rrr_stream(GemvParams p, int batch, const RsPlan& pl, const GemvD
     p.rs_ctas = pl.ctas;
     p.rs_slots_total = pl.slots_total;
     p.rs_partials = static_cast<int32_t*>(gd.workspace);
-    auto kern = gemv_q8_rrr_stream_kernel<RAW>;
+    const int reduce_blocks = ((p.n + 255) / 256) * p.m * batch;
+    const bool lean = reduce_blocks <= sm_count_cached();
+    auto kern = lean ? gemv_q8_rrr_stream_lean_kernel<RAW> : gemv_q8_rrr_stream_kernel<RAW>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -1219,7 +1333,7 @@ int32_t launch_rrr_stream(GemvParams p, int batch, const RsPlan& pl, const GemvD
     rcfg.stream = stream;
     rcfg.attrs = attr;
     rcfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&rcfg, gemv_q8_rrr_reduce_kernel<RAW>, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&rcfg, lean ? gemv_q8_rrr_reduce_lean_kernel<RAW> : gemv_q8_rrr_reduce_kernel<RAW>, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
     }
@@ -1242,6 +1356,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     p.mma_groups = 0;
     p.rs_items_per_block = 0; p.rs_blocks = 0; p.rs_slots = 0; p.rs_run_max = 0; p.rs_ctas = 0;
     p.rs_partials = nullptr; p.rs_slots_total = 0;
+    p.xq_x = nullptr; p.xq_ldx = 0; p.xq_qmin = -127; p.xq_qmax = 127; p.xq_scale_out = nullptr;
 
     // the streaming kernels need 16-byte alignment of every weight row segment they load
     bool fast = g.k > 0 && aligned16(g.a) && aligned16(g.b) && (g.stride_b % 16 == 0) && (g.ldb % 16 == 0);
@@ -1318,6 +1433,40 @@ size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, i
     }
     const size_t streamed = n * static_cast<int64_t>(k) >= (1 << 18) ? rrr_stream_workspace_bytes(m, n, batch) : 0;
     return direct > streamed ? direct : streamed;
+}
+
+// Shapes the fused-quantiser GEMV serves: K a whole number of 512-byte chunks that divides 16, K-contiguous weights.
+bool gemv_q8_quant_bf16_supported(int32_t m, int32_t n, int32_t k) {
+    if (m < 1 || m > 8 || n < 1 || k < 512 || (k % 512) != 0 || (16 % (k / 512)) != 0) return false;
+    const int sms = sm_count_cached();
+    if (sms <= 0) return true;  // no device to ask: the shape rules above are all that can be judged
+    const int want = (n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = want < sms ? want : sms;
+    const int groups = (want + ctas - 1) / ctas;
+    return groups <= MMA_MAX_GROUPS && mma_smem_bytes(512, 16, 3, 0, k, groups) + 1024 <= 232448;  // + the static part
+}
+
+int32_t launch_gemv_q8_quant_bf16(int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta,
+                                  const void* x_bf16, int64_t ldx, const int8_t* b, int64_t ldb, const float* scale_b,
+                                  float* scale_a_out, void* d, int64_t ldd, int32_t pdl, cudaStream_t stream) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    GemvParams p = {};
+    p.a = nullptr; p.lda = 0; p.stride_a = 0;
+    p.b = b; p.ldb = ldb; p.stride_b = 0;
+    p.sa = nullptr; p.stride_sa = 0;
+    p.sb = scale_b; p.stride_sb = 0;
+    p.d = d; p.ldd = ldd; p.stride_d = 0;
+    p.alpha = alpha; p.beta = beta;
+    p.m = m; p.n = n; p.k = k;
+    p.num_kslices = 1;
+    p.pdl = pdl;
+    p.xq_x = static_cast<const __nv_bfloat16*>(x_bf16);
+    p.xq_ldx = ldx;
+    p.xq_qmin = qmin;
+    p.xq_qmax = qmax;
+    p.xq_scale_out = scale_a_out;
+    return launch_rcr_mma_cfg<false, 512, 16, 3, true, true>(p, 1, sms, stream);
 }
 
 int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream) {

@@ -120,5 +120,10 @@ int32_t read_and_clear_gemv_device_status();
 // Launches one thread that waits on a barrier nothing completes; the wait gives up after limit_cycles and sets status 299.
 int32_t launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t stream);
 size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
+// Decode GEMV with the per-token quantiser inside: bf16 activations in, K-contiguous int8 weights, bf16 out.
+bool gemv_q8_quant_bf16_supported(int32_t m, int32_t n, int32_t k);
+int32_t launch_gemv_q8_quant_bf16(int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta,
+                                  const void* x_bf16, int64_t ldx, const int8_t* b, int64_t ldb, const float* scale_b,
+                                  float* scale_a_out, void* d, int64_t ldd, int32_t pdl, cudaStream_t stream);
 
 }  // namespace bq

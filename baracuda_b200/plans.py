@@ -541,9 +541,32 @@ class QuantizedLinearPlan:
     def workspace_size(self) -> int:
         return self._mm.workspace_size()
 
+    def fused_decode_ok(self, args: QuantizedLinearArgs) -> bool:
+        """True when the whole step runs as one launch: bf16 activation, m <= 8, and a K the fused-quantiser GEMV serves."""
+        d = self.desc
+        if not isinstance(self._mm, GemvQ8Plan) or args.activation.dtype != torch.bfloat16:
+            return False
+        st = _lib.load().baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(d.m, d.c_out, d.k, max(d.k, 1),
+                                                                                          max(d.k, 1), max(d.c_out, 1))
+        return st == 0 and args.activation.data_ptr() % 16 == 0 and args.weight_q.data_ptr() % 16 == 0
+
     def run(self, stream, workspace: Optional[torch.Tensor], args: QuantizedLinearArgs) -> None:
         if args.act_q_scratch.dtype != torch.int8:
             raise InvalidProblem("act_q_scratch must be int8")
+        d = self.desc
+        if self.fused_decode_ok(args):
+            # decode: quantiser and GEMV in one kernel; the scales still land in act_scale_scratch
+            _need(args.activation, _span(d.m, d.k, d.k), "activation")
+            _need(args.weight_q, _span(d.c_out, d.k, d.k), "weight_q")
+            _need(args.weight_scale, d.c_out, "weight_scale")
+            _need(args.act_scale_scratch, d.m, "act_scale_scratch")
+            _need(args.output, _span(d.m, d.c_out, d.c_out), "output")
+            st = _lib.load().baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
+                d.m, d.c_out, d.k, d.q_min, d.q_max, 1.0, 0.0, _ptr(args.activation), d.k, _ptr(args.weight_q), d.k,
+                _ptr(args.weight_scale), _ptr(args.act_scale_scratch), _ptr(args.output), d.c_out, None, 0,
+                _stream_ptr(stream))
+            status_to_result(st, "QuantizedLinearPlan")
+            return
         self._quant.run(stream, args.activation, args.act_scale_scratch, args.act_q_scratch)
         if isinstance(self._mm, GemvQ8Plan):
             self._mm.run(stream, workspace, GemvQ8Args(a=args.act_q_scratch, b=args.weight_q, d=args.output,

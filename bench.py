@@ -228,6 +228,31 @@ def side_workloads(peaks: dict) -> dict:
                     "us": tp * 1e6, "GBps": byts / tp / 1e9, "frac_of_hbm_peak": byts / tp / 1e9 / peaks["hbm_gbs"]}
         del weights
 
+    # the whole decode step from bf16 activations: per-token quantiser + GEMV as two launches, and fused into one
+    weights = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device="cuda", generator=g) for _ in range(nbuf)]
+    for m in (1, 4):
+        xb = torch.randn((m, k), device="cuda", generator=g).to(torch.bfloat16)
+        sb = torch.rand(n, device="cuda", generator=g)
+        d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        lin = bq.QuantizedLinearPlan.select(None, bq.QuantizedLinearDescriptor(m, n, k))
+        mk = lambda x, w: bq.QuantizedLinearArgs(activation=x, weight_q=w, weight_scale=sb, output=d,
+                                                 act_q_scratch=torch.empty((m, k), dtype=torch.int8, device="cuda"),
+                                                 act_scale_scratch=torch.empty(m, device="cuda"))
+        fused_args = [mk(xb, w) for w in weights]
+        split_args = [mk(xb.to(torch.float32), w) for w in weights]  # f32 activations take the two-launch path
+        byts = k * n + m * k * 2 + n * 4 + m * n * 2
+        for name, argl in (("fused", fused_args), ("two_launches", split_args)):
+            launchers = [(lambda i=i: lin.run(None, None, argl[i % nbuf])) for i in range(2 * nbuf)]
+            for pdl in (0, 1):
+                bq.set_tuning(3, pdl)
+                try:
+                    t = graph_launch_ms(launchers) * 1e-3
+                finally:
+                    bq.set_tuning(3, 0)
+                out[f"decode_step_m{m}_{name}" + ("_pdl" if pdl else "")] = {
+                    "us": t * 1e6, "GBps": byts / t / 1e9, "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
+    del weights
+
     def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False):
         gen = torch.Generator(device="cuda")
         gen.manual_seed(m + n + k)

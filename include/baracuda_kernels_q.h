@@ -335,6 +335,25 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run(
     void* stream);
 size_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_capacity(void);
 
+/* Decode step in one launch: the per-token quantiser of QuantizedLinearPlan's first launch
+ * (dynamic_range_quantize_per_token_symmetric_kernel, crates/baracuda-kernels-sys/kernels/include/
+ * baracuda_quantize_compose.cuh:144-201) runs inside the GEMV.  x is bf16 [m, ldx] (m <= 8), b the int8 weight
+ * [N, K] (K contiguous), scale_b float[N]; every CTA derives scale_a[r] = absmax(x[r,:]) / qmax (1.0 for a zero row),
+ * quantises the activation fragments it needs with q = clamp(rint_even(x * (1/scale_a)), qmin, qmax) and the result is
+ *     D = bf16( alpha * (scale_a[r]*scale_b[j]) * sum_k q[r,k] * b[j,k] + beta * D )
+ * -- the bits of quantize_per_token_sym_bf16_s8 followed by gemv_q8_m1_bf16.  scale_a_out (float[m]) receives the
+ * scales when not NULL.  Served shapes: K a multiple of 512 with 16 % (K / 512) == 0 (512 ... 8192), ldx a multiple of
+ * 8, ldb a multiple of 16, 16-byte aligned x and b; anything else returns status 3 from can_implement / run and the
+ * caller takes the two-launch path.  No workspace. */
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
+    int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax,
+    float alpha, float beta,
+    const void* x_bf16, int64_t ldx, const void* b, int64_t ldb, const void* scale_b,
+    void* scale_a_out, void* d, int64_t ldd,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(
+    int32_t m, int32_t n, int32_t k, int64_t ldx, int64_t ldb, int64_t ldd);
+
 /* The int32 sums of the same GEMV (D is int32); alpha 1, beta 0, no scales. */
 int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,

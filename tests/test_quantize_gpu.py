@@ -84,3 +84,44 @@ def test_quantized_linear_two_launch_path(oracle, m):
     full = a @ w.T
     got = out.to(torch.float32).cpu().numpy()
     assert np.linalg.norm(got - full) / np.linalg.norm(full) < 0.03
+
+
+@pytest.mark.parametrize("m", [1, 2, 5, 8])
+@pytest.mark.parametrize("nk", [(1024, 2048), (14336, 4096), (1000, 512), (4096, 8192)])
+def test_decode_step_in_one_launch(oracle, m, nk):
+    """bf16 activations, m <= 8: the per-token quantiser runs inside the GEMV.  The output and the scales must equal
+    the two-launch path (quantize_per_token_sym_bf16_s8, then gemv_q8_m1_bf16) and the oracle bit for bit."""
+    c_out, k = nk
+    rng = np.random.default_rng(m * 31 + k)
+    a_bf = torch.from_numpy(rng.standard_normal((m, k)).astype(np.float32)).to(torch.bfloat16)
+    if m >= 5:
+        a_bf[m - 1].zero_()  # an all-zero token: scale 1.0
+    a = a_bf.to(torch.float32).numpy()
+    w = (rng.standard_normal((c_out, k)) * 0.02).astype(np.float32)
+    wq, sw = oracle.quantize_rows_s8(w)
+    aq, sa = oracle.quantize_rows_s8(a)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, c_out, k), sa, sw)
+    plan = bq.QuantizedLinearPlan.select(None, bq.QuantizedLinearDescriptor(m, c_out, k))
+    out = torch.full((m, c_out), float("nan"), dtype=torch.bfloat16, device="cuda")
+    scales = torch.full((m,), float("nan"), device="cuda")
+    args = bq.QuantizedLinearArgs(activation=a_bf.cuda(), weight_q=dev(wq), weight_scale=dev(sw), output=out,
+                                  act_q_scratch=torch.empty((m, k), dtype=torch.int8, device="cuda"),
+                                  act_scale_scratch=scales)
+    assert plan.fused_decode_ok(args)
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    plan.run(None, ws, args)
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert np.array_equal(scales.cpu().numpy(), sa)
+    assert np.array_equal(bf16_bits(out), want)
+
+
+def test_decode_fusion_declines_other_shapes():
+    from baracuda_b200 import _lib
+    can = _lib.load().baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement
+    assert can(1, 14336, 4096, 4096, 4096, 14336) == 0
+    assert can(1, 4096, 14336, 14336, 14336, 4096) == 3   # 28 chunks of 512 do not divide 16
+    assert can(1, 1024, 4096 + 64, 4096 + 64, 4096 + 64, 1024) == 3
+    assert can(9, 1024, 4096, 4096, 4096, 1024) == 2
+    assert can(1, 1024, 4096, 4000, 4096, 1024) == 2      # ldx < k
+    assert can(0, 1024, 4096, 4096, 4096, 1024) == 0
