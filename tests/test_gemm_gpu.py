@@ -292,3 +292,25 @@ def test_row_major_weights_rrr(oracle, shape):
     torch.cuda.synchronize()
     assert bq.device_status() == 0
     assert oracle.compare_bitexact(oracle.scale_f32_bf16(ref8, one, one), bf16_bits(o8)) == -1
+
+
+def test_default_dispatch_over_random_shapes(oracle):
+    """Seeded random shapes on both sides of every dispatch rule (1-CTA tile widths, CTA-pair kernel from 24 pair tiles
+    up, ragged M / N, K down to one 16-byte row): the int32 accumulators of the default path equal the oracle's."""
+    from baracuda_b200 import _lib
+    lib = _lib.load()
+    rng = np.random.default_rng(20260)
+    shapes = [(int(rng.integers(1, 2200)), int(rng.integers(16, 3100)), int(rng.integers(1, 129)) * 16) for _ in range(14)]
+    shapes += [(512, 6144, 256), (511, 6144, 256), (768, 2048, 512), (1024, 1536, 64)]
+    for m, n, k in shapes:
+        a = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+        b = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        want = oracle.gemm_s8_s32(a, b, oracle.RCR, m, n, k)
+        ad, bd = dev(a), dev(b)
+        d = torch.full((m, n), -5, dtype=torch.int32, device="cuda")
+        st = lib.baracuda_kernels_gemm_s8_rcr_s32_sm100a_run(m, n, k, ad.data_ptr(), k, bd.data_ptr(), k, None, 0, d.data_ptr(), n,
+                                                              1.0, 0.0, None, 0, torch.cuda.current_stream().cuda_stream)
+        assert st == 0, (m, n, k)
+        torch.cuda.synchronize()
+        assert lib.baracuda_kernels_q_device_status() == 0
+        assert np.array_equal(d.cpu().numpy(), want), (m, n, k)
