@@ -398,13 +398,18 @@ __device__ __forceinline__ void mma_s8_16x8x32_top(int& c0, int& c1, uint32_t a0
 // scale = absmax / qmax (1.0 for a zero row) and quantises just the fragments its warps keep, with the arithmetic of
 // quantize_rows_kernel (multiply by the f32 reciprocal, round half to even, clamp), so the result equals the
 // two-kernel path bit for bit and one launch disappears from the decode step.
-template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING, bool XREG = false, bool XQ = false>
+// XSETS (with XREG): 1 when the number of K chunks divides the number of warps; 2 when it is twice the number of warps, so
+// that a warp alternates between two K chunks and keeps two sets of fragments.
+template <bool RAW, int MMA_KCHUNK, int MMA_WARPS, int MMA_RING, bool XREG = false, bool XQ = false, int XSETS = 1>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 1)
 gemv_q8_rcr_mma_kernel(const GemvParams p) {
-    static_assert(!XQ || XREG, "the fused quantiser fills register fragments");
+    static_assert(!XQ || (XREG && XSETS == 1), "the fused quantiser fills one set of register fragments");
+    static_assert(XSETS == 1 || XSETS == 2, "one or two K chunks per warp");
     __shared__ float xq_red[XQ ? MMA_WARPS * 8 : 1];
     __shared__ float xq_scale[8];
-    constexpr int MMA_PITCH = MMA_KCHUNK + 64;
+    // row pitch in the ring chosen so that the 16-byte reads of a quarter-warp (two rows x four pieces) cover all banks
+    // (pitch = 64 mod 128 bytes: the two rows of a quarter-warp start 16 banks apart)
+    constexpr int MMA_PITCH = (MMA_KCHUNK % 128 == 64) ? MMA_KCHUNK : MMA_KCHUNK + 64;
     constexpr int MMA_ITEM_BYTES = MMA_COLS * MMA_PITCH;
     extern __shared__ __align__(128) uint8_t mma_smem[];
     const int warp = threadIdx.x >> 5;
@@ -475,7 +480,7 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
 
     // activations into shared memory (rows beyond m are zero) or, XREG, this warp's K chunk of activation row gq
     // straight into registers in fragment order; accumulators cleared
-    uint4 xreg[XREG ? MMA_KCHUNK / 64 : 1];
+    uint4 xreg[XREG ? XSETS : 1][XREG ? MMA_KCHUNK / 64 : 1];
     uint4 xraw[XQ ? 8 : 1][2];  // XQ: 16 bf16 values of every activation row, until the row scales are known
     {
         if constexpr (XQ) {
@@ -505,11 +510,14 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
                 if (lane == 0) xq_red[warp * 8 + r] = amax;
             }
         } else if constexpr (XREG) {
-            const int k0 = (warp % chunks) * MMA_KCHUNK;
 #pragma unroll
-            for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
-                xreg[i] = gq < p.m ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(gq) * p.lda + k0 + i * 64 + tq * 16))
-                                   : make_uint4(0, 0, 0, 0);
+            for (int xs_i = 0; xs_i < XSETS; ++xs_i) {
+                const int k0 = ((warp + xs_i * MMA_WARPS) % chunks) * MMA_KCHUNK;
+#pragma unroll
+                for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
+                    xreg[xs_i][i] = gq < p.m ? __ldg(reinterpret_cast<const uint4*>(a + static_cast<int64_t>(gq) * p.lda + k0 + i * 64 + tq * 16))
+                                             : make_uint4(0, 0, 0, 0);
+                }
             }
         } else {
             const int k16 = p.k >> 4;
@@ -566,7 +574,7 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
-            xreg[i] = gq < p.m ? *reinterpret_cast<const uint4*>(stage + gq * MMA_KCHUNK + i * 64 + tq * 16) : make_uint4(0, 0, 0, 0);
+            xreg[0][i] = gq < p.m ? *reinterpret_cast<const uint4*>(stage + gq * MMA_KCHUNK + i * 64 + tq * 16) : make_uint4(0, 0, 0, 0);
         }
         __syncwarp();  // the staging area is free: it becomes the ring's last slot
         if (MMA_RING - 1 < my_items) issue(MMA_RING - 1);
@@ -598,12 +606,17 @@ gemv_q8_rcr_mma_kernel(const GemvParams p) {
             for (int i = 0; i < MMA_KCHUNK / 64; ++i) w[i] = *reinterpret_cast<const uint4*>(wrow + i * 64);
             __syncwarp();
             if (mine + MMA_RING < my_items) issue(mine + MMA_RING);
+            const bool second = XSETS == 2 && (mine & 1);  // which of the warp's K chunks this item belongs to
 #pragma unroll
-            for (int i = 0; i < MMA_KCHUNK / 64; i += 2) {
-                mma_s8_16x8x32(d, xreg[i].x, xreg[i].y, w[i].x, w[i].y);
-                mma_s8_16x8x32(d1, xreg[i].z, xreg[i].w, w[i].z, w[i].w);
-                mma_s8_16x8x32(d2, xreg[i + 1].x, xreg[i + 1].y, w[i + 1].x, w[i + 1].y);
-                mma_s8_16x8x32(d3, xreg[i + 1].z, xreg[i + 1].w, w[i + 1].z, w[i + 1].w);
+            for (int i = 0; i < MMA_KCHUNK / 64; ++i) {
+                const uint4 x = second ? xreg[XSETS - 1][i] : xreg[0][i];
+                if (i & 1) {
+                    mma_s8_16x8x32(d2, x.x, x.y, w[i].x, w[i].y);
+                    mma_s8_16x8x32(d3, x.z, x.w, w[i].z, w[i].w);
+                } else {
+                    mma_s8_16x8x32(d, x.x, x.y, w[i].x, w[i].y);
+                    mma_s8_16x8x32(d1, x.z, x.w, w[i].z, w[i].w);
+                }
             }
         } else {
 #pragma unroll 2
@@ -1147,13 +1160,13 @@ size_t mma_smem_bytes(int kchunk, int warps, int ring, int m, int k, int groups)
            static_cast<size_t>(groups) * 64 * 4 + static_cast<size_t>(groups) * MMA_COLS * 4 + warps * ring * 8 + warps * 4 + 16;
 }
 
-template <bool RAW, int KCHUNK, int WARPS, int RING, bool XREG = false, bool XQ = false>
+template <bool RAW, int KCHUNK, int WARPS, int RING, bool XREG = false, bool XQ = false, int XSETS = 1>
 int32_t launch_rcr_mma_cfg(GemvParams p, int batch, int sms, cudaStream_t stream) {
     const int want = (p.n + MMA_COLS - 1) / MMA_COLS;  // no more CTAs than 8-column groups
     const int ctas = want < sms ? want : sms;
     p.mma_groups = (want + ctas - 1) / ctas;
     const size_t smem = mma_smem_bytes(KCHUNK, WARPS, RING, XREG ? 0 : p.m, p.k, p.mma_groups);
-    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING, XREG, XQ>;
+    auto kern = gemv_q8_rcr_mma_kernel<RAW, KCHUNK, WARPS, RING, XREG, XQ, XSETS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -1175,6 +1188,23 @@ int32_t launch_rcr_mma_cfg(GemvParams p, int batch, int sms, cudaStream_t stream
     return BQ_STATUS_OK;
 }
 
+// Which register-activation configuration serves this K on sixteen warps: 1 = 512-byte chunks, a divisor of 16 of them
+// (K = 512 .. 8192); 2 = 32 chunks of 512 (K = 16384) and 3 = 32 chunks of 448 (K = 14336), two chunks per warp;
+// 4 = 16 chunks of 448 (K = 7168); 0 = none.
+int mma_xreg_config(const GemvParams& p) {
+    const int sms = sm_count_cached();
+    if (sms <= 0) return 0;
+    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
+    const int ctas = want < sms ? want : sms;
+    const int groups = (want + ctas - 1) / ctas;
+    if (groups > MMA_MAX_GROUPS || mma_smem_bytes(512, 16, 3, 0, p.k, groups) > 232448) return 0;
+    if (p.k % 512 == 0 && 16 % (p.k / 512) == 0) return 1;
+    if (p.k == 32 * 512) return 2;
+    if (p.k == 32 * 448) return 3;
+    if (p.k == 16 * 448) return 4;
+    return 0;
+}
+
 template <bool RAW>
 int32_t launch_rcr_mma(const GemvParams& p, int batch, int shape_variant, cudaStream_t stream) {
     const int sms = sm_count_cached();
@@ -1188,10 +1218,14 @@ int32_t launch_rcr_mma(const GemvParams& p, int batch, int shape_variant, cudaSt
     // 35: 512-byte copies on 16 warps, three items in flight, activations in registers -- when K is a whole number of
     // 512-byte chunks that divides 16 (K = 512, 1024, 2048, 4096, 8192)
     // (the default where it applies: 13.3 us against 16.5 us at m = 2..8, K = 4096, N = 14336; 36 keeps it off)
-    if ((shape_variant == 35 || shape_variant == 0 || shape_variant == 3) && p.k % 512 == 0 && 16 % (p.k / 512) == 0 &&
-        mma_smem_bytes(512, 16, 3, 0, p.k, groups) <= 232448) {
-        return launch_rcr_mma_cfg<RAW, 512, 16, 3, true>(p, batch, sms, stream);
+    switch ((shape_variant == 35 || shape_variant == 0 || shape_variant == 3) ? mma_xreg_config(p) : 0) {
+        case 1: return launch_rcr_mma_cfg<RAW, 512, 16, 3, true>(p, batch, sms, stream);
+        case 2: return launch_rcr_mma_cfg<RAW, 512, 16, 3, true, false, 2>(p, batch, sms, stream);
+        case 3: return launch_rcr_mma_cfg<RAW, 448, 16, 3, true, false, 2>(p, batch, sms, stream);
+        case 4: return launch_rcr_mma_cfg<RAW, 448, 16, 3, true>(p, batch, sms, stream);
+        default: break;
     }
+    if (p.k > MMA_MAX_K) return BQ_STATUS_UNSUPPORTED;  // the staged-activation configurations below hold all of K in shared memory
     // otherwise: 1 KiB copies on 8 warps, two items in flight per warp (a third measured no faster)
     if (shape_variant == 34 && mma_smem_bytes(1024, 8, 3, p.m, p.k, groups) <= 232448) {
         return launch_rcr_mma_cfg<RAW, 1024, 8, 3>(p, batch, sms, stream);
@@ -1207,7 +1241,7 @@ bool mma_gemv_ok(const GemvParams& p) {
     const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
     const int ctas = want < sms ? want : sms;
     const int per_cta = (want + ctas - 1) / ctas;
-    return (p.k % 64 == 0) && p.k <= MMA_MAX_K && per_cta <= MMA_MAX_GROUPS;
+    return (p.k % 64 == 0) && (p.k <= MMA_MAX_K || mma_xreg_config(p) != 0) && per_cta <= MMA_MAX_GROUPS;
 }
 
 template <int MR, bool RAW>
@@ -1373,10 +1407,13 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     }
     // K-contiguous weights, two or more activation rows: tensor-core streaming kernel
     // (variant 3 forces it also for m == 1, variant 2 and 1 keep it off)
-    if (g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
+    // (K beyond the activation staging area is only served by the register-activation configurations: variants 0, 3, 35)
+    const bool mma_ok = g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
+                        (g.k <= MMA_MAX_K || g.variant == 0 || g.variant == 3 || g.variant == 35);
+    if (mma_ok &&
         ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3 ||
          (g.variant >= 31 && g.variant <= 36) ||  // 31..36 force a copy-size / ring configuration
-         (g.variant == 0 && g.m == 1 && g.pdl && g.k % 512 == 0 && 16 % (g.k / 512) == 0 &&
+         (g.variant == 0 && g.m == 1 && g.pdl && mma_xreg_config(p) != 0 &&
           g.n * static_cast<int64_t>(g.k) >= (1 << 20)))) {  // dependent launch: the 16-warp tensor-core kernel also wins at m = 1
         return launch_rcr_mma<RAW>(p, g.batch, g.variant, stream);
     }

@@ -228,6 +228,28 @@ def side_workloads(peaks: dict) -> dict:
                     "us": tp * 1e6, "GBps": byts / tp / 1e9, "frac_of_hbm_peak": byts / tp / 1e9 / peaks["hbm_gbs"]}
         del weights
 
+    # the down projection of the same model in decode: K = 14336, N = 4096 (same 56 MiB of weights, K-contiguous)
+    n2, k2 = 4096, 14336
+    weights = [torch.randint(-127, 128, (n2 * k2,), dtype=torch.int8, device="cuda", generator=g) for _ in range(nbuf)]
+    for m in (1, 4):
+        x = torch.randint(-127, 128, (m, k2), dtype=torch.int8, device="cuda", generator=g)
+        sa = torch.rand(m, device="cuda", generator=g)
+        sb = torch.rand(n2, device="cuda", generator=g)
+        d = torch.empty((m, n2), dtype=torch.bfloat16, device="cuda")
+        plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n2, k2, layout=bq.LayoutSku.Rcr))
+        argl = [bq.GemvQ8Args(a=x, b=w, d=d, scale_a=sa, scale_b=sb) for w in weights]
+        launchers = [(lambda i=i: plan.run(None, None, argl[i % nbuf])) for i in range(2 * nbuf)]
+        byts = k2 * n2 + m * k2 + m * 4 + n2 * 4 + m * n2 * 2
+        for pdl in (0, 1):
+            bq.set_tuning(3, pdl)
+            try:
+                t = graph_launch_ms(launchers) * 1e-3
+            finally:
+                bq.set_tuning(3, 0)
+            out[f"gemv_rcr_k14336_n4096_m{m}" + ("_pdl" if pdl else "")] = {
+                "us": t * 1e6, "GBps": byts / t / 1e9, "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
+    del weights
+
     # the whole decode step from bf16 activations: per-token quantiser + GEMV as two launches, and fused into one
     weights = [torch.randint(-127, 128, (n * k,), dtype=torch.int8, device="cuda", generator=g) for _ in range(nbuf)]
     for m in (1, 4):

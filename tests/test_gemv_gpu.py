@@ -304,3 +304,23 @@ def test_graph_capture_and_replay(oracle, layout):
         want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
         assert np.array_equal(bf16_bits(d), want)
     assert bq.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(2, 1024, 14336), (8, 4096, 14336), (3, 520, 16384), (4, 1000, 7168), (1, 2048, 14336)])
+def test_k_contiguous_weights_long_k(oracle, shape):
+    """K = 14336 / 16384 (two K chunks per warp in the register-activation kernel) and 7168 (448-byte chunks), with and
+    without dependent launch (which also routes m = 1 to that kernel)."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=n + k + m)
+    acc = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+    want = oracle.dequant_s32_bf16(acc, sa, sb)
+    for pdl in (0, 1):
+        bq.set_tuning(3, pdl)
+        try:
+            got_raw = _run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=True).cpu().numpy()
+            got = bf16_bits(_run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=False))
+        finally:
+            bq.set_tuning(3, 0)
+        assert bq.device_status() == 0
+        assert np.array_equal(got_raw, acc), (shape, pdl)
+        assert np.array_equal(got, want), (shape, pdl)
