@@ -39,28 +39,53 @@ struct GemmParams {
     const void* bias;
     int bias_kind;  // 0 none, 1 float[N], 2 int32[N]
     int act;        // 0 none, 1 relu, 2 gelu (erf form), 3 silu
+    int bias_off;   // the epilogue warp's staged bias values sit bias_off floats after its staged column scales
     // raw-accumulator reduce-scatter (K-sharded GEMM): output row r belongs to rank r / rs_rows and is stored
     // into that rank's staging buffer peer_d[owner], slot peer_rank, row r % rs_rows (row pitch ldd); 0 = off
     int rs_world;
     int rs_rows;
 };
 
-// bias[col] then activation, in f32 — the formulas of the reference's epilogue header
-// (crates/baracuda-kernels-sys/kernels/include/baracuda_epilogue_int8.cuh:52-95).
-__device__ __forceinline__ float apply_bias_act(const GemmParams& p, float z, int col) {
-    if (p.bias_kind == 1) {
-        z = __fadd_rn(z, __ldg(reinterpret_cast<const float*>(p.bias) + col));
-    } else if (p.bias_kind == 2) {
-        z = __fadd_rn(z, static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col)));
+// bias then activation on 32 values, in f32 — the chain of the reference's epilogue header
+// (crates/baracuda-kernels-sys/kernels/include/baracuda_epilogue_int8.cuh:52-95).  The bias values come from the
+// warp's shared-memory copy (staged once per tile next to the column scales).
+// gelu = 0.5 z (1 + erf(z / sqrt 2)) with erf from the Abramowitz-Stegun 7.1.26 polynomial (|error| <= 1.5e-7, the
+// form the reference's own CPU check uses, crates/baracuda-kernels/tests/int8_rrr_smoke.rs:35-53) and
+// silu = z / (1 + exp(-z)) with the fast exponential and division: a dozen instructions each.  The library erff and an
+// IEEE division, inlined once per accumulator (32 copies per 32-column block), grew the epilogue loop beyond the
+// instruction cache and halved the speed even of launches that never ran them (8-bit-out GEMM 8192 x 8192 x 4096:
+// 404 us against 184 us for the bf16 SKU); called out of line they cost 3-6x the identity epilogue.  The results stay
+// inside the reference's tolerance for these two chains (+-1 output code, two e4m3 grid steps).
+__device__ __forceinline__ float gelu_erf_poly(float z) {
+    const float x = z * 0.70710678118654752440f;
+    const float ax = fabsf(x);
+    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    float poly = fmaf(1.061405429f, t, -1.453152027f);
+    poly = fmaf(poly, t, 1.421413741f);
+    poly = fmaf(poly, t, -0.284496736f);
+    poly = fmaf(poly, t, 0.254829592f);
+    const float erf_abs = fmaf(-poly * t, __expf(-ax * ax), 1.0f);
+    return 0.5f * z * (1.0f + copysignf(erf_abs, x));
+}
+
+__device__ __forceinline__ float silu_fast(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
+
+__device__ __forceinline__ void apply_bias_act_32(const GemmParams& p, float (&z)[32], const float* sb32) {
+    if (p.bias_kind != 0) {
+        const float* bias32 = sb32 + p.bias_off;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = __fadd_rn(z[j], bias32[j]);
     }
     if (p.act == 1) {
-        z = fmaxf(z, 0.0f);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = fmaxf(z[j], 0.0f);
     } else if (p.act == 2) {
-        z = 0.5f * z * (1.0f + erff(z * 0.70710678118654752440f));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = gelu_erf_poly(z[j]);
     } else if (p.act == 3) {
-        z = z / (1.0f + __expf(-z));
+#pragma unroll
+        for (int j = 0; j < 32; ++j) z[j] = silu_fast(z[j]);
     }
-    return z;
 }
 
 // One thread, one output row, 32 consecutive columns starting at col0 (a multiple of 32).
@@ -94,6 +119,40 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
         uint8_t* drow = reinterpret_cast<uint8_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
         const uint8_t* crow =
             p.c ? reinterpret_cast<const uint8_t*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0 : nullptr;
+        float z[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if constexpr (KIND == UMMA_KIND_I8) {
+                z[j] = __fmul_rn(p.alpha, static_cast<float>(static_cast<int32_t>(r[j])));
+            } else {
+                z[j] = __fmul_rn(p.alpha, __uint_as_float(r[j]));
+            }
+        }
+        if (crow) {
+            uint8_t cb[32];
+            if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
+                const uint4 lo = __ldg(reinterpret_cast<const uint4*>(crow));
+                const uint4 hi = __ldg(reinterpret_cast<const uint4*>(crow) + 1);
+                const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                for (int j = 0; j < 32; ++j) cb[j] = static_cast<uint8_t>(w[j >> 2] >> (8 * (j & 3)));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) cb[j] = col0 + j < p.n ? crow[j] : 0;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                float cv;
+                if constexpr (KIND == UMMA_KIND_I8) {
+                    cv = static_cast<float>(static_cast<int8_t>(cb[j]));
+                } else {
+                    const __half_raw hr = __nv_cvt_fp8_to_halfraw(cb[j], __NV_E4M3);
+                    cv = __half2float(__half(hr));
+                }
+                z[j] = __fadd_rn(z[j], __fmul_rn(p.beta, cv));
+            }
+        }
+        if ((p.bias_kind | p.act) != 0) apply_bias_act_32(p, z, sb32);
         uint32_t packed[8];
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
@@ -101,25 +160,13 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const int j = 4 * w + b;
-                float z;
                 uint8_t out;
                 if constexpr (KIND == UMMA_KIND_I8) {
-                    z = __fmul_rn(p.alpha, static_cast<float>(static_cast<int32_t>(r[j])));
-                    if (crow && col0 + j < p.n) {
-                        z = __fadd_rn(z, __fmul_rn(p.beta, static_cast<float>(static_cast<int8_t>(crow[j]))));
-                    }
-                    if ((p.bias_kind | p.act) != 0 && col0 + j < p.n) z = apply_bias_act(p, z, col0 + j);
-                    int q = __float2int_rn(z);
+                    int q = __float2int_rn(z[j]);
                     q = q < -128 ? -128 : (q > 127 ? 127 : q);
                     out = static_cast<uint8_t>(static_cast<int8_t>(q));
                 } else {
-                    z = __fmul_rn(p.alpha, __uint_as_float(r[j]));
-                    if (crow && col0 + j < p.n) {
-                        const __half_raw hr = __nv_cvt_fp8_to_halfraw(crow[j], __NV_E4M3);
-                        z = __fadd_rn(z, __fmul_rn(p.beta, __half2float(__half(hr))));
-                    }
-                    if ((p.bias_kind | p.act) != 0 && col0 + j < p.n) z = apply_bias_act(p, z, col0 + j);
-                    out = static_cast<uint8_t>(__nv_cvt_float_to_fp8(z, __NV_SATFINITE, __NV_E4M3));
+                    out = static_cast<uint8_t>(__nv_cvt_float_to_fp8(z[j], __NV_SATFINITE, __NV_E4M3));
                 }
                 word |= static_cast<uint32_t>(out) << (8 * b);
             }
@@ -150,12 +197,7 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
             const float s = __fmul_rn(sa_row, sb32[j]);
             y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
         }
-        if ((p.bias_kind | p.act) != 0) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                if (col0 + j < p.n) y[j] = apply_bias_act(p, y[j], col0 + j);
-            }
-        }
+        if ((p.bias_kind | p.act) != 0) apply_bias_act_32(p, y, sb32);
         uint4 pk[4];
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -216,10 +258,7 @@ __device__ __forceinline__ void dequant_pack_32(const GemmParams& p, const uint3
         const float s = __fmul_rn(sa_row, sb32[j]);
         y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
     }
-    if ((p.bias_kind | p.act) != 0) {  // the staged path only runs on full, in-range blocks
-#pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = apply_bias_act(p, y[j], col0 + j);
-    }
+    if ((p.bias_kind | p.act) != 0) apply_bias_act_32(p, y, sb32);
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
         __nv_bfloat162 h0 = __floats2bfloat162_rn(y[8 * v + 0], y[8 * v + 1]);

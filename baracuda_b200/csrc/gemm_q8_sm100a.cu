@@ -50,7 +50,7 @@ struct Smem {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
     static constexpr int STG_BYTES = 4 * 4096;        // per epilogue warp: 32 rows x 128 bytes of output staging
-    static constexpr int SB_BYTES = STG_BYTES + 4 * BLOCK_N * 4;  // + one private copy of the column scales per epilogue warp
+    static constexpr int SB_BYTES = STG_BYTES + 2 * 4 * BLOCK_N * 4;  // + private copies of the column scales and of the bias per epilogue warp
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
     static constexpr int TOTAL = TILE_BYTES + SB_BYTES + BAR_BYTES + 1024;  // + alignment slack
     static constexpr int TMEM_COLS = (2 * BLOCK_N <= 32) ? 32 : (2 * BLOCK_N <= 64) ? 64
@@ -188,11 +188,17 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // each warp stages its own copy of this tile's column scales, so the
             // epilogue warps never have to meet at a barrier
             float* sb_tile = sb_s + (warp - 2) * BLOCK_N;
-            if (!RAW && !p.out_q8) {
+            if (!RAW && (!p.out_q8 || p.bias_kind != 0)) {
                 __syncwarp();
                 for (int i = lane; i < BLOCK_N; i += 32) {
                     const int col = n_blk * BLOCK_N + i;
-                    sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                    if (!p.out_q8) sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                    if (p.bias_kind == 1) {
+                        sb_tile[p.bias_off + i] = col < p.n ? __ldg(reinterpret_cast<const float*>(p.bias) + col) : 0.0f;
+                    } else if (p.bias_kind == 2) {
+                        sb_tile[p.bias_off + i] =
+                            col < p.n ? static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col)) : 0.0f;
+                    }
                 }
                 __syncwarp();
             }
@@ -343,6 +349,7 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.bias = g.bias;
     p.bias_kind = g.bias ? g.bias_kind : 0;
     p.act = g.act;
+    p.bias_off = 4 * BLOCK_N;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;

@@ -41,7 +41,7 @@ constexpr int W_BH_BYTES = W_CTA_ROWS * W_BLOCK_K;       // one half's weight ro
 constexpr int W_STAGE_BYTES = W_A_BYTES + 2 * W_BH_BYTES;  // 48 KiB
 constexpr int W_TILE_BYTES = W_STAGES * W_STAGE_BYTES;
 constexpr int W_STG_BYTES = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes of output staging
-constexpr int W_SB_BYTES = W_STG_BYTES + 4 * W_TILE_N * 4;
+constexpr int W_SB_BYTES = W_STG_BYTES + 2 * 4 * W_TILE_N * 4;  // column scales and bias, one private copy per epilogue warp
 constexpr int W_BAR_BYTES = (2 * W_STAGES + 4) * 8 + 16;
 constexpr int W_SMEM_TOTAL = W_TILE_BYTES + W_SB_BYTES + W_BAR_BYTES + 1024;
 constexpr int W_TMEM_COLS = 512;
@@ -209,11 +209,17 @@ gemm_q8_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
             float* sb_tile = sb_s + (warp - 2) * W_TILE_N;
-            if (!RAW && !p.out_q8) {
+            if (!RAW && (!p.out_q8 || p.bias_kind != 0)) {
                 __syncwarp();
                 for (int i = lane; i < W_TILE_N; i += 32) {
                     const int col = n_blk * W_TILE_N + i;
-                    sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                    if (!p.out_q8) sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                    if (p.bias_kind == 1) {
+                        sb_tile[p.bias_off + i] = col < p.n ? __ldg(reinterpret_cast<const float*>(p.bias) + col) : 0.0f;
+                    } else if (p.bias_kind == 2) {
+                        sb_tile[p.bias_off + i] =
+                            col < p.n ? static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col)) : 0.0f;
+                    }
                 }
                 __syncwarp();
             }
@@ -306,6 +312,7 @@ int32_t launch_wide(const GemmDesc& g, cudaStream_t stream) {
     p.bias = g.bias;
     p.bias_kind = g.bias ? g.bias_kind : 0;
     p.act = g.act;
+    p.bias_off = 4 * W_TILE_N;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;
