@@ -28,6 +28,9 @@ from .plans import (  # noqa: F401
     SCALE_PER_ROW_COL,
     SCALE_PER_TENSOR,
     Fp8GemmPlan,
+    GatedMlpUpArgs,
+    GatedMlpUpDescriptor,
+    GatedMlpUpPlan,
     Fp8ScaledGemmPlan,
     IntGemmPlan,
     GemvQ8Args,

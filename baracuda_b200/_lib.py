@@ -99,6 +99,17 @@ SIGNATURES: dict[str, tuple] = {
         _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _f32, _vp, _vp, _vp]),
     "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run": (
         _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _vp, _f32, _vp, _vp, _vp]),
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run": (
+        _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _f32] + _TAIL),
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_workspace_size": (_sz, [_i32, _i32, _i32]),
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_can_implement": (
+        _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_run": (
+        _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _vp, _f32] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_workspace_size": (_sz, [_i32, _i32, _i32]),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_can_implement": (
+        _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64]),
+    "baracuda_kernels_q_interleave_gate_up_run": (_i32, [_i64, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _vp]),
     "baracuda_q_nccl_version": (_i32, []),
     "baracuda_q_nccl_unique_id": (_i32, [_vp]),
     "baracuda_q_nccl_comm_init_rank": (_i32, [C.POINTER(_vp), _i32, _vp, _i32]),

@@ -167,6 +167,29 @@ reduce_dequant_broadcast_kernel(const uint32_t* __restrict__ staging, int world,
     }
 }
 
+// Builds the interleaved gate/up operand of the gated-MLP GEMM: output row 64b + i is gate row 32b + i for i < 32 and
+// up row 32b + (i - 32) otherwise.  Rows are `row_bytes` bytes (a weight row of K bytes, or 4 for a scale / bias entry).
+__global__ void __launch_bounds__(256)
+    interleave_gate_up_kernel(const uint8_t* __restrict__ gate, int64_t gate_pitch, const uint8_t* __restrict__ up,
+                              int64_t up_pitch, uint8_t* __restrict__ out, int64_t out_pitch, int64_t f_rows,
+                              int64_t row_bytes, int vec) {
+    const int64_t per_row = vec ? row_bytes / 16 : row_bytes;
+    const int64_t total = 2 * f_rows * per_row;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / per_row;
+        const int64_t x = i - r * per_row;
+        const int64_t blk = r >> 6;
+        const int64_t in = r & 63;
+        const uint8_t* src = in < 32 ? gate + (blk * 32 + in) * gate_pitch : up + (blk * 32 + in - 32) * up_pitch;
+        if (vec) {
+            reinterpret_cast<uint4*>(out + r * out_pitch)[x] = __ldg(reinterpret_cast<const uint4*>(src) + x);
+        } else {
+            out[r * out_pitch + x] = __ldg(src + x);
+        }
+    }
+}
+
 }  // namespace
 
 int32_t launch_reduce_dequant_broadcast(int32_t kind, int32_t rank, int32_t world, int32_t rows, int32_t n,
@@ -225,6 +248,25 @@ int32_t launch_dequant_rows(int32_t kind, int32_t m, int32_t n, const void* acc,
             static_cast<const uint32_t*>(acc), ld_acc, scale_a, scale_b, scale_mode, alpha, bias,
             static_cast<__nv_bfloat16*>(d), ldd, m, n, vec);
     }
+    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+}
+
+int32_t launch_interleave_gate_up(int64_t f_rows, int64_t row_bytes, const void* gate, int64_t gate_pitch, const void* up,
+                                  int64_t up_pitch, void* out, int64_t out_pitch, cudaStream_t stream) {
+    if (f_rows <= 0 || row_bytes <= 0) return BQ_STATUS_OK;
+    const int sms = sm_count_of_current_device();
+    if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
+    const auto a16 = [](const void* p, int64_t pitch) {
+        return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (pitch & 15) == 0;
+    };
+    const int vec = (row_bytes % 16 == 0 && a16(gate, gate_pitch) && a16(up, up_pitch) && a16(out, out_pitch)) ? 1 : 0;
+    const int64_t total = 2 * f_rows * (vec ? row_bytes / 16 : row_bytes);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sms) * 16;
+    if (blocks > cap) blocks = cap;
+    interleave_gate_up_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        static_cast<const uint8_t*>(gate), gate_pitch, static_cast<const uint8_t*>(up), up_pitch,
+        static_cast<uint8_t*>(out), out_pitch, f_rows, row_bytes, vec);
     return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
 }
 

@@ -132,6 +132,57 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
+// Gated-MLP up-projection: weight [n2, K] with gate and up rows interleaved in blocks of 32, D = silu(z_gate) * z_up
+// as bf16 [M, n2 / 2].  No counterpart in the reference (its EpilogueKind has no gated form).
+int32_t gemm_swiglu_validate(int32_t m, int32_t n2, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                             const void* d, int64_t ldd) {
+    if (m < 0 || n2 < 0 || k < 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    const int64_t f = n2 / 2;
+    const int32_t st = gemm_validate(bq::BQ_LAYOUT_RCR, m, n2, k, a, lda, b, ldb, nullptr, 0, d,
+                                       ldd < (f > 0 ? f : 1) ? 0 : INT64_MAX);  // the output has n2 / 2 columns
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (n2 % 64 != 0) return bq::BQ_STATUS_UNSUPPORTED;
+    if ((d && !aligned16(d)) || (m > 1 && (ldd & 7))) return bq::BQ_STATUS_MISALIGNED;
+    return bq::BQ_STATUS_OK;
+}
+
+int32_t gemm_swiglu_run(int32_t kind, int32_t m, int32_t n2, int32_t k, const void* a, int64_t lda, const void* b,
+                        int64_t ldb, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,
+                        const void* bias, float alpha, void* stream) {
+    const int32_t st = gemm_swiglu_validate(m, n2, k, a, lda, b, ldb, d, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (bias && (reinterpret_cast<uintptr_t>(bias) & 3u)) return bq::BQ_STATUS_MISALIGNED;
+    if (k == 0 && bias) return bq::BQ_STATUS_UNSUPPORTED;
+    if (m == 0 || n2 == 0) return bq::BQ_STATUS_OK;
+    if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (!scale_a || !scale_b) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
+        return bq::BQ_STATUS_INVALID_PROBLEM;
+    bq::GemmDesc g = {};
+    g.b_layout = bq::BQ_LAYOUT_RCR;
+    g.kind = kind;
+    g.m = m;
+    g.n = n2;
+    g.k = k;
+    g.a = a;
+    g.lda = lda;
+    g.b = b;
+    g.ldb = ldb;
+    g.scale_a = static_cast<const float*>(scale_a);
+    g.scale_b = static_cast<const float*>(scale_b);
+    g.scale_mode = scale_mode;
+    g.alpha = alpha;
+    g.d = d;
+    g.ldd = ldd;
+    g.bias = bias;
+    g.bias_kind = bias ? 1 : 0;
+    g.swiglu = 1;
+    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
+    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    if (g.force_pair_tile_n % 64 != 0) g.force_pair_tile_n = 0;
+    return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
+}
+
 // The reference's own contract for the 8-bit GEMMs: D has the input type, D = sat(alpha*(A x B) + beta*C).
 int32_t gemm_q8_validate(int32_t layout, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,
                          int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd) {
@@ -346,6 +397,49 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
     return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
+// ---- gated-MLP up-projection: silu(gate) * up -> bf16 ---------------------------------------
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run(
+    int32_t m, int32_t n2, int32_t k, const void* a, int64_t lda, const void* b_gate_up, int64_t ldb, void* d,
+    int64_t ldd, const void* scale_a, const void* scale_b, const void* bias, float alpha, void* workspace,
+    size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_swiglu_run(bq::BQ_KIND_S8, m, n2, k, a, lda, b_gate_up, ldb, d, ldd, scale_a, scale_b,
+                           BARACUDA_Q_SCALE_PER_ROW_COL, bias, alpha, stream);
+}
+size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_can_implement(
+    int32_t m, int32_t n2, int32_t k, const void* a, int64_t lda, const void* b_gate_up, int64_t ldb, const void* d,
+    int64_t ldd) {
+    return gemm_swiglu_validate(m, n2, k, a, lda, b_gate_up, ldb, d, ldd);
+}
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_run(
+    int32_t m, int32_t n2, int32_t k, const void* a, int64_t lda, const void* b_gate_up, int64_t ldb, void* d,
+    int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode, const void* bias, float alpha,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemm_swiglu_run(bq::BQ_KIND_E4M3, m, n2, k, a, lda, b_gate_up, ldb, d, ldd, scale_a, scale_b, scale_mode, bias,
+                           alpha, stream);
+}
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_can_implement(
+    int32_t m, int32_t n2, int32_t k, const void* a, int64_t lda, const void* b_gate_up, int64_t ldb, const void* d,
+    int64_t ldd) {
+    return gemm_swiglu_validate(m, n2, k, a, lda, b_gate_up, ldb, d, ldd);
+}
+int32_t baracuda_kernels_q_interleave_gate_up_run(int64_t f_rows, int64_t row_bytes, const void* gate, int64_t gate_pitch,
+                                                  const void* up, int64_t up_pitch, void* out, int64_t out_pitch,
+                                                  void* stream) {
+    if (f_rows < 0 || row_bytes < 0) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (f_rows == 0 || row_bytes == 0) return bq::BQ_STATUS_OK;
+    if (!gate || !up || !out) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (f_rows % 32 != 0) return bq::BQ_STATUS_UNSUPPORTED;
+    if (gate_pitch < row_bytes || up_pitch < row_bytes || out_pitch < row_bytes) return bq::BQ_STATUS_INVALID_PROBLEM;
+    return bq::launch_interleave_gate_up(f_rows, row_bytes, gate, gate_pitch, up, up_pitch, out, out_pitch,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 // ---- s8 -> s32 accumulators --------------------------------------------------

@@ -44,6 +44,10 @@ struct GemmParams {
     // into that rank's staging buffer peer_d[owner], slot peer_rank, row r % rs_rows (row pitch ldd); 0 = off
     int rs_world;
     int rs_rows;
+    // gated-MLP mode (bf16 output only): the weight rows hold gate and up projections interleaved in blocks of 32
+    // (rows 64b..64b+31 = gate 32b..32b+31, rows 64b+32..64b+63 = up 32b..32b+31), n counts both, and the epilogue
+    // stores silu(gate) * up as n/2 columns
+    int swiglu;
 };
 
 // bias then activation on 32 values, in f32 — the chain of the reference's epilogue header
@@ -360,6 +364,65 @@ __device__ __forceinline__ void epilogue_block_32(const GemmParams& p, uint32_t 
                                               static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
                 }
             }
+        }
+    }
+    __syncwarp();
+}
+
+// Gated-MLP epilogue for one 64-column block of an interleaved gate/up weight: columns col0..col0+31 are 32 gate
+// projections, col0+32..col0+63 the matching up projections; the warp stores h = silu(z_gate) * z_up as 32 bf16
+// columns starting at col0 / 2 (z = alpha * (sa * sb) * acc + bias, as in the plain epilogue).  Rows go through the
+// staging buffer like epilogue_block_32.  Requires the full 64 columns in range and 16-byte-aligned output rows.
+template <uint32_t KIND>
+__device__ __forceinline__ void epilogue_block_64_swiglu(const GemmParams& p, uint32_t t_addr, int row_base, int lane,
+                                                         int col0, float sa_row, const float* sb64, uint4* stage) {
+    float h[32];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(t_addr + static_cast<uint32_t>(half * 32), r);
+        tmem_ld_wait();
+        const float* sb32 = sb64 + half * 32;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            float acc;
+            if constexpr (KIND == UMMA_KIND_I8) {
+                acc = static_cast<float>(static_cast<int32_t>(r[j]));
+            } else {
+                acc = __uint_as_float(r[j]);
+            }
+            const float s = __fmul_rn(sa_row, sb32[j]);
+            float z = __fmul_rn(__fmul_rn(s, acc), p.alpha);
+            if (p.bias_kind != 0) z += sb32[p.bias_off + j];
+            h[j] = half == 0 ? silu_fast(z) : h[j] * z;
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(h[8 * v + 0], h[8 * v + 1]);
+        __nv_bfloat162 h1 = __floats2bfloat162_rn(h[8 * v + 2], h[8 * v + 3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(h[8 * v + 4], h[8 * v + 5]);
+        __nv_bfloat162 h3 = __floats2bfloat162_rn(h[8 * v + 6], h[8 * v + 7]);
+        uint4 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&h0);
+        pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2);
+        pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = pk;
+    }
+    __syncwarp();
+    const int sub_row = lane >> 2;  // 0..7
+    const int c = lane & 3;
+    const int out_col0 = col0 >> 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int rr = i * 8 + sub_row;
+        const int row = row_base + rr;
+        const uint4 v = stage[rr * 4 + (c ^ ((rr >> 1) & 3))];
+        if (row < p.m) {
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.d) + static_cast<int64_t>(row) * p.ldd + out_col0 +
+                                      c * 8) = v;
         }
     }
     __syncwarp();

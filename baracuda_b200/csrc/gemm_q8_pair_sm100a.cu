@@ -235,6 +235,11 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     for (; c + 2 <= PAIR_TILE_N / 32; c += 2) {
                         const int col0 = n_blk * PAIR_TILE_N + c * 32;
                         if (col0 >= p.n) break;  // warp-uniform
+                        if (p.swiglu) {  // launch-uniform; the host guarantees whole 64-column blocks and aligned rows
+                            epilogue_block_64_swiglu<KIND>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
+                                                           sb_tile + c * 32, stage_buf);
+                            continue;
+                        }
                         if (!block_64_ok<FUSED>(p, col0)) break;
                         epilogue_block_64<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
                                                        sb_tile + c * 32, stage_buf);
@@ -325,6 +330,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     p.peer_col0 = g.peer_col0;
     p.peer_rank = g.peer_rank;
     p.rs_world = RAW ? g.rs_world : 0;
+    p.swiglu = (!RAW && !FUSED && !g.q8_out) ? g.swiglu : 0;
     p.rs_rows = g.rs_rows;
     p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
     for (int r = 0; r < 8; ++r) {
@@ -376,6 +382,7 @@ int pick_tile_n(const GemmDesc& g) {
     int best = 256;
     int64_t best_cost = INT64_MAX;
     for (int i = 0; i < 4; ++i) {
+        if (g.swiglu && cand[i] % 64 != 0) continue;  // gate/up blocks of 64 columns must not straddle tiles
         const int64_t tiles = m_tiles * ((g.n + cand[i] - 1) / cand[i]);
         const int64_t waves = (tiles + pairs - 1) / pairs;
         const int64_t cost = waves * (CTA_ROWS + cand[i] / 2);

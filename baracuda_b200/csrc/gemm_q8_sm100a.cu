@@ -222,6 +222,11 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                     for (; c + 2 <= BLOCK_N / 32; c += 2) {
                         const int col0 = n_blk * BLOCK_N + c * 32;
                         if (col0 >= p.n) break;  // warp-uniform
+                        if (p.swiglu) {  // launch-uniform; the host guarantees whole 64-column blocks and aligned rows
+                            epilogue_block_64_swiglu<KIND>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * BLOCK_M + q * 32, lane, col0, sa_row,
+                                                           sb_tile + c * 32, stage_buf);
+                            continue;
+                        }
                         if (!block_64_ok<FUSED>(p, col0)) break;
                         epilogue_block_64<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * BLOCK_M + q * 32, lane, col0, sa_row,
                                                        sb_tile + c * 32, stage_buf);
@@ -356,6 +361,7 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.peer_col0 = g.peer_col0;
     p.peer_rank = g.peer_rank;
     p.rs_world = RAW ? g.rs_world : 0;
+    p.swiglu = (!RAW && !FUSED && !g.q8_out) ? g.swiglu : 0;
     p.rs_rows = g.rs_rows;
     p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
     for (int r = 0; r < 8; ++r) {
@@ -382,7 +388,7 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
     if (g.b_layout == BQ_LAYOUT_RRR) return launch_gemm_q8_pair(g, stream);  // row-major weights: CTA-pair kernel only
-    if (g.force_block_n == 1024) return launch_gemm_q8_wide(g, stream);
+    if (g.force_block_n == 1024 && !g.swiglu) return launch_gemm_q8_wide(g, stream);
     // 256 x 256 tiles on CTA pairs (force_block_n 512 forces it, 256/128/64 forces it off) from 24 such tiles up:
     // measured at M = 512, K = 4096..14336 (32 to 48 tiles) the pair kernel is 1.4-1.7x faster than 128 x 64 tiles
     // on every SM, whose operand traffic per MAC is three times higher; at 16 tiles the narrow tiles still win.
@@ -417,13 +423,14 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
     if (g.k == 0) {
-        const int64_t total = static_cast<int64_t>(g.m) * g.n;
+        const int n_out = (g.swiglu && !g.raw_out) ? g.n / 2 : g.n;  // silu(0) * 0 = 0
+        const int64_t total = static_cast<int64_t>(g.m) * n_out;
         const int blocks = static_cast<int>((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
         if (g.raw_out) {
             fill_zero_kernel<uint32_t><<<blocks, 256, 0, stream>>>(static_cast<uint32_t*>(g.d), g.ldd, g.m, g.n);
         } else {
             fill_zero_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<__nv_bfloat16*>(g.d), g.ldd,
-                                                                        g.m, g.n);
+                                                                        g.m, n_out);
         }
         return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
     }

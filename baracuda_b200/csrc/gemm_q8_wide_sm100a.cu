@@ -319,6 +319,7 @@ int32_t launch_wide(const GemmDesc& g, cudaStream_t stream) {
     p.peer_col0 = g.peer_col0;
     p.peer_rank = g.peer_rank;
     p.rs_world = RAW ? g.rs_world : 0;
+    p.swiglu = 0;
     p.rs_rows = g.rs_rows;
     p.peer_vec = ((g.peer_ld * 2) & 15) == 0 && ((static_cast<int64_t>(g.peer_col0) * 2) & 15) == 0;
     for (int r = 0; r < 8; ++r) {

@@ -56,6 +56,8 @@ struct GemmDesc {
     // raw-accumulator reduce-scatter (raw_out only): row r goes to peer_d[r / rs_rows], slot peer_rank; 0 = off
     int32_t rs_world;
     int32_t rs_rows;
+    // gated-MLP epilogue (bf16 output, weights [N,K] only): n = 2F interleaved gate/up rows in blocks of 32, d is [M, F]
+    int32_t swiglu;
 };
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);
@@ -90,6 +92,9 @@ bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64
 bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k);
 int sm_count_of_current_device();
 // D = bf16((sa*sb) * acc * alpha (+ bias)) for an [m, n] matrix of int32 (BQ_KIND_S8) or f32 (BQ_KIND_E4M3) accumulators.
+// Interleaves gate and up rows in blocks of 32 (the operand layout of GemmDesc::swiglu): rows of `row_bytes` bytes.
+int32_t launch_interleave_gate_up(int64_t f_rows, int64_t row_bytes, const void* gate, int64_t gate_pitch, const void* up,
+                                  int64_t up_pitch, void* out, int64_t out_pitch, cudaStream_t stream);
 int32_t launch_dequant_rows(int32_t kind, int32_t m, int32_t n, const void* acc, int64_t ld_acc, const float* scale_a,
                             const float* scale_b, int32_t scale_mode, float alpha, const float* bias, void* d, int64_t ldd,
                             cudaStream_t stream);

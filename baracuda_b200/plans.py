@@ -576,6 +576,144 @@ class QuantizedLinearPlan:
                                                       scale_a=args.act_scale_scratch, scale_b=args.weight_scale))
 
 
+# --------------------------------------------------------------------------- gated-MLP up-projection
+OP_GATED_MLP_UP = "gemm_gate_up_swiglu"
+
+
+@dataclass(frozen=True)
+class GatedMlpUpDescriptor:
+    """One launch for the first half of a gated MLP: h[M, F] = silu(x Wg^T) * (x Wu^T) from 8-bit operands.
+    `element` is ElementKind.S8 (per-token x per-channel scales) or ElementKind.Fp8E4M3 (scales per `scale_mode`)."""
+    m: int
+    f: int
+    k: int
+    element: ElementKind = ElementKind.S8
+    scale_mode: int = SCALE_PER_ROW_COL
+
+
+@dataclass
+class GatedMlpUpArgs:
+    """`b_gate_up` is the interleaved [2F, K] weight, `scale_b` (and `bias`) the interleaved [2F] vectors built by
+    GatedMlpUpPlan.interleave; `d` is bf16 [M, F]."""
+    a: torch.Tensor
+    b_gate_up: torch.Tensor
+    d: torch.Tensor
+    scale_a: torch.Tensor
+    scale_b: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    lda: Optional[int] = None
+    ldb: Optional[int] = None
+    ldd: Optional[int] = None
+    alpha: float = 1.0
+
+
+class GatedMlpUpPlan:
+    """Gate and up projections plus SiLU-and-multiply in the GEMM epilogue.  The reference's EpilogueKind
+    (crates/baracuda-kernel-vocab/src/layout.rs:69-96) ends at BiasSilu, so there a gated MLP is the GEMM(s) followed
+    by an elementwise pass over [M, 2F]; here that intermediate stays in tensor memory."""
+
+    def __init__(self, desc: GatedMlpUpDescriptor, sku: KernelSku):
+        self.desc = desc
+        self._sku = sku
+        fam = "w8a8_s8" if desc.element is ElementKind.S8 else "fp8_e4m3"
+        self._base = f"baracuda_kernels_gemm_{fam}_rcr_bf16_sm100a_swiglu"
+
+    @classmethod
+    def select(cls, stream, desc: GatedMlpUpDescriptor, pref: PlanPreference = PlanPreference()) -> "GatedMlpUpPlan":
+        _check_backend(pref)
+        if desc.m < 0 or desc.f < 0 or desc.k < 0:
+            raise InvalidProblem("negative dimension")
+        if max(desc.m, 2 * desc.f, desc.k) >= 2**31:
+            raise InvalidProblem("dimension exceeds int32")
+        if desc.element not in (ElementKind.S8, ElementKind.Fp8E4M3):
+            raise Unsupported("gated-MLP up-projection takes s8 or e4m3 operands")
+        if desc.element is ElementKind.S8 and desc.scale_mode != SCALE_PER_ROW_COL:
+            raise InvalidProblem("the s8 SKU takes per-token and per-channel scales")
+        if desc.scale_mode not in (SCALE_PER_TENSOR, SCALE_PER_ROW_COL):
+            raise InvalidProblem("scale_mode must be 0 (per tensor) or 1 (per row / per column)")
+        if desc.f % 32 != 0:
+            raise Unsupported("F must be a multiple of 32 (gate and up rows are interleaved in blocks of 32)")
+        guarantee = _INT_GUARANTEE if desc.element is ElementKind.S8 else _FP8_GUARANTEE
+        sku = KernelSku(OpCategory.Gemm, OP_GATED_MLP_UP, desc.element, ElementKind.Bf16, LayoutSku.Rcr,
+                        EpilogueKind.Identity, ArchSku.Sm100a, BackendKind.Bespoke, guarantee)
+        return cls(desc, sku)
+
+    def sku(self) -> KernelSku:
+        return self._sku
+
+    def precision_guarantee(self) -> PrecisionGuarantee:
+        return self._sku.precision_guarantee
+
+    def workspace_size(self) -> int:
+        return int(getattr(_lib.load(), self._base + "_workspace_size")(self.desc.m, 2 * self.desc.f, self.desc.k))
+
+    @staticmethod
+    def interleave(gate: torch.Tensor, up: torch.Tensor, stream=None) -> torch.Tensor:
+        """Rows (2-D weights) or entries (1-D scale / bias vectors) of `gate` and `up` interleaved in blocks of 32."""
+        if gate.shape != up.shape or gate.dtype != up.dtype or gate.dim() not in (1, 2):
+            raise InvalidProblem("gate and up must have the same shape and dtype (1-D or 2-D)")
+        if not (gate.is_cuda and up.is_cuda):
+            raise InvalidProblem("operands must be device buffers")
+        gate, up = gate.contiguous(), up.contiguous()
+        f_rows = gate.shape[0]
+        row_bytes = gate.element_size() * (gate.shape[1] if gate.dim() == 2 else 1)
+        out = torch.empty((2 * f_rows,) + tuple(gate.shape[1:]), dtype=gate.dtype, device=gate.device)
+        st = _lib.load().baracuda_kernels_q_interleave_gate_up_run(
+            f_rows, row_bytes, _ptr(gate), row_bytes, _ptr(up), row_bytes, _ptr(out), row_bytes, _stream_ptr(stream))
+        status_to_result(st, "GatedMlpUpPlan.interleave")
+        return out
+
+    def _lds(self, args: GatedMlpUpArgs):
+        d = self.desc
+        return (args.lda if args.lda is not None else max(d.k, 1), args.ldb if args.ldb is not None else max(d.k, 1),
+                args.ldd if args.ldd is not None else max(d.f, 1))
+
+    def can_implement(self, args: GatedMlpUpArgs) -> None:
+        d = self.desc
+        lda, ldb, ldd = self._lds(args)
+        ok_in = (torch.int8,) if d.element is ElementKind.S8 else (torch.uint8, torch.float8_e4m3fn)
+        for t, name in ((args.a, "a"), (args.b_gate_up, "b_gate_up")):
+            if t.dtype not in ok_in:
+                raise InvalidProblem(f"{name}: dtype {t.dtype} not accepted by this plan")
+        if args.d.dtype != torch.bfloat16:
+            raise InvalidProblem("d: expected bfloat16")
+        if not (args.a.is_cuda and args.b_gate_up.is_cuda and args.d.is_cuda):
+            raise InvalidProblem("operands must be device buffers")
+        st = getattr(_lib.load(), self._base + "_can_implement")(d.m, 2 * d.f, d.k, _ptr(args.a), lda,
+                                                                 _ptr(args.b_gate_up), ldb, _ptr(args.d), ldd)
+        status_to_result(st, type(self).__name__)
+        if d.m == 0 or d.f == 0:
+            return
+        _need(args.a, _span(d.m, d.k, lda), "a")
+        _need(args.b_gate_up, _span(2 * d.f, d.k, ldb), "b_gate_up")
+        _need(args.d, _span(d.m, d.f, ldd), "d")
+        per_vec = d.scale_mode == SCALE_PER_ROW_COL
+        for t, n, name in ((args.scale_a, d.m if per_vec else 1, "scale_a"),
+                           (args.scale_b, 2 * d.f if per_vec else 1, "scale_b")):
+            if t is None or t.dtype != torch.float32:
+                raise InvalidProblem(f"{name}: expected a float32 device vector")
+            _need(t, n, name)
+        if args.bias is not None:
+            if args.bias.dtype != torch.float32 or not args.bias.is_cuda:
+                raise InvalidProblem("bias: expected a float32 device vector")
+            _need(args.bias, 2 * d.f, "bias")
+
+    def run(self, stream, workspace: Optional[torch.Tensor], args: GatedMlpUpArgs) -> None:
+        self.can_implement(args)
+        d = self.desc
+        lda, ldb, ldd = self._lds(args)
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        lib = _lib.load()
+        head = (d.m, 2 * d.f, d.k, _ptr(args.a), lda, _ptr(args.b_gate_up), ldb, _ptr(args.d), ldd, _ptr(args.scale_a),
+                _ptr(args.scale_b))
+        tail = (_ptr(args.bias), args.alpha, _ptr(workspace), ws_bytes, _stream_ptr(stream))
+        if d.element is ElementKind.S8:
+            st = getattr(lib, self._base + "_run")(*head, *tail)
+        else:
+            st = getattr(lib, self._base + "_run")(*head, d.scale_mode, *tail)
+        status_to_result(st, type(self).__name__)
+
+
 # --------------------------------------------------------------------------- the reference's 8-bit-out plans
 class IntGemmPlan(_QGemmPlanBase):
     """`IntGemmPlan<S8>` of the reference (crates/baracuda-kernels/src/gemm/int_gemm.rs:48-637), Rcr layout,

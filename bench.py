@@ -275,7 +275,7 @@ def side_workloads(peaks: dict) -> dict:
                     "us": t * 1e6, "GBps": byts / t / 1e9, "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
     del weights
 
-    def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False):
+    def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False, gated: bool = False):
         gen = torch.Generator(device="cuda")
         gen.manual_seed(m + n + k)
         if kind == "s8":
@@ -290,6 +290,10 @@ def side_workloads(peaks: dict) -> dict:
         sb = torch.rand(n, device="cuda", generator=gen)
         d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
         args = bq.QGemmArgs(a=a, b=b, d=d, scale_a=sa, scale_b=sb)
+        if gated:  # the n weight rows are gate and up interleaved; the epilogue stores silu(gate) * up as [m, n / 2]
+            plan = bq.GatedMlpUpPlan.select(None, bq.GatedMlpUpDescriptor(m, n // 2, k))
+            d = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+            args = bq.GatedMlpUpArgs(a=a, b_gate_up=b, d=d, scale_a=sa, scale_b=sb)
         if graph:  # launch-latency-bound shape: time a CUDA graph of 8 launches, operands stay in L2
             t = graph_launch_ms([lambda: plan.run(None, None, args)] * 8) * 1e-3
         else:
@@ -311,6 +315,7 @@ def side_workloads(peaks: dict) -> dict:
             tot_ops += 2.0 * m * nn * kk
             tot_t += r["us"] * 1e-6
         prefill[f"M{m}_layer_TOPS"] = tot_ops / tot_t / 1e12
+        prefill[f"M{m}_gate_up_swiglu_fused"] = gemm("s8", m, 28672, 4096, steps=5, gated=True)
     out["prefill_w8a8"] = prefill
     return out
 

@@ -280,6 +280,49 @@ BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm1
 BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run)
 
 /* ---------------------------------------------------------------------------
+ * Gated-MLP up-projection in one launch: D[M, F] = bf16( silu(z_gate) * z_up ),
+ *   z[m, j] = alpha * (scale_a[m] * scale_b[j]) * acc[m, j] (+ bias[j]),  silu(z) = z / (1 + exp(-z)),
+ * over ONE weight `b_gate_up` [n2 = 2F, K] that holds the gate and up projections interleaved in blocks of 32 rows:
+ * rows 64b .. 64b+31 are gate rows 32b .. 32b+31, rows 64b+32 .. 64b+63 the matching up rows; scale_b and the
+ * optional float bias are [n2] in the same order (baracuda_kernels_q_interleave_gate_up_run builds all three).
+ * No counterpart in the reference: its EpilogueKind (crates/baracuda-kernel-vocab/src/layout.rs:69-96) stops at
+ * BiasSilu, so a gated MLP there is two GEMMs (or one of width 2F) followed by an elementwise pass over [M, 2F];
+ * here the [M, 2F] intermediate never reaches memory.
+ * Status: n2 not a multiple of 64 -> 3; d not 16-byte aligned or ldd not a multiple of 8 -> 1; ldd < n2 / 2 -> 2;
+ * the other rules are those of the bf16 GEMM above.  workspace_size is 0.
+ * ------------------------------------------------------------------------- */
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run(
+    int32_t m, int32_t n2, int32_t k,
+    const void* a, int64_t lda, const void* b_gate_up, int64_t ldb,
+    void* d, int64_t ldd,
+    const void* scale_a, const void* scale_b, const void* bias /* float[n2] or NULL */,
+    float alpha,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_workspace_size(int32_t m, int32_t n2, int32_t k);
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_can_implement(
+    int32_t m, int32_t n2, int32_t k,
+    const void* a, int64_t lda, const void* b_gate_up, int64_t ldb,
+    const void* d, int64_t ldd);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_run(
+    int32_t m, int32_t n2, int32_t k,
+    const void* a, int64_t lda, const void* b_gate_up, int64_t ldb,
+    void* d, int64_t ldd,
+    const void* scale_a, const void* scale_b, int32_t scale_mode, const void* bias /* float[n2] or NULL */,
+    float alpha,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_workspace_size(int32_t m, int32_t n2, int32_t k);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_can_implement(
+    int32_t m, int32_t n2, int32_t k,
+    const void* a, int64_t lda, const void* b_gate_up, int64_t ldb,
+    const void* d, int64_t ldd);
+/* out row 64b + i = gate row 32b + i (i < 32) or up row 32b + i - 32; rows are `row_bytes` bytes (K for a weight,
+ * 4 for a scale or bias vector with pitches of 4), pitches in bytes; f_rows (= F) must be a multiple of 32. */
+int32_t baracuda_kernels_q_interleave_gate_up_run(
+    int64_t f_rows, int64_t row_bytes,
+    const void* gate, int64_t gate_pitch, const void* up, int64_t up_pitch,
+    void* out, int64_t out_pitch, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Decode GEMV with int8 weights, m = 1 (and the skinny extension m <= 8):
  *   D[g,r,j] = bf16( alpha * ((scale_a[g,r] * scale_b[g,j]) * (float)acc) + beta * D[g,r,j] )
  * Argument order is that of baracuda_kernels_gemv_dense_m1_bf16_run

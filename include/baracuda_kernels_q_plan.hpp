@@ -100,6 +100,7 @@ struct KernelSku {  // sku.rs:259-285
 constexpr uint16_t OP_W8A8_GEMM = 100;
 constexpr uint16_t OP_FP8_SCALED_GEMM = 101;
 constexpr uint16_t OP_GEMV_Q8 = 102;
+constexpr uint16_t OP_GATED_MLP_UP = 103;
 
 // A device view with its length in elements, so the typed layer can refuse a
 // launch that would run off a buffer (the soundness boundary of
@@ -365,6 +366,91 @@ class IntGemmPlan {
     QGemmDescriptor desc_{};
     KernelSku sku_{};
     bool fp8_ = false;
+};
+
+// Gated-MLP up-projection in one launch: h[M, F] = silu(x Wg^T) * (x Wu^T) from 8-bit operands, the [M, 2F]
+// intermediate staying in tensor memory.  The reference's EpilogueKind ends at BiasSilu (layout.rs:69-96); this plan
+// has no counterpart there.  `b_gate_up`, `scale_b` and `bias` hold gate and up interleaved in blocks of 32 rows
+// (baracuda_kernels_q_interleave_gate_up_run builds them once at weight-load time).
+struct GatedMlpUpDescriptor {
+    int32_t m = 0, f = 0, k = 0;
+    ElementKind element = ElementKind::S8;       // S8 or Fp8E4M3
+    ScaleMode scale_mode = ScaleMode::PerRowCol;  // the S8 SKU takes per-token x per-channel scales only
+};
+
+struct GatedMlpUpArgs {
+    DeviceSpan<const void> a;          // [M,K] bytes, row pitch lda
+    int64_t lda = 0;
+    DeviceSpan<const void> b_gate_up;  // [2F,K] bytes, row pitch ldb
+    int64_t ldb = 0;
+    DeviceSpan<void> d;                // bf16 [M,F], row pitch ldd (a multiple of 8)
+    int64_t ldd = 0;
+    DeviceSpan<const float> scale_a;
+    DeviceSpan<const float> scale_b;   // [2F] (or one value with ScaleMode::PerTensor)
+    DeviceSpan<const float> bias;      // [2F] or empty
+    float alpha = 1.0f;
+};
+
+class GatedMlpUpPlan {
+  public:
+    static Error select(const GatedMlpUpDescriptor& desc, const PlanPreference& pref, GatedMlpUpPlan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.m < 0 || desc.f < 0 || desc.k < 0 || desc.f > INT32_MAX / 2) return Error::InvalidProblem;
+        if (desc.element != ElementKind::S8 && desc.element != ElementKind::Fp8E4M3) return Error::Unsupported;
+        if (desc.element == ElementKind::S8 && desc.scale_mode != ScaleMode::PerRowCol) return Error::InvalidProblem;
+        if (desc.f % 32 != 0) return Error::Unsupported;
+        const bool fp8 = desc.element == ElementKind::Fp8E4M3;
+        out->desc_ = desc;
+        out->sku_ = KernelSku{OpCategory::Gemm, OP_GATED_MLP_UP, desc.element, ElementKind::Bf16, LayoutSku::Rcr,
+                              EpilogueKind::Identity, ArchSku::Sm100a, BackendKind::Bespoke,
+                              PrecisionGuarantee{fp8 ? MathPrecision::Fp8E4M3 : MathPrecision::Int8,
+                                                 fp8 ? ElementKind::F32 : ElementKind::I32, true, true}};
+        return Error::Ok;
+    }
+    const KernelSku& sku() const { return sku_; }
+    PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
+    const GatedMlpUpDescriptor& descriptor() const { return desc_; }
+    size_t workspace_size() const {
+        return baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_workspace_size(desc_.m, 2 * desc_.f, desc_.k);
+    }
+    Error can_implement(const GatedMlpUpArgs& x) const {
+        const bool fp8 = desc_.element == ElementKind::Fp8E4M3;
+        auto can = fp8 ? baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_can_implement
+                       : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_can_implement;
+        const int32_t st = can(desc_.m, 2 * desc_.f, desc_.k, x.a.ptr, x.lda, x.b_gate_up.ptr, x.ldb, x.d.ptr, x.ldd);
+        if (st != 0) return status_to_error(st);
+        if (desc_.m == 0 || desc_.f == 0) return Error::Ok;
+        if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
+        if (x.b_gate_up.len < detail::span_elems(2 * static_cast<int64_t>(desc_.f), desc_.k, x.ldb))
+            return Error::BufferTooSmall;
+        if (x.d.len < detail::span_elems(desc_.m, desc_.f, x.ldd)) return Error::BufferTooSmall;
+        if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
+        const bool vec = desc_.scale_mode == ScaleMode::PerRowCol;
+        if (x.scale_a.len < (vec ? static_cast<size_t>(desc_.m) : 1u) ||
+            x.scale_b.len < (vec ? 2 * static_cast<size_t>(desc_.f) : 1u))
+            return Error::BufferTooSmall;
+        if (x.bias.ptr && x.bias.len < 2 * static_cast<size_t>(desc_.f)) return Error::BufferTooSmall;
+        return Error::Ok;
+    }
+    Error run(void* stream, Workspace ws, const GatedMlpUpArgs& x) const {
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        int32_t st;
+        if (desc_.element == ElementKind::Fp8E4M3) {
+            st = baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_run(
+                desc_.m, 2 * desc_.f, desc_.k, x.a.ptr, x.lda, x.b_gate_up.ptr, x.ldb, x.d.ptr, x.ldd, x.scale_a.ptr,
+                x.scale_b.ptr, static_cast<int32_t>(desc_.scale_mode), x.bias.ptr, x.alpha, ws.ptr, ws.bytes, stream);
+        } else {
+            st = baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run(
+                desc_.m, 2 * desc_.f, desc_.k, x.a.ptr, x.lda, x.b_gate_up.ptr, x.ldb, x.d.ptr, x.ldd, x.scale_a.ptr,
+                x.scale_b.ptr, x.bias.ptr, x.alpha, ws.ptr, ws.bytes, stream);
+        }
+        return status_to_error(st);
+    }
+
+  private:
+    GatedMlpUpDescriptor desc_{};
+    KernelSku sku_{};
 };
 
 // ---------------------------------------------------------------------------- GEMV

@@ -222,6 +222,26 @@ def epilogue_chain(z: np.ndarray, bias, kind: int) -> np.ndarray:
     raise ValueError(f"epilogue kind {kind}")
 
 
+def interleave_gate_up(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """Rows (or entries) of gate and up interleaved in blocks of 32: out[64b + i] = gate[32b + i] for i < 32,
+    up[32b + i - 32] otherwise -- the operand layout of the gated-MLP GEMM (no counterpart in the reference)."""
+    gate, up = np.asarray(gate), np.asarray(up)
+    assert gate.shape == up.shape and gate.shape[0] % 32 == 0
+    f = gate.shape[0]
+    g = gate.reshape((f // 32, 32) + gate.shape[1:])
+    u = up.reshape((f // 32, 32) + up.shape[1:])
+    return np.concatenate([g, u], axis=1).reshape((2 * f,) + gate.shape[1:])
+
+
+def swiglu_f32(z_gate: np.ndarray, z_up: np.ndarray) -> np.ndarray:
+    """silu(z_gate) * z_up with silu = x / (1 + exp(-x)) as the reference states it
+    (crates/baracuda-kernels/tests/int8_rrr_smoke.rs:60-66), evaluated in f64 and rounded once to f32."""
+    g = np.asarray(z_gate, dtype=np.float32).astype(np.float64)
+    u = np.asarray(z_up, dtype=np.float32).astype(np.float64)
+    with np.errstate(over="ignore"):
+        return (g / (1.0 + np.exp(-g)) * u).astype(np.float32)
+
+
 def sat_s8(z: np.ndarray) -> np.ndarray:
     """Round half to even, clamp to [-128, 127] (int8_rrr_smoke.rs:76-78)."""
     return np.clip(np.rint(np.asarray(z, dtype=np.float32)), -128, 127).astype(np.int8)

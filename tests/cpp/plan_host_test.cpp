@@ -47,6 +47,38 @@ int main() {
     qa.ldb = 1024;
     qa.ldd = 1024;
     CHECK(q8.run(nullptr, Workspace::none(), qa) == Error::BufferTooSmall);  // the typed layer refuses empty views
+    {
+        GatedMlpUpPlan gp;
+        GatedMlpUpDescriptor gd;
+        gd.m = 64;
+        gd.f = 48;
+        gd.k = 128;
+        CHECK(GatedMlpUpPlan::select(gd, pref, &gp) == Error::Unsupported);  // F in blocks of 32
+        gd.f = 64;
+        gd.scale_mode = ScaleMode::PerTensor;
+        CHECK(GatedMlpUpPlan::select(gd, pref, &gp) == Error::InvalidProblem);  // s8 takes scale vectors
+        gd.scale_mode = ScaleMode::PerRowCol;
+        CHECK(GatedMlpUpPlan::select(gd, pref, &gp) == Error::Ok);
+        CHECK(gp.sku().op == OP_GATED_MLP_UP && *gp.sku().aux_element == ElementKind::Bf16);
+        CHECK(gp.workspace_size() == 0);
+        auto fk = [](uintptr_t addr) { return reinterpret_cast<void*>(addr); };
+        GatedMlpUpArgs ga;
+        ga.a = {fk(0x10000), size_t(64) * 128};
+        ga.lda = 128;
+        ga.b_gate_up = {fk(0x20000), size_t(128) * 128};
+        ga.ldb = 128;
+        ga.d = {fk(0x40000), size_t(64) * 64};
+        ga.ldd = 64;
+        ga.scale_a = {static_cast<const float*>(fk(0x60000)), 64};
+        ga.scale_b = {static_cast<const float*>(fk(0x61000)), 64};
+        CHECK(gp.can_implement(ga) == Error::BufferTooSmall);  // scale_b covers gate and up
+        ga.scale_b.len = 128;
+        CHECK(gp.can_implement(ga) == Error::Ok);
+        ga.ldd = 60;
+        CHECK(gp.can_implement(ga) == Error::InvalidProblem);
+        ga.ldd = 68;
+        CHECK(gp.can_implement(ga) == Error::MisalignedOperand);
+    }
     QGemmDescriptor bias = desc;
     bias.epilogue = EpilogueKind::BiasRelu;
     CHECK(W8A8GemmPlan::select(bias, pref, true, &p) == Error::Unsupported);  // raw accumulators: identity only
