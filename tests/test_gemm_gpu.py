@@ -246,6 +246,94 @@ def test_full_size_4096_cubed_properties(oracle):
     assert oracle.compare_tolerant(want8, out8[rows], 1e-2, 1e-4 * float(np.abs(want8).max())) == -1
 
 
+def _column_sums_f64(table, q, chunk=512):
+    """sum_i table[q[i, :]] and sum_i |table[q[i, :]]| in f64 without materialising the decoded matrix."""
+    tot = np.zeros(q.shape[1], dtype=np.float64)
+    tot_abs = np.zeros(q.shape[1], dtype=np.float64)
+    for r in range(0, q.shape[0], chunk):
+        v = table[q[r:r + chunk]]
+        tot += v.sum(axis=0)
+        tot_abs += np.abs(v).sum(axis=0)
+    return tot, tot_abs
+
+
+def _random_e4m3(rng, shape):
+    """Uniform e4m3 codes with magnitude below 4 (exponent field 0..8, subnormals included) and a random sign: every
+    byte is a finite value, generated directly because encoding 235 M floats on the host takes minutes."""
+    mag = rng.integers(0, 0x48, size=shape, dtype=np.uint8)
+    sign = rng.integers(0, 2, size=shape, dtype=np.uint8)
+    return mag | (sign << 7)
+
+
+def test_full_size_headline_fp8_8192x8192x28672(oracle):
+    """The configuration the headline metric is quoted on, at full size: a row sample against the oracle, the checksum
+    identity sum_ij acc = sum_k (sum_i A[i,k]) (sum_j B[j,k]) over every output, linearity in the scales
+    (doubling scale_a doubles every bf16 output exactly), and the bf16 store of the sampled rows."""
+    m, n, k = 8192, 8192, 28672
+    rng = np.random.default_rng(8192)
+    a8, w8 = _random_e4m3(rng, (m, k)), _random_e4m3(rng, (n, k))
+    plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), scale_mode=bq.SCALE_PER_TENSOR,
+                                       raw_accumulators=True)
+    a_d, w_d = dev(a8), dev(w8)
+    acc_d = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    plan.run(None, None, bq.QGemmArgs(a=a_d, b=w_d, d=acc_d))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    rows = np.sort(rng.choice(m, 8, replace=False))
+    ref_rows = oracle.gemm_e4m3_f32(a8[rows], w8, oracle.RCR, len(rows), n, k)
+    got_rows = acc_d[torch.from_numpy(rows).cuda()].cpu().numpy()
+    assert oracle.compare_tolerant(ref_rows, got_rows, 1e-3, 1e-5 * float(np.abs(ref_rows).max())) == -1
+    table = oracle.e4m3_decode_table().astype(np.float64)
+    ca, ca_abs = _column_sums_f64(table, a8)
+    cb, cb_abs = _column_sums_f64(table, w8)
+    total = float(acc_d.double().sum().item())
+    assert abs(total - float((ca * cb).sum())) <= 1e-6 * float((ca_abs * cb_abs).sum())
+
+    scaled = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), scale_mode=bq.SCALE_PER_TENSOR)
+    sa, sb = np.array([0.0123], dtype=np.float32), np.array([0.5], dtype=np.float32)
+    out1 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    out2 = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    scaled.run(None, None, bq.QGemmArgs(a=a_d, b=w_d, d=out1, scale_a=dev(sa), scale_b=dev(sb)))
+    scaled.run(None, None, bq.QGemmArgs(a=a_d, b=w_d, d=out2, scale_a=dev(sa * 2), scale_b=dev(sb)))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert torch.equal(out1.float() * 2, out2.float())
+    want = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(ref_rows, sa, sb))
+    got = out1[torch.from_numpy(rows).cuda()].float().cpu().numpy()
+    assert oracle.compare_tolerant(want, got, 1e-2, 1e-4 * float(np.abs(want).max())) == -1
+
+
+@pytest.mark.parametrize("shape", [(8192, 28672, 4096), (8192, 4096, 14336)])
+def test_full_size_prefill_w8a8(oracle, shape):
+    """The two largest prefill GEMMs at full size: exact row sample, exact integer checksum over every output, and the
+    bf16 dequant of the sampled rows bit for bit."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + k)
+    aq = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+    wq = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    sa = (rng.random(m, dtype=np.float32) + np.float32(0.5)) * np.float32(0.01)
+    sb = (rng.random(n, dtype=np.float32) + np.float32(0.5)) * np.float32(0.001)
+    a_d, w_d = dev(aq), dev(wq)
+    acc_d = torch.empty((m, n), dtype=torch.int32, device="cuda")
+    raw = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k), raw_accumulators=True)
+    raw.run(None, None, bq.QGemmArgs(a=a_d, b=w_d, d=acc_d))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    rows = np.sort(rng.choice(m, 8, replace=False))
+    ref_rows = oracle.gemm_s8_s32(aq[rows], wq, oracle.RCR, len(rows), n, k)
+    idx = torch.from_numpy(rows).cuda()
+    assert np.array_equal(acc_d[idx].cpu().numpy(), ref_rows)
+    col_a = aq.sum(axis=0, dtype=np.int64)
+    col_b = wq.sum(axis=0, dtype=np.int64)
+    assert int(acc_d.sum(dtype=torch.int64).item()) == int((col_a * col_b).sum())
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k))
+    plan.run(None, None, bq.QGemmArgs(a=a_d, b=w_d, d=out, scale_a=dev(sa), scale_b=dev(sb)))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert np.array_equal(bf16_bits(out[idx]), oracle.dequant_s32_bf16(ref_rows, sa[rows], sb))
+
+
 @pytest.mark.parametrize("shape", [(64, 64, 32), (128, 128, 128), (256, 128, 64), (100, 70, 50), (700, 1300, 656),
                                    (2048, 2560, 1024)])
 def test_row_major_weights_rrr(oracle, shape):
