@@ -44,6 +44,21 @@ int32_t gemm_rcr_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_
     return gemm_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
 
+// The bf16-out SKUs take C (bf16 [M, ldc], may alias D) and beta like the reference's GEMM family.
+int32_t gemm_bf16_validate(int32_t layout, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,
+                           int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd) {
+    const int32_t st = gemm_validate(layout, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (c != nullptr && ldc < (n > 0 ? n : 1)) return bq::BQ_STATUS_INVALID_PROBLEM;
+    if (c != nullptr && (reinterpret_cast<uintptr_t>(c) & 1u)) return bq::BQ_STATUS_MISALIGNED;
+    return bq::BQ_STATUS_OK;
+}
+
+int32_t gemm_rcr_bf16_validate(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,
+                               const void* c, int64_t ldc, const void* d, int64_t ldd) {
+    return gemm_bf16_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+}
+
 // Fused epilogue chain of the reference's EpilogueKind (crates/baracuda-kernel-vocab/src/layout.rs:69-96):
 // 0 Identity, 1 Bias, 2 BiasRelu, 3 BiasGelu, 4 BiasSilu; bias_kind 1 = float[N], 2 = int32[N].
 struct Epilogue {
@@ -84,14 +99,16 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
                  const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream, const Epilogue& epi) {
-    const int32_t st = gemm_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    const int32_t st = raw ? gemm_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd)
+                           : gemm_bf16_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (const int32_t es = epilogue_validate(epi, false); es != bq::BQ_STATUS_OK) return es;
     if (raw && epi.kind != 0) return bq::BQ_STATUS_UNSUPPORTED;
-    if (k == 0 && epi.kind != 0) return bq::BQ_STATUS_UNSUPPORTED;
+    if (k == 0 && (epi.kind != 0 || beta != 0.0f)) return bq::BQ_STATUS_UNSUPPORTED;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
-    if (beta != 0.0f) return bq::BQ_STATUS_UNSUPPORTED;
+    if (raw && beta != 0.0f) return bq::BQ_STATUS_UNSUPPORTED;
+    if (beta != 0.0f && !c) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (raw) {
         if (alpha != 1.0f) return bq::BQ_STATUS_UNSUPPORTED;
     } else {
@@ -126,9 +143,9 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     for (auto& pd : g.peer_d) pd = nullptr;
     epilogue_apply(epi, g);
     g.q8_out = 0;
-    g.c = nullptr;
-    g.ldc = 0;
-    g.beta = 0.0f;
+    g.c = (!raw && beta != 0.0f) ? c : nullptr;  // beta == 0: C is not read
+    g.ldc = ldc;
+    g.beta = beta;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -396,7 +413,7 @@ size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(int32_t, int
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return gemm_rcr_bf16_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
 
 // ---- gated-MLP up-projection: silu(gate) * up -> bf16 ---------------------------------------
@@ -473,7 +490,7 @@ size_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(int32_t, in
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return gemm_rcr_bf16_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
 }
 
 // ---- e4m3 -> f32 accumulators ---------------------------------------------------
@@ -540,7 +557,7 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run(
     return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
                     BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream);
 }
-BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a, gemm_validate)
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a, gemm_bf16_validate)
 
 int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
@@ -551,7 +568,7 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run(
     return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
                     scale_mode, alpha, beta, stream);
 }
-BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a, gemm_validate)
+BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a, gemm_bf16_validate)
 
 int32_t baracuda_kernels_gemm_s8_rrr_s32_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,

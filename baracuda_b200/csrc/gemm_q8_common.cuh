@@ -92,6 +92,30 @@ __device__ __forceinline__ void apply_bias_act_32(const GemmParams& p, float (&z
     }
 }
 
+// y += beta * C on the bf16-out SKUs (C is bf16 [M, ldc], may be D itself: every element is read by the warp that
+// later overwrites it, before that store).  Product and sum are rounded separately in f32.
+__device__ __forceinline__ void add_beta_c_bf16_32(const GemmParams& p, int row, int col0, float (&y)[32]) {
+    const __nv_bfloat16* crow = reinterpret_cast<const __nv_bfloat16*>(p.c) + static_cast<int64_t>(row) * p.ldc + col0;
+    if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(crow) & 15u) == 0) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const uint4 q = reinterpret_cast<const uint4*>(crow)[v];
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                y[8 * v + 2 * i] = __fadd_rn(y[8 * v + 2 * i], __fmul_rn(p.beta, __uint_as_float(w[i] << 16)));
+                y[8 * v + 2 * i + 1] =
+                    __fadd_rn(y[8 * v + 2 * i + 1], __fmul_rn(p.beta, __uint_as_float(w[i] & 0xffff0000u)));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.n) y[j] = __fadd_rn(y[j], __fmul_rn(p.beta, __bfloat162float(crow[j])));
+        }
+    }
+}
+
 // One thread, one output row, 32 consecutive columns starting at col0 (a multiple of 32).
 // `r` holds the accumulators as read from TMEM, `sb32` the 32 column scales.
 template <uint32_t KIND, bool RAW, bool FUSED>
@@ -201,6 +225,7 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
             const float s = __fmul_rn(sa_row, sb32[j]);
             y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
         }
+        if (p.c != nullptr) add_beta_c_bf16_32(p, row, col0, y);
         if ((p.bias_kind | p.act) != 0) apply_bias_act_32(p, y, sb32);
         uint4 pk[4];
 #pragma unroll
@@ -249,7 +274,7 @@ __device__ __forceinline__ void epilogue_store_32(const GemmParams& p, int row, 
 // Converts 32 accumulator columns of this thread's row into 32 bf16 (four 16-byte packets).
 template <uint32_t KIND>
 __device__ __forceinline__ void dequant_pack_32(const GemmParams& p, const uint32_t (&r)[32], float sa_row,
-                                                const float* sb32, uint4 (&pk)[4], int col0) {
+                                                const float* sb32, uint4 (&pk)[4], int row, int col0) {
     float y[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -262,6 +287,7 @@ __device__ __forceinline__ void dequant_pack_32(const GemmParams& p, const uint3
         const float s = __fmul_rn(sa_row, sb32[j]);
         y[j] = __fmul_rn(__fmul_rn(s, acc), p.alpha);
     }
+    if (p.c != nullptr && row < p.m) add_beta_c_bf16_32(p, row, col0, y);
     if ((p.bias_kind | p.act) != 0) apply_bias_act_32(p, y, sb32);
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
@@ -294,7 +320,7 @@ __device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t 
         tmem_ld_32x32b_x32(t_addr + static_cast<uint32_t>(half * 32), r);
         tmem_ld_wait();
         uint4 pk[4];
-        dequant_pack_32<KIND>(p, r, sa_row, sb64 + half * 32, pk, col0 + half * 32);
+        dequant_pack_32<KIND>(p, r, sa_row, sb64 + half * 32, pk, row_base + lane, col0 + half * 32);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
             const int c = half * 4 + v;
@@ -339,7 +365,7 @@ __device__ __forceinline__ void epilogue_block_32(const GemmParams& p, uint32_t 
         tmem_ld_32x32b_x32(t_addr, r);
         tmem_ld_wait();
         uint4 pk[4];
-        dequant_pack_32<KIND>(p, r, sa_row, sb32, pk, col0);
+        dequant_pack_32<KIND>(p, r, sa_row, sb32, pk, row_base + lane, col0);
 #pragma unroll
         for (int v = 0; v < 4; ++v) stage[lane * 4 + (v ^ ((lane >> 1) & 3))] = pk[v];
     }

@@ -159,11 +159,16 @@ class _QGemmPlanBase:
         if not (args.a.is_cuda and args.b.is_cuda and args.d.is_cuda):
             raise InvalidProblem("operands must be device buffers")
         lib = _lib.load()
+        ldc = args.ldc or max(d.n, 1)
         st = getattr(lib, self._can_symbol)(d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb,
-                                            _ptr(args.c), args.ldc, _ptr(args.d), ldd)
+                                            _ptr(args.c), ldc, _ptr(args.d), ldd)
         status_to_result(st, type(self).__name__)
         if d.m == 0 or d.n == 0:
             return  # empty problem: nothing is read or written
+        if args.c is not None:
+            if args.c.dtype != args.d.dtype or not args.c.is_cuda:
+                raise InvalidProblem("c: expected a device buffer of the output type")
+            _need(args.c, _span(d.m, d.n, ldc), "c")
         _need(args.a, _span(d.m, d.k, lda), "a")
         _need(args.b, _span(d.n, d.k, ldb) if d.layout is LayoutSku.Rcr else _span(d.k, d.n, ldb), "b")
         _need(args.d, _span(d.m, d.n, ldd), "d")
@@ -235,15 +240,15 @@ class W8A8GemmPlan(_QGemmPlanBase):
         d = self.desc
         if self.raw:
             return getattr(lib, self._run_symbol)(
-                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
         if d.epilogue is not EpilogueKind.Identity:
             return getattr(lib, self._run_symbol.replace("_run", "_epilogue_run"))(
-                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
                 _ptr(args.scale_a), _ptr(args.scale_b), SCALE_PER_ROW_COL, _ptr(args.bias), _EPILOGUE_CODE[d.epilogue],
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
         return getattr(lib, self._run_symbol)(
-            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
             _ptr(args.scale_a), _ptr(args.scale_b), args.alpha, args.beta, ws_ptr, ws_bytes, stream)
 
 
@@ -292,15 +297,15 @@ class Fp8ScaledGemmPlan(_QGemmPlanBase):
         d = self.desc
         if self.raw:
             return lib.baracuda_kernels_gemm_fp8_e4m3_rcr_f32_sm100a_run(
-                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
         if d.epilogue is not EpilogueKind.Identity:
             return getattr(lib, self._run_symbol.replace("_run", "_epilogue_run"))(
-                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+                d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
                 _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, _ptr(args.bias), _EPILOGUE_CODE[d.epilogue],
                 args.alpha, args.beta, ws_ptr, ws_bytes, stream)
         return getattr(lib, self._run_symbol)(
-            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc, _ptr(args.d), ldd,
+            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
             _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, args.alpha, args.beta, ws_ptr, ws_bytes, stream)
 
 

@@ -65,8 +65,11 @@ extern "C" {
  * followed by a dequant pass, and the one-thread-per-cell
  *   baracuda_kernels_quantized_linear_w8a8_f32_run
  *   (crates/baracuda-kernels-sys/kernels/include/baracuda_quantize_compose.cuh:340-370).
- * `c` / `ldc` / `beta` keep the GEMM family's argument order; this SKU needs
- * c == NULL and beta == 0 (anything else returns 3).
+ * `c` / `ldc` / `beta` keep the GEMM family's argument order: with beta != 0 the
+ * epilogue adds beta * C[m, j] (C bf16 [M, ldc], 2-byte aligned, may be D itself --
+ * the residual add of an output / down projection) before the bias and the
+ * activation, product and sum rounded separately in f32; beta != 0 without C
+ * returns 2; with beta == 0 C is not read.  The raw-accumulator SKUs take no C (3).
  * Alignment: a and b 16-byte aligned, lda and ldb multiples of 16.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(

@@ -145,6 +145,8 @@ struct QGemmArgs {
     float alpha = 1.0f;
     float beta = 0.0f;
     DeviceSpan<const float> bias;  // [N], read when the descriptor's epilogue has a bias
+    DeviceSpan<const void> c;      // bf16 [M,N] with row pitch ldc, read when beta != 0 (may be d); bf16-out plans only
+    int64_t ldc = 0;
 };
 
 class W8A8GemmPlan {
@@ -176,13 +178,14 @@ class W8A8GemmPlan {
                                : baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_can_implement)
                        : (raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement
                                : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement);
-        const int32_t st = can(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
+        const int32_t st = can(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd);
         if (st != 0) return status_to_error(st);
         if (desc_.m == 0 || desc_.n == 0) return Error::Ok;  // empty problem: nothing is read or written
         if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
         if (x.b.len < (rrr ? detail::span_elems(desc_.k, desc_.n, x.ldb) : detail::span_elems(desc_.n, desc_.k, x.ldb)))
             return Error::BufferTooSmall;
         if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
+        if (x.c.ptr && x.c.len < detail::span_elems(desc_.m, desc_.n, x.ldc)) return Error::BufferTooSmall;
         if (!raw_) {
             if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
             if (x.scale_a.len < static_cast<size_t>(desc_.m) || x.scale_b.len < static_cast<size_t>(desc_.n))
@@ -206,12 +209,12 @@ class W8A8GemmPlan {
         } else if (desc_.epilogue != EpilogueKind::Identity) {
             auto run = rrr ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run
                            : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run;
-            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd, x.scale_a.ptr,
                      x.scale_b.ptr, BARACUDA_Q_SCALE_PER_ROW_COL, x.bias.ptr, static_cast<int32_t>(desc_.epilogue), x.alpha,
                      x.beta, ws.ptr, ws.bytes, stream);
         } else {
             auto run = rrr ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run;
-            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd, x.scale_a.ptr,
                      x.scale_b.ptr, x.alpha, x.beta, ws.ptr, ws.bytes, stream);
         }
         return status_to_error(st);
@@ -249,13 +252,14 @@ class Fp8ScaledGemmPlan {
         const bool rrr = desc_.layout == LayoutSku::Rrr;
         auto can = rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_can_implement
                        : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement;
-        const int32_t st = can(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd);
+        const int32_t st = can(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd);
         if (st != 0) return status_to_error(st);
         if (desc_.m == 0 || desc_.n == 0) return Error::Ok;  // empty problem: nothing is read or written
         if (x.a.len < detail::span_elems(desc_.m, desc_.k, x.lda)) return Error::BufferTooSmall;
         if (x.b.len < (rrr ? detail::span_elems(desc_.k, desc_.n, x.ldb) : detail::span_elems(desc_.n, desc_.k, x.ldb)))
             return Error::BufferTooSmall;
         if (x.d.len < detail::span_elems(desc_.m, desc_.n, x.ldd)) return Error::BufferTooSmall;
+        if (x.c.ptr && x.c.len < detail::span_elems(desc_.m, desc_.n, x.ldc)) return Error::BufferTooSmall;
         if (!raw_) {
             if (!x.scale_a.ptr || !x.scale_b.ptr) return Error::InvalidProblem;
             const size_t na = mode_ == ScaleMode::PerRowCol ? static_cast<size_t>(desc_.m) : 1;
@@ -280,13 +284,13 @@ class Fp8ScaledGemmPlan {
         } else if (desc_.epilogue != EpilogueKind::Identity) {
             auto run = rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run
                            : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run;
-            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd, x.scale_a.ptr,
                      x.scale_b.ptr, static_cast<int32_t>(mode_), x.bias.ptr, static_cast<int32_t>(desc_.epilogue), x.alpha,
                      x.beta, ws.ptr, ws.bytes, stream);
         } else {
             auto run = rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run
                            : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run;
-            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, nullptr, 0, x.d.ptr, x.ldd, x.scale_a.ptr,
+            st = run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr, x.ldd, x.scale_a.ptr,
                      x.scale_b.ptr, static_cast<int32_t>(mode_), x.alpha, x.beta, ws.ptr, ws.bytes, stream);
         }
         return status_to_error(st);

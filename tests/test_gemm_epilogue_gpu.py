@@ -172,6 +172,73 @@ def test_bf16_out_bias_activation(oracle, family, layout, epi):
         assert np.array_equal(d.view(torch.int16).cpu().numpy().view(np.uint16), want_bits)
 
 
+@pytest.mark.parametrize("family", ["w8a8_s8", "fp8_e4m3"])
+@pytest.mark.parametrize("shape", [(300, 1096, 256), (1024, 2048, 128), (100, 70, 64)])
+@pytest.mark.parametrize("in_place", [False, True])
+def test_bf16_out_beta_c(oracle, family, shape, in_place):
+    """D = bf16(alpha * (sa*sb) * acc + beta * C [+ bias]) with C bf16 (the residual add of an o / down projection),
+    C separate with its own pitch or D itself; staged, ragged and CTA-pair store paths."""
+    m, n, k = shape
+    rng = np.random.default_rng(m + n + int(in_place))
+    if family == "w8a8_s8":
+        a = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+        b = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        acc = oracle.gemm_s8_s32(a, b, oracle.RCR, m, n, k)
+        sa = rng.uniform(0.001, 0.01, size=m).astype(np.float32)
+        sb = rng.uniform(0.001, 0.01, size=n).astype(np.float32)
+        y = oracle.dequant_s32_f32(acc, sa, sb)
+    else:
+        a = oracle.f32_to_e4m3(rng.standard_normal((m, k)).astype(np.float32))
+        b = oracle.f32_to_e4m3(rng.standard_normal((n, k)).astype(np.float32))
+        acc = oracle.gemm_e4m3_f32(a, b, oracle.RCR, m, n, k)
+        sa = rng.uniform(0.05, 0.2, size=m).astype(np.float32)
+        sb = rng.uniform(0.05, 0.2, size=n).astype(np.float32)
+        y = ((sa[:, None] * sb[None, :]).astype(np.float32) * acc).astype(np.float32)
+    alpha, beta = np.float32(0.5), np.float32(-1.25)
+    c_bits = oracle.f32_to_bf16_bits(rng.standard_normal((m, n)).astype(np.float32))
+    c = oracle.bf16_bits_to_f32(c_bits)
+    bias = rng.standard_normal(n).astype(np.float32)
+    z = ((y * alpha).astype(np.float32) + (beta * c).astype(np.float32)).astype(np.float32)
+    want = oracle.epilogue_chain(z, bias, 1)
+    lda = (k + 15) // 16 * 16
+    ad, bd = dev(pad_rows(a, lda)), dev(pad_rows(b, lda))
+    ldc = n if in_place else n + 3  # an odd pitch takes the scalar C loads
+    cd = torch.from_numpy(pad_rows(c_bits.view(np.int16), ldc)).cuda().view(torch.bfloat16)
+    d = cd if in_place else torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    sym = f"baracuda_kernels_gemm_{family}_rcr_bf16_sm100a_epilogue_run"
+    sad, sbd, biasd = dev(sa), dev(sb), dev(bias)
+    st = getattr(_lib.load(), sym)(m, n, k, ad.data_ptr(), lda, bd.data_ptr(), lda, cd.data_ptr(), ldc,
+                                   d.data_ptr(), n, sad.data_ptr(), sbd.data_ptr(), 1, biasd.data_ptr(), 1,
+                                   float(alpha), float(beta), None, 0, _stream())
+    assert st == 0
+    _status_clean()
+    got = d.float().cpu().numpy()
+    if family == "w8a8_s8":
+        assert np.array_equal(d.view(torch.int16).cpu().numpy().view(np.uint16), oracle.f32_to_bf16_bits(want))
+    else:
+        tol = np.abs(want) * 2.0 ** -7 + 1e-3
+        assert np.all(np.abs(got - want) <= tol)
+
+
+def test_bf16_out_beta_c_status_rules():
+    lib = _lib.load()
+    z = torch.zeros(1 << 16, dtype=torch.int8, device="cuda")
+    s = torch.ones(256, dtype=torch.float32, device="cuda")
+    d = torch.zeros(1 << 14, dtype=torch.bfloat16, device="cuda")
+    run = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run
+    can = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement
+    head = (64, 64, 64, z.data_ptr(), 64, z.data_ptr(), 64)
+    assert can(*head, d.data_ptr(), 64, d.data_ptr(), 64) == 0
+    assert can(*head, d.data_ptr(), 63, d.data_ptr(), 64) == 2                    # ldc < n
+    assert can(*head, d.data_ptr() + 1, 64, d.data_ptr(), 64) == 1                # C not 2-byte aligned
+    tail = (s.data_ptr(), s.data_ptr())
+    assert run(*head, None, 0, d.data_ptr(), 64, *tail, 1.0, 0.5, None, 0, _stream()) == 2   # beta without C
+    assert run(*head, d.data_ptr(), 64, d.data_ptr(), 64, *tail, 1.0, 0.0, None, 0, _stream()) == 0  # beta 0: C unread
+    raw = lib.baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement
+    assert raw(*head, d.data_ptr(), 64, d.data_ptr(), 64) == 3                    # the raw SKU takes no C
+    torch.cuda.synchronize()
+
+
 def test_epilogue_status_rules():
     lib = _lib.load()
     z = torch.zeros(4096, dtype=torch.int8, device="cuda")

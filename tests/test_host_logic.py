@@ -48,7 +48,9 @@ def test_gemm_can_implement_status_table(qlib):
     assert can(128, 256, 512, A + 4, 512, B, 512, None, 0, D, 256) == 1     # a not 16-byte aligned
     assert can(128, 256, 500, A, 500, B, 512, None, 0, D, 256) == 1         # lda not a multiple of 16
     assert can(128, 256, 500, A, 512, B, 512, None, 0, D, 256) == 0         # ragged k with padded pitch is fine
-    assert can(128, 256, 512, A, 512, B, 512, D, 256, D, 256) == 3          # beta*C not built
+    assert can(128, 256, 512, A, 512, B, 512, D, 256, D, 256) == 0          # C (bf16, may be D) is accepted
+    assert can(128, 256, 512, A, 512, B, 512, D, 255, D, 256) == 2          # ldc < n
+    assert can(128, 256, 512, A, 512, B, 512, D + 1, 256, D, 256) == 1      # C not 2-byte aligned
     assert can(0, 0, 0, None, 1, None, 1, None, 0, None, 1) == 0            # empty
     assert getattr(qlib, W8A8 + "_workspace_size")(128, 256, 512) == 0
 
@@ -82,8 +84,8 @@ def test_run_rejects_and_empty_without_a_gpu(qlib):
     assert run(0, 256, 512, None, 512, None, 512, None, 0, None, 256, None, None, 1.0, 0.0, None, 0, None) == 0
     # null operands on a non-empty problem
     assert run(128, 256, 512, None, 512, None, 512, None, 0, None, 256, None, None, 1.0, 0.0, None, 0, None) == 2
-    # beta != 0 is not built
-    assert run(128, 256, 512, 0x1000, 512, 0x2000, 512, None, 0, 0x3000, 256, 0x4000, 0x5000, 1.0, 0.5, None, 0, None) == 3
+    # beta != 0 needs C
+    assert run(128, 256, 512, 0x1000, 512, 0x2000, 512, None, 0, 0x3000, 256, 0x4000, 0x5000, 1.0, 0.5, None, 0, None) == 2
     assert qlib.baracuda_kernels_q_set_tuning(0, 100) == 2
     assert qlib.baracuda_kernels_q_set_tuning(0, 0) == 0
 
