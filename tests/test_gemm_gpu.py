@@ -402,3 +402,39 @@ def test_default_dispatch_over_random_shapes(oracle):
         torch.cuda.synchronize()
         assert lib.baracuda_kernels_q_device_status() == 0
         assert np.array_equal(d.cpu().numpy(), want), (m, n, k)
+
+
+def test_two_streams_share_nothing(oracle):
+    """Plans are plain data and the kernels keep no state between launches (ARCHITECTURE.md:253-282 of the reference:
+    caller-owned buffers and stream): a GEMM and a decode GEMV issued back to back on two streams, many times, give the
+    bits of the same calls run alone."""
+    m, n, k = 512, 2048, 1024
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=77)
+    gemm = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k))
+    a_d, w_d, sa_d, sb_d = dev(aq), dev(wq), dev(sa), dev(sb)
+    d_alone = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    gemm.run(None, None, bq.QGemmArgs(a=a_d, b=w_d, d=d_alone, scale_a=sa_d, scale_b=sb_d))
+    gk, gn = 4096, 14336
+    rng = np.random.default_rng(5)
+    xq = dev(rng.integers(-127, 128, size=(1, gk), dtype=np.int8))
+    gw = dev(rng.integers(-127, 128, size=(gn, gk), dtype=np.int8))
+    gsa, gsb = dev(np.array([0.01], dtype=np.float32)), dev(rng.random(gn, dtype=np.float32) * np.float32(0.001))
+    gemv = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(1, gn, gk, 1, layout=bq.LayoutSku.Rcr))
+    y_alone = torch.zeros((1, gn), dtype=torch.bfloat16, device="cuda")
+    gemv.run(None, None, bq.GemvQ8Args(a=xq, b=gw, d=y_alone, scale_a=gsa, scale_b=gsb))
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for i in range(12):
+        d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        y = torch.zeros((1, gn), dtype=torch.bfloat16, device="cuda")
+        outs.append((d, y))
+    torch.cuda.synchronize()
+    for d, y in outs:
+        gemm.run(s1, None, bq.QGemmArgs(a=a_d, b=w_d, d=d, scale_a=sa_d, scale_b=sb_d))
+        gemv.run(s2, None, bq.GemvQ8Args(a=xq, b=gw, d=y, scale_a=gsa, scale_b=gsb))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    for d, y in outs:
+        assert torch.equal(d.view(torch.int16), d_alone.view(torch.int16))
+        assert torch.equal(y.view(torch.int16), y_alone.view(torch.int16))
