@@ -3,6 +3,8 @@
 // or the raw int32 sums.  The weight matrix is streamed exactly once.  Kernels, in the order the dispatcher tries them:
 //   gemv_q8_rcr_mma_kernel      weights [N, K], m >= 2 (and m = 1 under dependent launch): bulk copies, mma.sync
 //   gemv_q8_rcr_stream_kernel   weights [N, K], m <= 4: bulk copies, dp4a + warp shuffles
+//   gemv_q8_rrr_umma_kernel     weights [K, N], one batch slot: tensor copies consumed as MN-major tcgen05 operands
+//                               (gemv_q8_umma.cuh); partial rows to the caller's scratch, a reduce kernel adds them
 //   gemv_q8_rrr_stream_kernel   weights [K, N]: tensor copies, byte-permute transposes, mma.sync; K is split over
 //                               CTAs, partial rows go to the caller's scratch, gemv_q8_rrr_reduce_kernel adds them
 //   gemv_q8_rcr_kernel / gemv_q8_rrr_kernel   128-bit loads that bypass L1 + dp4a, for shapes the above decline
@@ -62,6 +64,11 @@ struct GemvParams {
     int xq_qmin, xq_qmax;
     float* xq_scale_out;
     int pdl;  // launched with programmatic stream serialization: weights may be fetched before the dependency wait
+    // tcgen05 kernel for row-major weights: units of [128 K rows x 128 columns], column-tile major; CTA c owns units
+    // [c * gu_units / gu_ctas, (c + 1) * gu_units / gu_ctas); gu_partials is [gu_ctas][gu_smax][m][128]
+    int gu_kblocks, gu_smax, gu_ctas, gu_team;
+    int64_t gu_units;
+    int32_t* gu_partials;
 };
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
@@ -1374,6 +1381,8 @@ int32_t launch_rrr_stream(GemvParams p, int batch, const RsPlan& pl, const GemvD
     return BQ_STATUS_OK;
 }
 
+#include "gemv_q8_umma.cuh"
+
 template <bool RAW>
 int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     GemvParams p;
@@ -1391,6 +1400,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     p.rs_items_per_block = 0; p.rs_blocks = 0; p.rs_slots = 0; p.rs_run_max = 0; p.rs_ctas = 0;
     p.rs_partials = nullptr; p.rs_slots_total = 0;
     p.xq_x = nullptr; p.xq_ldx = 0; p.xq_qmin = -127; p.xq_qmax = 127; p.xq_scale_out = nullptr;
+    p.gu_kblocks = 0; p.gu_smax = 0; p.gu_ctas = 0; p.gu_team = 1; p.gu_units = 0; p.gu_partials = nullptr;
 
     // the streaming kernels need 16-byte alignment of every weight row segment they load
     bool fast = g.k > 0 && aligned16(g.a) && aligned16(g.b) && (g.stride_b % 16 == 0) && (g.ldb % 16 == 0);
@@ -1427,6 +1437,21 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
             case 2: return launch_rcr_stream<2, RAW>(p, g.batch, stream);
             case 3: return launch_rcr_stream<3, RAW>(p, g.batch, stream);
             default: return launch_rcr_stream<4, RAW>(p, g.batch, stream);
+        }
+    }
+    // N-contiguous weights, one batch slot: the tcgen05 kernel, which consumes the copied tiles without transposing them
+    // (variant 7 keeps the mma.sync streaming kernel, variant 8 the direct-load kernel)
+    if (g.layout == BQ_LAYOUT_RRR && g.variant != 8 && g.variant != 7 && g.batch == 1 &&
+        g.n * static_cast<int64_t>(g.k) >= (1 << 18) && (g.m == 1 || g.lda % 16 == 0)) {
+        // two CTAs per SM, each on its own run of units (variant 41: one per SM); variants 42 / 43 / 44 group the CTAs
+        // in teams of 4 / 8 / 16 that stream adjacent column tiles together (tuning and tests; measured no faster)
+        const int team = g.variant == 42 ? 4 : (g.variant == 43 ? 8 : (g.variant == 44 ? 16 : 1));
+        const GuPlan pl = plan_rrr_umma(g.m, g.n, g.k, sm_count_cached() * (g.variant == 41 ? 1 : 2), team);
+        const size_t need = gemv_q8_workspace_bytes(g.m, g.n, g.k, g.batch, BQ_LAYOUT_RRR);
+        if (pl.ok && pl.ws_bytes <= need) {
+            if (g.workspace == nullptr || g.workspace_bytes < need) return BQ_STATUS_WORKSPACE;
+            if (!aligned16(g.workspace)) return BQ_STATUS_MISALIGNED;
+            return launch_rrr_umma<RAW>(p, pl, g, stream);
         }
     }
     // N-contiguous weights: the tensor-copy streaming kernel (variant 8 keeps the direct-load kernel)

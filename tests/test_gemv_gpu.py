@@ -205,7 +205,7 @@ def test_dependent_launch_mode_gives_the_same_results(oracle):
         assert np.array_equal(bf16_bits(d), want)
 
 
-@pytest.mark.parametrize("variant", [0, 8])  # tensor-copy streaming kernel (default), direct-load split-K kernel
+@pytest.mark.parametrize("variant", [0, 41, 42, 43, 7, 8])  # tcgen05 kernel (default teams; teams of 1 / 4 / 8 CTAs), mma.sync streaming kernel, direct-load split-K kernel
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (2, 1040, 2064), (3, 272, 1000), (5, 14336, 512), (8, 2048, 4100),
                                    (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096), (2, 32768, 8192)])
 def test_both_row_major_weight_kernels_on_the_same_shapes(oracle, shape, variant):
@@ -223,6 +223,34 @@ def test_both_row_major_weight_kernels_on_the_same_shapes(oracle, shape, variant
     assert bq.device_status() == 0
     assert np.array_equal(got, want)
     assert np.array_equal(got_bf, oracle.dequant_s32_bf16(want, sa, sb))
+
+
+@pytest.mark.parametrize("shape", [(4, 14336, 4096), (8, 1024, 640), (1, 4096, 14336)])
+def test_row_major_weights_tensor_core_kernel_in_a_dependent_chain(oracle, shape):
+    """The tcgen05 kernel and its reduce kernel chained with programmatic stream serialization, several launches with
+    different activations sharing one workspace: a launch may not overwrite partial rows the previous reduce still reads."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=31 + m)
+    rng = np.random.default_rng(m)
+    acts = [aq] + [rng.integers(-127, 128, size=(m, k), dtype=np.int8) for _ in range(3)]
+    wants = [oracle.dequant_s32_bf16(oracle.gemm_s8_s32(a, wq, oracle.RCR, m, n, k), sa, sb) for a in acts]
+    plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=bq.LayoutSku.Rrr))
+    ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
+    b_d, sa_d, sb_d = dev(np.ascontiguousarray(wq.T)), dev(sa), dev(sb)
+    a_ds = [dev(a) for a in acts]
+    for pdl in (0, 1):
+        outs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in acts]
+        bq.set_tuning(3, pdl)
+        try:
+            for rep in range(3):
+                for a_d, d in zip(a_ds, outs):
+                    plan.run(None, ws, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d))
+            torch.cuda.synchronize()
+        finally:
+            bq.set_tuning(3, 0)
+        assert bq.device_status() == 0
+        for d, want in zip(outs, wants):
+            assert np.array_equal(bf16_bits(d), want), pdl
 
 
 def test_row_major_weights_strided_batch_and_dependent_launches(oracle):
