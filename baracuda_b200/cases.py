@@ -27,6 +27,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--buffers", type=int, default=3, help="distinct weight buffers rotated through (defeats L2 reuse)")
     ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--epilogue", default="identity", choices=["identity", "bias_gelu", "gated"],
+                    help="gemm --kind s8 only: fused bias + gelu, or the gated-MLP epilogue (n counts gate and up rows)")
     a = ap.parse_args()
 
     torch.cuda.set_device(0)
@@ -55,7 +57,16 @@ def main() -> None:
             mk = lambda r: torch.randn(r, k, device="cuda", generator=g).to(torch.float8_e4m3fn).view(torch.uint8)
         x = mk(m)
         weights = [mk(n) for _ in range(a.buffers)]
-        calls = [bq.QGemmArgs(a=x, b=w, d=d, scale_a=sa, scale_b=sb) for w in weights]
+        if a.epilogue == "gated" and a.kind == "s8":
+            plan = bq.GatedMlpUpPlan.select(None, bq.GatedMlpUpDescriptor(m, n // 2, k))
+            d = torch.empty((m, n // 2), dtype=torch.bfloat16, device="cuda")
+            calls = [bq.GatedMlpUpArgs(a=x, b_gate_up=w, d=d, scale_a=sa, scale_b=sb) for w in weights]
+        elif a.epilogue == "bias_gelu" and a.kind == "s8":
+            plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, epilogue=bq.EpilogueKind.BiasGelu))
+            bias = torch.randn(n, device="cuda", generator=g)
+            calls = [bq.QGemmArgs(a=x, b=w, d=d, scale_a=sa, scale_b=sb, bias=bias) for w in weights]
+        else:
+            calls = [bq.QGemmArgs(a=x, b=w, d=d, scale_a=sa, scale_b=sb) for w in weights]
         launch = lambda i: plan.run(None, None, calls[i % len(calls)])
 
     torch.cuda.synchronize()
