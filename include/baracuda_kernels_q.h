@@ -553,9 +553,11 @@ int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void
 
 /* ---------------------------------------------------------------------------
  * Diagnostics and tuning (no counterpart in the reference).
- * device_status: synchronous read-and-clear of the word a GEMM kernel sets
- * when one of its bounded barrier waits ran out (0 = none; 101..104 name the
- * waiting role).  Call it after synchronising the stream.
+ * device_status: synchronous read-and-clear of the word a kernel sets when one
+ * of its bounded barrier waits ran out (0 = none; the code names the kernel and
+ * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 121..125 wide
+ * GEMM, 131..134 tcgen05 GEMV, 201..206 streaming GEMVs, 299 the self-test).
+ * Call it after synchronising the stream.
  * set_tuning: key 0 forces the GEMM tile (0 = automatic; 64, 128, 256 = 1-CTA kernel with that N-tile;
  * 512 = the CTA-pair kernel); key 1 forces a GEMV kernel variant; key 2 forces the CTA-pair kernel's
  * tile width (0 = automatic, 256, 224, 192, 128); key 3 = 1 launches the K-contiguous streaming GEMV with
