@@ -442,7 +442,8 @@ int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
 
 int sm_count_of_current_device() { return sm_count_impl(); }
 
-bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k) {
+bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k,
+                             int l2_promotion) {
     auto enc = tensor_map_encoder();
     if (!enc) return false;
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(n_cols), static_cast<cuuint64_t>(k_rows)};
@@ -452,7 +453,7 @@ bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, in
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(static_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     static_cast<CUtensorMapL2promotion>(l2_promotion), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 

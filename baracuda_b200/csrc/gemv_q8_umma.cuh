@@ -288,7 +288,8 @@ int32_t launch_rrr_umma(GemvParams p, const GuPlan& pl, const GemvDesc& gd, cuda
     CUtensorMap map_x, map_b;
     if (!make_kmajor_tensor_map(&map_x, p.a, p.m, p.k, p.m > 1 ? p.lda : ((p.k + 15) / 16) * 16, 8))
         return BQ_STATUS_LAUNCH_FAILURE;
-    if (!make_mnmajor_tensor_map(&map_b, p.b, p.k, p.n, p.ldb, GU_BK)) return BQ_STATUS_LAUNCH_FAILURE;
+    // weights are read once: 128-byte L2 promotion measures 1-3 % faster than the 256-byte setting the GEMMs use
+    if (!make_mnmajor_tensor_map(&map_b, p.b, p.k, p.n, p.ldb, GU_BK, 2)) return BQ_STATUS_LAUNCH_FAILURE;
     p.gu_kblocks = pl.kblocks;
     p.gu_units = pl.units;
     p.gu_smax = pl.smax;

@@ -89,7 +89,9 @@ int32_t read_and_clear_gemm_wide_device_status();
 // helpers exported by the 1-CTA GEMM file
 bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
 // [k_rows x n_cols] bytes, N contiguous, row pitch ld; box = box_k rows x 128 bytes, 128-byte swizzle
-bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k);
+// l2_promotion: CUtensorMapL2promotion value (0 none, 1 64 B, 2 128 B, 3 256 B)
+bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k,
+                             int l2_promotion = 3);
 int sm_count_of_current_device();
 // D = bf16((sa*sb) * acc * alpha (+ bias)) for an [m, n] matrix of int32 (BQ_KIND_S8) or f32 (BQ_KIND_E4M3) accumulators.
 // Interleaves gate and up rows in blocks of 32 (the operand layout of GemmDesc::swiglu): rows of `row_bytes` bytes.
