@@ -43,6 +43,9 @@ from .plans import (  # noqa: F401
     QuantizedLinearPlan,
     QuantizePerTokenDescriptor,
     QuantizePerTokenPlan,
+    SmoothQuantLinearArgs,
+    SmoothQuantLinearDescriptor,
+    SmoothQuantLinearPlan,
     W8A8GemmPlan,
     device_status,
     set_tuning,

@@ -26,6 +26,11 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run": (_i32, _GEMM_PREFIX + [_vp, _vp, _f32, _f32] + _TAIL),
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size": _GEMM_WS,
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement": _GEMM_CAN,
+    "baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run": (
+        _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _f32, _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_workspace_size": _GEMM_WS,
+    "baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_can_implement": (
+        _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64]),
     "baracuda_kernels_gemm_s8_rcr_s32_sm100a_run": (_i32, _GEMM_PREFIX + [_f32, _f32] + _TAIL),
     "baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size": _GEMM_WS,
     "baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement": _GEMM_CAN,
@@ -68,6 +73,8 @@ SIGNATURES: dict[str, tuple] = {
        for fam in ("w8a8_s8", "fp8_e4m3") for lay in ("rcr", "rrr")},
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_run": (
         _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_pdl_run": (
+        _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size": _GEMV_WS,
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run": (
@@ -75,8 +82,11 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_capacity": (_sz, []),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run": (
         _i32, [_i32, _i32, _i32, _i32, _i32, _f32, _f32, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_pdl_run": (
+        _i32, [_i32, _i32, _i32, _i32, _i32, _f32, _f32, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement": (_i32, [_i32, _i32, _i32, _i64, _i64, _i64]),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
+    "baracuda_kernels_gemv_q8_m1_s32_sm100a_pdl_run": (_i32, _GEMV_HEAD + [_vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement": _GEMV_CAN,
     "baracuda_kernels_gemv_q8_m1_s32_sm100a_workspace_size": _GEMV_WS,
     "baracuda_kernels_quantize_per_token_sym_f32_s8_sm100a_run": (_i32, [_i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _i64] + _TAIL),
@@ -115,6 +125,7 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_q_nccl_comm_init_rank": (_i32, [C.POINTER(_vp), _i32, _vp, _i32]),
     "baracuda_q_nccl_comm_destroy": (_i32, [_vp]),
     "baracuda_q_nccl_stream_barrier": (_i32, [_vp, _vp, _vp]),
+    "baracuda_q_nccl_all_gather_bytes": (_i32, [_vp, _i32, _vp, _vp, _sz, _vp]),
     "baracuda_kernels_q_device_status": (_i32, []),
     "baracuda_kernels_q_set_tuning": (_i32, [_i32, _i32]),
 }

@@ -3,18 +3,20 @@
 // pointers -> 2, leading-dimension minimums -> 2, alignment -> 1), then the
 // launch.  No allocation, no host synchronisation, no library state.
 
-#include <atomic>
-
 #include "../../include/baracuda_kernels_q.h"
 #include "launch.h"
 
 namespace {
 
-std::atomic<int32_t> g_force_block_n{0};
-std::atomic<int32_t> g_gemv_variant{0};
-std::atomic<int32_t> g_force_pair_tile_n{0};
-std::atomic<int32_t> g_gemv_pdl{0};
-std::atomic<int32_t> g_direct_stores{0};
+// Test hooks of baracuda_kernels_q_set_tuning: per calling thread, so one thread forcing a kernel variant never
+// changes what another thread's launches do (the boundary keeps no process-wide mutable state).
+struct ThreadTuning {
+    int32_t force_block_n = 0;
+    int32_t gemv_variant = 0;
+    int32_t force_pair_tile_n = 0;
+    int32_t direct_stores = 0;
+};
+thread_local ThreadTuning t_tuning;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -133,9 +135,9 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.alpha = alpha;
     g.d = d;
     g.ldd = ldd;
-    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
-    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
-    g.direct_stores = g_direct_stores.load(std::memory_order_relaxed);
+    g.force_block_n = t_tuning.force_block_n;
+    g.force_pair_tile_n = t_tuning.force_pair_tile_n;
+    g.direct_stores = t_tuning.direct_stores;
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
@@ -194,8 +196,8 @@ int32_t gemm_swiglu_run(int32_t kind, int32_t m, int32_t n2, int32_t k, const vo
     g.bias = bias;
     g.bias_kind = bias ? 1 : 0;
     g.swiglu = 1;
-    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
-    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.force_block_n = t_tuning.force_block_n;
+    g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     if (g.force_pair_tile_n % 64 != 0) g.force_pair_tile_n = 0;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
@@ -240,8 +242,8 @@ int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t 
     g.alpha = alpha;
     g.d = d;
     g.ldd = ldd;
-    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
-    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.force_block_n = t_tuning.force_block_n;
+    g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     epilogue_apply(epi, g);
     g.direct_stores = 1;
     g.n_peers = 0;
@@ -271,7 +273,7 @@ int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, in
                  float beta, const void* a, int64_t lda, int64_t stride_a, const void* b, int64_t ldb,
                  int64_t stride_b, const void* scale_a, int64_t stride_scale_a, const void* scale_b,
                  int64_t stride_scale_b, void* d, int64_t ldd, int64_t stride_d, void* workspace,
-                 size_t workspace_bytes, void* stream) {
+                 size_t workspace_bytes, void* stream, int32_t pdl = 0) {
     const int32_t st = gemv_validate(m, n, k, batch, layout, lda, ldb, ldd, stride_d);
     if (st != bq::BQ_STATUS_OK) return st;
     if (m == 0 || n == 0 || batch == 0) return bq::BQ_STATUS_OK;
@@ -305,8 +307,8 @@ int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, in
     g.stride_d = stride_d;
     g.workspace = workspace;
     g.workspace_bytes = workspace_bytes;
-    g.variant = g_gemv_variant.load(std::memory_order_relaxed);
-    g.pdl = g_gemv_pdl.load(std::memory_order_relaxed);
+    g.variant = t_tuning.gemv_variant;
+    g.pdl = pdl;
     return bq::launch_gemv_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -345,9 +347,9 @@ int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t 
     g.alpha = alpha;
     g.d = d;
     g.ldd = ldd;
-    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
-    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
-    g.direct_stores = g_direct_stores.load(std::memory_order_relaxed);
+    g.force_block_n = t_tuning.force_block_n;
+    g.force_pair_tile_n = t_tuning.force_pair_tile_n;
+    g.direct_stores = t_tuning.direct_stores;
     g.q8_out = 0;
     g.c = nullptr;
     g.ldc = 0;
@@ -387,8 +389,8 @@ int32_t bq::launch_gemm_raw_reduce_scatter_checked(int32_t kind, int32_t m, int3
     g.alpha = 1.0f;
     g.d = staging[rank];  // alignment probe only: every row is stored through peer_d
     g.ldd = n;
-    g.force_block_n = g_force_block_n.load(std::memory_order_relaxed);
-    g.force_pair_tile_n = g_force_pair_tile_n.load(std::memory_order_relaxed);
+    g.force_block_n = t_tuning.force_block_n;
+    g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     g.direct_stores = 1;
     g.peer_rank = rank;
     g.rs_world = world;
@@ -457,6 +459,45 @@ int32_t baracuda_kernels_q_interleave_gate_up_run(int64_t f_rows, int64_t row_by
     if (gate_pitch < row_bytes || up_pitch < row_bytes || out_pitch < row_bytes) return bq::BQ_STATUS_INVALID_PROBLEM;
     return bq::launch_interleave_gate_up(f_rows, row_bytes, gate, gate_pitch, up, up_pitch, out, out_pitch,
                                          static_cast<cudaStream_t>(stream));
+}
+
+// ---- W8A8 with one per-tensor activation scale passed by value (SmoothQuant inference) -------------------
+int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_can_implement(int32_t m, int32_t n, int32_t k, const void* act_q,
+                                                                           int64_t lda, const void* weight_q, int64_t ldb,
+                                                                           const void* output, int64_t ldd) {
+    return gemm_rcr_bf16_validate(m, n, k, act_q, lda, weight_q, ldb, nullptr, 0, output, ldd);
+}
+size_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
+int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k, const void* act_q, int64_t lda, const void* weight_q, int64_t ldb, float act_scale,
+    const void* weight_scale, void* output, int64_t ldd, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    const int32_t st = gemm_rcr_bf16_validate(m, n, k, act_q, lda, weight_q, ldb, nullptr, 0, output, ldd);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
+    if (!output || (k > 0 && (!act_q || !weight_q)) || !weight_scale) return bq::BQ_STATUS_INVALID_PROBLEM;
+    bq::GemmDesc g = {};
+    g.b_layout = bq::BQ_LAYOUT_RCR;
+    g.kind = bq::BQ_KIND_S8;
+    g.m = m;
+    g.n = n;
+    g.k = k;
+    g.a = act_q;
+    g.lda = lda;
+    g.b = weight_q;
+    g.ldb = ldb;
+    g.scale_a = nullptr;
+    g.sa_const = act_scale;
+    g.scale_b = static_cast<const float*>(weight_scale);
+    g.scale_mode = 2;
+    g.alpha = 1.0f;
+    g.d = output;
+    g.ldd = ldd;
+    g.force_block_n = t_tuning.force_block_n;
+    g.force_pair_tile_n = t_tuning.force_pair_tile_n;
+    g.direct_stores = t_tuning.direct_stores;
+    return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
 // ---- s8 -> s32 accumulators --------------------------------------------------
@@ -680,6 +721,14 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
     return gemv_run(0, m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb, stride_b, scale_a,
                     stride_scale_a, scale_b, stride_scale_b, d, ldd, stride_d, workspace, workspace_bytes, stream);
 }
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_pdl_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, float alpha, float beta, const void* a,
+    int64_t lda, int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, const void* scale_a,
+    int64_t stride_scale_a, const void* scale_b, int64_t stride_scale_b, void* d, int64_t ldd, int64_t stride_d,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    return gemv_run(0, m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb, stride_b, scale_a,
+                    stride_scale_a, scale_b, stride_scale_b, d, ldd, stride_d, workspace, workspace_bytes, stream, 1);
+}
 int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, int64_t lda, int64_t ldb, int64_t ldd,
     int64_t stride_a, int64_t stride_b, int64_t stride_d) {
@@ -698,6 +747,13 @@ int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
     int64_t stride_d, void* workspace, size_t workspace_bytes, void* stream) {
     return gemv_run(1, m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb, stride_b, nullptr, 0, nullptr,
                     0, d, ldd, stride_d, workspace, workspace_bytes, stream);
+}
+int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_pdl_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, float alpha, float beta, const void* a,
+    int64_t lda, int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, void* d, int64_t ldd,
+    int64_t stride_d, void* workspace, size_t workspace_bytes, void* stream) {
+    return gemv_run(1, m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb, stride_b, nullptr, 0, nullptr,
+                    0, d, ldd, stride_d, workspace, workspace_bytes, stream, 1);
 }
 int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, int64_t lda, int64_t ldb, int64_t ldd,
@@ -722,12 +778,10 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(int32_t
     return bq::gemv_q8_quant_bf16_supported(m, n, k) ? bq::BQ_STATUS_OK : bq::BQ_STATUS_UNSUPPORTED;
 }
 
-int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
-    int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta, const void* x_bf16,
-    int64_t ldx, const void* b, int64_t ldb, const void* scale_b, void* scale_a_out, void* d, int64_t ldd,
-    void* workspace, size_t workspace_bytes, void* stream) {
-    (void)workspace;
-    (void)workspace_bytes;
+namespace {
+int32_t gemv_quant_bf16_run(int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta,
+                            const void* x_bf16, int64_t ldx, const void* b, int64_t ldb, const void* scale_b,
+                            void* scale_a_out, void* d, int64_t ldd, int32_t pdl, void* stream) {
     const int32_t st = baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(m, n, k, ldx, ldb, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
@@ -735,8 +789,28 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
     if (qmin > qmax || qmax <= 0 || qmin < -128 || qmax > 127) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (!aligned16(x_bf16) || !aligned16(b)) return bq::BQ_STATUS_UNSUPPORTED;
     return bq::launch_gemv_q8_quant_bf16(m, n, k, qmin, qmax, alpha, beta, x_bf16, ldx, static_cast<const int8_t*>(b), ldb,
-                                         static_cast<const float*>(scale_b), static_cast<float*>(scale_a_out), d, ldd,
-                                         g_gemv_pdl.load(std::memory_order_relaxed), static_cast<cudaStream_t>(stream));
+                                         static_cast<const float*>(scale_b), static_cast<float*>(scale_a_out), d, ldd, pdl,
+                                         static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
+    int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta, const void* x_bf16,
+    int64_t ldx, const void* b, int64_t ldb, const void* scale_b, void* scale_a_out, void* d, int64_t ldd,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemv_quant_bf16_run(m, n, k, qmin, qmax, alpha, beta, x_bf16, ldx, b, ldb, scale_b, scale_a_out, d, ldd, 0,
+                               stream);
+}
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_pdl_run(
+    int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax, float alpha, float beta, const void* x_bf16,
+    int64_t ldx, const void* b, int64_t ldb, const void* scale_b, void* scale_a_out, void* d, int64_t ldd,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return gemv_quant_bf16_run(m, n, k, qmin, qmax, alpha, beta, x_bf16, ldx, b, ldb, scale_b, scale_a_out, d, ldd, 1,
+                               stream);
 }
 
 // ---- diagnostics / tuning -------------------------------------------------------------
@@ -744,8 +818,6 @@ int32_t baracuda_kernels_q_device_status(void) {
     int32_t gemm = bq::read_and_clear_gemm_device_status();
     const int32_t pair = bq::read_and_clear_gemm_pair_device_status();
     if (gemm == 0) gemm = pair;
-    const int32_t wide = bq::read_and_clear_gemm_wide_device_status();
-    if (gemm == 0) gemm = wide;
     const int32_t gemv = bq::read_and_clear_gemv_device_status();
     return gemm != 0 ? gemm : gemv;
 }
@@ -757,23 +829,22 @@ int32_t baracuda_kernels_q_selftest_bounded_wait(int64_t limit_cycles, void* str
 int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
     switch (key) {
         case 0:
-            if (value != 0 && value != 64 && value != 128 && value != 256 && value != 512 && value != 1024) return bq::BQ_STATUS_INVALID_PROBLEM;
-            g_force_block_n.store(value);
+            if (value != 0 && value != 64 && value != 128 && value != 256 && value != 512) return bq::BQ_STATUS_INVALID_PROBLEM;
+            t_tuning.force_block_n = value;
             return bq::BQ_STATUS_OK;
         case 1:
-            g_gemv_variant.store(value);
-            return bq::BQ_STATUS_OK;
-        case 3:
-            g_gemv_pdl.store(value != 0 ? 1 : 0);
+            if (value != 0 && value != 1 && value != 2 && value != 3 && value != 7 && value != 8 && value != 9)
+                return bq::BQ_STATUS_INVALID_PROBLEM;
+            t_tuning.gemv_variant = value;
             return bq::BQ_STATUS_OK;
         case 4:
             if (value < 0 || value > 2) return bq::BQ_STATUS_INVALID_PROBLEM;
-            g_direct_stores.store(value);
+            t_tuning.direct_stores = value;
             return bq::BQ_STATUS_OK;
         case 2:
             if (value != 0 && value != 256 && value != 224 && value != 192 && value != 128)
                 return bq::BQ_STATUS_INVALID_PROBLEM;
-            g_force_pair_tile_n.store(value);
+            t_tuning.force_pair_tile_n = value;
             return bq::BQ_STATUS_OK;
         default:
             return bq::BQ_STATUS_INVALID_PROBLEM;

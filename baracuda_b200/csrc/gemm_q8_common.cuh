@@ -17,7 +17,8 @@ struct GemmParams {
     int64_t ldd;
     const float* sa;
     const float* sb;
-    int scale_mode;  // 0: sa/sb point at one float each; 1: sa[M], sb[N]
+    int scale_mode;  // 0: sa/sb point at one float each; 1: sa[M], sb[N]; 2: sa_const (by value) and sb[N]
+    float sa_const;
     float alpha;
     int m, n, k;
     int m_tiles, n_tiles;

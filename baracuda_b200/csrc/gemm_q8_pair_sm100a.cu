@@ -205,7 +205,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 __syncwarp();
                 for (int i = lane; i < PAIR_TILE_N; i += 32) {
                     const int col = n_blk * PAIR_TILE_N + i;
-                    if (!p.out_q8) sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                    if (!p.out_q8) sb_tile[i] = (p.scale_mode != 0) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
                     if (p.bias_kind == 1) {
                         sb_tile[p.bias_off + i] = col < p.n ? __ldg(reinterpret_cast<const float*>(p.bias) + col) : 0.0f;
                     } else if (p.bias_kind == 2) {
@@ -224,7 +224,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const bool row_ok = row < p.m;
             float sa_row = 1.0f;
             if (!RAW && !p.out_q8) {
-                sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
+                sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : (p.scale_mode == 2 ? p.sa_const : __ldg(p.sa));
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
@@ -309,6 +309,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     p.sa = g.scale_a;
     p.sb = g.scale_b;
     p.scale_mode = g.scale_mode;
+    p.sa_const = g.sa_const;
     p.alpha = g.alpha;
     p.m = g.m;
     p.n = g.n;

@@ -192,7 +192,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 __syncwarp();
                 for (int i = lane; i < BLOCK_N; i += 32) {
                     const int col = n_blk * BLOCK_N + i;
-                    if (!p.out_q8) sb_tile[i] = (p.scale_mode == 1) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                    if (!p.out_q8) sb_tile[i] = (p.scale_mode != 0) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
                     if (p.bias_kind == 1) {
                         sb_tile[p.bias_off + i] = col < p.n ? __ldg(reinterpret_cast<const float*>(p.bias) + col) : 0.0f;
                     } else if (p.bias_kind == 2) {
@@ -211,7 +211,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             const bool row_ok = row < p.m;
             float sa_row = 1.0f;
             if (!RAW && !p.out_q8) {
-                sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : __ldg(p.sa);
+                sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : (p.scale_mode == 2 ? p.sa_const : __ldg(p.sa));
             }
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * BLOCK_N);
@@ -340,6 +340,7 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.sa = g.scale_a;
     p.sb = g.scale_b;
     p.scale_mode = g.scale_mode;
+    p.sa_const = g.sa_const;
     p.alpha = g.alpha;
     p.m = g.m;
     p.n = g.n;
@@ -388,7 +389,6 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
     if (g.b_layout == BQ_LAYOUT_RRR) return launch_gemm_q8_pair(g, stream);  // row-major weights: CTA-pair kernel only
-    if (g.force_block_n == 1024 && !g.swiglu) return launch_gemm_q8_wide(g, stream);
     // 256 x 256 tiles on CTA pairs (force_block_n 512 forces it, 256/128/64 forces it off) from 24 such tiles up:
     // measured at M = 512, K = 4096..14336 (32 to 48 tiles) the pair kernel is 1.4-1.7x faster than 128 x 64 tiles
     // on every SM, whose operand traffic per MAC is three times higher; at 16 tiles the narrow tiles still win.

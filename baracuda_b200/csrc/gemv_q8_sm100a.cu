@@ -1118,15 +1118,8 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int sm_count_cached() {
-    static int cached = 0;
-    if (cached > 0) return cached;
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    cached = n;  // the GPUs of one box are identical
-    return n;
-}
+// per-device SM count (cached under a mutex by the GEMM file)
+int sm_count_cached() { return sm_count_of_current_device(); }
 
 template <int MR, bool RAW, int NW, int RING>
 int32_t launch_rcr_stream_cfg(const GemvParams& p, int batch, int sms, cudaStream_t stream) {
@@ -1213,30 +1206,21 @@ int mma_xreg_config(const GemvParams& p) {
 }
 
 template <bool RAW>
-int32_t launch_rcr_mma(const GemvParams& p, int batch, int shape_variant, cudaStream_t stream) {
+int32_t launch_rcr_mma(const GemvParams& p, int batch, cudaStream_t stream) {
     const int sms = sm_count_cached();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
-    // 32 = 2 KiB copies on 4 warps, 33 = 512-byte copies on 16 warps, 34 = three items in flight per warp
-    if (shape_variant == 32 && p.k <= 4096) return launch_rcr_mma_cfg<RAW, 2048, 4, 2>(p, batch, sms, stream);
-    if (shape_variant == 33) return launch_rcr_mma_cfg<RAW, 512, 16, 2>(p, batch, sms, stream);
-    const int want = (p.n + MMA_COLS - 1) / MMA_COLS;
-    const int ctas = want < sms ? want : sms;
-    const int groups = (want + ctas - 1) / ctas;
-    // 35: 512-byte copies on 16 warps, three items in flight, activations in registers -- when K is a whole number of
-    // 512-byte chunks that divides 16 (K = 512, 1024, 2048, 4096, 8192)
-    // (the default where it applies: 13.3 us against 16.5 us at m = 2..8, K = 4096, N = 14336; 36 keeps it off)
-    switch ((shape_variant == 35 || shape_variant == 0 || shape_variant == 3) ? mma_xreg_config(p) : 0) {
+    // 512-byte (or 448-byte) copies on 16 warps, three items in flight, activations in registers -- when K is a whole
+    // number of such chunks that divides (or is twice) the warp count: 13.3 us against 16.5 us at m = 2..8,
+    // K = 4096, N = 14336
+    switch (mma_xreg_config(p)) {
         case 1: return launch_rcr_mma_cfg<RAW, 512, 16, 3, true>(p, batch, sms, stream);
         case 2: return launch_rcr_mma_cfg<RAW, 512, 16, 3, true, false, 2>(p, batch, sms, stream);
         case 3: return launch_rcr_mma_cfg<RAW, 448, 16, 3, true, false, 2>(p, batch, sms, stream);
         case 4: return launch_rcr_mma_cfg<RAW, 448, 16, 3, true>(p, batch, sms, stream);
         default: break;
     }
-    if (p.k > MMA_MAX_K) return BQ_STATUS_UNSUPPORTED;  // the staged-activation configurations below hold all of K in shared memory
-    // otherwise: 1 KiB copies on 8 warps, two items in flight per warp (a third measured no faster)
-    if (shape_variant == 34 && mma_smem_bytes(1024, 8, 3, p.m, p.k, groups) <= 232448) {
-        return launch_rcr_mma_cfg<RAW, 1024, 8, 3>(p, batch, sms, stream);
-    }
+    if (p.k > MMA_MAX_K) return BQ_STATUS_UNSUPPORTED;  // the staged-activation configuration holds all of K in shared memory
+    // any other K: 1 KiB copies on 8 warps, two items in flight per warp (a third measured no faster)
     return launch_rcr_mma_cfg<RAW, 1024, 8, 2>(p, batch, sms, stream);
 }
 
@@ -1415,19 +1399,18 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
         gemv_q8_generic_kernel<RAW><<<dim3(blocks, g.batch), GEMV_THREADS, 0, stream>>>(p, g.layout);
         return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
     }
+    // Test hooks (set_tuning key 1): 1 = bulk-copy dp4a kernel where legal, 2 = register-streaming kernel, 3 = tensor-core
+    // streaming kernel also for m == 1, 7 = mma.sync streaming kernel for row-major weights, 8 = direct-load split-K
+    // kernel for row-major weights, 9 = byte-load kernel.
     // K-contiguous weights, two or more activation rows: tensor-core streaming kernel
-    // (variant 3 forces it also for m == 1, variant 2 and 1 keep it off)
-    // (K beyond the activation staging area is only served by the register-activation configurations: variants 0, 3, 35)
-    const bool mma_ok = g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p) &&
-                        (g.k <= MMA_MAX_K || g.variant == 0 || g.variant == 3 || g.variant == 35);
+    const bool mma_ok = g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p);
     if (mma_ok &&
         ((g.variant == 0 && g.m >= 2 && g.n * static_cast<int64_t>(g.k) >= (1 << 20)) || g.variant == 3 ||
-         (g.variant >= 31 && g.variant <= 36) ||  // 31..36 force a copy-size / ring configuration
          // m = 1: the 16-warp tensor-core kernel also wins under dependent launch, and for the long K of a down
          // projection (14.9 us against 16.5 us at K = 14336, N = 4096)
          (g.variant == 0 && g.m == 1 && ((g.pdl && mma_xreg_config(p) != 0) || mma_xreg_config(p) >= 2) &&
           g.n * static_cast<int64_t>(g.k) >= (1 << 20)))) {
-        return launch_rcr_mma<RAW>(p, g.batch, g.variant, stream);
+        return launch_rcr_mma<RAW>(p, g.batch, stream);
     }
     // K-contiguous weights with few activation rows: the bulk-copy streaming kernel
     // (variant 2 forces it off, variant 1 forces it on where it is legal)
@@ -1443,10 +1426,8 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     // (variant 7 keeps the mma.sync streaming kernel, variant 8 the direct-load kernel)
     if (g.layout == BQ_LAYOUT_RRR && g.variant != 8 && g.variant != 7 && g.batch == 1 &&
         g.n * static_cast<int64_t>(g.k) >= (1 << 18) && (g.m == 1 || g.lda % 16 == 0)) {
-        // two CTAs per SM, each on its own run of units (variant 41: one per SM); variants 42 / 43 / 44 group the CTAs
-        // in teams of 4 / 8 / 16 that stream adjacent column tiles together (tuning and tests; measured no faster)
-        const int team = g.variant == 42 ? 4 : (g.variant == 43 ? 8 : (g.variant == 44 ? 16 : 1));
-        const GuPlan pl = plan_rrr_umma(g.m, g.n, g.k, sm_count_cached() * (g.variant == 41 ? 1 : 2), team);
+        // two CTAs per SM, each on its own run of units
+        const GuPlan pl = plan_rrr_umma(g.m, g.n, g.k, sm_count_cached() * 2, 1);
         const size_t need = gemv_q8_workspace_bytes(g.m, g.n, g.k, g.batch, BQ_LAYOUT_RRR);
         if (pl.ok && pl.ws_bytes <= need) {
             if (g.workspace == nullptr || g.workspace_bytes < need) return BQ_STATUS_WORKSPACE;

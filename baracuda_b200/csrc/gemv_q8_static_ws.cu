@@ -62,15 +62,21 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run(
     int64_t lda, int64_t stride_a, const void* b, int64_t ldb, int64_t stride_b, const void* scale_a,
     int64_t stride_scale_a, const void* scale_b, int64_t stride_scale_b, void* d, int64_t ldd, int64_t stride_d,
     void* stream) {
-    // the scratch this shape needs must fit the fixed array
+    // the regular entry point's checks first, in its order, so that an invalid problem reports the same status here
+    const int32_t st = baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(m, n, k, batch, layout, lda, ldb, ldd, stride_a,
+                                                                             stride_b, stride_d);
+    if (st != bq::BQ_STATUS_OK) return st;
+    if (m == 0 || n == 0 || batch == 0) return bq::BQ_STATUS_OK;
+    if (!a || !b || !d || !scale_a || !scale_b) return bq::BQ_STATUS_INVALID_PROBLEM;
+    // only then: the scratch this shape needs must fit the fixed array
     const size_t need = baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size(m, n, k, batch, layout);
     if (need > BARACUDA_Q_GEMV_STATIC_SCRATCH_BYTES) return bq::BQ_STATUS_WORKSPACE;
     void* scratch = nullptr;
     if (need > 0) {
-        const int32_t st = scratch_for_current_device(&scratch);
-        if (st != bq::BQ_STATUS_OK) return st;
+        const int32_t ss = scratch_for_current_device(&scratch);
+        if (ss != bq::BQ_STATUS_OK) return ss;
     }
-    // same validation, same kernels as the regular entry point; only the scratch differs
+    // same kernels as the regular entry point; only the scratch differs
     return baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(m, n, k, batch, layout, alpha, beta, a, lda, stride_a, b, ldb,
                                                        stride_b, scale_a, stride_scale_a, scale_b, stride_scale_b, d, ldd,
                                                        stride_d, scratch, need, stream);

@@ -39,7 +39,8 @@ struct GemmDesc {
     int64_t ldb;
     const float* scale_a;
     const float* scale_b;
-    int32_t scale_mode;  // 0 per-tensor scalars, 1 per-row / per-column vectors
+    int32_t scale_mode;  // 0 per-tensor scalars, 1 per-row / per-column vectors, 2 sa_const by value + per-column vector
+    float sa_const;
     float alpha;
     void* d;
     int64_t ldd;
@@ -83,9 +84,6 @@ int32_t read_and_clear_gemm_device_status();
 // CTA-pair (cta_group::2) variant: 256 x 256 output tiles shared by two SMs.
 int32_t launch_gemm_q8_pair(const GemmDesc& g, cudaStream_t stream);
 int32_t read_and_clear_gemm_pair_device_status();
-// CTA-pair variant with 256 x 512 tiles (two 256-column accumulator halves).
-int32_t launch_gemm_q8_wide(const GemmDesc& g, cudaStream_t stream);
-int32_t read_and_clear_gemm_wide_device_status();
 // helpers exported by the 1-CTA GEMM file
 bool make_kmajor_tensor_map(void* map_out, const void* base, int64_t rows, int64_t k, int64_t ld, int box_rows);
 // [k_rows x n_cols] bytes, N contiguous, row pitch ld; box = box_k rows x 128 bytes, 128-byte swizzle

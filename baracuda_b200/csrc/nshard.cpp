@@ -235,6 +235,24 @@ int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void
                : BARACUDA_Q_STATUS_COMM_FAILURE;
 }
 
+int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* send, void* recv, size_t bytes_per_rank,
+                                         void* stream) {
+    if (world < 1 || (!send && bytes_per_rank) || (!recv && bytes_per_rank)) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (bytes_per_rank == 0) return BARACUDA_Q_STATUS_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (world == 1) {
+        if (recv != send && cudaMemcpyAsync(recv, send, bytes_per_rank, cudaMemcpyDeviceToDevice, s) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return BARACUDA_Q_STATUS_LAUNCH_FAILURE;
+        }
+        return BARACUDA_Q_STATUS_OK;
+    }
+    if (!comm) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    return nccl().AllGather(send, recv, bytes_per_rank, kNcclInt8, comm, s) == 0 ? BARACUDA_Q_STATUS_OK
+                                                                                 : BARACUDA_Q_STATUS_COMM_FAILURE;
+}
+
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(
     int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local, int32_t k, const void* a,
     int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd, const void* scale_a,

@@ -21,7 +21,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from .plans import SCALE_PER_ROW_COL, _ptr, _stream_ptr
+from .plans import SCALE_PER_ROW_COL, _need_typed, _ptr, _stream_ptr
 from .vocab import BaracudaError, InvalidProblem, status_to_result
 
 GATHER_NONE = 0
@@ -132,16 +132,41 @@ class ColumnParallelQGemmPlan:
         self.n_local, self.col0 = hi - lo, lo
         self.kind, self.scale_mode, self.gather = kind, scale_mode, gather
 
+    def _operand_dtypes(self):
+        return (torch.int8,) if self.kind == "w8a8" else (torch.uint8, torch.float8_e4m3fn)
+
+    def replicate_activations(self, stream, a_rows: torch.Tensor, scale_a_rows: torch.Tensor, a_full: torch.Tensor,
+                              scale_a_full: torch.Tensor) -> None:
+        """Each rank holds rows [rank*M/G, (rank+1)*M/G) of the activations (and of scale_a), e.g. freshly uploaded
+        from the host; all-gathers them over NVLink into the replicated [M, K] / [M] buffers the forward reads, so a
+        step moves M*K/G bytes over each GPU's host link instead of M*K.  M must divide by the world size."""
+        g = self.ctx.world
+        if self.m % g != 0:
+            raise InvalidProblem(f"M = {self.m} is not divisible by the world size {g}")
+        rows = self.m // g
+        _need_typed(a_rows, self._operand_dtypes(), rows * self.k, "a_rows")
+        _need_typed(a_full, self._operand_dtypes(), self.m * self.k, "a_full")
+        _need_typed(scale_a_rows, torch.float32, rows, "scale_a_rows")
+        _need_typed(scale_a_full, torch.float32, self.m, "scale_a_full")
+        lib = _lib.load()
+        s = _stream_ptr(stream)
+        _check(lib.baracuda_q_nccl_all_gather_bytes(self.ctx.comm, g, _ptr(a_rows), _ptr(a_full), rows * self.k, s),
+               "replicate_activations")
+        _check(lib.baracuda_q_nccl_all_gather_bytes(self.ctx.comm, g, _ptr(scale_a_rows), _ptr(scale_a_full), rows * 4, s),
+               "replicate_activations")
+
     def forward(self, stream, a: torch.Tensor, scale_a: torch.Tensor, w_local: torch.Tensor,
                 scale_b_local: torch.Tensor, y_local: torch.Tensor, y_full: Optional[torch.Tensor] = None,
                 peer_ptrs: Optional[Sequence[int]] = None, ldd_full: int = 0, alpha: float = 1.0) -> None:
         """Y_local[M, N/G] = dequant(A x W_local^T); then the selected gather.  Asynchronous on `stream`."""
-        if a.numel() < self.m * self.k or w_local.numel() < self.n_local * self.k:
-            raise InvalidProblem("operand shorter than the descriptor says")
-        if y_local.numel() < self.m * self.n_local:
-            raise InvalidProblem("y_local shorter than [M, N/G]")
-        if self.gather == GATHER_NCCL and (y_full is None or y_full.numel() < self.m * self.n):
-            raise InvalidProblem("y_full must hold [G, M, N/G]")
+        per_vec = self.kind == "w8a8" or self.scale_mode == SCALE_PER_ROW_COL
+        _need_typed(a, self._operand_dtypes(), self.m * self.k, "a")
+        _need_typed(w_local, self._operand_dtypes(), self.n_local * self.k, "w_local")
+        _need_typed(scale_a, torch.float32, self.m if per_vec else 1, "scale_a")
+        _need_typed(scale_b_local, torch.float32, self.n_local if per_vec else 1, "scale_b_local")
+        _need_typed(y_local, torch.bfloat16, self.m * self.n_local, "y_local")
+        if self.gather == GATHER_NCCL:
+            _need_typed(y_full, torch.bfloat16, self.m * self.n, "y_full")
         peers = None
         if self.gather == GATHER_FUSED_PEER_STORE:
             if peer_ptrs is None or len(peer_ptrs) != self.ctx.world:
@@ -187,16 +212,22 @@ class RowParallelQGemmPlan:
     def workspace_size(self) -> int:
         return int(_lib.load().baracuda_kernels_gemm_q8_kshard_workspace_size(self.m, self.n))
 
+    def _check_operands(self, a_local, scale_a, w_local, scale_b, bias) -> None:
+        ops = (torch.int8,) if self.kind == "w8a8" else (torch.uint8, torch.float8_e4m3fn)
+        per_vec = self.kind == "w8a8" or self.scale_mode == SCALE_PER_ROW_COL
+        _need_typed(a_local, ops, self.m * self.k_local, "a_local")
+        _need_typed(w_local, ops, self.n * self.k_local, "w_local")
+        _need_typed(scale_a, torch.float32, self.m if per_vec else 1, "scale_a")
+        _need_typed(scale_b, torch.float32, self.n if per_vec else 1, "scale_b")
+        if bias is not None:
+            _need_typed(bias, torch.float32, self.n, "bias")
+
     def forward(self, stream, a_local: torch.Tensor, scale_a: torch.Tensor, w_local: torch.Tensor,
                 scale_b: torch.Tensor, y: torch.Tensor, workspace: torch.Tensor,
                 bias: Optional[torch.Tensor] = None, alpha: float = 1.0) -> None:
         """Y[M, N] = bf16((scale_a x scale_b) * sum_ranks(A_local x W_local^T) * alpha + bias) on every rank."""
-        if a_local.numel() < self.m * self.k_local or w_local.numel() < self.n * self.k_local:
-            raise InvalidProblem("operand shorter than the descriptor says")
-        if y.numel() < self.m * self.n:
-            raise InvalidProblem("y shorter than [M, N]")
-        if bias is not None and (bias.dtype != torch.float32 or bias.numel() < self.n):
-            raise InvalidProblem("bias must be float32[N]")
+        self._check_operands(a_local, scale_a, w_local, scale_b, bias)
+        _need_typed(y, torch.bfloat16, self.m * self.n, "y")
         ws_bytes = workspace.numel() * workspace.element_size()
         lib = _lib.load()
         common = (self.ctx.rank, self.ctx.world, self.ctx.comm, self.reduce, self.m, self.n, self.k_local,
@@ -219,8 +250,8 @@ class RowParallelQGemmPlan:
             raise InvalidProblem("plan was not built for the fused mode")
         if len(peer_y) != self.ctx.world or len(peer_staging) != self.ctx.world:
             raise InvalidProblem("one pointer per rank is needed")
-        if a_local.numel() < self.m * self.k_local or w_local.numel() < self.n * self.k_local:
-            raise InvalidProblem("operand shorter than the descriptor says")
+        self._check_operands(a_local, scale_a, w_local, scale_b, bias)
+        _need_typed(barrier_scratch, torch.float32, 1, "barrier_scratch")
         ys = (C.c_void_p * self.ctx.world)(*peer_y)
         st_ptrs = (C.c_void_p * self.ctx.world)(*peer_staging)
         lib = _lib.load()

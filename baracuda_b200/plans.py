@@ -69,6 +69,19 @@ def _check_backend(pref: PlanPreference) -> None:
         raise Unsupported("these plans are bespoke-only")
 
 
+def _need_typed(t: Optional[torch.Tensor], dtype, elems: int, name: str) -> None:
+    """A device vector or matrix of exactly `dtype` with at least `elems` elements: the kernels read typed storage, so a
+    buffer of another element size would be read past its end even when its element count looks sufficient."""
+    if t is None:
+        raise InvalidProblem(f"{name} is required")
+    dtypes = dtype if isinstance(dtype, tuple) else (dtype,)
+    if t.dtype not in dtypes:
+        raise InvalidProblem(f"{name}: expected {' or '.join(str(d) for d in dtypes)}, got {t.dtype}")
+    if not t.is_cuda:
+        raise InvalidProblem(f"{name}: expected a device buffer")
+    _need(t, elems, name)
+
+
 def _span(rows: int, cols: int, ld: int) -> int:
     return 0 if rows == 0 or cols == 0 else (rows - 1) * ld + cols
 
@@ -392,6 +405,8 @@ class GemvQ8Plan:
             raise InvalidProblem("a and b must be int8")
         if args.d.dtype != (torch.int32 if self.raw else torch.bfloat16):
             raise InvalidProblem("d has the wrong dtype for this plan")
+        if not (args.a.is_cuda and args.b.is_cuda and args.d.is_cuda):
+            raise InvalidProblem("operands must be device buffers")
         lib = _lib.load()
         st = getattr(lib, self._base + "_can_implement")(d.m, d.n, d.k, d.batch, self._layout_code(), lda, ldb, ldd,
                                                          args.stride_a, args.stride_b, args.stride_d)
@@ -405,12 +420,15 @@ class GemvQ8Plan:
             _need(args.b, last * args.stride_b + _span(b_rows, b_cols, ldb), "b")
             _need(args.d, last * args.stride_d + _span(d.m, d.n, ldd), "d")
             if not self.raw:
-                if args.scale_a is None or args.scale_b is None:
-                    raise InvalidProblem("scale_a and scale_b are required")
-                _need(args.scale_a, last * args.stride_scale_a + d.m, "scale_a")
-                _need(args.scale_b, last * args.stride_scale_b + d.n, "scale_b")
+                if min(args.stride_scale_a, args.stride_scale_b) < 0:
+                    raise InvalidProblem("negative scale stride")
+                # the kernels read float[...]: a bf16 or f16 scale vector of the right length would be overrun
+                _need_typed(args.scale_a, torch.float32, last * args.stride_scale_a + d.m, "scale_a")
+                _need_typed(args.scale_b, torch.float32, last * args.stride_scale_b + d.n, "scale_b")
 
-    def run(self, stream, workspace: Optional[torch.Tensor], args: GemvQ8Args) -> None:
+    def run(self, stream, workspace: Optional[torch.Tensor], args: GemvQ8Args, dependent_launch: bool = False) -> None:
+        """`dependent_launch=True` selects the *_pdl_run symbol: the kernel may start while the previous kernel of the
+        stream drains and prefetches weights meanwhile; pass it only when that previous kernel does not write `b`."""
         self.can_implement(args)
         need = self.workspace_size()
         ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
@@ -420,13 +438,14 @@ class GemvQ8Plan:
         d = self.desc
         lda, ldb, ldd = self._lds(args)
         s = _stream_ptr(stream)
+        suffix = "_pdl_run" if dependent_launch else "_run"
         if self.raw:
-            st = lib.baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
+            st = getattr(lib, "baracuda_kernels_gemv_q8_m1_s32_sm100a" + suffix)(
                 d.m, d.n, d.k, d.batch, self._layout_code(), args.alpha, args.beta,
                 _ptr(args.a), lda, args.stride_a, _ptr(args.b), ldb, args.stride_b,
                 _ptr(args.d), ldd, args.stride_d, _ptr(workspace), ws_bytes, s)
         else:
-            st = lib.baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(
+            st = getattr(lib, "baracuda_kernels_gemv_q8_m1_bf16_sm100a" + suffix)(
                 d.m, d.n, d.k, d.batch, self._layout_code(), args.alpha, args.beta,
                 _ptr(args.a), lda, args.stride_a, _ptr(args.b), ldb, args.stride_b,
                 _ptr(args.scale_a), args.stride_scale_a, _ptr(args.scale_b), args.stride_scale_b,
@@ -440,6 +459,7 @@ def device_status() -> int:
 
 
 def set_tuning(key: int, value: int) -> None:
+    """Test hook: forces a kernel choice for the calling thread (see the header); 0 restores the automatic choice."""
     status_to_result(_lib.load().baracuda_kernels_q_set_tuning(key, value), "set_tuning")
 
 
@@ -555,18 +575,21 @@ class QuantizedLinearPlan:
                                                                                           max(d.k, 1), max(d.c_out, 1))
         return st == 0 and args.activation.data_ptr() % 16 == 0 and args.weight_q.data_ptr() % 16 == 0
 
-    def run(self, stream, workspace: Optional[torch.Tensor], args: QuantizedLinearArgs) -> None:
+    def run(self, stream, workspace: Optional[torch.Tensor], args: QuantizedLinearArgs,
+            dependent_launch: bool = False) -> None:
+        """`dependent_launch` as in GemvQ8Plan.run (decode shapes only; the prefill GEMM ignores it)."""
         if args.act_q_scratch.dtype != torch.int8:
             raise InvalidProblem("act_q_scratch must be int8")
         d = self.desc
         if self.fused_decode_ok(args):
             # decode: quantiser and GEMV in one kernel; the scales still land in act_scale_scratch
-            _need(args.activation, _span(d.m, d.k, d.k), "activation")
-            _need(args.weight_q, _span(d.c_out, d.k, d.k), "weight_q")
-            _need(args.weight_scale, d.c_out, "weight_scale")
-            _need(args.act_scale_scratch, d.m, "act_scale_scratch")
-            _need(args.output, _span(d.m, d.c_out, d.c_out), "output")
-            st = _lib.load().baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
+            _need_typed(args.activation, torch.bfloat16, _span(d.m, d.k, d.k), "activation")
+            _need_typed(args.weight_q, torch.int8, _span(d.c_out, d.k, d.k), "weight_q")
+            _need_typed(args.weight_scale, torch.float32, d.c_out, "weight_scale")
+            _need_typed(args.act_scale_scratch, torch.float32, d.m, "act_scale_scratch")
+            _need_typed(args.output, torch.bfloat16, _span(d.m, d.c_out, d.c_out), "output")
+            sym = "baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16" + ("_pdl_run" if dependent_launch else "_run")
+            st = getattr(_lib.load(), sym)(
                 d.m, d.c_out, d.k, d.q_min, d.q_max, 1.0, 0.0, _ptr(args.activation), d.k, _ptr(args.weight_q), d.k,
                 _ptr(args.weight_scale), _ptr(args.act_scale_scratch), _ptr(args.output), d.c_out, None, 0,
                 _stream_ptr(stream))
@@ -574,11 +597,92 @@ class QuantizedLinearPlan:
             return
         self._quant.run(stream, args.activation, args.act_scale_scratch, args.act_q_scratch)
         if isinstance(self._mm, GemvQ8Plan):
+            # the quantiser launched just before writes activations and scales, never the weights
             self._mm.run(stream, workspace, GemvQ8Args(a=args.act_q_scratch, b=args.weight_q, d=args.output,
-                                                       scale_a=args.act_scale_scratch, scale_b=args.weight_scale))
+                                                       scale_a=args.act_scale_scratch, scale_b=args.weight_scale),
+                         dependent_launch=dependent_launch)
         else:
             self._mm.run(stream, workspace, QGemmArgs(a=args.act_q_scratch, b=args.weight_q, d=args.output,
                                                       scale_a=args.act_scale_scratch, scale_b=args.weight_scale))
+
+
+# --------------------------------------------------------------------------- SmoothQuant linear (per-tensor activation scale)
+OP_SMOOTHQUANT_LINEAR = "smoothquant_linear_w8a8"
+
+
+@dataclass(frozen=True)
+class SmoothQuantLinearDescriptor:
+    """SmoothQuantLinearDescriptor (crates/baracuda-kernels/src/quantize/smoothquant.rs:70-118): the per-tensor
+    activation scale is frozen model metadata and lives in the descriptor."""
+    m: int
+    n: int
+    k: int
+    act_scale: float
+
+
+@dataclass
+class SmoothQuantLinearArgs:
+    """SmoothQuantLinearArgs (smoothquant.rs:120-150): pre-quantized int8 activation [M, K], smoothed-then-quantized
+    int8 weight [N, K], per-output-channel f32 weight scales, bf16 output.  `act_scale_scratch` is kept for source
+    compatibility with the reference and is not touched: the scale travels by value."""
+    act_q: torch.Tensor
+    weight_q: torch.Tensor
+    weight_scale: torch.Tensor
+    output: torch.Tensor
+    act_scale_scratch: Optional[torch.Tensor] = None
+
+
+class SmoothQuantLinearPlan:
+    """y[m, n] = bf16((act_scale * weight_scale[n]) * sum_k a_q[m, k] * w_q[n, k]) on the tcgen05 GEMM
+    (SmoothQuantLinearPlan, smoothquant.rs:152-330, whose two launches -- fill + W8A8 kernel -- become one)."""
+
+    _base = "baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a"
+
+    def __init__(self, desc: SmoothQuantLinearDescriptor, sku: KernelSku):
+        self.desc, self._sku = desc, sku
+
+    @classmethod
+    def select(cls, stream, desc: SmoothQuantLinearDescriptor, pref: PlanPreference = PlanPreference()):
+        _check_backend(pref)
+        if desc.m < 0 or desc.n < 0 or desc.k < 0:
+            raise InvalidProblem("negative dimension")
+        if max(desc.m, desc.n, desc.k) >= 2**31:
+            raise InvalidProblem("dimension exceeds int32")
+        if not (desc.act_scale == desc.act_scale) or desc.act_scale in (float("inf"), float("-inf")):
+            raise InvalidProblem("act_scale must be finite")
+        sku = KernelSku(OpCategory.Gemm, OP_SMOOTHQUANT_LINEAR, ElementKind.S8, ElementKind.Bf16, LayoutSku.Rcr,
+                        EpilogueKind.Identity, ArchSku.Sm100a, BackendKind.Bespoke, _INT_GUARANTEE)
+        return cls(desc, sku)
+
+    def sku(self) -> KernelSku:
+        return self._sku
+
+    def precision_guarantee(self) -> PrecisionGuarantee:
+        return self._sku.precision_guarantee
+
+    def workspace_size(self) -> int:
+        return 0
+
+    def can_implement(self, args: SmoothQuantLinearArgs) -> None:
+        d = self.desc
+        st = getattr(_lib.load(), self._base + "_can_implement")(d.m, d.n, d.k, _ptr(args.act_q), max(d.k, 1),
+                                                                 _ptr(args.weight_q), max(d.k, 1), _ptr(args.output),
+                                                                 max(d.n, 1))
+        status_to_result(st, "SmoothQuantLinearPlan")
+        if d.m == 0 or d.n == 0:
+            return
+        _need_typed(args.act_q, torch.int8, _span(d.m, d.k, d.k), "act_q")
+        _need_typed(args.weight_q, torch.int8, _span(d.n, d.k, d.k), "weight_q")
+        _need_typed(args.weight_scale, torch.float32, d.n, "weight_scale")
+        _need_typed(args.output, torch.bfloat16, _span(d.m, d.n, d.n), "output")
+
+    def run(self, stream, workspace: Optional[torch.Tensor], args: SmoothQuantLinearArgs) -> None:
+        self.can_implement(args)
+        d = self.desc
+        st = getattr(_lib.load(), self._base + "_run")(
+            d.m, d.n, d.k, _ptr(args.act_q), max(d.k, 1), _ptr(args.weight_q), max(d.k, 1), float(d.act_scale),
+            _ptr(args.weight_scale), _ptr(args.output), max(d.n, 1), None, 0, _stream_ptr(stream))
+        status_to_result(st, "SmoothQuantLinearPlan")
 
 
 # --------------------------------------------------------------------------- gated-MLP up-projection

@@ -85,6 +85,26 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
     const void* a, int64_t lda, const void* b, int64_t ldb,
     const void* c, int64_t ldc, const void* d, int64_t ldd);
 
+/* SmoothQuant inference forward, SmoothQuantLinearPlan of the reference
+ * (crates/baracuda-kernels/src/quantize/smoothquant.rs:1-60, 70-140): pre-quantized s8 activation [M, K], s8 weight
+ * [N, K], ONE per-tensor activation scale and per-output-channel weight scales:
+ *     output[m, n] = bf16( (act_scale * weight_scale[n]) * (float)sum_k act_q[m,k] * weight_q[n,k] )
+ * The reference broadcasts act_scale into a caller-owned [M] scratch with a fill launch and reuses its W8A8 kernel;
+ * here the scalar travels by value in the kernel parameters, so there is no scratch and no second launch.  Same
+ * product order as the reference's W8A8 formula, hence the same bits as the per-token symbol given a constant
+ * scale_a vector.  Alignment and statuses as baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run. */
+int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
+    int32_t m, int32_t n, int32_t k,
+    const void* act_q, int64_t lda, const void* weight_q, int64_t ldb,
+    float act_scale, const void* weight_scale,
+    void* output, int64_t ldd,
+    void* workspace, size_t workspace_bytes, void* stream);
+size_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_workspace_size(int32_t m, int32_t n, int32_t k);
+int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_can_implement(
+    int32_t m, int32_t n, int32_t k,
+    const void* act_q, int64_t lda, const void* weight_q, int64_t ldb,
+    const void* output, int64_t ldd);
+
 /* The same contraction with the int32 accumulators written as they are
  * (D is int32 [M,N]).  Exists so callers and tests can check the integer
  * result bit for bit, as the reference's CPU oracle defines it
@@ -270,8 +290,10 @@ BARACUDA_Q_DECLARE_BIAS_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_silu_
 
 /* The bf16-out SKUs with the same chain (no counterpart symbol in the reference; the quantized-linear forward
  * with a bias, bindings/burn/baracuda-burn/src/ops/quantize.rs, is the caller it serves):
- *     D = bf16( act( alpha * ((scale_a[i]*scale_b[j]) * acc) + bias[j] ) ),  bias float[N], beta must be 0.
- * scale_mode as for the fp8 bf16 symbol; the w8a8 symbols ignore it (always per row x per column). */
+ *     D = bf16( act( alpha * ((scale_a[i]*scale_b[j]) * acc) + beta * C[i,j] + bias[j] ) ),  bias float[N];
+ * C is bf16 [M, ldc] and may be D itself; beta != 0 needs C (status 2 without it), with beta == 0 C is not read.
+ * scale_mode as for the fp8 bf16 symbol; the w8a8 symbols ignore it (always per row x per column; the per-tensor
+ * activation scale of SmoothQuant has its own symbol, baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run). */
 #define BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(NAME)                                                                   \
     int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb,            \
                  const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b,         \
@@ -352,6 +374,21 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_can_implement(
     int64_t stride_a, int64_t stride_b, int64_t stride_d);
 size_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_workspace_size(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout);
+/* The same call launched with programmatic dependent launch (per call, no process state): the kernel may start
+ * while the previous kernel of `stream` is still finishing and fetches WEIGHTS during that overlap; activations,
+ * scales, workspace and outputs are touched only after the previous kernel has completed and its writes are
+ * visible.  The caller promises that the kernel launched just before on this stream does not write `b`
+ * (true for a decode loop over static weights).  Same arguments, results and statuses as *_run; also serves
+ * the s32 and the fused-quantiser forms below.  No counterpart in the reference (its GEMV predates the feature). */
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_pdl_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    float alpha, float beta,
+    const void* a, int64_t lda, int64_t stride_a,
+    const void* b, int64_t ldb, int64_t stride_b,
+    const void* scale_a, int64_t stride_scale_a,
+    const void* scale_b, int64_t stride_scale_b,
+    void* d, int64_t ldd, int64_t stride_d,
+    void* workspace, size_t workspace_bytes, void* stream);
 
 /* The same GEMV for callers that must not allocate device memory (a serving loop that has
  * given every byte to its own arena, a plugin host that forbids side allocations): the
@@ -397,11 +434,24 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run(
     const void* x_bf16, int64_t ldx, const void* b, int64_t ldb, const void* scale_b,
     void* scale_a_out, void* d, int64_t ldd,
     void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_pdl_run(
+    int32_t m, int32_t n, int32_t k, int32_t qmin, int32_t qmax,
+    float alpha, float beta,
+    const void* x_bf16, int64_t ldx, const void* b, int64_t ldb, const void* scale_b,
+    void* scale_a_out, void* d, int64_t ldd,
+    void* workspace, size_t workspace_bytes, void* stream);
 int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(
     int32_t m, int32_t n, int32_t k, int64_t ldx, int64_t ldb, int64_t ldd);
 
 /* The int32 sums of the same GEMV (D is int32); alpha 1, beta 0, no scales. */
 int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_run(
+    int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
+    float alpha, float beta,
+    const void* a, int64_t lda, int64_t stride_a,
+    const void* b, int64_t ldb, int64_t stride_b,
+    void* d, int64_t ldd, int64_t stride_d,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemv_q8_m1_s32_sm100a_pdl_run(
     int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout,
     float alpha, float beta,
     const void* a, int64_t lda, int64_t stride_a,
@@ -550,22 +600,29 @@ int32_t baracuda_q_nccl_unique_id(void* id_out_128_bytes);
 int32_t baracuda_q_nccl_comm_init_rank(void** comm_out, int32_t world, const void* id_128_bytes, int32_t rank);
 int32_t baracuda_q_nccl_comm_destroy(void* comm);
 int32_t baracuda_q_nccl_stream_barrier(void* comm, void* scratch_one_float, void* stream);
+/* Replicates a row-sharded operand over NVLink: every rank contributes `bytes_per_rank` contiguous bytes at `send`
+ * and receives all ranks' blocks, in rank order, at `recv` (world * bytes_per_rank bytes; send may point at this
+ * rank's block inside recv).  The column-parallel layer uses it so that each rank uploads only 1/world of the
+ * activation rows (and of scale_a) from the host and the rest arrives from its peers
+ * (Communicator::all_gather, crates/baracuda-nccl/src/lib.rs:468-489).  world == 1 is a device copy. */
+int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* send, void* recv, size_t bytes_per_rank,
+                                         void* stream);
 
 /* ---------------------------------------------------------------------------
- * Diagnostics and tuning (no counterpart in the reference).
+ * Diagnostics and test hooks (no counterpart in the reference).
  * device_status: synchronous read-and-clear of the word a kernel sets when one
  * of its bounded barrier waits ran out (0 = none; the code names the kernel and
- * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 121..125 wide
- * GEMM, 131..134 tcgen05 GEMV, 201..206 streaming GEMVs, 299 the self-test).
- * Call it after synchronising the stream.
- * set_tuning: key 0 forces the GEMM tile (0 = automatic; 64, 128, 256 = 1-CTA kernel with that N-tile;
- * 512 = the CTA-pair kernel); key 1 forces a GEMV kernel variant; key 2 forces the CTA-pair kernel's
- * tile width (0 = automatic, 256, 224, 192, 128); key 3 = 1 launches the K-contiguous streaming GEMV with
- * programmatic stream serialization: it starts fetching weights while the previous kernel of the stream is
- * still finishing and touches activations, scales and outputs only after that kernel has completed — use it
- * only when the kernel launched just before never writes the weights; key 4 picks the GEMM epilogue's store
- * path (0 = automatic, 1 = per-thread direct stores, 2 = rows staged through shared memory);
- * process-wide, meant for benchmarks and tests.
+ * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 131..134 tcgen05 GEMV,
+ * 201..206 streaming GEMVs, 299 the self-test).  Call it after synchronising the stream.
+ * set_tuning: forces a kernel choice for the CALLING THREAD only (thread-local; other threads' launches are not
+ * affected, nothing process-wide is kept), so tests can run every kernel on the same shapes:
+ *   key 0  GEMM tile: 0 automatic; 64, 128, 256 = 1-CTA kernel with that N-tile; 512 = the CTA-pair kernel;
+ *   key 1  GEMV kernel: 0 automatic; 1 bulk-copy dp4a kernel; 2 register-streaming kernel; 3 tensor-core streaming
+ *          kernel also for m = 1; 7 mma.sync streaming kernel (row-major weights); 8 direct-load split-K kernel
+ *          (row-major weights); 9 byte-load kernel;
+ *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128;
+ *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
+ * Any other key or value returns 2.
  * selftest_bounded_wait: launches one thread that waits, for at most limit_cycles SM clock cycles
  * (1 .. 2^28), on a barrier that nothing completes -- the time-out path of every kernel here.  After the
  * stream is synchronised device_status() returns 299 once and the context is as usable as before.

@@ -57,6 +57,8 @@ enum {
 };
 
 int orc_num_threads(void);
+/* Worker threads of the following calls (a launcher may have exported OMP_NUM_THREADS=1 for its ranks). */
+void orc_set_num_threads(int n);
 
 /* ---- codecs --------------------------------------------------------------*/
 /* f32 -> bf16 bits, RNE, NaN quieted (oracle.rs:397-404). */

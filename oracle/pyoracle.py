@@ -38,6 +38,8 @@ def lib() -> C.CDLL:
         L = C.CDLL(str(LIB_PATH))
         vp, i32, i64, f32, f64 = C.c_void_p, C.c_int32, C.c_int64, C.c_float, C.c_double
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.restype = None
+        L.orc_set_num_threads.argtypes = [C.c_int]
         L.orc_f32_to_bf16_bits.restype = C.c_uint16
         L.orc_f32_to_bf16_bits.argtypes = [f32]
         L.orc_bf16_bits_to_f32.restype = f32
@@ -85,6 +87,11 @@ def _c(a, dtype) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """Thread count of the following calls; overrides an OMP_NUM_THREADS a launcher exported for its ranks."""
+    lib().orc_set_num_threads(int(n))
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

@@ -18,14 +18,14 @@ def _weights_for(layout, wq_nk):
     return wq_nk if layout is bq.LayoutSku.Rcr else np.ascontiguousarray(wq_nk.T)
 
 
-def _run(m, n, k, layout, aq, wq_nk, sa, sb, raw, **kw):
+def _run(m, n, k, layout, aq, wq_nk, sa, sb, raw, dependent_launch=False, **kw):
     desc = bq.GemvQ8Descriptor(m, n, k, batch=1, layout=layout)
     plan = bq.GemvQ8Plan.select(None, desc, raw_accumulators=raw)
     ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
     d = torch.full((m, n), -7 if raw else float("nan"), dtype=torch.int32 if raw else torch.bfloat16, device="cuda")
     args = bq.GemvQ8Args(a=dev(aq), b=dev(_weights_for(layout, wq_nk)), d=d,
                          scale_a=None if raw else dev(sa), scale_b=None if raw else dev(sb), **kw)
-    plan.run(None, ws, args)
+    plan.run(None, ws, args, dependent_launch=dependent_launch)
     torch.cuda.synchronize()
     return d
 
@@ -74,12 +74,14 @@ def test_byte_load_kernel_equals_streaming_kernel(oracle, layout):
     assert np.array_equal(fast, oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k))
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 32, 33, 34, 35, 36])  # bulk-copy dp4a, register streaming, tensor-core (default / 2 KiB x 4 warps / 512 B x 16 warps / ring 2)
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])  # automatic, bulk-copy dp4a, register streaming, tensor-core streaming
 @pytest.mark.parametrize("shape", [(1, 300, 512), (2, 149, 4096), (3, 1000, 4112), (4, 2048, 9000 // 16 * 16), (1, 7, 16),
-                                   (8, 520, 2048), (5, 1187, 8192), (7, 3000, 1088)])
+                                   (8, 520, 2048), (5, 1187, 8192), (7, 3000, 1088), (6, 2048, 1536), (2, 4096, 3072)])
 def test_both_k_contiguous_kernels_on_the_same_shapes(oracle, shape, variant):
     """The bulk-copy streaming kernel (variant 1) and the register-streaming kernel (variant 2) are both
-    exercised on shapes that include partial K chunks, several chunks per row and fewer columns than SMs."""
+    exercised on shapes that include partial K chunks, several chunks per row and fewer columns than SMs; K = 1536 and
+    3072 (three / six 512-byte chunks, which do not divide the warp count) and 1088 take the tensor-core kernel's
+    staged-activation configuration, the other K its register-activation one."""
     m, n, k = shape
     aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=31 + n)
     acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
@@ -185,27 +187,23 @@ def test_workspace_contract():
 
 
 def test_dependent_launch_mode_gives_the_same_results(oracle):
-    """Programmatic stream serialization (tuning key 3): a chain of GEMVs on one stream, each consuming the
-    previous launch's output buffer as its canvas, equals the same chain launched normally."""
+    """Programmatic dependent launch, selected per call (the *_pdl_run symbols): a chain of GEMVs on one stream over
+    static weights equals the same chain launched normally."""
     m, n, k = 2, 4096, 4096
     aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=44)
     want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
     plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=bq.LayoutSku.Rcr))
     a_d, b_d, sa_d, sb_d = dev(aq), dev(wq), dev(sa), dev(sb)
     outs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
-    bq.set_tuning(3, 1)
-    try:
-        for d in outs:
-            plan.run(None, None, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d))
-        torch.cuda.synchronize()
-    finally:
-        bq.set_tuning(3, 0)
+    for d in outs:
+        plan.run(None, None, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d), dependent_launch=True)
+    torch.cuda.synchronize()
     assert bq.device_status() == 0
     for d in outs:
         assert np.array_equal(bf16_bits(d), want)
 
 
-@pytest.mark.parametrize("variant", [0, 41, 42, 43, 7, 8])  # tcgen05 kernel (default teams; teams of 1 / 4 / 8 CTAs), mma.sync streaming kernel, direct-load split-K kernel
+@pytest.mark.parametrize("variant", [0, 7, 8])  # automatic, mma.sync streaming kernel, direct-load split-K kernel
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (2, 1040, 2064), (3, 272, 1000), (5, 14336, 512), (8, 2048, 4100),
                                    (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096), (2, 32768, 8192)])
 def test_both_row_major_weight_kernels_on_the_same_shapes(oracle, shape, variant):
@@ -240,14 +238,10 @@ def test_row_major_weights_tensor_core_kernel_in_a_dependent_chain(oracle, shape
     a_ds = [dev(a) for a in acts]
     for pdl in (0, 1):
         outs = [torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in acts]
-        bq.set_tuning(3, pdl)
-        try:
-            for rep in range(3):
-                for a_d, d in zip(a_ds, outs):
-                    plan.run(None, ws, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d))
-            torch.cuda.synchronize()
-        finally:
-            bq.set_tuning(3, 0)
+        for rep in range(3):
+            for a_d, d in zip(a_ds, outs):
+                plan.run(None, ws, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d), dependent_launch=bool(pdl))
+        torch.cuda.synchronize()
         assert bq.device_status() == 0
         for d, want in zip(outs, wants):
             assert np.array_equal(bf16_bits(d), want), pdl
@@ -267,15 +261,12 @@ def test_row_major_weights_strided_batch_and_dependent_launches(oracle):
     a_d, b_d, sa_d, sb_d = dev(a_buf), dev(b_buf), dev(sa_buf), dev(sb_buf)
     outs = [torch.full((batch, m, n), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(4)]
     for pdl in (0, 1):
-        bq.set_tuning(3, pdl)
-        try:
-            for d in outs:
-                d.fill_(float("nan"))
-                plan.run(None, ws, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d, stride_a=m * k,
-                                                 stride_b=k * n, stride_d=m * n, stride_scale_a=m, stride_scale_b=n))
-            torch.cuda.synchronize()
-        finally:
-            bq.set_tuning(3, 0)
+        for d in outs:
+            d.fill_(float("nan"))
+            plan.run(None, ws, bq.GemvQ8Args(a=a_d, b=b_d, d=d, scale_a=sa_d, scale_b=sb_d, stride_a=m * k,
+                                             stride_b=k * n, stride_d=m * n, stride_scale_a=m, stride_scale_b=n),
+                     dependent_launch=bool(pdl))
+        torch.cuda.synchronize()
         assert bq.device_status() == 0
         for d in outs:
             for g, (aq, wq, sa, sb) in enumerate(cases):
@@ -343,12 +334,8 @@ def test_k_contiguous_weights_long_k(oracle, shape):
     acc = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
     want = oracle.dequant_s32_bf16(acc, sa, sb)
     for pdl in (0, 1):
-        bq.set_tuning(3, pdl)
-        try:
-            got_raw = _run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=True).cpu().numpy()
-            got = bf16_bits(_run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=False))
-        finally:
-            bq.set_tuning(3, 0)
+        got_raw = _run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=True, dependent_launch=bool(pdl)).cpu().numpy()
+        got = bf16_bits(_run(m, n, k, bq.LayoutSku.Rcr, aq, wq, sa, sb, raw=False, dependent_launch=bool(pdl)))
         assert bq.device_status() == 0
         assert np.array_equal(got_raw, acc), (shape, pdl)
         assert np.array_equal(got, want), (shape, pdl)

@@ -123,16 +123,7 @@ def test_plan_select_and_sku():
 
 def test_typed_layer_refuses_short_buffers():
     """The typed layer owns buffer-length soundness (gemv_dense.rs:218-268)."""
-    class FakeCuda:
-        """Shape/dtype stand-in so the length checks run without a device."""
-        def __init__(self, n, dtype):
-            self._n, self.dtype, self.is_cuda = n, dtype, True
-        def numel(self):
-            return self._n
-        def data_ptr(self):
-            return 0x10000
-        def element_size(self):
-            return 1
+    FakeCuda = _FakeCuda
     p = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(128, 256, 512))
     good = dict(a=FakeCuda(128 * 512, torch.int8), b=FakeCuda(256 * 512, torch.int8), d=FakeCuda(128 * 256, torch.bfloat16),
                 scale_a=FakeCuda(128, torch.float32), scale_b=FakeCuda(256, torch.float32))
@@ -145,6 +136,112 @@ def test_typed_layer_refuses_short_buffers():
         p.can_implement(bq.QGemmArgs(**{**good, "d": FakeCuda(128 * 256, torch.float16)}))
     with pytest.raises(bq.MisalignedOperand):
         p.can_implement(bq.QGemmArgs(**{**good, "lda": 520}))
+
+
+class _FakeCuda:
+    """Shape/dtype stand-in so the typed layer's checks run without a device."""
+    def __init__(self, n, dtype, cuda=True):
+        self._n, self.dtype, self.is_cuda = n, dtype, cuda
+    def numel(self):
+        return self._n
+    def data_ptr(self):
+        return 0x10000
+    def element_size(self):
+        return 1
+
+
+def test_gemv_typed_layer_checks_scale_dtypes():
+    """A bf16 scale vector of the right LENGTH is half the bytes the kernel reads: it must be refused, not overrun."""
+    m, n, k = 4, 256, 512
+    p = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=bq.LayoutSku.Rcr))
+    good = dict(a=_FakeCuda(m * k, torch.int8), b=_FakeCuda(n * k, torch.int8), d=_FakeCuda(m * n, torch.bfloat16),
+                scale_a=_FakeCuda(m, torch.float32), scale_b=_FakeCuda(n, torch.float32))
+    p.can_implement(bq.GemvQ8Args(**good))
+    for name, bad in (("scale_b", _FakeCuda(n, torch.bfloat16)), ("scale_a", _FakeCuda(m, torch.float16)),
+                      ("scale_b", _FakeCuda(n, torch.float32, cuda=False)), ("scale_a", None)):
+        with pytest.raises(bq.InvalidProblem):
+            p.can_implement(bq.GemvQ8Args(**{**good, name: bad}))
+    with pytest.raises(bq.BufferTooSmall):
+        p.can_implement(bq.GemvQ8Args(**{**good, "scale_b": _FakeCuda(n - 1, torch.float32)}))
+
+
+def test_fused_decode_branch_checks_dtypes(monkeypatch):
+    m, n, k = 1, 1024, 4096
+    lin = bq.QuantizedLinearPlan.select(None, bq.QuantizedLinearDescriptor(m, n, k))
+    monkeypatch.setattr(lin, "fused_decode_ok", lambda args: True)
+    good = dict(activation=_FakeCuda(m * k, torch.bfloat16), weight_q=_FakeCuda(n * k, torch.int8),
+                weight_scale=_FakeCuda(n, torch.float32), output=_FakeCuda(m * n, torch.bfloat16),
+                act_q_scratch=_FakeCuda(m * k, torch.int8), act_scale_scratch=_FakeCuda(m, torch.float32))
+    for name, bad in (("weight_scale", _FakeCuda(n, torch.bfloat16)), ("weight_q", _FakeCuda(n * k, torch.uint8)),
+                      ("act_scale_scratch", _FakeCuda(m, torch.float16)), ("output", _FakeCuda(m * n, torch.float32))):
+        with pytest.raises(bq.InvalidProblem):
+            lin.run(0, None, bq.QuantizedLinearArgs(**{**good, name: bad}))
+
+
+def test_parallel_forwards_check_dtypes_and_scale_lengths():
+    from baracuda_b200 import parallel as par
+
+    ctx = par.TensorParallelContext(0, 2, comm=None)
+    m, n, k = 64, 512, 256
+    col = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind="w8a8")
+    good = dict(a=_FakeCuda(m * k, torch.int8), scale_a=_FakeCuda(m, torch.float32), w_local=_FakeCuda(n // 2 * k, torch.int8),
+                scale_b_local=_FakeCuda(n // 2, torch.float32), y_local=_FakeCuda(m * n // 2, torch.bfloat16))
+    for name, bad in (("scale_a", _FakeCuda(m, torch.bfloat16)), ("scale_b_local", _FakeCuda(n // 2, torch.float16)),
+                      ("y_local", _FakeCuda(m * n // 2, torch.float16)), ("a", _FakeCuda(m * k, torch.uint8))):
+        with pytest.raises(bq.InvalidProblem):
+            col.forward(0, **{**good, name: bad})
+    with pytest.raises(bq.BufferTooSmall):
+        col.forward(0, **{**good, "scale_b_local": _FakeCuda(n // 2 - 1, torch.float32)})
+    with pytest.raises(bq.BufferTooSmall):
+        col.forward(0, **{**good, "scale_a": _FakeCuda(m - 1, torch.float32)})
+    row = par.RowParallelQGemmPlan(ctx, m, n, k, kind="w8a8")
+    rgood = dict(a_local=_FakeCuda(m * k // 2, torch.int8), scale_a=_FakeCuda(m, torch.float32),
+                 w_local=_FakeCuda(n * k // 2, torch.int8), scale_b=_FakeCuda(n, torch.float32),
+                 y=_FakeCuda(m * n, torch.bfloat16), workspace=_FakeCuda(m * n * 4, torch.uint8))
+    for name, bad in (("scale_b", _FakeCuda(n, torch.bfloat16)), ("y", _FakeCuda(m * n, torch.float32))):
+        with pytest.raises(bq.InvalidProblem):
+            row.forward(0, **{**rgood, name: bad})
+    with pytest.raises(bq.BufferTooSmall):
+        row.forward(0, **{**rgood, "scale_a": _FakeCuda(m - 1, torch.float32)})
+
+
+def test_static_scratch_entry_validates_before_the_size_limit(qlib):
+    """Invalid problems report the regular entry point's status (2), not the size limit's (4)."""
+    run = qlib.baracuda_kernels_gemv_q8_m1_bf16_sm100a_static_ws_run
+    P = 0x10000
+    n, k = 14336, 4096
+    assert run(9, n, k, 1, 0, 1.0, 0.0, P, k, 0, P, n, 0, P, 0, P, 0, P, n, 0, None) == 2          # m > 8
+    assert run(1, n, k, 1, 0, 1.0, 0.0, None, k, 0, P, n, 0, P, 0, P, 0, P, n, 0, None) == 2       # null a
+    assert run(1, n, k, 1, 0, 1.0, 0.0, P, k, 0, P, n - 1, 0, P, 0, P, 0, P, n, 0, None) == 2      # ldb < n
+    assert run(0, n, k, 1, 0, 1.0, 0.0, None, k, 0, None, n, 0, None, 0, None, 0, None, n, 0, None) == 0  # empty
+    assert run(8, 65536, 8192, 1, 0, 1.0, 0.0, P, 8192, 0, P, 65536, 0, P, 0, P, 0, P, 65536, 0, None) == 4  # too large
+
+
+def test_set_tuning_is_per_thread(qlib):
+    """The test hooks are thread-local: a value forced on one thread is invisible to another."""
+    import threading
+
+    assert qlib.baracuda_kernels_q_set_tuning(3, 1) == 2  # the old process-wide dependent-launch switch is gone
+    assert qlib.baracuda_kernels_q_set_tuning(1, 33) == 2  # removed experimental GEMV configurations
+    assert qlib.baracuda_kernels_q_set_tuning(1, 9) == 0
+    seen = []
+    t = threading.Thread(target=lambda: seen.append(qlib.baracuda_kernels_q_set_tuning(1, 0)))
+    t.start()
+    t.join()
+    assert seen == [0]
+    assert qlib.baracuda_kernels_q_set_tuning(1, 0) == 0
+
+
+def test_smoothquant_plan_surface():
+    p = bq.SmoothQuantLinearPlan.select(None, bq.SmoothQuantLinearDescriptor(128, 256, 512, act_scale=0.02))
+    assert p.workspace_size() == 0 and p.sku().arch is bq.ArchSku.Sm100a and p.sku().element is bq.ElementKind.S8
+    good = dict(act_q=_FakeCuda(128 * 512, torch.int8), weight_q=_FakeCuda(256 * 512, torch.int8),
+                weight_scale=_FakeCuda(256, torch.float32), output=_FakeCuda(128 * 256, torch.bfloat16))
+    p.can_implement(bq.SmoothQuantLinearArgs(**good))
+    with pytest.raises(bq.InvalidProblem):
+        p.can_implement(bq.SmoothQuantLinearArgs(**{**good, "weight_scale": _FakeCuda(256, torch.float64)}))
+    with pytest.raises(bq.InvalidProblem):
+        bq.SmoothQuantLinearPlan.select(None, bq.SmoothQuantLinearDescriptor(1, 1, 1, act_scale=float("nan")))
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

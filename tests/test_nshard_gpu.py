@@ -1,6 +1,7 @@
-"""Two-GPU parity of the column-parallel and row-parallel GEMMs: each rank computes its N-slice with the tcgen05 kernel;
-the sharded output, the NCCL-gathered output (rank-major) and the fused peer-store output (row-major)
-must all equal the unsharded oracle result.  Skipped with fewer than two GPUs."""
+"""Multi-GPU parity of the column-parallel and row-parallel GEMMs at every power-of-two world size the box offers (2, 4,
+8): each rank computes its N-slice with the tcgen05 kernel; the sharded output, the NCCL-gathered output (rank-major)
+and the fused peer-store output (row-major) must all equal the unsharded oracle result, and so must the K-sharded
+forward in both its forms.  Skipped with fewer than two GPUs."""
 import os
 import socket
 
@@ -32,7 +33,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         ctx = par.TensorParallelContext.from_torch_distributed()
         dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
         bits = lambda t: t.cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
-        for kind, (m, n, k) in (("w8a8", (300, 1024, 512)), ("fp8", (1024, 2048, 1024)), ("w8a8", (300, 224 * 4 * world, 512))):
+        for kind, (m, n, k) in (("w8a8", (300, 1024, 512)), ("fp8", (1024, 2048, 1024)), ("w8a8", (300, 224 * 4 * world, 512)),
+                                ("fp8", (512, 256 * 3 * world, 640))):
             rng = np.random.default_rng(5)
             a = rng.standard_normal((m, k)).astype(np.float32)
             w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -63,6 +65,18 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             plan.forward(None, dev(aq), dev(sa), w_local, sb_local, y_local)
             torch.cuda.synchronize()
             check(bits(y_local), want[:, lo:lo + n_local], "sharded")
+            if m % world == 0:
+                # activations uploaded as M/G rows per rank and replicated over NVLink before the GEMM
+                rows = m // world
+                a_full = torch.zeros((m, k), dtype=torch.from_numpy(aq).dtype, device="cuda")
+                sa_full = torch.zeros(m, dtype=torch.float32, device="cuda")
+                plan.replicate_activations(None, dev(aq[rank * rows:(rank + 1) * rows]), dev(sa[rank * rows:(rank + 1) * rows]),
+                                           a_full, sa_full)
+                y_local.zero_()
+                plan.forward(None, a_full, sa_full, w_local, sb_local, y_local)
+                torch.cuda.synchronize()
+                assert np.array_equal(a_full.cpu().numpy(), aq) and np.array_equal(sa_full.cpu().numpy(), sa)
+                check(bits(y_local), want[:, lo:lo + n_local], "sharded, replicated activations")
             # NCCL all-gather, rank-major [G, M, N/G]
             y_full = torch.zeros((world, m, n_local), dtype=torch.bfloat16, device="cuda")
             plan = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind=kind, gather=par.GATHER_NCCL)
@@ -84,6 +98,8 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             assert bq.device_status() == 0
         # K-sharded (row-parallel) forward: raw accumulators all-reduced, one dequant pass, bias added once
         for kind, (m, n, k) in (("w8a8", (300, 1040, 1024)), ("fp8", (512, 1024, 2048)), ("w8a8", (1024, 2048, 4096))):
+            if k % (128 * world) != 0:
+                continue
             rng = np.random.default_rng(11)
             a = rng.standard_normal((m, k)).astype(np.float32)
             w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -139,9 +155,16 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         dist.destroy_process_group()
 
 
-def test_column_parallel_two_gpus(tmp_path):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+def _worlds():
+    """2, and the largest power of two the box offers (4 or 8) when that is more."""
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    top = 8 if n >= 8 else (4 if n >= 4 else (2 if n >= 2 else 0))
+    return sorted({w for w in (2, top) if 2 <= w <= n})
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_column_and_row_parallel_parity(tmp_path, world):
+    if world not in _worlds():
+        pytest.skip(f"runs at world sizes {_worlds()} on this box")
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
