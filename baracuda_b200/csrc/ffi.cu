@@ -833,7 +833,7 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             t_tuning.force_block_n = value;
             return bq::BQ_STATUS_OK;
         case 1:
-            if (value != 0 && value != 1 && value != 2 && value != 3 && value != 7 && value != 8 && value != 9)
+            if (value != 0 && value != 1 && value != 2 && value != 3 && value != 8 && value != 9)
                 return bq::BQ_STATUS_INVALID_PROBLEM;
             t_tuning.gemv_variant = value;
             return bq::BQ_STATUS_OK;

@@ -3,10 +3,9 @@
 // or the raw int32 sums.  The weight matrix is streamed exactly once.  Kernels, in the order the dispatcher tries them:
 //   gemv_q8_rcr_mma_kernel      weights [N, K], m >= 2 (and m = 1 under dependent launch): bulk copies, mma.sync
 //   gemv_q8_rcr_stream_kernel   weights [N, K], m <= 4: bulk copies, dp4a + warp shuffles
-//   gemv_q8_rrr_umma_kernel     weights [K, N], one batch slot: tensor copies consumed as MN-major tcgen05 operands
-//                               (gemv_q8_umma.cuh); partial rows to the caller's scratch, a reduce kernel adds them
-//   gemv_q8_rrr_stream_kernel   weights [K, N]: tensor copies, byte-permute transposes, mma.sync; K is split over
-//                               CTAs, partial rows go to the caller's scratch, gemv_q8_rrr_reduce_kernel adds them
+//   gemv_q8_rrr_rows_kernel     weights [K, N]: 1 KiB bulk copies of row runs, ldmatrix-transposed fragments, mma.sync;
+//                               rows are split over CTAs, partial rows go to the caller's scratch,
+//                               gemv_q8_rrr_rows_reduce_kernel adds them (gemv_q8_rrr_rows.cuh)
 //   gemv_q8_rcr_kernel / gemv_q8_rrr_kernel   128-bit loads that bypass L1 + dp4a, for shapes the above decline
 //   gemv_q8_generic_kernel      byte loads, any alignment
 //
@@ -51,12 +50,12 @@ struct GemvParams {
     int kslice_rows, num_kslices;
     int32_t* ws_partials;
     unsigned int* ws_tickets;
-    // row-major-weight streaming kernel: chunks of [32 K rows x 2048 columns], numbered strip major; CTA c owns
-    // chunks [c * total / ctas, (c + 1) * total / ctas).  rs_items_per_block = chunks per strip, rs_blocks = strips,
-    // rs_slots = ring slots per warp, rs_run_max = longest run of any CTA
-    int rs_items_per_block, rs_blocks, rs_slots, rs_run_max, rs_ctas;
-    int32_t* rs_partials;  // [batch][slot][m][2048]; slot(c, strip) = c + strip
-    int rs_slots_total;
+    // row-major-weight streaming kernel (gemv_q8_rrr_rows.cuh): rr_rows_total 1 KiB row pieces, strip major, over
+    // rr_ctas CTAs; rr_run_max = most stages any CTA walks; rr_partials is [batch][rr_slots_total][m][1024],
+    // slot(c, strip) = c + strip
+    int rr_strips, rr_run_max, rr_ctas, rr_slots_total;
+    int64_t rr_rows_total;
+    int32_t* rr_partials;
     int mma_groups;  // tensor-core GEMV: 8-column groups per CTA (upper bound), sizes the shared accumulator
     // fused per-token quantiser (XQ kernels): bf16 activations [m, ldx], clamp range, optional scale output [m]
     const __nv_bfloat16* xq_x;
@@ -64,11 +63,6 @@ struct GemvParams {
     int xq_qmin, xq_qmax;
     float* xq_scale_out;
     int pdl;  // launched with programmatic stream serialization: weights may be fetched before the dependency wait
-    // tcgen05 kernel for row-major weights: units of [128 K rows x 128 columns], column-tile major; CTA c owns units
-    // [c * gu_units / gu_ctas, (c + 1) * gu_units / gu_ctas); gu_partials is [gu_ctas][gu_smax][m][128]
-    int gu_kblocks, gu_smax, gu_ctas, gu_team;
-    int64_t gu_units;
-    int32_t* gu_partials;
 };
 
 __device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
@@ -810,256 +804,6 @@ gemv_q8_rrr_kernel(const GemvParams p) {
     if (threadIdx.x == 0) *ticket = 0u;  // leave the ticket ready for the next call
 }
 
-// ---- weights stored [K, N] (N contiguous), tensor-copy fed: one persistent CTA per SM.  The
-// weight matrix is cut into chunks of 32 K rows x 2048 columns (a strip), numbered strip major;
-// every CTA owns an equal, contiguous run of chunks, i.e. a K range of one strip (sometimes the
-// end of one strip and the start of the next).  Warp w owns columns 128 w .. 128 w + 127 of the strip
-// for the whole run, so its sums never leave its registers until the run ends, and streams its share
-// of every chunk (one 4 KiB tensor copy with the 128-byte swizzle) through a private ring: it pulls
-// a landed box into registers, re-arms the slot at once, then does the arithmetic.  The sixteen
-// warps move down K roughly together, so every weight row is read in 2 KiB runs (with 128-byte runs
-// -- sixteen warps at sixteen different K offsets of one column group -- the same kernel measured
-// 1.5x slower).
-// The dot products run on the tensor cores (mma.sync m16n8k32, s8): lane (g, t) reads 8 adjacent
-// columns of four K rows, turns them with byte permutes into eight words of four K values -- the B
-// fragments of eight MMAs whose N index g stands for column 8 g + j -- and the activations (8 rows,
-// zero beyond m) are the A fragments, staged in shared memory in the same K order.  Which four rows
-// form a lane's K group is free (the instruction sums over all 32); rows {2t, 2t+1, 2t+8, 2t+9} make
-// the four t of one load fall into different swizzle phases, so the 64-bit shared loads run at full
-// rate.
-// Each CTA writes its sums as partial rows to the scratch (no atomics, nothing to clear) and a second,
-// small kernel adds the partial rows of every strip and applies the scales -- launched with
-// programmatic stream serialization so that its launch overlaps.  (Finishing inside the streaming
-// kernel -- the last CTA of a strip to draw an epoch-tagged ticket adds the rows -- measured slower:
-// some twenty CTAs reach a strip's ticket at the same moment and their compare-and-swaps queue up.) ----
-constexpr int RS_STRIP = 2048;               // columns per strip
-constexpr int RS_COLS = 128;                 // columns per warp: one 4 KiB tensor-copy box per chunk
-constexpr int RS_ROWS = 32;                  // K rows per chunk
-constexpr int RS_WARPS = RS_STRIP / RS_COLS;
-constexpr int RS_THREADS = RS_WARPS * 32;
-constexpr int RS_BOX_BYTES = RS_COLS * RS_ROWS;
-constexpr int RS_MAX_CTAS = 160;             // sizes the scratch without asking the device
-constexpr long long RS_WAIT_LIMIT = 1LL << 31;
-
-__device__ __forceinline__ int64_t rs_begin(int c, int64_t total, int ctas) {
-    return (static_cast<int64_t>(c) * total) / ctas;
-}
-
-// K row (0..31 within a chunk) that byte i of lane-quad position t's word `half` stands for
-__host__ __device__ __forceinline__ int rs_krow(int half, int t, int i) {
-    return 16 * half + 2 * t + (i & 1) + 8 * (i >> 1);
-}
-
-template <bool RAW>
-__device__ __forceinline__ void rrr_stream_body(const CUtensorMap& tmap_b, const GemvParams& p) {
-    extern __shared__ uint8_t rs_smem_raw[];
-    // swizzled tensor copies land on 1024-byte boundaries; round up inside the shared window
-    uint8_t* rs_smem = rs_smem_raw + ((1024u - (smem_u32(rs_smem_raw) & 1023u)) & 1023u);
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int g8 = lane >> 2;  // MMA row / column index
-    const int t4 = lane & 3;   // MMA K group
-    const int slots = p.rs_slots;
-    const int KC = p.rs_items_per_block;  // chunks per strip
-    uint8_t* ring = rs_smem + static_cast<size_t>(warp) * slots * RS_BOX_BYTES;
-    const int run_max = p.rs_run_max;  // longest run of any CTA: sizes the activation staging
-    uint32_t* xs = reinterpret_cast<uint32_t*>(rs_smem + static_cast<size_t>(RS_WARPS) * slots * RS_BOX_BYTES);  // [m][run_max][8]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(xs + p.m * run_max * 8) + warp * slots;
-    volatile uint32_t* abort_word =
-        reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint64_t*>(xs + p.m * run_max * 8) + RS_WARPS * slots) + warp;
-
-    const int64_t g = blockIdx.y;
-    const int8_t* a = p.a + g * p.stride_a;
-    const int64_t total = static_cast<int64_t>(p.rs_blocks) * KC;
-    const int64_t begin = rs_begin(blockIdx.x, total, gridDim.x);
-    const int64_t end = rs_begin(blockIdx.x + 1, total, gridDim.x);
-    const int run = static_cast<int>(end - begin);
-    // weights of batch g start stride_b / ldb rows further down (stride_b is 0 or a multiple of ldb here)
-    const int row0 = p.ldb > 0 ? static_cast<int>((g * p.stride_b) / p.ldb) : 0;
-
-    // every warp streams its own 128 columns of the run's chunks through its own ring: one 4 KiB box per chunk
-    auto issue = [&](int t) {
-        const int64_t chunk = begin + t;
-        const int strip = static_cast<int>(chunk / KC);
-        const int kc = static_cast<int>(chunk - static_cast<int64_t>(strip) * KC);
-        const int slot = t % slots;
-        mbar_arrive_expect_tx(&bars[slot], RS_BOX_BYTES);
-        tma_load_2d(ring + static_cast<size_t>(slot) * RS_BOX_BYTES, &tmap_b, &bars[slot], strip * RS_STRIP + warp * RS_COLS,
-                    row0 + kc * RS_ROWS);
-    };
-    if (lane == 0) {
-        *abort_word = 0u;
-        for (int s = 0; s < slots; ++s) mbar_init(&bars[s], 1);
-        fence_barrier_init();
-        fence_proxy_async_smem();
-        // the weights do not depend on the previous kernel of the stream: request them before the dependency wait
-        for (int t = 0; t < slots && t < run; ++t) issue(t);
-    }
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-
-    // activation words in MMA order: word [row][local chunk][half][t] holds K rows rs_krow(half, t, 0..3) of the chunk,
-    // zero beyond K
-    for (int i = threadIdx.x; i < p.m * run * 8; i += RS_THREADS) {
-        const int r = i / (run * 8), w = i - r * (run * 8);
-        const int lc = w >> 3, half = (w >> 2) & 1, t = w & 3;
-        const int kc = static_cast<int>((begin + lc) % KC);
-        const int8_t* arow = a + static_cast<int64_t>(r) * p.lda;
-        uint32_t word = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int kk = kc * RS_ROWS + rs_krow(half, t, j);
-            if (kk < p.k) word |= static_cast<uint32_t>(static_cast<uint8_t>(__ldg(arow + kk))) << (8 * j);
-        }
-        xs[(r * run_max + lc) * 8 + (w & 7)] = word;
-    }
-    __syncthreads();
-
-    // acc[sub][j][0..1]: activation row g8, columns 64 sub + 8 (2 t4) + j and 64 sub + 8 (2 t4 + 1) + j of this warp's 128
-    int acc[2][8][2];
-    int cur_strip = -1;
-    auto clear = [&]() {
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[sb][j][0] = acc[sb][j][1] = 0;
-    };
-    // this warp's sums for its 128 columns of one strip, as the CTA's partial rows: slot = cta + strip
-    auto finish_strip = [&]() {
-        if (g8 < p.m) {
-            int32_t* dst = p.rs_partials +
-                           ((g * p.rs_slots_total + blockIdx.x + cur_strip) * static_cast<int64_t>(p.m) + g8) * RS_STRIP +
-                           warp * RS_COLS;
-            // a lane holds 16 adjacent columns per sub-tile: four full 16-byte stores
-#pragma unroll
-            for (int sb = 0; sb < 2; ++sb) {
-                int4* q = reinterpret_cast<int4*>(dst + 64 * sb + 16 * t4);
-                __stcg(q + 0, make_int4(acc[sb][0][0], acc[sb][1][0], acc[sb][2][0], acc[sb][3][0]));
-                __stcg(q + 1, make_int4(acc[sb][4][0], acc[sb][5][0], acc[sb][6][0], acc[sb][7][0]));
-                __stcg(q + 2, make_int4(acc[sb][0][1], acc[sb][1][1], acc[sb][2][1], acc[sb][3][1]));
-                __stcg(q + 3, make_int4(acc[sb][4][1], acc[sb][5][1], acc[sb][6][1], acc[sb][7][1]));
-            }
-        }
-    };
-    // byte offsets of this lane's four loads inside a 4 KiB swizzled box, for column span g8 of sub-tile 0 / 1
-    // and K half 0 (half 1 is 16 rows = 2048 bytes further): row r, byte c -> r*128 + ((c/16) ^ (r%8))*16 + c%16
-    uint32_t off[2][4];
-#pragma unroll
-    for (int sp = 0; sp < 2; ++sp)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = rs_krow(0, t4, i);
-            const int c = 64 * sp + 8 * g8;
-            off[sp][i] = static_cast<uint32_t>(r * 128 + (((c >> 4) ^ (r & 7)) << 4) + (c & 15));
-        }
-
-    bool ok = true;
-    for (int t = 0; t < run; ++t) {
-        const int64_t chunk = begin + t;
-        const int strip = static_cast<int>(chunk / KC);
-        if (strip != cur_strip) {
-            if (cur_strip >= 0) finish_strip();
-            cur_strip = strip;
-            clear();
-        }
-        const int slot = t % slots;
-        if (!mbar_wait_bounded(&bars[slot], static_cast<uint32_t>((t / slots) & 1), abort_word, RS_WAIT_LIMIT)) {
-            *abort_word = 1u;
-            atomicCAS(&g_gemv_device_status, 0, 204);
-            ok = false;
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        // pull the box into registers, hand the slot back at once, then do the arithmetic
-        const uint8_t* box = ring + static_cast<size_t>(slot) * RS_BOX_BYTES;
-        uint2 w[2][2][4];  // [sub-tile][K half][row of the lane's K group]
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb)
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) w[sb][h][i] = *reinterpret_cast<const uint2*>(box + h * 2048 + off[sb][i]);
-        uint32_t a0 = 0, a2 = 0;
-        if (g8 < p.m) {
-            a0 = xs[(g8 * run_max + t) * 8 + t4];
-            a2 = xs[(g8 * run_max + t) * 8 + 4 + t4];
-        }
-        __syncwarp();  // every lane holds its part of the box
-        if (lane == 0 && t + slots < run) issue(t + slots);
-#pragma unroll
-        for (int sb = 0; sb < 2; ++sb) {
-            uint32_t b0[8], b1[8];
-            transpose4x4_bytes(w[sb][0][0].x, w[sb][0][1].x, w[sb][0][2].x, w[sb][0][3].x, *reinterpret_cast<uint32_t(*)[4]>(&b0[0]));
-            transpose4x4_bytes(w[sb][0][0].y, w[sb][0][1].y, w[sb][0][2].y, w[sb][0][3].y, *reinterpret_cast<uint32_t(*)[4]>(&b0[4]));
-            transpose4x4_bytes(w[sb][1][0].x, w[sb][1][1].x, w[sb][1][2].x, w[sb][1][3].x, *reinterpret_cast<uint32_t(*)[4]>(&b1[0]));
-            transpose4x4_bytes(w[sb][1][0].y, w[sb][1][1].y, w[sb][1][2].y, w[sb][1][3].y, *reinterpret_cast<uint32_t(*)[4]>(&b1[4]));
-#pragma unroll
-            for (int j = 0; j < 8; ++j) mma_s8_16x8x32_top(acc[sb][j][0], acc[sb][j][1], a0, a2, b0[j], b1[j]);
-        }
-    }
-    if (ok && cur_strip >= 0) finish_strip();
-}
-
-// Two builds of the streaming kernel.  The plain one may use the whole register file.  The other is capped at 112
-// registers so that, with the reduce kernel capped at 32, one reduce block fits on every SM beside a streaming CTA: under
-// programmatic stream serialization the reduce blocks are then already resident when the streaming kernel ends and their
-// launch latency disappears (23.1 -> 19.4 us at m = 1, 2).  That only pays while all reduce blocks fit (56 x m <= SMs);
-// with more rows the cap's spills cost more than the launch it hides (m = 4: 23.4 -> 24.6 us), so m > 2 uses the plain pair.
-template <bool RAW>
-__global__ void __launch_bounds__(RS_THREADS, 1)
-gemv_q8_rrr_stream_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemvParams p) {
-    rrr_stream_body<RAW>(tmap_b, p);
-}
-
-template <bool RAW>
-__global__ void __maxnreg__(112)
-gemv_q8_rrr_stream_lean_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemvParams p) {
-    rrr_stream_body<RAW>(tmap_b, p);
-}
-
-// Adds, for 256 columns of a strip and one activation row, the partial rows of the CTAs that shared the strip,
-// and stores the result.  Sixteen partial rows are requested at a time: the loads are all that this kernel waits for.
-template <bool RAW>
-__device__ __forceinline__ void rrr_reduce_body(const GemvParams& p) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // the streaming kernel's partial rows are complete and visible
-    const int col = blockIdx.x * 256 + threadIdx.x;
-    const int strip = col / RS_STRIP;
-    const int in_strip = col - strip * RS_STRIP;
-    const int r = blockIdx.y;
-    const int64_t g = blockIdx.z;
-    const int KC = p.rs_items_per_block;
-    const int ctas = p.rs_ctas;
-    const int64_t total = static_cast<int64_t>(p.rs_blocks) * KC;
-    // the CTA that owns a chunk is the largest c with c * total < (chunk + 1) * ctas
-    const int c_lo = static_cast<int>(((static_cast<int64_t>(strip) * KC + 1) * ctas - 1) / total);
-    const int c_hi = static_cast<int>(((static_cast<int64_t>(strip + 1) * KC) * ctas - 1) / total);
-    if (col >= p.n) return;
-    // partial row of CTA c: slot c + strip
-    const int32_t* base = p.rs_partials + ((g * p.rs_slots_total + strip) * static_cast<int64_t>(p.m) + r) * RS_STRIP + in_strip;
-    const int64_t step = static_cast<int64_t>(p.m) * RS_STRIP;
-    int sum = 0;
-    for (int c = c_lo; c <= c_hi; c += 16) {
-        int v[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = (c + u <= c_hi) ? __ldcg(base + (c + u) * step) : 0;
-#pragma unroll
-        for (int u = 0; u < 16; ++u) sum += v[u];
-    }
-    store_result<RAW>(p, g, r, col, sum);
-}
-
-template <bool RAW>
-__global__ void __launch_bounds__(256)
-gemv_q8_rrr_reduce_kernel(const GemvParams p) {
-    rrr_reduce_body<RAW>(p);
-}
-
-template <bool RAW>
-__global__ void __maxnreg__(32)
-gemv_q8_rrr_reduce_lean_kernel(const GemvParams p) {
-    rrr_reduce_body<RAW>(p);
-}
-
 // ---- any layout, any alignment: one warp per output column, byte loads ----
 template <bool RAW>
 __global__ void __launch_bounds__(GEMV_THREADS)
@@ -1108,6 +852,13 @@ RrrPlan plan_rrr(int32_t n, int32_t k) {
     rows = ((rows + 31) / 32) * 32;
     if (rows < 32) rows = 32;
     if (rows > 2048) rows = 2048;
+    // no more slices than keep the partial rows (slices x n per activation row) inside the scratch the streaming
+    // kernel asks for ((160 + strips of 1024 columns) x 1024), so one workspace size serves both
+    const int64_t cap = (160 + (static_cast<int64_t>(n) + 1023) / 1024) * 1024 / (n > 0 ? n : 1);
+    if (cap >= 1 && (k + rows - 1) / rows > cap) {
+        rows = static_cast<int>((k + cap - 1) / cap);
+        rows = ((rows + 31) / 32) * 32;
+    }
     pl.kslice_rows = rows;
     pl.num_kslices = (k + rows - 1) / rows;
     if (pl.num_kslices < 1) pl.num_kslices = 1;
@@ -1259,10 +1010,10 @@ int32_t launch_rrr(GemvParams p, int batch, const GemvDesc& gd, cudaStream_t str
     p.kslice_rows = pl.kslice_rows;
     p.num_kslices = pl.num_kslices;
     if (pl.num_kslices > 1) {
-        const size_t need = gemv_q8_workspace_bytes(p.m, p.n, p.k, batch, BQ_LAYOUT_RRR);
+        const size_t tickets_bytes = align_up(static_cast<size_t>(batch) * pl.col_blocks * sizeof(unsigned int), 256);
+        const size_t need = tickets_bytes + static_cast<size_t>(batch) * pl.num_kslices * p.m * p.n * sizeof(int32_t);
         if (gd.workspace == nullptr || gd.workspace_bytes < need) return BQ_STATUS_WORKSPACE;
         if (!aligned16(gd.workspace)) return BQ_STATUS_MISALIGNED;
-        const size_t tickets_bytes = align_up(static_cast<size_t>(batch) * pl.col_blocks * sizeof(unsigned int), 256);
         p.ws_tickets = static_cast<unsigned int*>(gd.workspace);
         p.ws_partials = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(gd.workspace) + tickets_bytes);
         // the workspace is opaque scratch: the tickets must start at zero on every call
@@ -1277,95 +1028,7 @@ int32_t launch_rrr(GemvParams p, int batch, const GemvDesc& gd, cudaStream_t str
     return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
 }
 
-struct RsPlan {
-    bool ok;
-    int chunks_per_strip, strips, ctas, slots, slots_total, run_max;
-    size_t smem;
-};
-
-// Needs the SM count: shape the run for the current device.
-RsPlan plan_rrr_stream(int m, int n, int k, int sms) {
-    RsPlan pl = {};
-    pl.ok = false;
-    if (sms <= 0 || m <= 0 || n <= 0 || k <= 0) return pl;
-    pl.chunks_per_strip = (k + RS_ROWS - 1) / RS_ROWS;
-    pl.strips = (n + RS_STRIP - 1) / RS_STRIP;
-    const int64_t total = static_cast<int64_t>(pl.strips) * pl.chunks_per_strip;
-    int ctas = sms < RS_MAX_CTAS ? sms : RS_MAX_CTAS;
-    if (total < ctas) ctas = static_cast<int>(total);
-    pl.ctas = ctas;
-    const int64_t per_cta = (total + ctas - 1) / ctas;
-    if (per_cta > 4096) return pl;
-    pl.run_max = static_cast<int>(per_cta);
-    pl.slots_total = ctas + pl.strips;
-    const size_t x_bytes = static_cast<size_t>(m) * pl.run_max * 8 * 4;
-    if (1024 + x_bytes + 2 * RS_WARPS * RS_BOX_BYTES + 1024 > 232448) return pl;  // two ring slots must still fit
-    const size_t fixed = 1024 + x_bytes + RS_WARPS * 3 * 8 + RS_WARPS * 4 + 64;
-    const size_t budget = 232448;  // 227 KiB of shared memory per CTA
-    int slots = static_cast<int>((budget - fixed) / (RS_WARPS * RS_BOX_BYTES));
-    if (slots > 3) slots = 3;
-    if (slots < 2) return pl;
-    pl.slots = slots;  // ring slots per warp
-    pl.smem = 1024 + static_cast<size_t>(RS_WARPS) * slots * RS_BOX_BYTES + x_bytes + RS_WARPS * slots * 8 + RS_WARPS * 4 + 64;
-    pl.ok = true;
-    return pl;
-}
-
-size_t rrr_stream_workspace_bytes(int m, int n, int batch) {
-    const size_t strips = static_cast<size_t>((n + RS_STRIP - 1) / RS_STRIP);
-    return static_cast<size_t>(batch) * (RS_MAX_CTAS + strips) * m * RS_STRIP * sizeof(int32_t);
-}
-
-template <bool RAW>
-int32_t launch_rrr_stream(GemvParams p, int batch, const RsPlan& pl, const GemvDesc& gd, cudaStream_t stream) {
-    CUtensorMap map_b;
-    const int64_t rows = (batch > 1 && gd.stride_b > 0) ? (static_cast<int64_t>(batch) - 1) * (gd.stride_b / gd.ldb) + p.k
-                                                        : p.k;
-    if (!make_mnmajor_tensor_map(&map_b, p.b, rows, p.n, p.ldb, RS_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
-    p.rs_items_per_block = pl.chunks_per_strip;
-    p.rs_blocks = pl.strips;
-    p.rs_slots = pl.slots;
-    p.rs_run_max = pl.run_max;
-    p.rs_ctas = pl.ctas;
-    p.rs_slots_total = pl.slots_total;
-    p.rs_partials = static_cast<int32_t*>(gd.workspace);
-    const int reduce_blocks = ((p.n + 255) / 256) * p.m * batch;
-    const bool lean = reduce_blocks <= sm_count_cached();
-    auto kern = lean ? gemv_q8_rrr_stream_lean_kernel<RAW> : gemv_q8_rrr_stream_kernel<RAW>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pl.smem)) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return BQ_STATUS_LAUNCH_FAILURE;
-    }
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(pl.ctas, batch, 1);
-    cfg.blockDim = dim3(RS_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = pl.smem;
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = p.pdl ? 1 : 0;
-    if (cudaLaunchKernelEx(&cfg, kern, map_b, p) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return BQ_STATUS_LAUNCH_FAILURE;
-    }
-    // the reduction may be scheduled while the streaming kernel runs; it waits for it on the device
-    cudaLaunchConfig_t rcfg = {};
-    rcfg.gridDim = dim3((p.n + 255) / 256, p.m, batch);
-    rcfg.blockDim = dim3(256, 1, 1);
-    rcfg.dynamicSmemBytes = 0;
-    rcfg.stream = stream;
-    rcfg.attrs = attr;
-    rcfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&rcfg, lean ? gemv_q8_rrr_reduce_lean_kernel<RAW> : gemv_q8_rrr_reduce_kernel<RAW>, p) != cudaSuccess) {
-        (void)cudaGetLastError();
-        return BQ_STATUS_LAUNCH_FAILURE;
-    }
-    return BQ_STATUS_OK;
-}
-
-#include "gemv_q8_umma.cuh"
+#include "gemv_q8_rrr_rows.cuh"
 
 template <bool RAW>
 int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
@@ -1381,10 +1044,8 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
     p.ws_partials = nullptr; p.ws_tickets = nullptr;
     p.pdl = g.pdl;
     p.mma_groups = 0;
-    p.rs_items_per_block = 0; p.rs_blocks = 0; p.rs_slots = 0; p.rs_run_max = 0; p.rs_ctas = 0;
-    p.rs_partials = nullptr; p.rs_slots_total = 0;
+    p.rr_strips = 0; p.rr_run_max = 0; p.rr_ctas = 0; p.rr_slots_total = 0; p.rr_rows_total = 0; p.rr_partials = nullptr;
     p.xq_x = nullptr; p.xq_ldx = 0; p.xq_qmin = -127; p.xq_qmax = 127; p.xq_scale_out = nullptr;
-    p.gu_kblocks = 0; p.gu_smax = 0; p.gu_ctas = 0; p.gu_team = 1; p.gu_units = 0; p.gu_partials = nullptr;
 
     // the streaming kernels need 16-byte alignment of every weight row segment they load
     bool fast = g.k > 0 && aligned16(g.a) && aligned16(g.b) && (g.stride_b % 16 == 0) && (g.ldb % 16 == 0);
@@ -1400,8 +1061,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
         return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
     }
     // Test hooks (set_tuning key 1): 1 = bulk-copy dp4a kernel where legal, 2 = register-streaming kernel, 3 = tensor-core
-    // streaming kernel also for m == 1, 7 = mma.sync streaming kernel for row-major weights, 8 = direct-load split-K
-    // kernel for row-major weights, 9 = byte-load kernel.
+    // streaming kernel also for m == 1, 8 = direct-load split-K kernel for row-major weights, 9 = byte-load kernel.
     // K-contiguous weights, two or more activation rows: tensor-core streaming kernel
     const bool mma_ok = g.layout == BQ_LAYOUT_RCR && mma_gemv_ok(p);
     if (mma_ok &&
@@ -1422,28 +1082,15 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
             default: return launch_rcr_stream<4, RAW>(p, g.batch, stream);
         }
     }
-    // N-contiguous weights, one batch slot: the tcgen05 kernel, which consumes the copied tiles without transposing them
-    // (variant 7 keeps the mma.sync streaming kernel, variant 8 the direct-load kernel)
-    if (g.layout == BQ_LAYOUT_RRR && g.variant != 8 && g.variant != 7 && g.batch == 1 &&
-        g.n * static_cast<int64_t>(g.k) >= (1 << 18) && (g.m == 1 || g.lda % 16 == 0)) {
-        // two CTAs per SM, each on its own run of units
-        const GuPlan pl = plan_rrr_umma(g.m, g.n, g.k, sm_count_cached() * 2, 1);
-        const size_t need = gemv_q8_workspace_bytes(g.m, g.n, g.k, g.batch, BQ_LAYOUT_RRR);
-        if (pl.ok && pl.ws_bytes <= need) {
-            if (g.workspace == nullptr || g.workspace_bytes < need) return BQ_STATUS_WORKSPACE;
-            if (!aligned16(g.workspace)) return BQ_STATUS_MISALIGNED;
-            return launch_rrr_umma<RAW>(p, pl, g, stream);
-        }
-    }
-    // N-contiguous weights: the tensor-copy streaming kernel (variant 8 keeps the direct-load kernel)
-    if (g.layout == BQ_LAYOUT_RRR && g.variant != 8 && g.n * static_cast<int64_t>(g.k) >= (1 << 18) &&
-        (g.batch == 1 || g.stride_b == 0 || g.stride_b % g.ldb == 0)) {
-        const RsPlan pl = plan_rrr_stream(g.m, g.n, g.k, sm_count_cached());
+    // N-contiguous weights: the row-run streaming kernel (1 KiB bulk copies, ldmatrix-transposed fragments).
+    // Each path below checks the scratch its own kernel needs.
+    const bool rrr_big = g.layout == BQ_LAYOUT_RRR && g.n * static_cast<int64_t>(g.k) >= (1 << 18);
+    if (rrr_big && g.variant == 0) {
+        const RrPlan pl = plan_rrr_rows(g.m, g.n, g.k, g.batch, sm_count_cached());
         if (pl.ok) {
-            const size_t need = gemv_q8_workspace_bytes(g.m, g.n, g.k, g.batch, BQ_LAYOUT_RRR);
-            if (g.workspace == nullptr || g.workspace_bytes < need) return BQ_STATUS_WORKSPACE;
+            if (g.workspace == nullptr || g.workspace_bytes < pl.ws_bytes) return BQ_STATUS_WORKSPACE;
             if (!aligned16(g.workspace)) return BQ_STATUS_MISALIGNED;
-            return launch_rrr_stream<RAW>(p, g.batch, pl, g, stream);
+            return launch_rrr_rows<RAW>(p, g.batch, pl, g.workspace, stream);
         }
     }
 #define BQ_GEMV_CASE(MRV)                                                                  \
@@ -1468,7 +1115,7 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
 
 size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout) {
     if (layout != BQ_LAYOUT_RRR || m <= 0 || n <= 0 || k <= 0 || batch <= 0) return 0;
-    // the larger of what the two row-major-weight kernels ask for: which one runs depends on alignment and device
+    // the larger of what the row-major-weight kernels ask for: which one runs depends on alignment and device
     const RrrPlan pl = plan_rrr(n, k);
     size_t direct = 0;
     if (pl.num_kslices > 1) {
@@ -1476,7 +1123,7 @@ size_t gemv_q8_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t batch, i
         const size_t partials = static_cast<size_t>(batch) * pl.num_kslices * m * n * sizeof(int32_t);
         direct = tickets + partials;
     }
-    const size_t streamed = n * static_cast<int64_t>(k) >= (1 << 18) ? rrr_stream_workspace_bytes(m, n, batch) : 0;
+    const size_t streamed = n * static_cast<int64_t>(k) >= (1 << 18) ? rrr_rows_workspace_bytes(m, n, k, batch) : 0;
     return direct > streamed ? direct : streamed;
 }
 

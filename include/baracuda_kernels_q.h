@@ -397,7 +397,12 @@ int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_pdl_run(
  * This entry point has no counterpart in the reference.
  *   - The array holds BARACUDA_Q_GEMV_STATIC_SCRATCH_BYTES (8 MiB) on every GPU that loads
  *     the library, until the process exits.  A shape whose *_workspace_size exceeds it is
- *     rejected with status 4; *_static_ws_capacity returns the limit.
+ *     rejected with status 4; *_static_ws_capacity returns the limit.  What fits: the scratch is
+ *     (160 + ceil(N / 1024)) * m * 4 KiB for row-major weights with up to 380 928 row pieces
+ *     (ceil(N / 1024) * K), so every m <= 8 fits for N <= 98 304 within that bound -- e.g. all decode
+ *     projections of an 8B- or 70B-class model (4096 x 14336, 14336 x 4096, 8192 x 28672 at m = 8:
+ *     5.4 to 6.0 MiB); K-contiguous weights (layout 1) need no scratch at all.  Invalid problems
+ *     report the same status as the regular entry point (the size limit is checked last).
  *   - Nothing is allocated or freed, here or in any routine it calls.
  *   - The first call on a device looks up the array's device address (with that device
  *     current); make that first call before starting any stream capture.
@@ -612,14 +617,12 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  * Diagnostics and test hooks (no counterpart in the reference).
  * device_status: synchronous read-and-clear of the word a kernel sets when one
  * of its bounded barrier waits ran out (0 = none; the code names the kernel and
- * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 131..134 tcgen05 GEMV,
- * 201..206 streaming GEMVs, 299 the self-test).  Call it after synchronising the stream.
+ * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 201..207 streaming GEMVs, 299 the self-test).  Call it after synchronising the stream.
  * set_tuning: forces a kernel choice for the CALLING THREAD only (thread-local; other threads' launches are not
  * affected, nothing process-wide is kept), so tests can run every kernel on the same shapes:
  *   key 0  GEMM tile: 0 automatic; 64, 128, 256 = 1-CTA kernel with that N-tile; 512 = the CTA-pair kernel;
  *   key 1  GEMV kernel: 0 automatic; 1 bulk-copy dp4a kernel; 2 register-streaming kernel; 3 tensor-core streaming
- *          kernel also for m = 1; 7 mma.sync streaming kernel (row-major weights); 8 direct-load split-K kernel
- *          (row-major weights); 9 byte-load kernel;
+ *          kernel also for m = 1; 8 direct-load split-K kernel (row-major weights); 9 byte-load kernel;
  *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128;
  *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
  * Any other key or value returns 2.

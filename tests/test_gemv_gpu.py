@@ -203,12 +203,15 @@ def test_dependent_launch_mode_gives_the_same_results(oracle):
         assert np.array_equal(bf16_bits(d), want)
 
 
-@pytest.mark.parametrize("variant", [0, 7, 8])  # automatic, mma.sync streaming kernel, direct-load split-K kernel
+@pytest.mark.parametrize("variant", [0, 8])  # automatic (row-run streaming kernel), direct-load split-K kernel
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (2, 1040, 2064), (3, 272, 1000), (5, 14336, 512), (8, 2048, 4100),
-                                   (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096), (2, 32768, 8192)])
+                                   (7, 528, 8192), (1, 16, 16400), (4, 14336, 4096), (2, 32768, 8192), (1, 65536, 8192),
+                                   (3, 1040, 30), (2, 2064, 33), (6, 48, 20000)])
 def test_both_row_major_weight_kernels_on_the_same_shapes(oracle, shape, variant):
     """Weights row-major [K, N] (the reference GEMV's layout, gemv_dense.cu:128-171): int32 sums are exact whichever
-    kernel runs; ragged K (not a multiple of the 32-row copy), N that is not a multiple of the 256-column block."""
+    kernel runs; ragged K (not a multiple of the 32-row stage, shorter than one stage), N that is not a multiple of the
+    1024-column strip, K so long that the run crosses several strips' worth of stages, and 65536 x 8192, which the
+    streaming kernel serves with two waves of CTAs."""
     m, n, k = shape
     aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m * 1000 + n + k)
     want = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)

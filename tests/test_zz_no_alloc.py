@@ -104,7 +104,7 @@ def test_static_scratch_entry_allocates_nothing():
     assert _free_bytes() == before
 
 
-@pytest.mark.parametrize("variant", [0, 7, 8])  # automatic, mma.sync streaming kernel, direct-load kernel (tickets in the scratch)
+@pytest.mark.parametrize("variant", [0, 8])  # automatic (streaming kernel), direct-load kernel (tickets in the scratch)
 def test_static_scratch_every_row_major_kernel_twice(oracle, variant):
     """Every kernel that takes scratch, twice in a row on the shared array: the direct-load kernel keeps tickets
     there that must be cleared per call, the streaming kernels partial rows."""
