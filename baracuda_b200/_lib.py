@@ -99,6 +99,12 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run": (
         _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _f32,
                _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_nshard_run": (
+        _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _f32,
+               _vp, _vp, _i64] + _TAIL),
+    "baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_nshard_run": (
+        _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _f32,
+               _vp, _vp, _i64] + _TAIL),
     "baracuda_kernels_q_selftest_bounded_wait": (_i32, [_i64, _vp]),
     "baracuda_kernels_gemm_q8_kshard_workspace_size": (_sz, [_i32, _i32]),
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run": (

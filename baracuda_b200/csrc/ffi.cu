@@ -20,6 +20,13 @@ thread_local ThreadTuning t_tuning;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Longest K for which an int8 contraction cannot leave the 32-bit accumulator: K * 128 * 128 < 2^31.  The reference's
+// tensor-core path saturates each mma.sync (".satfinite", baracuda_int8_rrr_sm80.cuh:86-92) and its test oracle adds
+// with saturation (crates/baracuda-kernels/tests/int8_rrr_smoke.rs:76-131); what tcgen05.mma kind::i8 does on overflow
+// is not specified, so beyond this K the int8 symbols answer UNSUPPORTED instead of returning sums that may differ.
+constexpr int32_t kMaxInt8K = 131071;
+int32_t int8_k_status(int32_t k) { return k > kMaxInt8K ? bq::BQ_STATUS_UNSUPPORTED : bq::BQ_STATUS_OK; }
+
 // Shape / leading-dimension / alignment rules shared by run and can_implement.
 // Pointer arguments may be null here (can_implement is callable before the
 // buffers exist); alignment of a null pointer is not judged.
@@ -105,6 +112,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
                            : gemm_bf16_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (const int32_t es = epilogue_validate(epi, false); es != bq::BQ_STATUS_OK) return es;
+    if (kind == bq::BQ_KIND_S8 && int8_k_status(k) != bq::BQ_STATUS_OK) return bq::BQ_STATUS_UNSUPPORTED;
     if (raw && epi.kind != 0) return bq::BQ_STATUS_UNSUPPORTED;
     if (k == 0 && (epi.kind != 0 || beta != 0.0f)) return bq::BQ_STATUS_UNSUPPORTED;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
@@ -171,6 +179,7 @@ int32_t gemm_swiglu_run(int32_t kind, int32_t m, int32_t n2, int32_t k, const vo
     const int32_t st = gemm_swiglu_validate(m, n2, k, a, lda, b, ldb, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (bias && (reinterpret_cast<uintptr_t>(bias) & 3u)) return bq::BQ_STATUS_MISALIGNED;
+    if (kind == bq::BQ_KIND_S8 && int8_k_status(k) != bq::BQ_STATUS_OK) return bq::BQ_STATUS_UNSUPPORTED;
     if (k == 0 && bias) return bq::BQ_STATUS_UNSUPPORTED;
     if (m == 0 || n2 == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
@@ -198,7 +207,7 @@ int32_t gemm_swiglu_run(int32_t kind, int32_t m, int32_t n2, int32_t k, const vo
     g.swiglu = 1;
     g.force_block_n = t_tuning.force_block_n;
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
-    if (g.force_pair_tile_n % 64 != 0) g.force_pair_tile_n = 0;
+    if (g.force_pair_tile_n % 64 != 0 && g.force_pair_tile_n != 2) g.force_pair_tile_n = 0;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -217,6 +226,7 @@ int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t 
     const int32_t st = gemm_q8_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (const int32_t es = epilogue_validate(epi, kind == bq::BQ_KIND_S8); es != bq::BQ_STATUS_OK) return es;
+    if (kind == bq::BQ_KIND_S8 && int8_k_status(k) != bq::BQ_STATUS_OK) return bq::BQ_STATUS_UNSUPPORTED;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b))) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (beta != 0.0f && !c) return bq::BQ_STATUS_INVALID_PROBLEM;
@@ -266,7 +276,7 @@ int32_t gemv_validate(int32_t m, int32_t n, int32_t k, int32_t batch, int32_t la
     const int64_t min_ldb = (layout == bq::BQ_LAYOUT_RRR) ? min_n : min_k;
     if (lda < min_k || ldb < min_ldb || ldd < min_n) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (batch > 1 && stride_d == 0) return bq::BQ_STATUS_INVALID_PROBLEM;
-    return bq::BQ_STATUS_OK;
+    return int8_k_status(k);  // dp4a and mma.sync (without .satfinite) wrap: refuse K that could overflow
 }
 
 int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, int32_t layout, float alpha,
@@ -314,24 +324,25 @@ int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, in
 
 }  // namespace
 
-int32_t bq::launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+int32_t bq::launch_gemm_bf16_checked(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                                     const void* b, int64_t ldb, void* d, int64_t ldd, const void* scale_a,
                                     const void* scale_b, int32_t scale_mode, float alpha, void* const* peer_d,
                                     int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream) {
+    if (layout != bq::BQ_LAYOUT_RCR && layout != bq::BQ_LAYOUT_RRR) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (!peer_d) {
-        return gemm_rcr_run(kind, 0, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd, scale_a, scale_b, scale_mode, alpha,
-                            0.0f, stream);
+        return gemm_run(layout, kind, 0, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd, scale_a, scale_b, scale_mode, alpha,
+                        0.0f, stream);
     }
-    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
+    const int32_t st = gemm_validate(layout, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!d || (k > 0 && (!a || !b)) || !scale_a || !scale_b) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
         return bq::BQ_STATUS_INVALID_PROBLEM;
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return bq::BQ_STATUS_INVALID_PROBLEM;
-    if (k == 0) return bq::BQ_STATUS_UNSUPPORTED;
+    if (k == 0 || (kind == bq::BQ_KIND_S8 && int8_k_status(k) != bq::BQ_STATUS_OK)) return bq::BQ_STATUS_UNSUPPORTED;
     bq::GemmDesc g = {};
-    g.b_layout = bq::BQ_LAYOUT_RCR;
+    g.b_layout = layout;
     g.kind = kind;
     g.raw_out = 0;
     g.m = m;
@@ -371,6 +382,9 @@ int32_t bq::launch_gemm_raw_reduce_scatter_checked(int32_t kind, int32_t m, int3
     const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, nullptr, 0, staging[rank], n);
     if (st != bq::BQ_STATUS_OK) return st;
     if (!a || !b) return bq::BQ_STATUS_INVALID_PROBLEM;
+    // every rank's K slice: the sum over ranks must stay inside 32 bits as well
+    if (kind == bq::BQ_KIND_S8 && int8_k_status(k > kMaxInt8K / world ? kMaxInt8K + 1 : k) != bq::BQ_STATUS_OK)
+        return bq::BQ_STATUS_UNSUPPORTED;
     for (int r = 0; r < world; ++r) {
         if (!staging[r]) return bq::BQ_STATUS_INVALID_PROBLEM;
         if (!aligned16(staging[r])) return bq::BQ_STATUS_MISALIGNED;
@@ -415,7 +429,8 @@ size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(int32_t, int
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_rcr_bf16_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    const int32_t st = gemm_rcr_bf16_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return st != bq::BQ_STATUS_OK ? st : int8_k_status(k);
 }
 
 // ---- gated-MLP up-projection: silu(gate) * up -> bf16 ---------------------------------------
@@ -465,7 +480,8 @@ int32_t baracuda_kernels_q_interleave_gate_up_run(int64_t f_rows, int64_t row_by
 int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_can_implement(int32_t m, int32_t n, int32_t k, const void* act_q,
                                                                            int64_t lda, const void* weight_q, int64_t ldb,
                                                                            const void* output, int64_t ldd) {
-    return gemm_rcr_bf16_validate(m, n, k, act_q, lda, weight_q, ldb, nullptr, 0, output, ldd);
+    const int32_t st = gemm_rcr_bf16_validate(m, n, k, act_q, lda, weight_q, ldb, nullptr, 0, output, ldd);
+    return st != bq::BQ_STATUS_OK ? st : int8_k_status(k);
 }
 size_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
 int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
@@ -475,6 +491,7 @@ int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
     (void)workspace_bytes;
     const int32_t st = gemm_rcr_bf16_validate(m, n, k, act_q, lda, weight_q, ldb, nullptr, 0, output, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
+    if (int8_k_status(k) != bq::BQ_STATUS_OK) return bq::BQ_STATUS_UNSUPPORTED;
     if (m == 0 || n == 0) return bq::BQ_STATUS_OK;
     if (!output || (k > 0 && (!act_q || !weight_q)) || !weight_scale) return bq::BQ_STATUS_INVALID_PROBLEM;
     bq::GemmDesc g = {};
@@ -514,7 +531,8 @@ size_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size(int32_t, int32_t, 
 int32_t baracuda_kernels_gemm_s8_rcr_s32_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    const int32_t st = gemm_rcr_validate(m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return st != bq::BQ_STATUS_OK ? st : int8_k_status(k);
 }
 
 // ---- e4m3 -> bf16 --------------------------------------------------------------
@@ -564,7 +582,8 @@ size_t baracuda_kernels_gemm_s8_rcr_sm100a_workspace_size(int32_t, int32_t, int3
 int32_t baracuda_kernels_gemm_s8_rcr_sm100a_can_implement(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, const void* d, int64_t ldd) {
-    return gemm_q8_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    const int32_t st = gemm_q8_validate(bq::BQ_LAYOUT_RCR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
+    return st != bq::BQ_STATUS_OK ? st : int8_k_status(k);
 }
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
@@ -589,6 +608,14 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_can_implement(
         return VALIDATE(bq::BQ_LAYOUT_RRR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);                                  \
     }
 
+#define BQ_GEMM_TRIPLE_TAIL_S8(NAME, VALIDATE)                                                                       \
+    size_t NAME##_workspace_size(int32_t, int32_t, int32_t) { return 0; }                                           \
+    int32_t NAME##_can_implement(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b,         \
+                                 int64_t ldb, const void* c, int64_t ldc, const void* d, int64_t ldd) {              \
+        const int32_t st = VALIDATE(bq::BQ_LAYOUT_RRR, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);                     \
+        return st != bq::BQ_STATUS_OK ? st : int8_k_status(k);                                                       \
+    }
+
 int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, float alpha, float beta,
@@ -598,7 +625,7 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run(
     return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
                     BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream);
 }
-BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a, gemm_bf16_validate)
+BQ_GEMM_TRIPLE_TAIL_S8(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a, gemm_bf16_validate)
 
 int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
@@ -620,7 +647,7 @@ int32_t baracuda_kernels_gemm_s8_rrr_s32_sm100a_run(
     return gemm_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, 1, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, nullptr, nullptr, 0, alpha,
                     beta, stream);
 }
-BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_s8_rrr_s32_sm100a, gemm_validate)
+BQ_GEMM_TRIPLE_TAIL_S8(baracuda_kernels_gemm_s8_rrr_s32_sm100a, gemm_validate)
 
 int32_t baracuda_kernels_gemm_s8_rrr_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
@@ -630,7 +657,7 @@ int32_t baracuda_kernels_gemm_s8_rrr_sm100a_run(
     (void)workspace_bytes;
     return gemm_q8_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, alpha, beta, stream);
 }
-BQ_GEMM_TRIPLE_TAIL(baracuda_kernels_gemm_s8_rrr_sm100a, gemm_q8_validate)
+BQ_GEMM_TRIPLE_TAIL_S8(baracuda_kernels_gemm_s8_rrr_sm100a, gemm_q8_validate)
 
 int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
@@ -842,7 +869,7 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             t_tuning.direct_stores = value;
             return bq::BQ_STATUS_OK;
         case 2:
-            if (value != 0 && value != 256 && value != 224 && value != 192 && value != 128)
+            if (value != 0 && value != 2 && value != 256 && value != 224 && value != 192 && value != 128)
                 return bq::BQ_STATUS_INVALID_PROBLEM;
             t_tuning.force_pair_tile_n = value;
             return bq::BQ_STATUS_OK;

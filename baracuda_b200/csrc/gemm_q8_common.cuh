@@ -49,6 +49,15 @@ struct GemmParams {
     // (rows 64b..64b+31 = gate 32b..32b+31, rows 64b+32..64b+63 = up 32b..32b+31), n counts both, and the epilogue
     // stores silu(gate) * up as n/2 columns
     int swiglu;
+    // CTA-pair kernel, mixed-width schedule (0 = off: tiles of one width handed out round robin).  Tile columns
+    // [0, mixed_full_cols) are 256 wide, the rest of N is cut into 128-wide tiles; pair q runs the 256-wide tiles
+    // [full_begin[q], full_begin[q + 1]) and then the 128-wide tiles [half_begin[q], half_begin[q + 1]) (each list
+    // numbered m fastest).  The host balances the two lists so that the last, partly filled wave of wide tiles is
+    // replaced by narrow ones spread over every pair.
+    int mixed;
+    int mixed_full_cols;
+    uint16_t full_begin[98];
+    uint16_t half_begin[98];
 };
 
 // bias then activation on 32 values, in f32 — the chain of the reference's epilogue header

@@ -56,7 +56,9 @@ __device__ __forceinline__ void pair_timeout(volatile uint32_t* abort_word, int 
 
 // B_MN: the weight is row-major [K, N] (N contiguous): its tile is loaded as [128 K-rows x 128 N-bytes] and
 // described to the MMA as an MN-major operand.  Needs TN == 256 (one 128-byte atom of N per CTA).
-template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false>
+// MIXED (TN == 256, K-contiguous weights): the launch follows GemmParams' mixed-width schedule; a 128-wide tile uses
+// half of the stage's weight area, the weight map's box is 64 rows (two loads per stage for a wide tile).
+template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false, bool MIXED = false>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
@@ -112,63 +114,86 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const uint32_t tmem_base = *tmem_slot;
 
     const int num_kb = (p.k + PAIR_BLOCK_K - 1) / PAIR_BLOCK_K;
-    const int total_tiles = p.m_tiles * p.n_tiles;  // counted in 256 x 256 pair tiles
+    const int total_tiles = p.m_tiles * p.n_tiles;  // counted in 256 x TN pair tiles
+    // Every role walks the same tile list: body(m_blk, col0, tn, it) returns false to stop.
+    auto for_each_tile = [&](auto&& body) {
+        int it = 0;
+        if constexpr (MIXED) {
+            for (int phase = 0; phase < 2; ++phase) {
+                const int lo = phase ? p.half_begin[pair_id] : p.full_begin[pair_id];
+                const int hi = phase ? p.half_begin[pair_id + 1] : p.full_begin[pair_id + 1];
+                for (int tile = lo; tile < hi; ++tile, ++it) {
+                    const int nb = tile / p.m_tiles;
+                    const int col0 = phase ? p.mixed_full_cols * 256 + nb * 128 : nb * 256;
+                    if (!body(tile - nb * p.m_tiles, col0, phase ? 128 : 256, it)) return;
+                }
+            }
+        } else {
+            for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++it) {
+                const int nb = tile / p.m_tiles;
+                if (!body(tile - nb * p.m_tiles, nb * PAIR_TILE_N, PAIR_TILE_N, it)) return;
+            }
+        }
+    };
 
     if (warp == 0) {
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs) {
-                const int m_blk = tile % p.m_tiles;
-                const int n_blk = tile / p.m_tiles;
+            for_each_tile([&](int m_blk, int col0, int tn, int) {
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, PAIR_WAIT_LIMIT)) {
                         pair_timeout(abort_word, 111);
-                        ok = false;
-                        break;
+                        return false;
                     }
                     uint8_t* a_tile = tiles + stage * PAIR_STAGE_BYTES;
-                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * PAIR_STAGE_BYTES);
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (PAIR_A_BYTES + (tn / 2) * PAIR_BLOCK_K));
                     // completion bytes of both CTAs' loads are counted on the leader's barrier
                     const uint32_t full_on_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
                     tma_load_2d_pair(a_tile, &tmap_a, full_on_leader, kb * PAIR_BLOCK_K,
                                      m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS);
                     if constexpr (B_MN) {
                         tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader,
-                                         n_blk * PAIR_TILE_N + static_cast<int>(rank) * C::B_ROWS, kb * PAIR_BLOCK_K);
+                                         col0 + static_cast<int>(rank) * C::B_ROWS, kb * PAIR_BLOCK_K);
+                    } else if constexpr (MIXED) {
+                        const int row0 = col0 + static_cast<int>(rank) * (tn / 2);
+                        tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K, row0);
+                        if (tn == 256) {
+                            tma_load_2d_pair(a_tile + PAIR_A_BYTES + 64 * PAIR_BLOCK_K, &tmap_b, full_on_leader,
+                                             kb * PAIR_BLOCK_K, row0 + 64);
+                        }
                     } else {
                         tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
-                                         n_blk * PAIR_TILE_N + static_cast<int>(rank) * C::B_ROWS);
+                                         col0 + static_cast<int>(rank) * C::B_ROWS);
                     }
                     if (++stage == PAIR_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-            }
+                return true;
+            });
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t idesc = umma_idesc(KIND, PAIR_TILE_M, PAIR_TILE_N, B_MN);
+            constexpr uint32_t idesc_full = umma_idesc(KIND, PAIR_TILE_M, PAIR_TILE_N, B_MN);
+            constexpr uint32_t idesc_half = umma_idesc(KIND, PAIR_TILE_M, 128, B_MN);
             int stage = 0;
             uint32_t phase = 0;
-            bool ok = true;
-            int it = 0;
-            for (int tile = pair_id; ok && tile < total_tiles; tile += num_pairs, ++it) {
+            for_each_tile([&](int, int, int tn, int it) {
+                const uint32_t idesc = (MIXED && tn == 128) ? idesc_half : idesc_full;
                 const int buf = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait_bounded(&tempty_bar[buf], acc_phase ^ 1u, abort_word, PAIR_WAIT_LIMIT)) {
                     pair_timeout(abort_word, 112);
-                    break;
+                    return false;
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, abort_word, PAIR_WAIT_LIMIT)) {
                         pair_timeout(abort_word, 113);
-                        ok = false;
-                        break;
+                        return false;
                     }
                     tc_fence_after_sync();
                     const uint32_t a_addr = smem_u32(tiles + stage * PAIR_STAGE_BYTES);
@@ -188,23 +213,21 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         phase ^= 1u;
                     }
                 }
-                if (ok) umma_commit_pair(&tfull_bar[buf], 0x3);  // accumulator ready, both CTAs' epilogues
-            }
+                umma_commit_pair(&tfull_bar[buf], 0x3);  // accumulator ready, both CTAs' epilogues
+                return true;
+            });
         }
     } else {
         const int q = warp & 3;
         uint4* stage_buf = stage_all + (warp - 2) * 256;
-        int it = 0;
-        for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++it) {
+        for_each_tile([&](int m_blk, int tile_col0, int tn, int it) {
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            const int m_blk = tile % p.m_tiles;
-            const int n_blk = tile / p.m_tiles;
             float* sb_tile = sb_s + (warp - 2) * PAIR_TILE_N;
             if (!RAW && (!p.out_q8 || p.bias_kind != 0)) {
                 __syncwarp();
-                for (int i = lane; i < PAIR_TILE_N; i += 32) {
-                    const int col = n_blk * PAIR_TILE_N + i;
+                for (int i = lane; i < tn; i += 32) {
+                    const int col = tile_col0 + i;
                     if (!p.out_q8) sb_tile[i] = (p.scale_mode != 0) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
                     if (p.bias_kind == 1) {
                         sb_tile[p.bias_off + i] = col < p.n ? __ldg(reinterpret_cast<const float*>(p.bias) + col) : 0.0f;
@@ -217,10 +240,11 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, PAIR_WAIT_LIMIT)) {
                 pair_timeout(abort_word, 114);
-                break;
+                return false;
             }
             tc_fence_after_sync();
-            const int row = m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32 + lane;
+            const int row_base = m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32;
+            const int row = row_base + lane;
             const bool row_ok = row < p.m;
             float sa_row = 1.0f;
             if (!RAW && !p.out_q8) {
@@ -229,36 +253,37 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
             {
+                const int blocks = tn / 32;
                 int c = 0;
                 if constexpr (!RAW) {
                     // 64 columns at a time through the warp's staging buffer (coalesced 128-byte row segments)
-                    for (; c + 2 <= PAIR_TILE_N / 32; c += 2) {
-                        const int col0 = n_blk * PAIR_TILE_N + c * 32;
+                    for (; c + 2 <= blocks; c += 2) {
+                        const int col0 = tile_col0 + c * 32;
                         if (col0 >= p.n) break;  // warp-uniform
                         if (p.swiglu) {  // launch-uniform; the host guarantees whole 64-column blocks and aligned rows
-                            epilogue_block_64_swiglu<KIND>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
+                            epilogue_block_64_swiglu<KIND>(p, t_row + static_cast<uint32_t>(c * 32), row_base, lane, col0, sa_row,
                                                            sb_tile + c * 32, stage_buf);
                             continue;
                         }
                         if (!block_64_ok<FUSED>(p, col0)) break;
-                        epilogue_block_64<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
+                        epilogue_block_64<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), row_base, lane, col0, sa_row,
                                                        sb_tile + c * 32, stage_buf);
                     }
                 }
 #pragma unroll 1
-                for (; c < PAIR_TILE_N / 32; ++c) {
-                    const int col0 = n_blk * PAIR_TILE_N + c * 32;
+                for (; c < blocks; ++c) {
+                    const int col0 = tile_col0 + c * 32;
                     if (col0 >= p.n) break;  // warp-uniform
                     if constexpr (!RAW) {
                         if (block_32_ok<FUSED>(p, col0)) {
-                            epilogue_block_32<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, sa_row,
+                            epilogue_block_32<KIND, FUSED>(p, t_row + static_cast<uint32_t>(c * 32), row_base, lane, col0, sa_row,
                                                            sb_tile + c * 32, stage_buf);
                             continue;
                         }
                     }
                     if constexpr (RAW) {
                         if (p.rs_world > 1 && p.vec_store && col0 + 32 <= p.n) {  // warp-uniform
-                            epilogue_block_raw32_scatter(p, t_row + static_cast<uint32_t>(c * 32), m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32, lane, col0, stage_buf);
+                            epilogue_block_raw32_scatter(p, t_row + static_cast<uint32_t>(c * 32), row_base, lane, col0, stage_buf);
                             continue;
                         }
                     }
@@ -272,7 +297,8 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
-        }
+            return true;
+        });
     }
 
     // Teardown: nobody leaves (or frees TMEM) while the partner may still signal or read.
@@ -289,8 +315,67 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
 }
 
-template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false>
-int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
+// Relative cost of a 256 x 128 tile against a 256 x 256 one (1.0).  Between the operand-feed model (each CTA loads
+// 128 + 64 rows instead of 128 + 128 per K step: 0.75) and the MMA count (0.5); measured on 4096^3 and the prefill set.
+constexpr double MIXED_HALF_COST = 0.72;
+constexpr int MIXED_MAX_PAIRS = 96;
+
+struct MixedSchedule {
+    bool ok = false;
+    int full_cols = 0, pairs = 0;
+    double makespan = 0.0;
+    uint16_t full_begin[98] = {0};
+    uint16_t half_begin[98] = {0};
+};
+
+// 256-wide tiles for the first `full_cols` tile columns, 128-wide tiles for the rest of N.  The wide tiles are dealt
+// out evenly (contiguous runs, so a pair keeps its weight columns), then the narrow ones level the pairs: the smallest
+// finishing time T with sum_q floor((T - load_q) / c) >= number of narrow tiles.
+MixedSchedule build_mixed_schedule(int m_tiles, int n, int sm_pairs, int full_cols) {
+    MixedSchedule sc;
+    const int64_t f_tiles = static_cast<int64_t>(full_cols) * m_tiles;
+    const int rest = n - full_cols * 256;
+    const int half_cols = rest > 0 ? (rest + 127) / 128 : 0;
+    const int64_t h_tiles = static_cast<int64_t>(half_cols) * m_tiles;
+    if (f_tiles > 60000 || h_tiles > 60000 || f_tiles + h_tiles == 0) return sc;
+    int pairs = sm_pairs < MIXED_MAX_PAIRS ? sm_pairs : MIXED_MAX_PAIRS;
+    if (f_tiles + h_tiles < pairs) pairs = static_cast<int>(f_tiles + h_tiles);
+    const int base = static_cast<int>(f_tiles / pairs), extra = static_cast<int>(f_tiles % pairs);
+    const double c = MIXED_HALF_COST;
+    auto cap = [&](double t, int load) { return t > load ? static_cast<int64_t>((t - load) / c + 1e-9) : 0; };
+    double lo = base, hi = base + 1 + (h_tiles / pairs + 2) * c;
+    for (int i = 0; i < 40; ++i) {
+        const double mid = 0.5 * (lo + hi);
+        const int64_t can = (pairs - extra) * cap(mid, base) + extra * cap(mid, base + 1);
+        if (can >= h_tiles) hi = mid; else lo = mid;
+    }
+    int64_t left = h_tiles;
+    int fpos = 0, hpos = 0;
+    double worst = 0.0;
+    for (int q = 0; q < pairs; ++q) {
+        const int load = base + (q < extra ? 1 : 0);
+        int64_t take = cap(hi, load);
+        if (take > left) take = left;
+        if (q == pairs - 1) take = left;  // rounding slack, if any, ends on the last pair
+        sc.full_begin[q] = static_cast<uint16_t>(fpos);
+        sc.half_begin[q] = static_cast<uint16_t>(hpos);
+        fpos += load;
+        hpos += static_cast<int>(take);
+        left -= take;
+        const double t = load + c * take;
+        if (t > worst) worst = t;
+    }
+    sc.full_begin[pairs] = static_cast<uint16_t>(fpos);
+    sc.half_begin[pairs] = static_cast<uint16_t>(hpos);
+    sc.ok = (fpos == f_tiles && hpos == h_tiles);
+    sc.full_cols = full_cols;
+    sc.pairs = pairs;
+    sc.makespan = worst;
+    return sc;
+}
+
+template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false, bool MIXED = false>
+int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedule* mixed = nullptr) {
     using C = PairCfg<TN>;
     constexpr int PAIR_TILE_N = TN;
     constexpr int PAIR_SMEM_TOTAL = C::SMEM_TOTAL;
@@ -301,9 +386,20 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
     if constexpr (B_MN) {
         if (!make_mnmajor_tensor_map(&map_b, g.b, g.k, g.n, g.ldb, PAIR_BLOCK_K)) return BQ_STATUS_LAUNCH_FAILURE;
     } else {
-        if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, C::B_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
+        if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, MIXED ? 64 : C::B_ROWS)) return BQ_STATUS_LAUNCH_FAILURE;
     }
     GemmParams p;
+    p.mixed = 0;
+    p.mixed_full_cols = 0;
+    if constexpr (MIXED) {
+        if (!mixed || !mixed->ok) return BQ_STATUS_LAUNCH_FAILURE;
+        p.mixed = 1;
+        p.mixed_full_cols = mixed->full_cols;
+        for (int i = 0; i < 98; ++i) {
+            p.full_begin[i] = mixed->full_begin[i];
+            p.half_begin[i] = mixed->half_begin[i];
+        }
+    }
     p.d = g.d;
     p.ldd = g.ldd;
     p.sa = g.scale_a;
@@ -338,13 +434,13 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
         p.peer_d[r] = g.peer_d[r];
         if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
     }
-    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN, B_MN>;
+    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN, B_MN, MIXED>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
     }
     const int64_t tiles = static_cast<int64_t>(p.m_tiles) * p.n_tiles;
-    const int64_t pairs = tiles < sms / 2 ? tiles : sms / 2;
+    const int64_t pairs = MIXED ? mixed->pairs : (tiles < sms / 2 ? tiles : sms / 2);
     // Output rows go through the shared-memory staging (full 128-byte row segments per store) when the
     // stores cross NVLink (fused mode) or when there are so few waves of tiles that the last epilogue is
     // exposed; in long steady-state runs the direct per-thread stores leave more shared-memory bandwidth
@@ -375,7 +471,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream) {
 // (128 rows of A plus TN/2 rows of the weight); pick the width that minimises
 // (waves of pair tiles) x (that cost).  Narrow tiles only win when they remove a whole wave.
 int pick_tile_n(const GemmDesc& g) {
-    if (g.force_pair_tile_n != 0) return g.force_pair_tile_n;
+    if (g.force_pair_tile_n != 0 && g.force_pair_tile_n != 2) return g.force_pair_tile_n;
     const int sms = sm_count_of_current_device();
     const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
     const int64_t m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
@@ -395,16 +491,34 @@ int pick_tile_n(const GemmDesc& g) {
     return best;
 }
 
+// Cost of the best single-width schedule, in 256 x 256 tile times.
+double single_width_cost(const GemmDesc& g, int tn) {
+    const int sms = sm_count_of_current_device();
+    const int64_t pairs = sms / 2 > 0 ? sms / 2 : 1;
+    const int64_t tiles = static_cast<int64_t>((g.m + PAIR_TILE_M - 1) / PAIR_TILE_M) * ((g.n + tn - 1) / tn);
+    return static_cast<double>((tiles + pairs - 1) / pairs) * (CTA_ROWS + tn / 2) / 256.0;
+}
+
 template <uint32_t KIND, bool RAW, bool FUSED>
 int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
-    if (g.b_layout == BQ_LAYOUT_RRR) {
-        if constexpr (FUSED) {
-            return BQ_STATUS_UNSUPPORTED;
-        } else {
-            return launch_pair_tn<KIND, RAW, false, 256, true>(g, stream);
+    if (g.b_layout == BQ_LAYOUT_RRR) return launch_pair_tn<KIND, RAW, FUSED, 256, true>(g, stream);
+    const int tn = pick_tile_n(g);
+    // Mixed widths: when the wide tiles do not fill their last wave, the columns of that wave are cut into 128-wide
+    // tiles spread over all pairs (force_pair_tile_n 2 forces the mixed schedule, any other forced width keeps it off).
+    if (g.force_pair_tile_n == 0 || g.force_pair_tile_n == 2) {
+        const int sm_pairs = sm_count_of_current_device() / 2;
+        const int m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
+        const int nc = g.n / 256;
+        MixedSchedule best;
+        for (int x = nc; x >= 0 && x >= nc - 3; --x) {
+            const MixedSchedule sc = build_mixed_schedule(m_tiles, g.n, sm_pairs, x);
+            if (sc.ok && (!best.ok || sc.makespan < best.makespan - 1e-9)) best = sc;
+        }
+        if (best.ok && (g.force_pair_tile_n == 2 || best.makespan < 0.98 * single_width_cost(g, tn))) {
+            return launch_pair_tn<KIND, RAW, FUSED, 256, false, true>(g, stream, &best);
         }
     }
-    switch (pick_tile_n(g)) {
+    switch (tn == 2 ? 256 : tn) {
         case 256: return launch_pair_tn<KIND, RAW, FUSED, 256>(g, stream);
         case 224: return launch_pair_tn<KIND, RAW, FUSED, 224>(g, stream);
         case 192: return launch_pair_tn<KIND, RAW, FUSED, 192>(g, stream);

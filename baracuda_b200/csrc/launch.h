@@ -76,7 +76,8 @@ int32_t launch_reduce_dequant_broadcast(int32_t kind, int32_t rank, int32_t worl
                                         cudaStream_t stream);
 // Validates like the flat *_run symbols, then launches the bf16-out GEMM; with `peer_d` the epilogue
 // additionally stores into the `world` peer buffers at column offset rank * n.
-int32_t launch_gemm_rcr_checked(int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
+// `layout` is the weight storage (BQ_LAYOUT_RCR: [N,K] rows, BQ_LAYOUT_RRR: row-major [K,N], ldb >= the full N).
+int32_t launch_gemm_bf16_checked(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                                 const void* b, int64_t ldb, void* d, int64_t ldd, const void* scale_a,
                                 const void* scale_b, int32_t scale_mode, float alpha, void* const* peer_d,
                                 int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream);

@@ -61,7 +61,7 @@ const NcclApi& nccl() {
     return api;
 }
 
-int32_t nshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local,
+int32_t nshard_run(int32_t layout, int32_t kind, int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local,
                    int32_t k, const void* a, int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd,
                    const void* scale_a, const void* scale_b_local, int32_t scale_mode, float alpha, void* d_full,
                    void* const* peer_d, int64_t ldd_full, void* stream) {
@@ -86,12 +86,12 @@ int32_t nshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_
 
     int32_t st;
     if (kind == bq::BQ_KIND_S8) {
-        st = bq::launch_gemm_rcr_checked(kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
+        st = bq::launch_gemm_bf16_checked(layout, kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
                                          BARACUDA_Q_SCALE_PER_ROW_COL, alpha,
                                          gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE ? peer_d : nullptr, world, rank,
                                          ldd_full, s);
     } else {
-        st = bq::launch_gemm_rcr_checked(kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
+        st = bq::launch_gemm_bf16_checked(layout, kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
                                          scale_mode, alpha,
                                          gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE ? peer_d : nullptr, world, rank,
                                          ldd_full, s);
@@ -135,6 +135,8 @@ int32_t kshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_
     const size_t count = static_cast<size_t>(m) * static_cast<size_t>(n);
     if (!workspace || workspace_bytes < count * 4) return BARACUDA_Q_STATUS_WORKSPACE;
     if (reinterpret_cast<uintptr_t>(workspace) & 15u) return BARACUDA_Q_STATUS_MISALIGNED;
+    // int32 partial sums are added across ranks: the whole K (k_local * world) must keep them inside 32 bits
+    if (kind == bq::BQ_KIND_S8 && static_cast<int64_t>(k_local) * world > 131071) return BARACUDA_Q_STATUS_UNSUPPORTED;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
     const int32_t st = kind == bq::BQ_KIND_S8
@@ -260,8 +262,19 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(
     void* workspace, size_t workspace_bytes, void* stream) {
     (void)workspace;
     (void)workspace_bytes;
-    return nshard_run(bq::BQ_KIND_E4M3, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb, d_local, ldd,
-                      scale_a, scale_b_local, scale_mode, alpha, d_full, peer_d, ldd_full, stream);
+    return nshard_run(bq::BQ_LAYOUT_RCR, bq::BQ_KIND_E4M3, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb,
+                      d_local, ldd, scale_a, scale_b_local, scale_mode, alpha, d_full, peer_d, ldd_full, stream);
+}
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local, int32_t k, const void* a,
+    int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd, const void* scale_a,
+    const void* scale_b_local, int32_t scale_mode, float alpha, void* d_full, void* const* peer_d, int64_t ldd_full,
+    void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return nshard_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb,
+                      d_local, ldd, scale_a, scale_b_local, scale_mode, alpha, d_full, peer_d, ldd_full, stream);
 }
 
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
@@ -271,8 +284,21 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
     size_t workspace_bytes, void* stream) {
     (void)workspace;
     (void)workspace_bytes;
-    return nshard_run(bq::BQ_KIND_S8, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb, d_local, ldd,
-                      scale_a, scale_b_local, BARACUDA_Q_SCALE_PER_ROW_COL, alpha, d_full, peer_d, ldd_full, stream);
+    return nshard_run(bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb,
+                      d_local, ldd, scale_a, scale_b_local, BARACUDA_Q_SCALE_PER_ROW_COL, alpha, d_full, peer_d, ldd_full,
+                      stream);
+}
+
+int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather, int32_t m, int32_t n_local, int32_t k, const void* a,
+    int64_t lda, const void* b_local, int64_t ldb, void* d_local, int64_t ldd, const void* scale_a,
+    const void* scale_b_local, float alpha, void* d_full, void* const* peer_d, int64_t ldd_full, void* workspace,
+    size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
+    return nshard_run(bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, rank, world, comm, gather, m, n_local, k, a, lda, b_local, ldb,
+                      d_local, ldd, scale_a, scale_b_local, BARACUDA_Q_SCALE_PER_ROW_COL, alpha, d_full, peer_d, ldd_full,
+                      stream);
 }
 
 size_t baracuda_kernels_gemm_q8_kshard_workspace_size(int32_t m, int32_t n) {

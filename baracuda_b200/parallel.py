@@ -22,7 +22,7 @@ import torch
 
 from . import _lib
 from .plans import SCALE_PER_ROW_COL, _need_typed, _ptr, _stream_ptr
-from .vocab import BaracudaError, InvalidProblem, status_to_result
+from .vocab import BaracudaError, InvalidProblem, LayoutSku, status_to_result
 
 GATHER_NONE = 0
 GATHER_NCCL = 1
@@ -120,11 +120,16 @@ class ColumnParallelQGemmPlan:
     """N-sharded FP8 or W8A8 GEMM with an optional replicated output."""
 
     def __init__(self, ctx: TensorParallelContext, m: int, out_features: int, k: int, kind: str = "fp8",
-                 scale_mode: int = SCALE_PER_ROW_COL, gather: int = GATHER_NONE):
+                 scale_mode: int = SCALE_PER_ROW_COL, gather: int = GATHER_NONE, layout: LayoutSku = LayoutSku.Rcr):
+        """`layout` Rcr: the shard is rows [lo, hi) of the [N, K] weight (contiguous).  Rrr: the weight is row-major
+        [K, N] and the shard is its column range [lo, hi) -- pass the strided view `w[:, lo:hi]` as `w_local`."""
         if kind not in ("fp8", "w8a8"):
             raise InvalidProblem("kind must be 'fp8' or 'w8a8'")
         if gather not in (GATHER_NONE, GATHER_NCCL, GATHER_FUSED_PEER_STORE):
             raise InvalidProblem("unknown gather mode")
+        if layout not in (LayoutSku.Rcr, LayoutSku.Rrr):
+            raise InvalidProblem("unknown layout")
+        self.layout = layout
         if min(m, out_features, k) < 0:
             raise InvalidProblem("negative dimension")
         lo, hi = shard_range(out_features, ctx.world, ctx.rank)
@@ -174,14 +179,21 @@ class ColumnParallelQGemmPlan:
             peers = (C.c_void_p * self.ctx.world)(*peer_ptrs)
             ldd_full = ldd_full or self.n
         lib = _lib.load()
+        if self.layout is LayoutSku.Rrr:
+            if w_local.dim() != 2 or w_local.stride(1) != 1 or w_local.stride(0) < self.n_local:
+                raise InvalidProblem("Rrr: w_local must be the [K, N/G] column view of a row-major [K, N] weight")
+            ldb = max(int(w_local.stride(0)), 1)
+        else:
+            ldb = max(self.k, 1)
         common = (self.ctx.rank, self.ctx.world, self.ctx.comm, self.gather, self.m, self.n_local, self.k,
-                  _ptr(a), max(self.k, 1), _ptr(w_local), max(self.k, 1), _ptr(y_local), max(self.n_local, 1),
+                  _ptr(a), max(self.k, 1), _ptr(w_local), ldb, _ptr(y_local), max(self.n_local, 1),
                   _ptr(scale_a), _ptr(scale_b_local))
         tail = (_ptr(y_full), peers, ldd_full, None, 0, _stream_ptr(stream))
+        lay = self.layout.value
         if self.kind == "fp8":
-            st = lib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(*common, self.scale_mode, alpha, *tail)
+            st = getattr(lib, f"baracuda_kernels_gemm_fp8_e4m3_{lay}_bf16_sm100a_nshard_run")(*common, self.scale_mode, alpha, *tail)
         else:
-            st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(*common, alpha, *tail)
+            st = getattr(lib, f"baracuda_kernels_gemm_w8a8_s8_{lay}_bf16_sm100a_nshard_run")(*common, alpha, *tail)
         _check(st, "ColumnParallelQGemmPlan.forward")
 
 

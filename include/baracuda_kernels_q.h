@@ -71,6 +71,12 @@ extern "C" {
  * activation, product and sum rounded separately in f32; beta != 0 without C
  * returns 2; with beta == 0 C is not read.  The raw-accumulator SKUs take no C (3).
  * Alignment: a and b 16-byte aligned, lda and ldb multiples of 16.
+ * Accumulator range: every int8 symbol of this header (GEMM, GEMV, sharded forms) returns 3 (unsupported) for
+ * K > 131 071, the longest contraction whose sums cannot leave 32 bits (K * 128 * 128 < 2^31; for the K-sharded
+ * forms the bound applies to the K of all ranks together).  The reference saturates instead (mma.sync
+ * ".satfinite", crates/baracuda-kernels-sys/kernels/include/baracuda_int8_rrr_sm80.cuh:86-92, and the saturating
+ * adds of its test oracle, crates/baracuda-kernels/tests/int8_rrr_smoke.rs:76-131); up to that K the two agree
+ * bit for bit, beyond it tcgen05's behaviour is unspecified, so the call is refused rather than answered differently.
  * ------------------------------------------------------------------------- */
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k,
@@ -540,6 +546,26 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
     void* d_full, void* const* peer_d, int64_t ldd_full,
     void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same for a row-major weight [K, N] (the "rrr" layout): rank r's shard is the column range
+ * [r*n_local, (r+1)*n_local) of every weight row, so b_local points at column r*n_local of the full matrix and
+ * ldb stays the full N (>= n_local); every gather mode is served. */
+int32_t baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather,
+    int32_t m, int32_t n_local, int32_t k,
+    const void* a, int64_t lda, const void* b_local, int64_t ldb,
+    void* d_local, int64_t ldd,
+    const void* scale_a, const void* scale_b_local, int32_t scale_mode, float alpha,
+    void* d_full, void* const* peer_d, int64_t ldd_full,
+    void* workspace, size_t workspace_bytes, void* stream);
+int32_t baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_nshard_run(
+    int32_t rank, int32_t world, void* comm, int32_t gather,
+    int32_t m, int32_t n_local, int32_t k,
+    const void* a, int64_t lda, const void* b_local, int64_t ldb,
+    void* d_local, int64_t ldd,
+    const void* scale_a, const void* scale_b_local, float alpha,
+    void* d_full, void* const* peer_d, int64_t ldd_full,
+    void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---------------------------------------------------------------------------
  * K-sharded ("row-parallel") forward, the partner of the N-sharded one in an MLP block
  * (RowParallelLinearPlan::forward, crates/baracuda-megatron/src/lib.rs:1002-1200): rank r holds
@@ -623,7 +649,7 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  *   key 0  GEMM tile: 0 automatic; 64, 128, 256 = 1-CTA kernel with that N-tile; 512 = the CTA-pair kernel;
  *   key 1  GEMV kernel: 0 automatic; 1 bulk-copy dp4a kernel; 2 register-streaming kernel; 3 tensor-core streaming
  *          kernel also for m = 1; 8 direct-load split-K kernel (row-major weights); 9 byte-load kernel;
- *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128;
+ *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128; 2 = the mixed 256 / 128 schedule;
  *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
  * Any other key or value returns 2.
  * selftest_bounded_wait: launches one thread that waits, for at most limit_cycles SM clock cycles

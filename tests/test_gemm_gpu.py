@@ -98,7 +98,7 @@ def test_config0_w8a8_128x1024x1024(oracle):
     assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
 
 
-@pytest.mark.parametrize("block_n,pair_tn", [(64, 0), (128, 0), (256, 0), (512, 256), (512, 224), (512, 192), (512, 128)])
+@pytest.mark.parametrize("block_n,pair_tn", [(64, 0), (128, 0), (256, 0), (512, 256), (512, 224), (512, 192), (512, 128), (512, 2)])  # 2 = mixed 256 / 128 schedule
 def test_every_tile_config_many_tiles_and_tails(oracle, block_n, pair_tn):
     """More tiles than SMs (persistent loop, both TMEM buffers, ring wrap-around) with ragged M, N and K."""
     m, n, k = 1100, 2100, 656
@@ -494,3 +494,30 @@ def test_smoothquant_linear_per_tensor_activation_scale(oracle, shape):
     torch.cuda.synchronize()
     assert bq.device_status() == 0
     assert oracle.compare_bitexact(want, bf16_bits(out)) == -1
+
+
+@pytest.mark.parametrize("kind", ["s8", "fp8"])
+@pytest.mark.parametrize("shape", [(2304, 4100, 384), (4096, 4096, 256), (700, 1216, 512), (256, 128, 128), (5000, 2700, 192)])
+def test_cta_pair_kernel_mixed_tile_widths(oracle, kind, shape):
+    """The mixed schedule (256-wide tiles, then 128-wide tiles that level the last wave) forced onto shapes with several
+    waves, with a ragged last 128-wide column, with fewer tiles than CTA pairs, and with no wide tile at all."""
+    m, n, k = shape
+    bq.set_tuning(0, 512)
+    bq.set_tuning(2, 2)
+    try:
+        if kind == "s8":
+            aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n)
+            acc_ref = oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k)
+            acc = _run_w8a8(m, n, k, aq, wq, raw=True).view(m, n).cpu().numpy()
+            assert oracle.compare_bitexact(acc_ref, acc) == -1
+            out = _run_w8a8(m, n, k, aq, wq, sa, sb)
+            assert oracle.compare_bitexact(oracle.dequant_s32_bf16(acc_ref, sa, sb), bf16_bits(out).reshape(m, n)) == -1
+        else:
+            aq, wq, sa, sb = fp8_case(oracle, m, n, k, seed=m + n)
+            acc_ref = oracle.gemm_e4m3_f32(aq, wq, oracle.RCR, m, n, k)
+            acc = _run_fp8(m, n, k, aq, wq, raw=True).cpu().numpy()
+            assert oracle.compare_tolerant(acc_ref, acc, 1e-3, 1e-5 * float(np.abs(acc_ref).max())) == -1
+    finally:
+        bq.set_tuning(0, 0)
+        bq.set_tuning(2, 0)
+    assert bq.device_status() == 0

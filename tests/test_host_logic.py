@@ -232,6 +232,25 @@ def test_set_tuning_is_per_thread(qlib):
     assert qlib.baracuda_kernels_q_set_tuning(1, 0) == 0
 
 
+def test_int8_symbols_refuse_k_that_could_overflow_32_bits(qlib):
+    A, B, D = 0x10000, 0x20000, 0x30000
+    k_ok, k_bad = 131056, 131072  # multiples of 16 either side of the 131 071 bound
+    s8 = getattr(qlib, W8A8 + "_can_implement")
+    fp8 = qlib.baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement
+    assert s8(128, 256, k_ok, A, k_ok, B, k_ok, None, 0, D, 256) == 0
+    assert s8(128, 256, k_bad, A, k_bad, B, k_bad, None, 0, D, 256) == 3
+    assert fp8(128, 256, k_bad, A, k_bad, B, k_bad, None, 0, D, 256) == 0          # f32 accumulators: no such bound
+    assert qlib.baracuda_kernels_gemm_s8_rrr_sm100a_can_implement(128, 256, k_bad, A, k_bad, B, 256, None, 0, D, 256) == 3
+    gemv = getattr(qlib, GEMV + "_can_implement")
+    assert gemv(1, 64, k_ok, 1, 1, k_ok, k_ok, 64, 0, 0, 0) == 0
+    assert gemv(1, 64, k_bad, 1, 1, k_bad, k_bad, 64, 0, 0, 0) == 3
+    with pytest.raises(bq.Unsupported):
+        p = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(128, 256, k_bad))
+        p.can_implement(bq.QGemmArgs(a=_FakeCuda(128 * k_bad, torch.int8), b=_FakeCuda(256 * k_bad, torch.int8),
+                                     d=_FakeCuda(128 * 256, torch.bfloat16), scale_a=_FakeCuda(128, torch.float32),
+                                     scale_b=_FakeCuda(256, torch.float32)))
+
+
 def test_smoothquant_plan_surface():
     p = bq.SmoothQuantLinearPlan.select(None, bq.SmoothQuantLinearDescriptor(128, 256, 512, act_scale=0.02))
     assert p.workspace_size() == 0 and p.sku().arch is bq.ArchSku.Sm100a and p.sku().element is bq.ElementKind.S8

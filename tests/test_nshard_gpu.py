@@ -96,6 +96,20 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             dist.barrier()
             check(bits(full_rm), want, "fused peer store")
             assert bq.device_status() == 0
+            # the same weight stored row-major [K, N]: rank r's shard is a column range (strided view), fused gather
+            if n_local % 16 == 0 and m >= 256:
+                w_kn = torch.from_numpy(np.ascontiguousarray(wq.T)).cuda()
+                full_rm.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                plan = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind=kind, gather=par.GATHER_FUSED_PEER_STORE,
+                                                   layout=bq.LayoutSku.Rrr)
+                plan.forward(None, dev(aq), dev(sa), w_kn[:, lo:lo + n_local], sb_local, y_local, peer_ptrs=ptrs, ldd_full=n)
+                ctx.stream_barrier(scratch)
+                torch.cuda.synchronize()
+                dist.barrier()
+                check(bits(full_rm), want, "fused peer store, row-major weight")
+                assert bq.device_status() == 0
         # K-sharded (row-parallel) forward: raw accumulators all-reduced, one dequant pass, bias added once
         for kind, (m, n, k) in (("w8a8", (300, 1040, 1024)), ("fp8", (512, 1024, 2048)), ("w8a8", (1024, 2048, 4096))):
             if k % (128 * world) != 0:
