@@ -56,6 +56,10 @@ struct GemmParams {
     // replaced by narrow ones spread over every pair.
     int mixed;
     int mixed_full_cols;
+    // Tile order of the round-robin schedule: tiles are numbered group by group, a group being raster_gm tile rows by
+    // all tile columns, row fastest inside it.  The tiles in flight at one time then share raster_gm row blocks of A
+    // (chosen to stay resident in L2) and a few weight column blocks, instead of every row block of A.
+    int raster_gm;
     uint16_t full_begin[98];
     uint16_t half_begin[98];
 };

@@ -129,9 +129,14 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         } else {
+            const int group_tiles = p.raster_gm * p.n_tiles;
             for (int tile = pair_id; tile < total_tiles; tile += num_pairs, ++it) {
-                const int nb = tile / p.m_tiles;
-                if (!body(tile - nb * p.m_tiles, nb * PAIR_TILE_N, PAIR_TILE_N, it)) return;
+                const int grp = tile / group_tiles;
+                const int within = tile - grp * group_tiles;
+                const int m0 = grp * p.raster_gm;
+                const int rows = p.m_tiles - m0 < p.raster_gm ? p.m_tiles - m0 : p.raster_gm;
+                const int nb = within / rows;
+                if (!body(m0 + within - nb * rows, nb * PAIR_TILE_N, PAIR_TILE_N, it)) return;
             }
         }
     };
@@ -391,6 +396,17 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     GemmParams p;
     p.mixed = 0;
     p.mixed_full_cols = 0;
+    {
+        // row blocks of A per group: as many as keep the group's A rows (256 x K bytes each) within about 36 MB, the
+        // share of the L2 that stays resident beside the weight and output streams; groups of equal height
+        const int m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
+        const int64_t row_block_bytes = static_cast<int64_t>(PAIR_TILE_M) * (g.k > 0 ? g.k : 1);
+        int64_t gm_max = (36LL << 20) / row_block_bytes;
+        if (gm_max < 2) gm_max = 2;
+        const int groups = static_cast<int>((m_tiles + gm_max - 1) / gm_max);
+        p.raster_gm = (m_tiles + groups - 1) / (groups > 0 ? groups : 1);
+        if (p.raster_gm < 1) p.raster_gm = 1;
+    }
     if constexpr (MIXED) {
         if (!mixed || !mixed->ok) return BQ_STATUS_LAUNCH_FAILURE;
         p.mixed = 1;
@@ -505,7 +521,10 @@ int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
     const int tn = pick_tile_n(g);
     // Mixed widths: when the wide tiles do not fill their last wave, the columns of that wave are cut into 128-wide
     // tiles spread over all pairs (force_pair_tile_n 2 forces the mixed schedule, any other forced width keeps it off).
-    if (g.force_pair_tile_n == 0 || g.force_pair_tile_n == 2) {
+    // Every pair walks its own contiguous run of tiles, so the pairs are spread over the whole matrix at any moment:
+    // fine while both operands fit in L2 (64 MB), which is also where partly filled waves matter.
+    const int64_t operand_bytes = (static_cast<int64_t>(g.m) + g.n) * g.k;
+    if (g.force_pair_tile_n == 2 || (g.force_pair_tile_n == 0 && operand_bytes <= (64LL << 20))) {
         const int sm_pairs = sm_count_of_current_device() / 2;
         const int m_tiles = (g.m + PAIR_TILE_M - 1) / PAIR_TILE_M;
         const int nc = g.n / 256;
