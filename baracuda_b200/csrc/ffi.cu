@@ -327,7 +327,7 @@ int32_t gemv_run(int32_t raw, int32_t m, int32_t n, int32_t k, int32_t batch, in
 int32_t bq::launch_gemm_bf16_checked(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                                     const void* b, int64_t ldb, void* d, int64_t ldd, const void* scale_a,
                                     const void* scale_b, int32_t scale_mode, float alpha, void* const* peer_d,
-                                    int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream) {
+                                    int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream, void* mc_d) {
     if (layout != bq::BQ_LAYOUT_RCR && layout != bq::BQ_LAYOUT_RRR) return bq::BQ_STATUS_INVALID_PROBLEM;
     if (!peer_d) {
         return gemm_run(layout, kind, 0, m, n, k, a, lda, b, ldb, nullptr, 0, d, ldd, scale_a, scale_b, scale_mode, alpha,
@@ -370,6 +370,7 @@ int32_t bq::launch_gemm_bf16_checked(int32_t layout, int32_t kind, int32_t m, in
     g.peer_col0 = rank * n;
     g.peer_rank = rank;
     for (int r = 0; r < 8; ++r) g.peer_d[r] = r < world ? peer_d[r] : nullptr;
+    g.mc_d = mc_d;
     return bq::launch_gemm_q8(g, stream);
 }
 

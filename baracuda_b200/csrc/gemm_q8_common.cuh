@@ -25,6 +25,7 @@ struct GemmParams {
     int vec_store;  // 1 when d and ldd allow 16-byte row stores
     // fused replicated output (FUSED kernels only)
     void* peer_d[8];
+    void* mc_d;  // multicast address of the same buffers (one store reaches every rank), or null: unicast stores to peer_d
     int n_peers;
     int64_t peer_ld;
     int peer_col0;
@@ -355,11 +356,16 @@ __device__ __forceinline__ void epilogue_block_64(const GemmParams& p, uint32_t 
                                           c * 8) = v;
             }
             if constexpr (FUSED) {
-                for (int i = 1; i <= p.n_peers; ++i) {
-                    int pr = p.peer_rank + i;
-                    if (pr >= p.n_peers) pr -= p.n_peers;
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
-                                              static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
+                if (p.mc_d != nullptr) {
+                    multimem_st_16(reinterpret_cast<__nv_bfloat16*>(p.mc_d) + static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 +
+                                       col0 + c * 8, v);
+                } else {
+                    for (int i = 1; i <= p.n_peers; ++i) {
+                        int pr = p.peer_rank + i;
+                        if (pr >= p.n_peers) pr -= p.n_peers;
+                        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
+                                                  static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
+                    }
                 }
             }
         }
@@ -397,11 +403,16 @@ __device__ __forceinline__ void epilogue_block_32(const GemmParams& p, uint32_t 
                                           c * 8) = v;
             }
             if constexpr (FUSED) {
-                for (int j = 1; j <= p.n_peers; ++j) {
-                    int pr = p.peer_rank + j;
-                    if (pr >= p.n_peers) pr -= p.n_peers;
-                    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
-                                              static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
+                if (p.mc_d != nullptr) {
+                    multimem_st_16(reinterpret_cast<__nv_bfloat16*>(p.mc_d) + static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 +
+                                       col0 + c * 8, v);
+                } else {
+                    for (int j = 1; j <= p.n_peers; ++j) {
+                        int pr = p.peer_rank + j;
+                        if (pr >= p.n_peers) pr -= p.n_peers;
+                        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_d[pr]) +
+                                                  static_cast<int64_t>(row) * p.peer_ld + p.peer_col0 + col0 + c * 8) = v;
+                    }
                 }
             }
         }

@@ -450,6 +450,9 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
         p.peer_d[r] = g.peer_d[r];
         if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
     }
+    // the multicast store is 16 bytes wide: used only where every tile takes the staged path, else the unicast stores run
+    p.mc_d = (FUSED && p.peer_vec && p.vec_store && (g.n % 32) == 0 && (reinterpret_cast<uintptr_t>(g.mc_d) & 15u) == 0) ? g.mc_d
+                                                                                                                  : nullptr;
     auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN, B_MN, MIXED>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();

@@ -369,6 +369,9 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
         p.peer_d[r] = g.peer_d[r];
         if (r < p.n_peers && (reinterpret_cast<uintptr_t>(g.peer_d[r]) & 15u) != 0) p.peer_vec = 0;
     }
+    // the multicast store is 16 bytes wide: used only where every tile takes the staged path, else the unicast stores run
+    p.mc_d = (FUSED && p.peer_vec && p.vec_store && (g.n % 32) == 0 && (reinterpret_cast<uintptr_t>(g.mc_d) & 15u) == 0) ? g.mc_d
+                                                                                                                  : nullptr;
     auto kern = gemm_q8_kernel<KIND, RAW, BLOCK_N, STAGES, FUSED>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();

@@ -50,6 +50,7 @@ struct GemmDesc {
     // fused replicated output: the epilogue also stores each tile into these row-major
     // [M, peer_ld] buffers (one per rank, peer-mapped) at column offset peer_col0
     void* peer_d[8];
+    void* mc_d;       // multicast address of the peers' buffers, or null (used only when every store can be 16 bytes)
     int32_t n_peers;  // 0 = off
     int64_t peer_ld;
     int32_t peer_col0;
@@ -80,7 +81,7 @@ int32_t launch_reduce_dequant_broadcast(int32_t kind, int32_t rank, int32_t worl
 int32_t launch_gemm_bf16_checked(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                                 const void* b, int64_t ldb, void* d, int64_t ldd, const void* scale_a,
                                 const void* scale_b, int32_t scale_mode, float alpha, void* const* peer_d,
-                                int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream);
+                                int32_t world, int32_t rank, int64_t peer_ld, cudaStream_t stream, void* mc_d = nullptr);
 int32_t read_and_clear_gemm_device_status();
 // CTA-pair (cta_group::2) variant: 256 x 256 output tiles shared by two SMs.
 int32_t launch_gemm_q8_pair(const GemmDesc& g, cudaStream_t stream);

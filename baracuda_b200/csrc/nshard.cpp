@@ -66,16 +66,22 @@ int32_t nshard_run(int32_t layout, int32_t kind, int32_t rank, int32_t world, vo
                    const void* scale_a, const void* scale_b_local, int32_t scale_mode, float alpha, void* d_full,
                    void* const* peer_d, int64_t ldd_full, void* stream) {
     if (world < 1 || rank < 0 || rank >= world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
-    if (gather < BARACUDA_Q_GATHER_NONE || gather > BARACUDA_Q_GATHER_FUSED_PEER_STORE)
+    if (gather < BARACUDA_Q_GATHER_NONE || gather > BARACUDA_Q_GATHER_FUSED_MULTICAST)
         return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     if (m < 0 || n_local < 0 || k < 0) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    if (gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE) {
+    const bool fused = gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE || gather == BARACUDA_Q_GATHER_FUSED_MULTICAST;
+    void* mc_d = nullptr;
+    if (fused) {
         if (world > BARACUDA_Q_MAX_PEERS || !peer_d) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
         if (ldd_full < static_cast<int64_t>(n_local) * world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
         for (int r = 0; r < world; ++r) {
             if (!peer_d[r]) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+        }
+        if (gather == BARACUDA_Q_GATHER_FUSED_MULTICAST) {
+            mc_d = peer_d[world];  // one more entry: the multicast address of the same buffers
+            if (!mc_d) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
         }
     }
     if (gather == BARACUDA_Q_GATHER_NCCL) {
@@ -87,14 +93,11 @@ int32_t nshard_run(int32_t layout, int32_t kind, int32_t rank, int32_t world, vo
     int32_t st;
     if (kind == bq::BQ_KIND_S8) {
         st = bq::launch_gemm_bf16_checked(layout, kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
-                                         BARACUDA_Q_SCALE_PER_ROW_COL, alpha,
-                                         gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE ? peer_d : nullptr, world, rank,
-                                         ldd_full, s);
+                                         BARACUDA_Q_SCALE_PER_ROW_COL, alpha, fused ? peer_d : nullptr, world, rank, ldd_full, s,
+                                         mc_d);
     } else {
         st = bq::launch_gemm_bf16_checked(layout, kind, m, n_local, k, a, lda, b_local, ldb, d_local, ldd, scale_a, scale_b_local,
-                                         scale_mode, alpha,
-                                         gather == BARACUDA_Q_GATHER_FUSED_PEER_STORE ? peer_d : nullptr, world, rank,
-                                         ldd_full, s);
+                                         scale_mode, alpha, fused ? peer_d : nullptr, world, rank, ldd_full, s, mc_d);
     }
     if (st != BARACUDA_Q_STATUS_OK) return st;
     if (gather != BARACUDA_Q_GATHER_NCCL) return BARACUDA_Q_STATUS_OK;

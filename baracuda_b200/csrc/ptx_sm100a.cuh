@@ -279,6 +279,14 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
         : "memory");
 }
 
+// One 16-byte store to a multicast address: the NVLink switch writes it to the same offset of every GPU bound to the
+// multicast object (the bits are opaque to the instruction; .v4.f32 is merely its 16-byte form).
+__device__ __forceinline__ void multimem_st_16(void* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

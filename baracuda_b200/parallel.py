@@ -27,6 +27,7 @@ from .vocab import BaracudaError, InvalidProblem, LayoutSku, status_to_result
 GATHER_NONE = 0
 GATHER_NCCL = 1
 GATHER_FUSED_PEER_STORE = 2
+GATHER_FUSED_MULTICAST = 3
 
 
 class CommUnavailable(BaracudaError):
@@ -125,7 +126,7 @@ class ColumnParallelQGemmPlan:
         [K, N] and the shard is its column range [lo, hi) -- pass the strided view `w[:, lo:hi]` as `w_local`."""
         if kind not in ("fp8", "w8a8"):
             raise InvalidProblem("kind must be 'fp8' or 'w8a8'")
-        if gather not in (GATHER_NONE, GATHER_NCCL, GATHER_FUSED_PEER_STORE):
+        if gather not in (GATHER_NONE, GATHER_NCCL, GATHER_FUSED_PEER_STORE, GATHER_FUSED_MULTICAST):
             raise InvalidProblem("unknown gather mode")
         if layout not in (LayoutSku.Rcr, LayoutSku.Rrr):
             raise InvalidProblem("unknown layout")
@@ -162,8 +163,10 @@ class ColumnParallelQGemmPlan:
 
     def forward(self, stream, a: torch.Tensor, scale_a: torch.Tensor, w_local: torch.Tensor,
                 scale_b_local: torch.Tensor, y_local: torch.Tensor, y_full: Optional[torch.Tensor] = None,
-                peer_ptrs: Optional[Sequence[int]] = None, ldd_full: int = 0, alpha: float = 1.0) -> None:
-        """Y_local[M, N/G] = dequant(A x W_local^T); then the selected gather.  Asynchronous on `stream`."""
+                peer_ptrs: Optional[Sequence[int]] = None, ldd_full: int = 0, alpha: float = 1.0,
+                multicast_ptr: int = 0) -> None:
+        """Y_local[M, N/G] = dequant(A x W_local^T); then the selected gather.  Asynchronous on `stream`.
+        GATHER_FUSED_MULTICAST also needs `multicast_ptr`, the multicast address of the peer buffers."""
         per_vec = self.kind == "w8a8" or self.scale_mode == SCALE_PER_ROW_COL
         _need_typed(a, self._operand_dtypes(), self.m * self.k, "a")
         _need_typed(w_local, self._operand_dtypes(), self.n_local * self.k, "w_local")
@@ -173,10 +176,15 @@ class ColumnParallelQGemmPlan:
         if self.gather == GATHER_NCCL:
             _need_typed(y_full, torch.bfloat16, self.m * self.n, "y_full")
         peers = None
-        if self.gather == GATHER_FUSED_PEER_STORE:
+        if self.gather in (GATHER_FUSED_PEER_STORE, GATHER_FUSED_MULTICAST):
             if peer_ptrs is None or len(peer_ptrs) != self.ctx.world:
                 raise InvalidProblem("fused mode needs one peer buffer pointer per rank")
-            peers = (C.c_void_p * self.ctx.world)(*peer_ptrs)
+            if self.gather == GATHER_FUSED_MULTICAST:
+                if not multicast_ptr:
+                    raise InvalidProblem("the multicast mode needs the buffers' multicast address")
+                peers = (C.c_void_p * (self.ctx.world + 1))(*peer_ptrs, multicast_ptr)
+            else:
+                peers = (C.c_void_p * self.ctx.world)(*peer_ptrs)
             ldd_full = ldd_full or self.n
         lib = _lib.load()
         if self.layout is LayoutSku.Rrr:
@@ -290,3 +298,16 @@ def alloc_peer_buffers(shape, dtype=torch.bfloat16, group=None):
     local = symm_mem.empty(*shape, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
     handle = symm_mem.rendezvous(local, group=group)
     return local, [int(p) for p in handle.buffer_ptrs]
+
+
+def alloc_peer_buffers_multicast(shape, dtype=torch.bfloat16, group=None):
+    """As alloc_peer_buffers, plus the buffers' multicast address (0 when the fabric or the allocator offers none):
+    a store to it lands at the same offset of every rank's buffer (GATHER_FUSED_MULTICAST)."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group if group is not None else dist.group.WORLD
+    local = symm_mem.empty(*shape, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+    handle = symm_mem.rendezvous(local, group=group)
+    mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+    return local, [int(p) for p in handle.buffer_ptrs], mc

@@ -170,6 +170,31 @@ def host_threads() -> int:
         return max(1, os.cpu_count() or 1)
 
 
+def pin_to_gpu_numa_node(device_index: int) -> str:
+    """Binds this process to the CPUs NVML reports as closest to the GPU, so that the pinned host buffers allocated
+    afterwards sit in the memory of that NUMA node (each rank's host link then carries only local traffic)."""
+    try:
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(device_index).uuid)
+        try:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except TypeError:
+            handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = {64 * w + b for w, bits in enumerate(mask) for b in range(64) if (bits >> b) & 1}
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return "not pinned (no overlap with the allowed CPUs)"
+        os.sched_setaffinity(0, allowed)
+        return f"pinned to {len(allowed)} CPUs near the GPU"
+    except Exception as exc:
+        return "not pinned (" + repr(exc)[:60] + ")"
+
+
 # --------------------------------------------------------------------------- reference arm
 def run_reference(args, rank: int, world: int, out) -> None:
     """The CPU restatement of the reference's oracle on all host threads (a launcher's OMP_NUM_THREADS=1 is overridden),
@@ -472,6 +497,8 @@ def main() -> None:
     from baracuda_b200 import synth
 
     torch.cuda.set_device(local_rank)
+    threads_before_pinning = host_threads()
+    numa_note = pin_to_gpu_numa_node(local_rank) if world > 1 else "single process, not pinned"
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -524,7 +551,7 @@ def main() -> None:
     # ---- parity of the timed output: a row sample of this rank's slice against the CPU oracle (checker only)
     from oracle import pyoracle as orc
 
-    orc.set_num_threads(max(1, host_threads() // world))
+    orc.set_num_threads(max(1, threads_before_pinning // world))
     rows = np.sort(np.random.default_rng(99).choice(C4_M, 8, replace=False))
     ridx = torch.from_numpy(rows).cuda()
     a_rows_h, sa_rows_h = a_q[ridx].cpu().numpy(), sa[ridx].cpu().numpy()
@@ -653,6 +680,33 @@ def main() -> None:
                 "layout": "row-major [M, N] on every rank", "nvlink_bytes_out_per_rank": C4_M * n_local * 2 * (world - 1)}
         except Exception as exc:  # symmetric memory not available on this box
             others["with_fused_peer_stores"] = {"unavailable": repr(exc)[:200]}
+        # (2b) the same through the NVLink switch: one multimem.st per tile to the buffers' multicast address
+        try:
+            mc_rm, mc_ptrs, mc = par.alloc_peer_buffers_multicast((C4_M, C4_N))
+            if not mc:
+                raise RuntimeError("no multicast address offered")
+            mc_rm.zero_()
+            mc_plan = par.ColumnParallelQGemmPlan(ctx, C4_M, C4_N, C4_K, kind="fp8", gather=par.GATHER_FUSED_MULTICAST)
+            mc_scratch = torch.zeros(1, device="cuda")
+
+            def mc_step():
+                mc_plan.forward(None, a_q, sa, w_q, sb, d, peer_ptrs=mc_ptrs, ldd_full=C4_N, multicast_ptr=mc)
+                ctx.stream_barrier(mc_scratch)
+
+            barrier()
+            m_ms = event_time_ms(mc_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+            barrier()
+            m_total = max_over_ranks(sum(m_ms))
+            parity["checked"]["fused_multicast_stores"] = all_ranks_ok(
+                slots_match(lambda g: mc_rm[:, g * n_local:(g + 1) * n_local]) and
+                rows_match(mc_rm[ridx][:, rank * n_local:(rank + 1) * n_local]))
+            others["with_fused_multicast_stores"] = {
+                "TFLOPs": ops_total * len(m_ms) / (m_total * 1e-3) / 1e12, "ms_per_step": m_total / len(m_ms),
+                "layout": "row-major [M, N] on every rank", "nvlink_bytes_out_per_rank": C4_M * n_local * 2,
+                "nvlink_bytes_in_per_rank": C4_M * C4_N * 2}
+            del mc_rm
+        except Exception as exc:
+            others["with_fused_multicast_stores"] = {"unavailable": repr(exc)[:200]}
         # (3) the partner layer of the MLP block: K-sharded (row-parallel) W8A8 down projection of the same model
         #     (28672 -> 8192 at M = 8192): raw int32 partial sums, ncclAllReduce, one dequant pass (bit-equal to unsharded)
         rp_m, rp_n, rp_k = C4_M, C4_K, C4_N
@@ -711,7 +765,7 @@ def main() -> None:
     if world == 1 and not args.no_others:
         gemv = gemv_m1(peaks)
         others.update(side_workloads(peaks))
-        orc.set_num_threads(host_threads())
+        orc.set_num_threads(threads_before_pinning)
         cpu_base = cpu_baseline_sample()
     if world > 1:
         ctx.destroy()
@@ -739,7 +793,7 @@ def main() -> None:
             "e2e": {"value": e2e_value, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": int(a_host.numel() + sa_host.numel() * 4),
                     "d2h_bytes_per_step": int(d_hosts[0].numel() * 2),
-                    "bytes_are": "per rank",
+                    "bytes_are": "per rank", "host_buffers": numa_note,
                     "note": "each rank uploads M/G activation rows + scales (pinned), NVLink all-gather replicates "
                             "them, GEMM, each rank reads its bf16 slice back; 3-stream pipeline over 2 buffer sets; "
                             "weights stay resident"},

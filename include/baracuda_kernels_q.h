@@ -521,12 +521,18 @@ int32_t baracuda_kernels_quantize_per_token_sym_bf16_e4m3_sm100a_run(
  *      NVLink transfer overlaps the tensor-core work tile by tile and the result
  *      is a true row-major [M, N].  The caller orders the ranks afterwards
  *      (baracuda_q_nccl_stream_barrier or a host barrier) before reading.
- * `comm` is the ncclComm_t of this rank (may be NULL for gather 0 and 2).
+ *   3  fused through the NVLink switch: as 2, but each tile is stored ONCE, with multimem.st, to the multicast
+ *      address of the `world` buffers (peer_d[world], one entry more than for 2; the unicast pointers
+ *      peer_d[0..world) are still required and serve shapes whose rows cannot take 16-byte stores).  A rank then
+ *      sends M*n_local*2 bytes instead of (world-1) times that; the switch replicates.  Needs buffers bound to
+ *      one multicast object (a symmetric-memory allocator that offers a multicast pointer).
+ * `comm` is the ncclComm_t of this rank (may be NULL for gather 0, 2 and 3).
  * Extra statuses: 6 NCCL not loadable, 7 NCCL call failed.
  * ------------------------------------------------------------------------- */
 #define BARACUDA_Q_GATHER_NONE 0
 #define BARACUDA_Q_GATHER_NCCL 1
 #define BARACUDA_Q_GATHER_FUSED_PEER_STORE 2
+#define BARACUDA_Q_GATHER_FUSED_MULTICAST 3
 #define BARACUDA_Q_MAX_PEERS 8
 
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(

@@ -96,6 +96,21 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             dist.barrier()
             check(bits(full_rm), want, "fused peer store")
             assert bq.device_status() == 0
+            # fused through the switch: one multimem.st per tile to the multicast address of the buffers
+            mc_rm, mc_ptrs, mc = par.alloc_peer_buffers_multicast((m, n))
+            if mc:
+                mc_rm.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                plan = par.ColumnParallelQGemmPlan(ctx, m, n, k, kind=kind, gather=par.GATHER_FUSED_MULTICAST)
+                for _ in range(2):
+                    plan.forward(None, dev(aq), dev(sa), w_local, sb_local, y_local, peer_ptrs=mc_ptrs, ldd_full=n,
+                                 multicast_ptr=mc)
+                    ctx.stream_barrier(scratch)
+                torch.cuda.synchronize()
+                dist.barrier()
+                check(bits(mc_rm), want, "fused multicast store")
+                assert bq.device_status() == 0
             # the same weight stored row-major [K, N]: rank r's shard is a column range (strided view), fused gather
             if n_local % 16 == 0 and m >= 256:
                 w_kn = torch.from_numpy(np.ascontiguousarray(wq.T)).cuda()
