@@ -71,6 +71,9 @@ SIGNATURES: dict[str, tuple] = {
     **{f"baracuda_kernels_gemm_{fam}_{lay}_bf16_sm100a_epilogue_run":
            (_i32, _GEMM_PREFIX + [_vp, _vp, _i32, _vp, _i32, _f32, _f32] + _TAIL)
        for fam in ("w8a8_s8", "fp8_e4m3") for lay in ("rcr", "rrr")},
+    **{f"baracuda_kernels_gemm_{fam}_{lay}_bf16_sm100a_pdl_run":
+           (_i32, _GEMM_PREFIX + [_vp, _vp, _i32, _vp, _i32, _f32, _f32] + _TAIL)
+       for fam in ("w8a8_s8", "fp8_e4m3") for lay in ("rcr", "rrr")},
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_run": (
         _i32, _GEMV_HEAD + [_vp, _i64, _vp, _i64, _vp, _i64, _i64] + _TAIL),
     "baracuda_kernels_gemv_q8_m1_bf16_sm100a_pdl_run": (

@@ -95,7 +95,7 @@ void epilogue_apply(const Epilogue& e, bq::GemmDesc& g) {
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
                  const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream,
-                 const Epilogue& epi = Epilogue());
+                 const Epilogue& epi = Epilogue(), int32_t pdl = 0);
 
 int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                      const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd,
@@ -107,7 +107,8 @@ int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k,
 
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
-                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream, const Epilogue& epi) {
+                 const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream, const Epilogue& epi,
+                 int32_t pdl) {
     const int32_t st = raw ? gemm_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd)
                            : gemm_bf16_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
@@ -156,6 +157,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.c = (!raw && beta != 0.0f) ? c : nullptr;  // beta == 0: C is not read
     g.ldc = ldc;
     g.beta = beta;
+    g.pdl = pdl;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -739,6 +741,26 @@ BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run,
 BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, false)
 BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_E4M3, true)
 BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, true)
+
+// ---- the bf16-out GEMMs as programmatic dependent launches (per call) ------------------------------------
+#define BQ_BF16_PDL_RUN(NAME, LAYOUT, KIND, HAS_MODE)                                                                      \
+    int32_t NAME(int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,   \
+                 int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,          \
+                 const void* bias, int32_t epilogue, float alpha, float beta, void* workspace, size_t workspace_bytes,     \
+                 void* stream) {                                                                                           \
+        (void)workspace;                                                                                                   \
+        (void)workspace_bytes;                                                                                             \
+        Epilogue e;                                                                                                        \
+        e.bias = bias;                                                                                                     \
+        e.bias_kind = 1;                                                                                                   \
+        e.kind = epilogue;                                                                                                 \
+        return gemm_run(LAYOUT, KIND, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,                        \
+                        HAS_MODE ? scale_mode : BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, e, 1);                  \
+    }
+BQ_BF16_PDL_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_pdl_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8, false)
+BQ_BF16_PDL_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_pdl_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, false)
+BQ_BF16_PDL_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_pdl_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_E4M3, true)
+BQ_BF16_PDL_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_pdl_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_E4M3, true)
 
 // ---- int8 GEMV ---------------------------------------------------------------------
 int32_t baracuda_kernels_gemv_q8_m1_bf16_sm100a_run(

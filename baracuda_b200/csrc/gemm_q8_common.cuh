@@ -61,6 +61,7 @@ struct GemmParams {
     // all tile columns, row fastest inside it.  The tiles in flight at one time then share raster_gm row blocks of A
     // (chosen to stay resident in L2) and a few weight column blocks, instead of every row block of A.
     int raster_gm;
+    int pdl;  // launched as a programmatic dependent: weights may be fetched before the dependency wait
     uint16_t full_begin[98];
     uint16_t half_begin[98];
 };

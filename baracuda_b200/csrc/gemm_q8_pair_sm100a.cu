@@ -141,43 +141,67 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     };
 
+    // All roles: let the next kernel of the stream be scheduled as soon as SMs free up (it only matters to a kernel
+    // that was itself launched as a programmatic dependent).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     if (warp == 0) {
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for_each_tile([&](int m_blk, int col0, int tn, int) {
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, PAIR_WAIT_LIMIT)) {
-                        pair_timeout(abort_word, 111);
-                        return false;
-                    }
-                    uint8_t* a_tile = tiles + stage * PAIR_STAGE_BYTES;
-                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * (PAIR_A_BYTES + (tn / 2) * PAIR_BLOCK_K));
-                    // completion bytes of both CTAs' loads are counted on the leader's barrier
-                    const uint32_t full_on_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
-                    tma_load_2d_pair(a_tile, &tmap_a, full_on_leader, kb * PAIR_BLOCK_K,
-                                     m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS);
-                    if constexpr (B_MN) {
-                        tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader,
-                                         col0 + static_cast<int>(rank) * C::B_ROWS, kb * PAIR_BLOCK_K);
-                    } else if constexpr (MIXED) {
-                        const int row0 = col0 + static_cast<int>(rank) * (tn / 2);
-                        tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K, row0);
-                        if (tn == 256) {
-                            tma_load_2d_pair(a_tile + PAIR_A_BYTES + 64 * PAIR_BLOCK_K, &tmap_b, full_on_leader,
-                                             kb * PAIR_BLOCK_K, row0 + 64);
+            // The producer numbers its (tile, K block) steps 0, 1, 2, ...; step i uses ring stage i % STAGES in phase
+            // (i / STAGES) & 1.  what: 0 = arm the barrier and load both operands, 1 = arm and load the weights only,
+            // 2 = load the activations only (barrier already armed, stage known to be free).
+            auto walk = [&](int first, int last, int what) {
+                int idx = 0;
+                for_each_tile([&](int m_blk, int col0, int tn, int) {
+                    for (int kb = 0; kb < num_kb; ++kb, ++idx) {
+                        if (idx < first) continue;
+                        if (idx >= last) return false;
+                        const int stage = idx % PAIR_STAGES;
+                        const uint32_t phase = static_cast<uint32_t>(idx / PAIR_STAGES) & 1u;
+                        if (what == 0 && !mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, PAIR_WAIT_LIMIT)) {
+                            pair_timeout(abort_word, 111);
+                            return false;
                         }
-                    } else {
-                        tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
-                                         col0 + static_cast<int>(rank) * C::B_ROWS);
+                        uint8_t* a_tile = tiles + stage * PAIR_STAGE_BYTES;
+                        if (rank == 0 && what != 2) {
+                            mbar_arrive_expect_tx(&full_bar[stage], 2 * (PAIR_A_BYTES + (tn / 2) * PAIR_BLOCK_K));
+                        }
+                        // completion bytes of both CTAs' loads are counted on the leader's barrier
+                        const uint32_t full_on_leader = map_to_cta(smem_u32(&full_bar[stage]), 0);
+                        if (what != 1) {
+                            tma_load_2d_pair(a_tile, &tmap_a, full_on_leader, kb * PAIR_BLOCK_K,
+                                             m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS);
+                        }
+                        if (what != 2) {
+                            if constexpr (B_MN) {
+                                tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader,
+                                                 col0 + static_cast<int>(rank) * C::B_ROWS, kb * PAIR_BLOCK_K);
+                            } else if constexpr (MIXED) {
+                                const int row0 = col0 + static_cast<int>(rank) * (tn / 2);
+                                tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K, row0);
+                                if (tn == 256) {
+                                    tma_load_2d_pair(a_tile + PAIR_A_BYTES + 64 * PAIR_BLOCK_K, &tmap_b, full_on_leader,
+                                                     kb * PAIR_BLOCK_K, row0 + 64);
+                                }
+                            } else {
+                                tma_load_2d_pair(a_tile + PAIR_A_BYTES, &tmap_b, full_on_leader, kb * PAIR_BLOCK_K,
+                                                 col0 + static_cast<int>(rank) * C::B_ROWS);
+                            }
+                        }
                     }
-                    if (++stage == PAIR_STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
-                }
-                return true;
-            });
+                    return true;
+                });
+            };
+            int done = 0;
+            if (p.pdl) {
+                // Dependent launch: the weights are static, so the first ring of weight tiles is requested while the
+                // previous kernel of the stream is still finishing; the activations follow once it has completed.
+                walk(0, PAIR_STAGES, 1);
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                walk(0, PAIR_STAGES, 2);
+                done = PAIR_STAGES;
+            }
+            walk(done, 0x7fffffff, 0);
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
@@ -225,6 +249,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     } else {
         const int q = warp & 3;
         uint4* stage_buf = stage_all + (warp - 2) * 256;
+        if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // scales, C and D belong to the stream's past
         for_each_tile([&](int m_blk, int tile_col0, int tn, int it) {
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -396,6 +421,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     GemmParams p;
     p.mixed = 0;
     p.mixed_full_cols = 0;
+    p.pdl = g.pdl;
     {
         // row blocks of A per group: as many as keep the group's A rows (256 x K bytes each) within about 36 MB, the
         // share of the L2 that stays resident beside the weight and output streams; groups of equal height
@@ -472,13 +498,15 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     cfg.blockDim = dim3(PAIR_THREADS, 1, 1);
     cfg.dynamicSmemBytes = PAIR_SMEM_TOTAL;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = g.pdl ? 2 : 1;
     if (cudaLaunchKernelEx(&cfg, kern, map_a, map_b, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;

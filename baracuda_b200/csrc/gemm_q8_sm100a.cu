@@ -110,30 +110,44 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int num_kb = (p.k + BLOCK_K - 1) / BLOCK_K;
     const int total_tiles = p.m_tiles * p.n_tiles;
 
+    // let the next kernel of the stream be scheduled as SMs free up (matters only to a programmatic dependent)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     if (warp == 0) {
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                const int m_blk = tile % p.m_tiles;
-                const int n_blk = tile / p.m_tiles;
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, WAIT_LIMIT_CYCLES)) {
-                        record_timeout(abort_word, 101);
-                        ok = false;
-                        break;
-                    }
-                    uint8_t* sa_tile = tiles + stage * L::STAGE_BYTES;
-                    mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-                    tma_load_2d(sa_tile, &tmap_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
-                    tma_load_2d(sa_tile + L::A_BYTES, &tmap_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
-                    if (++stage == STAGES) {
-                        stage = 0;
-                        phase ^= 1u;
+            // step i of this CTA's (tile, K block) sequence uses ring stage i % STAGES in phase (i / STAGES) & 1.
+            // what: 0 = arm the barrier and load both operands, 1 = arm and load the weights only, 2 = activations only
+            auto walk = [&](int first, int last, int what) {
+                int idx = 0;
+                for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                    const int m_blk = tile % p.m_tiles;
+                    const int n_blk = tile / p.m_tiles;
+                    for (int kb = 0; kb < num_kb; ++kb, ++idx) {
+                        if (idx < first) continue;
+                        if (idx >= last) return;
+                        const int stage = idx % STAGES;
+                        const uint32_t phase = static_cast<uint32_t>(idx / STAGES) & 1u;
+                        if (what == 0 && !mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, WAIT_LIMIT_CYCLES)) {
+                            record_timeout(abort_word, 101);
+                            return;
+                        }
+                        uint8_t* sa_tile = tiles + stage * L::STAGE_BYTES;
+                        if (what != 2) mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+                        if (what != 1) tma_load_2d(sa_tile, &tmap_a, &full_bar[stage], kb * BLOCK_K, m_blk * BLOCK_M);
+                        if (what != 2) tma_load_2d(sa_tile + L::A_BYTES, &tmap_b, &full_bar[stage], kb * BLOCK_K, n_blk * BLOCK_N);
                     }
                 }
+            };
+            int done = 0;
+            if (p.pdl) {
+                // dependent launch: the first ring of (static) weight tiles is requested while the previous kernel of
+                // the stream is still finishing; the activations follow once it has completed
+                walk(0, STAGES, 1);
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                walk(0, STAGES, 2);
+                done = STAGES;
             }
+            walk(done, 0x7fffffff, 0);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -179,6 +193,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     } else {
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         uint4* stage_buf = stage_all + (warp - 2) * 256;
+        if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // scales, C and D belong to the stream's past
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int buf = it & 1;
@@ -341,6 +356,10 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.sb = g.scale_b;
     p.scale_mode = g.scale_mode;
     p.sa_const = g.sa_const;
+    p.pdl = g.pdl;
+    p.mixed = 0;
+    p.mixed_full_cols = 0;
+    p.raster_gm = 1;
     p.alpha = g.alpha;
     p.m = g.m;
     p.n = g.n;
@@ -381,8 +400,21 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     const int grid = static_cast<int>(tiles < sms ? tiles : sms);
     p.coalesce = (g.direct_stores == 2) || (g.direct_stores == 0 && (FUSED || (tiles + grid - 1) / grid <= 6));
     if (p.out_q8) p.coalesce = 0;  // the staging path is bf16-only
-    kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(map_a, map_b, p);
-    return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g.pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kern, map_a, map_b, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    return BQ_STATUS_OK;
 }
 
 template <uint32_t KIND, bool RAW>

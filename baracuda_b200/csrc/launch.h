@@ -60,6 +60,7 @@ struct GemmDesc {
     int32_t rs_rows;
     // gated-MLP epilogue (bf16 output, weights [N,K] only): n = 2F interleaved gate/up rows in blocks of 32, d is [M, F]
     int32_t swiglu;
+    int32_t pdl;  // 1: launch with programmatic stream serialization (the caller promises the previous kernel does not write b)
 };
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);

@@ -203,7 +203,10 @@ class _QGemmPlanBase:
     def _call(self, lib, args: QGemmArgs, lda: int, ldb: int, ldd: int, ws_ptr, ws_bytes, stream) -> int:
         raise NotImplementedError
 
-    def run(self, stream, workspace: Optional[torch.Tensor], args: QGemmArgs) -> None:
+    def run(self, stream, workspace: Optional[torch.Tensor], args: QGemmArgs, dependent_launch: bool = False) -> None:
+        """`dependent_launch=True` (bf16-out plans only) selects the *_pdl_run symbol: the kernel may start while the
+        previous kernel of the stream finishes and prefetches weight tiles meanwhile; pass it only when that previous
+        kernel does not write `b`."""
         self.can_implement(args)
         need = self.workspace_size()
         ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
@@ -211,8 +214,14 @@ class _QGemmPlanBase:
             raise WorkspaceTooSmall(need, ws_bytes)
         lib = _lib.load()
         lda, ldb, ldd = self._lds(args)
-        st = self._call(lib, args, lda, ldb, ldd, _ptr(workspace), ws_bytes, _stream_ptr(stream))
+        if dependent_launch:
+            st = self._call_dependent(lib, args, lda, ldb, ldd, _ptr(workspace), ws_bytes, _stream_ptr(stream))
+        else:
+            st = self._call(lib, args, lda, ldb, ldd, _ptr(workspace), ws_bytes, _stream_ptr(stream))
         status_to_result(st, type(self).__name__)
+
+    def _call_dependent(self, lib, args: QGemmArgs, lda: int, ldb: int, ldd: int, ws_ptr, ws_bytes, stream) -> int:
+        raise Unsupported(f"{type(self).__name__} has no dependent-launch form")
 
 
 class W8A8GemmPlan(_QGemmPlanBase):
@@ -263,6 +272,16 @@ class W8A8GemmPlan(_QGemmPlanBase):
         return getattr(lib, self._run_symbol)(
             d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
             _ptr(args.scale_a), _ptr(args.scale_b), args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+
+
+    def _call_dependent(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
+        d = self.desc
+        if self.raw:
+            raise Unsupported("the raw-accumulator SKU has no dependent-launch form")
+        return getattr(lib, self._run_symbol.replace("_run", "_pdl_run"))(
+            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
+            _ptr(args.scale_a), _ptr(args.scale_b), SCALE_PER_ROW_COL, _ptr(args.bias), _EPILOGUE_CODE[d.epilogue],
+            args.alpha, args.beta, ws_ptr, ws_bytes, stream)
 
 
 class Fp8ScaledGemmPlan(_QGemmPlanBase):
@@ -320,6 +339,16 @@ class Fp8ScaledGemmPlan(_QGemmPlanBase):
         return getattr(lib, self._run_symbol)(
             d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
             _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, args.alpha, args.beta, ws_ptr, ws_bytes, stream)
+
+
+    def _call_dependent(self, lib, args, lda, ldb, ldd, ws_ptr, ws_bytes, stream):
+        d = self.desc
+        if self.raw:
+            raise Unsupported("the raw-accumulator SKU has no dependent-launch form")
+        return getattr(lib, self._run_symbol.replace("_run", "_pdl_run"))(
+            d.m, d.n, d.k, _ptr(args.a), lda, _ptr(args.b), ldb, _ptr(args.c), args.ldc or max(d.n, 1), _ptr(args.d), ldd,
+            _ptr(args.scale_a), _ptr(args.scale_b), self.scale_mode, _ptr(args.bias), _EPILOGUE_CODE[d.epilogue],
+            args.alpha, args.beta, ws_ptr, ws_bytes, stream)
 
 
 # --------------------------------------------------------------------------- GEMV
@@ -577,7 +606,8 @@ class QuantizedLinearPlan:
 
     def run(self, stream, workspace: Optional[torch.Tensor], args: QuantizedLinearArgs,
             dependent_launch: bool = False) -> None:
-        """`dependent_launch` as in GemvQ8Plan.run (decode shapes only; the prefill GEMM ignores it)."""
+        """`dependent_launch` as in GemvQ8Plan.run / the GEMM plans' run: the matrix kernel prefetches weights while the
+        kernel before it on the stream (here: the quantiser, which never writes weights) finishes."""
         if args.act_q_scratch.dtype != torch.int8:
             raise InvalidProblem("act_q_scratch must be int8")
         d = self.desc
@@ -603,7 +633,8 @@ class QuantizedLinearPlan:
                          dependent_launch=dependent_launch)
         else:
             self._mm.run(stream, workspace, QGemmArgs(a=args.act_q_scratch, b=args.weight_q, d=args.output,
-                                                      scale_a=args.act_scale_scratch, scale_b=args.weight_scale))
+                                                      scale_a=args.act_scale_scratch, scale_b=args.weight_scale),
+                         dependent_launch=dependent_launch)
 
 
 # --------------------------------------------------------------------------- SmoothQuant linear (per-tensor activation scale)

@@ -237,12 +237,11 @@ def run_reference(args, rank: int, world: int, out) -> None:
 
 
 # --------------------------------------------------------------------------- denominators and the GEMV half of the metric
-def fp8_library_probe() -> dict:
-    """A library FP8 matmul on the same GPU (torch._scaled_mm -> cuBLASLt), 8192^3, bf16 out, best of 10 by CUDA events:
+def fp8_library_probe(n: int = 8192) -> dict:
+    """A library FP8 matmul on the same GPU (torch._scaled_mm -> cuBLASLt), n^3, bf16 out, best of 10 by CUDA events:
     a measured 8-bit tensor-core denominator to put beside 2 x the measured bf16 peak.  Never on the product path."""
     import torch
 
-    n = 8192
     try:
         g = torch.Generator(device="cuda")
         g.manual_seed(7)
@@ -261,7 +260,7 @@ def fp8_library_probe() -> dict:
             e.record()
             torch.cuda.synchronize()
             best = min(best, s.elapsed_time(e))
-        return {"TFLOPs": 2.0 * n ** 3 / (best * 1e-3) / 1e12, "us": best * 1e3, "how": "torch._scaled_mm 8192^3 e4m3, bf16 out, best of 10"}
+        return {"TFLOPs": 2.0 * n ** 3 / (best * 1e-3) / 1e12, "us": best * 1e3, "how": f"torch._scaled_mm {n}^3 e4m3, bf16 out, best of 10"}
     except Exception as exc:  # the probe is a denominator, not a dependency
         return {"TFLOPs": None, "unavailable": repr(exc)[:100]}
 
@@ -410,6 +409,10 @@ def side_workloads(peaks: dict) -> dict:
 
     out["w8a8_4096x4096x4096"] = gemm("s8", 4096, 4096, 4096)
     out["fp8_4096x4096x4096"] = gemm("fp8", 4096, 4096, 4096)
+    lib4k = fp8_library_probe(4096)  # the library on the same 4096^3 shape (L2-warm, best of 10): a like-for-like denominator
+    out["fp8_4096x4096x4096"]["library_same_shape"] = lib4k
+    if lib4k.get("TFLOPs"):
+        out["fp8_4096x4096x4096"]["frac_of_library_same_shape"] = out["fp8_4096x4096x4096"]["TOPS"] / lib4k["TFLOPs"]
     out["w8a8_128x1024x1024"] = gemm("s8", 128, 1024, 1024, graph=True)
     prefill = {}
     for m in (512, 2048, 8192):
@@ -422,6 +425,35 @@ def side_workloads(peaks: dict) -> dict:
         prefill[f"M{m}_layer_TOPS"] = tot_ops / tot_t / 1e12
         prefill[f"M{m}_gate_up_swiglu_fused"] = gemm("s8", m, 28672, 4096, steps=5, gated=True)
     out["prefill_w8a8"] = prefill
+
+    # the four GEMMs of a layer back to back in one CUDA graph (three layers' worth, distinct weights per layer so nothing
+    # is L2 resident from the last round): plain launches, and per-call dependent launches that prefetch the next
+    # GEMM's weights while the current one finishes its last wave
+    def layer_chain(m: int) -> dict:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(m)
+        dims = [(4096, 6144), (4096, 4096), (4096, 28672), (14336, 4096)]  # (K, N): qkv, o, gate+up, down
+        layers = 3
+        launches = []
+        ops = 0.0
+        for _ in range(layers):
+            for kk, nn in dims:
+                a = torch.randint(-127, 128, (m, kk), dtype=torch.int8, device="cuda", generator=gen)
+                b = torch.randint(-127, 128, (nn, kk), dtype=torch.int8, device="cuda", generator=gen)
+                sa = torch.rand(m, device="cuda", generator=gen)
+                sb = torch.rand(nn, device="cuda", generator=gen)
+                d = torch.empty((m, nn), dtype=torch.bfloat16, device="cuda")
+                plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, nn, kk))
+                launches.append((plan, bq.QGemmArgs(a=a, b=b, d=d, scale_a=sa, scale_b=sb)))
+                ops += 2.0 * m * nn * kk
+        res = {}
+        for dep in (False, True):
+            fns = [(lambda p=p, g=g: p.run(None, None, g, dependent_launch=dep)) for p, g in launches]
+            t = min(graph_launch_ms(fns, replays=10) for _ in range(2)) * len(fns) * 1e-3  # seconds per graph replay
+            res["dependent_launch" if dep else "plain"] = {"us_per_layer": t / layers * 1e6, "TOPS": ops / t / 1e12}
+        return res
+
+    out["prefill_layer_chain_w8a8"] = {f"M{m}": layer_chain(m) for m in (512, 2048)}
     return out
 
 

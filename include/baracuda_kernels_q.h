@@ -310,6 +310,18 @@ BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm10
 BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run)
 BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run)
 
+/* The bf16-out GEMMs as programmatic dependent launches, chosen per call: the arguments of *_bf16_sm100a_epilogue_run
+ * (epilogue 0 and bias NULL for the plain GEMM).  The kernel may start while the previous kernel of `stream` is still
+ * finishing -- in a layer chain, on the SMs its last, partly filled wave leaves idle -- and requests its first ring of
+ * WEIGHT tiles during that overlap; activations, scales, bias, C and D are touched only after the previous kernel has
+ * completed and its writes are visible.  The caller promises that the kernel launched just before on this stream does
+ * not write `b` (static model weights).  Same results and statuses as the plain symbols.  No counterpart in the
+ * reference. */
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_pdl_run)
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_pdl_run)
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_pdl_run)
+BARACUDA_Q_DECLARE_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_pdl_run)
+
 /* ---------------------------------------------------------------------------
  * Gated-MLP up-projection in one launch: D[M, F] = bf16( silu(z_gate) * z_up ),
  *   z[m, j] = alpha * (scale_a[m] * scale_b[j]) * acc[m, j] (+ bias[j]),  silu(z) = z / (1 + exp(-z)),

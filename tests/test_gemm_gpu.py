@@ -521,3 +521,44 @@ def test_cta_pair_kernel_mixed_tile_widths(oracle, kind, shape):
         bq.set_tuning(0, 0)
         bq.set_tuning(2, 0)
     assert bq.device_status() == 0
+
+
+@pytest.mark.parametrize("kind", ["s8", "fp8"])
+def test_dependent_launch_chain_gives_the_same_results(oracle, kind):
+    """The bf16-out GEMMs launched as programmatic dependents (per call): a chain of launches of different shapes on one
+    stream -- pair kernel, 1-CTA kernel, mixed tile widths, bias epilogue, residual add -- each prefetching its weights
+    while its predecessor finishes, equals the same chain launched plainly, and the first of them the oracle."""
+    shapes = [(2304, 1536, 512), (128, 1024, 1024), (700, 3584, 256), (2048, 4096, 384), (300, 520, 640)]
+    cases = []
+    for i, (m, n, k) in enumerate(shapes):
+        if kind == "s8":
+            aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=50 + i)
+            plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, epilogue=bq.EpilogueKind.Bias if i == 2 else bq.EpilogueKind.Identity))
+        else:
+            aq, wq, sa, sb = fp8_case(oracle, m, n, k, seed=50 + i)
+            plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k, epilogue=bq.EpilogueKind.Bias if i == 2 else bq.EpilogueKind.Identity),
+                                               scale_mode=bq.SCALE_PER_ROW_COL)
+        bias = dev(np.linspace(-1, 1, n).astype(np.float32)) if i == 2 else None
+        cases.append((plan, m, n, dict(a=dev(aq), b=dev(wq), scale_a=dev(sa), scale_b=dev(sb), bias=bias), (aq, wq, sa, sb)))
+    outs = {}
+    for dependent in (False, True):
+        res = []
+        for rep in range(3):
+            for plan, m, n, kw, _ in cases:
+                d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+                plan.run(None, None, bq.QGemmArgs(d=d, **kw), dependent_launch=dependent)
+                res.append(d)
+        torch.cuda.synchronize()
+        assert bq.device_status() == 0
+        outs[dependent] = res
+    for plain, dep in zip(outs[False], outs[True]):
+        assert torch.equal(plain.view(torch.int16), dep.view(torch.int16))
+    m, n, k = shapes[0]
+    aq, wq, sa, sb = cases[0][4]
+    if kind == "s8":
+        want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+        assert oracle.compare_bitexact(want, bf16_bits(outs[True][0])) == -1
+    else:
+        want = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(oracle.gemm_e4m3_f32(aq, wq, oracle.RCR, m, n, k), sa, sb))
+        got = outs[True][0].float().cpu().numpy()
+        assert oracle.compare_tolerant(want, got, 1e-2, 1e-4 * float(np.abs(want).max())) == -1
