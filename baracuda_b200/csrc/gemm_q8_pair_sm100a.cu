@@ -43,7 +43,11 @@ struct PairCfg {
     static constexpr int STAGES = (192 * 1024) / STAGE_BYTES;
     static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
     static constexpr int STG_BYTES = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes of output staging
-    static constexpr int SB_BYTES = STG_BYTES + 2 * 4 * TN * 4;  // column scales and bias, one private copy per epilogue warp
+    // Staged column scales, then staged bias: a private slice per epilogue warp.  Four warps hold TN floats each; eight
+    // warps hold half of the tile's 32-column blocks each, rounded up (TN = 224: 4 + 3 blocks, 128 floats per slice).
+    static constexpr int SB_HALF = ((TN / 32 + 1) / 2) * 32;
+    static constexpr int SB_FLOATS = 8 * SB_HALF;  // >= 4 * TN
+    static constexpr int SB_BYTES = STG_BYTES + 2 * SB_FLOATS * 4;
     static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
     static constexpr int SMEM_TOTAL = TILE_BYTES + SB_BYTES + BAR_BYTES + 1024;
     static constexpr int TMEM_COLS = (2 * TN <= 256) ? 256 : 512;
@@ -58,8 +62,11 @@ __device__ __forceinline__ void pair_timeout(volatile uint32_t* abort_word, int 
 // described to the MMA as an MN-major operand.  Needs TN == 256 (one 128-byte atom of N per CTA).
 // MIXED (TN == 256, K-contiguous weights): the launch follows GemmParams' mixed-width schedule; a 128-wide tile uses
 // half of the stage's weight area, the weight map's box is 64 rows (two loads per stage for a wide tile).
-template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false, bool MIXED = false>
-__global__ void __launch_bounds__(PAIR_THREADS, 1)
+// EW8: eight epilogue warps instead of four -- two per tensor-memory lane quadrant, each taking half of the tile's
+// column blocks (32 columns at a time through a 2 KiB staging area) -- for epilogue chains whose arithmetic (bias + gelu /
+// silu: about 26 instructions per element) four warps cannot hide behind the next tile's MMAs at short K.
+template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false, bool MIXED = false, bool EW8 = false>
+__global__ void __launch_bounds__(EW8 ? PAIR_THREADS + 128 : PAIR_THREADS, 1)
 gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmParams p) {
     using C = PairCfg<TN>;
@@ -95,7 +102,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&tfull_bar[b], 1);   // one commit arrival
-            mbar_init(&tempty_bar[b], 8);  // one arrival per epilogue warp of both CTAs (leader's copy is used)
+            mbar_init(&tempty_bar[b], EW8 ? 16 : 8);  // one arrival per epilogue warp of both CTAs (leader's copy is used)
         }
         *abort_word = 0u;
         fence_barrier_init();
@@ -248,15 +255,19 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
     } else {
         const int q = warp & 3;
-        uint4* stage_buf = stage_all + (warp - 2) * 256;
+        const int half = EW8 ? (warp - 2) >> 2 : 0;  // EW8: which half of the tile's column blocks this warp takes
+        uint4* stage_buf = stage_all + (warp - 2) * (EW8 ? 128 : 256);
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // scales, C and D belong to the stream's past
         for_each_tile([&](int m_blk, int tile_col0, int tn, int it) {
             const int buf = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
-            float* sb_tile = sb_s + (warp - 2) * PAIR_TILE_N;
+            const int blocks = tn / 32;
+            const int c_begin = EW8 ? (half ? (blocks + 1) / 2 : 0) : 0;
+            const int c_end = EW8 ? (half ? blocks : (blocks + 1) / 2) : blocks;
+            float* sb_tile = sb_s + (warp - 2) * (EW8 ? C::SB_HALF : PAIR_TILE_N) - c_begin * 32;  // indexed by column of the tile
             if (!RAW && (!p.out_q8 || p.bias_kind != 0)) {
                 __syncwarp();
-                for (int i = lane; i < tn; i += 32) {
+                for (int i = c_begin * 32 + lane; i < c_end * 32; i += 32) {
                     const int col = tile_col0 + i;
                     if (!p.out_q8) sb_tile[i] = (p.scale_mode != 0) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
                     if (p.bias_kind == 1) {
@@ -283,11 +294,10 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
             {
-                const int blocks = tn / 32;
-                int c = 0;
-                if constexpr (!RAW) {
+                int c = c_begin;
+                if constexpr (!RAW && !EW8) {
                     // 64 columns at a time through the warp's staging buffer (coalesced 128-byte row segments)
-                    for (; c + 2 <= blocks; c += 2) {
+                    for (; c + 2 <= c_end; c += 2) {
                         const int col0 = tile_col0 + c * 32;
                         if (col0 >= p.n) break;  // warp-uniform
                         if (p.swiglu) {  // launch-uniform; the host guarantees whole 64-column blocks and aligned rows
@@ -301,7 +311,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
 #pragma unroll 1
-                for (; c < blocks; ++c) {
+                for (; c < c_end; ++c) {
                     const int col0 = tile_col0 + c * 32;
                     if (col0 >= p.n) break;  // warp-uniform
                     if constexpr (!RAW) {
@@ -404,7 +414,7 @@ MixedSchedule build_mixed_schedule(int m_tiles, int n, int sm_pairs, int full_co
     return sc;
 }
 
-template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false, bool MIXED = false>
+template <uint32_t KIND, bool RAW, bool FUSED, int TN, bool B_MN = false, bool MIXED = false, bool EW8 = false>
 int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedule* mixed = nullptr) {
     using C = PairCfg<TN>;
     constexpr int PAIR_TILE_N = TN;
@@ -462,7 +472,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     p.bias = g.bias;
     p.bias_kind = g.bias ? g.bias_kind : 0;
     p.act = g.act;
-    p.bias_off = 4 * TN;
+    p.bias_off = PairCfg<TN>::SB_FLOATS;
     p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
     p.n_peers = FUSED ? g.n_peers : 0;
     p.peer_ld = g.peer_ld;
@@ -479,7 +489,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     // the multicast store is 16 bytes wide: used only where every tile takes the staged path, else the unicast stores run
     p.mc_d = (FUSED && p.peer_vec && p.vec_store && (g.n % 32) == 0 && (reinterpret_cast<uintptr_t>(g.mc_d) & 15u) == 0) ? g.mc_d
                                                                                                                   : nullptr;
-    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN, B_MN, MIXED>;
+    auto kern = gemm_q8_pair_kernel<KIND, RAW, FUSED, TN, B_MN, MIXED, EW8>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -495,7 +505,7 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     if (p.out_q8) p.coalesce = 0;  // the staging path is bf16-only
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
-    cfg.blockDim = dim3(PAIR_THREADS, 1, 1);
+    cfg.blockDim = dim3(EW8 ? PAIR_THREADS + 128 : PAIR_THREADS, 1, 1);
     cfg.dynamicSmemBytes = PAIR_SMEM_TOTAL;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
@@ -566,6 +576,18 @@ int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
         }
         if (best.ok && (g.force_pair_tile_n == 2 || best.makespan < 0.98 * single_width_cost(g, tn))) {
             return launch_pair_tn<KIND, RAW, FUSED, 256, false, true>(g, stream, &best);
+        }
+    }
+    if constexpr (!RAW && !FUSED) {
+        // bias + gelu / silu: eight epilogue warps (the chain's arithmetic outlasts the next tile's MMAs on four)
+        if (g.act >= 2 && !g.swiglu) {
+            switch (tn) {
+                case 256: return launch_pair_tn<KIND, false, false, 256, false, false, true>(g, stream);
+                case 224: return launch_pair_tn<KIND, false, false, 224, false, false, true>(g, stream);
+                case 192: return launch_pair_tn<KIND, false, false, 192, false, false, true>(g, stream);
+                case 128: return launch_pair_tn<KIND, false, false, 128, false, false, true>(g, stream);
+                default: return BQ_STATUS_INVALID_PROBLEM;
+            }
         }
     }
     switch (tn == 2 ? 256 : tn) {

@@ -252,3 +252,53 @@ def test_epilogue_status_rules():
     frun = lib.baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_epilogue_run
     assert frun(*args, f.data_ptr(), 2, 1, 1.0, 0.0, None, 0, _stream()) == 2  # fp8 takes a float bias only
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("tn", [256, 224, 192, 128])
+@pytest.mark.parametrize("epi", [3, 4])
+@pytest.mark.parametrize("out", ["bf16", "s8"])
+def test_eight_epilogue_warps_gelu_silu_on_the_cta_pair_kernel(oracle, tn, epi, out):
+    """bias + gelu / silu on the CTA-pair kernel run with eight epilogue warps (two per tensor-memory lane quadrant, each
+    half of the column blocks): every tile width (224 has an odd number of 32-column blocks), ragged M / N, both the
+    staged bf16 stores and the direct 8-bit stores, checked against the oracle's chain."""
+    import baracuda_b200 as bq
+
+    m, n, k = 700, 1480, 256
+    rng = np.random.default_rng(tn + epi)
+    a = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    bias = rng.standard_normal(n).astype(np.float32)
+    acc = oracle.gemm_s8_s32(a, b, oracle.RCR, m, n, k)
+    lda = (k + 15) // 16 * 16
+    ad, bd, biasd = dev(pad_rows(a, lda)), dev(pad_rows(b, lda)), dev(bias)
+    lib = _lib.load()
+    bq.set_tuning(0, 512)
+    bq.set_tuning(2, tn)
+    try:
+        if out == "bf16":
+            sa = rng.uniform(0.001, 0.01, size=m).astype(np.float32)
+            sb = rng.uniform(0.001, 0.01, size=n).astype(np.float32)
+            want = oracle.epilogue_chain(oracle.dequant_s32_f32(acc, sa, sb), bias, epi)
+            d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+            sad, sbd = dev(sa), dev(sb)
+            st = lib.baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run(
+                m, n, k, ad.data_ptr(), lda, bd.data_ptr(), lda, None, 0, d.data_ptr(), n, sad.data_ptr(), sbd.data_ptr(), 1,
+                biasd.data_ptr(), epi, 1.0, 0.0, None, 0, _stream())
+            assert st == 0
+            _status_clean()
+            got = d.float().cpu().numpy()
+            assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -7 + 1e-6)
+        else:
+            alpha = np.float32(2.0 ** -9)
+            want = oracle.sat_s8(oracle.epilogue_chain(alpha * acc.astype(np.float32), bias, epi))
+            d = torch.full((m, n), 99, dtype=torch.int8, device="cuda")
+            st = lib.baracuda_kernels_gemm_s8_rcr_sm100a_epilogue_run(
+                m, n, k, ad.data_ptr(), lda, bd.data_ptr(), lda, None, 0, d.data_ptr(), n, biasd.data_ptr(), 1, epi,
+                float(alpha), 0.0, None, 0, _stream())
+            assert st == 0
+            _status_clean()
+            diff = np.abs(d.cpu().numpy().astype(np.int32) - want.astype(np.int32))
+            assert diff.max() <= 1 and (diff != 0).mean() < 0.01
+    finally:
+        bq.set_tuning(0, 0)
+        bq.set_tuning(2, 0)
