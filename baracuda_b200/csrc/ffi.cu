@@ -15,6 +15,7 @@ struct ThreadTuning {
     int32_t gemv_variant = 0;
     int32_t force_pair_tile_n = 0;
     int32_t direct_stores = 0;
+    int32_t epilogue_warps = 0;
 };
 thread_local ThreadTuning t_tuning;
 
@@ -147,6 +148,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.force_block_n = t_tuning.force_block_n;
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     g.direct_stores = t_tuning.direct_stores;
+    g.epilogue_warps = t_tuning.epilogue_warps;
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
@@ -258,6 +260,7 @@ int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t 
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     epilogue_apply(epi, g);
     g.direct_stores = 1;
+    g.epilogue_warps = t_tuning.epilogue_warps;
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
@@ -363,6 +366,7 @@ int32_t bq::launch_gemm_bf16_checked(int32_t layout, int32_t kind, int32_t m, in
     g.force_block_n = t_tuning.force_block_n;
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     g.direct_stores = t_tuning.direct_stores;
+    g.epilogue_warps = t_tuning.epilogue_warps;
     g.q8_out = 0;
     g.c = nullptr;
     g.ldc = 0;
@@ -409,6 +413,7 @@ int32_t bq::launch_gemm_raw_reduce_scatter_checked(int32_t kind, int32_t m, int3
     g.force_block_n = t_tuning.force_block_n;
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     g.direct_stores = 1;
+    g.epilogue_warps = t_tuning.epilogue_warps;
     g.peer_rank = rank;
     g.rs_world = world;
     g.rs_rows = m / world;
@@ -517,6 +522,7 @@ int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
     g.force_block_n = t_tuning.force_block_n;
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     g.direct_stores = t_tuning.direct_stores;
+    g.epilogue_warps = t_tuning.epilogue_warps;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -890,6 +896,10 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
         case 4:
             if (value < 0 || value > 2) return bq::BQ_STATUS_INVALID_PROBLEM;
             t_tuning.direct_stores = value;
+            return bq::BQ_STATUS_OK;
+        case 5:
+            if (value != 0 && value != 4 && value != 8) return bq::BQ_STATUS_INVALID_PROBLEM;
+            t_tuning.epilogue_warps = value;
             return bq::BQ_STATUS_OK;
         case 2:
             if (value != 0 && value != 2 && value != 256 && value != 224 && value != 192 && value != 128)

@@ -205,15 +205,25 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             float* sb_tile = sb_s + (warp - 2) * BLOCK_N;
             if (!RAW && (!p.out_q8 || p.bias_kind != 0)) {
                 __syncwarp();
-                for (int i = lane; i < BLOCK_N; i += 32) {
-                    const int col = n_blk * BLOCK_N + i;
-                    if (!p.out_q8) sb_tile[i] = (p.scale_mode != 0) ? (col < p.n ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                // all loads of the tile's scales and bias in flight together, then the shared-memory writes
+                float sv[BLOCK_N / 32], bv[BLOCK_N / 32];
+#pragma unroll
+                for (int j = 0; j < BLOCK_N / 32; ++j) {
+                    const int col = n_blk * BLOCK_N + j * 32 + lane;
+                    const bool in = col < p.n;
+                    sv[j] = 0.0f;
+                    bv[j] = 0.0f;
+                    if (!p.out_q8) sv[j] = (p.scale_mode != 0) ? (in ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
                     if (p.bias_kind == 1) {
-                        sb_tile[p.bias_off + i] = col < p.n ? __ldg(reinterpret_cast<const float*>(p.bias) + col) : 0.0f;
+                        if (in) bv[j] = __ldg(reinterpret_cast<const float*>(p.bias) + col);
                     } else if (p.bias_kind == 2) {
-                        sb_tile[p.bias_off + i] =
-                            col < p.n ? static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col)) : 0.0f;
+                        if (in) bv[j] = static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col));
                     }
+                }
+#pragma unroll
+                for (int j = 0; j < BLOCK_N / 32; ++j) {
+                    if (!p.out_q8) sb_tile[j * 32 + lane] = sv[j];
+                    if (p.bias_kind != 0) sb_tile[p.bias_off + j * 32 + lane] = bv[j];
                 }
                 __syncwarp();
             }

@@ -46,6 +46,7 @@ struct GemmDesc {
     int64_t ldd;
     int32_t force_block_n;  // 0 = choose; 64 / 128 / 256 = 1-CTA kernel with that N-tile; 512 = CTA-pair kernel
     int32_t direct_stores;  // 1: epilogue threads store their own rows directly (no staging); tuning
+    int32_t epilogue_warps;  // CTA-pair kernel: 0 = choose, 4 or 8 epilogue warps (tuning and tests)
     int32_t force_pair_tile_n;  // 0 = choose; else 256 / 224 / 192 / 128 (tuning and tests)
     // fused replicated output: the epilogue also stores each tile into these row-major
     // [M, peer_ld] buffers (one per rank, peer-mapped) at column offset peer_col0

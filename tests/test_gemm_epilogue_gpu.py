@@ -274,6 +274,7 @@ def test_eight_epilogue_warps_gelu_silu_on_the_cta_pair_kernel(oracle, tn, epi, 
     lib = _lib.load()
     bq.set_tuning(0, 512)
     bq.set_tuning(2, tn)
+    bq.set_tuning(5, 8)
     try:
         if out == "bf16":
             sa = rng.uniform(0.001, 0.01, size=m).astype(np.float32)
@@ -302,3 +303,4 @@ def test_eight_epilogue_warps_gelu_silu_on_the_cta_pair_kernel(oracle, tn, epi, 
     finally:
         bq.set_tuning(0, 0)
         bq.set_tuning(2, 0)
+        bq.set_tuning(5, 0)
