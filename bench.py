@@ -150,9 +150,18 @@ def graph_launch_ms(launchers, replays: int = 20, warmup: int = 3) -> float:
     return s.elapsed_time(e) / (replays * len(launchers))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of gemm_q8_pair_kernel at 8192 x 8192 x 4096 (70.9 + 97.5 MB),
-# divided by that launch's operand + output bytes (A 33.6 + B 33.6 + D 134.2 MB): each operand byte comes from
-# DRAM once, and part of the output is still in L2 when the kernel ends.
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of gemm_q8_pair_kernel on the timed workload, from ncu
+# captures of exactly these launches (FP8, M = 8192, K = 8192, bf16 out; mean of two launches), keyed by the columns one
+# GPU computes: the whole N at 1 GPU and the shards of 2, 4 and 8 GPUs.  Part of the output is still in L2 when the kernel
+# ends, so the write figure is below the output's size.
+NCU_C4_DRAM_BYTES = {
+    28672: 661_200_128 + 449_637_248,
+    14336: 345_948_544 + 214_073_344,
+    7168: 208_918_272 + 95_139_328,
+    3584: 145_565_184 + 37_088_512,
+}
+# Any other width: the 8192 x 8192 x 4096 capture (70.9 + 97.5 MB) divided by that launch's operand + output bytes
+# (A 33.6 + B 33.6 + D 134.2 MB), times this launch's operand + output bytes.
 NCU_TRAFFIC_PER_COMPULSORY_BYTE = 168_449_792 / 201_326_592
 
 
@@ -805,8 +814,11 @@ def main() -> None:
     if rank == 0:
         peak = 2.0 * peaks["bf16_tflops"]
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_PER_COMPULSORY_BYTE * (C4_M * C4_K + n_local * C4_K + 2 * C4_M * n_local),
-                    "traffic_is": "DRAM read+write per launch: ncu at 8192x8192x4096, scaled by operand+output bytes",
+                    "traffic": NCU_C4_DRAM_BYTES.get(
+                        n_local, NCU_TRAFFIC_PER_COMPULSORY_BYTE * (C4_M * C4_K + n_local * C4_K + 2 * C4_M * n_local)),
+                    "traffic_is": ("DRAM read+write per launch: ncu capture of this launch (M, K, columns per GPU)"
+                                   if n_local in NCU_C4_DRAM_BYTES else
+                                   "DRAM read+write per launch: ncu at 8192x8192x4096, scaled by operand+output bytes"),
                     "peak_is": f"2 x bf16 burst of {peaks['source']} peaks",
                     "frac_of_nominal_4500": achieved / 4500.0,
                     "peak_fp8_library": fp8_lib,
