@@ -220,6 +220,20 @@ class W8A8GemmPlan {
         return status_to_error(st);
     }
 
+    // The same launch as a programmatic dependent of the kernel before it on the stream (bf16-out plans): prologue
+    // and the first weight tiles are issued before that kernel has finished.  The caller asserts that it does not
+    // write `b`.
+    Error run_dependent(void* stream, Workspace ws, const QGemmArgs& x) const {
+        if (raw_) return Error::Unsupported;
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        auto run = desc_.layout == LayoutSku::Rrr ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_pdl_run
+                                                  : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_pdl_run;
+        return status_to_error(run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr,
+                                   x.ldd, x.scale_a.ptr, x.scale_b.ptr, BARACUDA_Q_SCALE_PER_ROW_COL, x.bias.ptr,
+                                   static_cast<int32_t>(desc_.epilogue), x.alpha, x.beta, ws.ptr, ws.bytes, stream));
+    }
+
   private:
     QGemmDescriptor desc_{};
     KernelSku sku_{};
@@ -294,6 +308,17 @@ class Fp8ScaledGemmPlan {
                      x.scale_b.ptr, static_cast<int32_t>(mode_), x.alpha, x.beta, ws.ptr, ws.bytes, stream);
         }
         return status_to_error(st);
+    }
+
+    Error run_dependent(void* stream, Workspace ws, const QGemmArgs& x) const {  // as W8A8GemmPlan::run_dependent
+        if (raw_) return Error::Unsupported;
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        auto run = desc_.layout == LayoutSku::Rrr ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_pdl_run
+                                                  : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_pdl_run;
+        return status_to_error(run(desc_.m, desc_.n, desc_.k, x.a.ptr, x.lda, x.b.ptr, x.ldb, x.c.ptr, x.ldc, x.d.ptr,
+                                   x.ldd, x.scale_a.ptr, x.scale_b.ptr, static_cast<int32_t>(mode_), x.bias.ptr,
+                                   static_cast<int32_t>(desc_.epilogue), x.alpha, x.beta, ws.ptr, ws.bytes, stream));
     }
 
   private:
@@ -534,10 +559,245 @@ class GemvQ8Plan {
         return status_to_error(st);
     }
 
+    // Programmatic dependent launch, chosen per call: the weight stream starts while the kernel before this one on the
+    // stream drains.  The caller asserts that that kernel does not write `b`.
+    Error run_dependent(void* stream, Workspace ws, const GemvQ8Args& x) const {
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        const int32_t st =
+            raw_ ? baracuda_kernels_gemv_q8_m1_s32_sm100a_pdl_run(desc_.m, desc_.n, desc_.k, desc_.batch, layout_code(),
+                                                                  x.alpha, x.beta, x.a.ptr, x.lda, x.stride_a, x.b.ptr,
+                                                                  x.ldb, x.stride_b, x.d.ptr, x.ldd, x.stride_d, ws.ptr,
+                                                                  ws.bytes, stream)
+                 : baracuda_kernels_gemv_q8_m1_bf16_sm100a_pdl_run(
+                       desc_.m, desc_.n, desc_.k, desc_.batch, layout_code(), x.alpha, x.beta, x.a.ptr, x.lda, x.stride_a,
+                       x.b.ptr, x.ldb, x.stride_b, x.scale_a.ptr, x.stride_scale_a, x.scale_b.ptr, x.stride_scale_b,
+                       x.d.ptr, x.ldd, x.stride_d, ws.ptr, ws.bytes, stream);
+        return status_to_error(st);
+    }
+
   private:
     GemvQ8Descriptor desc_{};
     KernelSku sku_{};
     bool raw_ = false;
+};
+
+// ---------------------------------------------------------------------------- activation quantiser and W8A8 linear
+constexpr uint16_t OP_QUANTIZE_PER_TOKEN = 104;
+constexpr uint16_t OP_SMOOTHQUANT_LINEAR = 105;
+
+// QuantizePerTokenPlan (crates/baracuda-kernels/src/quantize/per_token.rs; recipe of
+// dynamic_range_quantize_per_token_symmetric_kernel, baracuda_quantize_compose.cuh:144-201):
+// scale[r] = absmax / qmax (1.0 for a zero row), q = clamp(rint(x * (1 / scale))).  f32 or bf16 in, s8 or e4m3 out.
+struct QuantizePerTokenDescriptor {
+    int32_t rows = 0, cols = 0;
+    ElementKind input = ElementKind::F32;   // F32 or Bf16
+    ElementKind output = ElementKind::S8;   // S8 or Fp8E4M3
+    int32_t q_min = -127, q_max = 127;      // s8 only
+};
+
+class QuantizePerTokenPlan {
+  public:
+    static Error select(const QuantizePerTokenDescriptor& desc, const PlanPreference& pref, QuantizePerTokenPlan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.rows < 0 || desc.cols < 0) return Error::InvalidProblem;
+        if (desc.input != ElementKind::F32 && desc.input != ElementKind::Bf16) return Error::Unsupported;
+        if (desc.output != ElementKind::S8 && desc.output != ElementKind::Fp8E4M3) return Error::Unsupported;
+        if (desc.output == ElementKind::S8 && (desc.q_min > desc.q_max || desc.q_max <= 0)) return Error::InvalidProblem;
+        out->desc_ = desc;
+        return Error::Ok;
+    }
+    size_t workspace_size() const { return 0; }
+    // x: [rows, cols] of the input type with row pitch ld_in; q: bytes with row pitch ld_out; scale: float[rows].
+    Error run(void* stream, DeviceSpan<const void> x, int64_t ld_in, DeviceSpan<float> scale, DeviceSpan<void> q,
+              int64_t ld_out) const {
+        const QuantizePerTokenDescriptor& d = desc_;
+        if (x.len < detail::span_elems(d.rows, d.cols, ld_in) || q.len < detail::span_elems(d.rows, d.cols, ld_out))
+            return Error::BufferTooSmall;
+        if (scale.len < static_cast<size_t>(d.rows)) return Error::BufferTooSmall;
+        int32_t st;
+        if (d.output == ElementKind::S8) {
+            auto run = d.input == ElementKind::F32 ? baracuda_kernels_quantize_per_token_sym_f32_s8_sm100a_run
+                                                   : baracuda_kernels_quantize_per_token_sym_bf16_s8_sm100a_run;
+            st = run(d.rows, d.cols, d.q_min, d.q_max, x.ptr, ld_in, scale.ptr, q.ptr, ld_out, nullptr, 0, stream);
+        } else {
+            auto run = d.input == ElementKind::F32 ? baracuda_kernels_quantize_per_token_sym_f32_e4m3_sm100a_run
+                                                   : baracuda_kernels_quantize_per_token_sym_bf16_e4m3_sm100a_run;
+            st = run(d.rows, d.cols, x.ptr, ld_in, scale.ptr, q.ptr, ld_out, nullptr, 0, stream);
+        }
+        return status_to_error(st);
+    }
+
+  private:
+    QuantizePerTokenDescriptor desc_{};
+};
+
+// QuantizedLinearPlan (crates/baracuda-kernels/src/quantize/quantized_linear.rs:55-355): per-token quantiser, then the
+// W8A8 matrix product, bf16 out.  m <= 8 takes the streaming GEMV, larger m the tcgen05 GEMM; bf16 activations with
+// m <= 8 and a K the fused kernel serves run as ONE launch (quantiser inside the GEMV).
+struct QuantizedLinearDescriptor {
+    int32_t m = 0, c_out = 0, k = 0;
+    int32_t q_min = -127, q_max = 127;
+    ElementKind activation_element = ElementKind::Bf16;  // F32 or Bf16
+};
+
+struct QuantizedLinearArgs {  // quantized_linear.rs:82-120
+    DeviceSpan<const void> activation;   // [M, K] f32 or bf16, packed rows
+    DeviceSpan<const int8_t> weight_q;   // [C_out, K], packed rows
+    DeviceSpan<const float> weight_scale;
+    DeviceSpan<void> output;             // [M, C_out] bf16
+    DeviceSpan<int8_t> act_q_scratch;    // [M, K]
+    DeviceSpan<float> act_scale_scratch; // [M]
+};
+
+class QuantizedLinearPlan {
+  public:
+    static Error select(const QuantizedLinearDescriptor& desc, const PlanPreference& pref, QuantizedLinearPlan* out) {
+        out->desc_ = desc;
+        QuantizePerTokenDescriptor qd;
+        qd.rows = desc.m;
+        qd.cols = desc.k;
+        qd.input = desc.activation_element;
+        qd.output = ElementKind::S8;
+        qd.q_min = desc.q_min;
+        qd.q_max = desc.q_max;
+        if (Error e = QuantizePerTokenPlan::select(qd, pref, &out->quant_); e != Error::Ok) return e;
+        out->skinny_ = desc.m > 0 && desc.m <= 8;
+        if (out->skinny_) {
+            GemvQ8Descriptor gd;
+            gd.m = desc.m;
+            gd.n = desc.c_out;
+            gd.k = desc.k;
+            gd.batch = 1;
+            gd.layout = LayoutSku::Rcr;
+            return GemvQ8Plan::select(gd, pref, false, &out->gemv_);
+        }
+        return W8A8GemmPlan::select(QGemmDescriptor{desc.m, desc.c_out, desc.k, LayoutSku::Rcr, EpilogueKind::Identity}, pref,
+                                    false, &out->gemm_);
+    }
+    const KernelSku& sku() const { return skinny_ ? gemv_.sku() : gemm_.sku(); }
+    PrecisionGuarantee precision_guarantee() const { return sku().precision_guarantee; }
+    size_t workspace_size() const { return skinny_ ? gemv_.workspace_size() : gemm_.workspace_size(); }
+    // True when the whole step is one launch.
+    bool fused_decode(const QuantizedLinearArgs& x) const {
+        const int64_t ldk = desc_.k > 0 ? desc_.k : 1, ldn = desc_.c_out > 0 ? desc_.c_out : 1;
+        return skinny_ && desc_.activation_element == ElementKind::Bf16 &&
+               baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_can_implement(desc_.m, desc_.c_out, desc_.k, ldk, ldk,
+                                                                                  ldn) == 0 &&
+               (reinterpret_cast<uintptr_t>(x.activation.ptr) & 15u) == 0 &&
+               (reinterpret_cast<uintptr_t>(x.weight_q.ptr) & 15u) == 0;
+    }
+    // `dependent`: the matrix kernel is launched as a programmatic dependent (see GemvQ8Plan::run_dependent).
+    Error run(void* stream, Workspace ws, const QuantizedLinearArgs& x, bool dependent = false) const {
+        const QuantizedLinearDescriptor& d = desc_;
+        const int64_t ldk = d.k > 0 ? d.k : 1, ldn = d.c_out > 0 ? d.c_out : 1;
+        if (x.activation.len < detail::span_elems(d.m, d.k, ldk) || x.weight_q.len < detail::span_elems(d.c_out, d.k, ldk) ||
+            x.output.len < detail::span_elems(d.m, d.c_out, ldn))
+            return Error::BufferTooSmall;
+        if (x.weight_scale.len < static_cast<size_t>(d.c_out) || x.act_scale_scratch.len < static_cast<size_t>(d.m))
+            return Error::BufferTooSmall;
+        if (fused_decode(x)) {
+            auto run = dependent ? baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_pdl_run
+                                 : baracuda_kernels_gemv_q8_m1_bf16_sm100a_quant_bf16_run;
+            return status_to_error(run(d.m, d.c_out, d.k, d.q_min, d.q_max, 1.0f, 0.0f, x.activation.ptr, ldk, x.weight_q.ptr,
+                                       ldk, x.weight_scale.ptr, x.act_scale_scratch.ptr, x.output.ptr, ldn, nullptr, 0,
+                                       stream));
+        }
+        if (x.act_q_scratch.len < detail::span_elems(d.m, d.k, ldk)) return Error::BufferTooSmall;
+        if (Error e = quant_.run(stream, x.activation, ldk, x.act_scale_scratch, {x.act_q_scratch.ptr, x.act_q_scratch.len},
+                                 ldk);
+            e != Error::Ok)
+            return e;
+        const DeviceSpan<const float> sa{x.act_scale_scratch.ptr, x.act_scale_scratch.len};
+        if (skinny_) {
+            GemvQ8Args g;
+            g.a = {x.act_q_scratch.ptr, x.act_q_scratch.len};
+            g.lda = ldk;
+            g.b = x.weight_q;
+            g.ldb = ldk;
+            g.scale_a = sa;
+            g.scale_b = x.weight_scale;
+            g.d = x.output;
+            g.ldd = ldn;
+            return dependent ? gemv_.run_dependent(stream, ws, g) : gemv_.run(stream, ws, g);
+        }
+        QGemmArgs g;
+        g.a = {x.act_q_scratch.ptr, x.act_q_scratch.len};
+        g.lda = ldk;
+        g.b = {x.weight_q.ptr, x.weight_q.len};
+        g.ldb = ldk;
+        g.scale_a = sa;
+        g.scale_b = x.weight_scale;
+        g.d = x.output;
+        g.ldd = ldn;
+        return dependent ? gemm_.run_dependent(stream, ws, g) : gemm_.run(stream, ws, g);
+    }
+
+  private:
+    QuantizedLinearDescriptor desc_{};
+    QuantizePerTokenPlan quant_{};
+    GemvQ8Plan gemv_{};
+    W8A8GemmPlan gemm_{};
+    bool skinny_ = false;
+};
+
+// SmoothQuantLinearPlan (crates/baracuda-kernels/src/quantize/smoothquant.rs:1-60, 70-330): one per-tensor activation
+// scale (frozen model metadata, held by the descriptor and passed to the kernel by value) and per-channel weight
+// scales.  One launch, no scratch: the reference fills an [M] scratch with the scalar and reuses its W8A8 kernel.
+struct SmoothQuantLinearDescriptor {
+    int32_t m = 0, n = 0, k = 0;
+    float act_scale = 1.0f;
+};
+
+struct SmoothQuantLinearArgs {  // smoothquant.rs:120-150
+    DeviceSpan<const int8_t> act_q;     // [M, K]
+    DeviceSpan<const int8_t> weight_q;  // [N, K]
+    DeviceSpan<const float> weight_scale;
+    DeviceSpan<void> output;            // [M, N] bf16
+};
+
+class SmoothQuantLinearPlan {
+  public:
+    static Error select(const SmoothQuantLinearDescriptor& desc, const PlanPreference& pref, SmoothQuantLinearPlan* out) {
+        if (!detail::backend_ok(pref)) return Error::Unsupported;
+        if (desc.m < 0 || desc.n < 0 || desc.k < 0) return Error::InvalidProblem;
+        if (!(desc.act_scale == desc.act_scale) || desc.act_scale - desc.act_scale != 0.0f) return Error::InvalidProblem;
+        out->desc_ = desc;
+        out->sku_ = KernelSku{OpCategory::Gemm, OP_SMOOTHQUANT_LINEAR, ElementKind::S8, ElementKind::Bf16, LayoutSku::Rcr,
+                              EpilogueKind::Identity, ArchSku::Sm100a, BackendKind::Bespoke,
+                              PrecisionGuarantee{MathPrecision::Int8, ElementKind::I32, true, true}};
+        return Error::Ok;
+    }
+    const KernelSku& sku() const { return sku_; }
+    PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
+    size_t workspace_size() const {
+        return baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
+    }
+    Error can_implement(const SmoothQuantLinearArgs& x) const {
+        const int64_t ldk = desc_.k > 0 ? desc_.k : 1, ldn = desc_.n > 0 ? desc_.n : 1;
+        const int32_t st = baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_can_implement(
+            desc_.m, desc_.n, desc_.k, x.act_q.ptr, ldk, x.weight_q.ptr, ldk, x.output.ptr, ldn);
+        if (st != 0) return status_to_error(st);
+        if (desc_.m == 0 || desc_.n == 0) return Error::Ok;
+        if (x.act_q.len < detail::span_elems(desc_.m, desc_.k, ldk) || x.weight_q.len < detail::span_elems(desc_.n, desc_.k, ldk) ||
+            x.output.len < detail::span_elems(desc_.m, desc_.n, ldn))
+            return Error::BufferTooSmall;
+        if (!x.weight_scale.ptr) return Error::InvalidProblem;
+        if (x.weight_scale.len < static_cast<size_t>(desc_.n)) return Error::BufferTooSmall;
+        return Error::Ok;
+    }
+    Error run(void* stream, Workspace ws, const SmoothQuantLinearArgs& x) const {
+        if (Error e = can_implement(x); e != Error::Ok) return e;
+        if (ws.bytes < workspace_size()) return Error::WorkspaceTooSmall;
+        const int64_t ldk = desc_.k > 0 ? desc_.k : 1, ldn = desc_.n > 0 ? desc_.n : 1;
+        return status_to_error(baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
+            desc_.m, desc_.n, desc_.k, x.act_q.ptr, ldk, x.weight_q.ptr, ldk, desc_.act_scale, x.weight_scale.ptr,
+            x.output.ptr, ldn, ws.ptr, ws.bytes, stream));
+    }
+
+  private:
+    SmoothQuantLinearDescriptor desc_{};
+    KernelSku sku_{};
 };
 
 // ---------------------------------------------------------------------------- tensor parallel
@@ -560,18 +820,23 @@ inline Error shard_range(int32_t extent, const TensorParallelContext& ctx, int32
     return Error::Ok;
 }
 
+// FusedMulticast: as FusedPeerStore, with the multicast address of the ranks' buffers in peer_y[world]; every tile is
+// stored once and the NVLink switch replicates it.
 enum class GatherMode : int32_t { None = BARACUDA_Q_GATHER_NONE, Nccl = BARACUDA_Q_GATHER_NCCL,
-                                  FusedPeerStore = BARACUDA_Q_GATHER_FUSED_PEER_STORE };
+                                  FusedPeerStore = BARACUDA_Q_GATHER_FUSED_PEER_STORE,
+                                  FusedMulticast = BARACUDA_Q_GATHER_FUSED_MULTICAST };
 enum class ReduceMode : int32_t { None = BARACUDA_Q_REDUCE_NONE, Nccl = BARACUDA_Q_REDUCE_NCCL };
 
 struct ColumnParallelArgs {
     DeviceSpan<const void> a;        // replicated activations [M, K]
     DeviceSpan<const float> scale_a; // [M] (or one float, per-tensor FP8)
-    DeviceSpan<const void> w_local;  // this rank's weight rows [N/world, K]
+    DeviceSpan<const void> w_local;  // Rcr: this rank's weight rows [N/world, K]; Rrr: its columns of the row-major
+                                     // [K, N] weight (pointer at column rank * N/world, row pitch N)
     DeviceSpan<const float> scale_b_local;
     DeviceSpan<void> y_local;        // [M, N/world] bf16
     DeviceSpan<void> y_full;         // Nccl: [world, M, N/world] bf16
-    void* const* peer_y = nullptr;   // FusedPeerStore: one row-major [M, N] buffer per rank
+    void* const* peer_y = nullptr;   // FusedPeerStore / FusedMulticast: one row-major [M, N] buffer per rank (then the
+                                     // multicast address, for FusedMulticast)
     int64_t ldd_full = 0;
     float alpha = 1.0f;
 };
@@ -579,8 +844,10 @@ struct ColumnParallelArgs {
 class ColumnParallelQGemmPlan {
   public:
     static Error make(const TensorParallelContext& ctx, int32_t m, int32_t out_features, int32_t k, ElementKind element,
-                      ScaleMode mode, GatherMode gather, ColumnParallelQGemmPlan* out) {
+                      ScaleMode mode, GatherMode gather, ColumnParallelQGemmPlan* out,
+                      LayoutSku layout = LayoutSku::Rcr) {
         if (element != ElementKind::S8 && element != ElementKind::Fp8E4M3) return Error::Unsupported;
+        out->rrr_ = layout == LayoutSku::Rrr;
         if (m < 0 || k < 0) return Error::InvalidProblem;
         int32_t lo = 0, hi = 0;
         if (Error e = shard_range(out_features, ctx, &lo, &hi); e != Error::Ok) return e;
@@ -598,29 +865,36 @@ class ColumnParallelQGemmPlan {
     int32_t n_local() const { return n_local_; }
     int32_t first_column() const { return col0_; }
     Error forward(void* stream, const ColumnParallelArgs& x) const {
-        if (x.a.len < detail::span_elems(m_, k_, k_) || x.w_local.len < detail::span_elems(n_local_, k_, k_))
+        const int64_t ldk = k_ > 0 ? k_ : 1, ldn = n_local_ > 0 ? n_local_ : 1;
+        const int64_t ldb = rrr_ ? (n_ > 0 ? n_ : 1) : ldk;
+        if (x.a.len < detail::span_elems(m_, k_, k_)) return Error::BufferTooSmall;
+        if (x.w_local.len < (rrr_ ? detail::span_elems(k_, n_local_, ldb) : detail::span_elems(n_local_, k_, ldk)))
             return Error::BufferTooSmall;
         if (x.y_local.len < detail::span_elems(m_, n_local_, n_local_)) return Error::BufferTooSmall;
         if (gather_ == GatherMode::Nccl && x.y_full.len < static_cast<size_t>(m_) * n_) return Error::BufferTooSmall;
-        if (gather_ == GatherMode::FusedPeerStore && !x.peer_y) return Error::InvalidProblem;
-        const int64_t ldk = k_ > 0 ? k_ : 1, ldn = n_local_ > 0 ? n_local_ : 1;
-        const int32_t st =
-            fp8_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run(
-                       ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(gather_), m_, n_local_, k_, x.a.ptr, ldk,
-                       x.w_local.ptr, ldk, x.y_local.ptr, ldn, x.scale_a.ptr, x.scale_b_local.ptr,
-                       static_cast<int32_t>(mode_), x.alpha, x.y_full.ptr, x.peer_y, x.ldd_full ? x.ldd_full : n_, nullptr, 0,
-                       stream)
-                 : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run(
-                       ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(gather_), m_, n_local_, k_, x.a.ptr, ldk,
-                       x.w_local.ptr, ldk, x.y_local.ptr, ldn, x.scale_a.ptr, x.scale_b_local.ptr, x.alpha, x.y_full.ptr,
-                       x.peer_y, x.ldd_full ? x.ldd_full : n_, nullptr, 0, stream);
+        const bool fused = gather_ == GatherMode::FusedPeerStore || gather_ == GatherMode::FusedMulticast;
+        if (fused && !x.peer_y) return Error::InvalidProblem;
+        int32_t st;
+        if (fp8_) {
+            auto run = rrr_ ? baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_nshard_run
+                            : baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_nshard_run;
+            st = run(ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(gather_), m_, n_local_, k_, x.a.ptr, ldk,
+                     x.w_local.ptr, ldb, x.y_local.ptr, ldn, x.scale_a.ptr, x.scale_b_local.ptr, static_cast<int32_t>(mode_),
+                     x.alpha, x.y_full.ptr, x.peer_y, x.ldd_full ? x.ldd_full : n_, nullptr, 0, stream);
+        } else {
+            auto run = rrr_ ? baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_nshard_run
+                            : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_nshard_run;
+            st = run(ctx_.rank, ctx_.world, ctx_.comm, static_cast<int32_t>(gather_), m_, n_local_, k_, x.a.ptr, ldk,
+                     x.w_local.ptr, ldb, x.y_local.ptr, ldn, x.scale_a.ptr, x.scale_b_local.ptr, x.alpha, x.y_full.ptr,
+                     x.peer_y, x.ldd_full ? x.ldd_full : n_, nullptr, 0, stream);
+        }
         return status_to_error(st);
     }
 
   private:
     TensorParallelContext ctx_{};
     int32_t m_ = 0, n_ = 0, k_ = 0, n_local_ = 0, col0_ = 0;
-    bool fp8_ = false;
+    bool fp8_ = false, rrr_ = false;
     ScaleMode mode_ = ScaleMode::PerRowCol;
     GatherMode gather_ = GatherMode::None;
 };

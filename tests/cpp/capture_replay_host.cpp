@@ -4,7 +4,8 @@
 // then the same call captured into a CUDA graph and replayed WITHOUT re-zeroing, so a replay that drops or mis-writes
 // an element diverges from the host-computed expectation.  On top of that the inputs are rewritten between replays:
 // a replay must read the buffers' current contents.  Covered: the decode GEMV (both weight layouts), the one-launch
-// decode step from bf16 activations, and the W8A8 GEMM whose tensor maps travel as kernel parameters.
+// decode step from bf16 activations, the W8A8 GEMM whose tensor maps travel as kernel parameters, and the C++ Plan layer
+// (QuantizedLinearPlan as a chain of dependent launches inside one graph, SmoothQuantLinearPlan).
 //
 // Build: g++ -std=c++17 -O1 -I include -I <cuda>/include capture_replay_host.cpp -L baracuda_b200
 //        -lbaracuda_kernels_q -L <cuda>/lib64 -lcudart ; prints "capture_replay_host ok".
@@ -18,6 +19,7 @@
 #include <vector>
 
 #include "baracuda_kernels_q.h"
+#include "baracuda_kernels_q_plan.hpp"
 
 #define CK(x)                                                                                  \
     do {                                                                                       \
@@ -269,6 +271,93 @@ int main() {
         }
         CK(cudaGraphExecDestroy(g.exec));
         CK(cudaGraphDestroy(g.graph));
+    }
+
+    // ---- the C++ Plan layer: two decode steps chained as programmatic dependent launches in ONE graph, then SmoothQuant --
+    {
+        using namespace baracuda;
+        PlanPreference pref;
+        QuantizedLinearDescriptor ld;
+        ld.m = 1;
+        ld.c_out = n;
+        ld.k = k;
+        QuantizedLinearPlan ql;
+        REQUIRE(QuantizedLinearPlan::select(ld, pref, &ql) == Error::Ok);
+        std::vector<uint16_t> xh(k);
+        for (int t = 0; t < k; ++t) xh[t] = bf16_rne((static_cast<float>(lcg(seed) % 2001u) - 1000.0f) * 0.002f);
+        uint16_t* d_xh = to_device(xh);
+        REQUIRE(d_xh);
+        float* d_qs = nullptr;
+        int8_t* d_q = nullptr;
+        uint16_t* d_out2 = nullptr;
+        CK(cudaMalloc(&d_qs, 4));
+        CK(cudaMalloc(&d_q, k));
+        CK(cudaMalloc(&d_out2, static_cast<size_t>(n) * 2));
+        QuantizedLinearArgs la;
+        la.activation = {d_xh, static_cast<size_t>(k)};
+        la.weight_q = {d_w, static_cast<size_t>(n) * k};
+        la.weight_scale = {d_sb, static_cast<size_t>(n)};
+        la.output = {d_out, static_cast<size_t>(n)};
+        la.act_q_scratch = {d_q, static_cast<size_t>(k)};
+        la.act_scale_scratch = {d_qs, 1};
+        REQUIRE(ql.fused_decode(la));
+        QuantizedLinearArgs lb = la;
+        lb.output = {d_out2, static_cast<size_t>(n)};
+        void* d_ws = nullptr;
+        const size_t ws_bytes = ql.workspace_size();
+        if (ws_bytes) CK(cudaMalloc(&d_ws, ws_bytes));
+        CK(cudaMemset(d_out, 0, static_cast<size_t>(n) * 2));
+        CK(cudaMemset(d_out2, 0, static_cast<size_t>(n) * 2));
+        Graph g;
+        CK(cudaStreamBeginCapture(stream, cudaStreamCaptureModeGlobal));
+        const Error e1 = ql.run(stream, Workspace{d_ws, ws_bytes}, la, false);
+        const Error e2 = ql.run(stream, Workspace{d_ws, ws_bytes}, lb, true);  // prefetches weights while the first drains
+        CK(cudaStreamEndCapture(stream, &g.graph));
+        REQUIRE(e1 == Error::Ok && e2 == Error::Ok);
+        CK(cudaGraphInstantiate(&g.exec, g.graph, 0));
+        std::vector<int8_t> q;
+        std::vector<float> s1(1);
+        quantize_row(xh, k, q, s1[0]);
+        const auto want = expect_w8a8(q, w, true, s1, sb, 1, n, k);
+        for (int rep = 0; rep < 2; ++rep) {
+            CK(cudaGraphLaunch(g.exec, stream));
+            CK(cudaStreamSynchronize(stream));
+            CK(cudaMemcpy(got.data(), d_out, static_cast<size_t>(n) * 2, cudaMemcpyDeviceToHost));
+            REQUIRE(std::memcmp(got.data(), want.data(), static_cast<size_t>(n) * 2) == 0);
+            CK(cudaMemcpy(got.data(), d_out2, static_cast<size_t>(n) * 2, cudaMemcpyDeviceToHost));
+            REQUIRE(std::memcmp(got.data(), want.data(), static_cast<size_t>(n) * 2) == 0);
+        }
+        CK(cudaGraphExecDestroy(g.exec));
+        CK(cudaGraphDestroy(g.graph));
+
+        // SmoothQuant: one per-tensor activation scale by value; the same bits as the per-token kernel on a constant vector
+        const int m = 128, gn = 1024, gk = 1024;
+        SmoothQuantLinearDescriptor sd;
+        sd.m = m;
+        sd.n = gn;
+        sd.k = gk;
+        sd.act_scale = 0.0173f;
+        SmoothQuantLinearPlan sq;
+        REQUIRE(SmoothQuantLinearPlan::select(sd, pref, &sq) == Error::Ok);
+        std::vector<int8_t> a(static_cast<size_t>(m) * gk);
+        for (auto& v : a) v = static_cast<int8_t>(static_cast<int>(lcg(seed) % 255u) - 127);
+        std::vector<int8_t> gw(w.begin(), w.begin() + static_cast<size_t>(gn) * gk);
+        std::vector<float> gsa(m, sd.act_scale), gsb(sb.begin(), sb.begin() + gn);
+        int8_t* d_a = to_device(a);
+        uint16_t* d_y = nullptr;
+        CK(cudaMalloc(&d_y, static_cast<size_t>(m) * gn * 2));
+        REQUIRE(d_a);
+        SmoothQuantLinearArgs sx;
+        sx.act_q = {d_a, a.size()};
+        sx.weight_q = {d_w, gw.size()};
+        sx.weight_scale = {d_sb, static_cast<size_t>(gn)};
+        sx.output = {d_y, static_cast<size_t>(m) * gn};
+        REQUIRE(sq.run(stream, Workspace::none(), sx) == Error::Ok);
+        CK(cudaStreamSynchronize(stream));
+        std::vector<uint16_t> y(static_cast<size_t>(m) * gn);
+        CK(cudaMemcpy(y.data(), d_y, y.size() * 2, cudaMemcpyDeviceToHost));
+        const auto want_sq = expect_w8a8(a, gw, true, gsa, gsb, m, gn, gk);
+        REQUIRE(std::memcmp(y.data(), want_sq.data(), y.size() * 2) == 0);
     }
 
     REQUIRE(baracuda_kernels_q_device_status() == 0);

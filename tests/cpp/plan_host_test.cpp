@@ -166,6 +166,73 @@ int main() {
     ex.scale_b = {static_cast<const float*>(fake(0x600000)), 16};
     CHECK(e.run(nullptr, Workspace::none(), ex) == Error::Ok);
 
+    // the quantiser, the W8A8 linear built from it, and the SmoothQuant linear: selection rules and typed checks
+    {
+        QuantizePerTokenPlan qp;
+        QuantizePerTokenDescriptor qd;
+        qd.rows = 4;
+        qd.cols = 4096;
+        CHECK(QuantizePerTokenPlan::select(qd, pref, &qp) == Error::Ok);
+        qd.q_max = 0;
+        CHECK(QuantizePerTokenPlan::select(qd, pref, &qp) == Error::InvalidProblem);
+        qd.q_max = 127;
+        qd.input = ElementKind::S8;
+        CHECK(QuantizePerTokenPlan::select(qd, pref, &qp) == Error::Unsupported);
+
+        QuantizedLinearPlan ql;
+        QuantizedLinearDescriptor ld;
+        ld.m = 1;
+        ld.c_out = 14336;
+        ld.k = 4096;
+        CHECK(QuantizedLinearPlan::select(ld, pref, &ql) == Error::Ok);
+        CHECK(ql.sku().op == OP_GEMV_Q8 && *ql.sku().layout == LayoutSku::Rcr);  // decode: the streaming GEMV
+        QuantizedLinearArgs la;
+        la.activation = {fake(0x10000), 4096};
+        la.weight_q = {static_cast<const int8_t*>(fake(0x100000)), size_t(14336) * 4096};
+        la.weight_scale = {static_cast<const float*>(fake(0x8000000)), 14336};
+        la.output = {fake(0x9000000), 14336};
+        la.act_scale_scratch = {static_cast<float*>(fake(0x9100000)), 1};
+        CHECK(ql.fused_decode(la));  // bf16 activations, m <= 8, K = 8 x 512: one launch
+        la.activation.ptr = fake(0x10008);
+        CHECK(!ql.fused_decode(la));  // misaligned activations take the two-launch path
+        la.activation.ptr = fake(0x10000);
+        la.weight_scale.len = 14335;
+        CHECK(ql.run(nullptr, Workspace::none(), la) == Error::BufferTooSmall);
+        ld.m = 512;
+        CHECK(QuantizedLinearPlan::select(ld, pref, &ql) == Error::Ok);
+        CHECK(ql.sku().op == OP_W8A8_GEMM && !ql.fused_decode(la));  // prefill: the tcgen05 GEMM
+        ld.activation_element = ElementKind::S8;
+        CHECK(QuantizedLinearPlan::select(ld, pref, &ql) == Error::Unsupported);
+
+        SmoothQuantLinearPlan sq;
+        SmoothQuantLinearDescriptor sd;
+        sd.m = 128;
+        sd.n = 1024;
+        sd.k = 1024;
+        sd.act_scale = 0.02f;
+        CHECK(SmoothQuantLinearPlan::select(sd, pref, &sq) == Error::Ok);
+        CHECK(sq.sku().op == OP_SMOOTHQUANT_LINEAR && sq.workspace_size() == 0);
+        SmoothQuantLinearArgs sa;
+        sa.act_q = {static_cast<const int8_t*>(fake(0x10000)), size_t(128) * 1024};
+        sa.weight_q = {static_cast<const int8_t*>(fake(0x200000)), size_t(1024) * 1024};
+        sa.weight_scale = {static_cast<const float*>(fake(0x600000)), 1024};
+        sa.output = {fake(0x400000), size_t(128) * 1024};
+        CHECK(sq.can_implement(sa) == Error::Ok);
+        sa.weight_scale.len = 1023;
+        CHECK(sq.can_implement(sa) == Error::BufferTooSmall);
+        sd.act_scale = 1.0f / 0.0f;
+        CHECK(SmoothQuantLinearPlan::select(sd, pref, &sq) == Error::InvalidProblem);  // the scale must be finite
+    }
+    // dependent launches exist for the bf16-out plans only
+    {
+        W8A8GemmPlan r;
+        CHECK(W8A8GemmPlan::select(desc, pref, true, &r) == Error::Ok);
+        CHECK(r.run_dependent(nullptr, Workspace::none(), x) == Error::Unsupported);
+        W8A8GemmPlan e2;
+        CHECK(W8A8GemmPlan::select(QGemmDescriptor{0, 16, 16}, pref, false, &e2) == Error::Ok);
+        CHECK(e2.run_dependent(nullptr, Workspace::none(), ex) == Error::Ok);  // empty problem: status 0 before any launch
+    }
+
     // tensor-parallel plans: sharding rules and the typed checks in front of the sharded C entry points
     {
         TensorParallelContext ctx{1, 4, nullptr};
@@ -184,6 +251,15 @@ int main() {
                                             &cp) == Error::Unsupported);
         ColumnParallelArgs ca;
         CHECK(cp.forward(nullptr, ca) == Error::BufferTooSmall);  // empty views are refused before any launch
+        ColumnParallelQGemmPlan cr;  // row-major [K, N] weight: the shard is a column range with the full row pitch
+        CHECK(ColumnParallelQGemmPlan::make(ctx, 128, 1024, 512, ElementKind::S8, ScaleMode::PerRowCol,
+                                            GatherMode::FusedMulticast, &cr, LayoutSku::Rrr) == Error::Ok);
+        ca.a = {fake(0x10000), size_t(128) * 512};
+        ca.w_local = {fake(0x200000), size_t(511) * 1024 + 256 - 1};
+        ca.y_local = {fake(0x400000), size_t(128) * 256};
+        CHECK(cr.forward(nullptr, ca) == Error::BufferTooSmall);  // one element short of (K - 1) * N + N / world
+        ca.w_local.len += 1;
+        CHECK(cr.forward(nullptr, ca) == Error::InvalidProblem);  // fused gather without the peer buffers
         RowParallelQGemmPlan rp;
         CHECK(RowParallelQGemmPlan::make(ctx, 64, 256, 4096, ElementKind::Fp8E4M3, ScaleMode::PerRowCol, ReduceMode::Nccl,
                                          &rp) == Error::Ok);
