@@ -197,11 +197,11 @@ def pin_to_gpu_numa_node(device_index: int) -> str:
         cpus = {64 * w + b for w, bits in enumerate(mask) for b in range(64) if (bits >> b) & 1}
         allowed = cpus & set(os.sched_getaffinity(0))
         if not allowed:
-            return "not pinned (no overlap with the allowed CPUs)"
+            return "page-locked; process not bound to the GPU's NUMA node (no overlap with the allowed CPUs)"
         os.sched_setaffinity(0, allowed)
-        return f"pinned to {len(allowed)} CPUs near the GPU"
+        return f"page-locked, process bound to the {len(allowed)} CPUs of the GPU's NUMA node"
     except Exception as exc:
-        return "not pinned (" + repr(exc)[:60] + ")"
+        return "page-locked; process not bound to the GPU's NUMA node (" + repr(exc)[:60] + ")"
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -539,7 +539,7 @@ def main() -> None:
 
     torch.cuda.set_device(local_rank)
     threads_before_pinning = host_threads()
-    numa_note = pin_to_gpu_numa_node(local_rank) if world > 1 else "single process, not pinned"
+    numa_note = pin_to_gpu_numa_node(local_rank) if world > 1 else "page-locked; single process, no NUMA binding"
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
