@@ -463,6 +463,29 @@ def side_workloads(peaks: dict) -> dict:
         return res
 
     out["prefill_layer_chain_w8a8"] = {f"M{m}": layer_chain(m) for m in (512, 2048)}
+
+    # the fused epilogue chains of the bf16-out W8A8 GEMM on the gate/up shape (K = 4096: the shortest main loop the
+    # epilogue has to hide behind), best of three interleaved rounds
+    def epilogue_chains(m: int, n: int, k: int) -> dict:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(m + n)
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda", generator=gen)
+        b = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda", generator=gen)
+        sa = torch.rand(m, device="cuda", generator=gen) * 1e-3
+        sb = torch.rand(n, device="cuda", generator=gen) * 1e-3
+        bias = torch.randn(n, device="cuda", generator=gen)
+        d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        kinds = (bq.EpilogueKind.Identity, bq.EpilogueKind.Bias, bq.EpilogueKind.BiasGelu, bq.EpilogueKind.BiasSilu)
+        best = {}
+        for _ in range(3):
+            for e in kinds:
+                plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, epilogue=e))
+                x = bq.QGemmArgs(a=a, b=b, d=d, scale_a=sa, scale_b=sb, bias=None if e is bq.EpilogueKind.Identity else bias)
+                us = statistics.median(event_time_ms(lambda: plan.run(None, None, x), steps=4, warmup=2, flush=flush)) * 1e3
+                best[e.value] = min(best.get(e.value, us), us)
+        return {"shape": [m, n, k], "us": best, "TOPS": {key: 2.0 * m * n * k / v / 1e6 for key, v in best.items()}}
+
+    out["epilogue_chains_w8a8"] = epilogue_chains(8192, 28672, 4096)
     return out
 
 
