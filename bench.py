@@ -825,6 +825,19 @@ def main() -> None:
     parity["ok"] = all(parity["checked"].values()) and status == 0
 
     fp8_lib = fp8_library_probe() if rank == 0 else None
+    # The same launch on zero-filled operands (this rank's shard, rank 0 only, after all ranks' timed work): the tensor
+    # pipe and the operand feed do the same work, but nothing toggles, so the chip stays under its power cap -- the
+    # kernel's own rate, beside the rate the cap allows on real data.  A diagnostic, not the reported value.
+    zero_rate = None
+    if rank == 0:
+        az, wz = torch.zeros_like(a_q), torch.zeros_like(w_q)
+        zplan = par.ColumnParallelQGemmPlan(par.TensorParallelContext(0, 1, None), C4_M, n_local, C4_K, kind="fp8",
+                                            gather=par.GATHER_NONE)
+        z_ms = event_time_ms(lambda: zplan.forward(None, az, sa, wz, sb, d), steps=8, warmup=3, flush=flush)
+        z_t = statistics.median(z_ms) * 1e-3
+        zero_rate = {"TFLOPs": 2.0 * C4_M * n_local * C4_K / z_t / 1e12, "us": z_t * 1e6,
+                     "what": "this launch on zero-filled operands (no switching activity: not limited by the power cap)"}
+        del az, wz
     cpu_base, gemv = None, None
     if world == 1 and not args.no_others:
         gemv = gemv_m1(peaks)
@@ -845,6 +858,7 @@ def main() -> None:
                     "peak_is": f"2 x bf16 burst of {peaks['source']} peaks",
                     "frac_of_nominal_4500": achieved / 4500.0,
                     "peak_fp8_library": fp8_lib,
+                    "kernel_rate_zero_operands": zero_rate,
                     "frac_of_fp8_library": (achieved / fp8_lib["TFLOPs"]) if fp8_lib and fp8_lib.get("TFLOPs") else None,
                     "parity": parity}
         if gemv is not None:
