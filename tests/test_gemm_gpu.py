@@ -342,10 +342,12 @@ def test_full_size_long_k_fp8_8192x8192x28672(oracle):
     assert oracle.compare_tolerant(want, got, 1e-2, 1e-4 * float(np.abs(want).max())) == -1
 
 
-@pytest.mark.parametrize("shape", [(8192, 28672, 4096), (8192, 4096, 14336)])
+@pytest.mark.parametrize("shape", [(m, n, k) for m in (512, 2048, 8192)
+                                   for (n, k) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336))])
 def test_full_size_prefill_w8a8(oracle, shape):
-    """The two largest prefill GEMMs at full size: exact row sample, exact integer checksum over every output, and the
-    bf16 dequant of the sampled rows bit for bit."""
+    """Every prefill GEMM of the benchmark's layer (qkv, o, gate/up, down at M = 512, 2048, 8192) at full size, on the
+    schedule the dispatch picks for it: exact row sample, exact integer checksum over every output, and the bf16 dequant
+    of the sampled rows bit for bit."""
     m, n, k = shape
     rng = np.random.default_rng(m + n + k)
     aq = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
