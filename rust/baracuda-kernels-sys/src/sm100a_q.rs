@@ -86,6 +86,12 @@ gemm_bf16_epilogue_run!(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_r
 gemm_bf16_epilogue_run!(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run);
 gemm_bf16_epilogue_run!(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run);
 gemm_bf16_epilogue_run!(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run);
+// The same arguments, launched as programmatic dependents of the kernel before them on the stream (a per-call choice:
+// the caller promises that kernel does not write `b`).
+gemm_bf16_epilogue_run!(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_pdl_run);
+gemm_bf16_epilogue_run!(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_pdl_run);
+gemm_bf16_epilogue_run!(baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_pdl_run);
+gemm_bf16_epilogue_run!(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_pdl_run);
 
 macro_rules! gemm_same_type_family {
     ($run:ident, $can:ident, $ws:ident) => {
@@ -133,6 +139,39 @@ gemm_same_type_epilogue_run!(baracuda_kernels_gemm_s8_rcr_sm100a_epilogue_run);
 gemm_same_type_epilogue_run!(baracuda_kernels_gemm_s8_rrr_sm100a_epilogue_run);
 gemm_same_type_epilogue_run!(baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_epilogue_run);
 gemm_same_type_epilogue_run!(baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_epilogue_run);
+
+macro_rules! gemm_same_type_bias_run {
+    ($($name:ident),+ $(,)?) => {
+        extern "C" {
+            $(
+            /// Signature of the reference's `baracuda_kernels_gemm_s8_rrr_sm80_bias…_run` /
+            /// `baracuda_kernels_gemm_fp8_e4m3_{rcr,rrr}_sm89_bias…_run` (`bias` before `alpha`); the suffix names the
+            /// activation and, for s8, the bias element (`f32` or `i32`).
+            pub fn $name(
+                m: i32, n: i32, k: i32,
+                a: *const c_void, lda: i64, b: *const c_void, ldb: i64,
+                c: *const c_void, ldc: i64, d: *mut c_void, ldd: i64,
+                bias: *const c_void, alpha: f32, beta: f32,
+                workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+            ) -> i32;
+            )+
+        }
+    };
+}
+gemm_same_type_bias_run!(
+    baracuda_kernels_gemm_s8_rcr_sm100a_bias_f32_run, baracuda_kernels_gemm_s8_rcr_sm100a_bias_relu_f32_run,
+    baracuda_kernels_gemm_s8_rcr_sm100a_bias_gelu_f32_run, baracuda_kernels_gemm_s8_rcr_sm100a_bias_silu_f32_run,
+    baracuda_kernels_gemm_s8_rcr_sm100a_bias_i32_run, baracuda_kernels_gemm_s8_rcr_sm100a_bias_relu_i32_run,
+    baracuda_kernels_gemm_s8_rcr_sm100a_bias_gelu_i32_run, baracuda_kernels_gemm_s8_rcr_sm100a_bias_silu_i32_run,
+    baracuda_kernels_gemm_s8_rrr_sm100a_bias_f32_run, baracuda_kernels_gemm_s8_rrr_sm100a_bias_relu_f32_run,
+    baracuda_kernels_gemm_s8_rrr_sm100a_bias_gelu_f32_run, baracuda_kernels_gemm_s8_rrr_sm100a_bias_silu_f32_run,
+    baracuda_kernels_gemm_s8_rrr_sm100a_bias_i32_run, baracuda_kernels_gemm_s8_rrr_sm100a_bias_relu_i32_run,
+    baracuda_kernels_gemm_s8_rrr_sm100a_bias_gelu_i32_run, baracuda_kernels_gemm_s8_rrr_sm100a_bias_silu_i32_run,
+    baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_run, baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_relu_run,
+    baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_gelu_run, baracuda_kernels_gemm_fp8_e4m3_rcr_sm100a_bias_silu_run,
+    baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_run, baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_relu_run,
+    baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_gelu_run, baracuda_kernels_gemm_fp8_e4m3_rrr_sm100a_bias_silu_run,
+);
 
 extern "C" {
     /// SmoothQuant inference forward: one per-tensor activation scale by value, per-channel weight scales.
@@ -276,6 +315,116 @@ extern "C" {
         d_full: *mut c_void, peer_d: *const *mut c_void, ldd_full: i64,
         workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
     ) -> i32;
+
+    /// The same for a row-major `[K, N]` weight: `b_local` points at column `rank * n_local`, `ldb` stays the full N.
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_nshard_run(
+        rank: i32, world: i32, comm: *mut c_void, gather: i32,
+        m: i32, n_local: i32, k: i32,
+        a: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        d_local: *mut c_void, ldd: i64,
+        scale_a: *const c_void, scale_b_local: *const c_void, scale_mode: i32, alpha: f32,
+        d_full: *mut c_void, peer_d: *const *mut c_void, ldd_full: i64,
+        workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_nshard_run(
+        rank: i32, world: i32, comm: *mut c_void, gather: i32,
+        m: i32, n_local: i32, k: i32,
+        a: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        d_local: *mut c_void, ldd: i64,
+        scale_a: *const c_void, scale_b_local: *const c_void, alpha: f32,
+        d_full: *mut c_void, peer_d: *const *mut c_void, ldd_full: i64,
+        workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+
+    /// Row-parallel (K-sharded) forward: raw accumulators in `workspace` (`[M, N]` 32-bit words), `reduce` 0 none,
+    /// 1 `ncclAllReduce(sum)`, then one pass that applies scales, alpha and the optional `f32[N]` bias.
+    pub fn baracuda_kernels_gemm_q8_kshard_workspace_size(m: i32, n: i32) -> usize;
+    pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_run(
+        rank: i32, world: i32, comm: *mut c_void, reduce: i32,
+        m: i32, n: i32, k_local: i32,
+        a_local: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        d: *mut c_void, ldd: i64, scale_a: *const c_void, scale_b: *const c_void,
+        bias: *const c_void, alpha: f32,
+        workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_run(
+        rank: i32, world: i32, comm: *mut c_void, reduce: i32,
+        m: i32, n: i32, k_local: i32,
+        a_local: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        d: *mut c_void, ldd: i64, scale_a: *const c_void, scale_b: *const c_void, scale_mode: i32,
+        bias: *const c_void, alpha: f32,
+        workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+    /// Both exchanges inside the kernels over peer-mapped memory: `peer_y` and `peer_staging` hold `world` device
+    /// pointers valid on this rank (`[M, N]` bf16 results, `[world][M / world][N]` 32-bit staging).
+    pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_run(
+        rank: i32, world: i32, comm: *mut c_void,
+        m: i32, n: i32, k_local: i32,
+        a_local: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        peer_y: *const *mut c_void, ldy: i64, scale_a: *const c_void, scale_b: *const c_void,
+        bias: *const c_void, alpha: f32,
+        peer_staging: *const *mut c_void, barrier_scratch: *mut c_void, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run(
+        rank: i32, world: i32, comm: *mut c_void,
+        m: i32, n: i32, k_local: i32,
+        a_local: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        peer_y: *const *mut c_void, ldy: i64, scale_a: *const c_void, scale_b: *const c_void, scale_mode: i32,
+        bias: *const c_void, alpha: f32,
+        peer_staging: *const *mut c_void, barrier_scratch: *mut c_void, stream: *mut c_void,
+    ) -> i32;
+
+    /// Gated-MLP up-projection over an interleaved gate/up weight `[n2, K]`: `D = silu(z_gate) * z_up`, bf16 `[M, n2 / 2]`.
+    pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run(
+        m: i32, n2: i32, k: i32,
+        a: *const c_void, lda: i64, b_gate_up: *const c_void, ldb: i64,
+        d: *mut c_void, ldd: i64,
+        scale_a: *const c_void, scale_b: *const c_void, bias: *const c_void,
+        alpha: f32,
+        workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_workspace_size(m: i32, n2: i32, k: i32) -> usize;
+    pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_can_implement(
+        m: i32, n2: i32, k: i32,
+        a: *const c_void, lda: i64, b_gate_up: *const c_void, ldb: i64,
+        d: *const c_void, ldd: i64,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_run(
+        m: i32, n2: i32, k: i32,
+        a: *const c_void, lda: i64, b_gate_up: *const c_void, ldb: i64,
+        d: *mut c_void, ldd: i64,
+        scale_a: *const c_void, scale_b: *const c_void, scale_mode: i32, bias: *const c_void,
+        alpha: f32,
+        workspace: *mut c_void, workspace_bytes: usize, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_workspace_size(m: i32, n2: i32, k: i32) -> usize;
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_swiglu_can_implement(
+        m: i32, n2: i32, k: i32,
+        a: *const c_void, lda: i64, b_gate_up: *const c_void, ldb: i64,
+        d: *const c_void, ldd: i64,
+    ) -> i32;
+    /// Builds the interleaved operand (and, with 4-byte rows, the interleaved scale / bias vectors): out row
+    /// `64 b + i` = gate row `32 b + i` for `i < 32`, else up row `32 b + i - 32`; pitches in bytes.
+    pub fn baracuda_kernels_q_interleave_gate_up_run(
+        f_rows: i64, row_bytes: i64,
+        gate: *const c_void, gate_pitch: i64, up: *const c_void, up_pitch: i64,
+        out: *mut c_void, out_pitch: i64, stream: *mut c_void,
+    ) -> i32;
+
+    /// Communicator helpers over the run-time-loaded NCCL (`Communicator::{new_with_id, all_gather}` of baracuda-nccl).
+    pub fn baracuda_q_nccl_version() -> i32;
+    pub fn baracuda_q_nccl_unique_id(id_out_128_bytes: *mut c_void) -> i32;
+    pub fn baracuda_q_nccl_comm_init_rank(comm_out: *mut *mut c_void, world: i32, id_128_bytes: *const c_void, rank: i32) -> i32;
+    pub fn baracuda_q_nccl_comm_destroy(comm: *mut c_void) -> i32;
+    pub fn baracuda_q_nccl_stream_barrier(comm: *mut c_void, scratch_one_float: *mut c_void, stream: *mut c_void) -> i32;
+    pub fn baracuda_q_nccl_all_gather_bytes(
+        comm: *mut c_void, world: i32, send: *const c_void, recv: *mut c_void, bytes_per_rank: usize, stream: *mut c_void,
+    ) -> i32;
+
+    /// Test hooks: a kernel choice for the calling thread only (see the header for keys and values), and a launch
+    /// whose only thread waits `limit_cycles` on a barrier nothing completes (status 299 afterwards).
+    pub fn baracuda_kernels_q_set_tuning(key: i32, value: i32) -> i32;
+    pub fn baracuda_kernels_q_selftest_bounded_wait(limit_cycles: i64, stream: *mut c_void) -> i32;
 
     /// Read-and-clear of the word a kernel sets when one of its bounded waits ran out (0 = none).
     pub fn baracuda_kernels_q_device_status() -> i32;

@@ -192,7 +192,17 @@ impl Fp8ScaledGemmPlan {
     }
 
     /// Asynchronous launch on `stream`; graph-capture safe.
-    pub fn run(&self, stream: &Stream, _workspace: Workspace<'_>, args: Fp8ScaledGemmArgs<'_>) -> Result<()> {
+    pub fn run(&self, stream: &Stream, workspace: Workspace<'_>, args: Fp8ScaledGemmArgs<'_>) -> Result<()> {
+        self.launch(stream, workspace, args, false)
+    }
+
+    /// The same launch as a programmatic dependent of the kernel before it on `stream`: prologue and the first
+    /// weight tiles are issued while that kernel finishes.  The caller asserts that it does not write `args.b`.
+    pub fn run_dependent(&self, stream: &Stream, workspace: Workspace<'_>, args: Fp8ScaledGemmArgs<'_>) -> Result<()> {
+        self.launch(stream, workspace, args, true)
+    }
+
+    fn launch(&self, stream: &Stream, _workspace: Workspace<'_>, args: Fp8ScaledGemmArgs<'_>, dependent: bool) -> Result<()> {
         self.can_implement(&args)?;
         let d = &self.desc;
         let mode = match d.scale_mode {
@@ -217,16 +227,17 @@ impl Fp8ScaledGemmPlan {
         };
         let bias = args.bias.as_ref().map_or(core::ptr::null(), |v| v.data.as_raw().0 as *const c_void);
         let s = stream.as_raw() as *mut c_void;
-        let code = unsafe {
-            match d.layout {
-                LayoutSku::Rcr => sys::baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run(
-                    d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb, mode, bias, epi,
-                    args.alpha, args.beta, core::ptr::null_mut(), 0, s),
-                LayoutSku::Rrr => sys::baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run(
-                    d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb, mode, bias, epi,
-                    args.alpha, args.beta, core::ptr::null_mut(), 0, s),
-            }
+        // the four symbols share one signature
+        let f = match (d.layout, dependent) {
+            (LayoutSku::Rcr, false) => sys::baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_epilogue_run,
+            (LayoutSku::Rrr, false) => sys::baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run,
+            (LayoutSku::Rcr, true) => sys::baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_pdl_run,
+            (LayoutSku::Rrr, true) => sys::baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_pdl_run,
         };
-        map_status(code, "Fp8ScaledGemmPlan::run")
+        let code = unsafe {
+            f(d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb, mode, bias, epi,
+              args.alpha, args.beta, core::ptr::null_mut(), 0, s)
+        };
+        map_status(code, if dependent { "Fp8ScaledGemmPlan::run_dependent" } else { "Fp8ScaledGemmPlan::run" })
     }
 }

@@ -235,4 +235,28 @@ impl W8A8GemmPlan {
         };
         map_status(code, "W8A8GemmPlan::run")
     }
+
+    /// The same launch as a programmatic dependent of the kernel before it on `stream`: prologue and the first
+    /// weight tiles are issued while that kernel finishes.  The caller asserts that it does not write `args.b`.
+    pub fn run_dependent(&self, stream: &Stream, _workspace: Workspace<'_>, args: W8A8GemmArgs<'_>) -> Result<()> {
+        self.can_implement(&args)?;
+        let d = &self.desc;
+        let (c_ptr, ldc) = match &args.c {
+            Some(c) => (c.data.as_raw().0 as *const c_void, c.ld),
+            None => (core::ptr::null(), 0),
+        };
+        let bias = args.bias.as_ref().map_or(core::ptr::null(), |v| v.data.as_raw().0 as *const c_void);
+        let f = match d.layout {
+            LayoutSku::Rcr => sys::baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_pdl_run,
+            LayoutSku::Rrr => sys::baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_pdl_run,
+        };
+        let code = unsafe {
+            f(d.m, d.n, d.k, args.a.data.as_raw().0 as *const c_void, args.a.ld, args.b.data.as_raw().0 as *const c_void,
+              args.b.ld, c_ptr, ldc, args.d.data.as_raw().0 as *mut c_void, args.d.ld,
+              args.scale_a.data.as_raw().0 as *const c_void, args.scale_b.data.as_raw().0 as *const c_void,
+              sys::BARACUDA_Q_SCALE_PER_ROW_COL, bias, epilogue_code(d.epilogue), args.alpha, args.beta,
+              core::ptr::null_mut(), 0, stream.as_raw() as *mut c_void)
+        };
+        map_status(code, "W8A8GemmPlan::run_dependent")
+    }
 }
