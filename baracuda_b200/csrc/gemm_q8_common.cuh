@@ -76,19 +76,33 @@ struct GemmParams {
 // instruction cache and halved the speed even of launches that never ran them (8-bit-out GEMM 8192 x 8192 x 4096:
 // 404 us against 184 us for the bf16 SKU); called out of line they cost 3-6x the identity epilogue.  The results stay
 // inside the reference's tolerance for these two chains (+-1 output code, two e4m3 grid steps).
+// gelu(z) = 0.5 z (1 + erf(z / sqrt 2)) = relu(z) - 0.5 |z| (1 - erf(|z| / sqrt 2)), and 1 - erf(x) = poly(t) t exp(-x^2)
+// with t = 1 / (1 + p x) (Abramowitz-Stegun 7.1.26): fifteen instructions, two of them on the special-function unit,
+// and no cancellation for negative z (the direct form subtracts erf from 1 there).
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float gelu_erf_poly(float z) {
-    const float x = z * 0.70710678118654752440f;
-    const float ax = fabsf(x);
-    const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    const float az = fabsf(z);
+    const float t = rcp_approx(fmaf(0.3275911f * 0.70710678118654752440f, az, 1.0f));
+    const float e = ex2_approx((z * z) * (-0.5f * 1.44269504088896340736f));  // exp(-z^2 / 2)
     float poly = fmaf(1.061405429f, t, -1.453152027f);
     poly = fmaf(poly, t, 1.421413741f);
     poly = fmaf(poly, t, -0.284496736f);
     poly = fmaf(poly, t, 0.254829592f);
-    const float erf_abs = fmaf(-poly * t, __expf(-ax * ax), 1.0f);
-    return 0.5f * z * (1.0f + copysignf(erf_abs, x));
+    const float q = (poly * t) * e;  // 1 - erf(|z| / sqrt 2)
+    return fmaf(-0.5f * az, q, fmaxf(z, 0.0f));
 }
 
-__device__ __forceinline__ float silu_fast(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
+// silu(z) = z / (1 + exp(-z)): two special-function instructions and three others
+__device__ __forceinline__ float silu_fast(float z) { return z * rcp_approx(1.0f + ex2_approx(z * -1.44269504088896340736f)); }
 
 // 32 staged floats (column scales or bias values of one 32-column block; every lane reads the same addresses) as
 // eight 16-byte broadcast loads.  The epilogue shares the SM's shared-memory bandwidth with the operand tiles the

@@ -594,9 +594,13 @@ int32_t launch_pair(const GemmDesc& g, cudaStream_t stream) {
         }
     }
     if constexpr (!RAW && !FUSED) {
-        // bias + gelu on short K: eight epilogue warps (the chain's arithmetic outlasts the next tile's MMAs on four;
-        // measured 8-20 % faster at K = 4096, while at K = 8192 the extra warps slow the main loop by 6 %)
-        const bool ew8 = g.epilogue_warps == 8 || (g.epilogue_warps == 0 && g.act == 2 && g.k <= 6144);
+        // bias + gelu / silu with at most two waves of tiles: eight epilogue warps, because the last tile's epilogue is
+        // exposed (512 x 14336 x 4096 gelu 44 -> 42 us).  In longer runs four warps hide the chain behind the next
+        // tile's MMAs just as well since it shrank to fifteen instructions per element (8192 x 28672 x 4096: 660 us
+        // either way), and at K = 8192 the extra warps slow the main loop.
+        const int64_t ew_tiles = static_cast<int64_t>((g.m + PAIR_TILE_M - 1) / PAIR_TILE_M) * ((g.n + tn - 1) / tn);
+        const bool ew8 = g.epilogue_warps == 8 ||
+                         (g.epilogue_warps == 0 && g.act >= 2 && ew_tiles <= 2 * (sm_count_of_current_device() / 2));
         if (ew8 && !g.swiglu) {
             switch (tn) {
                 case 256: return launch_pair_tn<KIND, false, false, 256, false, false, true>(g, stream);

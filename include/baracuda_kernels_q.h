@@ -669,7 +669,7 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  *          kernel also for m = 1; 8 direct-load split-K kernel (row-major weights); 9 byte-load kernel;
  *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128; 2 = the mixed 256 / 128 schedule;
  *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
- *   key 5  CTA-pair GEMM epilogue warps: 0 automatic (eight for bias + gelu on K <= 6144), 4, 8.
+ *   key 5  CTA-pair GEMM epilogue warps: 0 automatic (eight for gelu / silu chains on at most two waves of tiles), 4, 8.
  * Any other key or value returns 2.
  * selftest_bounded_wait: launches one thread that waits, for at most limit_cycles SM clock cycles
  * (1 .. 2^28), on a barrier that nothing completes -- the time-out path of every kernel here.  After the
