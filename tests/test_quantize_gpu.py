@@ -10,7 +10,10 @@ from helpers import bf16_bits, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("shape", [(1, 4096), (8, 4096), (128, 1024), (37, 50), (5, 8200), (3, 20000), (2048, 8192)])
+# the register-resident kernel at every threads-per-row choice (32 ... 1024), row counts that do not fill a CTA of eight
+# warps, and the general kernel (columns not a whole number of vectors, rows longer than the registers hold)
+@pytest.mark.parametrize("shape", [(1, 4096), (8, 4096), (128, 1024), (37, 50), (5, 8200), (3, 20000), (2048, 8192),
+                                   (37, 4096), (13, 14336), (2, 40000), (2, 65536), (1, 70000), (3, 8)])
 @pytest.mark.parametrize("in_dtype", ["f32", "bf16"])
 def test_per_token_s8(oracle, shape, in_dtype):
     rows, cols = shape
@@ -31,18 +34,92 @@ def test_per_token_s8(oracle, shape, in_dtype):
     assert np.array_equal(q.cpu().numpy(), q_ref)
 
 
-@pytest.mark.parametrize("shape", [(8, 4096), (100, 70), (512, 8192)])
-def test_per_token_e4m3(oracle, shape):
+@pytest.mark.parametrize("shape", [(8, 4096), (100, 70), (512, 8192), (19, 14336), (2, 40000)])
+@pytest.mark.parametrize("in_dtype", ["f32", "bf16"])
+def test_per_token_e4m3(oracle, shape, in_dtype):
     rows, cols = shape
-    x = np.random.default_rng(cols).standard_normal((rows, cols)).astype(np.float32)
+    x = (np.random.default_rng(cols).standard_normal((rows, cols)) * 3.0).astype(np.float32)
+    xt = torch.from_numpy(x)
+    if in_dtype == "bf16":
+        xt = xt.to(torch.bfloat16)
+        x = xt.to(torch.float32).numpy()
     q_ref, s_ref = oracle.quantize_rows_e4m3(x)
     plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "e4m3"))
     scale = torch.empty(rows, device="cuda")
     q = torch.empty((rows, cols), dtype=torch.uint8, device="cuda")
-    plan.run(None, dev(x), scale, q)
+    plan.run(None, xt.cuda(), scale, q)
     torch.cuda.synchronize()
     assert np.array_equal(scale.cpu().numpy(), s_ref)
     assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+@pytest.mark.parametrize("in_dtype", ["f32", "bf16"])
+def test_aligned_padded_pitches_keep_the_vector_path_inside_the_row(oracle, in_dtype):
+    """Row pitches wider than the row (but 16-byte aligned, so the register-resident kernel runs): nothing beyond the
+    row's columns is read into the maximum or written, and non-finite padding cannot leak into the scales."""
+    rows, cols, ld_in, ld_out = 11, 4096, 4096 + 64, 4096 + 32
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((rows, ld_in)).astype(np.float32)
+    x[:, cols:] = 1e30  # padding far above every real value
+    xt = torch.from_numpy(x)
+    if in_dtype == "bf16":
+        xt = xt.to(torch.bfloat16)
+        x = xt.to(torch.float32).numpy()
+    q_ref, s_ref = oracle.quantize_rows_s8(np.ascontiguousarray(x[:, :cols]))
+    plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "s8"))
+    scale = torch.empty(rows, device="cuda")
+    q = torch.full((rows, ld_out), 77, dtype=torch.int8, device="cuda")
+    plan.run(None, xt.cuda(), scale, q, ld_in=ld_in, ld_out=ld_out)
+    torch.cuda.synchronize()
+    got = q.cpu().numpy()
+    assert np.array_equal(got[:, :cols], q_ref) and np.all(got[:, cols:] == 77)
+    assert np.array_equal(scale.cpu().numpy(), s_ref)
+
+
+@pytest.mark.parametrize("qrange", [(-127, 127), (-128, 127), (-7, 7), (-50, 100), (-100, 50), (0, 127)])
+@pytest.mark.parametrize("in_dtype", ["f32", "bf16"])
+def test_quantization_ranges_with_and_without_the_clamp(oracle, qrange, in_dtype):
+    """Symmetric ranges (and -128..127) take the clamp-free rounding of the register-resident kernel, ranges the scaled
+    values can leave keep the clamp; both against the oracle, on rows with ties (x.5 after scaling) in them."""
+    qmin, qmax = qrange
+    rows, cols = 16, 4096
+    rng = np.random.default_rng(qmax - qmin)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    # rows whose scale is a power of two, so that many scaled values land exactly on .5
+    x[0] = (rng.integers(-2 * qmax, 2 * qmax + 1, size=cols) * 0.5).astype(np.float32)
+    x[0, 0] = float(qmax)
+    x[1] = -x[0]
+    xt = torch.from_numpy(x)
+    if in_dtype == "bf16":
+        xt = xt.to(torch.bfloat16)
+        x = xt.to(torch.float32).numpy()
+    q_ref, s_ref = oracle.quantize_rows_s8(x, qmin, qmax)
+    plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "s8", qmin, qmax))
+    scale = torch.empty(rows, device="cuda")
+    q = torch.empty((rows, cols), dtype=torch.int8, device="cuda")
+    plan.run(None, xt.cuda(), scale, q)
+    torch.cuda.synchronize()
+    assert np.array_equal(scale.cpu().numpy(), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+def test_nan_entries_are_skipped_by_the_row_maximum_on_both_paths(oracle):
+    """fmaxf ignores a NaN operand; the bf16 fast path compares bit patterns and has to skip NaNs explicitly."""
+    rows, cols = 4, 4096
+    x = np.random.default_rng(5).standard_normal((rows, cols)).astype(np.float32)
+    x[1, 17] = np.nan
+    x[2, 4000] = np.nan
+    clean = np.where(np.isnan(x), 0.0, x).astype(np.float32)
+    _, s_ref = oracle.quantize_rows_s8(clean)
+    for xt in (torch.from_numpy(x), torch.from_numpy(x).to(torch.bfloat16)):
+        if xt.dtype == torch.bfloat16:
+            _, s_ref = oracle.quantize_rows_s8(np.where(np.isnan(x), 0.0, xt.to(torch.float32).numpy()).astype(np.float32))
+        plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, "s8"))
+        scale = torch.empty(rows, device="cuda")
+        q = torch.empty((rows, cols), dtype=torch.int8, device="cuda")
+        plan.run(None, xt.cuda(), scale, q)
+        torch.cuda.synchronize()
+        assert np.array_equal(scale.cpu().numpy(), s_ref)
 
 
 def test_padded_pitches_and_canaries(oracle):
