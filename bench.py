@@ -492,6 +492,24 @@ def side_workloads(peaks: dict) -> dict:
         return {"shape": [m, n, k], "us": best, "TOPS": {key: 2.0 * m * n * k / v / 1e6 for key, v in best.items()}}
 
     out["epilogue_chains_w8a8"] = epilogue_chains(8192, 28672, 4096)
+
+    # the per-token activation quantiser in front of the GEMM (HBM-bound: the row is read once, codes and one scale
+    # written): a CUDA graph over distinct inputs larger than L2 together, bytes = rows * cols * (in + 1) + rows * 4
+    quant = {}
+    for name, dtype, kind in (("bf16_to_s8", torch.bfloat16, "s8"), ("bf16_to_e4m3", torch.bfloat16, "e4m3"),
+                              ("f32_to_s8", torch.float32, "s8")):
+        rows, cols = 8192, 4096
+        esz = 2 if dtype == torch.bfloat16 else 4
+        xs = [torch.randn(rows, cols, device="cuda", dtype=dtype) for _ in range(max(3, 400_000_000 // (rows * cols * esz) + 1))]
+        qbuf = torch.empty((rows, cols), dtype=torch.int8 if kind == "s8" else torch.uint8, device="cuda")
+        sbuf = torch.empty(rows, dtype=torch.float32, device="cuda")
+        qplan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(rows, cols, kind))
+        t = min(graph_launch_ms([(lambda x=x: qplan.run(None, x, sbuf, qbuf)) for x in xs], replays=10) for _ in range(2)) * 1e-3
+        byts = rows * cols * (esz + 1) + rows * 4
+        quant[name] = {"shape": [rows, cols], "us": t * 1e6, "GBps": byts / t / 1e9, "algorithmic_bytes": byts,
+                       "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
+        del xs
+    out["quantize_per_token"] = quant
     return out
 
 
