@@ -82,6 +82,73 @@ dequant_rows_kernel(const uint32_t* __restrict__ acc, int64_t ld_acc, const floa
     }
 }
 
+// The aligned case (16-byte aligned rows on both sides, N a multiple of 8): a CTA walks whole rows, its threads the
+// 8-column groups of the row, four groups per thread at a time with all eight 16-byte loads requested before the first is
+// used -- 128 bytes per thread in flight instead of 32, no 64-bit division per group, the row scale read once per row.
+// (The general kernel below moved 0.60-0.64 of the copy bandwidth on 8192 x 8192; the pass is 4 bytes in, 2 out.)
+template <bool INT_ACC>
+__global__ void __launch_bounds__(256)
+dequant_rows_fast_kernel(const uint32_t* __restrict__ acc, int64_t ld_acc, const float* __restrict__ sa,
+                         const float* __restrict__ sb, int scale_mode, float alpha, const float* __restrict__ bias,
+                         __nv_bfloat16* __restrict__ d, int64_t ldd, int m, int n) {
+    constexpr int U = 4;
+    const int groups = n >> 3;
+    for (int row = blockIdx.x; row < m; row += gridDim.x) {
+        const float sa_row = scale_mode == 1 ? __ldg(sa + row) : __ldg(sa);
+        const uint4* src = reinterpret_cast<const uint4*>(acc + static_cast<int64_t>(row) * ld_acc);
+        uint4* dst = reinterpret_cast<uint4*>(d + static_cast<int64_t>(row) * ldd);
+        for (int g0 = threadIdx.x; g0 < groups; g0 += U * 256) {
+            uint4 lo[U], hi[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int g = g0 + u * 256;
+                if (g < groups) {
+                    lo[u] = __ldcs(src + 2 * g);
+                    hi[u] = __ldcs(src + 2 * g + 1);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int g = g0 + u * 256;
+                if (g >= groups) break;
+                const uint32_t r[8] = {lo[u].x, lo[u].y, lo[u].z, lo[u].w, hi[u].x, hi[u].y, hi[u].z, hi[u].w};
+                float sbv[8], bv[8];
+                if (scale_mode == 1) {
+                    const float4 s0 = __ldg(reinterpret_cast<const float4*>(sb + 8 * g));
+                    const float4 s1 = __ldg(reinterpret_cast<const float4*>(sb + 8 * g) + 1);
+                    sbv[0] = s0.x; sbv[1] = s0.y; sbv[2] = s0.z; sbv[3] = s0.w;
+                    sbv[4] = s1.x; sbv[5] = s1.y; sbv[6] = s1.z; sbv[7] = s1.w;
+                } else {
+                    const float s = __ldg(sb);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) sbv[j] = s;
+                }
+                if (bias) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + 8 * g));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + 8 * g) + 1);
+                    bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
+                    bv[4] = b1.x; bv[5] = b1.y; bv[6] = b1.z; bv[7] = b1.w;
+                }
+                float y[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // (sa*sb) first, then the accumulator, then alpha: the product order of the fused epilogue
+                    const float s = __fmul_rn(sa_row, sbv[j]);
+                    y[j] = __fmul_rn(__fmul_rn(s, acc_to_float<INT_ACC>(r[j])), alpha);
+                    if (bias) y[j] = __fadd_rn(y[j], bv[j]);
+                }
+                uint4 out;
+                __nv_bfloat162 h;
+                h = __floats2bfloat162_rn(y[0], y[1]); out.x = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(y[2], y[3]); out.y = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(y[4], y[5]); out.z = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(y[6], y[7]); out.w = *reinterpret_cast<uint32_t*>(&h);
+                dst[g] = out;
+            }
+        }
+    }
+}
+
 // The owner of a row block in the fused K-sharded forward: adds the `world` partial-sum slots that the ranks' GEMM
 // epilogues stored into its staging buffer, applies the scales like dequant_rows_kernel, and stores the bf16 rows into
 // every rank's output through peer pointers (plain stores over NVLink, peers visited from rank + 1 on so that no
@@ -239,6 +306,22 @@ int32_t launch_dequant_rows(int32_t kind, int32_t m, int32_t n, const void* acc,
                      (reinterpret_cast<uintptr_t>(d) & 15u) == 0 && ((ldd * 2) & 15) == 0)
                         ? 1
                         : 0;
+    // whole aligned rows of 8-column groups (and 16-byte aligned scale / bias vectors): the row-walking kernel
+    const bool fast = vec && (n % 8) == 0 && (scale_mode != 1 || (reinterpret_cast<uintptr_t>(scale_b) & 15u) == 0) &&
+                      (!bias || (reinterpret_cast<uintptr_t>(bias) & 15u) == 0);
+    if (fast) {
+        const unsigned grid = static_cast<unsigned>(m < sms * 8 ? m : sms * 8);
+        if (kind == BQ_KIND_S8) {
+            dequant_rows_fast_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(acc), ld_acc, scale_a, scale_b,
+                                                                      scale_mode, alpha, bias, static_cast<__nv_bfloat16*>(d),
+                                                                      ldd, m, n);
+        } else {
+            dequant_rows_fast_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint32_t*>(acc), ld_acc, scale_a, scale_b,
+                                                                       scale_mode, alpha, bias, static_cast<__nv_bfloat16*>(d),
+                                                                       ldd, m, n);
+        }
+        return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
+    }
     if (kind == BQ_KIND_S8) {
         dequant_rows_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
             static_cast<const uint32_t*>(acc), ld_acc, scale_a, scale_b, scale_mode, alpha, bias,
