@@ -515,7 +515,7 @@ __device__ __forceinline__ void epilogue_block_64_swiglu(const GemmParams& p, ui
     __syncwarp();
 }
 
-// Raw 32-bit accumulators of a 32-column block, reduce-scatter mode: 32 rows x 128 bytes go through the warp's
+// Raw 32-bit accumulators of a 32-column block (reduce-scatter mode, or the plain raw output): 32 rows x 128 bytes go through the warp's
 // staging buffer (16-byte packet c of row r at stage[r * 8 + (c ^ (r & 7))]) so that every store instruction writes
 // four complete 128-byte row segments -- what stores that cross NVLink need.  Row r of the tile lands in the staging
 // buffer of the rank that owns it (see GemmParams::rs_world).
@@ -540,9 +540,14 @@ __device__ __forceinline__ void epilogue_block_raw32_scatter(const GemmParams& p
         const int row = row_base + rr;
         const uint4 v = stage[rr * 8 + (c ^ (rr & 7))];
         if (row < p.m) {
-            const int owner = row / p.rs_rows;
-            uint32_t* dst = reinterpret_cast<uint32_t*>(p.peer_d[owner]) +
-                            (static_cast<int64_t>(p.peer_rank) * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd + col0 + c * 4;
+            uint32_t* dst;
+            if (p.rs_world > 1) {
+                const int owner = row / p.rs_rows;
+                dst = reinterpret_cast<uint32_t*>(p.peer_d[owner]) +
+                      (static_cast<int64_t>(p.peer_rank) * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd + col0 + c * 4;
+            } else {  // the local raw output, through the same staging: whole 128-byte row segments per store
+                dst = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0 + c * 4;
+            }
             *reinterpret_cast<uint4*>(dst) = v;
         }
     }

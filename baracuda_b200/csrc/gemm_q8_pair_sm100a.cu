@@ -337,7 +337,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         }
                     }
                     if constexpr (RAW) {
-                        if (p.rs_world > 1 && p.vec_store && col0 + 32 <= p.n) {  // warp-uniform
+                        if ((p.rs_world > 1 || p.coalesce) && p.vec_store && col0 + 32 <= p.n) {  // warp-uniform
                             epilogue_block_raw32_scatter(p, t_row + static_cast<uint32_t>(c * 32), row_base, lane, col0, stage_buf);
                             continue;
                         }
@@ -518,6 +518,8 @@ int32_t launch_pair_tn(const GemmDesc& g, cudaStream_t stream, const MixedSchedu
     const int64_t waves = (tiles + pairs - 1) / pairs;
     p.coalesce = (g.direct_stores == 2) || (g.direct_stores == 0 && (FUSED || waves <= 6));
     if (p.out_q8) p.coalesce = 0;  // the staging path is bf16-only
+    // raw 32-bit output: 128 bytes per row and block, always worth staging (8192 x 28672 x 4096: 704 -> 624 us)
+    if (RAW) p.coalesce = g.direct_stores != 1 ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), 1, 1);
     cfg.blockDim = dim3(EW8 ? PAIR_THREADS + 128 : PAIR_THREADS, 1, 1);

@@ -269,7 +269,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                         }
                     }
                     if constexpr (RAW) {
-                        if (p.rs_world > 1 && p.vec_store && col0 + 32 <= p.n) {  // warp-uniform
+                        if ((p.rs_world > 1 || p.coalesce) && p.vec_store && col0 + 32 <= p.n) {  // warp-uniform
                             epilogue_block_raw32_scatter(p, t_row + static_cast<uint32_t>(c * 32), m_blk * BLOCK_M + q * 32, lane, col0, stage_buf);
                             continue;
                         }
@@ -410,6 +410,8 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     const int grid = static_cast<int>(tiles < sms ? tiles : sms);
     p.coalesce = (g.direct_stores == 2) || (g.direct_stores == 0 && (FUSED || (tiles + grid - 1) / grid <= 6));
     if (p.out_q8) p.coalesce = 0;  // the staging path is bf16-only
+    // raw 32-bit output: 128 bytes per row and block, always worth staging (8192 x 28672 x 4096: 704 -> 624 us)
+    if (RAW) p.coalesce = g.direct_stores != 1 ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
