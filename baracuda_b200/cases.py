@@ -2,6 +2,7 @@
 
     python -m baracuda_b200.cases gemv --layout rcr --m 1 --n 14336 --k 4096 --iters 3
     python -m baracuda_b200.cases gemm --kind fp8 --m 8192 --n 8192 --k 4096 --iters 3
+    python -m baracuda_b200.cases quantize --m 8192 --k 4096 --in bf16 --kind s8 --iters 3
 
 Meant as the small, self-terminating command to put under a profiler (one
 kernel, a handful of launches, a few hundred MB on the device) and as a usage
@@ -18,7 +19,7 @@ import baracuda_b200 as bq
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemv", "gemm"])
+    ap.add_argument("kernel", choices=["gemv", "gemm", "quantize"])
     ap.add_argument("--layout", default="rcr", choices=["rcr", "rrr"])
     ap.add_argument("--kind", default="s8", choices=["s8", "fp8"])
     ap.add_argument("--m", type=int, default=1)
@@ -27,6 +28,8 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--buffers", type=int, default=3, help="distinct weight buffers rotated through (defeats L2 reuse)")
     ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--in", dest="in_dtype", default="bf16", choices=["bf16", "f32"],
+                    help="quantize only: the activation type ([m, k] in, --kind s8 or fp8 codes out)")
     ap.add_argument("--epilogue", default="identity", choices=["identity", "bias_gelu", "gated"],
                     help="gemm --kind s8 only: fused bias + gelu, or the gated-MLP epilogue (n counts gate and up rows)")
     a = ap.parse_args()
@@ -39,7 +42,13 @@ def main() -> None:
     sb = torch.rand(n, device="cuda", generator=g)
     d = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
     ws = None
-    if a.kernel == "gemv":
+    if a.kernel == "quantize":
+        dt = torch.bfloat16 if a.in_dtype == "bf16" else torch.float32
+        plan = bq.QuantizePerTokenPlan.select(None, bq.QuantizePerTokenDescriptor(m, k, "s8" if a.kind == "s8" else "e4m3"))
+        xs = [torch.randn(m, k, device="cuda", generator=g).to(dt) for _ in range(a.buffers)]
+        q = torch.empty((m, k), dtype=torch.int8 if a.kind == "s8" else torch.uint8, device="cuda")
+        launch = lambda i: plan.run(None, xs[i % len(xs)], sa, q)
+    elif a.kernel == "gemv":
         layout = bq.LayoutSku.Rcr if a.layout == "rcr" else bq.LayoutSku.Rrr
         plan = bq.GemvQ8Plan.select(None, bq.GemvQ8Descriptor(m, n, k, layout=layout))
         ws = torch.empty(max(plan.workspace_size(), 16), dtype=torch.uint8, device="cuda")
