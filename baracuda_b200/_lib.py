@@ -118,6 +118,12 @@ SIGNATURES: dict[str, tuple] = {
         _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _f32, _vp, _vp, _vp]),
     "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run": (
         _i32, [_i32, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _vp, _f32, _vp, _vp, _vp]),
+    "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_flags_run": (
+        _i32, [_i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _f32, _vp, _vp, _vp]),
+    "baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_flags_run": (
+        _i32, [_i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i32, _vp, _f32, _vp, _vp, _vp]),
+    "baracuda_q_peer_barrier_run": (_i32, [_vp, _i32, _i32, _i64, _vp]),
+    "baracuda_q_peer_barrier_flag_bytes": (_sz, []),
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run": (
         _i32, [_i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _f32] + _TAIL),
     "baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_workspace_size": (_sz, [_i32, _i32, _i32]),

@@ -874,7 +874,9 @@ int32_t baracuda_kernels_q_device_status(void) {
     int32_t gemm = bq::read_and_clear_gemm_device_status();
     const int32_t pair = bq::read_and_clear_gemm_pair_device_status();
     if (gemm == 0) gemm = pair;
-    const int32_t gemv = bq::read_and_clear_gemv_device_status();
+    int32_t gemv = bq::read_and_clear_gemv_device_status();
+    const int32_t barrier = bq::read_and_clear_peer_barrier_device_status();
+    if (gemv == 0) gemv = barrier;
     return gemm != 0 ? gemm : gemv;
 }
 

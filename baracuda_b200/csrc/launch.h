@@ -124,6 +124,10 @@ struct GemvDesc {
     int32_t pdl;      // 1: launch the streaming kernel with programmatic stream serialization
 };
 
+// One-block barrier kernel between the ranks of a box over peer-mapped flag buffers (32 zero-initialised words per rank).
+int32_t launch_peer_flag_barrier(void* const* peer_flags, int32_t rank, int32_t world, long long limit_cycles,
+                                 cudaStream_t stream);
+int32_t read_and_clear_peer_barrier_device_status();
 int32_t launch_gemv_q8(const GemvDesc& g, cudaStream_t stream);
 int32_t read_and_clear_gemv_device_status();
 // Launches one thread that waits on a barrier nothing completes; the wait gives up after limit_cycles and sets status 299.

@@ -168,31 +168,36 @@ int32_t kshard_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_
 int32_t kshard_fused_run(int32_t kind, int32_t rank, int32_t world, void* comm, int32_t m, int32_t n, int32_t k_local,
                          const void* a_local, int64_t lda, const void* b_local, int64_t ldb, void* const* peer_y, int64_t ldy,
                          const void* scale_a, const void* scale_b, int32_t scale_mode, const void* bias, float alpha,
-                         void* const* peer_staging, void* barrier_scratch, void* stream) {
+                         void* const* peer_staging, void* barrier_scratch, void* stream, void* const* peer_flags = nullptr) {
     if (world < 2 || world > BARACUDA_Q_MAX_PEERS || rank < 0 || rank >= world) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     if (m < 0 || n < 0 || k_local < 0 || (m % world) != 0) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     if (ldy < (n > 0 ? n : 1)) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     if (m == 0 || n == 0) return BARACUDA_Q_STATUS_OK;
-    if (!comm || !peer_y || !peer_staging || !barrier_scratch || !scale_a || !scale_b) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (!peer_y || !peer_staging || !scale_a || !scale_b) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    if (!peer_flags && (!comm || !barrier_scratch)) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     if (scale_mode != BARACUDA_Q_SCALE_PER_TENSOR && scale_mode != BARACUDA_Q_SCALE_PER_ROW_COL)
         return BARACUDA_Q_STATUS_INVALID_PROBLEM;
     if (k_local == 0) return BARACUDA_Q_STATUS_UNSUPPORTED;
-    if (!nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
+    if (!peer_flags && !nccl().ok) return BARACUDA_Q_STATUS_COMM_UNAVAILABLE;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the two points where the ranks must meet: a one-float all-reduce, or the flag barrier over peer memory
+    auto meet = [&]() -> int32_t {
+        if (peer_flags) return bq::launch_peer_flag_barrier(peer_flags, rank, world, 0, s);
+        return nccl().AllReduce(barrier_scratch, barrier_scratch, 1, kNcclFloat32, kNcclSum, comm, s) == 0
+                   ? BARACUDA_Q_STATUS_OK
+                   : BARACUDA_Q_STATUS_COMM_FAILURE;
+    };
     int32_t st = bq::launch_gemm_raw_reduce_scatter_checked(kind, m, n, k_local, a_local, lda, b_local, ldb, peer_staging, world,
                                                             rank, s);
     if (st != BARACUDA_Q_STATUS_OK) return st;
     // every rank's partial sums have landed in the owners' staging buffers
-    if (nccl().AllReduce(barrier_scratch, barrier_scratch, 1, kNcclFloat32, kNcclSum, comm, s) != 0)
-        return BARACUDA_Q_STATUS_COMM_FAILURE;
+    if (const int32_t b = meet(); b != BARACUDA_Q_STATUS_OK) return b;
     st = bq::launch_reduce_dequant_broadcast(kind, rank, world, m / world, n, peer_staging[rank],
                                              static_cast<const float*>(scale_a), static_cast<const float*>(scale_b), scale_mode,
                                              alpha, static_cast<const float*>(bias), peer_y, ldy, s);
     if (st != BARACUDA_Q_STATUS_OK) return st;
     // every owner's rows have landed in every rank's output, and the staging buffers may be written again
-    if (nccl().AllReduce(barrier_scratch, barrier_scratch, 1, kNcclFloat32, kNcclSum, comm, s) != 0)
-        return BARACUDA_Q_STATUS_COMM_FAILURE;
-    return BARACUDA_Q_STATUS_OK;
+    return meet();
 }
 
 }  // namespace
@@ -339,5 +344,31 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run(
     return kshard_fused_run(bq::BQ_KIND_E4M3, rank, world, comm, m, n, k_local, a_local, lda, b_local, ldb, peer_y, ldy,
                             scale_a, scale_b, scale_mode, bias, alpha, peer_staging, barrier_scratch, stream);
 }
+
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_flags_run(
+    int32_t rank, int32_t world, int32_t m, int32_t n, int32_t k_local, const void* a_local, int64_t lda,
+    const void* b_local, int64_t ldb, void* const* peer_y, int64_t ldy, const void* scale_a, const void* scale_b,
+    const void* bias, float alpha, void* const* peer_staging, void* const* peer_flags, void* stream) {
+    if (!peer_flags) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    return kshard_fused_run(bq::BQ_KIND_S8, rank, world, nullptr, m, n, k_local, a_local, lda, b_local, ldb, peer_y, ldy,
+                            scale_a, scale_b, BARACUDA_Q_SCALE_PER_ROW_COL, bias, alpha, peer_staging, nullptr, stream,
+                            peer_flags);
+}
+
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_flags_run(
+    int32_t rank, int32_t world, int32_t m, int32_t n, int32_t k_local, const void* a_local, int64_t lda,
+    const void* b_local, int64_t ldb, void* const* peer_y, int64_t ldy, const void* scale_a, const void* scale_b,
+    int32_t scale_mode, const void* bias, float alpha, void* const* peer_staging, void* const* peer_flags, void* stream) {
+    if (!peer_flags) return BARACUDA_Q_STATUS_INVALID_PROBLEM;
+    return kshard_fused_run(bq::BQ_KIND_E4M3, rank, world, nullptr, m, n, k_local, a_local, lda, b_local, ldb, peer_y, ldy,
+                            scale_a, scale_b, scale_mode, bias, alpha, peer_staging, nullptr, stream, peer_flags);
+}
+
+int32_t baracuda_q_peer_barrier_run(void* const* peer_flags, int32_t rank, int32_t world, int64_t limit_cycles, void* stream) {
+    return bq::launch_peer_flag_barrier(peer_flags, rank, world, static_cast<long long>(limit_cycles),
+                                        static_cast<cudaStream_t>(stream));
+}
+
+size_t baracuda_q_peer_barrier_flag_bytes(void) { return 128; }
 
 }  // extern "C"

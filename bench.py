@@ -788,6 +788,21 @@ def main() -> None:
             parity["checked"]["fused_multicast_stores"] = all_ranks_ok(
                 slots_match(lambda g: mc_rm[:, g * n_local:(g + 1) * n_local]) and
                 rows_match(mc_rm[ridx][:, rank * n_local:(rank + 1) * n_local]))
+            # the same step ordered by the flag barrier instead of the one-float all-reduce
+            mflag_buf, mflag_ptrs = par.alloc_peer_flags()
+
+            def mcf_step():
+                mc_plan.forward(None, a_q, sa, w_q, sb, d, peer_ptrs=mc_ptrs, ldd_full=C4_N, multicast_ptr=mc)
+                ctx.flag_barrier(mflag_ptrs)
+
+            barrier()
+            mf_ms = event_time_ms(mcf_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+            barrier()
+            mf_total = max_over_ranks(sum(mf_ms))
+            parity["checked"]["fused_multicast_stores_flag_barrier"] = all_ranks_ok(
+                slots_match(lambda g: mc_rm[:, g * n_local:(g + 1) * n_local]))
+            others["with_fused_multicast_stores_flag_barrier"] = {
+                "TFLOPs": ops_total * len(mf_ms) / (mf_total * 1e-3) / 1e12, "ms_per_step": mf_total / len(mf_ms)}
             others["with_fused_multicast_stores"] = {
                 "TFLOPs": ops_total * len(m_ms) / (m_total * 1e-3) / 1e12, "ms_per_step": m_total / len(m_ms),
                 "layout": "row-major [M, N] on every rank", "nvlink_bytes_out_per_rank": C4_M * n_local * 2,
@@ -833,6 +848,20 @@ def main() -> None:
             rf_total = max_over_ranks(sum(rf_ms))
             parity["checked"]["row_parallel_fused"] = all_ranks_ok(
                 bool(np.array_equal(bits16(y_sym[ridx]), rp_want)) and bool(torch.equal(y_sym, xy)))
+            # the same with the flag barrier over peer memory instead of the two one-float all-reduces per step
+            flag_buf, flag_ptrs = par.alloc_peer_flags()
+            rpg_step = lambda: rpf_plan.forward_fused(None, xa, xsa, xw, xsb, y_ptrs, st_ptrs, peer_flags=flag_ptrs)
+            barrier()
+            rg_ms = event_time_ms(rpg_step, steps=max(3, args.steps // 2), warmup=2, flush=flush)
+            barrier()
+            rg_total = max_over_ranks(sum(rg_ms))
+            parity["checked"]["row_parallel_fused_flag_barrier"] = all_ranks_ok(
+                bool(np.array_equal(bits16(y_sym[ridx]), rp_want)) and bool(torch.equal(y_sym, xy)))
+            others["row_parallel_w8a8_fused_flag_barrier"] = {
+                "shape": [rp_m, rp_n, rp_k], "TOPS": 2.0 * rp_m * rp_n * rp_k * len(rg_ms) / (rg_total * 1e-3) / 1e12,
+                "ms_per_step": rg_total / len(rg_ms),
+                "note": "as row_parallel_w8a8_fused, the ranks meeting through a one-block flag-barrier kernel over peer "
+                        "memory (no NCCL call in the step)"}
             others["row_parallel_w8a8_fused"] = {
                 "shape": [rp_m, rp_n, rp_k], "TOPS": 2.0 * rp_m * rp_n * rp_k * len(rf_ms) / (rf_total * 1e-3) / 1e12,
                 "ms_per_step": rf_total / len(rf_ms),

@@ -639,6 +639,36 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run(
     const void* bias, float alpha,
     void* const* peer_staging, void* barrier_scratch, void* stream);
 
+/* The same fused forward with the two meeting points done by a flag barrier over peer memory instead of the one-float
+ * all-reduce: no communicator, no NCCL.  peer_flags is an array of `world` device pointers valid on this rank, one
+ * flag buffer per rank (baracuda_q_peer_barrier_flag_bytes() bytes each, peer-mapped like the other buffers and
+ * zero-filled ONCE before first use; the barriers keep their own epoch in it).  Every rank must issue the same sequence
+ * of calls on these buffers. */
+int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_flags_run(
+    int32_t rank, int32_t world,
+    int32_t m, int32_t n, int32_t k_local,
+    const void* a_local, int64_t lda, const void* b_local, int64_t ldb,
+    void* const* peer_y, int64_t ldy, const void* scale_a, const void* scale_b,
+    const void* bias, float alpha,
+    void* const* peer_staging, void* const* peer_flags, void* stream);
+int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_flags_run(
+    int32_t rank, int32_t world,
+    int32_t m, int32_t n, int32_t k_local,
+    const void* a_local, int64_t lda, const void* b_local, int64_t ldb,
+    void* const* peer_y, int64_t ldy, const void* scale_a, const void* scale_b, int32_t scale_mode,
+    const void* bias, float alpha,
+    void* const* peer_staging, void* const* peer_flags, void* stream);
+
+/* The barrier itself, a one-block kernel on `stream`: this rank stores its next epoch into its slot of every rank's
+ * flag buffer and waits until every slot of its own buffer has reached it.  Whatever a rank wrote to peer memory on
+ * its stream before the barrier is visible to what every rank launches after it -- the ordering the fused peer-store
+ * modes need once per step (it replaces baracuda_q_nccl_stream_barrier there).  The wait is bounded: after
+ * limit_cycles SM clock cycles (0 = the default of 2^31, about a second) the kernel gives up, the context stays usable
+ * and baracuda_kernels_q_device_status() returns 301 once.  Ranks that share a GPU must not use it: the kernels wait
+ * on one another. */
+int32_t baracuda_q_peer_barrier_run(void* const* peer_flags, int32_t rank, int32_t world, int64_t limit_cycles, void* stream);
+size_t baracuda_q_peer_barrier_flag_bytes(void);
+
 /* Communicator helpers over the run-time-loaded NCCL
  * (Communicator::{new_with_id, all_gather}, crates/baracuda-nccl/src/lib.rs:243-261, 468-489).
  * unique_id writes the 128-byte ncclUniqueId; rank 0 creates it and the caller
@@ -661,7 +691,7 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  * Diagnostics and test hooks (no counterpart in the reference).
  * device_status: synchronous read-and-clear of the word a kernel sets when one
  * of its bounded barrier waits ran out (0 = none; the code names the kernel and
- * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 201..207 streaming GEMVs, 299 the self-test).  Call it after synchronising the stream.
+ * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 201..207 streaming GEMVs, 299 the self-test, 301 the peer barrier).  Call it after synchronising the stream.
  * set_tuning: forces a kernel choice for the CALLING THREAD only (thread-local; other threads' launches are not
  * affected, nothing process-wide is kept), so tests can run every kernel on the same shapes:
  *   key 0  GEMM tile: 0 automatic; 64, 128, 256 = 1-CTA kernel with that N-tile; 512 = the CTA-pair kernel;

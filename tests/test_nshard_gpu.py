@@ -177,6 +177,22 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
                 dist.barrier()
                 check_rp(y_sym, "row-parallel (fused)")
                 assert bq.device_status() == 0
+                # the same with the flag barrier over peer memory instead of the one-float all-reduces: three calls on
+                # stale staging contents, results cleared in between, no communicator involved in the exchange
+                flag_buf, flag_ptrs = par.alloc_peer_flags()
+                for rep in range(3):
+                    y_sym.zero_()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    fplan.forward_fused(None, a_l, dev(sa), w_l, dev(sb), y_ptrs, st_ptrs, bias=dev(bias), peer_flags=flag_ptrs)
+                    torch.cuda.synchronize()
+                    check_rp(y_sym, f"row-parallel (fused, flag barrier, call {rep})")
+                assert bq.device_status() == 0
+                assert int(flag_buf[16].item()) == 6  # two barriers per call, epochs kept in the buffer
+                ctx.flag_barrier(flag_ptrs)
+                torch.cuda.synchronize()
+                assert int(flag_buf[16].item()) == 7 and bq.device_status() == 0
+                dist.barrier()
         ctx.destroy()
         with open(os.path.join(out_dir, f"ok{rank}"), "w") as f:
             f.write("ok")
