@@ -950,6 +950,41 @@ class RowParallelQGemmPlan {
         return status_to_error(st);
     }
 
+    // Both exchanges inside the kernels over peer-mapped memory (no all-reduce of the sums): `peer_y` and `peer_staging`
+    // hold `world` device pointers valid on this rank ([M, N] bf16 results, [world][M / world][N] 32-bit staging).  The
+    // ranks meet twice per call: through the flag barrier when `peer_flags` is given (`world` flag buffers of
+    // baracuda_q_peer_barrier_flag_bytes() bytes, zeroed once; no communicator needed), else through a one-float
+    // all-reduce on `barrier_scratch`.
+    Error forward_fused(void* stream, const RowParallelArgs& x, void* const* peer_y, void* const* peer_staging,
+                        void* const* peer_flags, float* barrier_scratch = nullptr) const {
+        if (!peer_y || !peer_staging || (!peer_flags && !barrier_scratch)) return Error::InvalidProblem;
+        if (ctx_.world < 2 || m_ % ctx_.world != 0) return Error::InvalidProblem;
+        if (x.a_local.len < detail::span_elems(m_, k_local_, k_local_) ||
+            x.w_local.len < detail::span_elems(n_, k_local_, k_local_))
+            return Error::BufferTooSmall;
+        if (x.bias.ptr && x.bias.len < static_cast<size_t>(n_)) return Error::BufferTooSmall;
+        const int64_t ldk = k_local_ > 0 ? k_local_ : 1, ldn = n_ > 0 ? n_ : 1;
+        int32_t st;
+        if (peer_flags) {
+            st = fp8_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_flags_run(
+                            ctx_.rank, ctx_.world, m_, n_, k_local_, x.a_local.ptr, ldk, x.w_local.ptr, ldk, peer_y, ldn,
+                            x.scale_a.ptr, x.scale_b.ptr, static_cast<int32_t>(mode_), x.bias.ptr, x.alpha, peer_staging,
+                            peer_flags, stream)
+                      : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_flags_run(
+                            ctx_.rank, ctx_.world, m_, n_, k_local_, x.a_local.ptr, ldk, x.w_local.ptr, ldk, peer_y, ldn,
+                            x.scale_a.ptr, x.scale_b.ptr, x.bias.ptr, x.alpha, peer_staging, peer_flags, stream);
+        } else {
+            st = fp8_ ? baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_run(
+                            ctx_.rank, ctx_.world, ctx_.comm, m_, n_, k_local_, x.a_local.ptr, ldk, x.w_local.ptr, ldk, peer_y,
+                            ldn, x.scale_a.ptr, x.scale_b.ptr, static_cast<int32_t>(mode_), x.bias.ptr, x.alpha, peer_staging,
+                            barrier_scratch, stream)
+                      : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_run(
+                            ctx_.rank, ctx_.world, ctx_.comm, m_, n_, k_local_, x.a_local.ptr, ldk, x.w_local.ptr, ldk, peer_y,
+                            ldn, x.scale_a.ptr, x.scale_b.ptr, x.bias.ptr, x.alpha, peer_staging, barrier_scratch, stream);
+        }
+        return status_to_error(st);
+    }
+
   private:
     TensorParallelContext ctx_{};
     int32_t m_ = 0, n_ = 0, k_local_ = 0, k0_ = 0;

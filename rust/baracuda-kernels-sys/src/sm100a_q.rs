@@ -374,6 +374,30 @@ extern "C" {
         peer_staging: *const *mut c_void, barrier_scratch: *mut c_void, stream: *mut c_void,
     ) -> i32;
 
+    /// The fused forward with the ranks meeting through a flag barrier over peer memory (no communicator):
+    /// `peer_flags` holds `world` pointers to flag buffers of `baracuda_q_peer_barrier_flag_bytes()` bytes, zeroed once.
+    pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_kshard_fused_flags_run(
+        rank: i32, world: i32,
+        m: i32, n: i32, k_local: i32,
+        a_local: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        peer_y: *const *mut c_void, ldy: i64, scale_a: *const c_void, scale_b: *const c_void,
+        bias: *const c_void, alpha: f32,
+        peer_staging: *const *mut c_void, peer_flags: *const *mut c_void, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_kshard_fused_flags_run(
+        rank: i32, world: i32,
+        m: i32, n: i32, k_local: i32,
+        a_local: *const c_void, lda: i64, b_local: *const c_void, ldb: i64,
+        peer_y: *const *mut c_void, ldy: i64, scale_a: *const c_void, scale_b: *const c_void, scale_mode: i32,
+        bias: *const c_void, alpha: f32,
+        peer_staging: *const *mut c_void, peer_flags: *const *mut c_void, stream: *mut c_void,
+    ) -> i32;
+    /// The barrier itself (one-block kernel on `stream`; bounded wait, `limit_cycles` 0 = about a second; status 301).
+    pub fn baracuda_q_peer_barrier_run(
+        peer_flags: *const *mut c_void, rank: i32, world: i32, limit_cycles: i64, stream: *mut c_void,
+    ) -> i32;
+    pub fn baracuda_q_peer_barrier_flag_bytes() -> usize;
+
     /// Gated-MLP up-projection over an interleaved gate/up weight `[n2, K]`: `D = silu(z_gate) * z_up`, bf16 `[M, n2 / 2]`.
     pub fn baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_swiglu_run(
         m: i32, n2: i32, k: i32,

@@ -268,6 +268,10 @@ int main() {
                                          &rp) == Error::InvalidProblem);
         RowParallelArgs ra;
         CHECK(rp.forward(nullptr, Workspace::none(), ra) == Error::WorkspaceTooSmall);
+        void* fake_ptrs[4] = {fake(0x10000), fake(0x20000), fake(0x30000), fake(0x40000)};
+        CHECK(rp.forward_fused(nullptr, ra, fake_ptrs, fake_ptrs, nullptr, nullptr) == Error::InvalidProblem);  // no way to meet
+        CHECK(rp.forward_fused(nullptr, ra, fake_ptrs, fake_ptrs, fake_ptrs) == Error::BufferTooSmall);  // empty operand views
+        CHECK(baracuda_q_peer_barrier_flag_bytes() == 128);
     }
 
     if (failures == 0) std::printf("plan_host_test ok\n");
