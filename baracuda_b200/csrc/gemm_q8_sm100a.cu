@@ -440,10 +440,33 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     // measured at M = 512, K = 4096..14336 (32 to 48 tiles) the pair kernel is 1.4-1.7x faster than 128 x 64 tiles
     // on every SM, whose operand traffic per MAC is three times higher; at 16 tiles the narrow tiles still win.
     const int64_t pair_tiles = ((g.m + 255) / 256) * static_cast<int64_t>((g.n + 255) / 256);
-    if ((g.force_block_n == 0 && g.m >= 512 && g.n >= 512 && pair_tiles >= 24) || g.force_block_n == 512) {
-        return launch_gemm_q8_pair(g, stream);
-    }
+    const int64_t pairs = sms / 2;
+    bool use_pair = g.force_block_n == 512 || (g.force_block_n == 0 && g.m >= 512 && g.n >= 512 && pair_tiles >= 24);
     int bn = g.force_block_n;
+    if (g.force_block_n == 0) {
+        // One or two row blocks of 256 rows with at least a wave and a half of pair tiles also go to the pair kernel
+        // (256 x 28672 x 4096: 31.0 us against 35.6 us on 128 x 256 tiles).
+        if (!use_pair && g.m >= 256 && g.n >= 512 && (g.m % 256 == 0 || g.m % 256 > 128) && 2 * pair_tiles >= 3 * pairs) {
+            use_pair = true;
+        }
+        // A single, partly filled wave of pair tiles: if 128 x 256 or 128 x 128 tiles fill at least 80 % of the SMs in
+        // ONE wave, they win -- the 1-CTA kernel starts and ends about 2 us sooner (no cluster launch, no pair
+        // hand-shakes): 512 x 4096 x 4096 13.1 against 15.4 us, 1024 x 4096 x 4096 16.5 against 18.7 us,
+        // 512 x 4096 x 14336 33.5 against 38.0 us (CUDA-graph timing).  With less fill the pair kernel's lower operand
+        // traffic wins again (512 x 6144 x 4096: 96 tiles of 128 x 256, 18.3 against 16.7 us).
+        if (use_pair && pair_tiles <= pairs) {
+            const int cand[2] = {256, 128};
+            for (int i = 0; i < 2; ++i) {
+                const int64_t t = tiles_at(cand[i]);
+                if (t <= sms && 5 * t >= 4 * static_cast<int64_t>(sms)) {
+                    use_pair = false;
+                    bn = cand[i];
+                    break;
+                }
+            }
+        }
+    }
+    if (use_pair) return launch_gemm_q8_pair(g, stream);
     if (bn == 0) {
         // the widest tile that still gives every SM a tile; narrow tiles for small problems
         bn = tiles_at(256) >= sms ? 256 : (tiles_at(128) >= sms ? 128 : 64);
