@@ -294,11 +294,7 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, PAIR_WAIT_LIMIT)) {
-                pair_timeout(abort_word, 114);
-                return false;
-            }
-            tc_fence_after_sync();
+            // the row scale is requested before the wait for the accumulator, not after it
             const int row_base = m_blk * PAIR_TILE_M + static_cast<int>(rank) * CTA_ROWS + q * 32;
             const int row = row_base + lane;
             const bool row_ok = row < p.m;
@@ -306,6 +302,11 @@ gemm_q8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (!RAW && !p.out_q8) {
                 sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : (p.scale_mode == 2 ? p.sa_const : __ldg(p.sa));
             }
+            if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, PAIR_WAIT_LIMIT)) {
+                pair_timeout(abort_word, 114);
+                return false;
+            }
+            tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * (PAIR_TMEM_COLS / 2));
             {

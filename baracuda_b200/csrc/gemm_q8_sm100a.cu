@@ -227,17 +227,18 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 __syncwarp();
             }
-            if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, WAIT_LIMIT_CYCLES)) {
-                record_timeout(abort_word, 104);
-                break;
-            }
-            tc_fence_after_sync();
+            // the row scale is requested before the wait for the accumulator, not after it
             const int row = m_blk * BLOCK_M + q * 32 + lane;
             const bool row_ok = row < p.m;
             float sa_row = 1.0f;
             if (!RAW && !p.out_q8) {
                 sa_row = (p.scale_mode == 1) ? (row_ok ? __ldg(p.sa + row) : 0.0f) : (p.scale_mode == 2 ? p.sa_const : __ldg(p.sa));
             }
+            if (!mbar_wait_bounded(&tfull_bar[buf], acc_phase, abort_word, WAIT_LIMIT_CYCLES)) {
+                record_timeout(abort_word, 104);
+                break;
+            }
+            tc_fence_after_sync();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                    static_cast<uint32_t>(buf * BLOCK_N);
             {
