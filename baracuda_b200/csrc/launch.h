@@ -62,7 +62,23 @@ struct GemmDesc {
     // gated-MLP epilogue (bf16 output, weights [N,K] only): n = 2F interleaved gate/up rows in blocks of 32, d is [M, F]
     int32_t swiglu;
     int32_t pdl;  // 1: launch with programmatic stream serialization (the caller promises the previous kernel does not write b)
+    // Optional scratch of the bf16-out GEMMs with [N,K] weights.  With at least gemm_split_k_workspace_bytes(m, n, k)
+    // bytes (16-byte aligned), problems of few output tiles and long K run as K slices on otherwise idle SMs: a raw
+    // GEMM of the slices into the scratch, then a dependent pass that adds them and applies the epilogue.
+    void* workspace;
+    size_t workspace_bytes;
+    int32_t split_k;  // 0 = choose, 1 = never, 2..8 = that many slices if the scratch allows (tuning and tests)
+    // set by the dispatch for the raw GEMM of a split-K launch (d = scratch [m, k_slices * n]); 0 / 1 otherwise
+    int32_t k_slices;
+    int32_t kb_per_slice;
 };
+
+// Scratch that lets launch_gemm_q8 split K for this problem (0: the problem never splits).  Pure host arithmetic.
+size_t gemm_split_k_workspace_bytes(int32_t m, int32_t n, int32_t k);
+// Second pass of a split-K launch: D = epilogue(sum of the `slices` column blocks of g.workspace, [m, slices * n]
+// 32-bit words), everything else (scales, alpha, beta * C, bias, activation, d) as described by g.  Launched as a
+// programmatic dependent of the GEMM in front of it.
+int32_t launch_split_k_reduce(const GemmDesc& g, int32_t slices, cudaStream_t stream);
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);
 // Raw-accumulator GEMM of a K shard whose epilogue scatters the [m, n] partial sums by row block: rows

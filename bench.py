@@ -388,6 +388,29 @@ def side_workloads(peaks: dict) -> dict:
                     "us": t * 1e6, "GBps": byts / t / 1e9, "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
     del weights
 
+    # small batches against the down projection (K = 14336, N = 4096; 32 output tiles): one pass, and with the optional
+    # scratch that lets the GEMM cut K into slices on the idle SMs (raw GEMM + dependent reduce pass); CUDA graph over
+    # six weight buffers, like the GEMV figures above
+    weights = [torch.randint(-127, 128, (n2 * k2,), dtype=torch.int8, device="cuda", generator=g) for _ in range(nbuf)]
+    small = {}
+    for m in (32, 128):
+        x = torch.randint(-127, 128, (m, k2), dtype=torch.int8, device="cuda", generator=g)
+        sa = torch.rand(m, device="cuda", generator=g)
+        sb = torch.rand(n2, device="cuda", generator=g)
+        d = torch.empty((m, n2), dtype=torch.bfloat16, device="cuda")
+        plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n2, k2))
+        scratch = torch.empty(max(plan.split_k_workspace_size(), 16), dtype=torch.uint8, device="cuda")
+        argl = [bq.QGemmArgs(a=x, b=w.view(n2, k2), d=d, scale_a=sa, scale_b=sb) for w in weights]
+        byts = k2 * n2 + m * k2 + m * 4 + n2 * 4 + m * n2 * 2
+        for name, ws in (("one_pass", None), ("split_k", scratch)):
+            launchers = [(lambda i=i: plan.run(None, ws, argl[i % nbuf])) for i in range(2 * nbuf)]
+            t = min(graph_launch_ms(launchers) for _ in range(2)) * 1e-3
+            small[f"M{m}_{name}"] = {"us": t * 1e6, "TOPS": 2.0 * m * n2 * k2 / t / 1e12,
+                                     "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
+        small[f"M{m}_scratch_bytes"] = plan.split_k_workspace_size()
+    out["small_batch_down_proj_w8a8"] = small
+    del weights
+
     def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False, gated: bool = False):
         gen = torch.Generator(device="cuda")
         gen.manual_seed(m + n + k)
