@@ -688,6 +688,8 @@ class QuantizedLinearPlan {
     const KernelSku& sku() const { return skinny_ ? gemv_.sku() : gemm_.sku(); }
     PrecisionGuarantee precision_guarantee() const { return sku().precision_guarantee; }
     size_t workspace_size() const { return skinny_ ? gemv_.workspace_size() : gemm_.workspace_size(); }
+    // Optional scratch of the GEMM behind this layer (0 on the GEMV path): see W8A8GemmPlan::split_k_workspace_size.
+    size_t split_k_workspace_size() const { return skinny_ ? 0 : gemm_.split_k_workspace_size(); }
     // True when the whole step is one launch.
     bool fused_decode(const QuantizedLinearArgs& x) const {
         const int64_t ldk = desc_.k > 0 ? desc_.k : 1, ldn = desc_.c_out > 0 ? desc_.c_out : 1;
