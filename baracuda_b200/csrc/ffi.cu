@@ -17,6 +17,7 @@ struct ThreadTuning {
     int32_t direct_stores = 0;
     int32_t epilogue_warps = 0;
     int32_t split_k = 0;
+    int32_t cluster_split_k = 0;
 };
 thread_local ThreadTuning t_tuning;
 
@@ -164,6 +165,7 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.workspace = workspace;  // optional: enables the split-K path for problems of few tiles
     g.workspace_bytes = workspace ? workspace_bytes : 0;
     g.split_k = t_tuning.split_k;
+    g.cluster_split_k = t_tuning.cluster_split_k;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 
@@ -265,6 +267,7 @@ int32_t gemm_q8_run(int32_t layout, int32_t kind, int32_t m, int32_t n, int32_t 
     epilogue_apply(epi, g);
     g.direct_stores = 1;
     g.epilogue_warps = t_tuning.epilogue_warps;
+    g.cluster_split_k = t_tuning.cluster_split_k;
     g.n_peers = 0;
     g.peer_ld = 0;
     g.peer_col0 = 0;
@@ -872,6 +875,8 @@ int32_t baracuda_kernels_q_device_status(void) {
     int32_t gemm = bq::read_and_clear_gemm_device_status();
     const int32_t pair = bq::read_and_clear_gemm_pair_device_status();
     if (gemm == 0) gemm = pair;
+    const int32_t splitk = bq::read_and_clear_gemm_splitk_device_status();
+    if (gemm == 0) gemm = splitk;
     int32_t gemv = bq::read_and_clear_gemv_device_status();
     const int32_t barrier = bq::read_and_clear_peer_barrier_device_status();
     if (gemv == 0) gemv = barrier;
@@ -909,6 +914,10 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
         case 6:
             if (value < 0 || value > 8) return bq::BQ_STATUS_INVALID_PROBLEM;
             t_tuning.split_k = value;
+            return bq::BQ_STATUS_OK;
+        case 7:
+            if (value != 0 && value != 1 && value != 2 && value != 4) return bq::BQ_STATUS_INVALID_PROBLEM;
+            t_tuning.cluster_split_k = value;
             return bq::BQ_STATUS_OK;
         case 2:
             if (value != 0 && value != 2 && value != 256 && value != 224 && value != 192 && value != 128)

@@ -538,11 +538,49 @@ int split_k_slices(const GemmDesc& g, int sms) {
     return s < 2 ? 1 : static_cast<int>(s);
 }
 
+// Split-K inside a cluster (no scratch): slices of this launch, 0 = none.  Same model as split_k_rule with the smaller
+// fixed cost of the in-kernel exchange; all clusters must be resident at once.
+constexpr float CLUSTER_SPLIT_FIXED_US = 1.0f;
+
+int cluster_split_slices(const GemmDesc& g, int sms) {
+    if (g.cluster_split_k == 1 || g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.force_block_n != 0 ||
+        g.b_layout != BQ_LAYOUT_RCR) {
+        return 0;
+    }
+    const int64_t num_kb = (static_cast<int64_t>(g.k) + BLOCK_K - 1) / BLOCK_K;
+    const int64_t tiles = ((static_cast<int64_t>(g.m) + BLOCK_M - 1) / BLOCK_M) * ((static_cast<int64_t>(g.n) + 127) / 128);
+    if (g.cluster_split_k == 2 || g.cluster_split_k == 4) {
+        const int s = g.cluster_split_k;
+        const int64_t kbps = (num_kb + s - 1) / s;
+        return (num_kb >= s && (num_kb + kbps - 1) / kbps == s && gemm_q8_cluster_split_k_max_clusters(g.kind, s) > 0) ? s : 0;
+    }
+    if (num_kb < SPLIT_MIN_KB || 2 * tiles > sms) return 0;
+    const float hbm = static_cast<float>(g.n) * static_cast<float>(g.k) / HBM_BYTES_PER_US;
+    float best = one_pass_cost(g.m, g.n, g.k, sms, true, nullptr) - 1.0f;
+    int best_s = 0;
+    for (int s = 2; s <= 4; s += 2) {
+        const int64_t kbps = (num_kb + s - 1) / s;
+        if (s * tiles > sms || kbps < 4 || (num_kb + kbps - 1) / kbps != s) continue;
+        if (tiles > gemm_q8_cluster_split_k_max_clusters(g.kind, s)) continue;
+        const float walk = static_cast<float>(kbps) * COST_KB_128;
+        const float c = (walk > hbm ? walk : hbm) + CLUSTER_SPLIT_FIXED_US;
+        if (c < best) {
+            best = c;
+            best_s = s;
+        }
+    }
+    return best_s;
+}
+
 template <uint32_t KIND, bool RAW>
 int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     const int sms = sm_count_impl();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     if constexpr (!RAW) {
+        if (g.split_k < 2) {  // a forced scratch split goes first
+            const int cs = cluster_split_slices(g, sms);
+            if (cs > 1) return launch_gemm_q8_cluster_split_k(g, cs, stream);
+        }
         const int want = split_k_slices(g, sms);
         if (want > 1) {
             const int num_kb = (g.k + BLOCK_K - 1) / BLOCK_K;

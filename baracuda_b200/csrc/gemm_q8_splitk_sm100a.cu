@@ -1,0 +1,446 @@
+// Split-K form of the 8-bit tensor-core GEMM for problems of few output tiles (small batches against one layer's
+// weight): a thread-block cluster of S CTAs (S = 2 or 4) shares one 128 x 128 output tile, CTA s of the cluster
+// multiplies K slice s, and the partial sums meet through distributed shared memory -- no scratch in global memory,
+// no second launch.
+//
+// Per CTA (six warps, the roles of gemm_q8_kernel): warp 0 streams its slice's A and B tiles through a ring of
+// shared-memory stages by TMA, warp 1 issues tcgen05.mma into one TMEM accumulator, warps 2-5 (thread = output row)
+// then run the exchange: the tile's 128 columns are cut into S strips, CTA j owns strip j; every CTA stores its partial
+// sums of the strips it does not own into the owners' receive buffers (st.shared::cluster, column-major so that a warp
+// writes 128 contiguous bytes), the cluster meets at its hardware barrier, and every CTA adds what it received to its
+// own strip (int32 adds; f32 adds in slice order), applies the fused epilogue of the one-pass kernel
+// (epilogue_store_32: scales, alpha, beta * C, bias, activation, bf16 or 8-bit output) and stores 128 rows x 128 / S
+// columns.  Every mbarrier wait is bounded; a wait that runs out records a status word, and the CTA still walks to
+// the cluster barrier so that its partners are released.
+//
+// Replaces, for these shapes, the same reference kernels as gemm_q8_sm100a.cu
+//   crates/baracuda-cutlass-kernels-sys/kernels/gemm_s8_rcr_sm80.cu:48-198
+//   crates/baracuda-kernels-sys/kernels/include/baracuda_fp8_rcr_sm89.cuh:102-323
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "gemm_q8_common.cuh"
+#include "launch.h"
+#include "ptx_sm100a.cuh"
+
+namespace bq {
+
+__device__ int g_gemm_splitk_device_status = 0;
+
+namespace {
+
+constexpr int SK_BLOCK_M = 128;
+constexpr int SK_BLOCK_N = 128;
+constexpr int SK_BLOCK_K = 128;  // bytes of K per stage == one 128-byte swizzle row
+constexpr int SK_UMMA_K = 32;
+constexpr int SK_THREADS = 192;
+constexpr int SK_STAGES = 5;
+constexpr long long SK_WAIT_LIMIT = 1LL << 31;  // about a second
+
+template <int S>
+struct SkSmem {
+    static constexpr int A_BYTES = SK_BLOCK_M * SK_BLOCK_K;
+    static constexpr int B_BYTES = SK_BLOCK_N * SK_BLOCK_K;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TILE_BYTES = SK_STAGES * STAGE_BYTES;
+    static constexpr int STRIP = SK_BLOCK_N / S;                 // columns a CTA owns
+    static constexpr int SRC_WORDS = SK_BLOCK_M * STRIP;         // one partner's partial sums of that strip
+    static constexpr int RECV_BYTES = (S - 1) * SRC_WORDS * 4;
+    static constexpr int SB_BYTES = 2 * 4 * SK_BLOCK_N * 4;      // column scales and bias, one private copy per epilogue warp
+    static constexpr int BAR_BYTES = (2 * SK_STAGES + 1) * 8 + 16;
+    static constexpr int TOTAL = TILE_BYTES + RECV_BYTES + SB_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void sk_timeout(volatile uint32_t* abort_word, int code) {
+    *abort_word = 1u;
+    atomicCAS(&g_gemm_splitk_device_status, 0, code);
+}
+
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+template <uint32_t KIND, int S>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+gemm_q8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const GemmParams p) {
+    using L = SkSmem<S>;
+    extern __shared__ uint8_t sk_smem_raw[];
+    // every CTA of the cluster rounds up by the same amount (same kernel, same static layout), so an offset into this
+    // CTA's window is the same offset in a partner's
+    uint8_t* smem = sk_smem_raw + ((1024u - (smem_u32(sk_smem_raw) & 1023u)) & 1023u);
+    uint8_t* tiles = smem;
+    uint32_t* recv = reinterpret_cast<uint32_t*>(smem + L::TILE_BYTES);
+    float* sb_s = reinterpret_cast<float*>(smem + L::TILE_BYTES + L::RECV_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::TILE_BYTES + L::RECV_BYTES + L::SB_BYTES);
+    uint64_t* empty_bar = full_bar + SK_STAGES;
+    uint64_t* tfull_bar = empty_bar + SK_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull_bar + 1);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int slice = static_cast<int>(cluster_ctarank());
+    const int tile = static_cast<int>(blockIdx.x) / S;  // clusters are consecutive groups of S CTAs along x
+    const int m_blk = tile % p.m_tiles;
+    const int n_blk = tile / p.m_tiles;
+    const int num_kb = (p.k + SK_BLOCK_K - 1) / SK_BLOCK_K;
+    const int kb0 = slice * p.kb_per_slice;
+    int nk = num_kb - kb0;
+    if (nk > p.kb_per_slice) nk = p.kb_per_slice;
+    if (nk < 0) nk = 0;  // an empty slice contributes zeros (the host sizes the slices so that none is empty)
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SK_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_word = 0u;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, SK_BLOCK_N);
+        tmem_relinquish_alloc_permit();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    // every CTA of the cluster is running (and its shared memory live) before anyone may store into it
+    cluster_sync_all();
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    uint32_t own[L::STRIP];  // epilogue threads: this CTA's partial sums of its own strip, later the totals
+    float sa_row = 1.0f;
+    const int q = warp & 3;  // TMEM lane quarter an epilogue warp may read
+    const int row_local = q * 32 + lane;
+    const int row = m_blk * SK_BLOCK_M + row_local;
+    float* sb_tile = sb_s + (warp >= 2 ? warp - 2 : 0) * SK_BLOCK_N;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int first = 0;
+            if (p.pdl) {
+                // dependent launch: the first ring of (static) weight tiles is requested while the previous kernel of
+                // the stream is still finishing; the activations follow once it has completed
+                first = nk < SK_STAGES ? nk : SK_STAGES;
+                for (int i = 0; i < first; ++i) {
+                    mbar_arrive_expect_tx(&full_bar[i], L::STAGE_BYTES);
+                    tma_load_2d(tiles + i * L::STAGE_BYTES + L::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * SK_BLOCK_K,
+                                n_blk * SK_BLOCK_N);
+                }
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                for (int i = 0; i < first; ++i) {
+                    tma_load_2d(tiles + i * L::STAGE_BYTES, &tmap_a, &full_bar[i], (kb0 + i) * SK_BLOCK_K, m_blk * SK_BLOCK_M);
+                }
+            }
+            for (int i = first; i < nk; ++i) {
+                const int stage = i % SK_STAGES;
+                const uint32_t phase = static_cast<uint32_t>(i / SK_STAGES) & 1u;
+                if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_word, SK_WAIT_LIMIT)) {
+                    sk_timeout(abort_word, 121);
+                    break;
+                }
+                uint8_t* st = tiles + stage * L::STAGE_BYTES;
+                mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+                tma_load_2d(st, &tmap_a, &full_bar[stage], (kb0 + i) * SK_BLOCK_K, m_blk * SK_BLOCK_M);
+                tma_load_2d(st + L::A_BYTES, &tmap_b, &full_bar[stage], (kb0 + i) * SK_BLOCK_K, n_blk * SK_BLOCK_N);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(KIND, SK_BLOCK_M, SK_BLOCK_N);
+            bool ok = true;
+            for (int i = 0; i < nk; ++i) {
+                const int stage = i % SK_STAGES;
+                const uint32_t phase = static_cast<uint32_t>(i / SK_STAGES) & 1u;
+                if (!mbar_wait_bounded(&full_bar[stage], phase, abort_word, SK_WAIT_LIMIT)) {
+                    sk_timeout(abort_word, 122);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a_addr = smem_u32(tiles + stage * L::STAGE_BYTES);
+                const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
+                const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::A_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < SK_BLOCK_K / SK_UMMA_K; ++ks) {
+                    const uint64_t koff = static_cast<uint64_t>((ks * SK_UMMA_K) >> 4);
+                    umma_ss<KIND>(tmem_base, a_desc + koff, b_desc + koff, idesc, (i | ks) != 0 ? 1u : 0u);
+                }
+                umma_commit(&empty_bar[stage]);
+            }
+            if (ok && nk > 0) umma_commit(tfull_bar);
+        }
+    } else {
+        if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");  // scales, C and D belong to the stream's past
+        // this warp's private copy of the tile's column scales and bias (no barrier between the epilogue warps)
+        if (!p.out_q8 || p.bias_kind != 0) {
+            float sv[SK_BLOCK_N / 32], bv[SK_BLOCK_N / 32];
+#pragma unroll
+            for (int j = 0; j < SK_BLOCK_N / 32; ++j) {
+                const int col = n_blk * SK_BLOCK_N + j * 32 + lane;
+                const bool in = col < p.n;
+                sv[j] = 0.0f;
+                bv[j] = 0.0f;
+                if (!p.out_q8) sv[j] = (p.scale_mode != 0) ? (in ? __ldg(p.sb + col) : 0.0f) : __ldg(p.sb);
+                if (p.bias_kind == 1) {
+                    if (in) bv[j] = __ldg(reinterpret_cast<const float*>(p.bias) + col);
+                } else if (p.bias_kind == 2) {
+                    if (in) bv[j] = static_cast<float>(__ldg(reinterpret_cast<const int32_t*>(p.bias) + col));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < SK_BLOCK_N / 32; ++j) {
+                if (!p.out_q8) sb_tile[j * 32 + lane] = sv[j];
+                if (p.bias_kind != 0) sb_tile[p.bias_off + j * 32 + lane] = bv[j];
+            }
+            __syncwarp();
+        }
+        if (!p.out_q8) {
+            sa_row = (p.scale_mode == 1) ? (row < p.m ? __ldg(p.sa + row) : 0.0f) : (p.scale_mode == 2 ? p.sa_const : __ldg(p.sa));
+        }
+        bool have = nk > 0;
+        if (have && !mbar_wait_bounded(tfull_bar, 0u, abort_word, SK_WAIT_LIMIT)) {
+            sk_timeout(abort_word, 123);
+            have = false;
+        }
+        tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        // the strips of the partners, nearest partner first so that no CTA is everyone's target at once
+#pragma unroll 1
+        for (int dj = 1; dj < S; ++dj) {
+            const int dst = (slice + dj) % S;
+            const int slot = slice < dst ? slice : slice - 1;  // a receive buffer holds the S - 1 partners in rank order
+            const uint32_t remote = map_to_cta(smem_u32(recv), static_cast<uint32_t>(dst)) +
+                                    static_cast<uint32_t>(slot * L::SRC_WORDS * 4);
+#pragma unroll
+            for (int cb = 0; cb < L::STRIP / 32; ++cb) {
+                uint32_t r[32];
+                if (have) {
+                    __syncwarp();
+                    tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(dst * L::STRIP + cb * 32), r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) r[c] = 0u;
+                }
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    st_cluster_u32(remote + static_cast<uint32_t>(((cb * 32 + c) * SK_BLOCK_M + row_local) * 4), r[c]);
+                }
+            }
+        }
+#pragma unroll
+        for (int cb = 0; cb < L::STRIP / 32; ++cb) {
+            uint32_t r[32];
+            if (have) {
+                __syncwarp();
+                tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(slice * L::STRIP + cb * 32), r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = 0u;
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) own[cb * 32 + c] = r[c];
+        }
+        tc_fence_before_sync();
+    }
+
+    // all partial sums have been stored (release) -- and are visible after the wait (acquire).  Every thread of every
+    // CTA of the cluster comes here, also after a time-out.
+    __syncwarp();
+    cluster_sync_all();
+
+    if (warp >= 2) {
+#pragma unroll
+        for (int cb = 0; cb < L::STRIP / 32; ++cb) {
+            uint32_t r[32];
+            if constexpr (KIND == UMMA_KIND_I8) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = own[cb * 32 + c];
+#pragma unroll
+                for (int src = 0; src < S - 1; ++src) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) r[c] += recv[src * L::SRC_WORDS + (cb * 32 + c) * SK_BLOCK_M + row_local];
+                }
+            } else {
+                // f32: slices added in slice order, this CTA's own sum at its place
+                float f[32];
+#pragma unroll
+                for (int s = 0; s < S; ++s) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const uint32_t bits = (s == slice) ? own[cb * 32 + c]
+                                                           : recv[(s < slice ? s : s - 1) * L::SRC_WORDS + (cb * 32 + c) * SK_BLOCK_M + row_local];
+                        f[c] = (s == 0) ? __uint_as_float(bits) : __fadd_rn(f[c], __uint_as_float(bits));
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(f[c]);
+            }
+            const int local_col = slice * L::STRIP + cb * 32;
+            const int col0 = n_blk * SK_BLOCK_N + local_col;
+            if (row < p.m && col0 < p.n && *abort_word == 0u) {
+                epilogue_store_32<KIND, false, false>(p, row, col0, r, sa_row, sb_tile + local_col);
+            }
+        }
+    }
+
+    // Teardown.  On the error path give copies and MMAs still in flight a bounded time to land before TMEM goes back.
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_word != 0u) {
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, SK_BLOCK_N);
+    }
+}
+
+template <uint32_t KIND, int S>
+int32_t launch_splitk(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, int* max_clusters_out) {
+    using L = SkSmem<S>;
+    auto kern = gemm_q8_splitk_kernel<KIND, S>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    const int m_tiles = (g.m + SK_BLOCK_M - 1) / SK_BLOCK_M;
+    const int n_tiles = (g.n + SK_BLOCK_N - 1) / SK_BLOCK_N;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(m_tiles * n_tiles * S), 1, 1);
+    cfg.blockDim = dim3(SK_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    if (max_clusters_out) {  // how many clusters of this kernel the device holds at once (a host query, no launch)
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        *max_clusters_out = n;
+        return BQ_STATUS_OK;
+    }
+    cfg.numAttrs = g.pdl ? 2 : 1;
+    CUtensorMap map_a, map_b;
+    if (!make_kmajor_tensor_map(&map_a, g.a, g.m, g.k, g.lda, SK_BLOCK_M)) return BQ_STATUS_LAUNCH_FAILURE;
+    if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, SK_BLOCK_N)) return BQ_STATUS_LAUNCH_FAILURE;
+    GemmParams p;
+    p.d = g.d;
+    p.ldd = g.ldd;
+    p.sa = g.scale_a;
+    p.sb = g.scale_b;
+    p.scale_mode = g.scale_mode;
+    p.sa_const = g.sa_const;
+    p.alpha = g.alpha;
+    p.m = g.m;
+    p.n = g.n;
+    p.k = g.k;
+    p.m_tiles = m_tiles;
+    p.n_tiles = n_tiles;
+    const int64_t elem = g.q8_out ? 1 : 2;
+    p.vec_store = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * elem) & 15) == 0) ? 1 : 0;
+    for (auto& pd : p.peer_d) pd = nullptr;
+    p.mc_d = nullptr;
+    p.n_peers = 0;
+    p.peer_ld = 0;
+    p.peer_col0 = 0;
+    p.peer_vec = 0;
+    p.peer_rank = 0;
+    p.coalesce = 0;
+    p.out_q8 = g.q8_out;
+    p.c = g.c;
+    p.ldc = g.ldc;
+    p.beta = g.beta;
+    p.bias = g.bias;
+    p.bias_kind = g.bias ? g.bias_kind : 0;
+    p.act = g.act;
+    p.bias_off = 4 * SK_BLOCK_N;
+    p.rs_world = 0;
+    p.rs_rows = 0;
+    p.swiglu = 0;
+    p.mixed = 0;
+    p.mixed_full_cols = 0;
+    p.raster_gm = 1;
+    p.pdl = g.pdl;
+    p.k_slices = S;
+    p.kb_per_slice = kb_per_slice;
+    p.n_tiles_real = n_tiles;
+    if (cudaLaunchKernelEx(&cfg, kern, map_a, map_b, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return BQ_STATUS_LAUNCH_FAILURE;
+    }
+    return BQ_STATUS_OK;
+}
+
+template <int S>
+int32_t launch_splitk_kind(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, int* max_clusters_out) {
+    return g.kind == BQ_KIND_S8 ? launch_splitk<UMMA_KIND_I8, S>(g, kb_per_slice, stream, max_clusters_out)
+                                : launch_splitk<UMMA_KIND_F8, S>(g, kb_per_slice, stream, max_clusters_out);
+}
+
+}  // namespace
+
+int32_t launch_gemm_q8_cluster_split_k(const GemmDesc& g, int32_t slices, cudaStream_t stream) {
+    if (slices != 2 && slices != 4) return BQ_STATUS_INVALID_PROBLEM;
+    if (g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.b_layout != BQ_LAYOUT_RCR || g.k <= 0) {
+        return BQ_STATUS_INVALID_PROBLEM;
+    }
+    const int num_kb = (g.k + SK_BLOCK_K - 1) / SK_BLOCK_K;
+    if (num_kb < slices) return BQ_STATUS_INVALID_PROBLEM;
+    const int kb_per_slice = (num_kb + slices - 1) / slices;
+    if ((num_kb + kb_per_slice - 1) / kb_per_slice != slices) return BQ_STATUS_INVALID_PROBLEM;  // an empty slice
+    return slices == 2 ? launch_splitk_kind<2>(g, kb_per_slice, stream, nullptr)
+                       : launch_splitk_kind<4>(g, kb_per_slice, stream, nullptr);
+}
+
+int gemm_q8_cluster_split_k_max_clusters(int32_t kind, int32_t slices) {
+    if (slices != 2 && slices != 4) return 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    static int cache[64][2][2];  // [device][kind][slices == 4]; 0 = not asked yet, -1 = none
+    int& c = cache[dev][kind == BQ_KIND_S8 ? 0 : 1][slices == 4 ? 1 : 0];
+    if (c == 0) {
+        GemmDesc g = {};
+        g.kind = kind;
+        g.m = SK_BLOCK_M;
+        g.n = SK_BLOCK_N;
+        g.k = SK_BLOCK_K;
+        int n = 0;
+        (void)(slices == 2 ? launch_splitk_kind<2>(g, 1, nullptr, &n) : launch_splitk_kind<4>(g, 1, nullptr, &n));
+        c = n > 0 ? n : -1;
+    }
+    return c > 0 ? c : 0;
+}
+
+int32_t read_and_clear_gemm_splitk_device_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_splitk_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        int zero = 0;
+        (void)cudaMemcpyToSymbol(g_gemm_splitk_device_status, &zero, sizeof(int));
+    }
+    return v;
+}
+
+}  // namespace bq

@@ -68,6 +68,7 @@ struct GemmDesc {
     void* workspace;
     size_t workspace_bytes;
     int32_t split_k;  // 0 = choose, 1 = never, 2..8 = that many slices if the scratch allows (tuning and tests)
+    int32_t cluster_split_k;  // split-K inside a thread-block cluster: 0 = choose, 1 = never, 2 / 4 = that many slices
     // set by the dispatch for the raw GEMM of a split-K launch (d = scratch [m, k_slices * n]); 0 / 1 otherwise
     int32_t k_slices;
     int32_t kb_per_slice;
@@ -79,6 +80,13 @@ size_t gemm_split_k_workspace_bytes(int32_t m, int32_t n, int32_t k);
 // 32-bit words), everything else (scales, alpha, beta * C, bias, activation, d) as described by g.  Launched as a
 // programmatic dependent of the GEMM in front of it.
 int32_t launch_split_k_reduce(const GemmDesc& g, int32_t slices, cudaStream_t stream);
+// Split-K without scratch: clusters of `slices` (2 or 4) CTAs share a 128 x 128 tile and add their partial sums through
+// distributed shared memory (gemm_q8_splitk_sm100a.cu).  bf16 or 8-bit output, [N,K] weights, any M and N;
+// every slice needs at least one K block.
+int32_t launch_gemm_q8_cluster_split_k(const GemmDesc& g, int32_t slices, cudaStream_t stream);
+// Clusters of that kernel the current device holds at once (0: cannot run); cached per device.
+int gemm_q8_cluster_split_k_max_clusters(int32_t kind, int32_t slices);
+int32_t read_and_clear_gemm_splitk_device_status();
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);
 // Raw-accumulator GEMM of a K shard whose epilogue scatters the [m, n] partial sums by row block: rows

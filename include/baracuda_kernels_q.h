@@ -701,7 +701,7 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  * Diagnostics and test hooks (no counterpart in the reference).
  * device_status: synchronous read-and-clear of the word a kernel sets when one
  * of its bounded barrier waits ran out (0 = none; the code names the kernel and
- * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 201..207 streaming GEMVs, 299 the self-test, 301 the peer barrier).  Call it after synchronising the stream.
+ * the waiting role: 101..104 1-CTA GEMM, 111..115 CTA-pair GEMM, 121..123 cluster split-K GEMM, 201..207 streaming GEMVs, 299 the self-test, 301 the peer barrier).  Call it after synchronising the stream.
  * set_tuning: forces a kernel choice for the CALLING THREAD only (thread-local; other threads' launches are not
  * affected, nothing process-wide is kept), so tests can run every kernel on the same shapes:
  *   key 0  GEMM tile: 0 automatic; 64, 128, 256 = 1-CTA kernel with that N-tile; 512 = the CTA-pair kernel;
@@ -710,6 +710,8 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128; 2 = the mixed 256 / 128 schedule;
  *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
  *   key 5  CTA-pair GEMM epilogue warps: 0 automatic (eight for gelu / silu chains on at most two waves of tiles), 4, 8.
+ *   key 7  split-K inside thread-block clusters (no scratch; bf16-out and 8-bit-out GEMMs with [N,K] weights): 0 automatic,
+ *          1 never, 2 or 4 = that many K slices on any shape with at least that many 128-byte K blocks.
  *   key 6  split-K of the bf16-out GEMMs with [N,K] weights when a scratch is passed: 0 automatic, 1 never, 2..8 that
  *          many K slices on any shape with N a multiple of 128 (as far as the scratch holds m * n * 4 bytes per slice).
  * Any other key or value returns 2.

@@ -15,12 +15,14 @@ from helpers import bf16_bits, dev, fp8_case, w8a8_case
 pytestmark = pytest.mark.gpu
 
 KEY_SPLIT_K = 6
+KEY_CLUSTER_SPLIT_K = 7
 
 
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
     bq.set_tuning(KEY_SPLIT_K, 0)
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, 0)
 
 
 def _scratch(nbytes):
@@ -161,6 +163,116 @@ def test_split_k_in_a_cuda_graph(oracle):
     with torch.cuda.stream(stream):
         with torch.cuda.graph(graph, stream=stream):
             plan.run(stream, ws, args)
+    a_d.copy_(dev(aq2))
+    sa_d.copy_(dev(sa2))
+    d.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq2, wq, oracle.RCR, m, n, k), sa2, sb)
+    assert oracle.compare_bitexact(want, bf16_bits(d).reshape(m, n)) == -1
+
+
+# ---- split-K inside thread-block clusters (partial sums exchanged through distributed shared memory, no scratch) ----
+
+@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("shape", [(128, 1024, 4096), (16, 1024, 2048), (200, 520, 2240), (77, 100, 1024), (300, 136, 640)])
+def test_cluster_split_w8a8_matches_oracle(oracle, shape, slices):
+    """Ragged M (partly empty row blocks), N that ends inside a tile and inside a 32-column block, an odd output pitch
+    (N = 100: scalar stores), a K tail (2240 = 17.5 K blocks) and slices of unequal length (640 = 5 K blocks)."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n + k + slices)
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, slices)
+    got = _w8a8(m, n, k, dev(aq), dev(wq), dev(sa), dev(sb), None)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
+
+
+@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("epilogue", [bq.EpilogueKind.Bias, bq.EpilogueKind.BiasRelu, bq.EpilogueKind.BiasGelu,
+                                      bq.EpilogueKind.BiasSilu])
+def test_cluster_split_epilogue_chain_equals_the_one_pass_bits(oracle, epilogue, slices):
+    m, n, k = 96, 1024, 4096
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=13)
+    rng = np.random.default_rng(6)
+    bias = dev(rng.standard_normal(n).astype(np.float32))
+    c = dev(rng.standard_normal((m, n)).astype(np.float32)).to(torch.bfloat16)
+    ops = [dev(aq), dev(wq), dev(sa), dev(sb)]
+    kw = dict(epilogue=epilogue, bias=bias, c=c, beta=0.5, alpha=0.75)
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, 1)
+    one_pass = _w8a8(m, n, k, *ops, None, **kw)
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, slices)
+    split = _w8a8(m, n, k, *ops, None, **kw)
+    assert torch.equal(split.view(torch.int16), one_pass.view(torch.int16))
+    split_pdl = _w8a8(m, n, k, *ops, None, dependent=True, **kw)
+    assert torch.equal(split_pdl.view(torch.int16), one_pass.view(torch.int16))
+
+
+@pytest.mark.parametrize("slices", [2, 4])
+def test_cluster_split_8bit_output_with_bias_and_c(oracle, slices):
+    """The reference's own contract, D = sat_s8(alpha * acc + beta * C + bias), on the cluster kernel."""
+    m, n, k = 100, 392, 2048
+    rng = np.random.default_rng(31)
+    a = rng.integers(-7, 8, size=(m, k), dtype=np.int8)
+    b = rng.integers(-6, 7, size=(n, k), dtype=np.int8)
+    c = rng.integers(-100, 101, size=(m, n), dtype=np.int8)
+    bias = rng.integers(-40, 41, size=n).astype(np.int32)
+    alpha, beta = np.float32(0.03125), np.float32(0.5)
+    want = oracle.int_gemm_s8_out(a, b, oracle.RCR, m, n, k, alpha, beta=beta, c=c, bias=bias)
+    lib = _lib.load()
+    d = torch.full((m, n), 99, dtype=torch.int8, device="cuda")
+    ad, bd, cd, biasd = dev(a), dev(b), dev(c), dev(bias)
+    outs = {}
+    for mode in (1, slices):
+        bq.set_tuning(KEY_CLUSTER_SPLIT_K, mode)
+        st = lib.baracuda_kernels_gemm_s8_rcr_sm100a_bias_i32_run(
+            m, n, k, ad.data_ptr(), k, bd.data_ptr(), k, cd.data_ptr(), n, d.data_ptr(), n, biasd.data_ptr(),
+            float(alpha), float(beta), None, 0, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+        torch.cuda.synchronize()
+        assert bq.device_status() == 0
+        outs[mode] = d.cpu().numpy().copy()
+    assert np.array_equal(outs[slices], want)
+    assert np.array_equal(outs[slices], outs[1])
+
+
+@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("mode", ["per_row_col", "per_tensor"])
+def test_cluster_split_fp8_within_tolerance(oracle, mode, slices):
+    m, n, k = 128, 640, 4096
+    per_tensor = mode == "per_tensor"
+    aq, wq, sa, sb = fp8_case(oracle, m, n, k, seed=19, per_tensor=per_tensor)
+    scale_mode = bq.SCALE_PER_TENSOR if per_tensor else bq.SCALE_PER_ROW_COL
+    plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), scale_mode=scale_mode)
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, slices)
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    plan.run(None, None, bq.QGemmArgs(a=dev(aq), b=dev(wq), d=d, scale_a=dev(sa), scale_b=dev(sb)))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    acc = oracle.gemm_e4m3_f32(aq, wq, oracle.RCR, m, n, k)
+    want = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(acc, sa, sb))
+    got = d.to(torch.float32).cpu().numpy()
+    assert oracle.compare_tolerant(want, got, 1e-2, 1e-4 * float(np.abs(want).max())) == -1
+
+
+def test_cluster_split_in_a_cuda_graph_and_automatic_choice(oracle):
+    """Automatic dispatch (no tuning key): a small batch against K = 8192 takes the cluster kernel; captured and replayed."""
+    m, n, k = 48, 1024, 8192
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=41)
+    aq2, _, sa2, _ = w8a8_case(oracle, m, n, k, seed=42)
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k))
+    a_d, w_d, sa_d, sb_d = dev(aq), dev(wq), dev(sa), dev(sb)
+    d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    args = bq.QGemmArgs(a=a_d, b=w_d, d=d, scale_a=sa_d, scale_b=sb_d)
+    plan.run(None, None, args)
+    torch.cuda.synchronize()
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
+    assert oracle.compare_bitexact(want, bf16_bits(d).reshape(m, n)) == -1
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            plan.run(stream, None, args)
     a_d.copy_(dev(aq2))
     sa_d.copy_(dev(sa2))
     d.zero_()
