@@ -143,7 +143,6 @@ SIGNATURES: dict[str, tuple] = {
     "baracuda_q_nccl_all_gather_bytes": (_i32, [_vp, _i32, _vp, _vp, _sz, _vp]),
     "baracuda_kernels_q_device_status": (_i32, []),
     "baracuda_kernels_q_set_tuning": (_i32, [_i32, _i32]),
-    "baracuda_kernels_q_gemm_split_k_workspace_size": (_sz, [_i32, _i32, _i32]),
 }
 
 _lib = None

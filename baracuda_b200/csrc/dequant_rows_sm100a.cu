@@ -15,7 +15,6 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "gemm_q8_common.cuh"
 #include "launch.h"
 
 namespace bq {
@@ -235,119 +234,6 @@ reduce_dequant_broadcast_kernel(const uint32_t* __restrict__ staging, int world,
     }
 }
 
-// Second pass of a split-K GEMM: the raw GEMM left `slices` partial sums of every output element side by side in the
-// scratch ([m, slices * n] 32-bit words, slice s in columns [s * n, (s + 1) * n)); a thread adds the slices of eight
-// columns (int32 adds, or f32 adds in slice order) and applies the epilogue of the fused GEMM with its arithmetic:
-// (sa * sb) * acc, * alpha, + beta * C, + bias, activation, each product and sum rounded on its own, then bf16.
-// n is a multiple of 8 and the scratch 16-byte aligned (the split-K rule guarantees both).  All loads of a thread are
-// requested before the first is used.  Runs as a programmatic dependent of the GEMM: nothing is touched before the wait.
-struct SplitKEpilogue {
-    const float* sa;
-    const float* sb;
-    int scale_mode;  // 0 scalars, 1 vectors, 2 sa_const + column vector
-    float sa_const;
-    float alpha;
-    const __nv_bfloat16* c;  // or null
-    int64_t ldc;
-    float beta;
-    const void* bias;
-    int bias_kind;  // 0 none, 1 float, 2 int32
-    int act;        // 0 none, 1 relu, 2 gelu, 3 silu
-};
-
-template <bool INT_ACC, int SLICES>
-__device__ __forceinline__ void split_k_sum8(const uint4* src, int64_t slice_stride16, int slices, float (&acc)[8]) {
-    uint4 lo[SLICES], hi[SLICES];
-#pragma unroll
-    for (int s = 0; s < SLICES; ++s) {
-        if (s < slices) {
-            lo[s] = __ldcs(src + s * slice_stride16);
-            hi[s] = __ldcs(src + s * slice_stride16 + 1);
-        }
-    }
-    int isum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    float fsum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-    for (int s = 0; s < SLICES; ++s) {
-        if (s < slices) {
-            const uint32_t v[8] = {lo[s].x, lo[s].y, lo[s].z, lo[s].w, hi[s].x, hi[s].y, hi[s].z, hi[s].w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if constexpr (INT_ACC) {
-                    isum[j] += static_cast<int32_t>(v[j]);
-                } else {
-                    fsum[j] = s == 0 ? __uint_as_float(v[j]) : __fadd_rn(fsum[j], __uint_as_float(v[j]));
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = INT_ACC ? static_cast<float>(isum[j]) : fsum[j];
-}
-
-template <bool INT_ACC>
-__global__ void __launch_bounds__(256)
-split_k_reduce_kernel(const uint32_t* __restrict__ ws, int slices, int m, int n, SplitKEpilogue e,
-                      __nv_bfloat16* __restrict__ d, int64_t ldd, int vec) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int groups = n >> 3;
-    const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    if (idx >= static_cast<int64_t>(m) * groups) return;
-    const int row = static_cast<int>(idx / groups);
-    const int col0 = static_cast<int>(idx - static_cast<int64_t>(row) * groups) * 8;
-    const uint4* src = reinterpret_cast<const uint4*>(ws + static_cast<int64_t>(row) * slices * n + col0);
-    float acc[8];
-    if (slices <= 4) {
-        split_k_sum8<INT_ACC, 4>(src, n >> 2, slices, acc);
-    } else {
-        split_k_sum8<INT_ACC, 8>(src, n >> 2, slices, acc);
-    }
-    const float sa_row = e.scale_mode == 1 ? __ldg(e.sa + row) : (e.scale_mode == 2 ? e.sa_const : __ldg(e.sa));
-    float y[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float sb_col = e.scale_mode != 0 ? __ldg(e.sb + col0 + j) : __ldg(e.sb);
-        y[j] = __fmul_rn(__fmul_rn(__fmul_rn(sa_row, sb_col), acc[j]), e.alpha);
-    }
-    if (e.c) {
-        const __nv_bfloat16* crow = e.c + static_cast<int64_t>(row) * e.ldc + col0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = __fadd_rn(y[j], __fmul_rn(e.beta, __bfloat162float(crow[j])));
-    }
-    if (e.bias_kind == 1) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = __fadd_rn(y[j], __ldg(static_cast<const float*>(e.bias) + col0 + j));
-    } else if (e.bias_kind == 2) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            y[j] = __fadd_rn(y[j], static_cast<float>(__ldg(static_cast<const int32_t*>(e.bias) + col0 + j)));
-        }
-    }
-    if (e.act == 1) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = fmaxf(y[j], 0.0f);
-    } else if (e.act == 2) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = gelu_erf_poly(y[j]);
-    } else if (e.act == 3) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = silu_fast(y[j]);
-    }
-    __nv_bfloat16* dst = d + static_cast<int64_t>(row) * ldd + col0;
-    if (vec) {
-        uint4 out;
-        __nv_bfloat162 h;
-        h = __floats2bfloat162_rn(y[0], y[1]); out.x = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2bfloat162_rn(y[2], y[3]); out.y = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2bfloat162_rn(y[4], y[5]); out.z = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2bfloat162_rn(y[6], y[7]); out.w = *reinterpret_cast<uint32_t*>(&h);
-        *reinterpret_cast<uint4*>(dst) = out;
-    } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dst[j] = __float2bfloat16_rn(y[j]);
-    }
-}
-
 // Builds the interleaved gate/up operand of the gated-MLP GEMM: output row 64b + i is gate row 32b + i for i < 32 and
 // up row 32b + (i - 32) otherwise.  Rows are `row_bytes` bytes (a weight row of K bytes, or 4 for a scale / bias entry).
 __global__ void __launch_bounds__(256)
@@ -404,49 +290,6 @@ int32_t launch_reduce_dequant_broadcast(int32_t kind, int32_t rank, int32_t worl
             ldy, vec);
     }
     return cudaPeekAtLastError() == cudaSuccess ? BQ_STATUS_OK : BQ_STATUS_LAUNCH_FAILURE;
-}
-
-int32_t launch_split_k_reduce(const GemmDesc& g, int32_t slices, cudaStream_t stream) {
-    if (g.m <= 0 || g.n <= 0) return BQ_STATUS_OK;
-    if (slices < 2 || slices > 8 || (g.n % 8) != 0 || !g.workspace || (reinterpret_cast<uintptr_t>(g.workspace) & 15u) != 0) {
-        return BQ_STATUS_INVALID_PROBLEM;
-    }
-    SplitKEpilogue e;
-    e.sa = g.scale_a;
-    e.sb = g.scale_b;
-    e.scale_mode = g.scale_mode;
-    e.sa_const = g.sa_const;
-    e.alpha = g.alpha;
-    e.c = static_cast<const __nv_bfloat16*>(g.c);
-    e.ldc = g.ldc;
-    e.beta = g.beta;
-    e.bias = g.bias;
-    e.bias_kind = g.bias ? g.bias_kind : 0;
-    e.act = g.act;
-    const int vec = ((reinterpret_cast<uintptr_t>(g.d) & 15u) == 0 && ((g.ldd * 2) & 15) == 0) ? 1 : 0;
-    const int64_t total = static_cast<int64_t>(g.m) * (g.n / 8);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>((total + 255) / 256), 1, 1);
-    cfg.blockDim = dim3(256, 1, 1);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    const uint32_t* ws = static_cast<const uint32_t*>(g.workspace);
-    __nv_bfloat16* d = static_cast<__nv_bfloat16*>(g.d);
-    const int m = g.m, n = g.n;
-    const int64_t ldd = g.ldd;
-    const cudaError_t err = g.kind == BQ_KIND_S8
-                                ? cudaLaunchKernelEx(&cfg, split_k_reduce_kernel<true>, ws, slices, m, n, e, d, ldd, vec)
-                                : cudaLaunchKernelEx(&cfg, split_k_reduce_kernel<false>, ws, slices, m, n, e, d, ldd, vec);
-    if (err != cudaSuccess) {
-        (void)cudaGetLastError();
-        return BQ_STATUS_LAUNCH_FAILURE;
-    }
-    return BQ_STATUS_OK;
 }
 
 int32_t launch_dequant_rows(int32_t kind, int32_t m, int32_t n, const void* acc, int64_t ld_acc, const float* scale_a,

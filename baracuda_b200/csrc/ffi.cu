@@ -16,7 +16,6 @@ struct ThreadTuning {
     int32_t force_pair_tile_n = 0;
     int32_t direct_stores = 0;
     int32_t epilogue_warps = 0;
-    int32_t split_k = 0;
     int32_t cluster_split_k = 0;
 };
 thread_local ThreadTuning t_tuning;
@@ -98,20 +97,20 @@ void epilogue_apply(const Epilogue& e, bq::GemmDesc& g) {
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
                  const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream,
-                 const Epilogue& epi = Epilogue(), int32_t pdl = 0, void* workspace = nullptr, size_t workspace_bytes = 0);
+                 const Epilogue& epi = Epilogue(), int32_t pdl = 0);
 
 int32_t gemm_rcr_run(int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                      const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd,
                      const void* scale_a, const void* scale_b, int32_t scale_mode, float alpha, float beta,
-                     void* stream, void* workspace = nullptr, size_t workspace_bytes = 0) {
+                     void* stream) {
     return gemm_run(bq::BQ_LAYOUT_RCR, kind, raw, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b, scale_mode,
-                    alpha, beta, stream, Epilogue(), 0, workspace, workspace_bytes);
+                    alpha, beta, stream);
 }
 
 int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n, int32_t k, const void* a, int64_t lda,
                  const void* b, int64_t ldb, const void* c, int64_t ldc, void* d, int64_t ldd, const void* scale_a,
                  const void* scale_b, int32_t scale_mode, float alpha, float beta, void* stream, const Epilogue& epi,
-                 int32_t pdl, void* workspace, size_t workspace_bytes) {
+                 int32_t pdl) {
     const int32_t st = raw ? gemm_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd)
                            : gemm_bf16_validate(layout, m, n, k, a, lda, b, ldb, c, ldc, d, ldd);
     if (st != bq::BQ_STATUS_OK) return st;
@@ -162,9 +161,6 @@ int32_t gemm_run(int32_t layout, int32_t kind, int32_t raw, int32_t m, int32_t n
     g.ldc = ldc;
     g.beta = beta;
     g.pdl = pdl;
-    g.workspace = workspace;  // optional: enables the split-K path for problems of few tiles
-    g.workspace_bytes = workspace ? workspace_bytes : 0;
-    g.split_k = t_tuning.split_k;
     g.cluster_split_k = t_tuning.cluster_split_k;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
@@ -435,8 +431,10 @@ int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, float alpha, float beta,
     void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
     return gemm_rcr_run(bq::BQ_KIND_S8, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,
-                        BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, workspace, workspace_bytes);
+                        BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream);
 }
 size_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_can_implement(
@@ -554,8 +552,10 @@ int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k, const void* a, int64_t lda, const void* b, int64_t ldb, const void* c,
     int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode, float alpha,
     float beta, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;
     return gemm_rcr_run(bq::BQ_KIND_E4M3, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b, scale_mode,
-                        alpha, beta, stream, workspace, workspace_bytes);
+                        alpha, beta, stream);
 }
 size_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(int32_t, int32_t, int32_t) { return 0; }
 int32_t baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_can_implement(
@@ -737,13 +737,14 @@ BQ_FP8_BIAS_FAMILY(rrr, bq::BQ_LAYOUT_RRR)
                  int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,          \
                  const void* bias, int32_t epilogue, float alpha, float beta, void* workspace, size_t workspace_bytes,     \
                  void* stream) {                                                                                           \
+        (void)workspace;                                                                                                   \
+        (void)workspace_bytes;                                                                                             \
         Epilogue e;                                                                                                        \
         e.bias = bias;                                                                                                     \
         e.bias_kind = 1;                                                                                                   \
         e.kind = epilogue;                                                                                                 \
         return gemm_run(LAYOUT, KIND, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,                        \
-                        HAS_MODE ? scale_mode : BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, e, 0, workspace,        \
-                        workspace_bytes);                                                                                  \
+                        HAS_MODE ? scale_mode : BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, e);                     \
     }
 BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8, false)
 BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, false)
@@ -756,13 +757,14 @@ BQ_BF16_EPILOGUE_RUN(baracuda_kernels_gemm_fp8_e4m3_rrr_bf16_sm100a_epilogue_run
                  int64_t ldc, void* d, int64_t ldd, const void* scale_a, const void* scale_b, int32_t scale_mode,          \
                  const void* bias, int32_t epilogue, float alpha, float beta, void* workspace, size_t workspace_bytes,     \
                  void* stream) {                                                                                           \
+        (void)workspace;                                                                                                   \
+        (void)workspace_bytes;                                                                                             \
         Epilogue e;                                                                                                        \
         e.bias = bias;                                                                                                     \
         e.bias_kind = 1;                                                                                                   \
         e.kind = epilogue;                                                                                                 \
         return gemm_run(LAYOUT, KIND, 0, m, n, k, a, lda, b, ldb, c, ldc, d, ldd, scale_a, scale_b,                        \
-                        HAS_MODE ? scale_mode : BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, e, 1, workspace,        \
-                        workspace_bytes);                                                                                  \
+                        HAS_MODE ? scale_mode : BARACUDA_Q_SCALE_PER_ROW_COL, alpha, beta, stream, e, 1);                  \
     }
 BQ_BF16_PDL_RUN(baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_pdl_run, bq::BQ_LAYOUT_RCR, bq::BQ_KIND_S8, false)
 BQ_BF16_PDL_RUN(baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_pdl_run, bq::BQ_LAYOUT_RRR, bq::BQ_KIND_S8, false)
@@ -887,11 +889,6 @@ int32_t baracuda_kernels_q_selftest_bounded_wait(int64_t limit_cycles, void* str
     return bq::launch_bounded_wait_selftest(static_cast<long long>(limit_cycles), static_cast<cudaStream_t>(stream));
 }
 
-size_t baracuda_kernels_q_gemm_split_k_workspace_size(int32_t m, int32_t n, int32_t k) {
-    if (m < 0 || n < 0 || k < 0) return 0;
-    return bq::gemm_split_k_workspace_bytes(m, n, k);
-}
-
 int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
     switch (key) {
         case 0:
@@ -912,10 +909,6 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             t_tuning.epilogue_warps = value;
             return bq::BQ_STATUS_OK;
         case 6:
-            if (value < 0 || value > 8) return bq::BQ_STATUS_INVALID_PROBLEM;
-            t_tuning.split_k = value;
-            return bq::BQ_STATUS_OK;
-        case 7:
             if (value != 0 && value != 1 && value != 2 && value != 4) return bq::BQ_STATUS_INVALID_PROBLEM;
             t_tuning.cluster_split_k = value;
             return bq::BQ_STATUS_OK;

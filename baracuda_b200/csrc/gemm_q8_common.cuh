@@ -62,12 +62,8 @@ struct GemmParams {
     // (chosen to stay resident in L2) and a few weight column blocks, instead of every row block of A.
     int raster_gm;
     int pdl;  // launched as a programmatic dependent: weights may be fetched before the dependency wait
-    // 1-CTA kernel, split-K launches (k_slices > 1; raw output only): n and n_tiles describe the [M, k_slices * N]
-    // scratch, tile column block j computes weight column block j % n_tiles_real over the K blocks
-    // [s * kb_per_slice, (s + 1) * kb_per_slice) with s = j / n_tiles_real
-    int k_slices;
+    // cluster split-K kernel: CTA s of a cluster walks the K blocks [s * kb_per_slice, (s + 1) * kb_per_slice)
     int kb_per_slice;
-    int n_tiles_real;
     uint16_t full_begin[98];
     uint16_t half_begin[98];
 };

@@ -121,15 +121,8 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 int idx = 0;
                 for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                     const int m_blk = tile % p.m_tiles;
-                    int n_blk = tile / p.m_tiles;
-                    int kb0 = 0, kb1 = num_kb;
-                    if (p.k_slices > 1) {  // split-K: this tile is one K slice of a weight column block
-                        const int s = n_blk / p.n_tiles_real;
-                        n_blk -= s * p.n_tiles_real;
-                        kb0 = s * p.kb_per_slice;
-                        kb1 = (kb0 + p.kb_per_slice < num_kb) ? kb0 + p.kb_per_slice : num_kb;
-                    }
-                    for (int kb = kb0; kb < kb1; ++kb, ++idx) {
+                    const int n_blk = tile / p.m_tiles;
+                    for (int kb = 0; kb < num_kb; ++kb, ++idx) {
                         if (idx < first) continue;
                         if (idx >= last) return;
                         const int stage = idx % STAGES;
@@ -172,12 +165,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 }
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * BLOCK_N);
-                int nk = num_kb;
-                if (p.k_slices > 1) {  // the K blocks of this tile's slice (never empty: the host sizes the slices)
-                    const int kb0 = ((tile / p.m_tiles) / p.n_tiles_real) * p.kb_per_slice;
-                    nk = (p.kb_per_slice < num_kb - kb0) ? p.kb_per_slice : num_kb - kb0;
-                }
-                for (int kb = 0; kb < nk; ++kb) {
+                for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait_bounded(&full_bar[stage], phase, abort_word, WAIT_LIMIT_CYCLES)) {
                         record_timeout(abort_word, 103);
                         ok = false;
@@ -389,16 +377,7 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
     p.k = g.k;
     p.m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     p.n_tiles = (g.n + BLOCK_N - 1) / BLOCK_N;
-    p.k_slices = 1;
     p.kb_per_slice = 0;
-    p.n_tiles_real = p.n_tiles;
-    if (RAW && g.k_slices > 1) {  // split-K: the output is the [m, k_slices * n] scratch, whole tiles only
-        if (g.n % BLOCK_N != 0 || g.kb_per_slice < 1) return BQ_STATUS_INVALID_PROBLEM;
-        p.k_slices = g.k_slices;
-        p.kb_per_slice = g.kb_per_slice;
-        p.n = g.n * g.k_slices;
-        p.n_tiles = p.n_tiles_real * g.k_slices;
-    }
     const int64_t elem = RAW ? 4 : (g.q8_out ? 1 : 2);
     p.out_q8 = RAW ? 0 : g.q8_out;
     p.c = g.c;
@@ -458,7 +437,6 @@ int32_t launch_config(const GemmDesc& g, int sms, cudaStream_t stream) {
 // wave costs the same again, and a launch cannot beat the weight bytes over the HBM rate.
 constexpr float COST_KB_64 = 0.22f, COST_KB_128 = 0.25f, COST_KB_256 = 0.40f, COST_KB_PAIR = 0.33f;
 constexpr float PAIR_FIXED_US = 2.0f;      // cluster launch and pair hand-shakes
-constexpr float SPLIT_FIXED_US = 3.5f;     // the slices' sums through L2 and the dependent reduce pass
 constexpr float HBM_BYTES_PER_US = 6.5e6f;
 
 float wave_cost(int64_t tiles, int sms, float cost_kb, int64_t num_kb) {
@@ -493,53 +471,13 @@ float one_pass_cost(int64_t m, int64_t n, int64_t k, int sms, bool allow_pair, i
     return best > hbm ? best : hbm;
 }
 
-// Split-K rule.  A problem whose 128 x 128 tiles cover at most half of the SMs walks its whole K on a few SMs while
-// the others idle; cutting K into slices on the idle SMs shortens that walk, at the price of the slices' 32-bit sums
-// going through L2 and of a second (dependent) launch.  Slices of at least four K blocks, at most eight slices, all
-// (tile, slice) pairs in one wave; taken when the model gains at least a microsecond (long K: K = 14336 at M <= 256
-// 37 -> 26-28 us, 33.5 at M = 256; K = 8192 against 4096 columns 24.8 -> 21.3 us; K = 4096 never).
-constexpr int SPLIT_TILE_N = 128;
-constexpr int SPLIT_MAX_SLICES = 8;
+// Split-K inside a thread-block cluster (gemm_q8_splitk_sm100a.cu), slices of this launch (0 = none).  A problem whose
+// 128 x 128 tiles cover at most half of the SMs walks its whole K on a few SMs while the others idle; clusters of 2 or 4
+// CTAs per tile cut that walk, at the price of the exchange through distributed shared memory (about a microsecond).
+// Slices of at least four K blocks, every cluster resident at once; taken when the model gains at least a microsecond
+// (CUDA-graph timing over rotating weights, M <= 128: 4096 x 4096 12.5 -> 8.5 us, K = 14336 against 4096 columns
+// 32 -> 16 us, K = 8192 20.3 -> 12.2 us, 8192 x 8192 20.8 -> 17.5 us with two slices).
 constexpr int SPLIT_MIN_KB = 16;  // K >= 2048 bytes
-
-int split_k_rule(int64_t m, int64_t n, int64_t k, int sms) {
-    if (m < 1 || n < SPLIT_TILE_N || n % SPLIT_TILE_N != 0 || sms < 2) return 1;
-    const int64_t num_kb = (k + BLOCK_K - 1) / BLOCK_K;
-    const int64_t tiles = ((m + BLOCK_M - 1) / BLOCK_M) * (n / SPLIT_TILE_N);
-    if (num_kb < SPLIT_MIN_KB || 2 * tiles > sms) return 1;
-    const float hbm = static_cast<float>(n) * static_cast<float>(k) / HBM_BYTES_PER_US;
-    float best = one_pass_cost(m, n, k, sms, true, nullptr) - 1.0f;
-    int best_s = 1;
-    for (int64_t s = 2; s <= SPLIT_MAX_SLICES && s * tiles <= sms && s <= num_kb / 4; ++s) {
-        const float walk = static_cast<float>((num_kb + s - 1) / s) * COST_KB_128;
-        const float c = (walk > hbm ? walk : hbm) + SPLIT_FIXED_US;
-        if (c < best) {
-            best = c;
-            best_s = static_cast<int>(s);
-        }
-    }
-    return best_s;
-}
-
-// Slices of this launch (1 = no split): the rule or the forced count, limited by the scratch the caller passed.
-int split_k_slices(const GemmDesc& g, int sms) {
-    if (g.split_k == 1 || g.raw_out || g.q8_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.force_block_n != 0 ||
-        g.b_layout != BQ_LAYOUT_RCR) {
-        return 1;
-    }
-    if (!g.workspace || (reinterpret_cast<uintptr_t>(g.workspace) & 15u) != 0 || g.n % SPLIT_TILE_N != 0) return 1;
-    const int64_t num_kb = (static_cast<int64_t>(g.k) + BLOCK_K - 1) / BLOCK_K;
-    int64_t s = g.split_k >= 2 ? g.split_k : split_k_rule(g.m, g.n, g.k, sms);
-    if (s > SPLIT_MAX_SLICES) s = SPLIT_MAX_SLICES;
-    if (s > num_kb) s = num_kb;
-    const int64_t slice_bytes = static_cast<int64_t>(g.m) * g.n * 4;
-    const int64_t cap = static_cast<int64_t>(g.workspace_bytes / static_cast<size_t>(slice_bytes));
-    if (s > cap) s = cap;
-    return s < 2 ? 1 : static_cast<int>(s);
-}
-
-// Split-K inside a cluster (no scratch): slices of this launch, 0 = none.  Same model as split_k_rule with the smaller
-// fixed cost of the in-kernel exchange; all clusters must be resident at once.
 constexpr float CLUSTER_SPLIT_FIXED_US = 1.0f;
 
 int cluster_split_slices(const GemmDesc& g, int sms) {
@@ -577,31 +515,8 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     const int sms = sm_count_impl();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     if constexpr (!RAW) {
-        if (g.split_k < 2) {  // a forced scratch split goes first
-            const int cs = cluster_split_slices(g, sms);
-            if (cs > 1) return launch_gemm_q8_cluster_split_k(g, cs, stream);
-        }
-        const int want = split_k_slices(g, sms);
-        if (want > 1) {
-            const int num_kb = (g.k + BLOCK_K - 1) / BLOCK_K;
-            GemmDesc r = g;  // the slices' raw sums into the scratch, [m, slices * n] 32-bit words
-            r.kb_per_slice = (num_kb + want - 1) / want;
-            r.k_slices = (num_kb + r.kb_per_slice - 1) / r.kb_per_slice;  // no empty slice
-            r.raw_out = 1;
-            r.d = g.workspace;
-            r.ldd = static_cast<int64_t>(r.k_slices) * g.n;
-            r.scale_a = nullptr;
-            r.scale_b = nullptr;
-            r.bias = nullptr;
-            r.bias_kind = 0;
-            r.act = 0;
-            r.c = nullptr;
-            r.beta = 0.0f;
-            r.direct_stores = 0;
-            const int32_t st = launch_config<KIND, true, SPLIT_TILE_N, 6>(r, sms, stream);
-            if (st != BQ_STATUS_OK) return st;
-            return launch_split_k_reduce(g, r.k_slices, stream);
-        }
+        const int cs = cluster_split_slices(g, sms);
+        if (cs > 1) return launch_gemm_q8_cluster_split_k(g, cs, stream);
     }
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };
@@ -685,12 +600,6 @@ int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
 }
 
 int sm_count_of_current_device() { return sm_count_impl(); }
-
-size_t gemm_split_k_workspace_bytes(int32_t m, int32_t n, int32_t k) {
-    // sized for the SM count of a B200; a launch on a device with more SMs uses as many slices as the scratch holds
-    const int s = split_k_rule(m, n, k, 148);
-    return s < 2 ? 0 : static_cast<size_t>(s) * static_cast<size_t>(m) * static_cast<size_t>(n) * 4u;
-}
 
 bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k,
                              int l2_promotion) {

@@ -383,9 +383,7 @@ int32_t launch_splitk(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, 
     p.mixed_full_cols = 0;
     p.raster_gm = 1;
     p.pdl = g.pdl;
-    p.k_slices = S;
     p.kb_per_slice = kb_per_slice;
-    p.n_tiles_real = n_tiles;
     if (cudaLaunchKernelEx(&cfg, kern, map_a, map_b, p) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;

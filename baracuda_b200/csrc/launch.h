@@ -62,24 +62,9 @@ struct GemmDesc {
     // gated-MLP epilogue (bf16 output, weights [N,K] only): n = 2F interleaved gate/up rows in blocks of 32, d is [M, F]
     int32_t swiglu;
     int32_t pdl;  // 1: launch with programmatic stream serialization (the caller promises the previous kernel does not write b)
-    // Optional scratch of the bf16-out GEMMs with [N,K] weights.  With at least gemm_split_k_workspace_bytes(m, n, k)
-    // bytes (16-byte aligned), problems of few output tiles and long K run as K slices on otherwise idle SMs: a raw
-    // GEMM of the slices into the scratch, then a dependent pass that adds them and applies the epilogue.
-    void* workspace;
-    size_t workspace_bytes;
-    int32_t split_k;  // 0 = choose, 1 = never, 2..8 = that many slices if the scratch allows (tuning and tests)
     int32_t cluster_split_k;  // split-K inside a thread-block cluster: 0 = choose, 1 = never, 2 / 4 = that many slices
-    // set by the dispatch for the raw GEMM of a split-K launch (d = scratch [m, k_slices * n]); 0 / 1 otherwise
-    int32_t k_slices;
-    int32_t kb_per_slice;
 };
 
-// Scratch that lets launch_gemm_q8 split K for this problem (0: the problem never splits).  Pure host arithmetic.
-size_t gemm_split_k_workspace_bytes(int32_t m, int32_t n, int32_t k);
-// Second pass of a split-K launch: D = epilogue(sum of the `slices` column blocks of g.workspace, [m, slices * n]
-// 32-bit words), everything else (scales, alpha, beta * C, bias, activation, d) as described by g.  Launched as a
-// programmatic dependent of the GEMM in front of it.
-int32_t launch_split_k_reduce(const GemmDesc& g, int32_t slices, cudaStream_t stream);
 // Split-K without scratch: clusters of `slices` (2 or 4) CTAs share a 128 x 128 tile and add their partial sums through
 // distributed shared memory (gemm_q8_splitk_sm100a.cu).  bf16 or 8-bit output, [N,K] weights, any M and N;
 // every slice needs at least one K block.

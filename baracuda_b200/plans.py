@@ -154,14 +154,6 @@ class _QGemmPlanBase:
         lib = _lib.load()
         return int(getattr(lib, self._ws_symbol)(self.desc.m, self.desc.n, self.desc.k))
 
-    def split_k_workspace_size(self) -> int:
-        """Optional scratch: passing a workspace of at least this many bytes to `run` lets a bf16-out plan with [N,K]
-        weights cut K into slices on idle SMs (few output tiles, long K); 0 when the shape never splits."""
-        d = self.desc
-        if not isinstance(self, (W8A8GemmPlan, Fp8ScaledGemmPlan)) or self.raw or d.layout is not LayoutSku.Rcr:
-            return 0
-        return int(_lib.load().baracuda_kernels_q_gemm_split_k_workspace_size(d.m, d.n, d.k))
-
     def _lds(self, args: QGemmArgs):
         d = self.desc
         lda = args.lda if args.lda is not None else max(d.k, 1)
@@ -602,10 +594,6 @@ class QuantizedLinearPlan:
 
     def workspace_size(self) -> int:
         return self._mm.workspace_size()
-
-    def split_k_workspace_size(self) -> int:
-        """Optional scratch of the GEMM behind this layer (0 for the GEMV path): see W8A8GemmPlan.split_k_workspace_size."""
-        return self._mm.split_k_workspace_size() if isinstance(self._mm, W8A8GemmPlan) else 0
 
     def fused_decode_ok(self, args: QuantizedLinearArgs) -> bool:
         """True when the whole step runs as one launch: bf16 activation, m <= 8, and a K the fused-quantiser GEMV serves."""

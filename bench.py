@@ -388,28 +388,30 @@ def side_workloads(peaks: dict) -> dict:
                     "us": t * 1e6, "GBps": byts / t / 1e9, "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
     del weights
 
-    # small batches against the down projection (K = 14336, N = 4096; 32 output tiles): one pass, and with the optional
-    # scratch that lets the GEMM cut K into slices on the idle SMs (raw GEMM + dependent reduce pass); CUDA graph over
-    # six weight buffers, like the GEMV figures above
-    weights = [torch.randint(-127, 128, (n2 * k2,), dtype=torch.int8, device="cuda", generator=g) for _ in range(nbuf)]
+    # small batches (between the GEMV's m <= 8 and prefill) against the o projection and the down projection: 32 output
+    # tiles of 128 x 128, so the dispatch cuts K into four slices per tile on a thread-block cluster (partial sums meet in
+    # distributed shared memory); the one-pass kernel (set_tuning key 6 = 1) beside it.  CUDA graph over rotating weights.
     small = {}
-    for m in (32, 128):
-        x = torch.randint(-127, 128, (m, k2), dtype=torch.int8, device="cuda", generator=g)
-        sa = torch.rand(m, device="cuda", generator=g)
-        sb = torch.rand(n2, device="cuda", generator=g)
-        d = torch.empty((m, n2), dtype=torch.bfloat16, device="cuda")
-        plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n2, k2))
-        scratch = torch.empty(max(plan.split_k_workspace_size(), 16), dtype=torch.uint8, device="cuda")
-        argl = [bq.QGemmArgs(a=x, b=w.view(n2, k2), d=d, scale_a=sa, scale_b=sb) for w in weights]
-        byts = k2 * n2 + m * k2 + m * 4 + n2 * 4 + m * n2 * 2
-        for name, ws in (("one_pass", None), ("split_k", scratch)):
-            launchers = [(lambda i=i: plan.run(None, ws, argl[i % nbuf])) for i in range(2 * nbuf)]
-            t = min(graph_launch_ms(launchers) for _ in range(2)) * 1e-3
-            small[f"M{m}_{name}"] = {"us": t * 1e6, "TOPS": 2.0 * m * n2 * k2 / t / 1e12,
-                                     "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
-        small[f"M{m}_scratch_bytes"] = plan.split_k_workspace_size()
-    out["small_batch_down_proj_w8a8"] = small
-    del weights
+    for tag, (nn, kk) in {"o_proj": (4096, 4096), "down_proj": (4096, 14336)}.items():
+        nb = max(2, min(nbuf, (400 << 20) // (nn * kk) + 1))
+        weights = [torch.randint(-127, 128, (nn, kk), dtype=torch.int8, device="cuda", generator=g) for _ in range(nb)]
+        for m in (32, 128):
+            x = torch.randint(-127, 128, (m, kk), dtype=torch.int8, device="cuda", generator=g)
+            sa = torch.rand(m, device="cuda", generator=g)
+            sb = torch.rand(nn, device="cuda", generator=g)
+            d = torch.empty((m, nn), dtype=torch.bfloat16, device="cuda")
+            plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, nn, kk))
+            argl = [bq.QGemmArgs(a=x, b=w, d=d, scale_a=sa, scale_b=sb) for w in weights]
+            byts = kk * nn + m * kk + m * 4 + nn * 4 + m * nn * 2
+            for name, key in (("one_pass", 1), ("cluster_split_k", 0)):
+                bq.set_tuning(6, key)
+                launchers = [(lambda i=i: plan.run(None, None, argl[i % nb])) for i in range(2 * nb)]
+                t = min(graph_launch_ms(launchers) for _ in range(2)) * 1e-3
+                small[f"{tag}_M{m}_{name}"] = {"us": t * 1e6, "TOPS": 2.0 * m * nn * kk / t / 1e12,
+                                               "frac_of_hbm_peak": byts / t / 1e9 / peaks["hbm_gbs"]}
+            bq.set_tuning(6, 0)
+        del weights
+    out["small_batch_w8a8"] = small
 
     def gemm(kind: str, m: int, n: int, k: int, steps: int = 10, graph: bool = False, gated: bool = False):
         gen = torch.Generator(device="cuda")

@@ -77,17 +77,12 @@ extern "C" {
  * ".satfinite", crates/baracuda-kernels-sys/kernels/include/baracuda_int8_rrr_sm80.cuh:86-92, and the saturating
  * adds of its test oracle, crates/baracuda-kernels/tests/int8_rrr_smoke.rs:76-131); up to that K the two agree
  * bit for bit, beyond it tcgen05's behaviour is unspecified, so the call is refused rather than answered differently.
- * Optional scratch (split-K): *_workspace_size of the bf16-out GEMMs is 0 and `workspace` may be null.  A caller that
- * passes at least baracuda_kernels_q_gemm_split_k_workspace_size(m, n, k) bytes (16-byte aligned) to the *_rcr_bf16_*
- * run symbols (identity, *_epilogue_run, *_pdl_run) lets problems whose 128 x 128 output tiles cover at most half of
- * the SMs, with K >= 2048 and N a multiple of 128 (small batches against one layer's weight), run as 2..8 K slices on
- * the idle SMs: a raw GEMM of the slices into the scratch, then a dependent pass that adds them and applies the same
- * epilogue arithmetic.  The int8 result keeps its bits (integer sums); the e4m3 result adds the slices' f32 sums in
- * slice order, inside the tolerance of the SKU.  The query returns 0 for problems that never split; a smaller or
- * misaligned scratch simply leaves the call on the one-pass path (never status 4).  Overlapping calls must not share
- * a scratch.
+ * Small batches (the 128 x 128 output tiles cover at most half of the SMs, K >= 2048): the bf16-out and 8-bit-out GEMMs
+ * with [N,K] weights run as 2 or 4 K slices per tile on otherwise idle SMs -- a thread-block cluster per tile whose CTAs
+ * add their partial sums through distributed shared memory before the same epilogue.  Nothing changes for the caller:
+ * no scratch, one launch; the int8 result keeps its bits, the e4m3 result adds the slices' f32 sums in slice order
+ * (inside the tolerance of the SKU).
  * ------------------------------------------------------------------------- */
-size_t baracuda_kernels_q_gemm_split_k_workspace_size(int32_t m, int32_t n, int32_t k);
 int32_t baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
     int32_t m, int32_t n, int32_t k,
     const void* a, int64_t lda, const void* b, int64_t ldb,
@@ -710,10 +705,8 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128; 2 = the mixed 256 / 128 schedule;
  *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
  *   key 5  CTA-pair GEMM epilogue warps: 0 automatic (eight for gelu / silu chains on at most two waves of tiles), 4, 8.
- *   key 7  split-K inside thread-block clusters (no scratch; bf16-out and 8-bit-out GEMMs with [N,K] weights): 0 automatic,
- *          1 never, 2 or 4 = that many K slices on any shape with at least that many 128-byte K blocks.
- *   key 6  split-K of the bf16-out GEMMs with [N,K] weights when a scratch is passed: 0 automatic, 1 never, 2..8 that
- *          many K slices on any shape with N a multiple of 128 (as far as the scratch holds m * n * 4 bytes per slice).
+ *   key 6  split-K inside thread-block clusters (bf16-out and 8-bit-out GEMMs with [N,K] weights): 0 automatic, 1 never,
+ *          2 or 4 = that many K slices on any shape with at least that many 128-byte K blocks.
  * Any other key or value returns 2.
  * selftest_bounded_wait: launches one thread that waits, for at most limit_cycles SM clock cycles
  * (1 .. 2^28), on a barrier that nothing completes -- the time-out path of every kernel here.  After the

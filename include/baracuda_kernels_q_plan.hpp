@@ -172,12 +172,6 @@ class W8A8GemmPlan {
         return raw_ ? baracuda_kernels_gemm_s8_rcr_s32_sm100a_workspace_size(desc_.m, desc_.n, desc_.k)
                     : baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
     }
-    // Optional scratch: a Workspace of at least this many bytes lets `run` cut K into slices on idle SMs (bf16 output,
-    // [N,K] weights, few output tiles, long K); 0 when the shape never splits.  `run` works without it.
-    size_t split_k_workspace_size() const {
-        if (raw_ || desc_.layout != LayoutSku::Rcr) return 0;
-        return baracuda_kernels_q_gemm_split_k_workspace_size(desc_.m, desc_.n, desc_.k);
-    }
     Error can_implement(const QGemmArgs& x) const {
         const bool rrr = desc_.layout == LayoutSku::Rrr;
         auto can = rrr ? (raw_ ? baracuda_kernels_gemm_s8_rrr_s32_sm100a_can_implement
@@ -267,10 +261,6 @@ class Fp8ScaledGemmPlan {
     PrecisionGuarantee precision_guarantee() const { return sku_.precision_guarantee; }
     size_t workspace_size() const {
         return baracuda_kernels_gemm_fp8_e4m3_rcr_bf16_sm100a_workspace_size(desc_.m, desc_.n, desc_.k);
-    }
-    size_t split_k_workspace_size() const {  // as W8A8GemmPlan::split_k_workspace_size
-        if (raw_ || desc_.layout != LayoutSku::Rcr) return 0;
-        return baracuda_kernels_q_gemm_split_k_workspace_size(desc_.m, desc_.n, desc_.k);
     }
     Error can_implement(const QGemmArgs& x) const {
         const bool rrr = desc_.layout == LayoutSku::Rrr;
@@ -688,8 +678,6 @@ class QuantizedLinearPlan {
     const KernelSku& sku() const { return skinny_ ? gemv_.sku() : gemm_.sku(); }
     PrecisionGuarantee precision_guarantee() const { return sku().precision_guarantee; }
     size_t workspace_size() const { return skinny_ ? gemv_.workspace_size() : gemm_.workspace_size(); }
-    // Optional scratch of the GEMM behind this layer (0 on the GEMV path): see W8A8GemmPlan::split_k_workspace_size.
-    size_t split_k_workspace_size() const { return skinny_ ? 0 : gemm_.split_k_workspace_size(); }
     // True when the whole step is one launch.
     bool fused_decode(const QuantizedLinearArgs& x) const {
         const int64_t ldk = desc_.k > 0 ? desc_.k : 1, ldn = desc_.c_out > 0 ? desc_.c_out : 1;

@@ -445,10 +445,6 @@ extern "C" {
         comm: *mut c_void, world: i32, send: *const c_void, recv: *mut c_void, bytes_per_rank: usize, stream: *mut c_void,
     ) -> i32;
 
-    /// Optional scratch of the bf16-out `*_rcr_bf16_*` GEMM symbols: with at least this many bytes (16-byte aligned) in
-    /// `workspace`, problems of few output tiles and long K run as K slices on idle SMs; 0 = the shape never splits.
-    pub fn baracuda_kernels_q_gemm_split_k_workspace_size(m: i32, n: i32, k: i32) -> usize;
-
     /// Test hooks: a kernel choice for the calling thread only (see the header for keys and values), and a launch
     /// whose only thread waits `limit_cycles` on a barrier nothing completes (status 299 afterwards).
     pub fn baracuda_kernels_q_set_tuning(key: i32, value: i32) -> i32;

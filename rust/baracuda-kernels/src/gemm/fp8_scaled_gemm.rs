@@ -124,19 +124,9 @@ impl Fp8ScaledGemmPlan {
         self.sku.precision_guarantee
     }
 
-    /// No required scratch.
+    /// No scratch.
     pub fn workspace_size(&self) -> usize {
         0
-    }
-
-    /// Optional scratch: a workspace of at least this many bytes lets `run` cut K into slices on idle SMs
-    /// (`[N, K]` weights, few output tiles, long K); 0 when the shape never splits.
-    pub fn split_k_workspace_size(&self) -> usize {
-        let d = &self.desc;
-        match d.layout {
-            LayoutSku::Rcr => unsafe { sys::baracuda_kernels_q_gemm_split_k_workspace_size(d.m, d.n, d.k) },
-            LayoutSku::Rrr => 0,
-        }
     }
 
     /// Shape and buffer-length checks, then the C side's `can_implement`.
@@ -212,14 +202,9 @@ impl Fp8ScaledGemmPlan {
         self.launch(stream, workspace, args, true)
     }
 
-    fn launch(&self, stream: &Stream, workspace: Workspace<'_>, args: Fp8ScaledGemmArgs<'_>, dependent: bool) -> Result<()> {
+    fn launch(&self, stream: &Stream, _workspace: Workspace<'_>, args: Fp8ScaledGemmArgs<'_>, dependent: bool) -> Result<()> {
         self.can_implement(&args)?;
         let d = &self.desc;
-        // optional: a scratch of `split_k_workspace_size()` bytes enables the split-K path
-        let (ws_ptr, ws_bytes) = match workspace {
-            Workspace::None => (core::ptr::null_mut(), 0usize),
-            Workspace::Borrowed(s) => (s.as_raw().0 as *mut c_void, s.len()),
-        };
         let mode = match d.scale_mode {
             ScaleMode::PerTensor => sys::BARACUDA_Q_SCALE_PER_TENSOR,
             ScaleMode::PerRowCol => sys::BARACUDA_Q_SCALE_PER_ROW_COL,
@@ -251,7 +236,7 @@ impl Fp8ScaledGemmPlan {
         };
         let code = unsafe {
             f(d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb, mode, bias, epi,
-              args.alpha, args.beta, ws_ptr, ws_bytes, s)
+              args.alpha, args.beta, core::ptr::null_mut(), 0, s)
         };
         map_status(code, if dependent { "Fp8ScaledGemmPlan::run_dependent" } else { "Fp8ScaledGemmPlan::run" })
     }

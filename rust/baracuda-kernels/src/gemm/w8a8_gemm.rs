@@ -136,19 +136,9 @@ impl W8A8GemmPlan {
         self.sku.precision_guarantee
     }
 
-    /// No required scratch.
+    /// No scratch.
     pub fn workspace_size(&self) -> usize {
         0
-    }
-
-    /// Optional scratch: a workspace of at least this many bytes lets `run` cut K into slices on idle SMs
-    /// (`[N, K]` weights, few output tiles, long K); 0 when the shape never splits.
-    pub fn split_k_workspace_size(&self) -> usize {
-        let d = &self.desc;
-        match d.layout {
-            LayoutSku::Rcr => unsafe { sys::baracuda_kernels_q_gemm_split_k_workspace_size(d.m, d.n, d.k) },
-            LayoutSku::Rrr => 0,
-        }
     }
 
     /// Shape, leading-dimension, alignment and buffer-length checks; the typed layer is the soundness
@@ -211,14 +201,9 @@ impl W8A8GemmPlan {
     }
 
     /// Asynchronous launch on `stream`; no allocation, no host synchronisation (graph-capture safe).
-    pub fn run(&self, stream: &Stream, workspace: Workspace<'_>, args: W8A8GemmArgs<'_>) -> Result<()> {
+    pub fn run(&self, stream: &Stream, _workspace: Workspace<'_>, args: W8A8GemmArgs<'_>) -> Result<()> {
         self.can_implement(&args)?;
         let d = &self.desc;
-        // optional: a scratch of `split_k_workspace_size()` bytes enables the split-K path
-        let (ws_ptr, ws_bytes) = match workspace {
-            Workspace::None => (core::ptr::null_mut(), 0usize),
-            Workspace::Borrowed(s) => (s.as_raw().0 as *mut c_void, s.len()),
-        };
         let a = args.a.data.as_raw().0 as *const c_void;
         let b = args.b.data.as_raw().0 as *const c_void;
         let out = args.d.data.as_raw().0 as *mut c_void;
@@ -234,14 +219,14 @@ impl W8A8GemmPlan {
             match (d.layout, d.epilogue) {
                 (LayoutSku::Rcr, EpilogueKind::Identity) => sys::baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_run(
                     d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb,
-                    args.alpha, args.beta, ws_ptr, ws_bytes, s),
+                    args.alpha, args.beta, core::ptr::null_mut(), 0, s),
                 (LayoutSku::Rrr, EpilogueKind::Identity) => sys::baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_run(
                     d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb,
                     args.alpha, args.beta, core::ptr::null_mut(), 0, s),
                 (LayoutSku::Rcr, e) => sys::baracuda_kernels_gemm_w8a8_s8_rcr_bf16_sm100a_epilogue_run(
                     d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb,
                     sys::BARACUDA_Q_SCALE_PER_ROW_COL, bias, epilogue_code(e), args.alpha, args.beta,
-                    ws_ptr, ws_bytes, s),
+                    core::ptr::null_mut(), 0, s),
                 (LayoutSku::Rrr, e) => sys::baracuda_kernels_gemm_w8a8_s8_rrr_bf16_sm100a_epilogue_run(
                     d.m, d.n, d.k, a, args.a.ld, b, args.b.ld, c_ptr, ldc, out, args.d.ld, sa, sb,
                     sys::BARACUDA_Q_SCALE_PER_ROW_COL, bias, epilogue_code(e), args.alpha, args.beta,
@@ -253,13 +238,9 @@ impl W8A8GemmPlan {
 
     /// The same launch as a programmatic dependent of the kernel before it on `stream`: prologue and the first
     /// weight tiles are issued while that kernel finishes.  The caller asserts that it does not write `args.b`.
-    pub fn run_dependent(&self, stream: &Stream, workspace: Workspace<'_>, args: W8A8GemmArgs<'_>) -> Result<()> {
+    pub fn run_dependent(&self, stream: &Stream, _workspace: Workspace<'_>, args: W8A8GemmArgs<'_>) -> Result<()> {
         self.can_implement(&args)?;
         let d = &self.desc;
-        let (ws_ptr, ws_bytes) = match workspace {
-            Workspace::None => (core::ptr::null_mut(), 0usize),
-            Workspace::Borrowed(s) => (s.as_raw().0 as *mut c_void, s.len()),
-        };
         let (c_ptr, ldc) = match &args.c {
             Some(c) => (c.data.as_raw().0 as *const c_void, c.ld),
             None => (core::ptr::null(), 0),
@@ -274,7 +255,7 @@ impl W8A8GemmPlan {
               args.b.ld, c_ptr, ldc, args.d.data.as_raw().0 as *mut c_void, args.d.ld,
               args.scale_a.data.as_raw().0 as *const c_void, args.scale_b.data.as_raw().0 as *const c_void,
               sys::BARACUDA_Q_SCALE_PER_ROW_COL, bias, epilogue_code(d.epilogue), args.alpha, args.beta,
-              ws_ptr, ws_bytes, stream.as_raw() as *mut c_void)
+              core::ptr::null_mut(), 0, stream.as_raw() as *mut c_void)
         };
         map_status(code, "W8A8GemmPlan::run_dependent")
     }

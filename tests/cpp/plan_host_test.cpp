@@ -32,23 +32,6 @@ int main() {
     W8A8GemmPlan::select(desc, pref, false, &again);
     CHECK(cache.count(again.sku()) == 1 && cache.count(raw.sku()) == 0);
     CHECK(p.workspace_size() == 0);
-    CHECK(p.split_k_workspace_size() == 0);  // K = 1024: never split
-    {
-        // optional split-K scratch: small batch against a long-K weight (32 tiles of 128 x 128, 112 K blocks -> 4 slices)
-        W8A8GemmPlan down, down_raw, down_rrr;
-        QGemmDescriptor dd{128, 4096, 14336, LayoutSku::Rcr, EpilogueKind::Identity};
-        CHECK(W8A8GemmPlan::select(dd, pref, false, &down) == Error::Ok);
-        CHECK(down.workspace_size() == 0 && down.split_k_workspace_size() == size_t(4) * 128 * 4096 * 4);
-        CHECK(W8A8GemmPlan::select(dd, pref, true, &down_raw) == Error::Ok);
-        CHECK(down_raw.split_k_workspace_size() == 0);
-        dd.layout = LayoutSku::Rrr;
-        CHECK(W8A8GemmPlan::select(dd, pref, false, &down_rrr) == Error::Ok);
-        CHECK(down_rrr.split_k_workspace_size() == 0);
-        Fp8ScaledGemmPlan f8;
-        dd.layout = LayoutSku::Rcr;
-        CHECK(Fp8ScaledGemmPlan::select(dd, pref, ScaleMode::PerRowCol, false, &f8) == Error::Ok);
-        CHECK(f8.split_k_workspace_size() == size_t(4) * 128 * 4096 * 4);
-    }
 
     QGemmDescriptor rrr = desc;
     rrr.layout = LayoutSku::Rrr;

@@ -1,8 +1,9 @@
-"""GPU parity of the split-K path of the bf16-out GEMMs ([N,K] weights): with the optional scratch a problem of few
-output tiles and long K runs as K slices (raw GEMM into the scratch, then the dependent reduce + epilogue pass).
+"""GPU parity of the split-K form of the GEMMs with [N,K] weights: for problems of few output tiles a thread-block
+cluster of 2 or 4 CTAs shares one 128 x 128 tile, each CTA multiplies a K slice, and the partial sums meet through
+distributed shared memory before the fused epilogue (gemm_q8_splitk_sm100a.cu).
 
-W8A8: bit-exact against the CPU oracle and against the one-pass path of the same call (integer sums, same epilogue
-arithmetic), for the identity epilogue, the bias / activation chains, beta * C and the dependent-launch symbol.
+W8A8: bit-exact against the CPU oracle and against the one-pass kernel (integer sums, same epilogue arithmetic), for
+the identity epilogue, the bias / activation chains, beta * C, the 8-bit-output contract and the dependent-launch symbol.
 FP8: within the benchmark's rel 1e-2 of the oracle (the slices' f32 sums are added in slice order)."""
 import numpy as np
 import pytest
@@ -14,19 +15,13 @@ from helpers import bf16_bits, dev, fp8_case, w8a8_case
 
 pytestmark = pytest.mark.gpu
 
-KEY_SPLIT_K = 6
-KEY_CLUSTER_SPLIT_K = 7
+KEY_CLUSTER_SPLIT_K = 6  # set_tuning: 0 automatic, 1 never, 2 / 4 slices
 
 
 @pytest.fixture(autouse=True)
 def _reset_tuning():
     yield
-    bq.set_tuning(KEY_SPLIT_K, 0)
     bq.set_tuning(KEY_CLUSTER_SPLIT_K, 0)
-
-
-def _scratch(nbytes):
-    return torch.full((max(nbytes, 16),), 0x5A, dtype=torch.uint8, device="cuda")
 
 
 def _w8a8(m, n, k, aq, wq, sa, sb, workspace, epilogue=bq.EpilogueKind.Identity, bias=None, c=None, beta=0.0, alpha=1.0,
@@ -40,140 +35,27 @@ def _w8a8(m, n, k, aq, wq, sa, sb, workspace, epilogue=bq.EpilogueKind.Identity,
     return d
 
 
-def test_workspace_size_query():
-    q = _lib.load().baracuda_kernels_q_gemm_split_k_workspace_size
-    assert q(128, 4096, 14336) == 4 * 128 * 4096 * 4    # 32 tiles on 148 SMs, 112 K blocks: four slices
-    assert q(256, 4096, 14336) == 2 * 256 * 4096 * 4    # 64 tiles: two slices
-    assert q(16, 1024, 4096) == 8 * 16 * 1024 * 4       # eight tiles, 32 K blocks: the maximum of eight slices
-    assert q(128, 4096, 4096) == 0                      # K = 4096 against 32 tiles: the second pass costs what the slices save
-    assert q(512, 4096, 14336) == 0                     # 128 tiles fill the SMs
-    assert q(128, 1024, 1024) == 0                      # K too short
-    assert q(128, 4000, 14336) == 0                     # N not a multiple of 128
-    assert q(0, 4096, 4096) == 0 and q(-1, 4096, 4096) == 0
-    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(128, 4096, 14336))
-    assert plan.workspace_size() == 0 and plan.split_k_workspace_size() == 4 * 128 * 4096 * 4
-    raw = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(128, 4096, 14336), raw_accumulators=True)
-    assert raw.split_k_workspace_size() == 0
+def test_tuning_key_values():
+    for ok in (0, 1, 2, 4):
+        bq.set_tuning(KEY_CLUSTER_SPLIT_K, ok)
+    for bad in (-1, 3, 8):
+        with pytest.raises(bq.InvalidProblem):
+            bq.set_tuning(KEY_CLUSTER_SPLIT_K, bad)
 
 
-@pytest.mark.parametrize("shape", [(128, 1024, 8192), (16, 1024, 4096), (200, 512, 8256), (256, 2048, 8192), (77, 6144, 8192)])
-def test_w8a8_automatic_split_matches_oracle_and_one_pass(oracle, shape):
+@pytest.mark.parametrize("shape", [(128, 4096, 4096), (32, 1024, 14336), (256, 2048, 8192), (77, 6144, 8192)])
+def test_automatic_choice_matches_oracle_and_one_pass(oracle, shape):
+    """Shapes the dispatch splits by itself (32 / 8 / 32 / 48 tiles against 32 to 112 K blocks)."""
     m, n, k = shape
     aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n + k)
-    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k))
-    need = plan.split_k_workspace_size()
-    assert need > 0
     ops = [dev(aq), dev(wq), dev(sa), dev(sb)]
+    auto = _w8a8(m, n, k, *ops, None)
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, 1)
     one_pass = _w8a8(m, n, k, *ops, None)
-    split = _w8a8(m, n, k, *ops, _scratch(need))
     want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
-    assert oracle.compare_bitexact(want, bf16_bits(split).reshape(m, n)) == -1
-    assert torch.equal(split.view(torch.int16), one_pass.view(torch.int16))
+    assert oracle.compare_bitexact(want, bf16_bits(auto).reshape(m, n)) == -1
+    assert torch.equal(auto.view(torch.int16), one_pass.view(torch.int16))
 
-
-@pytest.mark.parametrize("slices", [2, 3, 5, 8])
-def test_w8a8_forced_slices_with_k_tail_and_many_tiles(oracle, slices):
-    """K = 2240 is 17.5 K blocks (the last one half out of range); 1024 x 1024 gives 64 tiles per slice, so CTAs walk
-    several (tile, slice) pairs."""
-    m, n, k = 1000, 1024, 2240
-    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=slices)
-    bq.set_tuning(KEY_SPLIT_K, slices)
-    got = _w8a8(m, n, k, dev(aq), dev(wq), dev(sa), dev(sb), _scratch(slices * m * n * 4))
-    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
-    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
-
-
-@pytest.mark.parametrize("epilogue", [bq.EpilogueKind.Bias, bq.EpilogueKind.BiasRelu, bq.EpilogueKind.BiasGelu,
-                                      bq.EpilogueKind.BiasSilu])
-def test_w8a8_epilogue_chain_beta_and_alpha_equal_the_one_pass_bits(oracle, epilogue):
-    m, n, k = 96, 2048, 4096
-    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=11)
-    rng = np.random.default_rng(5)
-    bias = dev(rng.standard_normal(n).astype(np.float32))
-    c = dev(rng.standard_normal((m, n)).astype(np.float32)).to(torch.bfloat16)
-    ops = [dev(aq), dev(wq), dev(sa), dev(sb)]
-    kw = dict(epilogue=epilogue, bias=bias, c=c, beta=0.5, alpha=0.75)
-    one_pass = _w8a8(m, n, k, *ops, None, **kw)
-    need = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, epilogue=epilogue)).split_k_workspace_size()
-    assert need > 0
-    split = _w8a8(m, n, k, *ops, _scratch(need), **kw)
-    assert torch.equal(split.view(torch.int16), one_pass.view(torch.int16))
-    # and as a programmatic dependent launch
-    split_pdl = _w8a8(m, n, k, *ops, _scratch(need), dependent=True, **kw)
-    assert torch.equal(split_pdl.view(torch.int16), one_pass.view(torch.int16))
-
-
-def test_small_or_misaligned_scratch_keeps_the_one_pass_path(oracle):
-    m, n, k = 128, 1024, 4096
-    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=3)
-    ops = [dev(aq), dev(wq), dev(sa), dev(sb)]
-    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), sa, sb)
-    small = _scratch(m * n * 4)  # room for one slice only
-    got = _w8a8(m, n, k, *ops, small)
-    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
-    assert bool((small == 0x5A).all())  # untouched
-    big = _scratch(8 * m * n * 4 + 16)
-    got = _w8a8(m, n, k, *ops, big[4:])  # not 16-byte aligned
-    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
-    assert bool((big == 0x5A).all())
-    bq.set_tuning(KEY_SPLIT_K, 1)  # switched off
-    got = _w8a8(m, n, k, *ops, big)
-    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
-    assert bool((big == 0x5A).all())
-
-
-@pytest.mark.parametrize("mode", ["per_row_col", "per_tensor"])
-def test_fp8_split_within_tolerance(oracle, mode):
-    m, n, k = 128, 2048, 4096
-    per_tensor = mode == "per_tensor"
-    aq, wq, sa, sb = fp8_case(oracle, m, n, k, seed=9, per_tensor=per_tensor)
-    scale_mode = bq.SCALE_PER_TENSOR if per_tensor else bq.SCALE_PER_ROW_COL
-    plan = bq.Fp8ScaledGemmPlan.select(None, bq.QGemmDescriptor(m, n, k), scale_mode=scale_mode)
-    need = plan.split_k_workspace_size()
-    assert need > 0
-    sa_d, sb_d = dev(sa), dev(sb)
-    outs = []
-    for ws in (None, _scratch(need)):
-        d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-        plan.run(None, ws, bq.QGemmArgs(a=dev(aq), b=dev(wq), d=d, scale_a=sa_d, scale_b=sb_d))
-        torch.cuda.synchronize()
-        assert bq.device_status() == 0
-        outs.append(d.to(torch.float32).cpu().numpy())
-    acc = oracle.gemm_e4m3_f32(aq, wq, oracle.RCR, m, n, k)
-    want = oracle.bf16_bits_to_f32(oracle.scale_f32_bf16(acc, sa, sb))
-    floor = 1e-2 * float(np.abs(want).max()) * 1e-2
-    assert oracle.compare_tolerant(want, outs[1], 1e-2, floor) == -1
-    assert oracle.compare_tolerant(outs[0], outs[1], 1e-2, floor) == -1
-
-
-def test_split_k_in_a_cuda_graph(oracle):
-    """The GEMM + dependent reduce pair captured once and replayed on fresh activations."""
-    m, n, k = 64, 2048, 4096
-    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=21)
-    aq2, _, sa2, _ = w8a8_case(oracle, m, n, k, seed=22)
-    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k))
-    ws = _scratch(plan.split_k_workspace_size())
-    a_d, w_d, sa_d, sb_d = dev(aq), dev(wq), dev(sa), dev(sb)
-    d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
-    args = bq.QGemmArgs(a=a_d, b=w_d, d=d, scale_a=sa_d, scale_b=sb_d)
-    plan.run(None, ws, args)  # warm-up outside the capture (function attributes, tensor-map encoder)
-    torch.cuda.synchronize()
-    stream = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph, stream=stream):
-            plan.run(stream, ws, args)
-    a_d.copy_(dev(aq2))
-    sa_d.copy_(dev(sa2))
-    d.zero_()
-    graph.replay()
-    torch.cuda.synchronize()
-    assert bq.device_status() == 0
-    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq2, wq, oracle.RCR, m, n, k), sa2, sb)
-    assert oracle.compare_bitexact(want, bf16_bits(d).reshape(m, n)) == -1
-
-
-# ---- split-K inside thread-block clusters (partial sums exchanged through distributed shared memory, no scratch) ----
 
 @pytest.mark.parametrize("slices", [2, 4])
 @pytest.mark.parametrize("shape", [(128, 1024, 4096), (16, 1024, 2048), (200, 520, 2240), (77, 100, 1024), (300, 136, 640)])
