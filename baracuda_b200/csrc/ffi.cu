@@ -526,6 +526,7 @@ int32_t baracuda_kernels_smoothquant_linear_w8a8_bf16_sm100a_run(
     g.force_pair_tile_n = t_tuning.force_pair_tile_n;
     g.direct_stores = t_tuning.direct_stores;
     g.epilogue_warps = t_tuning.epilogue_warps;
+    g.cluster_split_k = t_tuning.cluster_split_k;
     return bq::launch_gemm_q8(g, static_cast<cudaStream_t>(stream));
 }
 

@@ -163,3 +163,20 @@ def test_cluster_split_in_a_cuda_graph_and_automatic_choice(oracle):
     assert bq.device_status() == 0
     want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq2, wq, oracle.RCR, m, n, k), sa2, sb)
     assert oracle.compare_bitexact(want, bf16_bits(d).reshape(m, n)) == -1
+
+
+@pytest.mark.parametrize("slices", [0, 4])
+def test_cluster_split_smoothquant_per_tensor_activation_scale(oracle, slices):
+    """SmoothQuantLinearPlan (one activation scale passed by value) on a small batch: the bits of the W8A8 kernel fed a
+    constant scale_a vector, through the split-K kernel (automatic choice and forced)."""
+    m, n, k = 64, 1024, 4096
+    aq, wq, _, sb = w8a8_case(oracle, m, n, k, seed=55)
+    act_scale = np.float32(0.0173)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, wq, oracle.RCR, m, n, k), np.full(m, act_scale, dtype=np.float32), sb)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    plan = bq.SmoothQuantLinearPlan.select(None, bq.SmoothQuantLinearDescriptor(m, n, k, act_scale=float(act_scale)))
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, slices)
+    plan.run(None, None, bq.SmoothQuantLinearArgs(act_q=dev(aq), weight_q=dev(wq), weight_scale=dev(sb), output=out))
+    torch.cuda.synchronize()
+    assert bq.device_status() == 0
+    assert oracle.compare_bitexact(want, bf16_bits(out).reshape(m, n)) == -1
