@@ -910,7 +910,7 @@ int32_t baracuda_kernels_q_set_tuning(int32_t key, int32_t value) {
             t_tuning.epilogue_warps = value;
             return bq::BQ_STATUS_OK;
         case 6:
-            if (value != 0 && value != 1 && value != 2 && value != 4) return bq::BQ_STATUS_INVALID_PROBLEM;
+            if (value != 0 && value != 1 && value != 2 && value != 4 && value != 256) return bq::BQ_STATUS_INVALID_PROBLEM;
             t_tuning.cluster_split_k = value;
             return bq::BQ_STATUS_OK;
         case 2:

@@ -479,35 +479,65 @@ float one_pass_cost(int64_t m, int64_t n, int64_t k, int sms, bool allow_pair, i
 // 32 -> 16 us, K = 8192 20.3 -> 12.2 us, 8192 x 8192 20.8 -> 17.5 us with two slices).
 constexpr int SPLIT_MIN_KB = 16;  // K >= 2048 bytes
 constexpr float CLUSTER_SPLIT_FIXED_US = 1.0f;
+constexpr float COST_KB_WIDE_SPLIT = 0.39f;   // 128 x 256 tiles, every SM busy
+constexpr float WIDE_SPLIT_FIXED_US = 2.3f;   // two meetings of the cluster, 64 KB exchanged per CTA, 128 columns of epilogue
 
-int cluster_split_slices(const GemmDesc& g, int sms) {
+struct SplitChoice {
+    int slices = 0;  // 0 = none
+    int bn = 128;
+};
+
+SplitChoice cluster_split_choice(const GemmDesc& g, int sms) {
+    SplitChoice none, pick;
     if (g.cluster_split_k == 1 || g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.force_block_n != 0 ||
         g.b_layout != BQ_LAYOUT_RCR) {
-        return 0;
+        return none;
     }
     const int64_t num_kb = (static_cast<int64_t>(g.k) + BLOCK_K - 1) / BLOCK_K;
-    const int64_t tiles = ((static_cast<int64_t>(g.m) + BLOCK_M - 1) / BLOCK_M) * ((static_cast<int64_t>(g.n) + 127) / 128);
-    if (g.cluster_split_k == 2 || g.cluster_split_k == 4) {
-        const int s = g.cluster_split_k;
-        const int64_t kbps = (num_kb + s - 1) / s;
-        return (num_kb >= s && (num_kb + kbps - 1) / kbps == s && gemm_q8_cluster_split_k_max_clusters(g.kind, s) > 0) ? s : 0;
+    const int64_t m_tiles = (static_cast<int64_t>(g.m) + BLOCK_M - 1) / BLOCK_M;
+    if (g.cluster_split_k != 0) {  // forced: 2 / 4 slices of 128-wide tiles, 256 = two slices of 256-wide tiles
+        pick.slices = g.cluster_split_k == 256 ? 2 : g.cluster_split_k;
+        pick.bn = g.cluster_split_k == 256 ? 256 : 128;
+        const int64_t kbps = (num_kb + pick.slices - 1) / pick.slices;
+        const bool ok = num_kb >= pick.slices && (num_kb + kbps - 1) / kbps == pick.slices &&
+                        gemm_q8_cluster_split_k_max_clusters(g.kind, pick.slices, pick.bn) > 0;
+        return ok ? pick : none;
     }
-    if (num_kb < SPLIT_MIN_KB || 2 * tiles > sms) return 0;
+    if (num_kb < SPLIT_MIN_KB) return none;
     const float hbm = static_cast<float>(g.n) * static_cast<float>(g.k) / HBM_BYTES_PER_US;
     float best = one_pass_cost(g.m, g.n, g.k, sms, true, nullptr) - 1.0f;
-    int best_s = 0;
-    for (int s = 2; s <= 4; s += 2) {
-        const int64_t kbps = (num_kb + s - 1) / s;
-        if (s * tiles > sms || kbps < 4 || (num_kb + kbps - 1) / kbps != s) continue;
-        if (tiles > gemm_q8_cluster_split_k_max_clusters(g.kind, s)) continue;
-        const float walk = static_cast<float>(kbps) * COST_KB_128;
-        const float c = (walk > hbm ? walk : hbm) + CLUSTER_SPLIT_FIXED_US;
-        if (c < best) {
-            best = c;
-            best_s = s;
+    // small batches: 128 x 128 tiles on at most half of the SMs, two or four slices
+    const int64_t tiles = m_tiles * ((static_cast<int64_t>(g.n) + 127) / 128);
+    if (2 * tiles <= sms) {
+        for (int s = 2; s <= 4; s += 2) {
+            const int64_t kbps = (num_kb + s - 1) / s;
+            if (s * tiles > sms || kbps < 4 || (num_kb + kbps - 1) / kbps != s) continue;
+            if (tiles > gemm_q8_cluster_split_k_max_clusters(g.kind, s, 128)) continue;
+            const float walk = static_cast<float>(kbps) * COST_KB_128;
+            const float c = (walk > hbm ? walk : hbm) + CLUSTER_SPLIT_FIXED_US;
+            if (c < best) {
+                best = c;
+                pick.slices = s;
+                pick.bn = 128;
+            }
         }
     }
-    return best_s;
+    // three or more row blocks against few columns and a long K (prefill at M = 512 against the down projection): the
+    // 128 x 128 tiles already fill the SMs, but each SM ingests 32 KB per K block for a 128 x 128 tile; two CTAs per
+    // 128 x 256 tile, half of K each, ingest 48 KB per K block for twice the tile.  Fitted to CUDA-graph timing at
+    // M = 384..1024 (512 x 4096 x 14336 33.7 -> 29.6 us, 512 x 4096 x 8192 22.2 -> 20.2, 1024 x 2048 x 8192 21.8 -> 19.4;
+    // at K = 4096 the exchange costs what the walk saves).
+    const int64_t tiles256 = m_tiles * ((static_cast<int64_t>(g.n) + 255) / 256);
+    if (g.m > 256 && num_kb >= 60 && 2 * tiles256 <= sms && tiles256 <= gemm_q8_cluster_split_k_max_clusters(g.kind, 2, 256)) {
+        const float walk = static_cast<float>((num_kb + 1) / 2) * COST_KB_WIDE_SPLIT;
+        const float c = (walk > hbm ? walk : hbm) + WIDE_SPLIT_FIXED_US;
+        if (c < best) {
+            best = c;
+            pick.slices = 2;
+            pick.bn = 256;
+        }
+    }
+    return pick;
 }
 
 template <uint32_t KIND, bool RAW>
@@ -515,8 +545,8 @@ int32_t launch_kind(const GemmDesc& g, cudaStream_t stream) {
     const int sms = sm_count_impl();
     if (sms <= 0) return BQ_STATUS_LAUNCH_FAILURE;
     if constexpr (!RAW) {
-        const int cs = cluster_split_slices(g, sms);
-        if (cs > 1) return launch_gemm_q8_cluster_split_k(g, cs, stream);
+        const SplitChoice cs = cluster_split_choice(g, sms);
+        if (cs.slices > 1) return launch_gemm_q8_cluster_split_k(g, cs.slices, cs.bn, stream);
     }
     const int64_t m_tiles = (g.m + BLOCK_M - 1) / BLOCK_M;
     auto tiles_at = [&](int bn) { return m_tiles * ((g.n + bn - 1) / bn); };

@@ -62,15 +62,15 @@ struct GemmDesc {
     // gated-MLP epilogue (bf16 output, weights [N,K] only): n = 2F interleaved gate/up rows in blocks of 32, d is [M, F]
     int32_t swiglu;
     int32_t pdl;  // 1: launch with programmatic stream serialization (the caller promises the previous kernel does not write b)
-    int32_t cluster_split_k;  // split-K inside a thread-block cluster: 0 = choose, 1 = never, 2 / 4 = that many slices
+    int32_t cluster_split_k;  // split-K inside a thread-block cluster: 0 = choose, 1 = never, 2 / 4 = that many slices of 128-wide tiles, 256 = two slices of 256-wide tiles
 };
 
-// Split-K without scratch: clusters of `slices` (2 or 4) CTAs share a 128 x 128 tile and add their partial sums through
-// distributed shared memory (gemm_q8_splitk_sm100a.cu).  bf16 or 8-bit output, [N,K] weights, any M and N;
-// every slice needs at least one K block.
-int32_t launch_gemm_q8_cluster_split_k(const GemmDesc& g, int32_t slices, cudaStream_t stream);
+// Split-K without scratch: clusters of `slices` CTAs share a 128 x block_n tile and add their partial sums through
+// distributed shared memory (gemm_q8_splitk_sm100a.cu); (slices, block_n) is (2, 128), (4, 128) or (2, 256).  bf16 or
+// 8-bit output, [N,K] weights, any M and N; every slice needs at least one K block.
+int32_t launch_gemm_q8_cluster_split_k(const GemmDesc& g, int32_t slices, int32_t block_n, cudaStream_t stream);
 // Clusters of that kernel the current device holds at once (0: cannot run); cached per device.
-int gemm_q8_cluster_split_k_max_clusters(int32_t kind, int32_t slices);
+int gemm_q8_cluster_split_k_max_clusters(int32_t kind, int32_t slices, int32_t block_n);
 int32_t read_and_clear_gemm_splitk_device_status();
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);

@@ -15,7 +15,7 @@ from helpers import bf16_bits, dev, fp8_case, w8a8_case
 
 pytestmark = pytest.mark.gpu
 
-KEY_CLUSTER_SPLIT_K = 6  # set_tuning: 0 automatic, 1 never, 2 / 4 slices
+KEY_CLUSTER_SPLIT_K = 6  # set_tuning: 0 automatic, 1 never, 2 / 4 slices of 128-wide tiles, 256 = two slices of 256-wide tiles
 
 
 @pytest.fixture(autouse=True)
@@ -36,7 +36,7 @@ def _w8a8(m, n, k, aq, wq, sa, sb, workspace, epilogue=bq.EpilogueKind.Identity,
 
 
 def test_tuning_key_values():
-    for ok in (0, 1, 2, 4):
+    for ok in (0, 1, 2, 4, 256):
         bq.set_tuning(KEY_CLUSTER_SPLIT_K, ok)
     for bad in (-1, 3, 8):
         with pytest.raises(bq.InvalidProblem):
@@ -57,7 +57,7 @@ def test_automatic_choice_matches_oracle_and_one_pass(oracle, shape):
     assert torch.equal(auto.view(torch.int16), one_pass.view(torch.int16))
 
 
-@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("slices", [2, 4, 256])
 @pytest.mark.parametrize("shape", [(128, 1024, 4096), (16, 1024, 2048), (200, 520, 2240), (77, 100, 1024), (300, 136, 640)])
 def test_cluster_split_w8a8_matches_oracle(oracle, shape, slices):
     """Ragged M (partly empty row blocks), N that ends inside a tile and inside a 32-column block, an odd output pitch
@@ -70,7 +70,7 @@ def test_cluster_split_w8a8_matches_oracle(oracle, shape, slices):
     assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
 
 
-@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("slices", [2, 4, 256])
 @pytest.mark.parametrize("epilogue", [bq.EpilogueKind.Bias, bq.EpilogueKind.BiasRelu, bq.EpilogueKind.BiasGelu,
                                       bq.EpilogueKind.BiasSilu])
 def test_cluster_split_epilogue_chain_equals_the_one_pass_bits(oracle, epilogue, slices):
@@ -90,7 +90,7 @@ def test_cluster_split_epilogue_chain_equals_the_one_pass_bits(oracle, epilogue,
     assert torch.equal(split_pdl.view(torch.int16), one_pass.view(torch.int16))
 
 
-@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("slices", [2, 4, 256])
 def test_cluster_split_8bit_output_with_bias_and_c(oracle, slices):
     """The reference's own contract, D = sat_s8(alpha * acc + beta * C + bias), on the cluster kernel."""
     m, n, k = 100, 392, 2048
@@ -118,7 +118,7 @@ def test_cluster_split_8bit_output_with_bias_and_c(oracle, slices):
     assert np.array_equal(outs[slices], outs[1])
 
 
-@pytest.mark.parametrize("slices", [2, 4])
+@pytest.mark.parametrize("slices", [2, 4, 256])
 @pytest.mark.parametrize("mode", ["per_row_col", "per_tensor"])
 def test_cluster_split_fp8_within_tolerance(oracle, mode, slices):
     m, n, k = 128, 640, 4096
