@@ -489,23 +489,26 @@ struct SplitChoice {
 
 SplitChoice cluster_split_choice(const GemmDesc& g, int sms) {
     SplitChoice none, pick;
-    if (g.cluster_split_k == 1 || g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.force_block_n != 0 ||
-        g.b_layout != BQ_LAYOUT_RCR) {
-        return none;
-    }
+    if (g.cluster_split_k == 1 || g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.force_block_n != 0) return none;
+    const bool rrr = g.b_layout == BQ_LAYOUT_RRR;  // row-major weights: the 128-wide shapes only
     const int64_t num_kb = (static_cast<int64_t>(g.k) + BLOCK_K - 1) / BLOCK_K;
     const int64_t m_tiles = (static_cast<int64_t>(g.m) + BLOCK_M - 1) / BLOCK_M;
     if (g.cluster_split_k != 0) {  // forced: 2 / 4 slices of 128-wide tiles, 256 = two slices of 256-wide tiles
         pick.slices = g.cluster_split_k == 256 ? 2 : g.cluster_split_k;
         pick.bn = g.cluster_split_k == 256 ? 256 : 128;
         const int64_t kbps = (num_kb + pick.slices - 1) / pick.slices;
-        const bool ok = num_kb >= pick.slices && (num_kb + kbps - 1) / kbps == pick.slices &&
+        const bool ok = num_kb >= pick.slices && (num_kb + kbps - 1) / kbps == pick.slices && !(rrr && pick.bn != 128) &&
                         gemm_q8_cluster_split_k_max_clusters(g.kind, pick.slices, pick.bn) > 0;
         return ok ? pick : none;
     }
     if (num_kb < SPLIT_MIN_KB) return none;
     const float hbm = static_cast<float>(g.n) * static_cast<float>(g.k) / HBM_BYTES_PER_US;
     float best = one_pass_cost(g.m, g.n, g.k, sms, true, nullptr) - 1.0f;
+    if (rrr) {  // the one-pass form of this layout is the CTA-pair kernel, whatever the shape
+        const int64_t pair_tiles = ((static_cast<int64_t>(g.m) + 255) / 256) * ((static_cast<int64_t>(g.n) + 255) / 256);
+        const float c = wave_cost(pair_tiles, sms / 2 > 0 ? sms / 2 : 1, COST_KB_PAIR, num_kb) + PAIR_FIXED_US;
+        best = (c > hbm ? c : hbm) - 1.0f;
+    }
     // small batches: 128 x 128 tiles on at most half of the SMs, two or four slices
     const int64_t tiles = m_tiles * ((static_cast<int64_t>(g.n) + 127) / 128);
     if (2 * tiles <= sms) {
@@ -528,7 +531,7 @@ SplitChoice cluster_split_choice(const GemmDesc& g, int sms) {
     // M = 384..1024 (512 x 4096 x 14336 33.7 -> 29.6 us, 512 x 4096 x 8192 22.2 -> 20.2, 1024 x 2048 x 8192 21.8 -> 19.4;
     // at K = 4096 the exchange costs what the walk saves).
     const int64_t tiles256 = m_tiles * ((static_cast<int64_t>(g.n) + 255) / 256);
-    if (g.m > 256 && num_kb >= 60 && 2 * tiles256 <= sms && tiles256 <= gemm_q8_cluster_split_k_max_clusters(g.kind, 2, 256)) {
+    if (!rrr && g.m > 256 && num_kb >= 60 && 2 * tiles256 <= sms && tiles256 <= gemm_q8_cluster_split_k_max_clusters(g.kind, 2, 256)) {
         const float walk = static_cast<float>((num_kb + 1) / 2) * COST_KB_WIDE_SPLIT;
         const float c = (walk > hbm ? walk : hbm) + WIDE_SPLIT_FIXED_US;
         if (c < best) {

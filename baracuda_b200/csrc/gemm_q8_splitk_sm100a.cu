@@ -1,6 +1,6 @@
 // Split-K form of the 8-bit tensor-core GEMM for problems whose output tiles leave SMs idle (small batches against one
 // layer's weight; prefill at M = 512 against 4096 columns): a thread-block cluster of S CTAs shares one 128 x BN output
-// tile (S = 2 or 4 with BN = 128, S = 2 with BN = 256), CTA s of the cluster multiplies K slice s, and the partial sums
+// tile (S = 2 or 4 with BN = 128 -- either weight layout --, S = 2 with BN = 256), CTA s multiplies K slice s, and the partial sums
 // meet through distributed shared memory -- no scratch in global memory, no second launch.
 //
 // Per CTA (six warps, the roles of gemm_q8_kernel): warp 0 streams its slice's A and B tiles through a ring of
@@ -71,12 +71,15 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
                  : "memory");
 }
 
-template <uint32_t KIND, int S, int BN>
+// B_MN: the weight is row-major [K, N] (N contiguous): its tile is loaded as [128 K-rows x 128 N-bytes] and described to
+// the MMA as an MN-major operand (128-wide tiles only: one 128-byte swizzle atom of N).
+template <uint32_t KIND, int S, int BN, bool B_MN = false>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 gemm_q8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const GemmParams p) {
     using L = SkSmem<S, BN>;
     constexpr int STAGES = L::STAGES;
+    static_assert(!B_MN || BN == 128, "row-major weights: one swizzle atom of N per tile");
     extern __shared__ uint8_t sk_smem_raw[];
     // every CTA of the cluster rounds up by the same amount (same kernel, same static layout), so an offset into this
     // CTA's window is the same offset in a partner's
@@ -143,8 +146,12 @@ gemm_q8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 first = nk < STAGES ? nk : STAGES;
                 for (int i = 0; i < first; ++i) {
                     mbar_arrive_expect_tx(&full_bar[i], L::STAGE_BYTES);
-                    tma_load_2d(tiles + i * L::STAGE_BYTES + L::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * SK_BLOCK_K,
-                                n_blk * BN);
+                    if constexpr (B_MN) {
+                        tma_load_2d(tiles + i * L::STAGE_BYTES + L::A_BYTES, &tmap_b, &full_bar[i], n_blk * BN, (kb0 + i) * SK_BLOCK_K);
+                    } else {
+                        tma_load_2d(tiles + i * L::STAGE_BYTES + L::A_BYTES, &tmap_b, &full_bar[i], (kb0 + i) * SK_BLOCK_K,
+                                    n_blk * BN);
+                    }
                 }
                 asm volatile("griddepcontrol.wait;" ::: "memory");
                 for (int i = 0; i < first; ++i) {
@@ -161,12 +168,16 @@ gemm_q8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 uint8_t* st = tiles + stage * L::STAGE_BYTES;
                 mbar_arrive_expect_tx(&full_bar[stage], L::STAGE_BYTES);
                 tma_load_2d(st, &tmap_a, &full_bar[stage], (kb0 + i) * SK_BLOCK_K, m_blk * SK_BLOCK_M);
-                tma_load_2d(st + L::A_BYTES, &tmap_b, &full_bar[stage], (kb0 + i) * SK_BLOCK_K, n_blk * BN);
+                if constexpr (B_MN) {
+                    tma_load_2d(st + L::A_BYTES, &tmap_b, &full_bar[stage], n_blk * BN, (kb0 + i) * SK_BLOCK_K);
+                } else {
+                    tma_load_2d(st + L::A_BYTES, &tmap_b, &full_bar[stage], (kb0 + i) * SK_BLOCK_K, n_blk * BN);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(KIND, SK_BLOCK_M, BN);
+            constexpr uint32_t idesc = umma_idesc(KIND, SK_BLOCK_M, BN, B_MN);
             bool ok = true;
             for (int i = 0; i < nk; ++i) {
                 const int stage = i % STAGES;
@@ -179,11 +190,14 @@ gemm_q8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                 tc_fence_after_sync();
                 const uint32_t a_addr = smem_u32(tiles + stage * L::STAGE_BYTES);
                 const uint64_t a_desc = umma_desc_kmajor_sw128(a_addr);
-                const uint64_t b_desc = umma_desc_kmajor_sw128(a_addr + L::A_BYTES);
+                const uint64_t b_desc = B_MN ? umma_desc_mnmajor_sw128(a_addr + L::A_BYTES, L::B_BYTES, 1024)
+                                             : umma_desc_kmajor_sw128(a_addr + L::A_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < SK_BLOCK_K / SK_UMMA_K; ++ks) {
                     const uint64_t koff = static_cast<uint64_t>((ks * SK_UMMA_K) >> 4);
-                    umma_ss<KIND>(tmem_base, a_desc + koff, b_desc + koff, idesc, (i | ks) != 0 ? 1u : 0u);
+                    // MN-major: 32 K-rows are four 1024-byte atoms further down the tile
+                    const uint64_t boff = B_MN ? static_cast<uint64_t>((ks * SK_UMMA_K * 128) >> 4) : koff;
+                    umma_ss<KIND>(tmem_base, a_desc + koff, b_desc + boff, idesc, (i | ks) != 0 ? 1u : 0u);
                 }
                 umma_commit(&empty_bar[stage]);
             }
@@ -335,10 +349,10 @@ gemm_q8_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
 }
 
-template <uint32_t KIND, int S, int BN>
+template <uint32_t KIND, int S, int BN, bool B_MN>
 int32_t launch_splitk(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, int* max_clusters_out) {
     using L = SkSmem<S, BN>;
-    auto kern = gemm_q8_splitk_kernel<KIND, S, BN>;
+    auto kern = gemm_q8_splitk_kernel<KIND, S, BN, B_MN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess) {
         (void)cudaGetLastError();
         return BQ_STATUS_LAUNCH_FAILURE;
@@ -371,7 +385,11 @@ int32_t launch_splitk(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, 
     cfg.numAttrs = g.pdl ? 2 : 1;
     CUtensorMap map_a, map_b;
     if (!make_kmajor_tensor_map(&map_a, g.a, g.m, g.k, g.lda, SK_BLOCK_M)) return BQ_STATUS_LAUNCH_FAILURE;
-    if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, BN)) return BQ_STATUS_LAUNCH_FAILURE;
+    if constexpr (B_MN) {
+        if (!make_mnmajor_tensor_map(&map_b, g.b, g.k, g.n, g.ldb, SK_BLOCK_K)) return BQ_STATUS_LAUNCH_FAILURE;
+    } else {
+        if (!make_kmajor_tensor_map(&map_b, g.b, g.n, g.k, g.ldb, BN)) return BQ_STATUS_LAUNCH_FAILURE;
+    }
     GemmParams p;
     p.d = g.d;
     p.ldd = g.ldd;
@@ -418,24 +436,32 @@ int32_t launch_splitk(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, 
     return BQ_STATUS_OK;
 }
 
-template <int S, int BN>
+template <int S, int BN, bool B_MN>
 int32_t launch_splitk_kind(const GemmDesc& g, int kb_per_slice, cudaStream_t stream, int* max_clusters_out) {
-    return g.kind == BQ_KIND_S8 ? launch_splitk<UMMA_KIND_I8, S, BN>(g, kb_per_slice, stream, max_clusters_out)
-                                : launch_splitk<UMMA_KIND_F8, S, BN>(g, kb_per_slice, stream, max_clusters_out);
+    return g.kind == BQ_KIND_S8 ? launch_splitk<UMMA_KIND_I8, S, BN, B_MN>(g, kb_per_slice, stream, max_clusters_out)
+                                : launch_splitk<UMMA_KIND_F8, S, BN, B_MN>(g, kb_per_slice, stream, max_clusters_out);
 }
 
 int32_t launch_splitk_shape(const GemmDesc& g, int slices, int block_n, int kb_per_slice, cudaStream_t stream,
                             int* max_clusters_out) {
-    if (block_n == 256 && slices == 2) return launch_splitk_kind<2, 256>(g, kb_per_slice, stream, max_clusters_out);
-    if (block_n == 128 && slices == 2) return launch_splitk_kind<2, 128>(g, kb_per_slice, stream, max_clusters_out);
-    if (block_n == 128 && slices == 4) return launch_splitk_kind<4, 128>(g, kb_per_slice, stream, max_clusters_out);
+    const bool mn = g.b_layout == BQ_LAYOUT_RRR;
+    if (block_n == 256 && slices == 2 && !mn) return launch_splitk_kind<2, 256, false>(g, kb_per_slice, stream, max_clusters_out);
+    if (block_n == 128 && slices == 2) {
+        return mn ? launch_splitk_kind<2, 128, true>(g, kb_per_slice, stream, max_clusters_out)
+                  : launch_splitk_kind<2, 128, false>(g, kb_per_slice, stream, max_clusters_out);
+    }
+    if (block_n == 128 && slices == 4) {
+        return mn ? launch_splitk_kind<4, 128, true>(g, kb_per_slice, stream, max_clusters_out)
+                  : launch_splitk_kind<4, 128, false>(g, kb_per_slice, stream, max_clusters_out);
+    }
     return BQ_STATUS_INVALID_PROBLEM;
 }
 
 }  // namespace
 
 int32_t launch_gemm_q8_cluster_split_k(const GemmDesc& g, int32_t slices, int32_t block_n, cudaStream_t stream) {
-    if (g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.b_layout != BQ_LAYOUT_RCR || g.k <= 0) {
+    if (g.raw_out || g.swiglu || g.n_peers > 0 || g.rs_world > 0 || g.k <= 0 ||
+        (g.b_layout == BQ_LAYOUT_RRR && block_n != 128)) {
         return BQ_STATUS_INVALID_PROBLEM;
     }
     const int num_kb = (g.k + SK_BLOCK_K - 1) / SK_BLOCK_K;

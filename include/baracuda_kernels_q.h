@@ -78,7 +78,7 @@ extern "C" {
  * adds of its test oracle, crates/baracuda-kernels/tests/int8_rrr_smoke.rs:76-131); up to that K the two agree
  * bit for bit, beyond it tcgen05's behaviour is unspecified, so the call is refused rather than answered differently.
  * Small batches (the 128 x 128 output tiles cover at most half of the SMs, K >= 2048): the bf16-out and 8-bit-out GEMMs
- * with [N,K] weights run as 2 or 4 K slices per tile on otherwise idle SMs -- a thread-block cluster per tile whose CTAs
+ * (either weight layout) run as 2 or 4 K slices per tile on otherwise idle SMs -- a thread-block cluster per tile whose CTAs
  * add their partial sums through distributed shared memory before the same epilogue (and, for M > 256 against few
  * columns and K >= 7680, as two slices per 128 x 256 tile).  Nothing changes for the caller:
  * no scratch, one launch; the int8 result keeps its bits, the e4m3 result adds the slices' f32 sums in slice order
@@ -706,8 +706,8 @@ int32_t baracuda_q_nccl_all_gather_bytes(void* comm, int32_t world, const void* 
  *   key 2  CTA-pair tile width: 0 automatic, 256, 224, 192, 128; 2 = the mixed 256 / 128 schedule;
  *   key 4  GEMM epilogue store path: 0 automatic, 1 per-thread direct stores, 2 rows staged through shared memory.
  *   key 5  CTA-pair GEMM epilogue warps: 0 automatic (eight for gelu / silu chains on at most two waves of tiles), 4, 8.
- *   key 6  split-K inside thread-block clusters (bf16-out and 8-bit-out GEMMs with [N,K] weights): 0 automatic, 1 never,
- *          2 or 4 = that many K slices of 128 x 128 tiles, 256 = two slices of 128 x 256 tiles, on any shape with at
+ *   key 6  split-K inside thread-block clusters (bf16-out and 8-bit-out GEMMs): 0 automatic, 1 never, 2 or 4 = that many
+ *          K slices of 128 x 128 tiles, 256 = two slices of 128 x 256 tiles ([N,K] weights only), on any shape with at
  *          least that many 128-byte K blocks.
  * Any other key or value returns 2.
  * selftest_bounded_wait: launches one thread that waits, for at most limit_cycles SM clock cycles

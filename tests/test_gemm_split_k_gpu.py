@@ -25,8 +25,8 @@ def _reset_tuning():
 
 
 def _w8a8(m, n, k, aq, wq, sa, sb, workspace, epilogue=bq.EpilogueKind.Identity, bias=None, c=None, beta=0.0, alpha=1.0,
-          dependent=False):
-    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, epilogue=epilogue))
+          dependent=False, layout=bq.LayoutSku.Rcr):
+    plan = bq.W8A8GemmPlan.select(None, bq.QGemmDescriptor(m, n, k, layout=layout, epilogue=epilogue))
     d = torch.full((m, n), 123.0, dtype=torch.bfloat16, device="cuda")
     args = bq.QGemmArgs(a=aq, b=wq, d=d, scale_a=sa, scale_b=sb, bias=bias, c=c, beta=beta, alpha=alpha)
     plan.run(None, workspace, args, dependent_launch=dependent)
@@ -180,3 +180,20 @@ def test_cluster_split_smoothquant_per_tensor_activation_scale(oracle, slices):
     torch.cuda.synchronize()
     assert bq.device_status() == 0
     assert oracle.compare_bitexact(want, bf16_bits(out).reshape(m, n)) == -1
+
+
+@pytest.mark.parametrize("slices", [0, 2, 4])
+@pytest.mark.parametrize("shape", [(128, 1024, 4096), (16, 1024, 2048), (200, 528, 2240), (77, 112, 1024), (300, 144, 640)])
+def test_cluster_split_row_major_weights(oracle, shape, slices):
+    """Weights stored [K, N] (the layout of the reference's bespoke GEMMs): the tile arrives as an MN-major operand.
+    Automatic choice (0) and forced slices; ragged M, N inside a tile, K tail."""
+    m, n, k = shape
+    aq, wq, sa, sb = w8a8_case(oracle, m, n, k, seed=m + n + k + 7 * slices)
+    w_kn = np.ascontiguousarray(wq.T)  # [K, N]
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, slices)
+    got = _w8a8(m, n, k, dev(aq), dev(w_kn), dev(sa), dev(sb), None, layout=bq.LayoutSku.Rrr)
+    want = oracle.dequant_s32_bf16(oracle.gemm_s8_s32(aq, w_kn, oracle.RRR, m, n, k), sa, sb)
+    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
+    bq.set_tuning(KEY_CLUSTER_SPLIT_K, 256)  # the 256-wide shape does not take this layout: the call runs one pass
+    got = _w8a8(m, n, k, dev(aq), dev(w_kn), dev(sa), dev(sb), None, layout=bq.LayoutSku.Rrr)
+    assert oracle.compare_bitexact(want, bf16_bits(got).reshape(m, n)) == -1
