@@ -634,6 +634,11 @@ int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream) {
 
 int sm_count_of_current_device() { return sm_count_impl(); }
 
+bool gemm_q8_takes_cluster_split_k(const GemmDesc& g) {
+    const int sms = sm_count_impl();
+    return sms > 0 && g.k > 0 && !g.raw_out && cluster_split_choice(g, sms).slices > 1;
+}
+
 bool make_mnmajor_tensor_map(void* map_out, const void* base, int64_t k_rows, int64_t n_cols, int64_t ld, int box_k,
                              int l2_promotion) {
     auto enc = tensor_map_encoder();

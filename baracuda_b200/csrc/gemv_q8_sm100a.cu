@@ -1090,6 +1090,38 @@ int32_t dispatch(const GemvDesc& g, cudaStream_t stream) {
         if (pl.ok) {
             if (g.workspace == nullptr || g.workspace_bytes < pl.ws_bytes) return BQ_STATUS_WORKSPACE;
             if (!aligned16(g.workspace)) return BQ_STATUS_MISALIGNED;
+            if constexpr (!RAW) {
+                // Few 1024-column strips: the row-run kernel's CTAs then share few strips and its reduce pass adds dozens
+                // of partial rows per column, while the tensor-core GEMM's split-K kernel (clusters of four CTAs per
+                // 128 x 128 tile, MN-major weight operand) is flat in m.  Measured (CUDA graph, rotating weights), this
+                // kernel against the GEMM: N = 1024, K = 4096: 11.0 / 20.8 us at m = 1 / 8 against 7.0; N = 4096,
+                // K = 14336: 16.7 / 20.1 against 17.0 / 16.8; N = 4096, K = 4096: 9.4 / 12.8 against 10.4 / 10.2.
+                // Same arithmetic per element (the GEMM epilogue's alpha, beta * D), so the bits do not change.
+                const bool few_strips = g.n <= 2048 || (g.n <= 4096 && g.m >= 4);
+                if (few_strips && g.batch == 1 && (g.lda % 16 == 0 || g.m == 1)) {
+                    GemmDesc q = {};
+                    q.kind = BQ_KIND_S8;
+                    q.b_layout = BQ_LAYOUT_RRR;
+                    q.m = g.m;
+                    q.n = g.n;
+                    q.k = g.k;
+                    q.a = g.a;
+                    q.lda = g.lda;
+                    q.b = g.b;
+                    q.ldb = g.ldb;
+                    q.scale_a = g.scale_a;
+                    q.scale_b = g.scale_b;
+                    q.scale_mode = 1;
+                    q.alpha = g.alpha;
+                    q.beta = g.beta;
+                    q.c = g.beta != 0.0f ? g.d : nullptr;
+                    q.ldc = g.ldd;
+                    q.d = g.d;
+                    q.ldd = g.ldd;
+                    q.pdl = g.pdl;
+                    if (gemm_q8_takes_cluster_split_k(q)) return launch_gemm_q8(q, stream);
+                }
+            }
             return launch_rrr_rows<RAW>(p, g.batch, pl, g.workspace, stream);
         }
     }

@@ -72,6 +72,8 @@ int32_t launch_gemm_q8_cluster_split_k(const GemmDesc& g, int32_t slices, int32_
 // Clusters of that kernel the current device holds at once (0: cannot run); cached per device.
 int gemm_q8_cluster_split_k_max_clusters(int32_t kind, int32_t slices, int32_t block_n);
 int32_t read_and_clear_gemm_splitk_device_status();
+// True when launch_gemm_q8 would run this problem on the cluster split-K kernel.
+bool gemm_q8_takes_cluster_split_k(const GemmDesc& g);
 
 int32_t launch_gemm_q8(const GemmDesc& g, cudaStream_t stream);
 // Raw-accumulator GEMM of a K shard whose epilogue scatters the [m, n] partial sums by row block: rows
