@@ -24,7 +24,7 @@ enum : int32_t { BQ_LAYOUT_RRR = 0, BQ_LAYOUT_RCR = 1 };
 struct GemmDesc {
     int32_t kind;     // BQ_KIND_*
     int32_t raw_out;  // 1: write the 32-bit accumulators, 0: fused dequant -> bf16
-    int32_t b_layout; // BQ_LAYOUT_RCR: weight [N,K]; BQ_LAYOUT_RRR: weight row-major [K,N] (served by the CTA-pair kernel)
+    int32_t b_layout; // BQ_LAYOUT_RCR: weight [N,K]; BQ_LAYOUT_RRR: weight row-major [K,N] (CTA-pair kernel, or the cluster split-K kernel for small batches)
     int32_t q8_out;   // 1 (with raw_out 0): d = sat(alpha*acc + beta*C) in the input type (s8 / e4m3), no scales
     const void* c;    // q8_out only
     int64_t ldc;
