@@ -232,6 +232,21 @@ def test_set_tuning_is_per_thread(qlib):
     assert qlib.baracuda_kernels_q_set_tuning(1, 0) == 0
 
 
+def test_set_tuning_accepts_only_documented_values(qlib):
+    """Every key of the test hook: the documented values return 0 (and are reset), anything else 2."""
+    allowed = {0: (0, 64, 128, 256, 512), 1: (0, 1, 2, 3, 8, 9), 2: (0, 2, 256, 224, 192, 128), 4: (0, 1, 2), 5: (0, 4, 8),
+               6: (0, 1, 2, 4, 256)}
+    for key, values in allowed.items():
+        for v in values:
+            assert qlib.baracuda_kernels_q_set_tuning(key, v) == 0, (key, v)
+        for v in (-1, 3 if key not in (1,) else 4, 7, 100, 1 << 20):
+            if v not in values:
+                assert qlib.baracuda_kernels_q_set_tuning(key, v) == 2, (key, v)
+        assert qlib.baracuda_kernels_q_set_tuning(key, 0) == 0
+    for key in (-1, 3, 7, 8, 99):
+        assert qlib.baracuda_kernels_q_set_tuning(key, 0) == 2
+
+
 def test_int8_symbols_refuse_k_that_could_overflow_32_bits(qlib):
     A, B, D = 0x10000, 0x20000, 0x30000
     k_ok, k_bad = 131056, 131072  # multiples of 16 either side of the 131 071 bound
